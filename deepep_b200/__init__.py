@@ -1,0 +1,21 @@
+"""B200-native expert-parallel communication library.
+
+Public surface (names follow deep_ep/__init__.py:88-97 of the reference):
+``ElasticBuffer``, ``EPHandle``, ``Buffer``, ``Config``, ``EventOverlap``, ``EventHandle``,
+``topk_idx_t``, ``get_physical_domain_size``, ``get_logical_domain_size``.
+"""
+from __future__ import annotations
+
+import torch
+
+from ._native import _C, require_native  # noqa: F401
+from .buffers.elastic import ElasticBuffer, EPHandle  # noqa: F401
+from .utils.envs import get_logical_domain_size, get_physical_domain_size  # noqa: F401
+from .utils.event import EventOverlap  # noqa: F401
+
+topk_idx_t = torch.int64
+EventHandle = _C.EventHandle if _C is not None else None
+EPException = _C.EPException if _C is not None else RuntimeError
+EPTimeoutError = _C.EPTimeoutError if _C is not None else TimeoutError
+
+__version__ = '0.1.0'

@@ -1,0 +1,161 @@
+// Launch interface between the host runtime and the CUDA kernels. No torch types here:
+// every launcher takes plain parameter blocks and a stream, so that the kernels compile
+// in seconds and can also be driven from C (ctypes) or from the run-time compiler.
+//
+// Parity: csrc/kernels/elastic/{barrier,dispatch,combine}.hpp and the host wrappers at the
+// bottom of csrc/kernels/legacy/*.cu in the reference.
+#pragma once
+
+#include <cuda_runtime.h>
+#include <cstdint>
+
+#include "../common/layout.hpp"
+
+namespace ep {
+
+// ---------------------------------------------------------------- cross-rank barrier
+struct BarrierParams {
+    CommCtx c;
+    uint32_t epoch;
+};
+cudaError_t launch_barrier(const Multi<BarrierParams>& m, cudaStream_t stream);
+
+// ---------------------------------------------------------------- high-throughput dispatch
+enum QuantMode : int {
+    kQuantNone = 0,        // payload rows are sent as they are (bf16, or fp8 with caller-made scales)
+    kQuantE4M3 = 1,        // bf16 in, e4m3 + float 1x128 scales out (made in the kernel)
+    kQuantE4M3Pow2 = 2,    // same with power-of-two scales
+};
+
+struct DispatchParams {
+    CommCtx c;
+    // problem
+    int num_tokens;
+    int num_topk;
+    int num_experts;
+    int num_local_experts;
+    int num_max_tokens;     // per-rank upper bound, equal on all ranks
+    int src_row_bytes;      // bytes of one input row
+    int x_row_bytes;        // bytes of one payload row as it is sent and received
+    int sf_bytes;           // bytes of scale factors per token (0 = none)
+    int meta_bytes;         // bytes of one meta row
+    int quant_mode;
+    int expert_alignment;
+    int do_expand;          // expert prefix sums follow the expanded layout
+    int cached;             // reuse token_slot / pair_row of an earlier dispatch, no counting
+    // inputs
+    const uint8_t* x;
+    int64_t x_stride_bytes;
+    const uint8_t* sf;          // 4-byte packs, [tokens][packs] with the strides below (in packs)
+    int64_t sf_token_stride;
+    int64_t sf_pack_stride;
+    const int64_t* topk_idx;    // [T, K], -1 = unused lane
+    const float* topk_weights;  // [T, K] or null
+    // handle tensors (device, owned by the caller)
+    int* token_slot;        // [T, R]  row in the destination rank's receive region, -1 = not sent
+    int* pair_row;          // [T, K]  row in the destination rank's expanded (expert-major) layout
+    int* psum_rank;         // [R]     inclusive prefix of received tokens per source rank
+    int* psum_expert;       // [E_local + 1]
+    int* num_unaligned;     // [E_local] received (token, expert) pairs per local expert
+    int* recv_stats;        // [E_local] cumulative statistics or null
+    // heap
+    uint64_t off_recv_x;
+    uint64_t off_recv_meta;
+    uint32_t epoch;
+    uint64_t grid_bar_base;
+    uint64_t* host_counts;  // mapped pinned: [0] received tokens, [1] expanded rows, [2 + e] per local expert (aligned)
+};
+
+struct DispatchLaunch {
+    int num_sms;            // blocks per rank
+    int num_warps;          // send warps per block
+    int smem_bytes;
+};
+// Picks warps / shared memory for a dispatch of this shape. Returns false if a row does not fit.
+bool plan_dispatch(const DispatchParams& p, int num_sms, int smem_optin, DispatchLaunch* out);
+cudaError_t launch_dispatch(const Multi<DispatchParams>& m, const DispatchLaunch& l, cudaStream_t stream);
+
+struct DispatchEpilogueParams {
+    // receive side of one rank
+    int rank;
+    int num_ranks;
+    int num_topk;
+    int num_local_experts;
+    int num_max_tokens;
+    int x_row_bytes;
+    int sf_bytes;
+    int meta_bytes;
+    int do_expand;
+    int copy_x;              // 0: recv_x aliases the receive region (zero copy), rows are not moved
+    int expert_alignment;
+    int do_zero_padding;
+    int write_metadata;      // 0 for cached dispatches (metadata is reused)
+    const uint8_t* region_x;
+    const uint8_t* region_meta;
+    const int* psum_rank;    // [R] inclusive; [R-1] = number of received rows
+    const int* psum_expert;  // [E_local + 1]
+    const int* num_unaligned;
+    // outputs
+    uint8_t* recv_x;          // [rows, x_row_bytes]
+    uint8_t* recv_sf;         // packs of 4 bytes
+    int64_t recv_sf_row_stride, recv_sf_pack_stride;   // in packs
+    int64_t* recv_topk_idx;   // [N, K] (non-expand) or null
+    float* recv_topk_weights; // [N, K] or [rows] (expand) or null
+    int* recv_src_metadata;   // [N, K + 2]
+    int num_out_rows;         // capacity of recv_x in rows (expand: expanded rows)
+};
+cudaError_t launch_dispatch_epilogue(const DispatchEpilogueParams* params, int num_vranks, int num_sms, int smem_optin,
+                                     cudaStream_t stream);
+
+// ---------------------------------------------------------------- high-throughput combine
+struct CombineParams {
+    CommCtx c;
+    int num_topk;
+    int num_max_tokens;
+    int row_bytes;            // hidden * 2 (bf16)
+    int do_expand;
+    int num_lanes;            // rows per token in the receive region (ranks, or top-k)
+    int use_rank_layout;      // 1: lane = sending rank (pre-reduced), 0: lane = top-k slot
+    const uint8_t* x;         // [N or expanded rows, hidden] bf16
+    int64_t x_stride_bytes;
+    const float* topk_weights;   // non-expand [N, K]; expand [rows]; or null
+    const int* recv_src_metadata;   // [N, K + 2]
+    const int* psum_rank;     // [R] inclusive (device truth for N)
+    uint64_t off_comb_x;
+    uint64_t off_comb_w;
+    uint32_t epoch;
+    uint64_t grid_bar_base;
+};
+struct CombineLaunch {
+    int num_sms;
+    int num_warps;
+    int smem_bytes;
+};
+bool plan_combine(const CombineParams& p, int num_sms, int smem_optin, CombineLaunch* out);
+cudaError_t launch_combine(const Multi<CombineParams>& m, const CombineLaunch& l, cudaStream_t stream);
+
+struct CombineEpilogueParams {
+    int num_tokens;
+    int num_topk;
+    int num_ranks;
+    int num_local_experts;
+    int num_max_tokens;
+    int hidden;               // bf16 elements
+    int num_lanes;
+    int use_rank_layout;
+    const uint8_t* region_x;
+    const float* region_w;    // [lanes][T_max][K] or null
+    const int64_t* topk_idx;  // [T, K] the dispatch's routing
+    const uint8_t* bias0;
+    const uint8_t* bias1;
+    uint8_t* combined_x;              // [T, hidden] bf16
+    float* combined_topk_weights;     // [T, K] or null
+};
+cudaError_t launch_combine_epilogue(const CombineEpilogueParams* params, int num_vranks, int num_sms, cudaStream_t stream);
+
+// ---------------------------------------------------------------- layout (legacy get_dispatch_layout)
+cudaError_t launch_dispatch_layout(const int64_t* topk_idx, int num_tokens, int num_topk, int num_ranks, int num_experts,
+                                   int* num_tokens_per_rank, int* num_tokens_per_expert, bool* is_token_in_rank,
+                                   cudaStream_t stream);
+
+}  // namespace ep

@@ -1,0 +1,267 @@
+// High-throughput expert-parallel combine for one NVLink/NVSwitch domain (sm_100a).
+//
+// Send kernel (cooperative, `num_sms` blocks): every received row goes back to the rank it
+// came from, into row [lane][token] of that rank's combine region, where `lane` is the
+// sending rank (rank layout: one row per contributing rank, a rank's local experts are
+// summed in fp32 before the row leaves) or the top-k slot (top-k layout: one row per
+// expert, no intermediate rounding). Destinations are visited round-robin starting at
+// rank+1 so that at any moment the ranks of the domain target different receivers.
+// The combine region is double-buffered by epoch parity, which is what makes an entry
+// barrier unnecessary: a peer can only be two combines ahead after this rank has finished
+// reading the half it is about to overwrite.
+//
+// Reduce epilogue (all SMs): combined_x[t] = sum over lanes in ascending order (fp32)
+// + bias_0 + bias_1, one bf16 rounding at the end; top-k weights are gathered back.
+//
+// Parity: deep_ep/include/deep_ep/impls/combine.cuh:15-243, impls/combine_utils.cuh:41-170
+// and impls/combine_reduce_epilogue.cuh:12-143 of the reference.
+#include "api.hpp"
+#include "../common/device_utils.cuh"
+
+namespace ep {
+
+namespace {
+
+__device__ __forceinline__ void accumulate_bf16x8(float (&acc)[8], const int4& raw) {
+    const __nv_bfloat162* h2 = reinterpret_cast<const __nv_bfloat162*>(&raw);
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        const float2 v = __bfloat1622float2(h2[i]);
+        acc[2 * i] += v.x;
+        acc[2 * i + 1] += v.y;
+    }
+}
+
+__device__ __forceinline__ int4 pack_bf16x8(const float (&acc)[8]) {
+    int4 out;
+    __nv_bfloat162* h2 = reinterpret_cast<__nv_bfloat162*>(&out);
+#pragma unroll
+    for (int i = 0; i < 4; ++i) h2[i] = __floats2bfloat162_rn(acc[2 * i], acc[2 * i + 1]);
+    return out;
+}
+
+__global__ void __launch_bounds__(1024, 1) combine_kernel(const __grid_constant__ Multi<CombineParams> m) {
+    extern __shared__ __align__(128) uint8_t smem[];
+    const int vr = blockIdx.x / m.blocks_per_rank;
+    const int bid = blockIdx.x % m.blocks_per_rank;
+    const int nb = m.blocks_per_rank;
+    const CombineParams& p = m.r[vr];
+    const CommCtx& c = p.c;
+    const WaitCtx w = make_wait_ctx(c);
+    const int tid = threadIdx.x, lane = lane_id(), warp = warp_id();
+    const int num_warps = blockDim.x >> 5;
+    const int R = c.num_ranks, K = p.num_topk;
+    uint64_t* my_ctl = reinterpret_cast<uint64_t*>(c.heap[c.rank]);
+
+    const int stage = align_up(p.row_bytes, 128) + 16;
+    uint8_t* buf = smem + static_cast<size_t>(warp) * stage;
+    uint64_t* bar = reinterpret_cast<uint64_t*>(buf + align_up(p.row_bytes, 128));
+    if (lane == 0) {
+        mbar_init(bar, 1);
+        fence_mbar_init();
+    }
+    __syncwarp();
+
+    // groups of received rows per source rank
+    int group_begin = 0, group_size = 0, max_group = 0;
+    {
+        int prev = 0;
+        for (int s = 0; s < R; ++s) {
+            const int end = p.psum_rank[s];
+            const int size = end - prev;
+            max_group = max(max_group, size);
+            prev = end;
+        }
+    }
+    const int vec_per_row = p.row_bytes / 16;
+    uint32_t parity = 0;
+    const int64_t total_steps = static_cast<int64_t>(max_group) * R;
+    for (int64_t g = static_cast<int64_t>(bid) * num_warps + warp; g < total_steps; g += static_cast<int64_t>(nb) * num_warps) {
+        const int d = (c.rank + 1 + static_cast<int>(g % R)) % R;
+        const int idx = static_cast<int>(g / R);
+        group_begin = d == 0 ? 0 : p.psum_rank[d - 1];
+        group_size = p.psum_rank[d] - group_begin;
+        if (idx >= group_size) continue;
+        const int i = group_begin + idx;
+        const int* md = p.recv_src_metadata + static_cast<int64_t>(i) * (K + 2);
+        const int src_token = md[0] % p.num_max_tokens;
+        const int master_lane = md[1] % K;
+        uint8_t* heap = c.heap[d];
+
+        bulk_wait_read_all();
+        __syncwarp();
+        if (!p.do_expand) {
+            // one row per received token: forward it as it is
+            if (lane == 0) {
+                mbar_arrive_expect_tx(bar, p.row_bytes);
+                bulk_g2s(buf, p.x + static_cast<int64_t>(i) * p.x_stride_bytes, p.row_bytes, bar);
+            }
+            const int slot_lane = p.use_rank_layout ? c.rank : master_lane;
+            const uint64_t dst_row = static_cast<uint64_t>(slot_lane) * p.num_max_tokens + src_token;
+            if (p.topk_weights != nullptr && lane < K)
+                reinterpret_cast<float*>(heap + p.off_comb_w)[dst_row * K + lane] = p.topk_weights[static_cast<int64_t>(i) * K + lane];
+            const bool landed = mbar_wait(w, bar, parity, kStatusTmaLoad, i);
+            parity ^= 1;
+            if (!__all_sync(0xffffffffu, landed)) break;
+            if (lane == 0) {
+                bulk_s2g(heap + p.off_comb_x + dst_row * p.row_bytes, buf, p.row_bytes);
+                bulk_commit();
+            }
+        } else if (p.use_rank_layout) {
+            // expanded input: sum this token's local-expert rows in fp32 (ascending top-k lane), round once, send
+            int my_row = lane < K ? md[2 + lane] : -1;
+            const uint32_t valid = __ballot_sync(0xffffffffu, my_row >= 0);
+            for (int v = lane; v < vec_per_row; v += 32) {
+                float acc[8];
+#pragma unroll
+                for (int j = 0; j < 8; ++j) acc[j] = 0.f;
+                uint32_t todo = valid;
+                while (todo) {
+                    const int k = __ffs(todo) - 1;
+                    todo &= todo - 1;
+                    const int row = __shfl_sync(0xffffffffu, my_row, k);
+                    accumulate_bf16x8(acc, ld_nc_int4(p.x + static_cast<int64_t>(row) * p.x_stride_bytes + v * 16));
+                }
+                reinterpret_cast<int4*>(buf)[v] = pack_bf16x8(acc);
+            }
+            const uint64_t dst_row = static_cast<uint64_t>(c.rank) * p.num_max_tokens + src_token;
+            if (p.topk_weights != nullptr && my_row >= 0)
+                reinterpret_cast<float*>(heap + p.off_comb_w)[dst_row * K + lane] = p.topk_weights[my_row];
+            fence_proxy_async_smem();
+            __syncwarp();
+            if (lane == 0) {
+                bulk_s2g(heap + p.off_comb_x + dst_row * p.row_bytes, buf, p.row_bytes);
+                bulk_commit();
+            }
+        } else {
+            // expanded input, top-k layout: every expert row travels on its own
+            const int my_row = lane < K ? md[2 + lane] : -1;
+            uint32_t todo = __ballot_sync(0xffffffffu, my_row >= 0);
+            if (p.topk_weights != nullptr && my_row >= 0)
+                reinterpret_cast<float*>(heap + p.off_comb_w)[(static_cast<uint64_t>(lane) * p.num_max_tokens + src_token) * K + lane] = p.topk_weights[my_row];
+            bool failed = false;
+            while (todo) {
+                const int k = __ffs(todo) - 1;
+                todo &= todo - 1;
+                const int row = __shfl_sync(0xffffffffu, my_row, k);
+                bulk_wait_read_all();
+                __syncwarp();
+                if (lane == 0) {
+                    mbar_arrive_expect_tx(bar, p.row_bytes);
+                    bulk_g2s(buf, p.x + static_cast<int64_t>(row) * p.x_stride_bytes, p.row_bytes, bar);
+                }
+                const bool landed = mbar_wait(w, bar, parity, kStatusTmaLoad, row);
+                parity ^= 1;
+                if (!__all_sync(0xffffffffu, landed)) { failed = true; break; }
+                if (lane == 0) {
+                    bulk_s2g(heap + p.off_comb_x + (static_cast<uint64_t>(k) * p.num_max_tokens + src_token) * p.row_bytes, buf, p.row_bytes);
+                    bulk_commit();
+                }
+            }
+            if (failed) break;
+        }
+    }
+
+    bulk_wait_all();
+    fence_proxy_async_all();
+    __threadfence_system();
+    grid_barrier(w, c.local_ws + kWsGridBarrier, p.grid_bar_base + nb, 3);
+    if (bid == 0 && tid < R) {
+        uint64_t* remote = reinterpret_cast<uint64_t*>(c.heap[tid]) + kCtlCombineDone + c.rank;
+        st_release_sys_u64(remote, pack_epoch(p.epoch, 0));
+        const uint64_t* word = my_ctl + kCtlCombineDone + tid;
+        bounded_wait(w, kStatusCombineDone, tid, 0, [&]() { return epoch_reached(ld_acquire_sys_u64(word), p.epoch); });
+    }
+}
+
+// ==================================================================== reduce epilogue (local, all SMs)
+__global__ void __launch_bounds__(512) combine_epilogue_kernel(const __grid_constant__ Multi<CombineEpilogueParams> m) {
+    const int vr = blockIdx.x / m.blocks_per_rank;
+    const int bid = blockIdx.x % m.blocks_per_rank;
+    const int nb = m.blocks_per_rank;
+    const CombineEpilogueParams& p = m.r[vr];
+    const int lane = lane_id(), warp = warp_id();
+    const int num_warps = blockDim.x >> 5;
+    const int K = p.num_topk, EL = p.num_local_experts;
+    const int vec_per_row = p.hidden / 8;
+    const uint64_t row_bytes = static_cast<uint64_t>(p.hidden) * 2;
+
+    for (int t = bid * num_warps + warp; t < p.num_tokens; t += nb * num_warps) {
+        // which lanes of the region hold a row for this token
+        int e = -1;
+        if (lane < K) {
+            const int64_t raw = p.topk_idx[static_cast<int64_t>(t) * K + lane];
+            e = (raw >= 0 && raw < static_cast<int64_t>(EL) * p.num_ranks) ? static_cast<int>(raw) : -1;
+        }
+        const int slot_lane = e < 0 ? -1 : (p.use_rank_layout ? e / EL : lane);
+        uint32_t mask = 0;
+        {
+            uint32_t mine = slot_lane >= 0 ? (1u << slot_lane) : 0u;
+#pragma unroll
+            for (int o = 16; o > 0; o >>= 1) mine |= __shfl_xor_sync(0xffffffffu, mine, o);
+            mask = mine;
+        }
+        if (p.combined_topk_weights != nullptr && lane < K) {
+            float wv = 0.f;
+            if (slot_lane >= 0 && p.region_w != nullptr)
+                wv = p.region_w[(static_cast<uint64_t>(slot_lane) * p.num_max_tokens + t) * K + lane];
+            p.combined_topk_weights[static_cast<int64_t>(t) * K + lane] = wv;
+        }
+        const uint8_t* b0 = p.bias0 != nullptr ? p.bias0 + t * row_bytes : nullptr;
+        const uint8_t* b1 = p.bias1 != nullptr ? p.bias1 + t * row_bytes : nullptr;
+        for (int v = lane; v < vec_per_row; v += 32) {
+            float acc[8];
+#pragma unroll
+            for (int j = 0; j < 8; ++j) acc[j] = 0.f;
+            uint32_t todo = mask;
+            while (todo) {
+                const int l = __ffs(todo) - 1;
+                todo &= todo - 1;
+                accumulate_bf16x8(acc, ld_nc_int4(p.region_x + (static_cast<uint64_t>(l) * p.num_max_tokens + t) * row_bytes + v * 16));
+            }
+            if (b0 != nullptr) accumulate_bf16x8(acc, ld_nc_int4(b0 + v * 16));
+            if (b1 != nullptr) accumulate_bf16x8(acc, ld_nc_int4(b1 + v * 16));
+            st_na_int4(p.combined_x + t * row_bytes + v * 16, pack_bf16x8(acc));
+        }
+    }
+}
+
+}  // namespace
+
+bool plan_combine(const CombineParams& p, int num_sms, int smem_optin, CombineLaunch* out) {
+    const int stage = align_up(p.row_bytes, 128) + 16;
+    int warps = smem_optin / stage;
+    if (warps > 32) warps = 32;
+    if (warps < 1) return false;
+    out->num_sms = num_sms;
+    out->num_warps = warps;
+    out->smem_bytes = warps * stage;
+    return true;
+}
+
+cudaError_t launch_combine(const Multi<CombineParams>& m, const CombineLaunch& l, cudaStream_t stream) {
+    cudaError_t err = cudaFuncSetAttribute(combine_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, l.smem_bytes);
+    if (err != cudaSuccess) return err;
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(m.num_vranks * m.blocks_per_rank);
+    cfg.blockDim = dim3(l.num_warps * 32);
+    cfg.dynamicSmemBytes = l.smem_bytes;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeCooperative;
+    attr[0].val.cooperative = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    return cudaLaunchKernelEx(&cfg, combine_kernel, m);
+}
+
+cudaError_t launch_combine_epilogue(const CombineEpilogueParams* params, int num_vranks, int num_sms, cudaStream_t stream) {
+    Multi<CombineEpilogueParams> m;
+    m.num_vranks = num_vranks;
+    m.blocks_per_rank = num_sms;
+    for (int v = 0; v < num_vranks; ++v) m.r[v] = params[v];
+    combine_epilogue_kernel<<<num_vranks * num_sms, 512, 0, stream>>>(m);
+    return cudaGetLastError();
+}
+
+}  // namespace ep

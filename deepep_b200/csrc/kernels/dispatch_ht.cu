@@ -1,0 +1,508 @@
+// High-throughput expert-parallel dispatch for one NVLink/NVSwitch domain (sm_100a).
+//
+// ONE cooperative kernel per rank does, in order:
+//   A. count     every block scans its contiguous chunk of tokens: destination-rank set per
+//                token and the position of each (token, rank) and (token, expert) pair
+//                among the block's earlier tokens (token order, so the result is the same
+//                on every run)
+//   B. exchange  block 0 all-gathers this rank's per-rank and per-expert totals into every
+//                peer's control area as epoch-tagged words; every block waits for the whole
+//                matrix and derives, without further communication, the first row of its own
+//                tokens in each destination's receive region and in each expert's segment of
+//                the expanded (expert-major) layout
+//   C. send      one warp per token: bulk-load the row into shared memory, optionally cast it
+//                to e4m3 with 1x128 scales, build the meta row, and bulk-store payload and
+//                meta straight to row `slot` of every destination rank's receive region
+//                (peer pointers over NVLink; plain 1-D bulk copies, never multicast)
+//   D. finish    wait for the stores, tell every peer "my rows have landed", wait for theirs.
+//
+// Rows arrive grouped by source rank in token order, i.e. already in the order of the
+// non-expanded output: with zero copy the receive region IS recv_x. The epilogue kernel at
+// the bottom only unpacks the small meta rows, and moves payload rows when the caller wants
+// tensors of its own or the expanded layout.
+//
+// Parity: deep_ep/include/deep_ep/impls/dispatch.cuh:17-409 (notify + dispatch warps) and
+// impls/dispatch_copy_epilogue.cuh:11-323 of the reference; the fused cast follows the
+// arithmetic of csrc/kernels/legacy/internode_ll.cu:212-249.
+#include "api.hpp"
+#include "../common/device_utils.cuh"
+
+namespace ep {
+
+namespace {
+
+constexpr int kCntStride = kMaxRanks + kMaxExperts;   // words per source rank in the count matrix
+
+struct StageLayout {
+    int src_off, out_off, meta_off, bar_off, bytes;
+};
+
+__host__ __device__ inline StageLayout stage_layout(int src_row_bytes, int x_row_bytes, int meta_bytes, bool quant) {
+    StageLayout s;
+    s.src_off = 0;
+    int off = align_up(src_row_bytes, 128);
+    s.out_off = quant ? off : 0;
+    if (quant) off += align_up(x_row_bytes, 128);
+    s.meta_off = off;
+    off += align_up(meta_bytes, 16);
+    s.bar_off = off;
+    off += 16;
+    s.bytes = align_up(off, 128);
+    return s;
+}
+
+__host__ __device__ inline int header_bytes(int num_experts) {
+    return align_up((3 * kMaxRanks + 2 * num_experts) * 4, 128);
+}
+
+// bf16 row in shared memory -> e4m3 row + one float scale per 128 channels.
+__device__ __forceinline__ void quantize_row(const uint8_t* src, uint8_t* out, float* scales, int hidden, bool pow2, int lane) {
+    for (int base = 0; base < hidden; base += 256) {
+        const int ch = base + lane * 8;
+        const bool active = ch < hidden;
+        int4 raw = make_int4(0, 0, 0, 0);
+        if (active) raw = *reinterpret_cast<const int4*>(src + ch * 2);
+        const __nv_bfloat162* h2 = reinterpret_cast<const __nv_bfloat162*>(&raw);
+        float f[8];
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            const float2 v = __bfloat1622float2(h2[i]);
+            f[2 * i] = v.x;
+            f[2 * i + 1] = v.y;
+        }
+        float amax = 0.f;
+#pragma unroll
+        for (int i = 0; i < 8; ++i) amax = fmaxf(amax, fabsf(f[i]));
+        amax = warp_reduce_max_width(amax, 16);
+        float scale, inv;
+        fp8_scale_from_amax(amax, pow2, scale, inv);
+        uint2 packed;
+        packed.x = pack4_e4m3(f[0] * inv, f[1] * inv, f[2] * inv, f[3] * inv);
+        packed.y = pack4_e4m3(f[4] * inv, f[5] * inv, f[6] * inv, f[7] * inv);
+        if (active) {
+            *reinterpret_cast<uint2*>(out + ch) = packed;
+            if ((lane & 15) == 0) scales[ch >> 7] = scale;
+        }
+    }
+}
+
+__global__ void __launch_bounds__(1024, 1) dispatch_kernel(const __grid_constant__ Multi<DispatchParams> m) {
+    extern __shared__ __align__(128) uint8_t smem[];
+    const int vr = blockIdx.x / m.blocks_per_rank;
+    const int bid = blockIdx.x % m.blocks_per_rank;
+    const int nb = m.blocks_per_rank;
+    const DispatchParams& p = m.r[vr];
+    const CommCtx& c = p.c;
+    const WaitCtx w = make_wait_ctx(c);
+    const int tid = threadIdx.x, nthreads = blockDim.x, lane = lane_id(), warp = warp_id();
+    const int num_warps = nthreads >> 5;
+    const int R = c.num_ranks, E = p.num_experts, K = p.num_topk, T = p.num_tokens, EL = p.num_local_experts;
+    const int CW = R + E;
+
+    int* s_rank_base = reinterpret_cast<int*>(smem);   // [kMaxRanks] first row of this block's tokens per destination
+    int* s_recv_from = s_rank_base + kMaxRanks;         // [kMaxRanks] tokens this rank receives per source
+    int* s_flags = s_recv_from + kMaxRanks;             // [kMaxRanks] scratch
+    int* s_exp_tot = s_flags + kMaxRanks;               // [E]
+    int* s_exp_base = s_exp_tot + E;                    // [E]
+    uint8_t* s_bufs = smem + header_bytes(E);
+
+    const int chunk = ceil_div(T, nb);
+    const int t0 = min(T, bid * chunk), t1 = min(T, t0 + chunk);
+    int* blk_cnt = reinterpret_cast<int*>(c.local_ws + kWsScratch);   // [nb][CW]
+    uint64_t* my_ctl = reinterpret_cast<uint64_t*>(c.heap[c.rank]);
+    uint64_t* grid_counter = c.local_ws + kWsGridBarrier;
+    bool ok = true;
+
+    if (!p.cached) {
+        // ------------------------------------------------------------ A. count
+        for (int e = tid; e < E; e += nthreads) s_exp_tot[e] = 0;
+        __syncthreads();
+        if (warp == 0) {
+            int run[kMaxRanks];
+#pragma unroll
+            for (int d = 0; d < kMaxRanks; ++d) run[d] = 0;
+            for (int base = t0; base < t1; base += 32) {
+                const int t = base + lane;
+                uint32_t mask = 0;
+                if (t < t1) {
+                    for (int k = 0; k < K; ++k) {
+                        const int64_t e = p.topk_idx[static_cast<int64_t>(t) * K + k];
+                        if (e >= 0 && e < E) mask |= 1u << (static_cast<int>(e) / EL);
+                    }
+                }
+#pragma unroll
+                for (int d = 0; d < kMaxRanks; ++d) {
+                    if (d < R) {
+                        const bool in = (mask >> d) & 1u;
+                        const uint32_t b = __ballot_sync(0xffffffffu, in);
+                        if (t < t1) p.token_slot[static_cast<int64_t>(t) * R + d] = in ? run[d] + __popc(b & lanemask_lt()) : -1;
+                        run[d] += __popc(b);
+                    }
+                }
+            }
+#pragma unroll
+            for (int d = 0; d < kMaxRanks; ++d)
+                if (lane == d && d < R) blk_cnt[bid * CW + d] = run[d];
+        } else if (warp == 1) {
+            const int64_t p1 = static_cast<int64_t>(t1) * K;
+            for (int64_t p0 = static_cast<int64_t>(t0) * K; p0 < p1; p0 += 32) {
+                const int64_t pi = p0 + lane;
+                int e = -1;
+                if (pi < p1) {
+                    const int64_t raw = p.topk_idx[pi];
+                    e = (raw >= 0 && raw < E) ? static_cast<int>(raw) : -1;
+                }
+                const bool valid = e >= 0;
+                const uint32_t peers = __match_any_sync(0xffffffffu, valid ? e : (0x40000000 | lane));
+                int rel = -1;
+                if (valid) rel = s_exp_tot[e] + __popc(peers & lanemask_lt());
+                __syncwarp();
+                if (valid && (peers & lanemask_lt()) == 0) s_exp_tot[e] += __popc(peers);
+                __syncwarp();
+                if (pi < p1) p.pair_row[pi] = rel;
+            }
+        }
+        __syncthreads();
+        for (int e = tid; e < E; e += nthreads) blk_cnt[bid * CW + R + e] = s_exp_tot[e];
+        __threadfence();
+        ok &= grid_barrier(w, grid_counter, p.grid_bar_base + nb, 1);
+
+        // ------------------------------------------------------------ B. exchange
+        for (int j = tid; j < CW; j += nthreads) {
+            int before = 0, total = 0;
+            const int upto = bid == 0 ? nb : bid;
+            for (int b = 0; b < upto; ++b) {
+                const int v = __ldcg(blk_cnt + b * CW + j);
+                if (b < bid) before += v;
+                total += v;
+            }
+            if (j < R) s_rank_base[j] = before; else s_exp_base[j - R] = before;
+            if (bid == 0) {
+                const uint64_t word = pack_epoch(p.epoch, static_cast<uint32_t>(total));
+                const int col = j < R ? j : kMaxRanks + (j - R);
+                for (int d = 0; d < R; ++d) {
+                    uint64_t* remote = reinterpret_cast<uint64_t*>(c.heap[d]) + kCtlDispatchCnt + static_cast<size_t>(c.rank) * kCntStride + col;
+                    st_relaxed_sys_u64(remote, word);
+                }
+            }
+        }
+        for (int j = tid; j < CW; j += nthreads) {
+            const int col = j < R ? j : kMaxRanks + (j - R);
+            int tot = 0, pre = 0;
+            for (int s = 0; s < R; ++s) {
+                const uint64_t* word = my_ctl + kCtlDispatchCnt + static_cast<size_t>(s) * kCntStride + col;
+                uint64_t v = 0;
+                ok &= bounded_wait(w, kStatusDispatchCounts, s, j, [&]() {
+                    v = ld_relaxed_sys_u64(word);
+                    return epoch_matches(v, p.epoch);
+                });
+                const int cnt = static_cast<int>(static_cast<uint32_t>(v));
+                tot += cnt;
+                if (s < c.rank) pre += cnt;
+                if (j == c.rank) s_recv_from[s] = cnt;
+            }
+            if (j < R) {
+                s_rank_base[j] += pre;
+            } else {
+                s_exp_tot[j - R] = tot;
+                s_exp_base[j - R] += pre;
+            }
+        }
+        ok = !__syncthreads_or(!ok);
+        if (ok) {
+            // first row of every expert's segment on its rank (alignment applied)
+            if (tid < R) {
+                int start = 0;
+                for (int le = 0; le < EL; ++le) {
+                    const int e = tid * EL + le;
+                    s_exp_base[e] += start;
+                    start += align_up(s_exp_tot[e], p.expert_alignment);
+                }
+            }
+            if (bid == 0 && tid == 32) {
+                // receive-side description of this rank
+                int acc = 0;
+                for (int s = 0; s < R; ++s) {
+                    acc += s_recv_from[s];
+                    p.psum_rank[s] = acc;
+                }
+                int start = 0;
+                for (int le = 0; le < EL; ++le) {
+                    const int tot = s_exp_tot[c.rank * EL + le];
+                    const int aligned = align_up(tot, p.expert_alignment);
+                    p.num_unaligned[le] = tot;
+                    p.psum_expert[le] = p.do_expand ? start + tot : start + aligned;
+                    if (p.recv_stats != nullptr) p.recv_stats[le] += tot;
+                    if (p.host_counts != nullptr) p.host_counts[2 + le] = pack_epoch(p.epoch, static_cast<uint32_t>(aligned));
+                    start += aligned;
+                }
+                p.psum_expert[EL] = start;
+                if (p.host_counts != nullptr) {
+                    p.host_counts[1] = pack_epoch(p.epoch, static_cast<uint32_t>(start));
+                    __threadfence_system();
+                    p.host_counts[0] = pack_epoch(p.epoch, static_cast<uint32_t>(acc));
+                }
+            }
+        }
+        __syncthreads();
+    } else {
+        // ------------------------------------------------------------ cached: only announce entry and wait for the peers
+        if (bid == 0 && tid < R) {
+            uint64_t* remote = reinterpret_cast<uint64_t*>(c.heap[tid]) + kCtlDispatchEntry + c.rank;
+            st_release_sys_u64(remote, pack_epoch(p.epoch, 0));
+        }
+        if (tid < R) {
+            const uint64_t* word = my_ctl + kCtlDispatchEntry + tid;
+            ok &= bounded_wait(w, kStatusEntry, tid, 0, [&]() { return epoch_reached(ld_acquire_sys_u64(word), p.epoch); });
+        }
+        ok = !__syncthreads_or(!ok);
+    }
+
+    // ---------------------------------------------------------------- C. send
+    const bool quant = p.quant_mode != kQuantNone;
+    const StageLayout sl = stage_layout(p.src_row_bytes, p.x_row_bytes, p.meta_bytes, quant);
+    uint8_t* my = s_bufs + static_cast<size_t>(warp) * sl.bytes;
+    uint8_t* buf_src = my + sl.src_off;
+    uint8_t* buf_out = quant ? my + sl.out_off : buf_src;
+    uint8_t* buf_meta = my + sl.meta_off;
+    uint64_t* bar = reinterpret_cast<uint64_t*>(my + sl.bar_off);
+    if (ok) {
+        if (lane == 0) {
+            mbar_init(bar, 1);
+            fence_mbar_init();
+        }
+        __syncwarp();
+        const bool sf_in = p.sf != nullptr && p.sf_bytes > 0;
+        const bool sf_bulk = sf_in && p.sf_pack_stride == 1 && (p.sf_bytes & 15) == 0 &&
+                             ((reinterpret_cast<uintptr_t>(p.sf) | static_cast<uintptr_t>(p.sf_token_stride * 4)) & 15) == 0;
+        int* meta_idx = reinterpret_cast<int*>(buf_meta + p.sf_bytes);
+        float* meta_w = reinterpret_cast<float*>(meta_idx + K);
+        int* meta_row = meta_idx + 2 * K;
+        uint32_t parity = 0;
+        for (int t = t0 + warp; t < t1; t += num_warps) {
+            bulk_wait_read_all();   // the previous stores of every lane have read the buffers
+            __syncwarp();
+            if (lane == 0) {
+                mbar_arrive_expect_tx(bar, p.src_row_bytes + (sf_bulk ? p.sf_bytes : 0));
+                bulk_g2s(buf_src, p.x + static_cast<int64_t>(t) * p.x_stride_bytes, p.src_row_bytes, bar);
+                if (sf_bulk) bulk_g2s(buf_meta, p.sf + static_cast<int64_t>(t) * p.sf_token_stride * 4, p.sf_bytes, bar);
+            }
+            int slot = -1;
+            if (lane < R) {
+                slot = p.token_slot[static_cast<int64_t>(t) * R + lane];
+                if (!p.cached && slot >= 0) {
+                    slot += s_rank_base[lane];
+                    p.token_slot[static_cast<int64_t>(t) * R + lane] = slot;
+                }
+            }
+            if (lane < K) {
+                const int64_t pi = static_cast<int64_t>(t) * K + lane;
+                const int64_t raw = p.topk_idx[pi];
+                const int e = (raw >= 0 && raw < E) ? static_cast<int>(raw) : -1;
+                int row = p.pair_row[pi];
+                if (!p.cached && e >= 0) {
+                    row += s_exp_base[e];
+                    p.pair_row[pi] = row;
+                }
+                meta_idx[lane] = e;
+                meta_w[lane] = p.topk_weights != nullptr ? p.topk_weights[pi] : 0.f;
+                meta_row[lane] = row;
+            }
+            if (lane == 0) meta_row[K] = t;
+            if (sf_in && !sf_bulk) {
+                const uint32_t* sf32 = reinterpret_cast<const uint32_t*>(p.sf);
+                for (int i = lane; i < p.sf_bytes / 4; i += 32)
+                    reinterpret_cast<uint32_t*>(buf_meta)[i] = sf32[static_cast<int64_t>(t) * p.sf_token_stride + i * p.sf_pack_stride];
+            }
+            const bool landed = mbar_wait(w, bar, parity, kStatusTmaLoad, t);
+            parity ^= 1;
+            if (!__all_sync(0xffffffffu, landed)) break;
+            if (quant) quantize_row(buf_src, buf_out, reinterpret_cast<float*>(buf_meta), p.src_row_bytes / 2, p.quant_mode == kQuantE4M3Pow2, lane);
+            fence_proxy_async_smem();
+            __syncwarp();
+            if (slot >= 0) {
+                uint8_t* heap = c.heap[lane];
+                bulk_s2g(heap + p.off_recv_x + static_cast<uint64_t>(slot) * p.x_row_bytes, buf_out, p.x_row_bytes);
+                bulk_s2g(heap + p.off_recv_meta + static_cast<uint64_t>(slot) * p.meta_bytes, buf_meta, p.meta_bytes);
+                bulk_commit();
+            }
+        }
+    }
+
+    // ---------------------------------------------------------------- D. finish
+    bulk_wait_all();
+    fence_proxy_async_all();
+    __threadfence_system();
+    grid_barrier(w, grid_counter, p.grid_bar_base + (p.cached ? 1 : 2) * static_cast<uint64_t>(nb), 2);
+    if (bid == 0 && tid < R) {
+        uint64_t* remote = reinterpret_cast<uint64_t*>(c.heap[tid]) + kCtlDispatchDone + c.rank;
+        st_release_sys_u64(remote, pack_epoch(p.epoch, 0));
+        const uint64_t* word = my_ctl + kCtlDispatchDone + tid;
+        bounded_wait(w, kStatusDispatchDone, tid, 0, [&]() { return epoch_reached(ld_acquire_sys_u64(word), p.epoch); });
+    }
+}
+
+// ==================================================================== epilogue (local, all SMs)
+__global__ void __launch_bounds__(1024, 1) dispatch_epilogue_kernel(const __grid_constant__ Multi<DispatchEpilogueParams> m) {
+    extern __shared__ __align__(128) uint8_t smem[];
+    const int vr = blockIdx.x / m.blocks_per_rank;
+    const int bid = blockIdx.x % m.blocks_per_rank;
+    const int nb = m.blocks_per_rank;
+    const DispatchEpilogueParams& p = m.r[vr];
+    const int lane = lane_id(), warp = warp_id();
+    const int num_warps = blockDim.x >> 5;
+    const int R = p.num_ranks, K = p.num_topk, EL = p.num_local_experts;
+    const int N = p.psum_rank[R - 1];
+    const bool move_rows = p.copy_x || p.do_expand;
+
+    const int stage = align_up(p.x_row_bytes, 128) + 16;
+    uint8_t* buf = smem + static_cast<size_t>(warp) * stage;
+    uint64_t* bar = reinterpret_cast<uint64_t*>(buf + align_up(p.x_row_bytes, 128));
+    if (move_rows && lane == 0) {
+        mbar_init(bar, 1);
+        fence_mbar_init();
+    }
+    __syncwarp();
+    uint32_t parity = 0;
+    const int expert_begin = p.rank * EL;
+    const int sf_packs = p.sf_bytes / 4;
+
+    for (int i = bid * num_warps + warp; i < N; i += nb * num_warps) {
+        if (move_rows) {
+            bulk_wait_read_all();
+            __syncwarp();
+            if (lane == 0) {
+                mbar_arrive_expect_tx(bar, p.x_row_bytes);
+                bulk_g2s(buf, p.region_x + static_cast<uint64_t>(i) * p.x_row_bytes, p.x_row_bytes, bar);
+            }
+        }
+        const uint8_t* meta = p.region_meta + static_cast<uint64_t>(i) * p.meta_bytes;
+        const int* meta_idx = reinterpret_cast<const int*>(meta + p.sf_bytes);
+        int e = -1, row = -1;
+        float wt = 0.f;
+        if (lane < K) {
+            e = meta_idx[lane];
+            wt = reinterpret_cast<const float*>(meta_idx)[K + lane];
+            row = meta_idx[2 * K + lane];
+        }
+        const int src_token = meta_idx[3 * K];
+        const bool local = e >= expert_begin && e < expert_begin + EL;
+        const int local_e = local ? e - expert_begin : -1;
+        if (!p.do_expand || !local) row = -1;
+        const uint32_t local_mask = __ballot_sync(0xffffffffu, local);
+        int src_rank = 0;
+        while (src_rank < R - 1 && i >= p.psum_rank[src_rank]) ++src_rank;
+
+        if (!p.do_expand) {
+            if (lane < K) {
+                if (p.recv_topk_idx != nullptr) p.recv_topk_idx[static_cast<int64_t>(i) * K + lane] = local_e;
+                if (p.recv_topk_weights != nullptr) p.recv_topk_weights[static_cast<int64_t>(i) * K + lane] = wt;
+            }
+            if (p.recv_sf != nullptr) {
+                const uint32_t* sf = reinterpret_cast<const uint32_t*>(meta);
+                for (int k = lane; k < sf_packs; k += 32)
+                    reinterpret_cast<uint32_t*>(p.recv_sf)[static_cast<int64_t>(i) * p.recv_sf_row_stride + k * p.recv_sf_pack_stride] = sf[k];
+            }
+        } else {
+            if (row >= 0 && p.recv_topk_weights != nullptr) p.recv_topk_weights[row] = wt;
+            if (p.recv_sf != nullptr) {
+                const uint32_t* sf = reinterpret_cast<const uint32_t*>(meta);
+                uint32_t todo = local_mask;
+                while (todo) {
+                    const int src_lane = __ffs(todo) - 1;
+                    todo &= todo - 1;
+                    const int out_row = __shfl_sync(0xffffffffu, row, src_lane);
+                    for (int k = lane; k < sf_packs; k += 32)
+                        reinterpret_cast<uint32_t*>(p.recv_sf)[static_cast<int64_t>(out_row) * p.recv_sf_row_stride + k * p.recv_sf_pack_stride] = sf[k];
+                }
+            }
+        }
+        if (p.write_metadata) {
+            int* md = p.recv_src_metadata + static_cast<int64_t>(i) * (K + 2);
+            if (lane == 0) {
+                md[0] = src_rank * p.num_max_tokens + src_token;
+                md[1] = src_rank * K + (local_mask ? __ffs(local_mask) - 1 : 0);
+            }
+            if (lane < K) md[2 + lane] = row;
+        }
+        if (move_rows) {
+            // no WaitCtx here: a local bulk load cannot miss, but keep the wait bounded all the same
+            bool landed = false;
+            for (int spin = 0; spin < (1 << 24) && !landed; ++spin) landed = mbar_try_wait(bar, parity);
+            parity ^= 1;
+            if (!__all_sync(0xffffffffu, landed)) break;
+            if (!p.do_expand) {
+                if (lane == 0) {
+                    bulk_s2g(p.recv_x + static_cast<uint64_t>(i) * p.x_row_bytes, buf, p.x_row_bytes);
+                    bulk_commit();
+                }
+            } else if (row >= 0 && row < p.num_out_rows) {
+                bulk_s2g(p.recv_x + static_cast<uint64_t>(row) * p.x_row_bytes, buf, p.x_row_bytes);
+                bulk_commit();
+            }
+        }
+    }
+
+    // zero the alignment gaps of the expanded layout
+    if (p.do_expand && p.do_zero_padding) {
+        const int vec_per_row = p.x_row_bytes / 16;
+        for (int le = bid; le < EL; le += nb) {
+            const int begin = p.psum_expert[le];                               // start + real count
+            const int end = min(align_up(begin, p.expert_alignment), p.num_out_rows);
+            for (int64_t v = static_cast<int64_t>(begin) * vec_per_row + threadIdx.x; v < static_cast<int64_t>(end) * vec_per_row; v += blockDim.x)
+                reinterpret_cast<int4*>(p.recv_x)[v] = make_int4(0, 0, 0, 0);
+            if (p.recv_topk_weights != nullptr)
+                for (int r = begin + threadIdx.x; r < end; r += blockDim.x) p.recv_topk_weights[r] = 0.f;
+        }
+    }
+    bulk_wait_all();
+}
+
+}  // namespace
+
+bool plan_dispatch(const DispatchParams& p, int num_sms, int smem_optin, DispatchLaunch* out) {
+    const StageLayout sl = stage_layout(p.src_row_bytes, p.x_row_bytes, p.meta_bytes, p.quant_mode != kQuantNone);
+    const int avail = smem_optin - header_bytes(p.num_experts);
+    int warps = avail / sl.bytes;
+    if (warps > 32) warps = 32;
+    if (warps < 2) return false;
+    out->num_sms = num_sms;
+    out->num_warps = warps;
+    out->smem_bytes = header_bytes(p.num_experts) + warps * sl.bytes;
+    return true;
+}
+
+cudaError_t launch_dispatch(const Multi<DispatchParams>& m, const DispatchLaunch& l, cudaStream_t stream) {
+    cudaError_t err = cudaFuncSetAttribute(dispatch_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, l.smem_bytes);
+    if (err != cudaSuccess) return err;
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(m.num_vranks * m.blocks_per_rank);
+    cfg.blockDim = dim3(l.num_warps * 32);
+    cfg.dynamicSmemBytes = l.smem_bytes;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeCooperative;
+    attr[0].val.cooperative = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    return cudaLaunchKernelEx(&cfg, dispatch_kernel, m);
+}
+
+cudaError_t launch_dispatch_epilogue(const DispatchEpilogueParams* params, int num_vranks, int num_sms, int smem_optin,
+                                     cudaStream_t stream) {
+    Multi<DispatchEpilogueParams> m;
+    m.num_vranks = num_vranks;
+    m.blocks_per_rank = num_sms;
+    for (int v = 0; v < num_vranks; ++v) m.r[v] = params[v];
+    const int stage = align_up(params[0].x_row_bytes, 128) + 16;
+    int warps = smem_optin / stage;
+    if (warps > 16) warps = 16;
+    if (warps < 1) return cudaErrorInvalidValue;
+    const int smem_bytes = warps * stage;
+    cudaError_t err = cudaFuncSetAttribute(dispatch_epilogue_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_bytes);
+    if (err != cudaSuccess) return err;
+    dispatch_epilogue_kernel<<<num_vranks * num_sms, warps * 32, smem_bytes, stream>>>(m);
+    return cudaGetLastError();
+}
+
+}  // namespace ep
