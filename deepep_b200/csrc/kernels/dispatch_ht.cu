@@ -39,10 +39,13 @@ struct StageLayout {
 
 __host__ __device__ inline StageLayout stage_layout(int src_row_bytes, int x_row_bytes, int meta_bytes, bool quant) {
     StageLayout s;
+    // With the fused cast the e4m3 row overwrites the front of the bf16 row (see quantize_row),
+    // so payload and cast share one buffer.
+    (void)x_row_bytes;
+    (void)quant;
     s.src_off = 0;
     int off = align_up(src_row_bytes, 128);
-    s.out_off = quant ? off : 0;
-    if (quant) off += align_up(x_row_bytes, 128);
+    s.out_off = 0;
     s.meta_off = off;
     off += align_up(meta_bytes, 16);
     s.bar_off = off;
@@ -55,7 +58,10 @@ __host__ __device__ inline int header_bytes(int num_experts) {
     return align_up((3 * kMaxRanks + 2 * num_experts) * 4, 128);
 }
 
-// bf16 row in shared memory -> e4m3 row + one float scale per 128 channels.
+// bf16 row in shared memory -> e4m3 row + one float scale per 128 channels. `out` may alias
+// `src`: step `base` reads bytes [2*base, 2*base + 512) and writes bytes [base, base + 256),
+// which only earlier steps have read, and the lanes of a step have all loaded (the shuffles
+// of the reduction are past) before any of them stores.
 __device__ __forceinline__ void quantize_row(const uint8_t* src, uint8_t* out, float* scales, int hidden, bool pow2, int lane) {
     for (int base = 0; base < hidden; base += 256) {
         const int ch = base + lane * 8;
@@ -74,6 +80,7 @@ __device__ __forceinline__ void quantize_row(const uint8_t* src, uint8_t* out, f
 #pragma unroll
         for (int i = 0; i < 8; ++i) amax = fmaxf(amax, fabsf(f[i]));
         amax = warp_reduce_max_width(amax, 16);
+        __syncwarp();
         float scale, inv;
         fp8_scale_from_amax(amax, pow2, scale, inv);
         uint2 packed;
@@ -115,52 +122,63 @@ __global__ void __launch_bounds__(1024, 1) dispatch_kernel(const __grid_constant
 
     if (!p.cached) {
         // ------------------------------------------------------------ A. count
+        // The routing of the chunk is staged in shared memory (the send buffers are idle now) so
+        // that the two order-preserving scans below never wait on global memory.
         for (int e = tid; e < E; e += nthreads) s_exp_tot[e] = 0;
-        __syncthreads();
-        if (warp == 0) {
-            int run[kMaxRanks];
+        int* s_idx = reinterpret_cast<int*>(s_bufs);
+        const StageLayout sl0 = stage_layout(p.src_row_bytes, p.x_row_bytes, p.meta_bytes, p.quant_mode != kQuantNone);
+        const int cap_tokens = max(32, ((num_warps * sl0.bytes / 4) / K) & ~31);
+        int run[kMaxRanks];
 #pragma unroll
-            for (int d = 0; d < kMaxRanks; ++d) run[d] = 0;
-            for (int base = t0; base < t1; base += 32) {
-                const int t = base + lane;
-                uint32_t mask = 0;
-                if (t < t1) {
-                    for (int k = 0; k < K; ++k) {
-                        const int64_t e = p.topk_idx[static_cast<int64_t>(t) * K + k];
-                        if (e >= 0 && e < E) mask |= 1u << (static_cast<int>(e) / EL);
+        for (int d = 0; d < kMaxRanks; ++d) run[d] = 0;
+        for (int tile0 = t0; tile0 < t1; tile0 += cap_tokens) {
+            const int tile1 = min(t1, tile0 + cap_tokens);
+            const int n_pairs = (tile1 - tile0) * K;
+            __syncthreads();
+            for (int i = tid; i < n_pairs; i += nthreads) {
+                const int64_t raw = p.topk_idx[static_cast<int64_t>(tile0) * K + i];
+                s_idx[i] = (raw >= 0 && raw < E) ? static_cast<int>(raw) : -1;
+            }
+            __syncthreads();
+            if (warp == 0) {
+                for (int base = tile0; base < tile1; base += 32) {
+                    const int t = base + lane;
+                    uint32_t mask = 0;
+                    if (t < tile1) {
+                        for (int k = 0; k < K; ++k) {
+                            const int e = s_idx[(t - tile0) * K + k];
+                            if (e >= 0) mask |= 1u << (e / EL);
+                        }
+                    }
+#pragma unroll
+                    for (int d = 0; d < kMaxRanks; ++d) {
+                        if (d < R) {
+                            const bool in = (mask >> d) & 1u;
+                            const uint32_t b = __ballot_sync(0xffffffffu, in);
+                            if (t < tile1) p.token_slot[static_cast<int64_t>(t) * R + d] = in ? run[d] + __popc(b & lanemask_lt()) : -1;
+                            run[d] += __popc(b);
+                        }
                     }
                 }
-#pragma unroll
-                for (int d = 0; d < kMaxRanks; ++d) {
-                    if (d < R) {
-                        const bool in = (mask >> d) & 1u;
-                        const uint32_t b = __ballot_sync(0xffffffffu, in);
-                        if (t < t1) p.token_slot[static_cast<int64_t>(t) * R + d] = in ? run[d] + __popc(b & lanemask_lt()) : -1;
-                        run[d] += __popc(b);
-                    }
+            } else if (warp == 1) {
+                for (int p0 = 0; p0 < n_pairs; p0 += 32) {
+                    const int pi = p0 + lane;
+                    const int e = pi < n_pairs ? s_idx[pi] : -1;
+                    const bool valid = e >= 0;
+                    const uint32_t peers = __match_any_sync(0xffffffffu, valid ? e : (0x40000000 | lane));
+                    int rel = -1;
+                    if (valid) rel = s_exp_tot[e] + __popc(peers & lanemask_lt());
+                    __syncwarp();
+                    if (valid && (peers & lanemask_lt()) == 0) s_exp_tot[e] += __popc(peers);
+                    __syncwarp();
+                    if (pi < n_pairs) p.pair_row[static_cast<int64_t>(tile0) * K + pi] = rel;
                 }
             }
+        }
+        if (warp == 0) {
 #pragma unroll
             for (int d = 0; d < kMaxRanks; ++d)
                 if (lane == d && d < R) blk_cnt[bid * CW + d] = run[d];
-        } else if (warp == 1) {
-            const int64_t p1 = static_cast<int64_t>(t1) * K;
-            for (int64_t p0 = static_cast<int64_t>(t0) * K; p0 < p1; p0 += 32) {
-                const int64_t pi = p0 + lane;
-                int e = -1;
-                if (pi < p1) {
-                    const int64_t raw = p.topk_idx[pi];
-                    e = (raw >= 0 && raw < E) ? static_cast<int>(raw) : -1;
-                }
-                const bool valid = e >= 0;
-                const uint32_t peers = __match_any_sync(0xffffffffu, valid ? e : (0x40000000 | lane));
-                int rel = -1;
-                if (valid) rel = s_exp_tot[e] + __popc(peers & lanemask_lt());
-                __syncwarp();
-                if (valid && (peers & lanemask_lt()) == 0) s_exp_tot[e] += __popc(peers);
-                __syncwarp();
-                if (pi < p1) p.pair_row[pi] = rel;
-            }
         }
         __syncthreads();
         for (int e = tid; e < E; e += nthreads) blk_cnt[bid * CW + R + e] = s_exp_tot[e];

@@ -125,6 +125,8 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
         .def("check_status", &Runtime::check_status)
         .def("clear_status", &Runtime::clear_status)
         .def("set_gpu_timeout", &Runtime::set_gpu_timeout)
+        .def("enable_profiling", &Runtime::enable_profiling)
+        .def("last_timings", &Runtime::last_timings)
         .def("rank", &Runtime::rank)
         .def("num_ranks", &Runtime::num_ranks)
         .def("num_bytes", &Runtime::num_bytes)

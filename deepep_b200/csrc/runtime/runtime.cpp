@@ -102,6 +102,24 @@ void Runtime::destroy() {
     host_words_ = nullptr;
 }
 
+void Runtime::enable_profiling(bool on) {
+    if (on && prof_events_[0] == nullptr)
+        for (auto& e : prof_events_) CUDA_RUNTIME_CHECK(cudaEventCreate(&e));
+    profiling_ = on;
+    prof_valid_[0] = prof_valid_[1] = false;
+}
+
+std::vector<float> Runtime::last_timings() {
+    std::vector<float> out(4, -1.f);
+    for (int op = 0; op < 2; ++op) {
+        if (!prof_valid_[op]) continue;
+        CUDA_RUNTIME_CHECK(cudaEventSynchronize(prof_events_[3 * op + 2]));
+        CUDA_RUNTIME_CHECK(cudaEventElapsedTime(&out[2 * op], prof_events_[3 * op], prof_events_[3 * op + 1]));
+        CUDA_RUNTIME_CHECK(cudaEventElapsedTime(&out[2 * op + 1], prof_events_[3 * op + 1], prof_events_[3 * op + 2]));
+    }
+    return out;
+}
+
 void Runtime::connect_local(const std::vector<std::shared_ptr<Runtime>>& runtimes) {
     std::vector<SymmetricHeap*> heaps;
     for (const auto& rt : runtimes) heaps.push_back(rt->heap_.get());
@@ -289,7 +307,9 @@ std::vector<DispatchResult> Runtime::dispatch(const std::vector<std::shared_ptr<
 
     DispatchLaunch launch;
     EP_HOST_ASSERT_MSG(plan_dispatch(m.r[0], num_sms, rt0.smem_optin_, &launch), "a token row does not fit into shared memory");
+    rt0.prof_record(0, stream);
     CUDA_RUNTIME_CHECK(launch_dispatch(m, launch, stream));
+    rt0.prof_record(1, stream);
 
     // ---- sizes of the outputs
     const int worst_rows = R * T_max;
@@ -386,6 +406,8 @@ std::vector<DispatchResult> Runtime::dispatch(const std::vector<std::shared_ptr<
     if (a0.sc.previous_event_before_epilogue.has_value()) a0.sc.previous_event_before_epilogue->stream_wait(scope.comm);
     const int epi_sms = std::max(1, rt0.num_device_sms_ / V);
     CUDA_RUNTIME_CHECK(launch_dispatch_epilogue(ep.data(), V, epi_sms, rt0.smem_optin_, stream));
+    rt0.prof_record(2, stream);
+    rt0.prof_valid_[0] = rt0.profiling_;
 
     auto event = scope.finish(a0.sc, touched);
     for (auto& r : res) r.event = event;
@@ -489,10 +511,14 @@ std::vector<CombineResult> Runtime::combine(const std::vector<std::shared_ptr<Ru
     }
     CombineLaunch launch;
     EP_HOST_ASSERT_MSG(plan_combine(m.r[0], num_sms, rt0.smem_optin_, &launch), "a token row does not fit into shared memory");
+    rt0.prof_record(3, stream);
     CUDA_RUNTIME_CHECK(launch_combine(m, launch, stream));
+    rt0.prof_record(4, stream);
     if (a0.sc.previous_event_before_epilogue.has_value()) a0.sc.previous_event_before_epilogue->stream_wait(scope.comm);
     const int epi_sms = std::max(1, rt0.num_device_sms_ / V);
     CUDA_RUNTIME_CHECK(launch_combine_epilogue(ep.data(), V, epi_sms, stream));
+    rt0.prof_record(5, stream);
+    rt0.prof_valid_[1] = rt0.profiling_;
     auto event = scope.finish(a0.sc, touched);
     for (auto& r : res) r.event = event;
     return res;

@@ -115,6 +115,11 @@ public:
     at::Tensor heap_tensor(int64_t offset, int64_t num_bytes) const;   // uint8 view of the own heap (no ownership)
     void set_gpu_timeout(double secs) { gpu_timeout_ns_ = static_cast<uint64_t>(secs * 1e9); }
 
+    // Optional device timing of the last dispatch / combine: events around the communication
+    // kernel and around the local epilogue (what the reference reports as two separate kernels).
+    void enable_profiling(bool on);
+    std::vector<float> last_timings();   // {dispatch kernel, dispatch epilogue, combine kernel, combine epilogue} in ms, -1 = not run
+
     // drivers
     static void barrier(const std::vector<std::shared_ptr<Runtime>>& rts, bool use_comm_stream, bool with_cpu_sync);
     static std::vector<DispatchResult> dispatch(const std::vector<std::shared_ptr<Runtime>>& rts, std::vector<DispatchArgs>& args);
@@ -147,6 +152,12 @@ private:
     at::cuda::CUDAStream comm_stream_;
     int num_device_sms_ = 0, smem_optin_ = 0;
     bool destroyed_ = false;
+    bool profiling_ = false;
+    cudaEvent_t prof_events_[6] = {nullptr, nullptr, nullptr, nullptr, nullptr, nullptr};
+    bool prof_valid_[2] = {false, false};
+    void prof_record(int idx, cudaStream_t stream) {
+        if (profiling_) cudaEventRecord(prof_events_[idx], stream);
+    }
 };
 
 }  // namespace ep

@@ -97,3 +97,15 @@ class LocalCluster:
         torch.cuda.synchronize()
         for b in self.buffers:
             b.destroy()
+
+
+class SingleProcessGroup:
+    """A group of one rank for single-GPU use without ``torch.distributed`` (EP1)."""
+
+    is_local_emulation = False
+
+    def rank(self) -> int:
+        return 0
+
+    def size(self) -> int:
+        return 1

@@ -60,8 +60,11 @@ def per_token_cast_to_fp8(x: torch.Tensor, round_scale: bool = False) -> Tuple[t
         scale = torch.exp2(torch.ceil(torch.log2(amax / FP8_MAX)))
         q = blocks * (1.0 / scale).unsqueeze(2)
     else:
-        scale = amax / FP8_MAX
-        q = blocks * (FP8_MAX / amax).unsqueeze(2)
+        # tensor / tensor divisions: `scalar / tensor` and `tensor / scalar` go through a reciprocal on
+        # some devices, which changes the last bit; the device kernels use one IEEE division each
+        full = torch.full_like(amax, FP8_MAX)
+        scale = torch.div(amax, full)
+        q = blocks * torch.div(full, amax).unsqueeze(2)
     q = q.clamp(-FP8_MAX, FP8_MAX).to(torch.float8_e4m3fn).view(m, -1)[:, :n].contiguous()
     return q, scale
 
