@@ -32,6 +32,7 @@ namespace ep {
 namespace {
 
 constexpr int kCntStride = kMaxRanks + kMaxExperts;   // words per source rank in the count matrix
+constexpr int kTotOffset = (kMaxBlocks - 1) * (kMaxRanks + kMaxExperts);   // last row of the per-block scratch: totals
 
 struct StageLayout {
     int src_off, out_off, meta_off, bar_off, bytes;
@@ -59,36 +60,48 @@ __host__ __device__ inline int header_bytes(int num_experts) {
 }
 
 // bf16 row in shared memory -> e4m3 row + one float scale per 128 channels. `out` may alias
-// `src`: step `base` reads bytes [2*base, 2*base + 512) and writes bytes [base, base + 256),
-// which only earlier steps have read, and the lanes of a step have all loaded (the shuffles
-// of the reduction are past) before any of them stores.
+// `src`: a step covers channels [base, base + 1024), reads bytes [2*base, 2*base + 2048) and
+// writes bytes [base, base + 1024), which only earlier steps have read, and the lanes of a step
+// have all loaded (the shuffles of the reduction are past) before any of them stores.
 __device__ __forceinline__ void quantize_row(const uint8_t* src, uint8_t* out, float* scales, int hidden, bool pow2, int lane) {
-    for (int base = 0; base < hidden; base += 256) {
-        const int ch = base + lane * 8;
-        const bool active = ch < hidden;
-        int4 raw = make_int4(0, 0, 0, 0);
-        if (active) raw = *reinterpret_cast<const int4*>(src + ch * 2);
-        const __nv_bfloat162* h2 = reinterpret_cast<const __nv_bfloat162*>(&raw);
-        float f[8];
+    constexpr int kUnroll = 4;   // independent 256-channel steps in flight per lane (hides shuffle / divide latency)
+    for (int base = 0; base < hidden; base += 256 * kUnroll) {
+        int4 raw[kUnroll];
+        float amax[kUnroll];
 #pragma unroll
-        for (int i = 0; i < 4; ++i) {
-            const float2 v = __bfloat1622float2(h2[i]);
-            f[2 * i] = v.x;
-            f[2 * i + 1] = v.y;
+        for (int u = 0; u < kUnroll; ++u) {
+            const int ch = base + u * 256 + lane * 8;
+            raw[u] = ch < hidden ? *reinterpret_cast<const int4*>(src + ch * 2) : make_int4(0, 0, 0, 0);
+            const __nv_bfloat162* h2 = reinterpret_cast<const __nv_bfloat162*>(&raw[u]);
+            float m = 0.f;
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+                const float2 v = __bfloat1622float2(h2[i]);
+                m = fmaxf(m, fmaxf(fabsf(v.x), fabsf(v.y)));
+            }
+            amax[u] = m;
         }
-        float amax = 0.f;
 #pragma unroll
-        for (int i = 0; i < 8; ++i) amax = fmaxf(amax, fabsf(f[i]));
-        amax = warp_reduce_max_width(amax, 16);
+        for (int o = 8; o > 0; o >>= 1) {
+#pragma unroll
+            for (int u = 0; u < kUnroll; ++u) amax[u] = fmaxf(amax[u], __shfl_xor_sync(0xffffffffu, amax[u], o));
+        }
         __syncwarp();
-        float scale, inv;
-        fp8_scale_from_amax(amax, pow2, scale, inv);
-        uint2 packed;
-        packed.x = pack4_e4m3(f[0] * inv, f[1] * inv, f[2] * inv, f[3] * inv);
-        packed.y = pack4_e4m3(f[4] * inv, f[5] * inv, f[6] * inv, f[7] * inv);
-        if (active) {
-            *reinterpret_cast<uint2*>(out + ch) = packed;
-            if ((lane & 15) == 0) scales[ch >> 7] = scale;
+#pragma unroll
+        for (int u = 0; u < kUnroll; ++u) {
+            const int ch = base + u * 256 + lane * 8;
+            float scale, inv;
+            fp8_scale_from_amax(amax[u], pow2, scale, inv);
+            const __nv_bfloat162* h2 = reinterpret_cast<const __nv_bfloat162*>(&raw[u]);
+            const float2 a = __bfloat1622float2(h2[0]), b = __bfloat1622float2(h2[1]);
+            const float2 c = __bfloat1622float2(h2[2]), d = __bfloat1622float2(h2[3]);
+            uint2 packed;
+            packed.x = pack4_e4m3(a.x * inv, a.y * inv, b.x * inv, b.y * inv);
+            packed.y = pack4_e4m3(c.x * inv, c.y * inv, d.x * inv, d.y * inv);
+            if (ch < hidden) {
+                *reinterpret_cast<uint2*>(out + ch) = packed;
+                if ((lane & 15) == 0) scales[ch >> 7] = scale;
+            }
         }
     }
 }
@@ -119,34 +132,52 @@ __global__ void __launch_bounds__(1024, 1) dispatch_kernel(const __grid_constant
     uint64_t* my_ctl = reinterpret_cast<uint64_t*>(c.heap[c.rank]);
     uint64_t* grid_counter = c.local_ws + kWsGridBarrier;
     bool ok = true;
+    // phase timestamps of block 0 (ns, %globaltimer): start, counted, exchanged, sent, finished
+    uint64_t* stamps = c.local_ws + kWsStamps;
+    const bool stamper = bid == 0 && tid == 0;
+    if (stamper) stamps[0] = globaltimer_ns();
 
     if (!p.cached) {
         // ------------------------------------------------------------ A. count
-        // The routing of the chunk is staged in shared memory (the send buffers are idle now) so
-        // that the two order-preserving scans below never wait on global memory.
-        for (int e = tid; e < E; e += nthreads) s_exp_tot[e] = 0;
-        int* s_idx = reinterpret_cast<int*>(s_bufs);
+        // The routing of the chunk is staged in shared memory (the send buffers are idle now).
+        // The chunk is cut into contiguous sub-ranges, one per counting warp; every warp ranks its
+        // (token, rank) and (token, expert) pairs among its own earlier tokens, a prefix over the
+        // warps turns that into positions inside the block. Everything is in token order, so the
+        // result does not depend on timing.
         const StageLayout sl0 = stage_layout(p.src_row_bytes, p.x_row_bytes, p.meta_bytes, p.quant_mode != kQuantNone);
-        const int cap_tokens = max(32, ((num_warps * sl0.bytes / 4) / K) & ~31);
-        int run[kMaxRanks];
-#pragma unroll
-        for (int d = 0; d < kMaxRanks; ++d) run[d] = 0;
+        const int scratch_bytes = num_warps * sl0.bytes;
+        int cw = min(num_warps, 16);
+        while (cw > 1 && cw * (E + kMaxRanks) * 4 > scratch_bytes / 2) --cw;
+        int* s_wcnt = reinterpret_cast<int*>(s_bufs);          // [cw][E]  per-warp expert counters, then bases
+        int* s_wrank = s_wcnt + cw * E;                         // [cw][kMaxRanks]
+        int* s_idx = s_wrank + cw * kMaxRanks;                  // [cap_tokens][K]
+        const int cap_tokens = max(32, ((scratch_bytes - cw * (E + kMaxRanks) * 4) / ((K + R) * 4)) & ~31);
+        int* s_slot = s_idx + cap_tokens * K;                   // [cap_tokens][R]
+        for (int e = tid; e < E; e += nthreads) s_exp_tot[e] = 0;
+        if (tid < kMaxRanks) s_flags[tid] = 0;
         for (int tile0 = t0; tile0 < t1; tile0 += cap_tokens) {
             const int tile1 = min(t1, tile0 + cap_tokens);
-            const int n_pairs = (tile1 - tile0) * K;
+            const int n_tok = tile1 - tile0;
+            const int n_pairs = n_tok * K;
+            const int tpw = ceil_div(n_tok, cw);
             __syncthreads();
             for (int i = tid; i < n_pairs; i += nthreads) {
                 const int64_t raw = p.topk_idx[static_cast<int64_t>(tile0) * K + i];
                 s_idx[i] = (raw >= 0 && raw < E) ? static_cast<int>(raw) : -1;
             }
+            for (int i = tid; i < cw * E; i += nthreads) s_wcnt[i] = 0;
             __syncthreads();
-            if (warp == 0) {
-                for (int base = tile0; base < tile1; base += 32) {
+            if (warp < cw) {
+                const int a = min(n_tok, warp * tpw), b = min(n_tok, a + tpw);
+                int run[kMaxRanks];
+#pragma unroll
+                for (int d = 0; d < kMaxRanks; ++d) run[d] = 0;
+                for (int base = a; base < b; base += 32) {
                     const int t = base + lane;
                     uint32_t mask = 0;
-                    if (t < tile1) {
+                    if (t < b) {
                         for (int k = 0; k < K; ++k) {
-                            const int e = s_idx[(t - tile0) * K + k];
+                            const int e = s_idx[t * K + k];
                             if (e >= 0) mask |= 1u << (e / EL);
                         }
                     }
@@ -154,70 +185,115 @@ __global__ void __launch_bounds__(1024, 1) dispatch_kernel(const __grid_constant
                     for (int d = 0; d < kMaxRanks; ++d) {
                         if (d < R) {
                             const bool in = (mask >> d) & 1u;
-                            const uint32_t b = __ballot_sync(0xffffffffu, in);
-                            if (t < tile1) p.token_slot[static_cast<int64_t>(t) * R + d] = in ? run[d] + __popc(b & lanemask_lt()) : -1;
-                            run[d] += __popc(b);
+                            const uint32_t bal = __ballot_sync(0xffffffffu, in);
+                            if (t < b) s_slot[t * R + d] = in ? run[d] + __popc(bal & lanemask_lt()) : -1;
+                            run[d] += __popc(bal);
                         }
                     }
                 }
-            } else if (warp == 1) {
-                for (int p0 = 0; p0 < n_pairs; p0 += 32) {
+#pragma unroll
+                for (int d = 0; d < kMaxRanks; ++d)
+                    if (lane == d) s_wrank[warp * kMaxRanks + d] = run[d];
+                int* mine = s_wcnt + warp * E;
+                for (int p0 = a * K; p0 < b * K; p0 += 32) {
                     const int pi = p0 + lane;
-                    const int e = pi < n_pairs ? s_idx[pi] : -1;
+                    const int e = pi < b * K ? s_idx[pi] : -1;
                     const bool valid = e >= 0;
                     const uint32_t peers = __match_any_sync(0xffffffffu, valid ? e : (0x40000000 | lane));
-                    int rel = -1;
-                    if (valid) rel = s_exp_tot[e] + __popc(peers & lanemask_lt());
+                    int rel = 0;
+                    if (valid) rel = mine[e] + __popc(peers & lanemask_lt());
                     __syncwarp();
-                    if (valid && (peers & lanemask_lt()) == 0) s_exp_tot[e] += __popc(peers);
+                    if (valid && (peers & lanemask_lt()) == 0) mine[e] += __popc(peers);
                     __syncwarp();
-                    if (pi < n_pairs) p.pair_row[static_cast<int64_t>(tile0) * K + pi] = rel;
+                    if (valid) s_idx[pi] = (rel << 11) | e;
                 }
             }
-        }
-        if (warp == 0) {
-#pragma unroll
-            for (int d = 0; d < kMaxRanks; ++d)
-                if (lane == d && d < R) blk_cnt[bid * CW + d] = run[d];
+            __syncthreads();
+            for (int e = tid; e < E; e += nthreads) {
+                int acc = s_exp_tot[e];
+                for (int wi = 0; wi < cw; ++wi) {
+                    const int v = s_wcnt[wi * E + e];
+                    s_wcnt[wi * E + e] = acc;
+                    acc += v;
+                }
+                s_exp_tot[e] = acc;
+            }
+            if (tid < R) {
+                int acc = s_flags[tid];
+                for (int wi = 0; wi < cw; ++wi) {
+                    const int v = s_wrank[wi * kMaxRanks + tid];
+                    s_wrank[wi * kMaxRanks + tid] = acc;
+                    acc += v;
+                }
+                s_flags[tid] = acc;
+            }
+            __syncthreads();
+            for (int i = tid; i < n_pairs; i += nthreads) {
+                const int packed = s_idx[i];
+                const int wi = (i / K) / tpw;
+                p.pair_row[static_cast<int64_t>(tile0) * K + i] = packed < 0 ? -1 : s_wcnt[wi * E + (packed & 2047)] + (packed >> 11);
+            }
+            for (int i = tid; i < n_tok * R; i += nthreads) {
+                const int v = s_slot[i];
+                const int wi = (i / R) / tpw;
+                p.token_slot[static_cast<int64_t>(tile0) * R + i] = v < 0 ? -1 : v + s_wrank[wi * kMaxRanks + (i % R)];
+            }
         }
         __syncthreads();
-        for (int e = tid; e < E; e += nthreads) blk_cnt[bid * CW + R + e] = s_exp_tot[e];
+        int* tot_cnt = blk_cnt + kTotOffset;   // [CW] totals over the blocks
+        for (int j = tid; j < CW; j += nthreads) {
+            const int v = j < R ? s_flags[j] : s_exp_tot[j - R];
+            blk_cnt[bid * CW + j] = v;
+            if (v != 0) atomicAdd(tot_cnt + j, v);
+        }
         __threadfence();
         ok &= grid_barrier(w, grid_counter, p.grid_bar_base + nb, 1);
+        if (stamper) stamps[1] = globaltimer_ns();
 
         // ------------------------------------------------------------ B. exchange
         for (int j = tid; j < CW; j += nthreads) {
-            int before = 0, total = 0;
-            const int upto = bid == 0 ? nb : bid;
-            for (int b = 0; b < upto; ++b) {
-                const int v = __ldcg(blk_cnt + b * CW + j);
-                if (b < bid) before += v;
-                total += v;
-            }
-            if (j < R) s_rank_base[j] = before; else s_exp_base[j - R] = before;
             if (bid == 0) {
-                const uint64_t word = pack_epoch(p.epoch, static_cast<uint32_t>(total));
+                const uint64_t word = pack_epoch(p.epoch, static_cast<uint32_t>(__ldcg(tot_cnt + j)));
                 const int col = j < R ? j : kMaxRanks + (j - R);
                 for (int d = 0; d < R; ++d) {
                     uint64_t* remote = reinterpret_cast<uint64_t*>(c.heap[d]) + kCtlDispatchCnt + static_cast<size_t>(c.rank) * kCntStride + col;
                     st_relaxed_sys_u64(remote, word);
                 }
             }
+            int before = 0;
+            for (int b0 = 0; b0 < bid; b0 += 8) {
+                int v[8];
+#pragma unroll
+                for (int u = 0; u < 8; ++u) v[u] = (b0 + u < bid) ? __ldcg(blk_cnt + (b0 + u) * CW + j) : 0;
+#pragma unroll
+                for (int u = 0; u < 8; ++u) before += v[u];
+            }
+            if (j < R) s_rank_base[j] = before; else s_exp_base[j - R] = before;
         }
         for (int j = tid; j < CW; j += nthreads) {
             const int col = j < R ? j : kMaxRanks + (j - R);
+            const uint64_t* words = my_ctl + kCtlDispatchCnt + col;
+            uint64_t v[kMaxRanks];
+            ok &= bounded_wait(w, kStatusDispatchCounts, -1, j, [&]() {
+                bool all = true;
+#pragma unroll
+                for (int s = 0; s < kMaxRanks; ++s) {
+                    if (s < R) {
+                        v[s] = ld_relaxed_sys_u64(words + static_cast<size_t>(s) * kCntStride);
+                        all &= epoch_matches(v[s], p.epoch);
+                    }
+                }
+                return all;
+            });
             int tot = 0, pre = 0;
-            for (int s = 0; s < R; ++s) {
-                const uint64_t* word = my_ctl + kCtlDispatchCnt + static_cast<size_t>(s) * kCntStride + col;
-                uint64_t v = 0;
-                ok &= bounded_wait(w, kStatusDispatchCounts, s, j, [&]() {
-                    v = ld_relaxed_sys_u64(word);
-                    return epoch_matches(v, p.epoch);
-                });
-                const int cnt = static_cast<int>(static_cast<uint32_t>(v));
-                tot += cnt;
-                if (s < c.rank) pre += cnt;
-                if (j == c.rank) s_recv_from[s] = cnt;
+#pragma unroll
+            for (int s = 0; s < kMaxRanks; ++s) {
+                if (s < R) {
+                    const int cnt = static_cast<int>(static_cast<uint32_t>(v[s]));
+                    tot += cnt;
+                    if (s < c.rank) pre += cnt;
+                    if (j == c.rank) s_recv_from[s] = cnt;
+                }
             }
             if (j < R) {
                 s_rank_base[j] += pre;
@@ -228,38 +304,49 @@ __global__ void __launch_bounds__(1024, 1) dispatch_kernel(const __grid_constant
         }
         ok = !__syncthreads_or(!ok);
         if (ok) {
-            // first row of every expert's segment on its rank (alignment applied)
-            if (tid < R) {
-                int start = 0;
-                for (int le = 0; le < EL; ++le) {
-                    const int e = tid * EL + le;
-                    s_exp_base[e] += start;
-                    start += align_up(s_exp_tot[e], p.expert_alignment);
+            // First row of every expert's segment on its rank (alignment applied): one warp per
+            // destination rank runs an exclusive scan over that rank's experts. The warp that scans
+            // this rank's own experts in block 0 also writes the receive-side description.
+            for (int d = warp; d < R; d += num_warps) {
+                const bool owner = bid == 0 && d == c.rank;
+                int carry = 0;
+                for (int base = 0; base < EL; base += 32) {
+                    const int le = base + lane;
+                    const int e = d * EL + le;
+                    const int tot = le < EL ? s_exp_tot[e] : 0;
+                    const int aligned = align_up(tot, p.expert_alignment);
+                    int incl = aligned;
+#pragma unroll
+                    for (int o = 1; o < 32; o <<= 1) {
+                        const int up = __shfl_up_sync(0xffffffffu, incl, o);
+                        if (lane >= o) incl += up;
+                    }
+                    const int start = carry + incl - aligned;
+                    if (le < EL) {
+                        s_exp_base[e] += start;
+                        if (owner) {
+                            p.num_unaligned[le] = tot;
+                            p.psum_expert[le] = p.do_expand ? start + tot : start + aligned;
+                            if (p.recv_stats != nullptr) p.recv_stats[le] += tot;
+                            if (p.host_counts != nullptr) p.host_counts[2 + le] = pack_epoch(p.epoch, static_cast<uint32_t>(aligned));
+                        }
+                    }
+                    carry += __shfl_sync(0xffffffffu, incl, 31);
+                }
+                if (owner && lane == 0) {
+                    p.psum_expert[EL] = carry;
+                    if (p.host_counts != nullptr) p.host_counts[1] = pack_epoch(p.epoch, static_cast<uint32_t>(carry));
                 }
             }
-            if (bid == 0 && tid == 32) {
-                // receive-side description of this rank
-                int acc = 0;
-                for (int s = 0; s < R; ++s) {
-                    acc += s_recv_from[s];
-                    p.psum_rank[s] = acc;
+            if (bid == 0 && warp == num_warps - 1) {
+                int incl = lane < R ? s_recv_from[lane] : 0;
+#pragma unroll
+                for (int o = 1; o < kMaxRanks; o <<= 1) {
+                    const int up = __shfl_up_sync(0xffffffffu, incl, o);
+                    if (lane >= o) incl += up;
                 }
-                int start = 0;
-                for (int le = 0; le < EL; ++le) {
-                    const int tot = s_exp_tot[c.rank * EL + le];
-                    const int aligned = align_up(tot, p.expert_alignment);
-                    p.num_unaligned[le] = tot;
-                    p.psum_expert[le] = p.do_expand ? start + tot : start + aligned;
-                    if (p.recv_stats != nullptr) p.recv_stats[le] += tot;
-                    if (p.host_counts != nullptr) p.host_counts[2 + le] = pack_epoch(p.epoch, static_cast<uint32_t>(aligned));
-                    start += aligned;
-                }
-                p.psum_expert[EL] = start;
-                if (p.host_counts != nullptr) {
-                    p.host_counts[1] = pack_epoch(p.epoch, static_cast<uint32_t>(start));
-                    __threadfence_system();
-                    p.host_counts[0] = pack_epoch(p.epoch, static_cast<uint32_t>(acc));
-                }
+                if (lane < R) p.psum_rank[lane] = incl;
+                if (lane == R - 1 && p.host_counts != nullptr) p.host_counts[0] = pack_epoch(p.epoch, static_cast<uint32_t>(incl));
             }
         }
         __syncthreads();
@@ -276,6 +363,7 @@ __global__ void __launch_bounds__(1024, 1) dispatch_kernel(const __grid_constant
         ok = !__syncthreads_or(!ok);
     }
 
+    if (stamper) stamps[2] = globaltimer_ns();
     // ---------------------------------------------------------------- C. send
     const bool quant = p.quant_mode != kQuantNone;
     const StageLayout sl = stage_layout(p.src_row_bytes, p.x_row_bytes, p.meta_bytes, quant);
@@ -351,13 +439,20 @@ __global__ void __launch_bounds__(1024, 1) dispatch_kernel(const __grid_constant
     bulk_wait_all();
     fence_proxy_async_all();
     __threadfence_system();
+    if (stamper) stamps[3] = globaltimer_ns();
     grid_barrier(w, grid_counter, p.grid_bar_base + (p.cached ? 1 : 2) * static_cast<uint64_t>(nb), 2);
+    if (stamper) stamps[4] = globaltimer_ns();
+    if (!p.cached && bid == 0) {
+        int* tot_cnt = blk_cnt + kTotOffset;
+        for (int j = tid; j < CW; j += nthreads) tot_cnt[j] = 0;   // ready for the next launch (stream order)
+    }
     if (bid == 0 && tid < R) {
         uint64_t* remote = reinterpret_cast<uint64_t*>(c.heap[tid]) + kCtlDispatchDone + c.rank;
         st_release_sys_u64(remote, pack_epoch(p.epoch, 0));
         const uint64_t* word = my_ctl + kCtlDispatchDone + tid;
         bounded_wait(w, kStatusDispatchDone, tid, 0, [&]() { return epoch_reached(ld_acquire_sys_u64(word), p.epoch); });
     }
+    if (stamper) stamps[5] = globaltimer_ns();
 }
 
 // ==================================================================== epilogue (local, all SMs)

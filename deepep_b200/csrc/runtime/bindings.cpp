@@ -127,6 +127,7 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
         .def("set_gpu_timeout", &Runtime::set_gpu_timeout)
         .def("enable_profiling", &Runtime::enable_profiling)
         .def("last_timings", &Runtime::last_timings)
+        .def("last_dispatch_phases", &Runtime::last_dispatch_phases)
         .def("rank", &Runtime::rank)
         .def("num_ranks", &Runtime::num_ranks)
         .def("num_bytes", &Runtime::num_bytes)

@@ -120,6 +120,15 @@ std::vector<float> Runtime::last_timings() {
     return out;
 }
 
+std::vector<int64_t> Runtime::last_dispatch_phases() {
+    CUDA_RUNTIME_CHECK(cudaDeviceSynchronize());
+    uint64_t raw[6];
+    CUDA_RUNTIME_CHECK(cudaMemcpy(raw, local_ws_ + kWsStamps, sizeof(raw), cudaMemcpyDeviceToHost));
+    std::vector<int64_t> out;
+    for (int i = 1; i < 6; ++i) out.push_back(static_cast<int64_t>(raw[i] - raw[0]));
+    return out;
+}
+
 void Runtime::connect_local(const std::vector<std::shared_ptr<Runtime>>& runtimes) {
     std::vector<SymmetricHeap*> heaps;
     for (const auto& rt : runtimes) heaps.push_back(rt->heap_.get());
@@ -323,18 +332,25 @@ std::vector<DispatchResult> Runtime::dispatch(const std::vector<std::shared_ptr<
             r.num_recv_tokens = a.h_num_recv_tokens;
             r.num_expanded_tokens = a.h_num_expanded_tokens;
         } else if (a.do_cpu_sync) {
+            // every count word carries the epoch of this dispatch: wait for each of them on its own
             volatile uint64_t* words = rt.host_words_ + kHostStatusWords;
             const uint32_t epoch = rt.dispatch_epoch;
             const auto start = std::chrono::steady_clock::now();
-            while (static_cast<uint32_t>(words[0] >> 32) != epoch) {
-                rt.check_status();
-                const double waited = std::chrono::duration<double>(std::chrono::steady_clock::now() - start).count();
-                if (waited > rt.cpu_timeout_secs_) throw EPTimeoutError("EP host wait for the received token counts timed out", 0);
-            }
-            r.num_recv_tokens = static_cast<int>(static_cast<uint32_t>(words[0]));
-            r.num_expanded_tokens = static_cast<int>(static_cast<uint32_t>(words[1]));
+            auto wait_word = [&](int i) -> int {
+                uint64_t v;
+                int spins = 0;
+                while (static_cast<uint32_t>((v = words[i]) >> 32) != epoch) {
+                    if ((++spins & 1023) != 0) continue;
+                    rt.check_status();
+                    const double waited = std::chrono::duration<double>(std::chrono::steady_clock::now() - start).count();
+                    if (waited > rt.cpu_timeout_secs_) throw EPTimeoutError("EP host wait for the received token counts timed out", 0);
+                }
+                return static_cast<int>(static_cast<uint32_t>(v));
+            };
+            r.num_recv_tokens = wait_word(0);
+            r.num_expanded_tokens = wait_word(1);
             r.num_recv_tokens_per_expert_list.resize(EL);
-            for (int le = 0; le < EL; ++le) r.num_recv_tokens_per_expert_list[le] = static_cast<int>(static_cast<uint32_t>(words[2 + le]));
+            for (int le = 0; le < EL; ++le) r.num_recv_tokens_per_expert_list[le] = wait_word(2 + le);
         } else {
             r.num_recv_tokens = worst_rows;
             r.num_expanded_tokens = worst_expanded;

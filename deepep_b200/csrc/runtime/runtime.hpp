@@ -120,6 +120,10 @@ public:
     void enable_profiling(bool on);
     std::vector<float> last_timings();   // {dispatch kernel, dispatch epilogue, combine kernel, combine epilogue} in ms, -1 = not run
 
+    // Phase timestamps (ns) that block 0 of the last dispatch kernel wrote: start, counted, exchanged,
+    // send loop done (block 0), all blocks done, peers done. Synchronises the device.
+    std::vector<int64_t> last_dispatch_phases();
+
     // drivers
     static void barrier(const std::vector<std::shared_ptr<Runtime>>& rts, bool use_comm_stream, bool with_cpu_sync);
     static std::vector<DispatchResult> dispatch(const std::vector<std::shared_ptr<Runtime>>& rts, std::vector<DispatchArgs>& args);
