@@ -61,6 +61,7 @@ enum StatusCode : int {
 constexpr int kWsGridBarrier = 0;    // monotonically growing arrival counter
 constexpr int kWsPoison = 1;         // non-zero after any wait of this rank gave up
 constexpr int kWsStamps = 2;         // [8] phase timestamps of the last dispatch (block 0, ns)
+constexpr int kWsWork = 10;          // next token index handed out by the dynamic send loops
 constexpr int kWsScratch = 16;       // start of per-block scratch counters
 // scratch: int32 [kMaxBlocks][kMaxRanks + kMaxExperts]
 constexpr size_t kWsScratchInts = static_cast<size_t>(kMaxBlocks) * (kMaxRanks + kMaxExperts);

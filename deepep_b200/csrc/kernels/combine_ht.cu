@@ -76,12 +76,21 @@ __global__ void __launch_bounds__(1024, 1) combine_kernel(const __grid_constant_
     const int vec_per_row = p.row_bytes / 16;
     uint32_t parity = 0;
     const int64_t total_steps = static_cast<int64_t>(max_group) * R;
-    for (int64_t g = static_cast<int64_t>(bid) * num_warps + warp; g < total_steps; g += static_cast<int64_t>(nb) * num_warps) {
+    // rows are handed out dynamically (SMs differ in how fast their peer stores drain)
+    unsigned long long* work = reinterpret_cast<unsigned long long*>(c.local_ws + kWsWork);
+    int64_t g = static_cast<int64_t>(bid) * num_warps + warp;
+    int64_t next_g = 0;
+    bool fatal = false;
+    for (; g < total_steps && !fatal; g = next_g) {
+        // the next index is requested now and only read at the end of the step (latency hidden)
+        long long fetched = 0;
+        if (lane == 0) fetched = static_cast<long long>(atomicAdd(work, 1ull)) + static_cast<long long>(nb) * num_warps;
+        do {
         const int d = (c.rank + 1 + static_cast<int>(g % R)) % R;
         const int idx = static_cast<int>(g / R);
         group_begin = d == 0 ? 0 : p.psum_rank[d - 1];
         group_size = p.psum_rank[d] - group_begin;
-        if (idx >= group_size) continue;
+        if (idx >= group_size) break;
         const int i = group_begin + idx;
         const int* md = p.recv_src_metadata + static_cast<int64_t>(i) * (K + 2);
         const int src_token = md[0] % p.num_max_tokens;
@@ -102,7 +111,7 @@ __global__ void __launch_bounds__(1024, 1) combine_kernel(const __grid_constant_
                 reinterpret_cast<float*>(heap + p.off_comb_w)[dst_row * K + lane] = p.topk_weights[static_cast<int64_t>(i) * K + lane];
             const bool landed = mbar_wait(w, bar, parity, kStatusTmaLoad, i);
             parity ^= 1;
-            if (!__all_sync(0xffffffffu, landed)) break;
+            if (!__all_sync(0xffffffffu, landed)) { fatal = true; break; }
             if (lane == 0) {
                 bulk_s2g(heap + p.off_comb_x + dst_row * p.row_bytes, buf, p.row_bytes);
                 bulk_commit();
@@ -158,14 +167,17 @@ __global__ void __launch_bounds__(1024, 1) combine_kernel(const __grid_constant_
                     bulk_commit();
                 }
             }
-            if (failed) break;
+            if (failed) fatal = true;
         }
+        } while (false);
+        next_g = __shfl_sync(0xffffffffu, fetched, 0);
     }
 
     bulk_wait_all();
     fence_proxy_async_all();
     __threadfence_system();
     grid_barrier(w, c.local_ws + kWsGridBarrier, p.grid_bar_base + nb, 3);
+    if (bid == 0 && tid == 0) c.local_ws[kWsWork] = 0;   // ready for the next launch (stream order)
     if (bid == 0 && tid < R) {
         uint64_t* remote = reinterpret_cast<uint64_t*>(c.heap[tid]) + kCtlCombineDone + c.rank;
         st_release_sys_u64(remote, pack_epoch(p.epoch, 0));

@@ -350,6 +350,22 @@ __global__ void __launch_bounds__(1024, 1) dispatch_kernel(const __grid_constant
             }
         }
         __syncthreads();
+        // Make the positions of this block's chunk absolute, so that ANY block can send ANY token.
+        if (ok) {
+            const int n_tok = t1 - t0;
+            for (int i = tid; i < n_tok * R; i += nthreads) {
+                int* slot = p.token_slot + static_cast<int64_t>(t0) * R + i;
+                const int v = *slot;
+                if (v >= 0) *slot = v + s_rank_base[i % R];
+            }
+            for (int i = tid; i < n_tok * K; i += nthreads) {
+                const int64_t pi = static_cast<int64_t>(t0) * K + i;
+                const int v = p.pair_row[pi];
+                if (v >= 0) p.pair_row[pi] = v + s_exp_base[static_cast<int>(p.topk_idx[pi])];
+            }
+        }
+        __threadfence();
+        ok &= grid_barrier(w, grid_counter, p.grid_bar_base + 2 * static_cast<uint64_t>(nb), 4);
     } else {
         // ------------------------------------------------------------ cached: only announce entry and wait for the peers
         if (bid == 0 && tid < R) {
@@ -385,7 +401,14 @@ __global__ void __launch_bounds__(1024, 1) dispatch_kernel(const __grid_constant
         float* meta_w = reinterpret_cast<float*>(meta_idx + K);
         int* meta_row = meta_idx + 2 * K;
         uint32_t parity = 0;
-        for (int t = t0 + warp; t < t1; t += num_warps) {
+        // Tokens are handed out dynamically: SMs differ in how fast their peer stores drain, and a
+        // static split would leave the fast ones idle. Every warp starts with a fixed token and
+        // then draws the next index from a counter of this rank.
+        unsigned long long* work = reinterpret_cast<unsigned long long*>(c.local_ws + kWsWork);
+        int t = bid * num_warps + warp;
+        while (t < T) {
+            int fetched = 0;
+            if (lane == 0) fetched = static_cast<int>(atomicAdd(work, 1ull)) + nb * num_warps;
             bulk_wait_read_all();   // the previous stores of every lane have read the buffers
             __syncwarp();
             if (lane == 0) {
@@ -394,22 +417,12 @@ __global__ void __launch_bounds__(1024, 1) dispatch_kernel(const __grid_constant
                 if (sf_bulk) bulk_g2s(buf_meta, p.sf + static_cast<int64_t>(t) * p.sf_token_stride * 4, p.sf_bytes, bar);
             }
             int slot = -1;
-            if (lane < R) {
-                slot = p.token_slot[static_cast<int64_t>(t) * R + lane];
-                if (!p.cached && slot >= 0) {
-                    slot += s_rank_base[lane];
-                    p.token_slot[static_cast<int64_t>(t) * R + lane] = slot;
-                }
-            }
+            if (lane < R) slot = p.token_slot[static_cast<int64_t>(t) * R + lane];
             if (lane < K) {
                 const int64_t pi = static_cast<int64_t>(t) * K + lane;
                 const int64_t raw = p.topk_idx[pi];
                 const int e = (raw >= 0 && raw < E) ? static_cast<int>(raw) : -1;
-                int row = p.pair_row[pi];
-                if (!p.cached && e >= 0) {
-                    row += s_exp_base[e];
-                    p.pair_row[pi] = row;
-                }
+                const int row = p.pair_row[pi];
                 meta_idx[lane] = e;
                 meta_w[lane] = p.topk_weights != nullptr ? p.topk_weights[pi] : 0.f;
                 meta_row[lane] = row;
@@ -432,6 +445,7 @@ __global__ void __launch_bounds__(1024, 1) dispatch_kernel(const __grid_constant
                 bulk_s2g(heap + p.off_recv_meta + static_cast<uint64_t>(slot) * p.meta_bytes, buf_meta, p.meta_bytes);
                 bulk_commit();
             }
+            t = __shfl_sync(0xffffffffu, fetched, 0);
         }
     }
 
@@ -440,11 +454,14 @@ __global__ void __launch_bounds__(1024, 1) dispatch_kernel(const __grid_constant
     fence_proxy_async_all();
     __threadfence_system();
     if (stamper) stamps[3] = globaltimer_ns();
-    grid_barrier(w, grid_counter, p.grid_bar_base + (p.cached ? 1 : 2) * static_cast<uint64_t>(nb), 2);
+    grid_barrier(w, grid_counter, p.grid_bar_base + (p.cached ? 1 : 3) * static_cast<uint64_t>(nb), 2);
     if (stamper) stamps[4] = globaltimer_ns();
-    if (!p.cached && bid == 0) {
-        int* tot_cnt = blk_cnt + kTotOffset;
-        for (int j = tid; j < CW; j += nthreads) tot_cnt[j] = 0;   // ready for the next launch (stream order)
+    if (bid == 0) {   // ready for the next launch (stream order)
+        if (tid == 0) c.local_ws[kWsWork] = 0;
+        if (!p.cached) {
+            int* tot_cnt = blk_cnt + kTotOffset;
+            for (int j = tid; j < CW; j += nthreads) tot_cnt[j] = 0;
+        }
     }
     if (bid == 0 && tid < R) {
         uint64_t* remote = reinterpret_cast<uint64_t*>(c.heap[tid]) + kCtlDispatchDone + c.rank;

@@ -153,7 +153,7 @@ void Runtime::clear_status() {
     host_words_[0] = 0;
     CUDA_RUNTIME_CHECK(cudaMemset(local_ws_ + kWsPoison, 0, sizeof(uint64_t)));
     // the grid-barrier counter may be anywhere after a failed launch: restart it
-    CUDA_RUNTIME_CHECK(cudaMemset(local_ws_ + kWsGridBarrier, 0, sizeof(uint64_t)));
+    CUDA_RUNTIME_CHECK(cudaMemset(local_ws_, 0, kWsBytes));
     grid_bar_base = 0;
 }
 
@@ -310,7 +310,7 @@ std::vector<DispatchResult> Runtime::dispatch(const std::vector<std::shared_ptr<
         p.off_recv_x = lay.dispatch_x[slot];
         p.off_recv_meta = lay.dispatch_meta[slot];
         p.grid_bar_base = rt.grid_bar_base;
-        rt.grid_bar_base += static_cast<uint64_t>(cached ? 1 : 2) * num_sms;
+        rt.grid_bar_base += static_cast<uint64_t>(cached ? 1 : 3) * num_sms;
         p.host_counts = (a.do_cpu_sync && !cached) ? rt.host_words_dev_ + kHostStatusWords : nullptr;
     }
 
