@@ -10,6 +10,7 @@ import torch
 
 from ._native import _C, require_native  # noqa: F401
 from .buffers.elastic import ElasticBuffer, EPHandle  # noqa: F401
+from .buffers.legacy import Buffer, Config  # noqa: F401
 from .utils.envs import get_logical_domain_size, get_physical_domain_size  # noqa: F401
 from .utils.event import EventOverlap  # noqa: F401
 

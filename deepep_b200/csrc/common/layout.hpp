@@ -62,10 +62,15 @@ constexpr int kWsGridBarrier = 0;    // monotonically growing arrival counter
 constexpr int kWsPoison = 1;         // non-zero after any wait of this rank gave up
 constexpr int kWsStamps = 2;         // [8] phase timestamps of the last dispatch (block 0, ns)
 constexpr int kWsWork = 10;          // next token index handed out by the dynamic send loops
+constexpr int kWsLLCalls = 11;       // [4] low-latency call counters: dispatch send, dispatch recv, combine send, combine recv
 constexpr int kWsScratch = 16;       // start of per-block scratch counters
 // scratch: int32 [kMaxBlocks][kMaxRanks + kMaxExperts]
 constexpr size_t kWsScratchInts = static_cast<size_t>(kMaxBlocks) * (kMaxRanks + kMaxExperts);
-constexpr size_t kWsBytes = kWsScratch * 8 + kWsScratchInts * 4 + 4096;
+// low-latency area (int32): [kMaxExperts] dispatch finish counters, [kMaxExperts] combine finish counters,
+// [kMaxRanks] rank mask, [4] blocks-done counters of the four phases
+constexpr size_t kWsLLOffsetBytes = kWsScratch * 8 + kWsScratchInts * 4;
+constexpr size_t kWsLLInts = 2 * kMaxExperts + kMaxRanks + 4;
+constexpr size_t kWsBytes = kWsLLOffsetBytes + kWsLLInts * 4 + 4096;
 
 // ---------------------------------------------------------------- control area of the symmetric heap, in uint64 words
 constexpr size_t kCtlBarrier = 0;                                        // [kMaxRanks]
@@ -135,11 +140,19 @@ EP_HD HtLayout ht_layout(int num_ranks, int num_max_tokens, int hidden, int num_
 }
 
 // ---------------------------------------------------------------- low-latency EP layout
-// Per buffer half: receive area [local experts][ranks][max tokens] of messages
-// (16-byte header + payload + scales), receive count words [local experts][ranks],
-// combine receive area [experts][max tokens] rows of bf16 and combine flags [experts].
+// Two halves (calls alternate). Per half:
+//   recv_x        [local experts][ranks][max tokens] messages: 16-byte header {token, top-k lane},
+//                 payload (e4m3 + 1x128 scales, or bf16)
+//   recv_count    [local experts][ranks] epoch-tagged words (count of the messages above)
+//   combine_x     [kMaxLLTopk][max tokens] bf16 rows, indexed by the token's top-k lane
+//   combine_flag  [experts] epoch-tagged words ("all rows of this expert for you have landed")
+//   send_x        [local experts][ranks * max tokens] bf16 rows: optional staging area the caller may
+//                 let its expert GEMM write into (zero-copy combine)
+constexpr int kMaxLLTopk = 16;
+
 EP_HD int ll_dispatch_msg_bytes(int hidden, bool fp8) {
-    return 16 + (fp8 ? hidden + ceil_div(hidden, 128) * 4 : hidden * 2);
+    const int payload = fp8 ? hidden + align_up(ceil_div(hidden, 128) * 4, 16) : hidden * 2;
+    return 16 + payload;
 }
 
 struct LLLayout {
@@ -147,6 +160,7 @@ struct LLLayout {
     uint64_t recv_count[2];
     uint64_t combine_x[2];
     uint64_t combine_flag[2];
+    uint64_t send_x[2];
     uint64_t end;
 };
 
@@ -156,14 +170,16 @@ EP_HD LLLayout ll_layout(int num_ranks, int num_max_tokens, int hidden, int num_
     const uint64_t msg = ll_dispatch_msg_bytes(hidden, false);   // widest message
     const uint64_t recv = align_up<uint64_t>(static_cast<uint64_t>(num_local) * num_ranks * num_max_tokens * msg, 256);
     const uint64_t cnt = align_up<uint64_t>(static_cast<uint64_t>(num_local) * num_ranks * 8, 256);
-    const uint64_t comb = align_up<uint64_t>(static_cast<uint64_t>(num_experts) * num_max_tokens * hidden * 2, 256);
+    const uint64_t comb = align_up<uint64_t>(static_cast<uint64_t>(kMaxLLTopk) * num_max_tokens * hidden * 2, 256);
     const uint64_t flag = align_up<uint64_t>(static_cast<uint64_t>(num_experts) * 8, 256);
+    const uint64_t send = align_up<uint64_t>(static_cast<uint64_t>(num_local) * num_ranks * num_max_tokens * hidden * 2, 256);
     uint64_t off = kCtlBytes;
     for (int s = 0; s < 2; ++s) {
         l.recv_x[s] = off; off += recv;
         l.recv_count[s] = off; off += cnt;
         l.combine_x[s] = off; off += comb;
         l.combine_flag[s] = off; off += flag;
+        l.send_x[s] = off; off += send;
     }
     l.end = align_up<uint64_t>(off, kHeapAlignment);
     return l;

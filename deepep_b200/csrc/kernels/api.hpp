@@ -158,4 +158,46 @@ cudaError_t launch_dispatch_layout(const int64_t* topk_idx, int num_tokens, int 
                                    int* num_tokens_per_rank, int* num_tokens_per_expert, bool* is_token_in_rank,
                                    cudaStream_t stream);
 
+// ---------------------------------------------------------------- low-latency dispatch / combine
+enum LLPhase : int { kLLSend = 1, kLLRecv = 2 };
+
+struct LLDispatchParams {
+    CommCtx c;
+    int num_tokens, hidden, num_topk, num_experts, num_local_experts, num_max_tokens;
+    int use_fp8, round_scale, use_ue8m0;
+    int phases;
+    int shrink;                      // a peer that does not answer in time is masked instead of reported
+    const uint8_t* x;                // [T, hidden] bf16
+    const int64_t* topk_idx;         // [T, K]
+    uint8_t* packed_recv_x;          // [EL][R * T_max][hidden] e4m3 or bf16
+    uint8_t* packed_recv_sf;         // float [EL][hidden / 128][R * T_max] or int32 [EL][hidden / 512][R * T_max]
+    int* packed_recv_src_info;       // [EL][R * T_max]  token | lane << 16
+    int64_t* packed_recv_layout_range;   // [EL][R]  begin << 32 | count
+    int* packed_recv_count;          // [EL]
+    int* cumulative_stats;           // [EL] or null
+    int64_t* wait_stats;             // [R] accumulated wait time per source rank (ns) or null
+    uint64_t off_recv_x[2], off_recv_count[2];
+};
+cudaError_t launch_ll_dispatch(const Multi<LLDispatchParams>& m, int num_sms, cudaStream_t stream);
+
+struct LLCombineParams {
+    CommCtx c;
+    int num_tokens, hidden, num_topk, num_experts, num_local_experts, num_max_tokens;
+    int phases;
+    int shrink;
+    const uint8_t* x;                // [EL][R * T_max][hidden] bf16
+    const int64_t* topk_idx;         // [T, K] routing of the tokens this rank dispatched
+    const float* topk_weights;       // [T, K]
+    const int* src_info;             // handle
+    const int64_t* layout_range;     // handle
+    uint8_t* combined_x;             // [T, hidden] bf16
+    int64_t* wait_stats;             // [R] or null
+    uint64_t off_combine_x[2], off_combine_flag[2];
+};
+cudaError_t launch_ll_combine(const Multi<LLCombineParams>& m, int num_sms, int smem_optin, cudaStream_t stream);
+
+// rank mask (shrink mode) kept in the private workspace
+cudaError_t ll_update_mask(uint64_t* local_ws, int rank, int value, cudaStream_t stream);
+cudaError_t ll_query_mask(uint64_t* local_ws, int* out, int num_ranks, cudaStream_t stream);
+
 }  // namespace ep

@@ -1,0 +1,441 @@
+// Low-latency expert-parallel dispatch / combine for decode batches (sm_100a, NVLink only).
+//
+// Dispatch, SEND phase: one thread block per token (round-robin). The block casts the bf16 row
+// to e4m3 with 1x128 scales (optionally power-of-two scales, optionally packed as UE8M0) into a
+// shared-memory message, then one warp per selected expert bulk-stores the message into slot
+// [local expert][source rank][position] of the owner's receive area. Positions are the token's
+// rank among this source's earlier tokens for that expert, so they do not depend on timing.
+// A per-expert completion counter tells the warp responsible for the expert when every message
+// has landed; it then publishes the (epoch-tagged) count to the owner.
+// Dispatch, RECV phase: one block per local expert waits for the counts of all source ranks,
+// and packs the messages expert-major: rows grouped by source rank in ascending order, scales
+// column-major, plus src_info / layout_range / recv_count for the combine.
+//
+// Combine, SEND phase: every packed row goes back to row [top-k lane][token] of its source
+// rank's combine area (the lane travelled with the token, which keeps the area at
+// lanes x tokens rows, small enough to stay in L2); per (expert, rank) completion counters
+// drive one flag per expert. Combine, RECV phase: per token, wait for the flags of its experts,
+// accumulate sum_k w_k * row_k in fp32 in ascending lane order, round to bf16 once.
+//
+// No host synchronisation, no launch parameter that changes from call to call: the call
+// counters that select the buffer half and tag the flags live in device memory, so a captured
+// CUDA graph replays correctly. SEND and RECV can be launched separately (receive hooks).
+//
+// Parity: csrc/kernels/legacy/internode_ll.cu:128-462 (dispatch), :714-1138 (combine),
+// :21-126 and :1240-1285 (clean / mask) of the reference.
+#include "api.hpp"
+#include "../common/device_utils.cuh"
+
+namespace ep {
+
+namespace {
+
+__device__ __forceinline__ int* ll_ints(const CommCtx& c) {
+    return reinterpret_cast<int*>(reinterpret_cast<uint8_t*>(c.local_ws) + kWsLLOffsetBytes);
+}
+__device__ __forceinline__ int* ll_finish_dispatch(const CommCtx& c) { return ll_ints(c); }
+__device__ __forceinline__ int* ll_finish_combine(const CommCtx& c) { return ll_ints(c) + kMaxExperts; }
+__device__ __forceinline__ int* ll_mask(const CommCtx& c) { return ll_ints(c) + 2 * kMaxExperts; }
+__device__ __forceinline__ int* ll_done(const CommCtx& c) { return ll_ints(c) + 2 * kMaxExperts + kMaxRanks; }
+
+__device__ __forceinline__ int ld_volatile_int(const int* p) {
+    return *reinterpret_cast<const volatile int*>(p);
+}
+
+// Last block of a phase advances that phase's call counter (all blocks have read it by then).
+__device__ __forceinline__ void ll_phase_done(const CommCtx& c, int phase_idx, int nb) {
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        __threadfence();
+        const int old = atomicAdd(ll_done(c) + phase_idx, 1);
+        if (old == nb - 1) {
+            ll_done(c)[phase_idx] = 0;
+            __threadfence();
+            atomicAdd(reinterpret_cast<unsigned long long*>(c.local_ws + kWsLLCalls + phase_idx), 1ull);
+        }
+    }
+}
+
+// A wait that either reports (normal mode) or masks the silent peer (shrink mode).
+template <typename Pred>
+__device__ __forceinline__ bool ll_wait(const WaitCtx& w, const CommCtx& c, int shrink, int code, int peer, uint32_t tag, Pred pred) {
+    if (!shrink) return bounded_wait(w, code, peer, tag, pred);
+    uint32_t spins = 0;
+    while (!pred()) {
+        if ((++spins & 63u) == 0) {
+            if (ld_volatile_int(ll_mask(c) + peer) != 0) return false;
+            if (globaltimer_ns() > w.deadline_ns) {
+                atomicExch(ll_mask(c) + peer, 1);
+                return false;
+            }
+        }
+    }
+    return true;
+}
+
+// ==================================================================== dispatch
+__global__ void __launch_bounds__(1024, 1) ll_dispatch_kernel(const __grid_constant__ Multi<LLDispatchParams> m) {
+    extern __shared__ __align__(128) uint8_t smem[];
+    const int vr = blockIdx.x / m.blocks_per_rank;
+    const int bid = blockIdx.x % m.blocks_per_rank;
+    const int nb = m.blocks_per_rank;
+    const LLDispatchParams& p = m.r[vr];
+    const CommCtx& c = p.c;
+    const WaitCtx w = make_wait_ctx(c);
+    const int tid = threadIdx.x, lane = lane_id(), warp = warp_id();
+    const int num_warps = blockDim.x >> 5;
+    const int T = p.num_tokens, H = p.hidden, K = p.num_topk, E = p.num_experts, EL = p.num_local_experts;
+    const int R = c.num_ranks, Tm = p.num_max_tokens;
+    const int msg_bytes = ll_dispatch_msg_bytes(H, p.use_fp8);
+    const int payload_bytes = p.use_fp8 ? H : H * 2;
+    const int* mask = ll_mask(c);
+
+    if (p.phases & kLLSend) {
+        const uint32_t epoch = static_cast<uint32_t>(*reinterpret_cast<volatile uint64_t*>(c.local_ws + kWsLLCalls + 0)) + 1;
+        const int half = epoch & 1;
+        int* finish = ll_finish_dispatch(c);
+        int* s_topk = reinterpret_cast<int*>(smem);                         // [T * K]
+        uint8_t* s_msg = smem + align_up(T * K * 4, 128);                   // [2][msg_bytes aligned]
+        const int msg_stride = align_up(msg_bytes, 128);
+        for (int i = tid; i < T * K; i += blockDim.x) {
+            const int64_t raw = p.topk_idx[i];
+            s_topk[i] = (raw >= 0 && raw < E) ? static_cast<int>(raw) : -1;
+        }
+        __syncthreads();
+
+        int iter = 0;
+        for (int t = bid; t < T; t += nb, ++iter) {
+            uint8_t* msg = s_msg + (iter & 1) * msg_stride;
+            uint8_t* payload = msg + 16;
+            // ---- cast / copy the row into the message
+            const int ch = tid * 8;
+            const bool active = ch < H;
+            int4 raw = make_int4(0, 0, 0, 0);
+            if (active) raw = ld_nc_int4(p.x + (static_cast<int64_t>(t) * H + ch) * 2);
+            if (!p.use_fp8) {
+                if (active) *reinterpret_cast<int4*>(payload + ch * 2) = raw;
+            } else {
+                const __nv_bfloat162* h2 = reinterpret_cast<const __nv_bfloat162*>(&raw);
+                float f[8];
+#pragma unroll
+                for (int i = 0; i < 4; ++i) {
+                    const float2 v = __bfloat1622float2(h2[i]);
+                    f[2 * i] = v.x;
+                    f[2 * i + 1] = v.y;
+                }
+                float amax = 0.f;
+#pragma unroll
+                for (int i = 0; i < 8; ++i) amax = fmaxf(amax, fabsf(f[i]));
+                // every thread takes part in the shuffles (inactive lanes carry zeros); hidden % 128 == 0,
+                // so a 16-lane scale group is either all active or all inactive
+                amax = warp_reduce_max_width(amax, 16);
+                float scale, inv;
+                fp8_scale_from_amax(amax, p.round_scale != 0, scale, inv);
+                uint2 packed;
+                packed.x = pack4_e4m3(f[0] * inv, f[1] * inv, f[2] * inv, f[3] * inv);
+                packed.y = pack4_e4m3(f[4] * inv, f[5] * inv, f[6] * inv, f[7] * inv);
+                if (active) {
+                    *reinterpret_cast<uint2*>(payload + ch) = packed;
+                    if ((lane & 15) == 0) {
+                        if (p.use_ue8m0) payload[H + (ch >> 7)] = static_cast<uint8_t>(__float_as_uint(scale) >> 23);
+                        else reinterpret_cast<float*>(payload + H)[ch >> 7] = scale;
+                    }
+                }
+            }
+            fence_proxy_async_smem();
+            __syncthreads();   // message complete; also: the stores of two tokens ago have finished reading this buffer
+            // ---- one warp per selected expert
+            if (warp < K) {
+                const int e = s_topk[t * K + warp];
+                const int dst = e >= 0 ? e / EL : -1;
+                if (e >= 0 && ld_volatile_int(mask + dst) == 0) {
+                    int before = 0;
+                    for (int i = lane; i < t * K; i += 32) before += s_topk[i] == e;
+                    const int slot = warp_reduce_sum(before);
+                    if (lane == 0) {
+                        uint8_t* dst_msg = c.heap[dst] + p.off_recv_x[half] +
+                                           ((static_cast<uint64_t>(e - dst * EL) * R + c.rank) * Tm + slot) * msg_bytes;
+                        *reinterpret_cast<int4*>(dst_msg) = make_int4(t, warp, 0, 0);
+                        bulk_s2g(dst_msg + 16, payload, msg_bytes - 16);
+                        bulk_commit();
+                        bulk_wait_all();
+                        fence_proxy_async_all();
+                        __threadfence_system();
+                        atomicAdd(finish + e, 1);
+                    }
+                }
+                __syncwarp();
+            }
+        }
+        // ---- publish the per-expert counts once every message of the expert has landed
+        for (int e = bid + warp * nb; e < E; e += nb * num_warps) {
+            const int dst = e / EL;
+            if (ld_volatile_int(mask + dst) != 0) continue;
+            int total = 0;
+            for (int i = lane; i < T * K; i += 32) total += s_topk[i] == e;
+            total = warp_reduce_sum(total);
+            if (lane == 0) {
+                bounded_wait(w, kStatusLLRecv, dst, e, [&]() { return ld_volatile_int(finish + e) >= total; });
+                finish[e] = 0;
+                __threadfence_system();
+                uint64_t* word = reinterpret_cast<uint64_t*>(c.heap[dst] + p.off_recv_count[half]) + (e - dst * EL) * R + c.rank;
+                st_release_sys_u64(word, pack_epoch(epoch, static_cast<uint32_t>(total)));
+            }
+            __syncwarp();
+        }
+        ll_phase_done(c, 0, nb);
+    }
+
+    if (p.phases & kLLRecv) {
+        const uint32_t epoch = static_cast<uint32_t>(*reinterpret_cast<volatile uint64_t*>(c.local_ws + kWsLLCalls + 1)) + 1;
+        const int half = epoch & 1;
+        __shared__ int s_cnt[kMaxRanks], s_begin[kMaxRanks + 1];
+        const int rows_per_expert = R * Tm;
+        const int sf_per_row = p.use_fp8 ? (p.use_ue8m0 ? H / 512 : H / 128) : 0;
+        for (int le = bid; le < EL; le += nb) {
+            __syncthreads();
+            if (tid < R) {
+                int cnt = 0;
+                if (ld_volatile_int(mask + tid) == 0) {
+                    const uint64_t* word = reinterpret_cast<const uint64_t*>(c.heap[c.rank] + p.off_recv_count[half]) + le * R + tid;
+                    uint64_t v = 0;
+                    const uint64_t t0 = globaltimer_ns();
+                    const bool ok = ll_wait(w, c, p.shrink, kStatusLLRecv, tid, le, [&]() {
+                        v = ld_acquire_sys_u64(word);
+                        return epoch_matches(v, epoch);
+                    });
+                    if (ok) cnt = static_cast<int>(static_cast<uint32_t>(v));
+                    if (p.wait_stats != nullptr) atomicAdd(reinterpret_cast<unsigned long long*>(p.wait_stats + tid), globaltimer_ns() - t0);
+                }
+                s_cnt[tid] = cnt;
+            }
+            __syncthreads();
+            if (tid == 0) {
+                int acc = 0;
+                for (int s = 0; s < R; ++s) {
+                    s_begin[s] = acc;
+                    p.packed_recv_layout_range[le * R + s] = (static_cast<int64_t>(acc) << 32) | static_cast<uint32_t>(s_cnt[s]);
+                    acc += s_cnt[s];
+                }
+                s_begin[R] = acc;
+                p.packed_recv_count[le] = acc;
+                if (p.cumulative_stats != nullptr) atomicAdd(p.cumulative_stats + le, acc);
+            }
+            __syncthreads();
+            const int total = s_begin[R];
+            for (int j = warp; j < total; j += num_warps) {
+                int s = 0;
+                while (s < R - 1 && j >= s_begin[s + 1]) ++s;
+                const int slot = j - s_begin[s];
+                const uint8_t* src = c.heap[c.rank] + p.off_recv_x[half] + ((static_cast<uint64_t>(le) * R + s) * Tm + slot) * msg_bytes;
+                const int64_t out_row = static_cast<int64_t>(le) * rows_per_expert + j;
+                if (lane == 0) {
+                    const int4 hdr = *reinterpret_cast<const int4*>(src);
+                    p.packed_recv_src_info[out_row] = hdr.x | (hdr.y << 16);
+                }
+                uint8_t* dst = p.packed_recv_x + out_row * payload_bytes;
+                for (int v = lane; v < payload_bytes / 16; v += 32) st_na_int4(dst + v * 16, ld_nc_int4(src + 16 + v * 16));
+                if (sf_per_row > 0) {
+                    const uint32_t* sf = reinterpret_cast<const uint32_t*>(src + 16 + H);
+                    uint32_t* out_sf = reinterpret_cast<uint32_t*>(p.packed_recv_sf);
+                    for (int i = lane; i < sf_per_row; i += 32)
+                        out_sf[(static_cast<int64_t>(le) * sf_per_row + i) * rows_per_expert + j] = sf[i];
+                }
+            }
+        }
+        ll_phase_done(c, 1, nb);
+    }
+}
+
+// ==================================================================== combine
+__global__ void __launch_bounds__(1024, 1) ll_combine_kernel(const __grid_constant__ Multi<LLCombineParams> m) {
+    extern __shared__ __align__(128) uint8_t smem[];
+    const int vr = blockIdx.x / m.blocks_per_rank;
+    const int bid = blockIdx.x % m.blocks_per_rank;
+    const int nb = m.blocks_per_rank;
+    const LLCombineParams& p = m.r[vr];
+    const CommCtx& c = p.c;
+    const WaitCtx w = make_wait_ctx(c);
+    const int tid = threadIdx.x, lane = lane_id(), warp = warp_id();
+    const int num_warps = blockDim.x >> 5;
+    const int T = p.num_tokens, H = p.hidden, K = p.num_topk, E = p.num_experts, EL = p.num_local_experts;
+    const int R = c.num_ranks, Tm = p.num_max_tokens;
+    const int row_bytes = H * 2;
+    const int* mask = ll_mask(c);
+
+    if (p.phases & kLLSend) {
+        const uint32_t epoch = static_cast<uint32_t>(*reinterpret_cast<volatile uint64_t*>(c.local_ws + kWsLLCalls + 2)) + 1;
+        const int half = epoch & 1;
+        int* finish = ll_finish_combine(c);
+        __shared__ int s_pref[kMaxLocalExperts + 1];
+        if (tid == 0) {
+            int acc = 0;
+            for (int le = 0; le < EL; ++le) {
+                s_pref[le] = acc;
+                const int64_t last = p.layout_range[le * R + R - 1];
+                acc += static_cast<int>(last >> 32) + static_cast<int>(last & 0xffffffff);
+            }
+            s_pref[EL] = acc;
+        }
+        __syncthreads();
+        const int total_rows = s_pref[EL];
+        const int stage = align_up(row_bytes, 128) + 16;
+        uint8_t* buf = smem + static_cast<size_t>(warp) * stage;
+        uint64_t* bar = reinterpret_cast<uint64_t*>(buf + align_up(row_bytes, 128));
+        if (lane == 0) {
+            mbar_init(bar, 1);
+            fence_mbar_init();
+        }
+        __syncwarp();
+        uint32_t parity = 0;
+        for (int g = bid * num_warps + warp; g < total_rows; g += nb * num_warps) {
+            int le = 0;
+            while (le < EL - 1 && g >= s_pref[le + 1]) ++le;
+            const int j = g - s_pref[le];
+            int s = 0;
+            while (s < R - 1 && j >= static_cast<int>(p.layout_range[le * R + s + 1] >> 32)) ++s;
+            if (ld_volatile_int(mask + s) != 0) continue;
+            const int64_t row = static_cast<int64_t>(le) * R * Tm + j;
+            const int info = p.src_info[row];
+            const int token = info & 0xffff, k = info >> 16;
+            bulk_wait_read_all();
+            __syncwarp();
+            if (lane == 0) {
+                mbar_arrive_expect_tx(bar, row_bytes);
+                bulk_g2s(buf, p.x + row * row_bytes, row_bytes, bar);
+            }
+            const bool landed = mbar_wait(w, bar, parity, kStatusTmaLoad, g);
+            parity ^= 1;
+            if (!__all_sync(0xffffffffu, landed)) break;
+            if (lane == 0) {
+                bulk_s2g(c.heap[s] + p.off_combine_x[half] + (static_cast<uint64_t>(k) * Tm + token) * row_bytes, buf, row_bytes);
+                bulk_commit();
+                bulk_wait_all();
+                fence_proxy_async_all();
+                __threadfence_system();
+                atomicAdd(finish + le * R + s, 1);
+            }
+            __syncwarp();
+        }
+        // ---- one flag per (expert, destination rank) once all its rows have landed
+        for (int q = bid + warp * nb; q < EL * R; q += nb * num_warps) {
+            const int le = q / R, s = q % R;
+            const int cnt = static_cast<int>(p.layout_range[q] & 0xffffffff);
+            if (cnt == 0 || ld_volatile_int(mask + s) != 0) continue;
+            if (lane == 0) {
+                bounded_wait(w, kStatusLLCombine, s, q, [&]() { return ld_volatile_int(finish + q) >= cnt; });
+                finish[q] = 0;
+                __threadfence_system();
+                uint64_t* word = reinterpret_cast<uint64_t*>(c.heap[s] + p.off_combine_flag[half]) + (c.rank * EL + le);
+                st_release_sys_u64(word, pack_epoch(epoch, 1));
+            }
+            __syncwarp();
+        }
+        ll_phase_done(c, 2, nb);
+    }
+
+    if (p.phases & kLLRecv) {
+        const uint32_t epoch = static_cast<uint32_t>(*reinterpret_cast<volatile uint64_t*>(c.local_ws + kWsLLCalls + 3)) + 1;
+        const int half = epoch & 1;
+        __shared__ float s_w[kMaxTopk];
+        __shared__ int s_ok[kMaxTopk];
+        const uint8_t* region = c.heap[c.rank] + p.off_combine_x[half];
+        for (int t = bid; t < T; t += nb) {
+            __syncthreads();
+            if (tid < K) {
+                const int64_t raw = p.topk_idx[static_cast<int64_t>(t) * K + tid];
+                const int e = (raw >= 0 && raw < E) ? static_cast<int>(raw) : -1;
+                int ok = 0;
+                if (e >= 0 && ld_volatile_int(mask + e / EL) == 0) {
+                    const uint64_t* word = reinterpret_cast<const uint64_t*>(c.heap[c.rank] + p.off_combine_flag[half]) + e;
+                    const uint64_t t0 = globaltimer_ns();
+                    ok = ll_wait(w, c, p.shrink, kStatusLLCombine, e / EL, e, [&]() { return epoch_matches(ld_acquire_sys_u64(word), epoch); });
+                    if (p.wait_stats != nullptr) atomicAdd(reinterpret_cast<unsigned long long*>(p.wait_stats + e / EL), globaltimer_ns() - t0);
+                }
+                s_ok[tid] = ok;
+                s_w[tid] = p.topk_weights[static_cast<int64_t>(t) * K + tid];
+            }
+            __syncthreads();
+            for (int ch = tid * 8; ch < H; ch += blockDim.x * 8) {
+                float acc[8];
+#pragma unroll
+                for (int i = 0; i < 8; ++i) acc[i] = 0.f;
+                for (int k = 0; k < K; ++k) {
+                    if (!s_ok[k]) continue;
+                    const int4 raw = ld_nc_int4(region + ((static_cast<uint64_t>(k) * Tm + t) * H + ch) * 2);
+                    const __nv_bfloat162* h2 = reinterpret_cast<const __nv_bfloat162*>(&raw);
+                    const float wk = s_w[k];
+#pragma unroll
+                    for (int i = 0; i < 4; ++i) {
+                        const float2 v = __bfloat1622float2(h2[i]);
+                        acc[2 * i] = fmaf(wk, v.x, acc[2 * i]);
+                        acc[2 * i + 1] = fmaf(wk, v.y, acc[2 * i + 1]);
+                    }
+                }
+                int4 out;
+                __nv_bfloat162* o2 = reinterpret_cast<__nv_bfloat162*>(&out);
+#pragma unroll
+                for (int i = 0; i < 4; ++i) o2[i] = __floats2bfloat162_rn(acc[2 * i], acc[2 * i + 1]);
+                st_na_int4(p.combined_x + (static_cast<int64_t>(t) * H + ch) * 2, out);
+            }
+        }
+        ll_phase_done(c, 3, nb);
+    }
+}
+
+__global__ void ll_mask_kernel(uint64_t* local_ws, int rank, int value, int* out, int num_ranks) {
+    int* mask = reinterpret_cast<int*>(reinterpret_cast<uint8_t*>(local_ws) + kWsLLOffsetBytes) + 2 * kMaxExperts;
+    if (out != nullptr) {
+        if (threadIdx.x < num_ranks) out[threadIdx.x] = mask[threadIdx.x];
+    } else if (rank < 0) {
+        if (threadIdx.x < kMaxRanks) mask[threadIdx.x] = 0;
+    } else if (threadIdx.x == 0) {
+        mask[rank] = value;
+    }
+}
+
+cudaError_t coop_launch(const void* fn, void** args, int grid, int block, int smem, cudaStream_t stream) {
+    return cudaLaunchCooperativeKernel(fn, dim3(grid), dim3(block), args, smem, stream);
+}
+
+}  // namespace
+
+cudaError_t launch_ll_dispatch(const Multi<LLDispatchParams>& m, int num_sms, cudaStream_t stream) {
+    const LLDispatchParams& p = m.r[0];
+    const int msg_stride = align_up(ll_dispatch_msg_bytes(p.hidden, p.use_fp8), 128);
+    const int smem_bytes = align_up(p.num_max_tokens * p.num_topk * 4, 128) + 2 * msg_stride;
+    cudaError_t err = cudaFuncSetAttribute(ll_dispatch_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_bytes);
+    if (err != cudaSuccess) return err;
+    Multi<LLDispatchParams> copy = m;
+    copy.blocks_per_rank = num_sms;
+    void* args[] = {&copy};
+    // cooperative: the blocks of the SEND phase wait on counters that other blocks advance
+    return coop_launch(reinterpret_cast<const void*>(ll_dispatch_kernel), args, m.num_vranks * num_sms, 1024, smem_bytes, stream);
+}
+
+cudaError_t launch_ll_combine(const Multi<LLCombineParams>& m, int num_sms, int smem_optin, cudaStream_t stream) {
+    const LLCombineParams& p = m.r[0];
+    const int stage = align_up(p.hidden * 2, 128) + 16;
+    int warps = smem_optin / stage;
+    if (warps > 32) warps = 32;
+    if (warps < 1) return cudaErrorInvalidValue;
+    const int smem_bytes = warps * stage;
+    cudaError_t err = cudaFuncSetAttribute(ll_combine_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_bytes);
+    if (err != cudaSuccess) return err;
+    Multi<LLCombineParams> copy = m;
+    copy.blocks_per_rank = num_sms;
+    void* args[] = {&copy};
+    return coop_launch(reinterpret_cast<const void*>(ll_combine_kernel), args, m.num_vranks * num_sms, warps * 32, smem_bytes, stream);
+}
+
+cudaError_t ll_update_mask(uint64_t* local_ws, int rank, int value, cudaStream_t stream) {
+    ll_mask_kernel<<<1, 32, 0, stream>>>(local_ws, rank, value, nullptr, 0);
+    return cudaGetLastError();
+}
+
+cudaError_t ll_query_mask(uint64_t* local_ws, int* out, int num_ranks, cudaStream_t stream) {
+    ll_mask_kernel<<<1, 32, 0, stream>>>(local_ws, 0, 0, out, num_ranks);
+    return cudaGetLastError();
+}
+
+}  // namespace ep

@@ -4,4 +4,8 @@
 
 namespace py = pybind11;
 
-void register_extra_bindings(py::module_& m) { (void)m; }
+namespace ep {
+void register_ll_bindings(py::module_& m);
+}
+
+void register_extra_bindings(py::module_& m) { ep::register_ll_bindings(m); }

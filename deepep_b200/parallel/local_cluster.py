@@ -89,6 +89,38 @@ class LocalCluster:
         results = self._C.Runtime.combine(self.runtimes, args)
         return [(r.combined_x, r.combined_topk_weights, EventOverlap(r.event)) for r in results]
 
+    # ------------------------------------------------------------------ low-latency mode
+    def low_latency_dispatch(self, xs, topk_idxs, num_max_dispatch_tokens_per_rank: int, num_experts: int, use_fp8: bool = True,
+                             round_scale: bool = False, use_ue8m0: bool = False, phases: Optional[int] = None, ios=None,
+                             num_sms: int = 0, shrink: bool = False):
+        """All ranks' ``Buffer.low_latency_dispatch`` as one launch. Returns the per-rank IO blocks
+        (``packed_recv_x``, ``packed_recv_sf``, ``packed_recv_count``, ``src_info``, ``layout_range``)."""
+        C = self._C
+        if ios is None:
+            ios = []
+            for x, idx in zip(xs, topk_idxs):
+                io = C.LLDispatchIO()
+                io.x, io.topk_idx = x, idx
+                ios.append(io)
+        phases = (C.LL_SEND | C.LL_RECV) if phases is None else phases
+        C.ll_dispatch(self.runtimes, ios, num_max_dispatch_tokens_per_rank, num_experts, use_fp8, round_scale, use_ue8m0, phases,
+                      num_sms, shrink, False, True)
+        return ios
+
+    def low_latency_combine(self, ys, topk_idxs, topk_weights, dispatch_ios, num_max_dispatch_tokens_per_rank: int,
+                            num_experts: int, phases: Optional[int] = None, ios=None, num_sms: int = 0, shrink: bool = False):
+        C = self._C
+        if ios is None:
+            ios = []
+            for y, idx, w, d in zip(ys, topk_idxs, topk_weights, dispatch_ios):
+                io = C.LLCombineIO()
+                io.x, io.topk_idx, io.topk_weights = y, idx, w
+                io.src_info, io.layout_range = d.src_info, d.layout_range
+                ios.append(io)
+        phases = (C.LL_SEND | C.LL_RECV) if phases is None else phases
+        C.ll_combine(self.runtimes, ios, num_max_dispatch_tokens_per_rank, num_experts, phases, num_sms, shrink, False, True)
+        return ios
+
     def check_status(self) -> None:
         for b in self.buffers:
             b.check_status()
