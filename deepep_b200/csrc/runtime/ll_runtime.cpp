@@ -52,7 +52,7 @@ struct LLStreams {
     }
 };
 
-std::optional<EventHandle> ll_dispatch(const std::vector<std::shared_ptr<Runtime>>& rts, std::vector<LLDispatchIO>& ios,
+std::optional<EventHandle> ll_dispatch(const std::vector<std::shared_ptr<Runtime>>& rts, std::vector<LLDispatchIO*>& ios,
                                        int num_max_tokens, int num_experts, bool use_fp8, bool round_scale, bool use_ue8m0,
                                        int phases, int num_sms, bool shrink, bool async_finish, bool on_compute_stream) {
     const int V = static_cast<int>(rts.size());
@@ -62,7 +62,7 @@ std::optional<EventHandle> ll_dispatch(const std::vector<std::shared_ptr<Runtime
     c10::cuda::CUDAGuard guard(static_cast<c10::DeviceIndex>(device));
     LLStreams streams(rt0, on_compute_stream);
     const int R = rt0.num_ranks();
-    const int H = static_cast<int>(ios[0].x.size(1)), K = static_cast<int>(ios[0].topk_idx.size(1));
+    const int H = static_cast<int>(ios[0]->x.size(1)), K = static_cast<int>(ios[0]->topk_idx.size(1));
     const int E = num_experts, EL = E / R, Tm = num_max_tokens;
     EP_HOST_ASSERT(E % R == 0 && E <= kMaxExperts && EL <= kMaxLocalExperts && K <= kMaxLLTopk && Tm >= 1 && Tm < 65536);
     EP_HOST_ASSERT_MSG(H % 128 == 0 && H <= 8192, "low-latency dispatch needs hidden % 128 == 0 and hidden <= 8192");
@@ -77,7 +77,7 @@ std::optional<EventHandle> ll_dispatch(const std::vector<std::shared_ptr<Runtime
     m.blocks_per_rank = num_sms;
     for (int v = 0; v < V; ++v) {
         auto& rt = *rts[v];
-        auto& io = ios[v];
+        auto& io = *ios[v];
         EP_HOST_ASSERT(io.x.scalar_type() == at::kBFloat16 && io.x.is_contiguous() && io.x.size(1) == H && io.x.size(0) <= Tm);
         EP_HOST_ASSERT(io.topk_idx.scalar_type() == at::kLong && io.topk_idx.is_contiguous() && io.topk_idx.size(0) == io.x.size(0) && io.topk_idx.size(1) == K);
         if (!io.packed_recv_x.defined()) {
@@ -121,7 +121,7 @@ std::optional<EventHandle> ll_dispatch(const std::vector<std::shared_ptr<Runtime
     return streams.finish(async_finish);
 }
 
-std::optional<EventHandle> ll_combine(const std::vector<std::shared_ptr<Runtime>>& rts, std::vector<LLCombineIO>& ios,
+std::optional<EventHandle> ll_combine(const std::vector<std::shared_ptr<Runtime>>& rts, std::vector<LLCombineIO*>& ios,
                                       int num_max_tokens, int num_experts, int phases, int num_sms, bool shrink,
                                       bool async_finish, bool on_compute_stream) {
     const int V = static_cast<int>(rts.size());
@@ -131,7 +131,7 @@ std::optional<EventHandle> ll_combine(const std::vector<std::shared_ptr<Runtime>
     c10::cuda::CUDAGuard guard(static_cast<c10::DeviceIndex>(device));
     LLStreams streams(rt0, on_compute_stream);
     const int R = rt0.num_ranks();
-    const int H = static_cast<int>(ios[0].x.size(2)), K = static_cast<int>(ios[0].topk_idx.size(1));
+    const int H = static_cast<int>(ios[0]->x.size(2)), K = static_cast<int>(ios[0]->topk_idx.size(1));
     const int E = num_experts, EL = E / R, Tm = num_max_tokens;
     EP_HOST_ASSERT(E % R == 0 && K <= kMaxLLTopk && K <= kMaxTopk && (H * 2) % 16 == 0);
     const LLLayout lay = ll_layout(R, Tm, H, E);
@@ -144,7 +144,7 @@ std::optional<EventHandle> ll_combine(const std::vector<std::shared_ptr<Runtime>
     m.blocks_per_rank = num_sms;
     for (int v = 0; v < V; ++v) {
         auto& rt = *rts[v];
-        auto& io = ios[v];
+        auto& io = *ios[v];
         EP_HOST_ASSERT(io.x.scalar_type() == at::kBFloat16 && io.x.is_contiguous() && io.x.dim() == 3 && io.x.size(0) == EL &&
                        io.x.size(1) == R * Tm && io.x.size(2) == H);
         EP_HOST_ASSERT(io.topk_idx.scalar_type() == at::kLong && io.topk_idx.is_contiguous());
