@@ -1,0 +1,314 @@
+// Plain and grouped GEMM on the tcgen05 core (see gemm_sm100.cuh): bf16 inputs, or e4m3 inputs
+// with 1x128 (activations) and 128x128 (weights) fp32 block scales applied in the epilogue warps.
+// The grouped form consumes the expanded (expert-major) output of the dispatch directly:
+// `group_end` is the device-resident prefix array of the dispatch handle, so no host
+// synchronisation sits between dispatch and the expert GEMM.
+//
+// The reference library contains no GEMM; this is the compute half of the fused MoE layer and of
+// the all-gather -> GEMM / GEMM -> reduce-scatter operators (tp_fused.cu).
+#include "gemm_api.hpp"
+#include "gemm_sm100.cuh"
+
+namespace ep {
+namespace gemm {
+
+namespace {
+
+struct Tile {
+    int g, m0, m_end, n0;
+};
+
+// Walks the tiles of a (grouped) problem in a fixed order: group, then n-block, then m-block.
+struct Scheduler {
+    const GemmParams& p;
+    int tiles_n, BN;
+    int g = 0, base = 0, start = 0, end = 0;
+    __device__ Scheduler(const GemmParams& p_, int bn) : p(p_), tiles_n(p_.N / bn), BN(bn) {
+        end = p.group_end != nullptr ? p.group_end[0] : p.M;
+    }
+    __device__ bool get(int t, Tile& out) {
+        while (g < p.num_groups) {
+            const int rows = max(end - start, 0);
+            const int tiles_m = ceil_div(rows, BM);
+            const int tiles = tiles_m * tiles_n;
+            if (t < base + tiles) {
+                const int local = t - base;
+                out.g = g;
+                out.m0 = start + (local % tiles_m) * BM;
+                out.m_end = end;
+                out.n0 = (local / tiles_m) * BN;
+                return true;
+            }
+            base += tiles;
+            ++g;
+            if (g < p.num_groups) {
+                start = align_up(end, p.group_alignment);
+                end = p.group_end[g];
+            }
+        }
+        return false;
+    }
+};
+
+template <int BN, bool kFp8>
+struct Cfg {
+    static constexpr int kEpiWarps = kFp8 ? 8 : 4;
+    static constexpr int kThreads = (2 + kEpiWarps) * 32;
+    static constexpr int BK = kFp8 ? 128 : 64;          // one 128-byte swizzle span per row
+    static constexpr int UMMA_K = kFp8 ? 32 : 16;
+    static constexpr int A_BYTES = BM * 128, B_BYTES = BN * 128, STAGE = A_BYTES + B_BYTES;
+    static constexpr int kStages = (192 * 1024) / STAGE;
+    static constexpr int kBarBytes = (2 * kStages + 4) * 8 + 16;
+    static constexpr int kSmem = kStages * STAGE + kBarBytes + 1024;   // + slack to align the ring to 1024 bytes
+    static constexpr int kTmemCols = 2 * BN;
+};
+
+template <int BN, bool kFp8>
+__global__ void __launch_bounds__(Cfg<BN, kFp8>::kThreads, 1)
+gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b, const GemmParams p) {
+    using C = Cfg<BN, kFp8>;
+    extern __shared__ uint8_t smem_raw[];
+    uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~static_cast<uintptr_t>(1023));
+    uint64_t* full = reinterpret_cast<uint64_t*>(smem + C::kStages * C::STAGE);
+    uint64_t* empty = full + C::kStages;
+    uint64_t* tmem_full = empty + C::kStages;
+    uint64_t* tmem_empty = tmem_full + 2;
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(tmem_empty + 2);
+
+    const int warp = warp_id(), lane = lane_id();
+    const int num_kb = p.K / C::BK;
+    PipeCtx pc{p.error, globaltimer_ns() + p.timeout_ns};
+
+    if (warp == 0 && lane == 0) {
+        prefetch_tensormap(&map_a);
+        prefetch_tensormap(&map_b);
+        for (int s = 0; s < C::kStages; ++s) {
+            mbar_init(full + s, 1);
+            mbar_init(empty + s, 1);
+        }
+        for (int a = 0; a < 2; ++a) {
+            mbar_init(tmem_full + a, 1);
+            mbar_init(tmem_empty + a, C::kEpiWarps * 32);
+        }
+        fence_mbar_init();
+    }
+    if (warp == 1) {
+        tmem_alloc(tmem_slot, C::kTmemCols);
+        tmem_relinquish();
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem_base = *tmem_slot;
+
+    if (warp == 0) {
+        // ------------------------------------------------------------ TMA producer
+        if (lane == 0) {
+            Scheduler sched(p, BN);
+            Tile t;
+            int s = 0;
+            uint32_t ph = 0;
+            bool ok = true;
+            for (int ti = blockIdx.x; ok && sched.get(ti, t); ti += gridDim.x) {
+                for (int kb = 0; kb < num_kb; ++kb) {
+                    if (!(ok = pipe_wait(pc, empty + s, ph ^ 1))) break;
+                    uint8_t* sa = smem + s * C::STAGE;
+                    mbar_arrive_expect_tx(full + s, C::STAGE);
+                    tma_load_2d(sa, &map_a, kb * C::BK, t.m0, full + s);
+                    tma_load_2d(sa + C::A_BYTES, &map_b, kb * C::BK, t.g * p.N + t.n0, full + s);
+                    if (++s == C::kStages) { s = 0; ph ^= 1; }
+                }
+            }
+        }
+    } else if (warp == 1) {
+        // ------------------------------------------------------------ MMA issuer
+        if (lane == 0) {
+            Scheduler sched(p, BN);
+            Tile t;
+            constexpr uint32_t idesc = make_idesc<kFp8>(BM, BN);
+            int s = 0, acc = 0;
+            uint32_t ph = 0, acc_ph = 0;
+            bool ok = true;
+            for (int ti = blockIdx.x; ok && sched.get(ti, t); ti += gridDim.x) {
+                if constexpr (!kFp8) {
+                    if (!(ok = pipe_wait(pc, tmem_empty + acc, acc_ph ^ 1))) break;
+                    tc_fence_after();
+                }
+                for (int kb = 0; kb < num_kb; ++kb) {
+                    if constexpr (kFp8) {
+                        if (!(ok = pipe_wait(pc, tmem_empty + acc, acc_ph ^ 1))) break;
+                    }
+                    if (!(ok = pipe_wait(pc, full + s, ph))) break;
+                    tc_fence_after();
+                    const uint8_t* sa = smem + s * C::STAGE;
+                    const uint64_t da = make_smem_desc(sa), db = make_smem_desc(sa + C::A_BYTES);
+                    const uint32_t d_addr = tmem_base + acc * BN;
+#pragma unroll
+                    for (int k = 0; k < C::BK / C::UMMA_K; ++k) {
+                        const uint32_t accumulate = kFp8 ? (k != 0) : ((kb | k) != 0);
+                        umma<kFp8>(d_addr, da + 2 * k, db + 2 * k, idesc, accumulate);
+                    }
+                    umma_commit(empty + s);
+                    if (++s == C::kStages) { s = 0; ph ^= 1; }
+                    if constexpr (kFp8) {
+                        umma_commit(tmem_full + acc);
+                        acc ^= 1;
+                        if (acc == 0) acc_ph ^= 1;
+                    }
+                }
+                if constexpr (!kFp8) {
+                    if (!ok) break;
+                    umma_commit(tmem_full + acc);
+                    acc ^= 1;
+                    if (acc == 0) acc_ph ^= 1;
+                }
+            }
+        }
+    } else {
+        // ------------------------------------------------------------ epilogue warps
+        const int quarter = warp & 3;                  // the TMEM lanes this warp may read: [32 * quarter, +32)
+        const int part = (warp - 2) / 4;               // fp8: which half of the columns
+        constexpr int kCols = kFp8 ? BN / 2 : BN;      // columns per thread
+        Scheduler sched(p, BN);
+        Tile t;
+        int acc = 0;
+        uint32_t acc_ph = 0;
+        bool ok = true;
+        for (int ti = blockIdx.x; ok && sched.get(ti, t); ti += gridDim.x) {
+            const int row = t.m0 + quarter * 32 + lane;
+            const bool row_ok = row < t.m_end && row < p.M;
+            const uint32_t lane_addr = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16);
+            __nv_bfloat16* c_row = p.C + static_cast<int64_t>(row) * p.ldc + t.n0 + part * kCols;
+            if constexpr (!kFp8) {
+                if (!(ok = pipe_wait(pc, tmem_full + acc, acc_ph))) break;
+                tc_fence_after();
+#pragma unroll 1
+                for (int c = 0; c < BN / 32; ++c) {
+                    uint32_t r[32];
+                    tmem_ld_32x32(lane_addr + acc * BN + c * 32, r);
+                    tmem_ld_wait();
+                    if (row_ok) {
+#pragma unroll
+                        for (int v = 0; v < 4; ++v) {
+                            int4 out;
+                            __nv_bfloat162* o2 = reinterpret_cast<__nv_bfloat162*>(&out);
+#pragma unroll
+                            for (int i = 0; i < 4; ++i)
+                                o2[i] = __floats2bfloat162_rn(__uint_as_float(r[v * 8 + 2 * i]), __uint_as_float(r[v * 8 + 2 * i + 1]));
+                            *reinterpret_cast<int4*>(c_row + c * 32 + v * 8) = out;
+                        }
+                    }
+                }
+                tc_fence_before();
+                mbar_arrive(tmem_empty + acc);
+                acc ^= 1;
+                if (acc == 0) acc_ph ^= 1;
+            } else {
+                float sum[kCols];
+#pragma unroll
+                for (int i = 0; i < kCols; ++i) sum[i] = 0.f;
+                const int kblocks_b = p.K / 128;
+                const float* sfb = p.sfb + (static_cast<int64_t>(t.g) * (p.N / 128) + t.n0 / 128) * kblocks_b;
+                const float* sfa = p.sfa + static_cast<int64_t>(row_ok ? row : 0) * p.sfa_row_stride;
+                float next_scale = sfa[0] * sfb[0];
+                for (int kb = 0; kb < num_kb; ++kb) {
+                    const float scale = next_scale;
+                    if (kb + 1 < num_kb) next_scale = sfa[static_cast<int64_t>(kb + 1) * p.sfa_k_stride] * sfb[kb + 1];
+                    if (!(ok = pipe_wait(pc, tmem_full + acc, acc_ph))) break;
+                    tc_fence_after();
+#pragma unroll
+                    for (int c = 0; c < kCols / 32; ++c) {
+                        uint32_t r[32];
+                        tmem_ld_32x32(lane_addr + acc * BN + part * kCols + c * 32, r);
+                        tmem_ld_wait();
+#pragma unroll
+                        for (int i = 0; i < 32; ++i) sum[c * 32 + i] = fmaf(scale, __uint_as_float(r[i]), sum[c * 32 + i]);
+                    }
+                    tc_fence_before();
+                    mbar_arrive(tmem_empty + acc);
+                    acc ^= 1;
+                    if (acc == 0) acc_ph ^= 1;
+                }
+                if (ok && row_ok) {
+#pragma unroll
+                    for (int v = 0; v < kCols / 8; ++v) {
+                        int4 out;
+                        __nv_bfloat162* o2 = reinterpret_cast<__nv_bfloat162*>(&out);
+#pragma unroll
+                        for (int i = 0; i < 4; ++i) o2[i] = __floats2bfloat162_rn(sum[v * 8 + 2 * i], sum[v * 8 + 2 * i + 1]);
+                        *reinterpret_cast<int4*>(c_row + v * 8) = out;
+                    }
+                }
+            }
+        }
+    }
+
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 1) {
+        tc_fence_after();
+        tmem_dealloc(tmem_base, C::kTmemCols);
+    }
+}
+
+// ---------------------------------------------------------------- host side
+using EncodeFn = CUresult (*)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
+                              const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                              CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeFn get_encode_fn() {
+    static EncodeFn fn = nullptr;
+    if (fn == nullptr) {
+        void* ptr = nullptr;
+        cudaDriverEntryPointQueryResult res;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &ptr, cudaEnableDefault, &res) == cudaSuccess &&
+            res == cudaDriverEntryPointSuccess)
+            fn = reinterpret_cast<EncodeFn>(ptr);
+    }
+    return fn;
+}
+
+}  // namespace
+
+// 2-D K-major tensor map: `rows` x `cols` elements of `elem_bytes`, row pitch `row_stride_bytes`,
+// box = `box_rows` x (128 / elem_bytes) elements, 128-byte swizzle.
+bool make_kmajor_map(CUtensorMap* map, const void* base, int elem_bytes, uint64_t rows, uint64_t cols, uint64_t row_stride_bytes,
+                     uint32_t box_rows) {
+    EncodeFn encode = get_encode_fn();
+    if (encode == nullptr) return false;
+    const cuuint64_t dims[2] = {cols, rows};
+    const cuuint64_t strides[1] = {row_stride_bytes};
+    const cuuint32_t box[2] = {static_cast<cuuint32_t>(128 / elem_bytes), box_rows};
+    const cuuint32_t elem_strides[2] = {1, 1};
+    const CUtensorMapDataType dtype = elem_bytes == 2 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_UINT8;
+    return encode(map, dtype, 2, const_cast<void*>(base), dims, strides, box, elem_strides, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                  CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
+template <int BN, bool kFp8>
+static cudaError_t launch_cfg(const CUtensorMap& map_a, const CUtensorMap& map_b, const GemmParams& p, int num_sms, cudaStream_t stream) {
+    using C = Cfg<BN, kFp8>;
+    cudaError_t err = cudaFuncSetAttribute(gemm_kernel<BN, kFp8>, cudaFuncAttributeMaxDynamicSharedMemorySize, C::kSmem);
+    if (err != cudaSuccess) return err;
+    gemm_kernel<BN, kFp8><<<num_sms, C::kThreads, C::kSmem, stream>>>(map_a, map_b, p);
+    return cudaGetLastError();
+}
+
+cudaError_t launch_gemm(const GemmParams& p, const void* a, int64_t a_row_stride_bytes, const void* b, bool fp8, int num_sms,
+                        cudaStream_t stream) {
+    const int elem = fp8 ? 1 : 2;
+    const int bn = fp8 ? 128 : ((p.N % 256 == 0) ? 256 : 128);
+    const int bk = fp8 ? 128 : 64;
+    if (p.N % bn != 0 || p.K % bk != 0 || p.M <= 0) return cudaErrorInvalidValue;
+    CUtensorMap map_a, map_b;
+    if (!make_kmajor_map(&map_a, a, elem, static_cast<uint64_t>(p.M), static_cast<uint64_t>(p.K), static_cast<uint64_t>(a_row_stride_bytes), BM) ||
+        !make_kmajor_map(&map_b, b, elem, static_cast<uint64_t>(p.num_groups) * p.N, static_cast<uint64_t>(p.K),
+                         static_cast<uint64_t>(p.K) * elem, static_cast<uint32_t>(bn)))
+        return cudaErrorInvalidValue;
+    if (fp8) return launch_cfg<128, true>(map_a, map_b, p, num_sms, stream);
+    if (bn == 256) return launch_cfg<256, false>(map_a, map_b, p, num_sms, stream);
+    return launch_cfg<128, false>(map_a, map_b, p, num_sms, stream);
+}
+
+}  // namespace gemm
+}  // namespace ep

@@ -1,0 +1,99 @@
+// PyTorch-facing wrappers of the compute kernels (tcgen05 GEMM family, and the small hot ops).
+// The reference library has no compute kernels; these exist for the fused MoE layer and the
+// tensor-parallel fused operators built on the same runtime.
+#include <ATen/cuda/CUDAContext.h>
+#include <ATen/ops/empty.h>
+#include <ATen/ops/zeros.h>
+#include <c10/cuda/CUDAGuard.h>
+#include <pybind11/stl.h>
+#include <torch/extension.h>
+
+#include <map>
+#include <optional>
+
+#include "../common/exception.hpp"
+#include "../common/layout.hpp"
+#include "../kernels/gemm_api.hpp"
+
+namespace py = pybind11;
+
+namespace ep {
+
+namespace {
+
+// one status word per device for the GEMM pipelines (0 = healthy)
+at::Tensor& gemm_status(int device) {
+    static std::map<int, at::Tensor> words;
+    auto it = words.find(device);
+    if (it == words.end())
+        it = words.emplace(device, at::zeros({1}, at::TensorOptions().dtype(at::kInt).device(at::Device(at::kCUDA, static_cast<c10::DeviceIndex>(device))))).first;
+    return it->second;
+}
+
+int gemm_check_status() {
+    int device = 0;
+    CUDA_RUNTIME_CHECK(cudaGetDevice(&device));
+    return gemm_status(device).item<int>();
+}
+
+at::Tensor gemm_impl(const at::Tensor& a, const at::Tensor& b, const std::optional<at::Tensor>& sfa, const std::optional<at::Tensor>& sfb,
+                     const std::optional<at::Tensor>& group_end, int group_alignment, std::optional<at::Tensor> out, int num_sms) {
+    EP_HOST_ASSERT(a.is_cuda() && b.is_cuda() && a.dim() == 2 && a.stride(1) == 1 && b.is_contiguous());
+    const bool fp8 = a.scalar_type() == at::kFloat8_e4m3fn;
+    EP_HOST_ASSERT(fp8 || a.scalar_type() == at::kBFloat16);
+    EP_HOST_ASSERT(b.scalar_type() == a.scalar_type());
+    const bool grouped = b.dim() == 3;
+    EP_HOST_ASSERT(b.dim() == 2 || b.dim() == 3);
+    const int G = grouped ? static_cast<int>(b.size(0)) : 1;
+    const int N = static_cast<int>(b.size(grouped ? 1 : 0)), K = static_cast<int>(b.size(grouped ? 2 : 1));
+    const int M = static_cast<int>(a.size(0));
+    EP_HOST_ASSERT(a.size(1) == K);
+    const int elem = fp8 ? 1 : 2;
+    EP_HOST_ASSERT((a.stride(0) * elem) % 16 == 0 && reinterpret_cast<uintptr_t>(a.data_ptr()) % 16 == 0);
+    EP_HOST_ASSERT_MSG(N % 128 == 0 && K % (fp8 ? 128 : 64) == 0, "N must be a multiple of 128 and K of 64 (bf16) / 128 (fp8)");
+    const int device = a.get_device();
+    c10::cuda::CUDAGuard guard(static_cast<c10::DeviceIndex>(device));
+    if (!out.has_value()) out = at::empty({M, N}, a.options().dtype(at::kBFloat16));
+    EP_HOST_ASSERT(out->scalar_type() == at::kBFloat16 && out->size(0) == M && out->size(1) == N && out->stride(1) == 1 &&
+                   (out->stride(0) * 2) % 16 == 0);
+    if (M == 0) return *out;
+
+    gemm::GemmParams p = {};
+    p.M = M;
+    p.N = N;
+    p.K = K;
+    p.num_groups = G;
+    p.group_end = nullptr;
+    p.group_alignment = std::max(group_alignment, 1);
+    if (grouped) {
+        EP_HOST_ASSERT(group_end.has_value() && group_end->scalar_type() == at::kInt && group_end->is_contiguous() && group_end->numel() >= G);
+        p.group_end = group_end->data_ptr<int>();
+    }
+    p.C = reinterpret_cast<__nv_bfloat16*>(out->data_ptr());
+    p.ldc = out->stride(0);
+    if (fp8) {
+        EP_HOST_ASSERT(sfa.has_value() && sfb.has_value() && sfa->scalar_type() == at::kFloat && sfb->scalar_type() == at::kFloat);
+        EP_HOST_ASSERT(sfa->dim() == 2 && sfa->size(0) == M && sfa->size(1) == K / 128);
+        EP_HOST_ASSERT(sfb->is_contiguous() && sfb->numel() == static_cast<int64_t>(G) * (N / 128) * (K / 128));
+        p.sfa = sfa->data_ptr<float>();
+        p.sfa_row_stride = sfa->stride(0);
+        p.sfa_k_stride = sfa->stride(1);
+        p.sfb = sfb->data_ptr<float>();
+    }
+    p.error = gemm_status(device).data_ptr<int>();
+    p.timeout_ns = 10ull * 1000 * 1000 * 1000;
+    const int sms = num_sms > 0 ? num_sms : at::cuda::getCurrentDeviceProperties()->multiProcessorCount;
+    CUDA_RUNTIME_CHECK(gemm::launch_gemm(p, a.data_ptr(), a.stride(0) * elem, b.data_ptr(), fp8, sms, at::cuda::getCurrentCUDAStream().stream()));
+    return *out;
+}
+
+}  // namespace
+
+void register_ops_bindings(py::module_& m) {
+    m.def("gemm", &gemm_impl, py::arg("a"), py::arg("b"), py::arg("sfa") = py::none(), py::arg("sfb") = py::none(),
+          py::arg("group_end") = py::none(), py::arg("group_alignment") = 1, py::arg("out") = py::none(), py::arg("num_sms") = 0,
+          "C = A @ B^T on the tcgen05 tensor cores (bf16, or e4m3 with 1x128 / 128x128 block scales); 3-D B = grouped");
+    m.def("gemm_check_status", &gemm_check_status);
+}
+
+}  // namespace ep

@@ -1,0 +1,77 @@
+"""tcgen05 GEMM family against plain PyTorch fp32 references: bf16, grouped bf16 (expert-major
+row segments with alignment gaps), and e4m3 with 1x128 / 128x128 block scales."""
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+
+def _rel_err(got, ref):
+    return ((got.float() - ref.float()).norm() / ref.float().norm().clamp(min=1e-6)).item()
+
+
+@pytest.mark.parametrize('M,N,K', [(128, 128, 64), (256, 256, 512), (1000, 384, 1024), (4096, 2304, 7168)])
+def test_gemm_bf16(M, N, K):
+    import deepep_b200
+    g = torch.Generator(device='cuda').manual_seed(0)
+    a = torch.randn((M, K), device='cuda', generator=g).bfloat16()
+    b = (torch.randn((N, K), device='cuda', generator=g) * 0.05).bfloat16()
+    out = deepep_b200._C.gemm(a, b)
+    torch.cuda.synchronize()
+    assert deepep_b200._C.gemm_check_status() == 0
+    ref = a.float() @ b.float().t()
+    assert _rel_err(out, ref) < 1e-2
+
+
+def test_grouped_gemm_bf16_with_gaps():
+    import deepep_b200
+    G, N, K, align = 4, 256, 512, 128
+    counts = [200, 0, 130, 57]
+    g = torch.Generator(device='cuda').manual_seed(1)
+    ends, start = [], 0
+    for c in counts:
+        ends.append(start + c)
+        start = -(-(start + c) // align) * align
+    M = start
+    a = torch.randn((M, K), device='cuda', generator=g).bfloat16()
+    b = (torch.randn((G, N, K), device='cuda', generator=g) * 0.05).bfloat16()
+    out = torch.full((M, N), 7.0, device='cuda', dtype=torch.bfloat16)
+    deepep_b200._C.gemm(a, b, group_end=torch.tensor(ends, dtype=torch.int32, device='cuda'), group_alignment=align, out=out)
+    torch.cuda.synchronize()
+    assert deepep_b200._C.gemm_check_status() == 0
+    start = 0
+    for gi, c in enumerate(counts):
+        ref = a[start:start + c].float() @ b[gi].float().t()
+        if c:
+            assert _rel_err(out[start:start + c], ref) < 1e-2
+        nxt = -(-(start + c) // align) * align
+        assert bool((out[start + c:nxt] == 7.0).all())      # alignment gaps are not written
+        start = nxt
+
+
+@pytest.mark.parametrize('grouped', [False, True])
+def test_gemm_fp8_block_scaled(grouped):
+    import deepep_b200
+    from deepep_b200.utils.math import per_token_cast_back, per_token_cast_to_fp8
+    G, M, N, K = (3 if grouped else 1), 384, 256, 1024
+    g = torch.Generator(device='cuda').manual_seed(2)
+    a = torch.randn((M, K), device='cuda', generator=g).bfloat16()
+    aq, sfa = per_token_cast_to_fp8(a)
+    w = torch.randn((G, N, K), device='cuda', generator=g) * 0.05
+    # 128x128 block quantisation of the weights
+    wb = w.view(G, N // 128, 128, K // 128, 128)
+    amax = wb.abs().amax(dim=(2, 4)).clamp(1e-4)
+    sfb = (amax / 448.0).contiguous()
+    wq = (wb / sfb[:, :, None, :, None]).clamp(-448, 448).to(torch.float8_e4m3fn).view(G, N, K)
+    w_deq = (wq.float().view(G, N // 128, 128, K // 128, 128) * sfb[:, :, None, :, None]).view(G, N, K)
+    a_deq = per_token_cast_back(aq, sfa).float()
+    if grouped:
+        ends = torch.tensor([128, 256, 384], dtype=torch.int32, device='cuda')
+        out = deepep_b200._C.gemm(aq, wq, sfa=sfa, sfb=sfb, group_end=ends, group_alignment=128)
+        ref = torch.cat([a_deq[i * 128:(i + 1) * 128] @ w_deq[i].t() for i in range(3)])
+    else:
+        out = deepep_b200._C.gemm(aq, wq[0], sfa=sfa, sfb=sfb)
+        ref = a_deq @ w_deq[0].t()
+    torch.cuda.synchronize()
+    assert deepep_b200._C.gemm_check_status() == 0
+    assert _rel_err(out, ref) < 1e-2
