@@ -70,7 +70,10 @@ constexpr size_t kWsScratchInts = static_cast<size_t>(kMaxBlocks) * (kMaxRanks +
 // [kMaxRanks] rank mask, [4] blocks-done counters of the four phases
 constexpr size_t kWsLLOffsetBytes = kWsScratch * 8 + kWsScratchInts * 4;
 constexpr size_t kWsLLInts = 2 * kMaxExperts + kMaxRanks + 4;
-constexpr size_t kWsBytes = kWsLLOffsetBytes + kWsLLInts * 4 + 4096;
+// tensor-parallel fused operators (int32): [64 chunks][kMaxRanks] rows-landed counters of the all-gather push
+constexpr size_t kWsTpOffsetBytes = kWsLLOffsetBytes + kWsLLInts * 4;
+constexpr size_t kWsTpInts = 64 * kMaxRanks;
+constexpr size_t kWsBytes = kWsTpOffsetBytes + kWsTpInts * 4 + 4096;
 
 // ---------------------------------------------------------------- control area of the symmetric heap, in uint64 words
 constexpr size_t kCtlBarrier = 0;                                        // [kMaxRanks]

@@ -1,0 +1,513 @@
+// Tensor-parallel GEMMs fused with their collective, one kernel each (bf16, sm_100a):
+//
+//   all-gather -> GEMM    C[R*Ml, N] = gather_r(A_r[Ml, K]) * B[N, K]^T
+//       A few "comm" CTAs push this rank's shard, 128-row chunk by chunk, into every peer's gather
+//       buffer with bulk copies over NVLink and raise one flag per (source, chunk) at the peer.
+//       The other CTAs run the tcgen05 main loop; the TMA producer of a tile waits (bounded) for
+//       the flag of the chunk it is about to read, so the math on early chunks overlaps the
+//       transfer of late ones. Own rows are read straight from the input and go first.
+//       All TMA loads read LOCAL memory (the input or the local gather buffer); none is multicast.
+//
+//   GEMM -> reduce-scatter    out[Ml, N] = sum_r (A_r[R*Ml, Kl] * B_r[N, Kl]^T)[rows of this rank]
+//       Tiles are computed destination by destination (next rank first, own rows last). The
+//       epilogue converts the accumulator to bf16, stages it in shared memory and bulk-stores it
+//       into slot [this rank] of the destination's partial buffer, then raises a per-tile flag
+//       there. After its GEMM tiles a CTA turns to the reduction of this rank's own tiles: it waits
+//       for the flags of all sources and sums the partials in fp32 in rank order.
+//
+// The reference has neither operator (its AGRS path is a copy-engine all-gather only, and
+// reduce-scatter is listed as not implemented); the baseline to beat is NCCL all-gather /
+// reduce-scatter followed / preceded by an unfused GEMM.
+#include "gemm_api.hpp"
+#include "gemm_sm100.cuh"
+#include "tp_api.hpp"
+
+namespace ep {
+namespace gemm {
+
+namespace {
+
+constexpr int BN = 256;
+constexpr int BK = 64;
+constexpr int UMMA_K = 16;
+constexpr int A_BYTES = BM * 128, B_BYTES = BN * 128, STAGE = A_BYTES + B_BYTES;
+
+__device__ __forceinline__ void init_pipeline(uint64_t* full, uint64_t* empty, uint64_t* tmem_full, uint64_t* tmem_empty, int stages,
+                                              int epi_threads) {
+    for (int s = 0; s < stages; ++s) {
+        mbar_init(full + s, 1);
+        mbar_init(empty + s, 1);
+    }
+    for (int a = 0; a < 2; ++a) {
+        mbar_init(tmem_full + a, 1);
+        mbar_init(tmem_empty + a, epi_threads);
+    }
+    fence_mbar_init();
+}
+
+// the MMA warp is the same for both operators: consume stages, accumulate one tile per accumulator
+template <int kStages>
+__device__ __forceinline__ void mma_role(const PipeCtx& pc, uint8_t* smem, uint64_t* full, uint64_t* empty, uint64_t* tmem_full,
+                                         uint64_t* tmem_empty, uint32_t tmem_base, int num_tiles_mine, int num_kb) {
+    constexpr uint32_t idesc = make_idesc<false>(BM, BN);
+    int s = 0, acc = 0;
+    uint32_t ph = 0, acc_ph = 0;
+    for (int i = 0; i < num_tiles_mine; ++i) {
+        if (!pipe_wait(pc, tmem_empty + acc, acc_ph ^ 1)) return;
+        tc_fence_after();
+        for (int kb = 0; kb < num_kb; ++kb) {
+            if (!pipe_wait(pc, full + s, ph)) return;
+            tc_fence_after();
+            const uint8_t* sa = smem + s * STAGE;
+            const uint64_t da = make_smem_desc(sa), db = make_smem_desc(sa + A_BYTES);
+#pragma unroll
+            for (int k = 0; k < BK / UMMA_K; ++k) umma<false>(tmem_base + acc * BN, da + 2 * k, db + 2 * k, idesc, (kb | k) != 0);
+            umma_commit(empty + s);
+            if (++s == kStages) { s = 0; ph ^= 1; }
+        }
+        umma_commit(tmem_full + acc);
+        acc ^= 1;
+        if (acc == 0) acc_ph ^= 1;
+    }
+}
+
+__device__ __forceinline__ int tiles_of(int total, int first, int stride) {
+    return total > first ? (total - first + stride - 1) / stride : 0;
+}
+
+// ==================================================================== all-gather -> GEMM
+constexpr int kAgStages = 4;
+constexpr int kAgBarBytes = (2 * kAgStages + 4) * 8 + 16;
+constexpr int kAgSmem = kAgStages * STAGE + kAgBarBytes + 1024;
+constexpr int kAgThreads = 6 * 32;
+
+// one launch may carry several virtual ranks (single-GPU emulation): CTAs [v * ctas_per_rank, ...) act as rank v
+struct AgLaunch {
+    int num_vranks, ctas_per_rank;
+    AgGemmParams p[kTpMaxVRanks];
+    CUtensorMap map_local[kTpMaxVRanks], map_gather[kTpMaxVRanks], map_b[kTpMaxVRanks];
+};
+struct RsLaunch {
+    int num_vranks, ctas_per_rank;
+    GemmRsParams p[kTpMaxVRanks];
+    CUtensorMap map_a[kTpMaxVRanks], map_b[kTpMaxVRanks];
+};
+
+__global__ void __launch_bounds__(kAgThreads, 1) ag_gemm_kernel(const __grid_constant__ AgLaunch L) {
+    const int vr = blockIdx.x / L.ctas_per_rank;
+    const int bid = blockIdx.x % L.ctas_per_rank, nctas = L.ctas_per_rank;
+    const AgGemmParams& p = L.p[vr];
+    const CUtensorMap& map_local = L.map_local[vr];
+    const CUtensorMap& map_gather = L.map_gather[vr];
+    const CUtensorMap& map_b = L.map_b[vr];
+    extern __shared__ uint8_t smem_raw[];
+    uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~static_cast<uintptr_t>(1023));
+    const int warp = warp_id(), lane = lane_id();
+    const CommCtx& c = p.c;
+    const int R = c.num_ranks, Ml = p.rows_per_rank, K = p.K;
+    const int chunks = Ml / BM;
+    const WaitCtx w = make_wait_ctx(c);
+
+    if (bid < p.num_comm_ctas) {
+        // ------------------------------------------------------------ comm CTAs: push the local shard to every peer
+        // unit = (chunk, peer, row): one warp moves one row (K * 2 bytes) through its shared-memory buffer
+        const int row_bytes = K * 2;
+        const int stage = align_up(row_bytes, 128) + 16;
+        uint8_t* buf = smem + static_cast<size_t>(warp) * stage;
+        uint64_t* bar = reinterpret_cast<uint64_t*>(buf + align_up(row_bytes, 128));
+        if (lane == 0) {
+            mbar_init(bar, 1);
+            fence_mbar_init();
+        }
+        __syncwarp();
+        int* done = reinterpret_cast<int*>(reinterpret_cast<uint8_t*>(c.local_ws) + kWsTpOffsetBytes);   // [chunks][R] rows landed, reset by the flag sender
+        // Entry handshake: a peer's gather buffer half may only be overwritten once that peer has entered
+        // this call (and so has finished the call that last read the half).
+        if (warp == 0 && lane < R && lane != c.rank) {
+            uint64_t* remote = reinterpret_cast<uint64_t*>(c.heap[lane]) + kCtlTileFlags + c.rank * 64 + 63;
+            if (bid == 0) st_release_sys_u64(remote, pack_epoch(p.epoch, 0));
+            const uint64_t* mine_flag = reinterpret_cast<const uint64_t*>(c.heap[c.rank]) + kCtlTileFlags + lane * 64 + 63;
+            if (!bounded_wait(w, kStatusTileFlag, lane, 63, [&]() { return epoch_reached(ld_acquire_sys_u64(mine_flag), p.epoch); }))
+                atomicExch(p.error, static_cast<int>(kStatusTileFlag));
+        }
+        __syncthreads();
+        const int num_warps = kAgThreads / 32;
+        const int workers = p.num_comm_ctas * num_warps;
+        const int me = bid * num_warps + warp;
+        uint32_t parity = 0;
+        // Two buffers per warp: the store of row i is in flight while row i+1 is loaded. A row is
+        // counted as landed one step late, once wait_group has confirmed its store.
+        auto landed_row = [&](int chunk) {
+            fence_proxy_async_all();
+            __threadfence_system();
+            const int old = atomicAdd(done + chunk * kMaxRanks + lane, 1);
+            if (old == BM - 1) {
+                done[chunk * kMaxRanks + lane] = 0;
+                __threadfence_system();
+                uint64_t* flag = reinterpret_cast<uint64_t*>(c.heap[lane]) + kCtlTileFlags + c.rank * 64 + chunk;
+                st_release_sys_u64(flag, pack_epoch(p.epoch, 1));
+            }
+        };
+        const bool sender = lane < R && lane != c.rank;
+        uint8_t* buf2[2] = {buf, buf + num_warps * stage};
+        int prev_chunk = -1, it = 0;
+        for (int row = me; row < Ml && R > 1; row += workers, ++it) {
+            uint8_t* cur = buf2[it & 1];
+            if (lane == 0) {
+                mbar_arrive_expect_tx(bar, row_bytes);
+                bulk_g2s(cur, p.a_local + static_cast<int64_t>(row) * p.a_stride_bytes, row_bytes, bar);
+            }
+            const bool landed = mbar_wait(w, bar, parity, kStatusTmaLoad, row);
+            parity ^= 1;
+            if (!__all_sync(0xffffffffu, landed)) break;
+            if (sender) {
+                bulk_s2g(c.heap[lane] + p.off_gather + (static_cast<uint64_t>(c.rank) * Ml + row) * row_bytes, cur, row_bytes);
+                bulk_commit();
+                bulk_wait<1>();                      // the previous row's store is complete (and its buffer free)
+                if (prev_chunk >= 0) landed_row(prev_chunk);
+                prev_chunk = row / BM;
+            }
+            __syncwarp();
+        }
+        if (sender) {
+            bulk_wait_all();
+            if (prev_chunk >= 0) landed_row(prev_chunk);
+        }
+        bulk_wait_all();
+        return;
+    }
+
+    // ---------------------------------------------------------------- GEMM CTAs
+    uint64_t* full = reinterpret_cast<uint64_t*>(smem + kAgStages * STAGE);
+    uint64_t* empty = full + kAgStages;
+    uint64_t* tmem_full = empty + kAgStages;
+    uint64_t* tmem_empty = tmem_full + 2;
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(tmem_empty + 2);
+    PipeCtx pc{p.error, globaltimer_ns() + c.timeout_ns};
+    const int num_kb = K / BK;
+    const int tiles_n = p.N / BN;
+    const int total_tiles = R * chunks * tiles_n;
+    const int first = bid - p.num_comm_ctas, stride = nctas - p.num_comm_ctas;
+    const int mine = tiles_of(total_tiles, first, stride);
+
+    if (warp == 0 && lane == 0) {
+        prefetch_tensormap(&map_local);
+        prefetch_tensormap(&map_gather);
+        prefetch_tensormap(&map_b);
+        init_pipeline(full, empty, tmem_full, tmem_empty, kAgStages, 4 * 32);
+    }
+    if (warp == 1) {
+        tmem_alloc(tmem_slot, 2 * BN);
+        tmem_relinquish();
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem_base = *tmem_slot;
+
+    // tile t -> (order index o, n block): o walks own rows first, then chunk by chunk over the sources rank+1, rank+2, ...
+    auto decode = [&](int t, int& src, int& chunk, int& n0) {
+        const int o = t / tiles_n;
+        n0 = (t % tiles_n) * BN;
+        if (o < chunks) {
+            src = c.rank;
+            chunk = o;
+        } else {
+            const int q = o - chunks;
+            chunk = q / (R - 1);
+            src = (c.rank + 1 + q % (R - 1)) % R;
+        }
+    };
+
+    if (warp == 0) {
+        if (lane == 0) {
+            int s = 0;
+            uint32_t ph = 0;
+            bool ok = true;
+            for (int t = first; ok && t < total_tiles; t += stride) {
+                int src, chunk, n0;
+                decode(t, src, chunk, n0);
+                if (src != c.rank) {
+                    const uint64_t* flag = reinterpret_cast<const uint64_t*>(c.heap[c.rank]) + kCtlTileFlags + src * 64 + chunk;
+                    ok = bounded_wait(w, kStatusTileFlag, src, chunk, [&]() { return epoch_reached(ld_acquire_sys_u64(flag), p.epoch); });
+                    if (!ok) {
+                        atomicExch(p.error, static_cast<int>(kStatusTileFlag));
+                        break;
+                    }
+                }
+                for (int kb = 0; kb < num_kb; ++kb) {
+                    if (!(ok = pipe_wait(pc, empty + s, ph ^ 1))) break;
+                    uint8_t* sa = smem + s * STAGE;
+                    mbar_arrive_expect_tx(full + s, STAGE);
+                    if (src == c.rank) tma_load_2d(sa, &map_local, kb * BK, chunk * BM, full + s);
+                    else tma_load_2d(sa, &map_gather, kb * BK, src * Ml + chunk * BM, full + s);
+                    tma_load_2d(sa + A_BYTES, &map_b, kb * BK, n0, full + s);
+                    if (++s == kAgStages) { s = 0; ph ^= 1; }
+                }
+            }
+        }
+    } else if (warp == 1) {
+        if (lane == 0) mma_role<kAgStages>(pc, smem, full, empty, tmem_full, tmem_empty, tmem_base, mine, num_kb);
+    } else {
+        const int quarter = warp & 3;
+        int acc = 0;
+        uint32_t acc_ph = 0;
+        for (int t = first; t < total_tiles; t += stride) {
+            int src, chunk, n0;
+            decode(t, src, chunk, n0);
+            const int row = src * Ml + chunk * BM + quarter * 32 + lane;
+            if (!pipe_wait(pc, tmem_full + acc, acc_ph)) break;
+            tc_fence_after();
+            __nv_bfloat16* c_row = p.C + static_cast<int64_t>(row) * p.ldc + n0;
+#pragma unroll 1
+            for (int cc = 0; cc < BN / 32; ++cc) {
+                uint32_t r[32];
+                tmem_ld_32x32(tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + acc * BN + cc * 32, r);
+                tmem_ld_wait();
+#pragma unroll
+                for (int v = 0; v < 4; ++v) {
+                    int4 out;
+                    __nv_bfloat162* o2 = reinterpret_cast<__nv_bfloat162*>(&out);
+#pragma unroll
+                    for (int i = 0; i < 4; ++i)
+                        o2[i] = __floats2bfloat162_rn(__uint_as_float(r[v * 8 + 2 * i]), __uint_as_float(r[v * 8 + 2 * i + 1]));
+                    *reinterpret_cast<int4*>(c_row + cc * 32 + v * 8) = out;
+                }
+            }
+            tc_fence_before();
+            mbar_arrive(tmem_empty + acc);
+            acc ^= 1;
+            if (acc == 0) acc_ph ^= 1;
+        }
+    }
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 1) {
+        tc_fence_after();
+        tmem_dealloc(tmem_base, 2 * BN);
+    }
+}
+
+// ==================================================================== GEMM -> reduce-scatter
+constexpr int kRsStages = 3;
+constexpr int kRsRowPitch = BN * 2 + 16;                       // padded rows: lanes of a warp fall into different banks
+constexpr int kRsStageTile = BM * kRsRowPitch;                 // bf16 staging tile of the epilogue
+constexpr int kRsBarBytes = (2 * kRsStages + 4) * 8 + 16;
+constexpr int kRsSmem = kRsStages * STAGE + kRsStageTile + kRsBarBytes + 1024;
+constexpr int kRsThreads = 6 * 32;
+
+__global__ void __launch_bounds__(kRsThreads, 1) gemm_rs_kernel(const __grid_constant__ RsLaunch L) {
+    const int vr = blockIdx.x / L.ctas_per_rank;
+    const int bid = blockIdx.x % L.ctas_per_rank, nctas = L.ctas_per_rank;
+    const GemmRsParams& p = L.p[vr];
+    const CUtensorMap& map_a = L.map_a[vr];
+    const CUtensorMap& map_b = L.map_b[vr];
+    extern __shared__ uint8_t smem_raw[];
+    uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~static_cast<uintptr_t>(1023));
+    uint8_t* stage_tile = smem + kRsStages * STAGE;
+    uint64_t* full = reinterpret_cast<uint64_t*>(stage_tile + kRsStageTile);
+    uint64_t* empty = full + kRsStages;
+    uint64_t* tmem_full = empty + kRsStages;
+    uint64_t* tmem_empty = tmem_full + 2;
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(tmem_empty + 2);
+    const int warp = warp_id(), lane = lane_id();
+    const CommCtx& c = p.c;
+    const int R = c.num_ranks, Ml = p.rows_per_rank, N = p.N;
+    const int chunks = Ml / BM, tiles_n = N / BN;
+    const int tiles_per_dst = chunks * tiles_n;
+    const int total_tiles = R * tiles_per_dst;
+    const int num_kb = p.K / BK;
+    const WaitCtx w = make_wait_ctx(c);
+    PipeCtx pc{p.error, globaltimer_ns() + c.timeout_ns};
+    const int first = bid, stride = nctas;
+    const int mine = tiles_of(total_tiles, first, stride);
+    const int half = p.epoch & 1;
+    const uint64_t part_off = p.off_partial[half], flag_off = p.off_flags[half];
+
+    if (warp == 0 && lane == 0) {
+        prefetch_tensormap(&map_a);
+        prefetch_tensormap(&map_b);
+        init_pipeline(full, empty, tmem_full, tmem_empty, kRsStages, 4 * 32);
+    }
+    if (warp == 1) {
+        tmem_alloc(tmem_slot, 2 * BN);
+        tmem_relinquish();
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem_base = *tmem_slot;
+
+    // tile t -> destination (next rank first, own rows last), tile index inside the destination's chunk
+    auto decode = [&](int t, int& dst, int& local_tile) {
+        dst = (c.rank + 1 + t / tiles_per_dst) % R;
+        local_tile = t % tiles_per_dst;
+    };
+
+    if (warp == 0) {
+        if (lane == 0) {
+            int s = 0;
+            uint32_t ph = 0;
+            bool ok = true;
+            for (int t = first; ok && t < total_tiles; t += stride) {
+                int dst, lt;
+                decode(t, dst, lt);
+                const int m0 = dst * Ml + (lt / tiles_n) * BM, n0 = (lt % tiles_n) * BN;
+                for (int kb = 0; kb < num_kb; ++kb) {
+                    if (!(ok = pipe_wait(pc, empty + s, ph ^ 1))) break;
+                    uint8_t* sa = smem + s * STAGE;
+                    mbar_arrive_expect_tx(full + s, STAGE);
+                    tma_load_2d(sa, &map_a, kb * BK, m0, full + s);
+                    tma_load_2d(sa + A_BYTES, &map_b, kb * BK, n0, full + s);
+                    if (++s == kRsStages) { s = 0; ph ^= 1; }
+                }
+            }
+        }
+    } else if (warp == 1) {
+        if (lane == 0) mma_role<kRsStages>(pc, smem, full, empty, tmem_full, tmem_empty, tmem_base, mine, num_kb);
+    } else {
+        // epilogue: accumulator -> bf16 -> staging tile -> bulk stores into the destination's partial slot -> flag
+        const int quarter = warp & 3;
+        int acc = 0;
+        uint32_t acc_ph = 0;
+        for (int t = first; t < total_tiles; t += stride) {
+            int dst, lt;
+            decode(t, dst, lt);
+            const int local_m0 = (lt / tiles_n) * BM, n0 = (lt % tiles_n) * BN;
+            if (!pipe_wait(pc, tmem_full + acc, acc_ph)) break;
+            tc_fence_after();
+            // (the previous tile's bulk store of this lane has completed: it is waited for right after it is issued)
+            const int r_in_tile = quarter * 32 + lane;
+            __nv_bfloat16* srow = reinterpret_cast<__nv_bfloat16*>(stage_tile + static_cast<size_t>(r_in_tile) * kRsRowPitch);
+#pragma unroll 1
+            for (int cc = 0; cc < BN / 32; ++cc) {
+                uint32_t r[32];
+                tmem_ld_32x32(tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + acc * BN + cc * 32, r);
+                tmem_ld_wait();
+#pragma unroll
+                for (int v = 0; v < 4; ++v) {
+                    int4 out;
+                    __nv_bfloat162* o2 = reinterpret_cast<__nv_bfloat162*>(&out);
+#pragma unroll
+                    for (int i = 0; i < 4; ++i)
+                        o2[i] = __floats2bfloat162_rn(__uint_as_float(r[v * 8 + 2 * i]), __uint_as_float(r[v * 8 + 2 * i + 1]));
+                    *reinterpret_cast<int4*>(srow + cc * 32 + v * 8) = out;
+                }
+            }
+            tc_fence_before();
+            mbar_arrive(tmem_empty + acc);
+            acc ^= 1;
+            if (acc == 0) acc_ph ^= 1;
+            fence_proxy_async_smem();
+            __syncwarp();
+            uint8_t* dst_base = c.heap[dst] + part_off + ((static_cast<uint64_t>(c.rank) * Ml + local_m0 + r_in_tile) * N + n0) * 2;
+            bulk_s2g(dst_base, srow, BN * 2);
+            bulk_commit();
+            bulk_wait_all();
+            fence_proxy_async_all();
+            __threadfence_system();
+            __syncwarp();
+            // one arrival per epilogue warp on the tile's flag word: the reducer waits for 4 * epoch-tagged arrivals
+            if (lane == 0) {
+                uint64_t* flag = reinterpret_cast<uint64_t*>(c.heap[dst] + flag_off) + static_cast<uint64_t>(c.rank) * tiles_per_dst + lt;
+                red_add_release_sys_u64(flag, 1);
+            }
+        }
+    }
+
+    // ---------------------------------------------------------------- reduction of this rank's own tiles
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 1) {
+        tc_fence_after();
+        tmem_dealloc(tmem_base, 2 * BN);
+    }
+    const uint64_t* my_flags = reinterpret_cast<const uint64_t*>(c.heap[c.rank] + flag_off);
+    const uint8_t* my_part = c.heap[c.rank] + part_off;
+    const uint64_t target = static_cast<uint64_t>(p.flag_target);
+    for (int lt = bid; lt < tiles_per_dst; lt += nctas) {
+        if (threadIdx.x < R) {
+            const uint64_t* flag = my_flags + static_cast<uint64_t>(threadIdx.x) * tiles_per_dst + lt;
+            if (!bounded_wait(w, kStatusTileFlag, threadIdx.x, lt, [&]() { return ld_acquire_sys_u64(flag) >= target; }))
+                atomicExch(p.error, static_cast<int>(kStatusTileFlag));
+        }
+        __syncthreads();
+        const int local_m0 = (lt / tiles_n) * BM, n0 = (lt % tiles_n) * BN;
+        for (int v = threadIdx.x; v < BM * BN / 8; v += blockDim.x) {
+            const int r = v / (BN / 8), cv = v % (BN / 8);
+            float accv[8];
+#pragma unroll
+            for (int i = 0; i < 8; ++i) accv[i] = 0.f;
+            for (int s = 0; s < R; ++s) {
+                const int4 raw = ld_nc_int4(my_part + ((static_cast<uint64_t>(s) * Ml + local_m0 + r) * N + n0 + cv * 8) * 2);
+                const __nv_bfloat162* h2 = reinterpret_cast<const __nv_bfloat162*>(&raw);
+#pragma unroll
+                for (int i = 0; i < 4; ++i) {
+                    const float2 f = __bfloat1622float2(h2[i]);
+                    accv[2 * i] += f.x;
+                    accv[2 * i + 1] += f.y;
+                }
+            }
+            int4 out;
+            __nv_bfloat162* o2 = reinterpret_cast<__nv_bfloat162*>(&out);
+#pragma unroll
+            for (int i = 0; i < 4; ++i) o2[i] = __floats2bfloat162_rn(accv[2 * i], accv[2 * i + 1]);
+            *reinterpret_cast<int4*>(p.out + (static_cast<int64_t>(local_m0 + r) * p.ldo + n0 + cv * 8)) = out;
+        }
+        __syncthreads();
+    }
+}
+
+}  // namespace
+
+static cudaError_t coop(const void* fn, void* arg, int grid, int block, int smem, cudaStream_t stream) {
+    void* args[] = {arg};
+    return cudaLaunchCooperativeKernel(fn, dim3(grid), dim3(block), args, smem, stream);
+}
+
+cudaError_t launch_ag_gemm(const AgGemmParams* params, const void* const* b, const void* const* gather_base, int num_vranks,
+                           int ctas_per_rank, cudaStream_t stream) {
+    if (num_vranks < 1 || num_vranks > kTpMaxVRanks) return cudaErrorInvalidValue;
+    AgLaunch L;
+    L.num_vranks = num_vranks;
+    L.ctas_per_rank = ctas_per_rank;
+    for (int v = 0; v < num_vranks; ++v) {
+        const AgGemmParams& p = params[v];
+        const int R = p.c.num_ranks;
+        if (p.N % BN != 0 || p.K % BK != 0 || p.rows_per_rank % BM != 0 || p.rows_per_rank / BM > 63) return cudaErrorInvalidValue;
+        if (p.num_comm_ctas >= ctas_per_rank) return cudaErrorInvalidValue;
+        // the comm warps stage two rows (K * 2 bytes) each
+        if (2 * 6 * (align_up(p.K * 2, 128) + 16) > kAgSmem - 1024) return cudaErrorInvalidValue;
+        L.p[v] = p;
+        if (!make_kmajor_map(&L.map_local[v], p.a_local, 2, p.rows_per_rank, p.K, p.a_stride_bytes, BM) ||
+            !make_kmajor_map(&L.map_gather[v], gather_base[v], 2, static_cast<uint64_t>(R) * p.rows_per_rank, p.K, static_cast<uint64_t>(p.K) * 2, BM) ||
+            !make_kmajor_map(&L.map_b[v], b[v], 2, p.N, p.K, static_cast<uint64_t>(p.K) * 2, BN))
+            return cudaErrorInvalidValue;
+    }
+    cudaError_t err = cudaFuncSetAttribute(ag_gemm_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kAgSmem);
+    if (err != cudaSuccess) return err;
+    return coop(reinterpret_cast<const void*>(ag_gemm_kernel), &L, num_vranks * ctas_per_rank, kAgThreads, kAgSmem, stream);
+}
+
+cudaError_t launch_gemm_rs(const GemmRsParams* params, const void* const* a, const int64_t* a_stride_bytes, const void* const* b,
+                           int num_vranks, int ctas_per_rank, cudaStream_t stream) {
+    if (num_vranks < 1 || num_vranks > kTpMaxVRanks) return cudaErrorInvalidValue;
+    RsLaunch L;
+    L.num_vranks = num_vranks;
+    L.ctas_per_rank = ctas_per_rank;
+    for (int v = 0; v < num_vranks; ++v) {
+        const GemmRsParams& p = params[v];
+        const int R = p.c.num_ranks;
+        if (p.N % BN != 0 || p.K % BK != 0 || p.rows_per_rank % BM != 0) return cudaErrorInvalidValue;
+        L.p[v] = p;
+        if (!make_kmajor_map(&L.map_a[v], a[v], 2, static_cast<uint64_t>(R) * p.rows_per_rank, p.K, a_stride_bytes[v], BM) ||
+            !make_kmajor_map(&L.map_b[v], b[v], 2, p.N, p.K, static_cast<uint64_t>(p.K) * 2, BN))
+            return cudaErrorInvalidValue;
+    }
+    cudaError_t err = cudaFuncSetAttribute(gemm_rs_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kRsSmem);
+    if (err != cudaSuccess) return err;
+    return coop(reinterpret_cast<const void*>(gemm_rs_kernel), &L, num_vranks * ctas_per_rank, kRsThreads, kRsSmem, stream);
+}
+
+}  // namespace gemm
+}  // namespace ep

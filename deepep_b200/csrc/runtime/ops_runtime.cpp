@@ -14,6 +14,7 @@
 #include "../common/exception.hpp"
 #include "../common/layout.hpp"
 #include "../kernels/gemm_api.hpp"
+#include "../kernels/ops_api.hpp"
 
 namespace py = pybind11;
 
@@ -87,9 +88,90 @@ at::Tensor gemm_impl(const at::Tensor& a, const at::Tensor& b, const std::option
     return *out;
 }
 
+cudaStream_t cur_stream() { return at::cuda::getCurrentCUDAStream().stream(); }
+
+std::tuple<at::Tensor, at::Tensor> router_topk(const at::Tensor& logits, int num_topk) {
+    EP_HOST_ASSERT(logits.is_cuda() && logits.dim() == 2 && logits.scalar_type() == at::kFloat && logits.is_contiguous());
+    c10::cuda::CUDAGuard guard(logits.device());
+    const int T = static_cast<int>(logits.size(0)), E = static_cast<int>(logits.size(1));
+    auto idx = at::empty({T, num_topk}, logits.options().dtype(at::kLong));
+    auto w = at::empty({T, num_topk}, logits.options());
+    CUDA_RUNTIME_CHECK(ops::router_topk(logits.data_ptr<float>(), T, E, num_topk, idx.data_ptr<int64_t>(), w.data_ptr<float>(), cur_stream()));
+    return {idx, w};
+}
+
+std::tuple<at::Tensor, at::Tensor> quant_1x128(const at::Tensor& x, bool pow2, bool col_major_sf) {
+    EP_HOST_ASSERT(x.is_cuda() && x.dim() == 2 && x.scalar_type() == at::kBFloat16 && x.stride(1) == 1 && (x.stride(0) * 2) % 16 == 0);
+    c10::cuda::CUDAGuard guard(x.device());
+    const int M = static_cast<int>(x.size(0)), H = static_cast<int>(x.size(1));
+    EP_HOST_ASSERT(H % 128 == 0);
+    auto q = at::empty({M, H}, x.options().dtype(at::kFloat8_e4m3fn));
+    at::Tensor sf = col_major_sf ? at::empty({H / 128, align_up(std::max(M, 1), 4)}, x.options().dtype(at::kFloat)).t().slice(0, 0, M)
+                                 : at::empty({M, H / 128}, x.options().dtype(at::kFloat));
+    CUDA_RUNTIME_CHECK(ops::quant_1x128(x.data_ptr(), x.stride(0) * 2, M, H, pow2, q.data_ptr(), sf.data_ptr<float>(), sf.stride(0),
+                                        sf.stride(1), cur_stream()));
+    return {q, sf};
+}
+
+at::Tensor dequant_1x128(const at::Tensor& q, const at::Tensor& sf) {
+    EP_HOST_ASSERT(q.is_cuda() && q.dim() == 2 && q.scalar_type() == at::kFloat8_e4m3fn && q.is_contiguous() && sf.scalar_type() == at::kFloat);
+    c10::cuda::CUDAGuard guard(q.device());
+    const int M = static_cast<int>(q.size(0)), H = static_cast<int>(q.size(1));
+    EP_HOST_ASSERT(H % 128 == 0 && sf.size(0) == M && sf.size(1) == H / 128);
+    auto out = at::empty({M, H}, q.options().dtype(at::kBFloat16));
+    CUDA_RUNTIME_CHECK(ops::dequant_1x128(q.data_ptr(), sf.data_ptr<float>(), sf.stride(0), sf.stride(1), M, H, out.data_ptr(), cur_stream()));
+    return out;
+}
+
+// returns (out, scales or None)
+std::tuple<at::Tensor, std::optional<at::Tensor>> swiglu(const at::Tensor& x, const std::optional<at::Tensor>& row_weight,
+                                                          const std::optional<at::Tensor>& num_valid_rows, bool quant) {
+    EP_HOST_ASSERT(x.is_cuda() && x.dim() == 2 && x.scalar_type() == at::kBFloat16 && x.is_contiguous() && x.size(1) % 16 == 0);
+    c10::cuda::CUDAGuard guard(x.device());
+    const int M = static_cast<int>(x.size(0)), I = static_cast<int>(x.size(1) / 2);
+    const float* rw = nullptr;
+    if (row_weight.has_value()) {
+        EP_HOST_ASSERT(row_weight->scalar_type() == at::kFloat && row_weight->is_contiguous() && row_weight->numel() >= M);
+        rw = row_weight->data_ptr<float>();
+    }
+    const int* nv = num_valid_rows.has_value() ? num_valid_rows->data_ptr<int>() : nullptr;
+    at::Tensor out = at::empty({M, I}, x.options().dtype(quant ? at::kFloat8_e4m3fn : at::kBFloat16));
+    std::optional<at::Tensor> sf;
+    if (quant) sf = at::empty({M, I / 128}, x.options().dtype(at::kFloat));
+    CUDA_RUNTIME_CHECK(ops::swiglu(x.data_ptr(), M, I, rw, nv, out.data_ptr(), quant, quant ? sf->data_ptr<float>() : nullptr,
+                                   quant ? sf->stride(0) : 0, quant ? sf->stride(1) : 0, cur_stream()));
+    return {out, sf};
+}
+
+at::Tensor swiglu_backward(const at::Tensor& x, const at::Tensor& dout, const std::optional<at::Tensor>& row_weight) {
+    EP_HOST_ASSERT(x.is_cuda() && x.scalar_type() == at::kBFloat16 && x.is_contiguous() && dout.scalar_type() == at::kBFloat16 && dout.is_contiguous());
+    c10::cuda::CUDAGuard guard(x.device());
+    const int M = static_cast<int>(x.size(0)), I = static_cast<int>(x.size(1) / 2);
+    EP_HOST_ASSERT(dout.size(0) == M && dout.size(1) == I);
+    auto dx = at::empty_like(x);
+    CUDA_RUNTIME_CHECK(ops::swiglu_backward(x.data_ptr(), dout.data_ptr(), M, I, row_weight.has_value() ? row_weight->data_ptr<float>() : nullptr,
+                                            dx.data_ptr(), cur_stream()));
+    return dx;
+}
+
+at::Tensor transpose_bf16(const at::Tensor& x) {
+    EP_HOST_ASSERT(x.is_cuda() && x.dim() == 2 && x.scalar_type() == at::kBFloat16 && x.stride(1) == 1);
+    c10::cuda::CUDAGuard guard(x.device());
+    auto out = at::empty({x.size(1), x.size(0)}, x.options());
+    CUDA_RUNTIME_CHECK(ops::transpose_bf16(x.data_ptr(), x.stride(0), static_cast<int>(x.size(0)), static_cast<int>(x.size(1)), out.data_ptr(),
+                                           out.stride(0), cur_stream()));
+    return out;
+}
+
 }  // namespace
 
 void register_ops_bindings(py::module_& m) {
+    m.def("router_topk", &router_topk);
+    m.def("quant_1x128", &quant_1x128, py::arg("x"), py::arg("pow2") = false, py::arg("col_major_sf") = false);
+    m.def("dequant_1x128", &dequant_1x128);
+    m.def("swiglu", &swiglu, py::arg("x"), py::arg("row_weight") = py::none(), py::arg("num_valid_rows") = py::none(), py::arg("quant") = false);
+    m.def("swiglu_backward", &swiglu_backward, py::arg("x"), py::arg("dout"), py::arg("row_weight") = py::none());
+    m.def("transpose_bf16", &transpose_bf16);
     m.def("gemm", &gemm_impl, py::arg("a"), py::arg("b"), py::arg("sfa") = py::none(), py::arg("sfb") = py::none(),
           py::arg("group_end") = py::none(), py::arg("group_alignment") = 1, py::arg("out") = py::none(), py::arg("num_sms") = 0,
           "C = A @ B^T on the tcgen05 tensor cores (bf16, or e4m3 with 1x128 / 128x128 block scales); 3-D B = grouped");

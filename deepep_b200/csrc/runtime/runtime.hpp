@@ -137,6 +137,9 @@ public:
     // epoch counters are public to the sibling subsystems (low latency, AGRS, PP) that share the heap
     uint32_t barrier_epoch = 0, dispatch_epoch = 0, combine_epoch = 0;
     uint64_t grid_bar_base = 0;
+    // fused tensor-parallel operators
+    uint32_t tp_ag_epoch = 0, tp_rs_epoch = 0;
+    int64_t tp_rs_config = 0;   // (rows_per_rank, N, flag offsets) of the first GEMM->RS call: arrival counters depend on it
     uint64_t* host_words() const { return host_words_; }
     uint64_t* host_words_dev() const { return host_words_dev_; }
     uint64_t* local_ws() const { return local_ws_; }

@@ -32,8 +32,8 @@ public:
         EP_HOST_ASSERT(num_bytes % kHeapAlignment == 0);
         CUDA_RUNTIME_CHECK(cudaGetDevice(&device_));
         CUDA_RUNTIME_CHECK(cudaMalloc(&base_, num_bytes));
-        // control words start at epoch 0; data regions need no initialisation
-        CUDA_RUNTIME_CHECK(cudaMemset(base_, 0, kCtlBytes));
+        // control words start at epoch 0, arrival counters that live in the data regions at zero
+        CUDA_RUNTIME_CHECK(cudaMemset(base_, 0, num_bytes));
         peers_.assign(num_ranks, nullptr);
         peers_[rank] = static_cast<uint8_t*>(base_);
     }

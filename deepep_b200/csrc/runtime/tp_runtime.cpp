@@ -1,0 +1,150 @@
+// Host drivers of the fused tensor-parallel operators (all-gather -> GEMM, GEMM -> reduce-scatter).
+#include <ATen/cuda/CUDAContext.h>
+#include <ATen/ops/empty.h>
+#include <ATen/ops/zeros.h>
+#include <pybind11/stl.h>
+#include <torch/extension.h>
+
+#include "../kernels/tp_api.hpp"
+#include "runtime.hpp"
+
+namespace py = pybind11;
+
+namespace ep {
+
+namespace {
+
+at::Tensor& tp_status(int device) {
+    static std::map<int, at::Tensor> words;
+    auto it = words.find(device);
+    if (it == words.end())
+        it = words.emplace(device, at::zeros({1}, at::TensorOptions().dtype(at::kInt).device(at::Device(at::kCUDA, static_cast<c10::DeviceIndex>(device))))).first;
+    return it->second;
+}
+
+int tp_check_status() {
+    int device = 0;
+    CUDA_RUNTIME_CHECK(cudaGetDevice(&device));
+    return tp_status(device).item<int>();
+}
+
+// C_r[R * Ml, N] = gather(A)[R * Ml, K] * B_r[N, K]^T, one launch for all listed (virtual) ranks.
+// `gather_offsets` = the two halves of the gather buffer inside every heap (bytes from the heap base).
+std::vector<at::Tensor> tp_ag_gemm(const std::vector<std::shared_ptr<Runtime>>& rts, const std::vector<at::Tensor>& a_local,
+                                   const std::vector<at::Tensor>& b, const std::vector<int64_t>& gather_offsets, int num_comm_ctas,
+                                   int num_sms) {
+    const int V = static_cast<int>(rts.size());
+    EP_HOST_ASSERT(V >= 1 && V <= gemm::kTpMaxVRanks && static_cast<int>(a_local.size()) == V && static_cast<int>(b.size()) == V);
+    EP_HOST_ASSERT(gather_offsets.size() == 2);
+    auto& rt0 = *rts[0];
+    const int device = rt0.heap().device();
+    c10::cuda::CUDAGuard guard(static_cast<c10::DeviceIndex>(device));
+    const int R = rt0.num_ranks();
+    const int Ml = static_cast<int>(a_local[0].size(0)), K = static_cast<int>(a_local[0].size(1)), N = static_cast<int>(b[0].size(0));
+    const uint64_t half_bytes = static_cast<uint64_t>(R) * Ml * K * 2;
+    if (num_sms <= 0) num_sms = rt0.num_device_sms() / V;
+    if (num_comm_ctas <= 0) num_comm_ctas = R > 1 ? 16 : 0;
+    if (R == 1) num_comm_ctas = 0;
+    std::vector<gemm::AgGemmParams> params(V);
+    std::vector<const void*> bptr(V), gptr(V);
+    std::vector<at::Tensor> outs(V);
+    for (int v = 0; v < V; ++v) {
+        auto& rt = *rts[v];
+        const auto& a = a_local[v];
+        EP_HOST_ASSERT(a.scalar_type() == at::kBFloat16 && a.dim() == 2 && a.stride(1) == 1 && a.size(0) == Ml && a.size(1) == K);
+        EP_HOST_ASSERT(b[v].scalar_type() == at::kBFloat16 && b[v].is_contiguous() && b[v].size(0) == N && b[v].size(1) == K);
+        EP_HOST_ASSERT((a.stride(0) * 2) % 16 == 0 && reinterpret_cast<uintptr_t>(a.data_ptr()) % 16 == 0);
+        const uint32_t epoch = ++rt.tp_ag_epoch;
+        const uint64_t off = static_cast<uint64_t>(gather_offsets[epoch & 1]);
+        EP_HOST_ASSERT_MSG(off + half_bytes <= rt.heap().num_bytes() && off >= kCtlBytes, "gather buffer does not fit the heap");
+        outs[v] = at::empty({static_cast<int64_t>(R) * Ml, N}, a.options());
+        gemm::AgGemmParams& p = params[v];
+        p.c = rt.ctx();
+        p.rows_per_rank = Ml;
+        p.N = N;
+        p.K = K;
+        p.a_local = static_cast<const uint8_t*>(a.data_ptr());
+        p.a_stride_bytes = a.stride(0) * 2;
+        p.C = reinterpret_cast<__nv_bfloat16*>(outs[v].data_ptr());
+        p.ldc = N;
+        p.off_gather = off;
+        p.epoch = epoch;
+        p.num_comm_ctas = num_comm_ctas;
+        p.error = tp_status(device).data_ptr<int>();
+        bptr[v] = b[v].data_ptr();
+        gptr[v] = rt.heap().base() + off;
+    }
+    CUDA_RUNTIME_CHECK(gemm::launch_ag_gemm(params.data(), bptr.data(), gptr.data(), V, num_sms, at::cuda::getCurrentCUDAStream().stream()));
+    return outs;
+}
+
+// out_r[Ml, N] = sum over ranks of (A_s[R * Ml, Kl] * B_s[N, Kl]^T) restricted to the rows of rank r.
+// `partial_offsets` / `flag_offsets` = the two halves of the partial buffer and of its arrival counters.
+std::vector<at::Tensor> tp_gemm_rs(const std::vector<std::shared_ptr<Runtime>>& rts, const std::vector<at::Tensor>& a,
+                                   const std::vector<at::Tensor>& b, const std::vector<int64_t>& partial_offsets,
+                                   const std::vector<int64_t>& flag_offsets, int num_sms) {
+    const int V = static_cast<int>(rts.size());
+    EP_HOST_ASSERT(V >= 1 && V <= gemm::kTpMaxVRanks && static_cast<int>(a.size()) == V && static_cast<int>(b.size()) == V);
+    EP_HOST_ASSERT(partial_offsets.size() == 2 && flag_offsets.size() == 2);
+    auto& rt0 = *rts[0];
+    const int device = rt0.heap().device();
+    c10::cuda::CUDAGuard guard(static_cast<c10::DeviceIndex>(device));
+    const int R = rt0.num_ranks();
+    const int M = static_cast<int>(a[0].size(0)), K = static_cast<int>(a[0].size(1)), N = static_cast<int>(b[0].size(0));
+    EP_HOST_ASSERT(M % R == 0);
+    const int Ml = M / R;
+    const uint64_t part_bytes = static_cast<uint64_t>(R) * Ml * N * 2;
+    const uint64_t flag_bytes = static_cast<uint64_t>(R) * (Ml / 128) * (N / 256) * 8;
+    if (num_sms <= 0) num_sms = rt0.num_device_sms() / V;
+    std::vector<gemm::GemmRsParams> params(V);
+    std::vector<const void*> aptr(V), bptr(V);
+    std::vector<int64_t> astride(V);
+    std::vector<at::Tensor> outs(V);
+    for (int v = 0; v < V; ++v) {
+        auto& rt = *rts[v];
+        EP_HOST_ASSERT(a[v].scalar_type() == at::kBFloat16 && a[v].dim() == 2 && a[v].stride(1) == 1 && a[v].size(0) == M && a[v].size(1) == K);
+        EP_HOST_ASSERT(b[v].scalar_type() == at::kBFloat16 && b[v].is_contiguous() && b[v].size(0) == N && b[v].size(1) == K);
+        EP_HOST_ASSERT((a[v].stride(0) * 2) % 16 == 0 && reinterpret_cast<uintptr_t>(a[v].data_ptr()) % 16 == 0);
+        // arrival counters only grow, so their meaning is tied to the first configuration used on this heap
+        const int64_t config = (static_cast<int64_t>(Ml) << 40) ^ (static_cast<int64_t>(N) << 20) ^ flag_offsets[0] ^ (flag_offsets[1] << 1);
+        if (rt.tp_rs_config == 0) rt.tp_rs_config = config;
+        EP_HOST_ASSERT_MSG(rt.tp_rs_config == config, "GEMM->reduce-scatter on one buffer must keep its shape and offsets");
+        const uint32_t epoch = ++rt.tp_rs_epoch;
+        gemm::GemmRsParams& p = params[v];
+        p.c = rt.ctx();
+        p.rows_per_rank = Ml;
+        p.N = N;
+        p.K = K;
+        outs[v] = at::empty({Ml, N}, a[v].options());
+        p.out = reinterpret_cast<__nv_bfloat16*>(outs[v].data_ptr());
+        p.ldo = N;
+        for (int h = 0; h < 2; ++h) {
+            p.off_partial[h] = static_cast<uint64_t>(partial_offsets[h]);
+            p.off_flags[h] = static_cast<uint64_t>(flag_offsets[h]);
+            EP_HOST_ASSERT(p.off_partial[h] + part_bytes <= rt.heap().num_bytes() && p.off_flags[h] + flag_bytes <= rt.heap().num_bytes());
+            EP_HOST_ASSERT(p.off_partial[h] >= kCtlBytes && p.off_flags[h] >= kCtlBytes && p.off_partial[h] % 16 == 0 && p.off_flags[h] % 8 == 0);
+        }
+        p.epoch = epoch;
+        p.flag_target = 4 * static_cast<int>((epoch + 1) / 2);   // four epilogue warps arrive per tile and call on this half
+        p.error = tp_status(device).data_ptr<int>();
+        aptr[v] = a[v].data_ptr();
+        bptr[v] = b[v].data_ptr();
+        astride[v] = a[v].stride(0) * 2;
+    }
+    CUDA_RUNTIME_CHECK(gemm::launch_gemm_rs(params.data(), aptr.data(), astride.data(), bptr.data(), V, num_sms,
+                                            at::cuda::getCurrentCUDAStream().stream()));
+    return outs;
+}
+
+}  // namespace
+
+void register_tp_bindings(py::module_& m) {
+    m.def("tp_ag_gemm", &tp_ag_gemm, py::arg("runtimes"), py::arg("a_local"), py::arg("b"), py::arg("gather_offsets"),
+          py::arg("num_comm_ctas") = 0, py::arg("num_sms") = 0);
+    m.def("tp_gemm_rs", &tp_gemm_rs, py::arg("runtimes"), py::arg("a"), py::arg("b"), py::arg("partial_offsets"), py::arg("flag_offsets"),
+          py::arg("num_sms") = 0);
+    m.def("tp_check_status", &tp_check_status);
+    m.attr("TP_MAX_VRANKS") = gemm::kTpMaxVRanks;
+}
+
+}  // namespace ep

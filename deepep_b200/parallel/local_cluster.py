@@ -141,3 +141,23 @@ class SingleProcessGroup:
 
     def size(self) -> int:
         return 1
+
+
+class VirtualRanks:
+    """Bare set of virtual ranks for subsystems that build their own buffers (tensor-parallel contexts,
+    AGRS / PP sessions): hand ``groups[r]`` to the constructor of rank r's object, then call
+    :meth:`connect` with the created buffers to wire their peer tables."""
+
+    def __init__(self, num_ranks: int):
+        self._C = require_native()
+        self.num_ranks = num_ranks
+        self.groups = [LocalGroup(self, r) for r in range(num_ranks)]
+        self._registered = {}
+
+    def _register(self, rank: int, buffer) -> None:
+        self._registered[rank] = buffer
+
+    def connect(self) -> None:
+        buffers = [self._registered[r] for r in range(self.num_ranks)]
+        self._C.Runtime.connect_local([b.runtime for b in buffers])
+        torch.cuda.synchronize()

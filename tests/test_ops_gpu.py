@@ -1,0 +1,52 @@
+"""Small MoE operators against plain PyTorch fp32 references."""
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.mark.parametrize('T,E,K', [(37, 16, 2), (300, 256, 8), (64, 2048, 32)])
+def test_router_topk_softmax(T, E, K):
+    import deepep_b200
+    logits = torch.randn((T, E), device='cuda', generator=torch.Generator(device='cuda').manual_seed(0))
+    idx, w = deepep_b200._C.router_topk(logits, K)
+    vals, ref_idx = torch.topk(logits, K, dim=1, sorted=True)
+    assert torch.equal(idx, ref_idx)
+    assert torch.allclose(w, torch.softmax(vals, dim=1), atol=1e-6, rtol=1e-5)
+
+
+@pytest.mark.parametrize('pow2,col_major', [(False, False), (True, False), (False, True)])
+def test_quant_dequant_1x128(pow2, col_major):
+    import deepep_b200
+    from deepep_b200.utils.math import per_token_cast_back, per_token_cast_to_fp8
+    x = torch.randn((333, 1024), device='cuda', generator=torch.Generator(device='cuda').manual_seed(1)).bfloat16()
+    q, sf = deepep_b200._C.quant_1x128(x, pow2, col_major)
+    rq, rsf = per_token_cast_to_fp8(x, round_scale=pow2)
+    assert torch.equal(q.view(torch.uint8), rq.view(torch.uint8)) and torch.equal(sf, rsf)
+    if col_major:
+        assert sf.stride(0) == 1
+    back = deepep_b200._C.dequant_1x128(q, sf.contiguous())
+    assert torch.equal(back, per_token_cast_back(rq, rsf))
+
+
+def test_swiglu_forward_backward_and_fused_cast():
+    import deepep_b200
+    from deepep_b200.utils.math import per_token_cast_to_fp8
+    C = deepep_b200._C
+    g = torch.Generator(device='cuda').manual_seed(2)
+    M, I = 200, 512
+    x = torch.randn((M, 2 * I), device='cuda', generator=g).bfloat16()
+    rw = torch.rand(M, device='cuda', generator=g)
+    out, _ = C.swiglu(x, rw)
+    xf = x.float().requires_grad_(True)
+    ref = torch.nn.functional.silu(xf[:, :I]) * xf[:, I:] * rw[:, None]
+    assert torch.allclose(out.float(), ref.detach(), rtol=2e-2, atol=2e-2)
+    q, sf = C.swiglu(x, rw, None, True)
+    rq, rsf = per_token_cast_to_fp8(out)
+    assert torch.equal(q.view(torch.uint8), rq.view(torch.uint8)) and torch.equal(sf, rsf)
+    dout = torch.randn((M, I), device='cuda', generator=g).bfloat16()
+    ref.backward(dout.float())
+    dx = C.swiglu_backward(x, dout, rw)
+    assert torch.allclose(dx.float(), xf.grad, rtol=3e-2, atol=3e-2)
+    t = C.transpose_bf16(x)
+    assert torch.equal(t, x.t().contiguous())
