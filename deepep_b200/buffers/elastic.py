@@ -251,6 +251,89 @@ class ElasticBuffer:
     def get_logical_domain_size(self) -> Tuple[int, int]:
         return get_logical_domain_size(self.group, self.allow_hybrid_mode)
 
+    # ------------------------------------------------------------------ Engram / PP / AGRS (experimental in the reference too)
+    def _engram_store(self):
+        if self._engram is None:
+            from ..parallel.engram import EngramStore
+            self._engram = EngramStore(self)
+        return self._engram
+
+    def engram_write(self, storage: torch.Tensor, sf: Optional[torch.Tensor] = None) -> None:
+        """Stores this rank's shard ``[entries_per_rank, hidden]`` (bf16, or e4m3 with the replicated scale
+        table ``sf [total entries, packs]``) in the heap. Barriers before and after."""
+        self._engram_store().write(storage, sf)
+
+    def engram_fetch(self, indices: torch.Tensor, num_qps: int = 0, use_tma_aligned_col_major_sf: bool = False):
+        """Starts fetching the rows ``indices [tokens, entries per token]`` (int32) from their owner ranks and
+        returns a hook; ``hook()`` waits and returns ``(data [tokens * entries, hidden], sf or None)``."""
+        return self._engram_store().fetch(indices, use_tma_aligned_col_major_sf)
+
+    def _pp_ring(self):
+        if self._pp is None:
+            from ..parallel.pp import PipelineRing
+            self._pp = PipelineRing(self)
+        return self._pp
+
+    def pp_set_config(self, num_max_tensor_bytes: int, num_max_inflight_tensors: int):
+        """Sizes the PP slot rings. Includes a barrier to flush earlier operations on the heap."""
+        self.barrier()
+        self._pp_ring().set_config(num_max_tensor_bytes, num_max_inflight_tensors)
+        self.barrier()
+
+    def pp_send(self, t: torch.Tensor, dst_rank_idx: int, num_sms: int = 0) -> None:
+        """Sends ``t`` to the previous or next rank of the ring (copy engine, no SMs)."""
+        self._pp_ring().send(t, dst_rank_idx)
+
+    def pp_recv(self, t: torch.Tensor, src_rank_idx: int, num_sms: int = 0) -> None:
+        """Receives into ``t`` from the previous or next rank of the ring."""
+        self._pp_ring().recv(t, src_rank_idx)
+
+    def _agrs_manager(self):
+        if self._agrs is None:
+            from ..parallel.agrs import AgrsManager
+            self._agrs = AgrsManager(self)
+        return self._agrs
+
+    def create_agrs_session(self) -> None:
+        self._agrs_manager().create_session()
+
+    def destroy_agrs_session(self) -> None:
+        self._agrs_manager().destroy_session()
+
+    def agrs_new_session(self, enabled: bool = True):
+        """Context manager around :meth:`create_agrs_session` / :meth:`destroy_agrs_session`."""
+        from contextlib import contextmanager
+
+        @contextmanager
+        def session():
+            if not enabled:
+                yield
+                return
+            self.create_agrs_session()
+            try:
+                yield
+            finally:
+                self.destroy_agrs_session()
+        return session()
+
+    def agrs_set_config(self, num_max_session_bytes: int, num_max_all_gathers_per_session: int) -> None:
+        self.barrier()
+        self._agrs_manager().set_config(num_max_session_bytes, num_max_all_gathers_per_session)
+        self.barrier()
+
+    def agrs_get_inplace_tensor(self, shapes, dtype: torch.dtype):
+        """Tensor(s) inside this rank's slot of the next all-gather(s) of the open session."""
+        return self._agrs_manager().get_inplace_tensor(shapes, dtype)
+
+    def all_gather(self, t: Union[torch.Tensor, Sequence[torch.Tensor]]):
+        """All-gather inside the open AGRS session: returns ``(gathered [ranks, ...], handle)`` (or
+        ``(*gathered, handle)`` for a sequence); ``handle()`` makes the current stream wait for arrival."""
+        return self._agrs_manager().all_gather(t)
+
+    def reduce_scatter(self, t: torch.Tensor) -> torch.Tensor:
+        """Sum over ranks of ``t`` (bf16 / fp32, leading dim divisible by the ranks), scattered by leading chunk."""
+        return self._agrs_manager().reduce_scatter(t)
+
     # ------------------------------------------------------------------ SM / QP model
     @weak_lru(maxsize=None)
     def get_theoretical_num_sms(self, num_experts: int, num_topk: int, num_scaleout_topk: int = 0, rdma_gbs: float = 0,
