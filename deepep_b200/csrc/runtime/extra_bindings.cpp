@@ -9,6 +9,7 @@ void register_ll_bindings(py::module_& m);
 void register_ops_bindings(py::module_& m);
 void register_tp_bindings(py::module_& m);
 void register_aux_bindings(py::module_& m);
+void register_jit_bindings(py::module_& m);
 }
 
 void register_extra_bindings(py::module_& m) {
@@ -16,4 +17,5 @@ void register_extra_bindings(py::module_& m) {
     ep::register_ops_bindings(m);
     ep::register_tp_bindings(m);
     ep::register_aux_bindings(m);
+    ep::register_jit_bindings(m);
 }
