@@ -54,6 +54,14 @@ __device__ __forceinline__ uint64_t ld_acquire_gpu_u64(const uint64_t* p) {
     asm volatile("ld.acquire.gpu.global.u64 %0, [%1];" : "=l"(v) : "l"(p) : "memory");
     return v;
 }
+__device__ __forceinline__ uint32_t ld_acquire_gpu_u32(const uint32_t* p) {
+    uint32_t v;
+    asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+    return v;
+}
+__device__ __forceinline__ void st_release_gpu_u32(uint32_t* p, uint32_t v) {
+    asm volatile("st.release.gpu.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+}
 __device__ __forceinline__ uint32_t ld_acquire_sys_u32(const uint32_t* p) {
     uint32_t v;
     asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
@@ -241,9 +249,20 @@ __device__ __forceinline__ void fp8_scale_from_amax(float amax, bool round_pow2,
         scale = ldexpf(1.0f, ce);
         inv = ldexpf(1.0f, -ce);
     } else {
-        scale = amax / kFP8Max;
-        inv = kFP8Max / amax;
+        // one correctly rounded reciprocal and two multiplications (the PyTorch restatement in
+        // utils/math.py does exactly the same, so kernel and reference agree bit for bit)
+        scale = amax * (1.0f / kFP8Max);
+        inv = kFP8Max * __frcp_rn(amax);
     }
+}
+
+// max |x| over the eight bf16 values of a 16-byte vector, computed with packed bf16 min/max (exact)
+__device__ __forceinline__ float amax_bf16x8(const int4& raw) {
+    const __nv_bfloat162* h2 = reinterpret_cast<const __nv_bfloat162*>(&raw);
+    __nv_bfloat162 m = __hmax2(__habs2(h2[0]), __habs2(h2[1]));
+    m = __hmax2(m, __hmax2(__habs2(h2[2]), __habs2(h2[3])));
+    const float2 f = __bfloat1622float2(m);
+    return fmaxf(f.x, f.y);
 }
 
 __device__ __forceinline__ uint32_t pack4_e4m3(float a, float b, float c, float d) {

@@ -73,7 +73,11 @@ constexpr size_t kWsLLInts = 2 * kMaxExperts + kMaxRanks + 4;
 // tensor-parallel fused operators (int32): [64 chunks][kMaxRanks] rows-landed counters of the all-gather push
 constexpr size_t kWsTpOffsetBytes = kWsLLOffsetBytes + kWsLLInts * 4;
 constexpr size_t kWsTpInts = 64 * kMaxRanks;
-constexpr size_t kWsBytes = kWsTpOffsetBytes + kWsTpInts * 4 + 4096;
+// dispatch work sharing (int32): [kMaxBlocks] next token of every block's chunk, [kMaxBlocks] "bases published" epochs,
+// [kMaxBlocks][kMaxRanks + kMaxExperts] the published first rows of every block's chunk
+constexpr size_t kWsStealOffsetBytes = kWsTpOffsetBytes + kWsTpInts * 4;
+constexpr size_t kWsStealInts = 2 * static_cast<size_t>(kMaxBlocks) + static_cast<size_t>(kMaxBlocks) * (kMaxRanks + kMaxExperts);
+constexpr size_t kWsBytes = kWsStealOffsetBytes + kWsStealInts * 4 + 4096;
 
 // ---------------------------------------------------------------- control area of the symmetric heap, in uint64 words
 constexpr size_t kCtlBarrier = 0;                                        // [kMaxRanks]

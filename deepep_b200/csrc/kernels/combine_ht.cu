@@ -221,15 +221,38 @@ __global__ void __launch_bounds__(512) combine_epilogue_kernel(const __grid_cons
         }
         const uint8_t* b0 = p.bias0 != nullptr ? p.bias0 + t * row_bytes : nullptr;
         const uint8_t* b1 = p.bias1 != nullptr ? p.bias1 + t * row_bytes : nullptr;
+        if (__popc(mask) == 1 && b0 == nullptr && b1 == nullptr) {
+            // a single contribution (e.g. one rank): the sum is a copy; keep four loads in flight per lane
+            const uint8_t* src = p.region_x + (static_cast<uint64_t>(__ffs(mask) - 1) * p.num_max_tokens + t) * row_bytes;
+            uint8_t* dst = p.combined_x + t * row_bytes;
+            for (int v = lane; v < vec_per_row; v += 128) {
+                int4 raw[4];
+#pragma unroll
+                for (int j = 0; j < 4; ++j)
+                    if (v + 32 * j < vec_per_row) raw[j] = ld_nc_int4(src + (v + 32 * j) * 16);
+#pragma unroll
+                for (int j = 0; j < 4; ++j)
+                    if (v + 32 * j < vec_per_row) st_na_int4(dst + (v + 32 * j) * 16, raw[j]);
+            }
+            continue;
+        }
         for (int v = lane; v < vec_per_row; v += 32) {
             float acc[8];
 #pragma unroll
             for (int j = 0; j < 8; ++j) acc[j] = 0.f;
-            uint32_t todo = mask;
-            while (todo) {
-                const int l = __ffs(todo) - 1;
-                todo &= todo - 1;
-                accumulate_bf16x8(acc, ld_nc_int4(p.region_x + (static_cast<uint64_t>(l) * p.num_max_tokens + t) * row_bytes + v * 16));
+            // all loads of a group of eight lanes are issued before the first add (memory-level parallelism);
+            // the adds then run in ascending lane order
+            for (int base = 0; base < p.num_lanes; base += 8) {
+                const uint32_t group = (mask >> base) & 0xffu;
+                if (group == 0) continue;
+                int4 raw[8];
+#pragma unroll
+                for (int l = 0; l < 8; ++l)
+                    if ((group >> l) & 1u)
+                        raw[l] = ld_nc_int4(p.region_x + (static_cast<uint64_t>(base + l) * p.num_max_tokens + t) * row_bytes + v * 16);
+#pragma unroll
+                for (int l = 0; l < 8; ++l)
+                    if ((group >> l) & 1u) accumulate_bf16x8(acc, raw[l]);
             }
             if (b0 != nullptr) accumulate_bf16x8(acc, ld_nc_int4(b0 + v * 16));
             if (b1 != nullptr) accumulate_bf16x8(acc, ld_nc_int4(b1 + v * 16));

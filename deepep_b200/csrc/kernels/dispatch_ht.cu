@@ -72,14 +72,7 @@ __device__ __forceinline__ void quantize_row(const uint8_t* src, uint8_t* out, f
         for (int u = 0; u < kUnroll; ++u) {
             const int ch = base + u * 256 + lane * 8;
             raw[u] = ch < hidden ? *reinterpret_cast<const int4*>(src + ch * 2) : make_int4(0, 0, 0, 0);
-            const __nv_bfloat162* h2 = reinterpret_cast<const __nv_bfloat162*>(&raw[u]);
-            float m = 0.f;
-#pragma unroll
-            for (int i = 0; i < 4; ++i) {
-                const float2 v = __bfloat1622float2(h2[i]);
-                m = fmaxf(m, fmaxf(fabsf(v.x), fabsf(v.y)));
-            }
-            amax[u] = m;
+            amax[u] = amax_bf16x8(raw[u]);
         }
 #pragma unroll
         for (int o = 8; o > 0; o >>= 1) {
@@ -131,6 +124,9 @@ __global__ void __launch_bounds__(1024, 1) dispatch_kernel(const __grid_constant
     int* blk_cnt = reinterpret_cast<int*>(c.local_ws + kWsScratch);   // [nb][CW]
     uint64_t* my_ctl = reinterpret_cast<uint64_t*>(c.heap[c.rank]);
     uint64_t* grid_counter = c.local_ws + kWsGridBarrier;
+    int* steal_next = reinterpret_cast<int*>(reinterpret_cast<uint8_t*>(c.local_ws) + kWsStealOffsetBytes);   // [nb]
+    uint32_t* steal_ready = reinterpret_cast<uint32_t*>(steal_next + kMaxBlocks);                               // [nb]
+    int* steal_base = reinterpret_cast<int*>(steal_ready + kMaxBlocks);                                          // [nb][CW]
     bool ok = true;
     // phase timestamps of block 0 (ns, %globaltimer): start, counted, exchanged, sent, finished
     uint64_t* stamps = c.local_ws + kWsStamps;
@@ -350,22 +346,14 @@ __global__ void __launch_bounds__(1024, 1) dispatch_kernel(const __grid_constant
             }
         }
         __syncthreads();
-        // Make the positions of this block's chunk absolute, so that ANY block can send ANY token.
+        // Publish the first rows of this block's chunk: a block that runs out of own tokens takes tokens of
+        // other chunks and needs their bases (no grid barrier, only a per-block "published" word).
         if (ok) {
-            const int n_tok = t1 - t0;
-            for (int i = tid; i < n_tok * R; i += nthreads) {
-                int* slot = p.token_slot + static_cast<int64_t>(t0) * R + i;
-                const int v = *slot;
-                if (v >= 0) *slot = v + s_rank_base[i % R];
-            }
-            for (int i = tid; i < n_tok * K; i += nthreads) {
-                const int64_t pi = static_cast<int64_t>(t0) * K + i;
-                const int v = p.pair_row[pi];
-                if (v >= 0) p.pair_row[pi] = v + s_exp_base[static_cast<int>(p.topk_idx[pi])];
-            }
+            for (int j = tid; j < CW; j += nthreads) steal_base[bid * CW + j] = j < R ? s_rank_base[j] : s_exp_base[j - R];
         }
         __threadfence();
-        ok &= grid_barrier(w, grid_counter, p.grid_bar_base + 2 * static_cast<uint64_t>(nb), 4);
+        __syncthreads();
+        if (tid == 0 && ok) st_release_gpu_u32(steal_ready + bid, p.epoch);
     } else {
         // ------------------------------------------------------------ cached: only announce entry and wait for the peers
         if (bid == 0 && tid < R) {
@@ -401,14 +389,48 @@ __global__ void __launch_bounds__(1024, 1) dispatch_kernel(const __grid_constant
         float* meta_w = reinterpret_cast<float*>(meta_idx + K);
         int* meta_row = meta_idx + 2 * K;
         uint32_t parity = 0;
-        // Tokens are handed out dynamically: SMs differ in how fast their peer stores drain, and a
-        // static split would leave the fast ones idle. Every warp starts with a fixed token and
-        // then draws the next index from a counter of this rank.
-        unsigned long long* work = reinterpret_cast<unsigned long long*>(c.local_ws + kWsWork);
-        int t = bid * num_warps + warp;
-        while (t < T) {
+        // Tokens are handed out dynamically: SMs differ in how fast their peer stores drain, and a static
+        // split would leave the fast ones idle. Every chunk has a counter; a block serves its own chunk
+        // first and then walks the other chunks, taking whatever tokens are left there.
+        int victim = bid, v_t0 = t0, v_t1 = t1;
+        constexpr int visited_base = 0;
+        int t_local = 0;
+        if (lane == 0) t_local = atomicAdd(steal_next + victim, 1);
+        t_local = __shfl_sync(0xffffffffu, t_local, 0);
+        while (true) {
+            bool victim_ok = true;
+            while (v_t0 + t_local >= v_t1) {
+                // Own chunk (or the current victim) is exhausted: look at the counters of the next chunks,
+                // 32 at a time, and take a token from the first one that still has some.
+                int found = -1;
+                for (int off = 1; off < nb && found < 0; off += 32) {
+                    const int cand = (bid + visited_base + off + lane) % nb;
+                    bool has = false;
+                    if (off + lane < nb) {
+                        const int c0 = min(T, cand * chunk), c1 = min(T, c0 + chunk);
+                        has = c0 + __ldcg(steal_next + cand) < c1;
+                    }
+                    const uint32_t bal = __ballot_sync(0xffffffffu, has);
+                    if (bal != 0) found = (bid + visited_base + off + (__ffs(bal) - 1)) % nb;
+                }
+                if (found < 0) { victim = -1; break; }
+                victim = found;
+                v_t0 = min(T, victim * chunk);
+                v_t1 = min(T, v_t0 + chunk);
+                if (lane == 0) t_local = atomicAdd(steal_next + victim, 1);
+                t_local = __shfl_sync(0xffffffffu, t_local, 0);
+                if (!p.cached && v_t0 + t_local < v_t1) {
+                    // the victim's bases must be published (they are, unless it is still in its prologue)
+                    victim_ok = bounded_wait(w, kStatusGridBarrier, victim, 5, [&]() { return ld_acquire_gpu_u32(steal_ready + victim) == p.epoch; });
+                    victim_ok = __all_sync(0xffffffffu, victim_ok);
+                    if (!victim_ok) break;
+                }
+            }
+            if (victim < 0 || !victim_ok) break;
+            const int t = v_t0 + t_local;
+            const bool foreign = victim != bid;
             int fetched = 0;
-            if (lane == 0) fetched = static_cast<int>(atomicAdd(work, 1ull)) + nb * num_warps;
+            if (lane == 0) fetched = atomicAdd(steal_next + victim, 1);   // next index, read at the end of the step
             bulk_wait_read_all();   // the previous stores of every lane have read the buffers
             __syncwarp();
             if (lane == 0) {
@@ -417,12 +439,22 @@ __global__ void __launch_bounds__(1024, 1) dispatch_kernel(const __grid_constant
                 if (sf_bulk) bulk_g2s(buf_meta, p.sf + static_cast<int64_t>(t) * p.sf_token_stride * 4, p.sf_bytes, bar);
             }
             int slot = -1;
-            if (lane < R) slot = p.token_slot[static_cast<int64_t>(t) * R + lane];
+            if (lane < R) {
+                slot = p.token_slot[static_cast<int64_t>(t) * R + lane];
+                if (!p.cached && slot >= 0) {   // block-relative -> absolute, kept in the handle for cached replays and the combine
+                    slot += foreign ? __ldcg(steal_base + victim * CW + lane) : s_rank_base[lane];
+                    p.token_slot[static_cast<int64_t>(t) * R + lane] = slot;
+                }
+            }
             if (lane < K) {
                 const int64_t pi = static_cast<int64_t>(t) * K + lane;
                 const int64_t raw = p.topk_idx[pi];
                 const int e = (raw >= 0 && raw < E) ? static_cast<int>(raw) : -1;
-                const int row = p.pair_row[pi];
+                int row = p.pair_row[pi];
+                if (!p.cached && e >= 0) {
+                    row += foreign ? __ldcg(steal_base + victim * CW + R + e) : s_exp_base[e];
+                    p.pair_row[pi] = row;
+                }
                 meta_idx[lane] = e;
                 meta_w[lane] = p.topk_weights != nullptr ? p.topk_weights[pi] : 0.f;
                 meta_row[lane] = row;
@@ -445,7 +477,7 @@ __global__ void __launch_bounds__(1024, 1) dispatch_kernel(const __grid_constant
                 bulk_s2g(heap + p.off_recv_meta + static_cast<uint64_t>(slot) * p.meta_bytes, buf_meta, p.meta_bytes);
                 bulk_commit();
             }
-            t = __shfl_sync(0xffffffffu, fetched, 0);
+            t_local = __shfl_sync(0xffffffffu, fetched, 0);
         }
     }
 
@@ -454,10 +486,10 @@ __global__ void __launch_bounds__(1024, 1) dispatch_kernel(const __grid_constant
     fence_proxy_async_all();
     __threadfence_system();
     if (stamper) stamps[3] = globaltimer_ns();
-    grid_barrier(w, grid_counter, p.grid_bar_base + (p.cached ? 1 : 3) * static_cast<uint64_t>(nb), 2);
+    grid_barrier(w, grid_counter, p.grid_bar_base + (p.cached ? 1 : 2) * static_cast<uint64_t>(nb), 2);
     if (stamper) stamps[4] = globaltimer_ns();
     if (bid == 0) {   // ready for the next launch (stream order)
-        if (tid == 0) c.local_ws[kWsWork] = 0;
+        for (int b = tid; b < nb; b += nthreads) steal_next[b] = 0;
         if (!p.cached) {
             int* tot_cnt = blk_cnt + kTotOffset;
             for (int j = tid; j < CW; j += nthreads) tot_cnt[j] = 0;

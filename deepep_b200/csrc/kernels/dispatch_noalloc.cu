@@ -144,7 +144,7 @@ extern "C" int deepep_b200_dispatch_local_noalloc(const void* x, long long x_str
     p.epoch = ++st->epoch;
     p.grid_bar_base = st->grid_bar_base;
     p.host_counts = nullptr;
-    st->grid_bar_base += 3ull * num_sms;
+    st->grid_bar_base += 2ull * num_sms;
 
     DispatchLaunch launch;
     if (!plan_dispatch(p, num_sms, st->smem_optin, &launch)) return DEEPEP_B200_NOALLOC_ERR_ROW_BYTES;

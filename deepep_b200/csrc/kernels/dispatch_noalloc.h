@@ -24,7 +24,7 @@
  * Limits (fixed at build time, a call beyond them returns an error code and launches nothing):
  *   tokens <= DEEPEP_B200_NOALLOC_MAX_TOKENS, row bytes <= DEEPEP_B200_NOALLOC_MAX_ROW_BYTES
  *   (multiple of 16), top-k <= DEEPEP_B200_NOALLOC_MAX_TOPK, experts <=
- *   DEEPEP_B200_NOALLOC_MAX_EXPERTS. The scratch array is about 11 MB
+ *   DEEPEP_B200_NOALLOC_MAX_EXPERTS. The scratch array is about 12 MB
  *   (deepep_b200_noalloc_scratch_bytes() gives the exact figure); every GPU that loads the
  *   library holds that much from load until the process exits, whether or not this function is
  *   ever called.

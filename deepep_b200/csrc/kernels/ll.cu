@@ -268,14 +268,26 @@ __global__ void __launch_bounds__(1024, 1) ll_combine_kernel(const __grid_consta
         const int half = epoch & 1;
         int* finish = ll_finish_combine(c);
         __shared__ int s_pref[kMaxLocalExperts + 1];
-        if (tid == 0) {
-            int acc = 0;
-            for (int le = 0; le < EL; ++le) {
-                s_pref[le] = acc;
-                const int64_t last = p.layout_range[le * R + R - 1];
-                acc += static_cast<int>(last >> 32) + static_cast<int>(last & 0xffffffff);
+        // rows per local expert (begin + count of the last source rank), prefix-summed by warp 0
+        if (warp == 0) {
+            int carry = 0;
+            for (int base = 0; base < EL; base += 32) {
+                const int le = base + lane;
+                int rows = 0;
+                if (le < EL) {
+                    const int64_t last = p.layout_range[le * R + R - 1];
+                    rows = static_cast<int>(last >> 32) + static_cast<int>(last & 0xffffffff);
+                }
+                int incl = rows;
+#pragma unroll
+                for (int o = 1; o < 32; o <<= 1) {
+                    const int up = __shfl_up_sync(0xffffffffu, incl, o);
+                    if (lane >= o) incl += up;
+                }
+                if (le < EL) s_pref[le] = carry + incl - rows;
+                carry += __shfl_sync(0xffffffffu, incl, 31);
             }
-            s_pref[EL] = acc;
+            if (lane == 0) s_pref[EL] = carry;
         }
         __syncthreads();
         const int total_rows = s_pref[EL];

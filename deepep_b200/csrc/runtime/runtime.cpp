@@ -310,7 +310,7 @@ std::vector<DispatchResult> Runtime::dispatch(const std::vector<std::shared_ptr<
         p.off_recv_x = lay.dispatch_x[slot];
         p.off_recv_meta = lay.dispatch_meta[slot];
         p.grid_bar_base = rt.grid_bar_base;
-        rt.grid_bar_base += static_cast<uint64_t>(cached ? 1 : 3) * num_sms;
+        rt.grid_bar_base += static_cast<uint64_t>(cached ? 1 : 2) * num_sms;
         p.host_counts = (a.do_cpu_sync && !cached) ? rt.host_words_dev_ + kHostStatusWords : nullptr;
     }
 

@@ -1,0 +1,118 @@
+"""Single-GPU micro-benchmarks of the individual kernels (also the command that ncu captures wrap).
+
+    python -m deepep_b200.utils.kernel_bench --op dispatch --tokens 8192 --iters 5
+    python -m deepep_b200.utils.kernel_bench --op gemm --m 8192 --n 2304 --k 7168
+    ncu --set full --clock-control none -k regex:dispatch_kernel -s 3 -c 1 -o prof \\
+        python -m deepep_b200.utils.kernel_bench --op dispatch --tokens 8192 --iters 2 --warmup 3
+
+Ops: ``dispatch`` (fused FP8 cast), ``dispatch_prequant``, ``dispatch_bf16``, ``combine``, ``gemm``,
+``gemm_fp8_grouped``, ``ll`` (low-latency dispatch + combine). Times are CUDA-event means on one
+rank (EP1: all traffic is local, so dispatch / combine show the SM-side cost of the kernels, not
+NVLink).
+"""
+from __future__ import annotations
+
+import argparse
+
+import torch
+
+
+def _timeit(fn, iters, warmup):
+    for _ in range(warmup):
+        fn()
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(iters):
+        fn()
+    e1.record()
+    torch.cuda.synchronize()
+    return e0.elapsed_time(e1) / iters
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument('--op', default='dispatch')
+    ap.add_argument('--tokens', type=int, default=8192)
+    ap.add_argument('--hidden', type=int, default=7168)
+    ap.add_argument('--experts', type=int, default=256)
+    ap.add_argument('--topk', type=int, default=8)
+    ap.add_argument('--sms', type=int, default=24)
+    ap.add_argument('--m', type=int, default=8192)
+    ap.add_argument('--n', type=int, default=2304)
+    ap.add_argument('--k', type=int, default=7168)
+    ap.add_argument('--iters', type=int, default=10)
+    ap.add_argument('--warmup', type=int, default=3)
+    a = ap.parse_args()
+
+    import deepep_b200
+    from deepep_b200.parallel.local_cluster import SingleProcessGroup
+    from deepep_b200.utils import gate
+    from deepep_b200.utils.math import per_token_cast_to_fp8
+    C = deepep_b200._C
+    torch.cuda.set_device(0)
+    g = torch.Generator().manual_seed(0)
+    T, H, E, K = a.tokens, a.hidden, a.experts, a.topk
+
+    if a.op.startswith('dispatch') or a.op == 'combine':
+        buf = deepep_b200.ElasticBuffer(SingleProcessGroup(), num_max_tokens_per_rank=T, hidden=H, num_topk=K, num_gpu_timeout_secs=20)
+        buf.runtime.enable_profiling(True)
+        x = torch.randn((T, H), generator=g).bfloat16().cuda()
+        idx, w = gate.topk_from_scores(gate.get_balanced_scores(T, E, generator=g), K)
+        idx, w = idx.cuda(), w.cuda()
+        xin, kw = x, dict(fused_fp8=True)
+        if a.op == 'dispatch_prequant':
+            xin, kw = per_token_cast_to_fp8(x), {}
+        elif a.op == 'dispatch_bf16':
+            kw = dict(fused_fp8=False)
+        out = buf.dispatch(xin, topk_idx=idx, topk_weights=w, num_experts=E, num_sms=a.sms, **kw)
+        handle = out[3]
+        y = torch.randn((handle.num_recv_tokens, H), device='cuda', dtype=torch.bfloat16)
+        if a.op == 'combine':
+            ms = _timeit(lambda: buf.combine(y, handle), a.iters, a.warmup)
+        else:
+            ms = _timeit(lambda: buf.dispatch(xin, topk_idx=idx, topk_weights=w, num_experts=E, num_sms=a.sms, **kw), a.iters, a.warmup)
+        t = buf.runtime.last_timings()
+        print(f'{a.op}: {ms * 1e3:.1f} us per call (kernel {t[0 if a.op != "combine" else 2] * 1e3:.1f} us, '
+              f'epilogue {t[1 if a.op != "combine" else 3] * 1e3:.1f} us), tokens {T}, hidden {H}, sms {a.sms}')
+        buf.check_status()
+        buf.destroy()
+    elif a.op == 'gemm':
+        x = torch.randn((a.m, a.k), generator=g).bfloat16().cuda()
+        wt = torch.randn((a.n, a.k), generator=g).bfloat16().cuda()
+        out = torch.empty((a.m, a.n), device='cuda', dtype=torch.bfloat16)
+        ms = _timeit(lambda: C.gemm(x, wt, out=out), a.iters, a.warmup)
+        print(f'gemm bf16 {a.m}x{a.n}x{a.k}: {ms * 1e3:.1f} us, {2 * a.m * a.n * a.k / ms / 1e9:.0f} TFLOP/s')
+    elif a.op == 'gemm_fp8_grouped':
+        G, rows = 8, a.m // 8 // 128 * 128
+        M = G * rows
+        xq = torch.randn((M, a.k), generator=g).cuda().to(torch.float8_e4m3fn)
+        sfa = torch.rand((M, a.k // 128), generator=g).cuda() + 0.5
+        wq = torch.randn((G, a.n, a.k), generator=g).cuda().to(torch.float8_e4m3fn)
+        sfb = torch.rand((G, a.n // 128, a.k // 128), generator=g).cuda() + 0.5
+        ends = (torch.arange(1, G + 1, device='cuda') * rows).int()
+        out = torch.empty((M, a.n), device='cuda', dtype=torch.bfloat16)
+        ms = _timeit(lambda: C.gemm(xq, wq, sfa=sfa, sfb=sfb, group_end=ends, group_alignment=128, out=out), a.iters, a.warmup)
+        print(f'gemm fp8 grouped {G}x{rows}x{a.n}x{a.k}: {ms * 1e3:.1f} us, {2 * M * a.n * a.k / ms / 1e9:.0f} TFLOP/s')
+    elif a.op == 'll':
+        Tl = min(T, 128)
+        hint = deepep_b200.Buffer.get_low_latency_rdma_size_hint(Tl, H, 1, E)
+        ll = deepep_b200.Buffer(SingleProcessGroup(), num_rdma_bytes=hint, low_latency_mode=True, num_gpu_timeout_secs=20)
+        x = torch.randn((Tl, H), generator=g).bfloat16().cuda()
+        idx, w = gate.topk_from_scores(gate.get_balanced_scores(Tl, E, generator=g), K)
+        idx, w = idx.cuda(), w.cuda()
+        yy = torch.randn((E, Tl, H), device='cuda', dtype=torch.bfloat16)
+
+        def step():
+            _, _, h, _, _ = ll.low_latency_dispatch(x, idx, Tl, E)
+            ll.low_latency_combine(yy, idx, w, h)
+        ms = _timeit(step, a.iters, a.warmup)
+        print(f'll dispatch+combine: {ms * 1e3:.1f} us, tokens {Tl}')
+        ll.check_status()
+        ll.destroy()
+    else:
+        raise SystemExit(f'unknown op {a.op}')
+
+
+if __name__ == '__main__':
+    main()

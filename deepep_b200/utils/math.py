@@ -60,11 +60,10 @@ def per_token_cast_to_fp8(x: torch.Tensor, round_scale: bool = False) -> Tuple[t
         scale = torch.exp2(torch.ceil(torch.log2(amax / FP8_MAX)))
         q = blocks * (1.0 / scale).unsqueeze(2)
     else:
-        # tensor / tensor divisions: `scalar / tensor` and `tensor / scalar` go through a reciprocal on
-        # some devices, which changes the last bit; the device kernels use one IEEE division each
-        full = torch.full_like(amax, FP8_MAX)
-        scale = torch.div(amax, full)
-        q = blocks * torch.div(full, amax).unsqueeze(2)
+        # the device kernels compute scale = amax * (1 / 448) and payload * (448 * (1 / amax)) with one correctly
+        # rounded reciprocal; the same operations in the same order here give identical bits on CPU and GPU
+        scale = amax * torch.tensor(1.0 / FP8_MAX, dtype=torch.float32, device=amax.device)
+        q = blocks * (amax.reciprocal() * FP8_MAX).unsqueeze(2)
     q = q.clamp(-FP8_MAX, FP8_MAX).to(torch.float8_e4m3fn).view(m, -1)[:, :n].contiguous()
     return q, scale
 
