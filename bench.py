@@ -32,7 +32,7 @@ BASELINE_COMBINE_GBS = 740.0    # reference README: EP8, SM100, 64 SMs, BF16 com
 def parse_args():
     p = argparse.ArgumentParser()
     p.add_argument('--gpus', type=int, default=1)
-    p.add_argument('--steps', type=int, default=20)
+    p.add_argument('--steps', type=int, default=50)
     p.add_argument('--warmup', type=int, default=5)
     p.add_argument('--impl', default='ours', choices=['ours', 'reference'])
     p.add_argument('--num-tokens', type=int, default=8192)
@@ -45,55 +45,86 @@ def parse_args():
 
 
 class ClockSampler:
-    """Samples SM clock and throttle reasons of one GPU with nvidia-smi while the timed region runs."""
+    """Samples SM clock, power and throttle reasons of one GPU while the timed region runs.
 
-    QUERY = ('clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,'
-             'clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap')
+    NVML is opened once, before the warm-up, and polled from a thread of this process (a light query
+    every 20 ms). Spawning ``nvidia-smi`` next to the timed loop attaches a second client to every GPU of
+    the box and was measured to stall kernel launches of multi-GPU runs by milliseconds per step; it is
+    only the fallback when the NVML bindings are missing."""
+
+    REASONS = {'hw_slowdown': 0x8, 'sw_power_cap': 0x4, 'sw_thermal_slowdown': 0x20, 'hw_thermal_slowdown': 0x40}
 
     def __init__(self, gpu_index: int):
         self.gpu_index = gpu_index
-        self.proc = None
-        self.lines = []
+        self.samples = []          # (time, sm_mhz, max_mhz, power_w, reason bits)
+        self._stop = threading.Event()
+        self._thread = None
+        self._nvml = None
+        self._handle = None
+        self._proc = None
+        try:
+            import pynvml
+            pynvml.nvmlInit()
+            visible = os.environ.get('CUDA_VISIBLE_DEVICES')
+            index = int(visible.split(',')[gpu_index]) if visible and visible.split(',')[gpu_index].isdigit() else gpu_index
+            self._handle = pynvml.nvmlDeviceGetHandleByIndex(index)
+            self._max = pynvml.nvmlDeviceGetMaxClockInfo(self._handle, pynvml.NVML_CLOCK_SM)
+            self._nvml = pynvml
+        except Exception:   # noqa: BLE001
+            self._nvml = None
+
+    def _poll_nvml(self):
+        n = self._nvml
+        while not self._stop.is_set():
+            try:
+                sm = n.nvmlDeviceGetClockInfo(self._handle, n.NVML_CLOCK_SM)
+                try:
+                    reasons = n.nvmlDeviceGetCurrentClocksEventReasons(self._handle)
+                except Exception:   # noqa: BLE001 - older bindings
+                    reasons = n.nvmlDeviceGetCurrentClocksThrottleReasons(self._handle)
+                self.samples.append((time.time(), float(sm), float(self._max), 0.0, int(reasons)))
+            except Exception:   # noqa: BLE001
+                pass
+            self._stop.wait(0.025)
 
     def start(self):
+        """Call before the warm-up steps."""
+        if self._nvml is not None:
+            self._thread = threading.Thread(target=self._poll_nvml, daemon=True)
+            self._thread.start()
+            return
+        query = 'clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active'
         try:
-            self.proc = subprocess.Popen(['nvidia-smi', f'--query-gpu={self.QUERY}', '--format=csv,noheader,nounits',
-                                          '-lms', '100', '-i', str(self.gpu_index)], stdout=subprocess.PIPE, text=True)
-            self.thread = threading.Thread(target=self._read, daemon=True)
-            self.thread.start()
-        except OSError:
-            self.proc = None
+            self._proc = subprocess.Popen(['nvidia-smi', f'--query-gpu={query}', '--format=csv,noheader,nounits', '-lms', '200',
+                                           '-i', str(self.gpu_index)], stdout=subprocess.PIPE, text=True)
 
-    def _read(self):
-        for line in self.proc.stdout:
-            self.lines.append((time.time(), line.strip()))
+            def read():
+                for line in self._proc.stdout:
+                    cols = [c.strip() for c in line.split(',')]
+                    try:
+                        self.samples.append((time.time(), float(cols[0]), float(cols[1]), float(cols[2]), int(cols[3], 16)))
+                    except (ValueError, IndexError):
+                        continue
+            self._thread = threading.Thread(target=read, daemon=True)
+            self._thread.start()
+        except OSError:
+            self._proc = None
 
     def stop(self, t0: float, t1: float):
-        if self.proc is None:
-            return {'sm_mhz': None, 'sm_max_mhz': None, 'reasons': ['nvidia-smi unavailable']}
-        time.sleep(0.15)
-        self.proc.terminate()
-        try:
-            self.proc.wait(timeout=2)
-        except subprocess.TimeoutExpired:
-            self.proc.kill()
-        rows = [l for ts, l in self.lines if t0 - 0.05 <= ts <= t1 + 0.15] or [l for _, l in self.lines]
-        sm, mx, reasons = [], [], set()
-        names = ['hw_slowdown', 'hw_thermal_slowdown', 'sw_thermal_slowdown', 'sw_power_cap']
-        for row in rows:
-            cols = [c.strip() for c in row.split(',')]
-            if len(cols) < 7:
-                continue
-            try:
-                sm.append(float(cols[0]))
-                mx.append(float(cols[1]))
-            except ValueError:
-                continue
-            for name, val in zip(names, cols[3:7]):
-                if val.lower().startswith('active'):
-                    reasons.add(name)
-        return {'sm_mhz': statistics.median(sm) if sm else None, 'sm_max_mhz': max(mx) if mx else None,
-                'reasons': sorted(reasons), 'samples': len(sm)}
+        self._stop.set()
+        if self._proc is not None:
+            self._proc.terminate()
+        if self._thread is not None:
+            self._thread.join(timeout=2)
+        rows = [s for s in self.samples if t0 <= s[0] <= t1] or [s for s in self.samples if t0 - 0.5 <= s[0] <= t1 + 0.5]
+        if not rows:
+            return {'sm_mhz': None, 'sm_max_mhz': None, 'reasons': ['no clock samples'], 'samples': 0}
+        bits = 0
+        for r in rows:
+            bits |= r[4]
+        return {'sm_mhz': statistics.median(r[1] for r in rows), 'sm_max_mhz': max(r[2] for r in rows),
+                'reasons': sorted(name for name, bit in self.REASONS.items() if bits & bit), 'samples': len(rows),
+                'source': 'nvml' if self._nvml is not None else 'nvidia-smi'}
 
 
 def reference_arm(args):
@@ -260,12 +291,11 @@ def main():
 
     # ------------------------------------------------------------------ headline: device-timed full steps
     sampler = ClockSampler(local_rank) if rank == 0 else None
+    if sampler:
+        sampler.start()
     for i in range(args.warmup):
         step(i, args.num_sms)
     sync_all()
-    if sampler:
-        sampler.start()
-        time.sleep(0.25)
     t_wall0 = time.time()
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     e0.record()
