@@ -192,7 +192,10 @@ __global__ void __launch_bounds__(1024, 1) ll_dispatch_kernel(const __grid_const
         __shared__ int s_cnt[kMaxRanks], s_begin[kMaxRanks + 1];
         const int rows_per_expert = R * Tm;
         const int sf_per_row = p.use_fp8 ? (p.use_ue8m0 ? H / 512 : H / 128) : 0;
-        for (int le = bid; le < EL; le += nb) {
+        // work item = (local expert, source rank): a block waits for the counts of all sources of that expert
+        // (it needs the prefix), then packs the rows of its own source only
+        for (int item = bid; item < EL * R; item += nb) {
+            const int le = item / R, src_rank = item % R;
             __syncthreads();
             if (tid < R) {
                 int cnt = 0;
@@ -205,7 +208,8 @@ __global__ void __launch_bounds__(1024, 1) ll_dispatch_kernel(const __grid_const
                         return epoch_matches(v, epoch);
                     });
                     if (ok) cnt = static_cast<int>(static_cast<uint32_t>(v));
-                    if (p.wait_stats != nullptr) atomicAdd(reinterpret_cast<unsigned long long*>(p.wait_stats + tid), globaltimer_ns() - t0);
+                    if (p.wait_stats != nullptr && src_rank == 0)
+                        atomicAdd(reinterpret_cast<unsigned long long*>(p.wait_stats + tid), globaltimer_ns() - t0);
                 }
                 s_cnt[tid] = cnt;
             }
@@ -214,20 +218,21 @@ __global__ void __launch_bounds__(1024, 1) ll_dispatch_kernel(const __grid_const
                 int acc = 0;
                 for (int s = 0; s < R; ++s) {
                     s_begin[s] = acc;
-                    p.packed_recv_layout_range[le * R + s] = (static_cast<int64_t>(acc) << 32) | static_cast<uint32_t>(s_cnt[s]);
+                    if (src_rank == 0)
+                        p.packed_recv_layout_range[le * R + s] = (static_cast<int64_t>(acc) << 32) | static_cast<uint32_t>(s_cnt[s]);
                     acc += s_cnt[s];
                 }
                 s_begin[R] = acc;
-                p.packed_recv_count[le] = acc;
-                if (p.cumulative_stats != nullptr) atomicAdd(p.cumulative_stats + le, acc);
+                if (src_rank == 0) {
+                    p.packed_recv_count[le] = acc;
+                    if (p.cumulative_stats != nullptr) atomicAdd(p.cumulative_stats + le, acc);
+                }
             }
             __syncthreads();
-            const int total = s_begin[R];
-            for (int j = warp; j < total; j += num_warps) {
-                int s = 0;
-                while (s < R - 1 && j >= s_begin[s + 1]) ++s;
-                const int slot = j - s_begin[s];
-                const uint8_t* src = c.heap[c.rank] + p.off_recv_x[half] + ((static_cast<uint64_t>(le) * R + s) * Tm + slot) * msg_bytes;
+            const int begin = s_begin[src_rank], count = s_cnt[src_rank];
+            for (int slot = warp; slot < count; slot += num_warps) {
+                const int j = begin + slot;
+                const uint8_t* src = c.heap[c.rank] + p.off_recv_x[half] + ((static_cast<uint64_t>(le) * R + src_rank) * Tm + slot) * msg_bytes;
                 const int64_t out_row = static_cast<int64_t>(le) * rows_per_expert + j;
                 if (lane == 0) {
                     const int4 hdr = *reinterpret_cast<const int4*>(src);

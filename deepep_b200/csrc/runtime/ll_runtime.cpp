@@ -69,7 +69,7 @@ std::optional<EventHandle> ll_dispatch(const std::vector<std::shared_ptr<Runtime
     if (use_ue8m0) EP_HOST_ASSERT_MSG(round_scale && use_fp8 && H % 512 == 0, "UE8M0 scales need round_scale, FP8 and hidden % 512 == 0");
     const LLLayout lay = ll_layout(R, Tm, H, E);
     EP_HOST_ASSERT_MSG(lay.end <= rt0.heap().num_bytes(), "symmetric buffer too small for low-latency mode");
-    if (num_sms <= 0) num_sms = std::min(rt0.num_device_sms(), std::max(EL, 32));
+    if (num_sms <= 0) num_sms = rt0.num_device_sms();   // latency-bound: one token / one (expert, source) pair per block
     if (num_sms * V > rt0.num_device_sms()) num_sms = rt0.num_device_sms() / V;
 
     Multi<LLDispatchParams> m;
@@ -136,7 +136,7 @@ std::optional<EventHandle> ll_combine(const std::vector<std::shared_ptr<Runtime>
     EP_HOST_ASSERT(E % R == 0 && K <= kMaxLLTopk && K <= kMaxTopk && (H * 2) % 16 == 0);
     const LLLayout lay = ll_layout(R, Tm, H, E);
     EP_HOST_ASSERT_MSG(lay.end <= rt0.heap().num_bytes(), "symmetric buffer too small for low-latency mode");
-    if (num_sms <= 0) num_sms = std::min(rt0.num_device_sms(), std::max(EL, 32));
+    if (num_sms <= 0) num_sms = rt0.num_device_sms();   // latency-bound: one token / one (expert, source) pair per block
     if (num_sms * V > rt0.num_device_sms()) num_sms = rt0.num_device_sms() / V;
 
     Multi<LLCombineParams> m;

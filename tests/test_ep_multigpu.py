@@ -66,3 +66,125 @@ def test_two_or_more_gpus(fused_fp8):
         pytest.skip('needs at least two GPUs')
     world = 8 if n >= 8 else (4 if n >= 4 else 2)
     torch.multiprocessing.spawn(_worker, args=(world, _free_port(), fused_fp8), nprocs=world, join=True)
+
+
+def _subsystems_worker(rank: int, world: int, port: int):
+    """Low-latency mode, AGRS, reduce-scatter, PP ring, Engram, fused TP GEMMs and the MoE module on real ranks."""
+    import torch.distributed as dist
+    os.environ['MASTER_ADDR'] = '127.0.0.1'
+    os.environ['MASTER_PORT'] = str(port)
+    os.environ.setdefault('NCCL_NVLS_ENABLE', '0')
+    torch.cuda.set_device(rank)
+    dev = torch.device('cuda', rank)
+    dist.init_process_group('nccl', rank=rank, world_size=world, device_id=dev)
+    group = dist.group.WORLD
+    import deepep_b200
+    from deepep_b200.utils import gate
+    g = torch.Generator().manual_seed(500 + rank)
+
+    # ---- low-latency dispatch / combine through the legacy front end
+    T, H, E, K = 32, 1024, 4 * world, 2
+    EL = E // world
+    ll = deepep_b200.Buffer(group, num_rdma_bytes=deepep_b200.Buffer.get_low_latency_rdma_size_hint(T, H, world, E),
+                            low_latency_mode=True, num_gpu_timeout_secs=10, explicitly_destroy=True)
+    x = torch.randn((T, H), generator=g).bfloat16().to(dev)
+    idx, w = gate.topk_from_scores(gate.get_balanced_scores(T, E, generator=g), K)
+    idx, w = idx.to(dev), w.to(dev)
+    for it in range(3):
+        rx, cnt, handle, _, _ = ll.low_latency_dispatch(x, idx, T, E, use_fp8=False)
+        # every received row must be the source row its src_info names
+        all_x = [torch.empty_like(x) for _ in range(world)]
+        dist.all_gather(all_x, x)
+        for le in range(EL):
+            n = int(cnt[le])
+            info = handle[0][le, :n]
+            lay = handle[1][le]
+            begin = 0
+            for s in range(world):
+                c = int(lay[s]) & 0xffffffff
+                tok = (info[begin:begin + c] & 0xffff).long()
+                assert torch.equal(rx[le, begin:begin + c], all_x[s][tok])
+                begin += c
+        out, _, _ = ll.low_latency_combine(rx, idx, w, handle)
+        valid_w = torch.where(idx >= 0, w, torch.zeros_like(w)).sum(dim=1, keepdim=True)
+        assert torch.allclose(out.float(), x.float() * valid_w, rtol=2e-2, atol=2e-2)
+    ll.check_status()
+    dist.barrier()
+    ll.destroy()
+
+    # ---- AGRS, reduce-scatter, PP, Engram on one elastic buffer
+    buf = deepep_b200.ElasticBuffer(group, num_bytes=64 << 20, num_gpu_timeout_secs=10, explicitly_destroy=True)
+    buf.agrs_set_config(4 << 20, 8)
+    for it in range(2):
+        with buf.agrs_new_session():
+            t = torch.full((64, 32), float(rank + it), device=dev)
+            gathered, wait = buf.all_gather(t)
+            wait()
+            assert torch.equal(gathered, torch.stack([torch.full((64, 32), float(r + it), device=dev) for r in range(world)]))
+            z = torch.randn((world * 8, 64), generator=g).bfloat16().to(dev)
+            rs = buf.reduce_scatter(z)
+            ref = z.float().clone()
+            dist.all_reduce(ref)
+            assert torch.allclose(rs.float(), ref[rank * 8:(rank + 1) * 8], rtol=2e-2, atol=2e-2)
+            torch.cuda.synchronize()
+    buf.pp_set_config(1 << 16, 2)
+    nxt, prv = (rank + 1) % world, (rank - 1) % world
+    for it in range(5):
+        buf.pp_send(torch.full((1000,), float(rank * 10 + it), device=dev), nxt)
+        got = torch.empty(1000, device=dev)
+        buf.pp_recv(got, prv)
+        assert torch.equal(got, torch.full((1000,), float(prv * 10 + it), device=dev))
+    per_rank, hidden = 32, 128
+    table = torch.arange(world * per_rank, device=dev).float().unsqueeze(1).expand(-1, hidden).bfloat16().contiguous()
+    buf.engram_write(table[rank * per_rank:(rank + 1) * per_rank].contiguous())
+    q = torch.randint(0, world * per_rank, (9, 2), device=dev, dtype=torch.int32)
+    data, _ = buf.engram_fetch(q)()
+    torch.cuda.synchronize()
+    assert torch.equal(data, table[q.flatten().long()])
+    buf.check_status()
+    dist.barrier()
+    buf.destroy()
+
+    # ---- fused tensor-parallel GEMMs against NCCL + matmul
+    from deepep_b200.parallel.tp_fused import TensorParallelContext, nccl_all_gather_gemm, nccl_gemm_reduce_scatter
+    ctx = TensorParallelContext(group, 256, 512, 512, num_gpu_timeout_secs=10)
+    gc = torch.Generator(device='cuda').manual_seed(rank)
+    for it in range(3):
+        xs = torch.randn((256, 512), device=dev, generator=gc).bfloat16()
+        w1 = (torch.randn((512, 512), device=dev, generator=gc) * 0.05).bfloat16()
+        a = ctx.all_gather_gemm(xs, w1, num_comm_ctas=2, num_sms=24)
+        b = nccl_all_gather_gemm(xs, w1, group)
+        assert ((a.float() - b.float()).norm() / b.float().norm()).item() < 1e-2
+        x2 = torch.randn((world * 256, 256), device=dev, generator=gc).bfloat16()
+        w2 = (torch.randn((512, 256), device=dev, generator=gc) * 0.05).bfloat16()
+        c = ctx.gemm_reduce_scatter(x2, w2, num_sms=24)
+        d = nccl_gemm_reduce_scatter(x2, w2, group)
+        assert ((c.float() - d.float()).norm() / d.float().norm()).item() < 2e-2
+    torch.cuda.synchronize()
+    ctx.check_status()
+    dist.barrier()
+    ctx.destroy()
+
+    # ---- the MoE module: forward + backward runs and produces finite gradients on every rank
+    from deepep_b200.models.moe import FusedMoE, MoEConfig
+    Tm, Hm, Im, Em, Km = 64, 256, 128, 2 * world, 2
+    mbuf = deepep_b200.ElasticBuffer(group, num_max_tokens_per_rank=Tm, hidden=Hm, num_topk=Km, num_gpu_timeout_secs=10, explicitly_destroy=True)
+    layer = FusedMoE(mbuf, MoEConfig(hidden=Hm, intermediate=Im, num_experts=Em, num_topk=Km, num_sms=8))
+    xm = torch.randn((Tm, Hm), generator=g).bfloat16().to(dev).requires_grad_(True)
+    ym = layer(xm)
+    (ym.float() ** 2).mean().backward()
+    torch.cuda.synchronize()
+    mbuf.check_status()
+    for p in (xm, layer.router, layer.w13, layer.w2):
+        assert p.grad is not None and torch.isfinite(p.grad.float()).all()
+    dist.barrier()
+    mbuf.destroy()
+    dist.destroy_process_group()
+
+
+def test_subsystems_on_real_ranks():
+    n = torch.cuda.device_count()
+    if n < 2:
+        pytest.skip('needs at least two GPUs')
+    world = 4 if n >= 4 else 2
+    torch.multiprocessing.spawn(_subsystems_worker, args=(world, _free_port()), nprocs=world, join=True)
