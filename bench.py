@@ -39,7 +39,8 @@ def parse_args():
     p.add_argument('--hidden', type=int, default=7168)
     p.add_argument('--num-experts', type=int, default=256)
     p.add_argument('--num-topk', type=int, default=8)
-    p.add_argument('--num-sms', type=int, default=24)
+    p.add_argument('--num-sms', type=int, default=0, help='SMs of the communication kernels; 0 = 24 with peers, all SMs at EP1 '
+                   '(no NVLink traffic to leave SMs free for: the SM model of the library picks the whole GPU there too)')
     p.add_argument('--no-extra', action='store_true', help='skip the kernel-only / 64-SM / NCCL detail sections')
     return p.parse_args()
 
@@ -228,6 +229,8 @@ def main():
 
     T, H, E, K = args.num_tokens, args.hidden, args.num_experts, args.num_topk
     assert E % world == 0
+    if args.num_sms <= 0:
+        args.num_sms = 24 if world > 1 else torch.cuda.get_device_properties(dev).multi_processor_count
     buf = deepep_b200.ElasticBuffer(group, num_max_tokens_per_rank=T, hidden=H, num_topk=K, use_fp8_dispatch=True,
                                     num_gpu_timeout_secs=20, explicitly_destroy=True)
     buf.runtime.enable_profiling(True)
@@ -266,8 +269,9 @@ def main():
 
     def step(i: int, num_sms: int):
         j = i % pool
+        # zero_copy: recv_x is the receive region itself (valid until the second next dispatch; it is consumed here)
         (recv_x, recv_sf), recv_idx, recv_w, handle, _ = buf.dispatch(xs[j], topk_idx=idxs[j], topk_weights=ws[j],
-                                                                      num_experts=E, num_sms=num_sms)
+                                                                      num_experts=E, num_sms=num_sms, zero_copy=True)
         n = recv_x.size(0)
         y = y_cache.get(n)
         if y is None:   # stands for the experts' bf16 output, one row per received token
@@ -411,19 +415,42 @@ def main():
 
     # ------------------------------------------------------------------ end to end through the public API
     # every step: pinned host -> device copy of tokens and routing, dispatch, combine, device -> host read of a checksum
-    x_dev = torch.empty((T, H), dtype=torch.bfloat16, device=dev)
-    idx_dev = torch.empty((T, K), dtype=torch.int64, device=dev)
-    w_dev = torch.empty((T, K), dtype=torch.float32, device=dev)
-    h2d = x_dev.numel() * 2 + idx_dev.numel() * 8 + w_dev.numel() * 4
+    # two sets of device input buffers: the pinned-host -> device copy of step i+1 runs on a copy stream while step i computes
+    x_dev = [torch.empty((T, H), dtype=torch.bfloat16, device=dev) for _ in range(2)]
+    idx_dev = [torch.empty((T, K), dtype=torch.int64, device=dev) for _ in range(2)]
+    w_dev = [torch.empty((T, K), dtype=torch.float32, device=dev) for _ in range(2)]
+    h2d = x_dev[0].numel() * 2 + idx_dev[0].numel() * 8 + w_dev[0].numel() * 4
     d2h = 4
+    copy_stream = torch.cuda.Stream()
+    copied = [None, None]      # event: inputs of the step that uses this buffer set have landed
+    consumed = [None, None]    # event: the step that used this buffer set has finished reading it
+
+    def issue_copy(i: int):
+        b, j = i % 2, i % pool
+        with torch.cuda.stream(copy_stream):
+            if consumed[b] is not None:
+                copy_stream.wait_event(consumed[b])
+            x_dev[b].copy_(xs_host[j], non_blocking=True)
+            idx_dev[b].copy_(idx_host[j], non_blocking=True)
+            w_dev[b].copy_(w_host[j], non_blocking=True)
+            ev = torch.cuda.Event()
+            ev.record(copy_stream)
+            copied[b] = ev
+
+    state = {'next': None}
 
     def e2e_step(i: int):
-        j = i % pool
-        x_dev.copy_(xs_host[j], non_blocking=True)
-        idx_dev.copy_(idx_host[j], non_blocking=True)
-        w_dev.copy_(w_host[j], non_blocking=True)
-        (rx, rsf), ridx, rw, h, _ = buf.dispatch(x_dev, topk_idx=idx_dev, topk_weights=w_dev, num_experts=E,
-                                                 num_sms=args.num_sms)
+        if state['next'] != i:          # first step of a loop: nothing was prefetched for it
+            issue_copy(i)
+        b = i % 2
+        torch.cuda.current_stream().wait_event(copied[b])
+        (rx, rsf), ridx, rw, h, _ = buf.dispatch(x_dev[b], topk_idx=idx_dev[b], topk_weights=w_dev[b], num_experts=E,
+                                                 num_sms=args.num_sms, zero_copy=True)
+        ev = torch.cuda.Event()
+        ev.record()
+        consumed[b] = ev
+        issue_copy(i + 1)               # overlaps with the rest of this step
+        state['next'] = i + 1
         n = rx.size(0)
         y = y_cache.get(n)
         if y is None:
@@ -448,7 +475,8 @@ def main():
                    'baseline': 'reference README EP8 SM100: 726 GB/s dispatch, 740 GB/s combine (kernel only, 64 SMs), per GPU'},
         'clocks': clocks,
         'e2e': {'value': round(e2e_value, 2), 'unit': 'GB/s', 'ms_per_step': round(e2e_ms, 4), 'steps': e2e_steps,
-                'h2d_bytes_per_step': h2d, 'd2h_bytes_per_step': d2h},
+                'h2d_bytes_per_step': h2d, 'd2h_bytes_per_step': d2h,
+                'note': 'public API; the host->device copy of step i+1 is issued during step i on a copy stream (every step copies its own inputs)'},
         'gpu_launches': 4 * args.steps,
         'detail': detail,
     }

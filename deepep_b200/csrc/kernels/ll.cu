@@ -89,6 +89,9 @@ __global__ void __launch_bounds__(1024, 1) ll_dispatch_kernel(const __grid_const
     const int msg_bytes = ll_dispatch_msg_bytes(H, p.use_fp8);
     const int payload_bytes = p.use_fp8 ? H : H * 2;
     const int* mask = ll_mask(c);
+    uint64_t* stamps = c.local_ws + kWsStamps;          // phase timestamps of block 0 (ns), read by the profiling helpers
+    const bool stamper = bid == 0 && tid == 0;
+    if (stamper) stamps[0] = globaltimer_ns();
 
     if (p.phases & kLLSend) {
         const uint32_t epoch = static_cast<uint32_t>(*reinterpret_cast<volatile uint64_t*>(c.local_ws + kWsLLCalls + 0)) + 1;
@@ -160,13 +163,13 @@ __global__ void __launch_bounds__(1024, 1) ll_dispatch_kernel(const __grid_const
                         bulk_commit();
                         bulk_wait_all();
                         fence_proxy_async_all();
-                        __threadfence_system();
-                        atomicAdd(finish + e, 1);
+                        red_add_release_gpu_s32(finish + e, 1);   // the flag sender acquires this and releases to the peer
                     }
                 }
                 __syncwarp();
             }
         }
+        if (stamper) stamps[1] = globaltimer_ns();
         // ---- publish the per-expert counts once every message of the expert has landed
         for (int e = bid + warp * nb; e < E; e += nb * num_warps) {
             const int dst = e / EL;
@@ -175,15 +178,16 @@ __global__ void __launch_bounds__(1024, 1) ll_dispatch_kernel(const __grid_const
             for (int i = lane; i < T * K; i += 32) total += s_topk[i] == e;
             total = warp_reduce_sum(total);
             if (lane == 0) {
-                bounded_wait(w, kStatusLLRecv, dst, e, [&]() { return ld_volatile_int(finish + e) >= total; });
+                bounded_wait(w, kStatusLLRecv, dst, e, [&]() { return ld_acquire_gpu_s32(finish + e) >= total; });
                 finish[e] = 0;
-                __threadfence_system();
                 uint64_t* word = reinterpret_cast<uint64_t*>(c.heap[dst] + p.off_recv_count[half]) + (e - dst * EL) * R + c.rank;
                 st_release_sys_u64(word, pack_epoch(epoch, static_cast<uint32_t>(total)));
             }
             __syncwarp();
         }
+        if (stamper) stamps[2] = globaltimer_ns();
         ll_phase_done(c, 0, nb);
+        if (stamper) stamps[3] = globaltimer_ns();
     }
 
     if (p.phases & kLLRecv) {
@@ -239,7 +243,15 @@ __global__ void __launch_bounds__(1024, 1) ll_dispatch_kernel(const __grid_const
                     p.packed_recv_src_info[out_row] = hdr.x | (hdr.y << 16);
                 }
                 uint8_t* dst = p.packed_recv_x + out_row * payload_bytes;
-                for (int v = lane; v < payload_bytes / 16; v += 32) st_na_int4(dst + v * 16, ld_nc_int4(src + 16 + v * 16));
+                for (int v = lane; v < payload_bytes / 16; v += 32 * 8) {   // eight loads in flight per lane
+                    int4 tmp[8];
+#pragma unroll
+                    for (int u = 0; u < 8; ++u)
+                        if (v + 32 * u < payload_bytes / 16) tmp[u] = ld_nc_int4(src + 16 + (v + 32 * u) * 16);
+#pragma unroll
+                    for (int u = 0; u < 8; ++u)
+                        if (v + 32 * u < payload_bytes / 16) st_na_int4(dst + (v + 32 * u) * 16, tmp[u]);
+                }
                 if (sf_per_row > 0) {
                     const uint32_t* sf = reinterpret_cast<const uint32_t*>(src + 16 + H);
                     uint32_t* out_sf = reinterpret_cast<uint32_t*>(p.packed_recv_sf);
@@ -248,7 +260,9 @@ __global__ void __launch_bounds__(1024, 1) ll_dispatch_kernel(const __grid_const
                 }
             }
         }
+        if (stamper) stamps[4] = globaltimer_ns();
         ll_phase_done(c, 1, nb);
+        if (stamper) stamps[5] = globaltimer_ns();
     }
 }
 
@@ -307,7 +321,14 @@ __global__ void __launch_bounds__(1024, 1) ll_combine_kernel(const __grid_consta
         uint32_t parity = 0;
         for (int g = bid * num_warps + warp; g < total_rows; g += nb * num_warps) {
             int le = 0;
-            while (le < EL - 1 && g >= s_pref[le + 1]) ++le;
+            {   // largest le with s_pref[le] <= g
+                int lo = 0, hi = EL - 1;
+                while (lo < hi) {
+                    const int mid = (lo + hi + 1) >> 1;
+                    if (s_pref[mid] <= g) lo = mid; else hi = mid - 1;
+                }
+                le = lo;
+            }
             const int j = g - s_pref[le];
             int s = 0;
             while (s < R - 1 && j >= static_cast<int>(p.layout_range[le * R + s + 1] >> 32)) ++s;
@@ -329,8 +350,7 @@ __global__ void __launch_bounds__(1024, 1) ll_combine_kernel(const __grid_consta
                 bulk_commit();
                 bulk_wait_all();
                 fence_proxy_async_all();
-                __threadfence_system();
-                atomicAdd(finish + le * R + s, 1);
+                red_add_release_gpu_s32(finish + le * R + s, 1);
             }
             __syncwarp();
         }
@@ -340,9 +360,8 @@ __global__ void __launch_bounds__(1024, 1) ll_combine_kernel(const __grid_consta
             const int cnt = static_cast<int>(p.layout_range[q] & 0xffffffff);
             if (cnt == 0 || ld_volatile_int(mask + s) != 0) continue;
             if (lane == 0) {
-                bounded_wait(w, kStatusLLCombine, s, q, [&]() { return ld_volatile_int(finish + q) >= cnt; });
+                bounded_wait(w, kStatusLLCombine, s, q, [&]() { return ld_acquire_gpu_s32(finish + q) >= cnt; });
                 finish[q] = 0;
-                __threadfence_system();
                 uint64_t* word = reinterpret_cast<uint64_t*>(c.heap[s] + p.off_combine_flag[half]) + (c.rank * EL + le);
                 st_release_sys_u64(word, pack_epoch(epoch, 1));
             }
@@ -377,16 +396,24 @@ __global__ void __launch_bounds__(1024, 1) ll_combine_kernel(const __grid_consta
                 float acc[8];
 #pragma unroll
                 for (int i = 0; i < 8; ++i) acc[i] = 0.f;
-                for (int k = 0; k < K; ++k) {
-                    if (!s_ok[k]) continue;
-                    const int4 raw = ld_nc_int4(region + ((static_cast<uint64_t>(k) * Tm + t) * H + ch) * 2);
-                    const __nv_bfloat162* h2 = reinterpret_cast<const __nv_bfloat162*>(&raw);
-                    const float wk = s_w[k];
+                for (int k0 = 0; k0 < K; k0 += 8) {      // up to eight rows in flight, added in ascending lane order
+                    int4 raw[8];
 #pragma unroll
-                    for (int i = 0; i < 4; ++i) {
-                        const float2 v = __bfloat1622float2(h2[i]);
-                        acc[2 * i] = fmaf(wk, v.x, acc[2 * i]);
-                        acc[2 * i + 1] = fmaf(wk, v.y, acc[2 * i + 1]);
+                    for (int u = 0; u < 8; ++u)
+                        if (k0 + u < K && s_ok[k0 + u])
+                            raw[u] = ld_nc_int4(region + ((static_cast<uint64_t>(k0 + u) * Tm + t) * H + ch) * 2);
+#pragma unroll
+                    for (int u = 0; u < 8; ++u) {
+                        if (k0 + u < K && s_ok[k0 + u]) {
+                            const __nv_bfloat162* h2 = reinterpret_cast<const __nv_bfloat162*>(&raw[u]);
+                            const float wk = s_w[k0 + u];
+#pragma unroll
+                            for (int i = 0; i < 4; ++i) {
+                                const float2 v = __bfloat1622float2(h2[i]);
+                                acc[2 * i] = fmaf(wk, v.x, acc[2 * i]);
+                                acc[2 * i + 1] = fmaf(wk, v.y, acc[2 * i + 1]);
+                            }
+                        }
                     }
                 }
                 int4 out;
