@@ -52,15 +52,18 @@ struct Scheduler {
 
 template <int BN, bool kFp8>
 struct Cfg {
-    static constexpr int kEpiWarps = kFp8 ? 8 : 4;
+    static constexpr int kEpiWarps = kFp8 ? 16 : 4;     // FP8: 4 lane quarters x 4 column quarters, so that many passes overlap
     static constexpr int kThreads = (2 + kEpiWarps) * 32;
     static constexpr int BK = kFp8 ? 128 : 64;          // one 128-byte swizzle span per row
     static constexpr int UMMA_K = kFp8 ? 32 : 16;
     static constexpr int A_BYTES = BM * 128, B_BYTES = BN * 128, STAGE = A_BYTES + B_BYTES;
     static constexpr int kStages = (192 * 1024) / STAGE;
-    static constexpr int kBarBytes = (2 * kStages + 4) * 8 + 16;
+    // accumulators in tensor memory: two tiles for bf16; with FP8 every k-block is an accumulator pass and the
+    // epilogue is the slower side, so four passes may be in flight
+    static constexpr int kAccStages = kFp8 ? 4 : 2;
+    static constexpr int kBarBytes = (2 * kStages + 2 * kAccStages) * 8 + 16;
     static constexpr int kSmem = kStages * STAGE + kBarBytes + 1024;   // + slack to align the ring to 1024 bytes
-    static constexpr int kTmemCols = 2 * BN;
+    static constexpr int kTmemCols = kAccStages * BN;
 };
 
 template <int BN, bool kFp8>
@@ -72,8 +75,8 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
     uint64_t* full = reinterpret_cast<uint64_t*>(smem + C::kStages * C::STAGE);
     uint64_t* empty = full + C::kStages;
     uint64_t* tmem_full = empty + C::kStages;
-    uint64_t* tmem_empty = tmem_full + 2;
-    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(tmem_empty + 2);
+    uint64_t* tmem_empty = tmem_full + C::kAccStages;
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(tmem_empty + C::kAccStages);
 
     const int warp = warp_id(), lane = lane_id();
     const int num_kb = p.K / C::BK;
@@ -86,7 +89,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
             mbar_init(full + s, 1);
             mbar_init(empty + s, 1);
         }
-        for (int a = 0; a < 2; ++a) {
+        for (int a = 0; a < C::kAccStages; ++a) {
             mbar_init(tmem_full + a, 1);
             mbar_init(tmem_empty + a, C::kEpiWarps * 32);
         }
@@ -152,23 +155,21 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
                     if (++s == C::kStages) { s = 0; ph ^= 1; }
                     if constexpr (kFp8) {
                         umma_commit(tmem_full + acc);
-                        acc ^= 1;
-                        if (acc == 0) acc_ph ^= 1;
+                        if (++acc == C::kAccStages) { acc = 0; acc_ph ^= 1; }
                     }
                 }
                 if constexpr (!kFp8) {
                     if (!ok) break;
                     umma_commit(tmem_full + acc);
-                    acc ^= 1;
-                    if (acc == 0) acc_ph ^= 1;
+                    if (++acc == C::kAccStages) { acc = 0; acc_ph ^= 1; }
                 }
             }
         }
     } else {
         // ------------------------------------------------------------ epilogue warps
         const int quarter = warp & 3;                  // the TMEM lanes this warp may read: [32 * quarter, +32)
-        const int part = (warp - 2) / 4;               // fp8: which half of the columns
-        constexpr int kCols = kFp8 ? BN / 2 : BN;      // columns per thread
+        const int part = (warp - 2) / 4;               // fp8: which quarter of the columns
+        constexpr int kCols = kFp8 ? BN / 4 : BN;      // columns per thread
         Scheduler sched(p, BN);
         Tile t;
         int acc = 0;
@@ -205,8 +206,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
                 }
                 tc_fence_before();
                 mbar_arrive(tmem_empty + acc);
-                acc ^= 1;
-                if (acc == 0) acc_ph ^= 1;
+                if (++acc == C::kAccStages) { acc = 0; acc_ph ^= 1; }
             } else {
                 float sum[kCols];
 #pragma unroll
@@ -220,18 +220,15 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
                     if (kb + 1 < num_kb) next_scale = sfa[static_cast<int64_t>(kb + 1) * p.sfa_k_stride] * sfb[kb + 1];
                     if (!(ok = pipe_wait(pc, tmem_full + acc, acc_ph))) break;
                     tc_fence_after();
-#pragma unroll
-                    for (int c = 0; c < kCols / 32; ++c) {
-                        uint32_t r[32];
-                        tmem_ld_32x32(lane_addr + acc * BN + part * kCols + c * 32, r);
-                        tmem_ld_wait();
-#pragma unroll
-                        for (int i = 0; i < 32; ++i) sum[c * 32 + i] = fmaf(scale, __uint_as_float(r[i]), sum[c * 32 + i]);
-                    }
+                    static_assert(kCols == 32, "the FP8 epilogue is written for 32 columns per thread");
+                    uint32_t r0[32];
+                    tmem_ld_32x32(lane_addr + acc * BN + part * kCols, r0);
+                    tmem_ld_wait();
                     tc_fence_before();
-                    mbar_arrive(tmem_empty + acc);
-                    acc ^= 1;
-                    if (acc == 0) acc_ph ^= 1;
+                    mbar_arrive(tmem_empty + acc);      // the values are in registers: the accumulator can be reused
+                    if (++acc == C::kAccStages) { acc = 0; acc_ph ^= 1; }
+#pragma unroll
+                    for (int i = 0; i < 32; ++i) sum[i] = fmaf(scale, __uint_as_float(r0[i]), sum[i]);
                 }
                 if (ok && zero_row) {
 #pragma unroll
