@@ -135,24 +135,27 @@ __global__ void __launch_bounds__(kAgThreads, 1) ag_gemm_kernel(const __grid_con
         const int workers = p.num_comm_ctas * num_warps;
         const int me = bid * num_warps + warp;
         uint32_t parity = 0;
-        // Two buffers per warp: the store of row i is in flight while row i+1 is loaded. A row is
-        // counted as landed one step late, once wait_group has confirmed its store.
+        // Two buffers per warp; a buffer is reused once its store has READ it (wait_group.read), while a row is
+        // counted as landed four rows late, once wait_group has confirmed the remote writes. Several rows per
+        // lane are therefore on the wire at any time and the NVLink round trip stays off the critical path.
         auto landed_row = [&](int chunk) {
             fence_proxy_async_all();
-            __threadfence_system();
+            __threadfence();
             const int old = atomicAdd(done + chunk * kMaxRanks + lane, 1);
             if (old == BM - 1) {
                 done[chunk * kMaxRanks + lane] = 0;
-                __threadfence_system();
+                __threadfence();
                 uint64_t* flag = reinterpret_cast<uint64_t*>(c.heap[lane]) + kCtlTileFlags + c.rank * 64 + chunk;
                 st_release_sys_u64(flag, pack_epoch(p.epoch, 1));
             }
         };
         const bool sender = lane < R && lane != c.rank;
         uint8_t* buf2[2] = {buf, buf + num_warps * stage};
-        int prev_chunk = -1, it = 0;
+        int pend0 = -1, pend1 = -1, pend2 = -1, pend3 = -1, it = 0;   // chunks of the last four rows sent (oldest first)
         for (int row = me; row < Ml && R > 1; row += workers, ++it) {
             uint8_t* cur = buf2[it & 1];
+            bulk_wait_read<1>();        // the store that used this buffer two rows ago has read it
+            __syncwarp();
             if (lane == 0) {
                 mbar_arrive_expect_tx(bar, row_bytes);
                 bulk_g2s(cur, p.a_local + static_cast<int64_t>(row) * p.a_stride_bytes, row_bytes, bar);
@@ -163,15 +166,21 @@ __global__ void __launch_bounds__(kAgThreads, 1) ag_gemm_kernel(const __grid_con
             if (sender) {
                 bulk_s2g(c.heap[lane] + p.off_gather + (static_cast<uint64_t>(c.rank) * Ml + row) * row_bytes, cur, row_bytes);
                 bulk_commit();
-                bulk_wait<1>();                      // the previous row's store is complete (and its buffer free)
-                if (prev_chunk >= 0) landed_row(prev_chunk);
-                prev_chunk = row / BM;
+                bulk_wait<4>();
+                if (pend0 >= 0) landed_row(pend0);
+                pend0 = pend1;
+                pend1 = pend2;
+                pend2 = pend3;
+                pend3 = row / BM;
             }
             __syncwarp();
         }
         if (sender) {
             bulk_wait_all();
-            if (prev_chunk >= 0) landed_row(prev_chunk);
+            if (pend0 >= 0) landed_row(pend0);
+            if (pend1 >= 0) landed_row(pend1);
+            if (pend2 >= 0) landed_row(pend2);
+            if (pend3 >= 0) landed_row(pend3);
         }
         bulk_wait_all();
         return;
@@ -370,6 +379,7 @@ __global__ void __launch_bounds__(kRsThreads, 1) gemm_rs_kernel(const __grid_con
         const int quarter = warp & 3;
         int acc = 0;
         uint32_t acc_ph = 0;
+        uint64_t* prev_flag = nullptr;
         for (int t = first; t < total_tiles; t += stride) {
             int dst, lt;
             decode(t, dst, lt);
@@ -403,15 +413,26 @@ __global__ void __launch_bounds__(kRsThreads, 1) gemm_rs_kernel(const __grid_con
             uint8_t* dst_base = c.heap[dst] + part_off + ((static_cast<uint64_t>(c.rank) * Ml + local_m0 + r_in_tile) * N + n0) * 2;
             bulk_s2g(dst_base, srow, BN * 2);
             bulk_commit();
-            bulk_wait_all();
-            fence_proxy_async_all();
-            __threadfence_system();
-            __syncwarp();
-            // one arrival per epilogue warp on the tile's flag word: the reducer waits for 4 * epoch-tagged arrivals
-            if (lane == 0) {
-                uint64_t* flag = reinterpret_cast<uint64_t*>(c.heap[dst] + flag_off) + static_cast<uint64_t>(c.rank) * tiles_per_dst + lt;
-                red_add_release_sys_u64(flag, 1);
+            // The flag of the PREVIOUS tile is raised now (its stores have had a whole tile time to complete); this
+            // tile's store only has to have read the staging row before the next tile overwrites it.
+            bulk_wait<1>();
+            if (prev_flag != nullptr) {
+                fence_proxy_async_all();
+                __threadfence();
+                __syncwarp();
+                if (lane == 0) red_add_release_sys_u64(prev_flag, 1);
             }
+            prev_flag = reinterpret_cast<uint64_t*>(c.heap[dst] + flag_off) + static_cast<uint64_t>(c.rank) * tiles_per_dst + lt;
+            bulk_wait_read_all();
+            __syncwarp();
+        }
+        bulk_wait_all();
+        if (prev_flag != nullptr) {
+            fence_proxy_async_all();
+            __threadfence();
+            __syncwarp();
+            // one arrival per epilogue warp on the tile's flag word: the reducer waits for 4 arrivals per call
+            if (lane == 0) red_add_release_sys_u64(prev_flag, 1);
         }
     }
 
@@ -433,26 +454,45 @@ __global__ void __launch_bounds__(kRsThreads, 1) gemm_rs_kernel(const __grid_con
         }
         __syncthreads();
         const int local_m0 = (lt / tiles_n) * BM, n0 = (lt % tiles_n) * BN;
-        for (int v = threadIdx.x; v < BM * BN / 8; v += blockDim.x) {
-            const int r = v / (BN / 8), cv = v % (BN / 8);
-            float accv[8];
+        // Two 16-byte columns per thread and pass, all sources loaded before the first add: up to 16 loads in flight
+        // per thread, so the phase runs at memory speed instead of one load latency per source.
+        for (int v0 = threadIdx.x; v0 < BM * BN / 8; v0 += 2 * blockDim.x) {
+            int4 raw[2][kMaxRanks];
 #pragma unroll
-            for (int i = 0; i < 8; ++i) accv[i] = 0.f;
-            for (int s = 0; s < R; ++s) {
-                const int4 raw = ld_nc_int4(my_part + ((static_cast<uint64_t>(s) * Ml + local_m0 + r) * N + n0 + cv * 8) * 2);
-                const __nv_bfloat162* h2 = reinterpret_cast<const __nv_bfloat162*>(&raw);
+            for (int u = 0; u < 2; ++u) {
+                const int v = v0 + u * blockDim.x;
+                const int r = v / (BN / 8), cv = v % (BN / 8);
 #pragma unroll
-                for (int i = 0; i < 4; ++i) {
-                    const float2 f = __bfloat1622float2(h2[i]);
-                    accv[2 * i] += f.x;
-                    accv[2 * i + 1] += f.y;
-                }
+                for (int s = 0; s < kMaxRanks; ++s)
+                    if (s < R && v < BM * BN / 8)
+                        raw[u][s] = ld_nc_int4(my_part + ((static_cast<uint64_t>(s) * Ml + local_m0 + r) * N + n0 + cv * 8) * 2);
             }
-            int4 out;
-            __nv_bfloat162* o2 = reinterpret_cast<__nv_bfloat162*>(&out);
 #pragma unroll
-            for (int i = 0; i < 4; ++i) o2[i] = __floats2bfloat162_rn(accv[2 * i], accv[2 * i + 1]);
-            *reinterpret_cast<int4*>(p.out + (static_cast<int64_t>(local_m0 + r) * p.ldo + n0 + cv * 8)) = out;
+            for (int u = 0; u < 2; ++u) {
+                const int v = v0 + u * blockDim.x;
+                if (v >= BM * BN / 8) break;
+                const int r = v / (BN / 8), cv = v % (BN / 8);
+                float accv[8];
+#pragma unroll
+                for (int i = 0; i < 8; ++i) accv[i] = 0.f;
+#pragma unroll
+                for (int s = 0; s < kMaxRanks; ++s) {
+                    if (s < R) {
+                        const __nv_bfloat162* h2 = reinterpret_cast<const __nv_bfloat162*>(&raw[u][s]);
+#pragma unroll
+                        for (int i = 0; i < 4; ++i) {
+                            const float2 f = __bfloat1622float2(h2[i]);
+                            accv[2 * i] += f.x;
+                            accv[2 * i + 1] += f.y;
+                        }
+                    }
+                }
+                int4 out;
+                __nv_bfloat162* o2 = reinterpret_cast<__nv_bfloat162*>(&out);
+#pragma unroll
+                for (int i = 0; i < 4; ++i) o2[i] = __floats2bfloat162_rn(accv[2 * i], accv[2 * i + 1]);
+                *reinterpret_cast<int4*>(p.out + (static_cast<int64_t>(local_m0 + r) * p.ldo + n0 + cv * 8)) = out;
+            }
         }
         __syncthreads();
     }
