@@ -267,14 +267,18 @@ class Buffer:
         """Weighted combine of the packed expert outputs: ``combined_x[t] = sum_k w[t, k] * x_k``.
 
         ``x`` is ``[local experts, ranks * max tokens, hidden]`` bf16 (with ``zero_copy`` it is the tensor
-        from :meth:`get_next_low_latency_combine_buffer`). Returns ``(combined_x, event, hook)``.
+        from :meth:`get_next_low_latency_combine_buffer`). With ``use_logfmt`` every group of 128 channels whose
+        largest magnitude is below 1 travels as 10-bit log-format values (160 instead of 256 bytes), the other
+        groups stay bf16; ``deepep_b200.utils.math.logfmt_roundtrip`` restates the rounding. Returns
+        ``(combined_x, event, hook)``. Reference: ``deep_ep/buffers/legacy.py:640-700``.
         """
         check_torch_deterministic()
-        assert not use_logfmt, 'the LogFMT wire format is not implemented: rows travel as bf16 over NVLink'
+        assert not (use_logfmt and zero_copy), 'LogFMT encodes while staging the row: it cannot be combined with zero_copy'
         src_info, layout_range, num_max_dispatch_tokens_per_rank, hidden, num_experts = handle
         io = _C.LLCombineIO()
         io.x, io.topk_idx, io.topk_weights = x, topk_idx, topk_weights
         io.src_info, io.layout_range = src_info, layout_range
+        io.use_logfmt = bool(use_logfmt)
         if out is not None:
             io.combined_x = out
         io.wait_stats = combine_wait_recv_cost_stats[self.rank] if combine_wait_recv_cost_stats is not None and \

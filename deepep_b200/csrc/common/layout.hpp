@@ -171,13 +171,19 @@ struct LLLayout {
     uint64_t end;
 };
 
+// Bytes of one [lane][token] slot of the combine area. A LogFMT row is a table of (amax, amin) bf16 pairs, one per
+// 128 channels, followed by the groups back to back: 160 bytes for a group in the 10-bit log format, 256 for one
+// left in bf16. The slot is sized for the worst case (no group cast).
+EP_HD int ll_logfmt_meta_bytes(int hidden) { return align_up(hidden / 128 * 4, 16); }
+EP_HD int ll_combine_slot_bytes(int hidden, bool logfmt) { return hidden * 2 + (logfmt ? ll_logfmt_meta_bytes(hidden) : 0); }
+
 EP_HD LLLayout ll_layout(int num_ranks, int num_max_tokens, int hidden, int num_experts) {
     LLLayout l;
     const int num_local = num_experts / num_ranks;
     const uint64_t msg = ll_dispatch_msg_bytes(hidden, false);   // widest message
     const uint64_t recv = align_up<uint64_t>(static_cast<uint64_t>(num_local) * num_ranks * num_max_tokens * msg, 256);
     const uint64_t cnt = align_up<uint64_t>(static_cast<uint64_t>(num_local) * num_ranks * 8, 256);
-    const uint64_t comb = align_up<uint64_t>(static_cast<uint64_t>(kMaxLLTopk) * num_max_tokens * hidden * 2, 256);
+    const uint64_t comb = align_up<uint64_t>(static_cast<uint64_t>(kMaxLLTopk) * num_max_tokens * ll_combine_slot_bytes(hidden, true), 256);
     const uint64_t flag = align_up<uint64_t>(static_cast<uint64_t>(num_experts) * 8, 256);
     const uint64_t send = align_up<uint64_t>(static_cast<uint64_t>(num_local) * num_ranks * num_max_tokens * hidden * 2, 256);
     uint64_t off = kCtlBytes;

@@ -185,6 +185,7 @@ struct LLCombineParams {
     int num_tokens, hidden, num_topk, num_experts, num_local_experts, num_max_tokens;
     int phases;
     int shrink;
+    int use_logfmt;                  // rows travel in the 10-bit log format where a group of 128 channels allows it
     const uint8_t* x;                // [EL][R * T_max][hidden] bf16
     const int64_t* topk_idx;         // [T, K] routing of the tokens this rank dispatched
     const float* topk_weights;       // [T, K]

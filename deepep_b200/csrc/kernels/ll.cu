@@ -57,6 +57,144 @@ __device__ __forceinline__ void ll_phase_done(const CommCtx& c, int phase_idx, i
 }
 
 // A wait that either reports (normal mode) or masks the silent peer (shrink mode).
+
+// -------------------------------------------------------------------- LogFMT-10 (combine wire format)
+// Per group of 128 channels the sender records amax and amin of |x| (bf16). If amax < 1 and amin < amax, every value
+// becomes a sign bit and a 9-bit code on a logarithmic grid between amin and amax: code 0 is zero, code c >= 1 is
+// 2^(log_amin + (c - 1) * step) with step = (log_amax - log_amin) / 510, log_amin clipped to log_amax - 32. Sixteen
+// values pack into 160 bits (codes first, the sixteen sign bits last). Groups that do not qualify stay bf16. The
+// receiver redoes the same arithmetic on the same two bf16 numbers, so both sides agree on which groups were cast.
+// Same format and thresholds as csrc/kernels/legacy/internode_ll.cu:556-712 of the reference.
+__device__ __forceinline__ float lg2_approx(float x) {
+    float y;
+    asm("lg2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+    return y;
+}
+__device__ __forceinline__ float ex2_approx(float x) {
+    float y;
+    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+    return y;
+}
+
+struct LogFmtGroup {
+    float log_amin, step;
+    bool cast;
+};
+
+__device__ __forceinline__ LogFmtGroup logfmt_group(float amax, float amin) {
+    LogFmtGroup q;
+    const float la = lg2_approx(amax);
+    q.log_amin = fmaxf(lg2_approx(amin), la - 32.f);
+    q.cast = la < 0.f && q.log_amin < la;
+    q.step = (la - q.log_amin) * (1.f / 510.f);
+    return q;
+}
+
+// Sixteen bf16 values (eight packed words) -> five words.
+__device__ __forceinline__ void logfmt_pack16(const uint32_t* v, float log_amin, float step_inv, float rounding, uint32_t* out) {
+    uint64_t acc = 0;
+    int nbits = 0, w = 0;
+    uint32_t signs = 0;
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+        signs |= ((v[i] >> 15) & 1u) << (2 * i) | ((v[i] >> 31) & 1u) << (2 * i + 1);
+        const uint32_t a = v[i] & 0x7fff7fffu;
+        const float2 f = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&a));
+#pragma unroll
+        for (int h = 0; h < 2; ++h) {
+            const float mag = h == 0 ? f.x : f.y;
+            const uint32_t code = __float2uint_rd(fmaxf((lg2_approx(mag) - log_amin) * step_inv + rounding, 0.f));
+            acc |= static_cast<uint64_t>(code) << nbits;
+            nbits += 9;
+            if (nbits >= 32) {
+                out[w++] = static_cast<uint32_t>(acc);
+                acc >>= 32;
+                nbits -= 32;
+            }
+        }
+    }
+    out[4] = static_cast<uint32_t>(acc) | (signs << 16);   // 16 bits of codes are left, the signs fill the word
+}
+
+// acc[16] += weight * decoded value, from five words.
+__device__ __forceinline__ void logfmt_unpack16_fma(const uint32_t* in, float log_amin, float step, float weight, float* acc) {
+    const uint32_t signs = in[4] >> 16;
+#pragma unroll
+    for (int i = 0; i < 16; ++i) {
+        const int bit = 9 * i, w = bit >> 5, sh = bit & 31;
+        const uint32_t code = (sh + 9 <= 32 ? in[w] >> sh : __funnelshift_r(in[w], in[w + 1], sh)) & 0x1ffu;
+        float val = code == 0 ? 0.f : ex2_approx(static_cast<float>(code - 1) * step + log_amin);
+        if ((signs >> i) & 1u) val = -val;
+        acc[i] = fmaf(weight, val, acc[i]);
+    }
+}
+
+// Warp-collective: encodes the bf16 row at `payload` in place and fills `meta`; returns the packed payload bytes.
+// Eight groups per pass, 32 channels per lane (four lanes share a group). Every lane holds its 32 channels in
+// registers before any lane writes, and the output of a pass never reaches the input of the next one.
+__device__ __forceinline__ int logfmt_encode_row(uint8_t* meta, uint8_t* payload, int hidden, int lane) {
+    const int G = hidden / 128;
+    int packed = 0;
+    for (int b = 0; b * 8 < G; ++b) {
+        const int g = b * 8 + (lane >> 2);
+        const bool valid = g < G;
+        uint32_t v[16];
+        if (valid) {
+            const int4* src = reinterpret_cast<const int4*>(payload + (static_cast<size_t>(b) * 1024 + lane * 32) * 2);
+#pragma unroll
+            for (int i = 0; i < 4; ++i) *reinterpret_cast<int4*>(v + 4 * i) = src[i];
+        } else {
+#pragma unroll
+            for (int i = 0; i < 16; ++i) v[i] = 0;
+        }
+        __nv_bfloat162 amax2 = __floats2bfloat162_rn(0.f, 0.f);
+        uint32_t inf2 = 0x7f807f80u;
+        __nv_bfloat162 amin2 = *reinterpret_cast<__nv_bfloat162*>(&inf2);
+#pragma unroll
+        for (int i = 0; i < 16; ++i) {
+            const uint32_t a = v[i] & 0x7fff7fffu;
+            const __nv_bfloat162 h = *reinterpret_cast<const __nv_bfloat162*>(&a);
+            amax2 = __hmax2(amax2, h);
+            amin2 = __hmin2(amin2, h);
+        }
+        float amax = fmaxf(__low2float(amax2), __high2float(amax2));
+        float amin = fminf(__low2float(amin2), __high2float(amin2));
+#pragma unroll
+        for (int o = 1; o <= 2; o <<= 1) {
+            amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, o));
+            amin = fminf(amin, __shfl_xor_sync(0xffffffffu, amin, o));
+        }
+        const LogFmtGroup q = logfmt_group(amax, amin);
+        const bool cast = valid && q.cast;
+        if (valid && (lane & 3) == 0) {
+            const __nv_bfloat162 mm = __floats2bfloat162_rn(amax, amin);
+            reinterpret_cast<uint32_t*>(meta)[g] = *reinterpret_cast<const uint32_t*>(&mm);
+        }
+        const unsigned cast_mask = __ballot_sync(0xffffffffu, cast);
+        const unsigned valid_mask = __ballot_sync(0xffffffffu, valid);
+        const int off = packed + lane * 64 - 24 * __popc(cast_mask & ((1u << lane) - 1u));
+        __syncwarp();
+        if (valid) {
+            uint32_t* dst = reinterpret_cast<uint32_t*>(payload + off);
+            if (cast) {
+                const float step_inv = 1.f / q.step;
+                const float rounding = 2.f - lg2_approx((1.f + ex2_approx(q.step)) * 0.5f) * step_inv;
+                uint32_t out[10];
+                logfmt_pack16(v, q.log_amin, step_inv, rounding, out);
+                logfmt_pack16(v + 8, q.log_amin, step_inv, rounding, out + 5);
+#pragma unroll
+                for (int i = 0; i < 5; ++i) *reinterpret_cast<uint2*>(dst + 2 * i) = make_uint2(out[2 * i], out[2 * i + 1]);
+            } else if (off != (b * 1024 + lane * 32) * 2) {
+#pragma unroll
+                for (int i = 0; i < 8; ++i) *reinterpret_cast<uint2*>(dst + 2 * i) = make_uint2(v[2 * i], v[2 * i + 1]);
+            }
+        }
+        packed += __popc(valid_mask) * 64 - 24 * __popc(cast_mask);
+        __syncwarp();
+    }
+    return packed;
+}
+
 template <typename Pred>
 __device__ __forceinline__ bool ll_wait(const WaitCtx& w, const CommCtx& c, int shrink, int code, int peer, uint32_t tag, Pred pred) {
     if (!shrink) return bounded_wait(w, code, peer, tag, pred);
@@ -267,7 +405,7 @@ __global__ void __launch_bounds__(1024, 1) ll_dispatch_kernel(const __grid_const
 }
 
 // ==================================================================== combine
-__global__ void __launch_bounds__(1024, 1) ll_combine_kernel(const __grid_constant__ Multi<LLCombineParams> m) {
+__global__ void __launch_bounds__(512, 1) ll_combine_kernel(const __grid_constant__ Multi<LLCombineParams> m) {
     extern __shared__ __align__(128) uint8_t smem[];
     const int vr = blockIdx.x / m.blocks_per_rank;
     const int bid = blockIdx.x % m.blocks_per_rank;
@@ -280,6 +418,8 @@ __global__ void __launch_bounds__(1024, 1) ll_combine_kernel(const __grid_consta
     const int T = p.num_tokens, H = p.hidden, K = p.num_topk, E = p.num_experts, EL = p.num_local_experts;
     const int R = c.num_ranks, Tm = p.num_max_tokens;
     const int row_bytes = H * 2;
+    const int meta_bytes = p.use_logfmt ? ll_logfmt_meta_bytes(H) : 0;
+    const int slot_bytes = row_bytes + meta_bytes;
     const int* mask = ll_mask(c);
 
     if (p.phases & kLLSend) {
@@ -310,9 +450,10 @@ __global__ void __launch_bounds__(1024, 1) ll_combine_kernel(const __grid_consta
         }
         __syncthreads();
         const int total_rows = s_pref[EL];
-        const int stage = align_up(row_bytes, 128) + 16;
-        uint8_t* buf = smem + static_cast<size_t>(warp) * stage;
-        uint64_t* bar = reinterpret_cast<uint64_t*>(buf + align_up(row_bytes, 128));
+        const int stage = meta_bytes + align_up(row_bytes, 128) + 16;
+        uint8_t* buf = smem + static_cast<size_t>(warp) * stage;   // [meta table (LogFMT only)][row]
+        uint8_t* payload = buf + meta_bytes;
+        uint64_t* bar = reinterpret_cast<uint64_t*>(payload + align_up(row_bytes, 128));
         if (lane == 0) {
             mbar_init(bar, 1);
             fence_mbar_init();
@@ -340,13 +481,19 @@ __global__ void __launch_bounds__(1024, 1) ll_combine_kernel(const __grid_consta
             __syncwarp();
             if (lane == 0) {
                 mbar_arrive_expect_tx(bar, row_bytes);
-                bulk_g2s(buf, p.x + row * row_bytes, row_bytes, bar);
+                bulk_g2s(payload, p.x + row * row_bytes, row_bytes, bar);
             }
             const bool landed = mbar_wait(w, bar, parity, kStatusTmaLoad, g);
             parity ^= 1;
             if (!__all_sync(0xffffffffu, landed)) break;
+            int send_bytes = row_bytes;
+            if (p.use_logfmt) {
+                send_bytes = meta_bytes + logfmt_encode_row(buf, payload, H, lane);
+                fence_proxy_async_smem();
+                __syncwarp();
+            }
             if (lane == 0) {
-                bulk_s2g(c.heap[s] + p.off_combine_x[half] + (static_cast<uint64_t>(k) * Tm + token) * row_bytes, buf, row_bytes);
+                bulk_s2g(c.heap[s] + p.off_combine_x[half] + (static_cast<uint64_t>(k) * Tm + token) * slot_bytes, buf, send_bytes);
                 bulk_commit();
                 bulk_wait_all();
                 fence_proxy_async_all();
@@ -392,6 +539,91 @@ __global__ void __launch_bounds__(1024, 1) ll_combine_kernel(const __grid_consta
                 s_w[tid] = p.topk_weights[static_cast<int64_t>(t) * K + tid];
             }
             __syncthreads();
+            if (p.use_logfmt) {
+                // ---- per (lane, group): cast or not, grid parameters, byte offset of the group in the packed row
+                const int G = H / 128;
+                float* s_lmin = reinterpret_cast<float*>(smem);
+                float* s_step = s_lmin + K * G;
+                int* s_off = reinterpret_cast<int*>(s_step + K * G);
+                for (int k = warp; k < K; k += num_warps) {
+                    if (!s_ok[k]) continue;
+                    const uint8_t* row = region + (static_cast<uint64_t>(k) * Tm + t) * slot_bytes;
+                    int carry = 0;
+                    for (int g0 = 0; g0 < G; g0 += 32) {
+                        const int g = g0 + lane;
+                        int size = 0;
+                        if (g < G) {
+                            const uint32_t mw = ld_nc_u32(row + g * 4);
+                            const __nv_bfloat162 mm = *reinterpret_cast<const __nv_bfloat162*>(&mw);
+                            const LogFmtGroup q = logfmt_group(__low2float(mm), __high2float(mm));
+                            size = q.cast ? 160 : 256;
+                            s_lmin[k * G + g] = q.log_amin;
+                            s_step[k * G + g] = q.cast ? q.step : -1.f;
+                        }
+                        int incl = size;
+#pragma unroll
+                        for (int o = 1; o < 32; o <<= 1) {
+                            const int up = __shfl_up_sync(0xffffffffu, incl, o);
+                            if (lane >= o) incl += up;
+                        }
+                        if (g < G) s_off[k * G + g] = carry + incl - size;
+                        carry += __shfl_sync(0xffffffffu, incl, 31);
+                    }
+                }
+                __syncthreads();
+                for (int u = tid; u < H / 16; u += blockDim.x) {     // sixteen channels per thread and pass
+                    const int g = u >> 3, j = u & 7;
+                    float acc[16];
+#pragma unroll
+                    for (int i = 0; i < 16; ++i) acc[i] = 0.f;
+                    for (int k0 = 0; k0 < K; k0 += 4) {              // four rows in flight, added in ascending lane order
+                        uint32_t raw[4][8];
+                        float step[4];
+#pragma unroll
+                        for (int q = 0; q < 4; ++q) {
+                            const int k = k0 + q;
+                            step[q] = 0.f;
+                            if (k < K && s_ok[k]) {
+                                const uint8_t* src = region + (static_cast<uint64_t>(k) * Tm + t) * slot_bytes + meta_bytes + s_off[k * G + g];
+                                step[q] = s_step[k * G + g];
+                                if (step[q] >= 0.f) {
+#pragma unroll
+                                    for (int i = 0; i < 5; ++i) raw[q][i] = ld_nc_u32(src + j * 20 + i * 4);
+                                } else {
+                                    *reinterpret_cast<int4*>(raw[q]) = ld_nc_int4(src + j * 32);
+                                    *reinterpret_cast<int4*>(raw[q] + 4) = ld_nc_int4(src + j * 32 + 16);
+                                }
+                            }
+                        }
+#pragma unroll
+                        for (int q = 0; q < 4; ++q) {
+                            const int k = k0 + q;
+                            if (k < K && s_ok[k]) {
+                                const float wk = s_w[k];
+                                if (step[q] >= 0.f) {
+                                    logfmt_unpack16_fma(raw[q], s_lmin[k * G + g], step[q], wk, acc);
+                                } else {
+#pragma unroll
+                                    for (int i = 0; i < 8; ++i) {
+                                        const float2 v = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&raw[q][i]));
+                                        acc[2 * i] = fmaf(wk, v.x, acc[2 * i]);
+                                        acc[2 * i + 1] = fmaf(wk, v.y, acc[2 * i + 1]);
+                                    }
+                                }
+                            }
+                        }
+                    }
+#pragma unroll
+                    for (int h = 0; h < 2; ++h) {
+                        int4 out;
+                        __nv_bfloat162* o2 = reinterpret_cast<__nv_bfloat162*>(&out);
+#pragma unroll
+                        for (int i = 0; i < 4; ++i) o2[i] = __floats2bfloat162_rn(acc[h * 8 + 2 * i], acc[h * 8 + 2 * i + 1]);
+                        st_na_int4(p.combined_x + (static_cast<int64_t>(t) * H + u * 16 + h * 8) * 2, out);
+                    }
+                }
+                continue;
+            }
             for (int ch = tid * 8; ch < H; ch += blockDim.x * 8) {
                 float acc[8];
 #pragma unroll
@@ -459,11 +691,13 @@ cudaError_t launch_ll_dispatch(const Multi<LLDispatchParams>& m, int num_sms, cu
 
 cudaError_t launch_ll_combine(const Multi<LLCombineParams>& m, int num_sms, int smem_optin, cudaStream_t stream) {
     const LLCombineParams& p = m.r[0];
-    const int stage = align_up(p.hidden * 2, 128) + 16;
+    const int stage = (p.use_logfmt ? ll_logfmt_meta_bytes(p.hidden) : 0) + align_up(p.hidden * 2, 128) + 16;
     int warps = smem_optin / stage;
-    if (warps > 32) warps = 32;
+    if (warps > 16) warps = 16;   // 512 threads: the receive loop wants more than 64 registers per thread
     if (warps < 1) return cudaErrorInvalidValue;
     const int smem_bytes = warps * stage;
+    // the receive phase of a LogFMT call keeps three words per (lane, group) in the same shared memory
+    if (p.use_logfmt && p.num_topk * (p.hidden / 128) * 12 > smem_bytes) return cudaErrorInvalidValue;
     cudaError_t err = cudaFuncSetAttribute(ll_combine_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_bytes);
     if (err != cudaSuccess) return err;
     Multi<LLCombineParams> copy = m;

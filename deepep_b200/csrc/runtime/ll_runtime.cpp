@@ -31,6 +31,7 @@ struct LLDispatchIO {
 struct LLCombineIO {
     at::Tensor x, topk_idx, topk_weights, src_info, layout_range, combined_x;
     std::optional<at::Tensor> wait_stats;
+    bool use_logfmt = false;   // send rows in the 10-bit log format (same for all emulated ranks of a call)
 };
 
 int64_t ll_buffer_size(int num_ranks, int num_max_tokens, int hidden, int num_experts) {
@@ -134,6 +135,7 @@ std::optional<EventHandle> ll_combine(const std::vector<std::shared_ptr<Runtime>
     const int H = static_cast<int>(ios[0]->x.size(2)), K = static_cast<int>(ios[0]->topk_idx.size(1));
     const int E = num_experts, EL = E / R, Tm = num_max_tokens;
     EP_HOST_ASSERT(E % R == 0 && K <= kMaxLLTopk && K <= kMaxTopk && (H * 2) % 16 == 0);
+    EP_HOST_ASSERT_MSG(!ios[0]->use_logfmt || H % 128 == 0, "LogFMT needs a hidden size that is a multiple of 128");
     const LLLayout lay = ll_layout(R, Tm, H, E);
     EP_HOST_ASSERT_MSG(lay.end <= rt0.heap().num_bytes(), "symmetric buffer too small for low-latency mode");
     if (num_sms <= 0) num_sms = rt0.num_device_sms();   // latency-bound: one token / one (expert, source) pair per block
@@ -162,6 +164,7 @@ std::optional<EventHandle> ll_combine(const std::vector<std::shared_ptr<Runtime>
         p.num_max_tokens = Tm;
         p.phases = phases;
         p.shrink = shrink;
+        p.use_logfmt = ios[0]->use_logfmt ? 1 : 0;
         p.x = static_cast<const uint8_t*>(io.x.data_ptr());
         p.topk_idx = io.topk_idx.data_ptr<int64_t>();
         p.topk_weights = io.topk_weights.data_ptr<float>();
@@ -255,7 +258,8 @@ void register_ll_bindings(py::module_& m) {
         .def_readwrite("src_info", &LLCombineIO::src_info)
         .def_readwrite("layout_range", &LLCombineIO::layout_range)
         .def_readwrite("combined_x", &LLCombineIO::combined_x)
-        .def_readwrite("wait_stats", &LLCombineIO::wait_stats);
+        .def_readwrite("wait_stats", &LLCombineIO::wait_stats)
+        .def_readwrite("use_logfmt", &LLCombineIO::use_logfmt);
     m.def("get_dispatch_layout", &get_dispatch_layout);
     m.def("ll_buffer_size", &ll_buffer_size);
     m.def("ll_dispatch", &ll_dispatch);

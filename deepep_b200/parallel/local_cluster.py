@@ -108,7 +108,8 @@ class LocalCluster:
         return ios
 
     def low_latency_combine(self, ys, topk_idxs, topk_weights, dispatch_ios, num_max_dispatch_tokens_per_rank: int,
-                            num_experts: int, phases: Optional[int] = None, ios=None, num_sms: int = 0, shrink: bool = False):
+                            num_experts: int, phases: Optional[int] = None, ios=None, num_sms: int = 0, shrink: bool = False,
+                            use_logfmt: bool = False):
         C = self._C
         if ios is None:
             ios = []
@@ -116,6 +117,7 @@ class LocalCluster:
                 io = C.LLCombineIO()
                 io.x, io.topk_idx, io.topk_weights = y, idx, w
                 io.src_info, io.layout_range = d.src_info, d.layout_range
+                io.use_logfmt = use_logfmt
                 ios.append(io)
         phases = (C.LL_SEND | C.LL_RECV) if phases is None else phases
         C.ll_combine(self.runtimes, ios, num_max_dispatch_tokens_per_rank, num_experts, phases, num_sms, shrink, False, True)

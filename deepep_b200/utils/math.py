@@ -88,6 +88,35 @@ def per_token_cast_back(x_fp8: torch.Tensor, scales: torch.Tensor) -> torch.Tens
     return out.view(m, -1)[:, :n].to(torch.bfloat16).contiguous()
 
 
+def logfmt_roundtrip(x: torch.Tensor) -> torch.Tensor:
+    """What a bf16 tensor looks like after the LogFMT-10 wire format of the low-latency combine.
+
+    Per group of 128 channels (last dimension): with ``amax`` / ``amin`` the largest / smallest magnitude, the group
+    is encoded only if ``amax < 1`` and ``amin < amax``; then every value becomes its sign and a 9-bit code on a
+    logarithmic grid of 510 steps from ``amin`` (clipped to ``amax * 2**-32``) to ``amax``, rounded to the nearest
+    grid value in the linear domain; code 0 is an exact zero. Other groups are returned unchanged. The result is
+    float32 (the receiver accumulates in float32 before its single rounding to bf16). The GPU kernel uses the
+    hardware's approximate ``log2`` / ``exp2``, so a value that sits on a rounding boundary may land one grid step
+    away from this restatement. Reference: ``csrc/kernels/legacy/internode_ll.cu:556-712``.
+    """
+    assert x.size(-1) % 128 == 0
+    xf = x.float().reshape(-1, x.size(-1) // 128, 128)
+    mag = xf.abs()
+    amax = mag.amax(dim=-1, keepdim=True)
+    amin = mag.amin(dim=-1, keepdim=True)
+    log_amax = torch.log2(amax)
+    log_amin = torch.maximum(torch.log2(amin), log_amax - 32.0)
+    cast = (log_amax < 0) & (log_amin < log_amax)
+    step = (log_amax - log_amin) / 510.0
+    safe_step = torch.where(cast, step, torch.ones_like(step))
+    rounding = 2.0 - torch.log2((1.0 + torch.exp2(safe_step)) * 0.5) / safe_step
+    base = torch.where(cast, log_amin, torch.zeros_like(log_amin))
+    code = torch.floor(torch.clamp((torch.log2(mag) - base) / safe_step + rounding, min=0.0)).clamp(max=511.0)
+    decoded = torch.where(code == 0, torch.zeros_like(mag), torch.exp2((code - 1.0) * safe_step + base))
+    decoded = torch.where(xf < 0, -decoded, decoded)
+    return torch.where(cast, decoded, xf).reshape(x.shape)
+
+
 def inplace_unique(x: torch.Tensor, num_slots: int) -> None:
     """Rewrites every row of ``x`` to its distinct non-negative values (descending), padded with -1."""
     assert x.dim() == 2

@@ -108,6 +108,11 @@ def _subsystems_worker(rank: int, world: int, port: int):
         out, _, _ = ll.low_latency_combine(rx, idx, w, handle)
         valid_w = torch.where(idx >= 0, w, torch.zeros_like(w)).sum(dim=1, keepdim=True)
         assert torch.allclose(out.float(), x.float() * valid_w, rtol=2e-2, atol=2e-2)
+        # LogFMT wire format: small rows are really encoded (result differs from bf16) and stay within its precision
+        small = (rx.float() * 0.05).bfloat16()
+        out_log, _, _ = ll.low_latency_combine(small, idx, w, handle, use_logfmt=True)
+        want = x.float() * 0.05 * valid_w
+        assert deepep_b200.utils.math.calc_diff(out_log.float(), want) < 2e-4
     ll.check_status()
     dist.barrier()
     ll.destroy()

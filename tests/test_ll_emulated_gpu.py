@@ -92,6 +92,58 @@ def test_ll_dispatch_combine(use_fp8, round_scale, use_ue8m0):
     cl.destroy()
 
 
+def test_ll_combine_logfmt():
+    """LogFMT-10 combine: groups below 1 in magnitude travel as 10-bit codes, others as bf16; hidden sizes with a
+    partial pass of groups; checked against the torch restatement of the format and against the exact sum."""
+    from deepep_b200.utils.math import calc_diff, logfmt_roundtrip
+    for H in (1024, 1152, 7168):
+        R, T, E, K = 4, 16, 16, 4
+        EL = E // R
+        cl = _cluster(R, T, H, E)
+        xs, idxs, ws = make_routed_inputs(R, T, H, E, K, seed=21, device='cuda', masked_ratio=0.1)
+        for call in range(3):
+            ios = cl.low_latency_dispatch(xs, idxs, T, E, False, num_sms=8)
+            torch.cuda.synchronize()
+            g = torch.Generator(device='cuda').manual_seed(100 + call)
+            ys = []
+            for r in range(R):
+                y = torch.randn((EL, R * T, H), device='cuda', generator=g) * 0.1
+                y[:, :, 128:256] *= 30.0            # a group that is too large to be cast
+                y[:, :, 256:384] = 0.0              # an all-zero group
+                y[:, :, 384:512] = 0.5              # a group with amin == amax
+                y[:, ::3, 512:640] *= 1e-3          # rows with a different range
+                y[:, :, 640] = 0.0                  # an exact zero inside a cast group
+                ys.append(y.bfloat16())
+            cios = cl.low_latency_combine(ys, idxs, ws, ios, T, E, num_sms=8, use_logfmt=True)
+            torch.cuda.synchronize()
+            cl.check_status()
+            for r in range(R):
+                Tr = xs[r].size(0)
+                ref = torch.zeros((Tr, H), dtype=torch.float32, device='cuda')
+                exact = torch.zeros_like(ref)
+                for t in range(Tr):
+                    for k in range(K):
+                        e = int(idxs[r][t, k])
+                        if e < 0:
+                            continue
+                        owner, le = e // EL, e % EL
+                        j = _expected_rows(idxs, owner, le, EL).index((r, t, k))
+                        row = ys[owner][le, j]
+                        ref[t] += ws[r][t, k] * logfmt_roundtrip(row[None])[0]
+                        exact[t] += ws[r][t, k] * row.float()
+                got = cios[r].combined_x.float()
+                assert calc_diff(got, ref) < 5e-6, (H, call, r, calc_diff(got, ref))
+                assert calc_diff(got, exact) < 2e-4
+                # groups that are not cast (too large, all zero, single value) differ by the final bf16 rounding only
+                assert torch.allclose(got[:, 128:512], exact[:, 128:512], rtol=8e-3, atol=1e-6)
+                assert not torch.equal(cios[r].combined_x, exact.bfloat16())   # the format was really used
+            # the same buffers serve a plain bf16 combine afterwards
+            cios = cl.low_latency_combine(ys, idxs, ws, ios, T, E, num_sms=8)
+            torch.cuda.synchronize()
+            cl.check_status()
+        cl.destroy()
+
+
 def test_ll_recv_hook_split():
     R, T, H, E, K = 2, 16, 512, 8, 2
     import deepep_b200

@@ -114,3 +114,25 @@ def test_nvlink_status_parser():
     text = 'GPU 0: NVIDIA B200\n\t Link 0: 53.125 GB/s\n\t Link 1: 53.125 GB/s\n'
     assert parse_nvlink_status(text) == (2, 53.125)
     assert parse_nvlink_status('nothing') == (0, 0.0)
+
+
+def test_logfmt_roundtrip_oracle():
+    """The torch restatement of the LogFMT-10 wire format: which groups are encoded, exact values, error bound."""
+    from deepep_b200.utils.math import logfmt_roundtrip
+    torch.manual_seed(3)
+    x = (torch.randn(8, 512) * 0.1).bfloat16()
+    x[:, 128:256] *= 40          # amax >= 1: stays bf16
+    x[:, 256:384] = 0            # all zero: stays as is
+    x[:, 384:512] = -0.25        # single magnitude: stays as is
+    x[0, 5] = 0
+    y = logfmt_roundtrip(x)
+    assert torch.equal(y[:, 128:], x[:, 128:].float())
+    assert y[0, 5] == 0
+    a, b = y[:, :128], x[:, :128].float()
+    assert not torch.equal(a, b)
+    assert torch.equal(torch.sign(a), torch.sign(b))
+    nz = b != 0
+    assert ((a - b).abs()[nz] / b.abs()[nz]).max() < 0.025       # half a grid step of at most 32 / 510 octaves
+    # the extreme values of a group are grid points
+    amax = b.abs().amax(dim=1)
+    assert torch.allclose(a.abs().amax(dim=1), amax, rtol=1e-5)
