@@ -122,6 +122,9 @@ class ElasticBuffer:
         assert 1 <= self.num_ranks <= _C.MAX_RANKS, f'one NVLink domain holds at most {_C.MAX_RANKS} ranks'
         self.allow_hybrid_mode = allow_hybrid_mode
         self.allow_multiple_reduction = allow_multiple_reduction
+        # the combine sums a token's rows inside the send kernel while later rows are still in flight;
+        # EP_COMBINE_FUSED_REDUCE=0 brings back the separate reduce kernel on all SMs
+        self.fuse_combine_reduce = os.environ.get('EP_COMBINE_FUSED_REDUCE', '1') != '0'
         self.prefer_overlap_with_compute = prefer_overlap_with_compute
         self.deterministic = deterministic
         self.use_fp8_dispatch = use_fp8_dispatch
@@ -495,6 +498,8 @@ class ElasticBuffer:
         a.num_sms = num_sms if num_sms > 0 else handle.num_sms
         a.do_expand = handle.do_expand
         a.allow_multiple_reduction = self.allow_multiple_reduction
+        a.dst_slot = handle.dst_buffer_slot_idx
+        a.fuse_reduce = self.fuse_combine_reduce
         sc = a.sc
         sc.previous_event = previous_event
         sc.previous_event_before_epilogue = previous_event_before_epilogue

@@ -98,6 +98,12 @@ __device__ __forceinline__ int ld_acquire_gpu_s32(const int* p) {
 __device__ __forceinline__ void fence_acq_rel_sys() { asm volatile("fence.acq_rel.sys;" ::: "memory"); }
 __device__ __forceinline__ void fence_acq_rel_gpu() { asm volatile("fence.acq_rel.gpu;" ::: "memory"); }
 
+__device__ __forceinline__ int atom_add_acq_rel_gpu_s32(int* p, int v) {
+    int old;
+    asm volatile("atom.add.acq_rel.gpu.global.s32 %0, [%1], %2;" : "=r"(old) : "l"(p), "r"(v) : "memory");
+    return old;
+}
+
 // 16-byte streaming accesses (read-once data: keep it out of L1).
 __device__ __forceinline__ int4 ld_nc_int4(const void* p) {
     int4 v;

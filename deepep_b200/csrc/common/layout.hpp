@@ -63,6 +63,7 @@ constexpr int kWsPoison = 1;         // non-zero after any wait of this rank gav
 constexpr int kWsStamps = 2;         // [8] phase timestamps of the last dispatch (block 0, ns)
 constexpr int kWsWork = 10;          // next token index handed out by the dynamic send loops
 constexpr int kWsLLCalls = 11;       // [4] low-latency call counters: dispatch send, dispatch recv, combine send, combine recv
+constexpr int kWsWorkReduce = 15;    // next token handed out by the fused reduce of the combine
 constexpr int kWsScratch = 16;       // start of per-block scratch counters
 // scratch: int32 [kMaxBlocks][kMaxRanks + kMaxExperts]
 constexpr size_t kWsScratchInts = static_cast<size_t>(kMaxBlocks) * (kMaxRanks + kMaxExperts);
@@ -120,12 +121,17 @@ EP_HD int ht_meta_bytes_max(int hidden, int num_topk) {
     return ht_meta_bytes(ceil_div(hidden, 128) * 4, num_topk);
 }
 
+// received rows per arrival flag of the combine with fused reduce
+constexpr int kCombineFlagRows = 32;
+
 struct HtLayout {
     // all offsets are bytes from the heap base
     uint64_t dispatch_x[2];
     uint64_t dispatch_meta[2];
     uint64_t combine_x[2];
     uint64_t combine_w[2];
+    uint64_t combine_flag;     // [ranks][flag chunks] arrival flags of the fused reduce + [flag chunks] int32 counters
+    int combine_flag_chunks;
     uint64_t end;
 };
 
@@ -142,6 +148,9 @@ EP_HD HtLayout ht_layout(int num_ranks, int num_max_tokens, int hidden, int num_
     uint64_t off = kCtlBytes;
     for (int s = 0; s < 2; ++s) { l.dispatch_x[s] = off; off += x_bytes; l.dispatch_meta[s] = off; off += meta_bytes; }
     for (int s = 0; s < 2; ++s) { l.combine_x[s] = off; off += crow; l.combine_w[s] = off; off += cw; }
+    l.combine_flag_chunks = static_cast<int>(ceil_div<uint64_t>(rows, kCombineFlagRows));
+    l.combine_flag = off;
+    off += align_up<uint64_t>(static_cast<uint64_t>(l.combine_flag_chunks) * (num_ranks * 8 + 4), 256);
     l.end = align_up<uint64_t>(off, kHeapAlignment);
     return l;
 }

@@ -108,32 +108,6 @@ cudaError_t launch_dispatch_epilogue(const DispatchEpilogueParams* params, int n
                                      cudaStream_t stream);
 
 // ---------------------------------------------------------------- high-throughput combine
-struct CombineParams {
-    CommCtx c;
-    int num_topk;
-    int num_max_tokens;
-    int row_bytes;            // hidden * 2 (bf16)
-    int do_expand;
-    int num_lanes;            // rows per token in the receive region (ranks, or top-k)
-    int use_rank_layout;      // 1: lane = sending rank (pre-reduced), 0: lane = top-k slot
-    const uint8_t* x;         // [N or expanded rows, hidden] bf16
-    int64_t x_stride_bytes;
-    const float* topk_weights;   // non-expand [N, K]; expand [rows]; or null
-    const int* recv_src_metadata;   // [N, K + 2]
-    const int* psum_rank;     // [R] inclusive (device truth for N)
-    uint64_t off_comb_x;
-    uint64_t off_comb_w;
-    uint32_t epoch;
-    uint64_t grid_bar_base;
-};
-struct CombineLaunch {
-    int num_sms;
-    int num_warps;
-    int smem_bytes;
-};
-bool plan_combine(const CombineParams& p, int num_sms, int smem_optin, CombineLaunch* out);
-cudaError_t launch_combine(const Multi<CombineParams>& m, const CombineLaunch& l, cudaStream_t stream);
-
 struct CombineEpilogueParams {
     int num_tokens;
     int num_topk;
@@ -151,6 +125,42 @@ struct CombineEpilogueParams {
     uint8_t* combined_x;              // [T, hidden] bf16
     float* combined_topk_weights;     // [T, K] or null
 };
+struct CombineParams {
+    CommCtx c;
+    int num_topk;
+    int num_max_tokens;
+    int row_bytes;            // hidden * 2 (bf16)
+    int do_expand;
+    int num_lanes;            // rows per token in the receive region (ranks, or top-k)
+    int use_rank_layout;      // 1: lane = sending rank (pre-reduced), 0: lane = top-k slot
+    const uint8_t* x;         // [N or expanded rows, hidden] bf16
+    int64_t x_stride_bytes;
+    const float* topk_weights;   // non-expand [N, K]; expand [rows]; or null
+    const int* recv_src_metadata;   // [N, K + 2]
+    const int* psum_rank;     // [R] inclusive (device truth for N)
+    uint64_t off_comb_x;
+    uint64_t off_comb_w;
+    uint32_t epoch;
+    uint64_t grid_bar_base;
+    // Reduce fused into the send kernel: every `kCombineFlagRows` received rows that have landed raise one flag at
+    // their source rank(s); warps that have no row to send (and the send warps once they are done) sum this rank's
+    // tokens as soon as the flags of all their contributions are up. No epilogue launch then.
+    int fuse_reduce;
+    int num_send_warps;       // warps [0, num_send_warps) send; the block may carry more warps that only reduce
+    int flag_chunks;          // flag words per source rank = ceil(ranks * max tokens / kCombineFlagRows)
+    const int* dst_slot;      // [T, R] row of each of this rank's tokens in every destination's receive region (-1 = none)
+    uint64_t off_comb_flag;   // [R][flag_chunks] epoch-tagged words, then [flag_chunks] int32 rows-landed counters
+    CombineEpilogueParams red;
+};
+struct CombineLaunch {
+    int num_sms;
+    int num_warps;            // send warps (one staging buffer each)
+    int num_reduce_warps;     // extra warps of the fused reduce
+    int smem_bytes;
+};
+bool plan_combine(const CombineParams& p, int num_sms, int smem_optin, CombineLaunch* out);
+cudaError_t launch_combine(const Multi<CombineParams>& m, const CombineLaunch& l, cudaStream_t stream);
+
 cudaError_t launch_combine_epilogue(const CombineEpilogueParams* params, int num_vranks, int num_sms, cudaStream_t stream);
 
 // ---------------------------------------------------------------- layout (legacy get_dispatch_layout)

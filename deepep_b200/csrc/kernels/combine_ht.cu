@@ -10,8 +10,15 @@
 // barrier unnecessary: a peer can only be two combines ahead after this rank has finished
 // reading the half it is about to overwrite.
 //
-// Reduce epilogue (all SMs): combined_x[t] = sum over lanes in ascending order (fp32)
-// + bias_0 + bias_1, one bf16 rounding at the end; top-k weights are gathered back.
+// Reduce: combined_x[t] = sum over lanes in ascending order (fp32) + bias_0 + bias_1, one bf16
+// rounding at the end; top-k weights are gathered back. With more than one rank it runs inside
+// the send kernel: a block carries more warps than staging buffers, the extra warps (and the
+// send warps once their rows are gone) take this rank's tokens in ascending order and sum a
+// token as soon as every rank that contributes to it has raised the arrival flag of the 32-row
+// group holding its row. Senders count a row as landed three rows late (wait_group confirms the
+// remote writes by then), so the NVLink round trip never stalls a send warp. The rows just
+// received are still in L2 when they are summed. A separate epilogue kernel on all SMs does the
+// same sum for a single rank, or when an event has to be awaited between send and reduce.
 //
 // Parity: deep_ep/include/deep_ep/impls/combine.cuh:15-243, impls/combine_utils.cuh:41-170
 // and impls/combine_reduce_epilogue.cuh:12-143 of the reference.
@@ -40,6 +47,81 @@ __device__ __forceinline__ int4 pack_bf16x8(const float (&acc)[8]) {
     return out;
 }
 
+// ==================================================================== reduce of one token (one warp)
+// combined_x[t] = sum over the lanes that hold a row for the token, ascending, fp32, + bias_0 + bias_1, one bf16 rounding.
+// `e` is the lane's expert (-1 = unused top-k lane), identical on both callers.
+__device__ __forceinline__ void reduce_token(const CombineEpilogueParams& p, int t, int e, int lane) {
+    const int K = p.num_topk, EL = p.num_local_experts;
+    const int vec_per_row = p.hidden / 8;
+    const uint64_t row_bytes = static_cast<uint64_t>(p.hidden) * 2;
+    const int slot_lane = e < 0 ? -1 : (p.use_rank_layout ? e / EL : lane);
+    uint32_t mask = slot_lane >= 0 ? (1u << slot_lane) : 0u;
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) mask |= __shfl_xor_sync(0xffffffffu, mask, o);
+    if (p.combined_topk_weights != nullptr && lane < K) {
+        float wv = 0.f;
+        if (slot_lane >= 0 && p.region_w != nullptr)
+            wv = p.region_w[(static_cast<uint64_t>(slot_lane) * p.num_max_tokens + t) * K + lane];
+        p.combined_topk_weights[static_cast<int64_t>(t) * K + lane] = wv;
+    }
+    const uint8_t* b0 = p.bias0 != nullptr ? p.bias0 + t * row_bytes : nullptr;
+    const uint8_t* b1 = p.bias1 != nullptr ? p.bias1 + t * row_bytes : nullptr;
+    if (__popc(mask) == 1 && b0 == nullptr && b1 == nullptr) {
+        // a single contribution (e.g. one rank): the sum is a copy; keep four loads in flight per lane
+        const uint8_t* src = p.region_x + (static_cast<uint64_t>(__ffs(mask) - 1) * p.num_max_tokens + t) * row_bytes;
+        uint8_t* dst = p.combined_x + t * row_bytes;
+        for (int v = lane; v < vec_per_row; v += 128) {
+            int4 raw[4];
+#pragma unroll
+            for (int j = 0; j < 4; ++j)
+                if (v + 32 * j < vec_per_row) raw[j] = ld_nc_int4(src + (v + 32 * j) * 16);
+#pragma unroll
+            for (int j = 0; j < 4; ++j)
+                if (v + 32 * j < vec_per_row) st_na_int4(dst + (v + 32 * j) * 16, raw[j]);
+        }
+        return;
+    }
+    for (int v = lane; v < vec_per_row; v += 32) {
+        float acc[8];
+#pragma unroll
+        for (int j = 0; j < 8; ++j) acc[j] = 0.f;
+        // all loads of a group of eight lanes are issued before the first add (memory-level parallelism);
+        // the adds then run in ascending lane order
+        for (int base = 0; base < p.num_lanes; base += 8) {
+            const uint32_t group = (mask >> base) & 0xffu;
+            if (group == 0) continue;
+            int4 raw[8];
+#pragma unroll
+            for (int l = 0; l < 8; ++l)
+                if ((group >> l) & 1u)
+                    raw[l] = ld_nc_int4(p.region_x + (static_cast<uint64_t>(base + l) * p.num_max_tokens + t) * row_bytes + v * 16);
+#pragma unroll
+            for (int l = 0; l < 8; ++l)
+                if ((group >> l) & 1u) accumulate_bf16x8(acc, raw[l]);
+        }
+        if (b0 != nullptr) accumulate_bf16x8(acc, ld_nc_int4(b0 + v * 16));
+        if (b1 != nullptr) accumulate_bf16x8(acc, ld_nc_int4(b1 + v * 16));
+        st_na_int4(p.combined_x + t * row_bytes + v * 16, pack_bf16x8(acc));
+    }
+}
+
+__device__ __forceinline__ int token_expert(const CombineEpilogueParams& p, int t, int lane) {
+    if (lane >= p.num_topk) return -1;
+    const int64_t raw = p.topk_idx[static_cast<int64_t>(t) * p.num_topk + lane];
+    return (raw >= 0 && raw < static_cast<int64_t>(p.num_local_experts) * p.num_ranks) ? static_cast<int>(raw) : -1;
+}
+
+// ==================================================================== reduce epilogue (local, all SMs)
+__global__ void __launch_bounds__(512) combine_epilogue_kernel(const __grid_constant__ Multi<CombineEpilogueParams> m) {
+    const int vr = blockIdx.x / m.blocks_per_rank;
+    const int bid = blockIdx.x % m.blocks_per_rank;
+    const int nb = m.blocks_per_rank;
+    const CombineEpilogueParams& p = m.r[vr];
+    const int lane = lane_id(), warp = warp_id();
+    const int num_warps = blockDim.x >> 5;
+    for (int t = bid * num_warps + warp; t < p.num_tokens; t += nb * num_warps) reduce_token(p, t, token_expert(p, t, lane), lane);
+}
+
 __global__ void __launch_bounds__(1024, 1) combine_kernel(const __grid_constant__ Multi<CombineParams> m) {
     extern __shared__ __align__(128) uint8_t smem[];
     const int vr = blockIdx.x / m.blocks_per_rank;
@@ -49,18 +131,58 @@ __global__ void __launch_bounds__(1024, 1) combine_kernel(const __grid_constant_
     const CommCtx& c = p.c;
     const WaitCtx w = make_wait_ctx(c);
     const int tid = threadIdx.x, lane = lane_id(), warp = warp_id();
-    const int num_warps = blockDim.x >> 5;
+    const int num_warps = p.num_send_warps;           // warps that send; the block may carry more, which only reduce
+    const bool is_sender = warp < num_warps;
     const int R = c.num_ranks, K = p.num_topk;
     uint64_t* my_ctl = reinterpret_cast<uint64_t*>(c.heap[c.rank]);
 
     const int stage = align_up(p.row_bytes, 128) + 16;
-    uint8_t* buf = smem + static_cast<size_t>(warp) * stage;
+    uint8_t* buf = smem + static_cast<size_t>(is_sender ? warp : 0) * stage;
     uint64_t* bar = reinterpret_cast<uint64_t*>(buf + align_up(p.row_bytes, 128));
-    if (lane == 0) {
+    if (is_sender && lane == 0) {
         mbar_init(bar, 1);
         fence_mbar_init();
     }
     __syncwarp();
+
+    // ---- arrival accounting of the fused reduce (lane 0 of a send warp): a row counts as landed three rows late,
+    // when wait_group has confirmed its remote writes; the warp that completes a group of kCombineFlagRows rows of
+    // this rank's receive order raises the flag at every source rank that owns one of them.
+    const int num_recv = p.psum_rank[R - 1];
+    int* landed_cnt = reinterpret_cast<int*>(c.heap[c.rank] + p.off_comb_flag + static_cast<uint64_t>(R) * p.flag_chunks * 8);
+    auto chunk_row_landed = [&](int q) {
+        fence_proxy_async_all();
+        const int lo = q * kCombineFlagRows;
+        const int hi = min(lo + kCombineFlagRows, num_recv);
+        if (atom_add_acq_rel_gpu_s32(landed_cnt + q, 1) != hi - lo - 1) return;
+        landed_cnt[q] = 0;      // the next combine starts from zero again (stream order)
+        int begin = 0;
+        for (int d = 0; d < R; ++d) {
+            const int end = p.psum_rank[d];
+            if (begin < hi && end > lo) {
+                uint64_t* flag = reinterpret_cast<uint64_t*>(c.heap[d] + p.off_comb_flag) + static_cast<uint64_t>(c.rank) * p.flag_chunks + q;
+                st_release_sys_u64(flag, pack_epoch(p.epoch, 1));
+            }
+            begin = end;
+        }
+    };
+    int pend0 = -1, pend1 = -1, pend2 = -1;       // flag groups of the last three rows sent (oldest first)
+    auto row_sent = [&](int row) {               // after bulk_commit of the row's only store
+        if (!p.fuse_reduce) return;
+        bulk_wait<3>();
+        if (pend0 >= 0) chunk_row_landed(pend0);
+        pend0 = pend1;
+        pend1 = pend2;
+        pend2 = row / kCombineFlagRows;
+    };
+    auto flush_sent = [&]() {
+        if (!p.fuse_reduce) return;
+        bulk_wait_all();
+        if (pend0 >= 0) chunk_row_landed(pend0);
+        if (pend1 >= 0) chunk_row_landed(pend1);
+        if (pend2 >= 0) chunk_row_landed(pend2);
+        pend0 = pend1 = pend2 = -1;
+    };
 
     // groups of received rows per source rank
     int group_begin = 0, group_size = 0, max_group = 0;
@@ -78,7 +200,7 @@ __global__ void __launch_bounds__(1024, 1) combine_kernel(const __grid_constant_
     const int64_t total_steps = static_cast<int64_t>(max_group) * R;
     // rows are handed out dynamically (SMs differ in how fast their peer stores drain)
     unsigned long long* work = reinterpret_cast<unsigned long long*>(c.local_ws + kWsWork);
-    int64_t g = static_cast<int64_t>(bid) * num_warps + warp;
+    int64_t g = is_sender ? static_cast<int64_t>(bid) * num_warps + warp : total_steps;
     int64_t next_g = 0;
     bool fatal = false;
     for (; g < total_steps && !fatal; g = next_g) {
@@ -115,6 +237,7 @@ __global__ void __launch_bounds__(1024, 1) combine_kernel(const __grid_constant_
             if (lane == 0) {
                 bulk_s2g(heap + p.off_comb_x + dst_row * p.row_bytes, buf, p.row_bytes);
                 bulk_commit();
+                row_sent(i);
             }
         } else if (p.use_rank_layout) {
             // expanded input: sum this token's local-expert rows in fp32 (ascending top-k lane), round once, send
@@ -141,6 +264,7 @@ __global__ void __launch_bounds__(1024, 1) combine_kernel(const __grid_constant_
             if (lane == 0) {
                 bulk_s2g(heap + p.off_comb_x + dst_row * p.row_bytes, buf, p.row_bytes);
                 bulk_commit();
+                row_sent(i);
             }
         } else {
             // expanded input, top-k layout: every expert row travels on its own
@@ -168,96 +292,56 @@ __global__ void __launch_bounds__(1024, 1) combine_kernel(const __grid_constant_
                 }
             }
             if (failed) fatal = true;
+            if (lane == 0 && p.fuse_reduce) {     // several stores per token: settle all of them, then count the token
+                flush_sent();
+                chunk_row_landed(i / kCombineFlagRows);
+            }
         }
         } while (false);
         next_g = __shfl_sync(0xffffffffu, fetched, 0);
+    }
+
+    if (lane == 0) flush_sent();
+    __syncwarp();
+
+    // ---- fused reduce: tokens in ascending order, each by one warp, as soon as the flags of its contributions are up
+    if (p.fuse_reduce) {
+        const CombineEpilogueParams& q = p.red;
+        unsigned long long* next_token = reinterpret_cast<unsigned long long*>(c.local_ws + kWsWorkReduce);
+        const uint64_t* my_flags = reinterpret_cast<const uint64_t*>(c.heap[c.rank] + p.off_comb_flag);
+        while (!fatal) {
+            unsigned long long tk = 0;
+            if (lane == 0) tk = atomicAdd(next_token, 1ull);
+            const int t = static_cast<int>(__shfl_sync(0xffffffffu, tk, 0));
+            if (t >= q.num_tokens) break;
+            const int e = token_expert(q, t, lane);
+            bool ok = true;
+            if (e >= 0) {
+                const int src = e / q.num_local_experts;
+                const int slot = p.dst_slot[static_cast<int64_t>(t) * R + src];
+                if (slot >= 0) {
+                    const uint64_t* flag = my_flags + static_cast<uint64_t>(src) * p.flag_chunks + slot / kCombineFlagRows;
+                    ok = bounded_wait(w, kStatusCombineDone, src, t, [&]() { return epoch_reached(ld_acquire_sys_u64(flag), p.epoch); });
+                }
+            }
+            if (!__all_sync(0xffffffffu, ok)) break;
+            reduce_token(q, t, e, lane);
+        }
     }
 
     bulk_wait_all();
     fence_proxy_async_all();
     __threadfence_system();
     grid_barrier(w, c.local_ws + kWsGridBarrier, p.grid_bar_base + nb, 3);
-    if (bid == 0 && tid == 0) c.local_ws[kWsWork] = 0;   // ready for the next launch (stream order)
+    if (bid == 0 && tid == 0) {   // ready for the next launch (stream order)
+        c.local_ws[kWsWork] = 0;
+        c.local_ws[kWsWorkReduce] = 0;
+    }
     if (bid == 0 && tid < R) {
         uint64_t* remote = reinterpret_cast<uint64_t*>(c.heap[tid]) + kCtlCombineDone + c.rank;
         st_release_sys_u64(remote, pack_epoch(p.epoch, 0));
         const uint64_t* word = my_ctl + kCtlCombineDone + tid;
         bounded_wait(w, kStatusCombineDone, tid, 0, [&]() { return epoch_reached(ld_acquire_sys_u64(word), p.epoch); });
-    }
-}
-
-// ==================================================================== reduce epilogue (local, all SMs)
-__global__ void __launch_bounds__(512) combine_epilogue_kernel(const __grid_constant__ Multi<CombineEpilogueParams> m) {
-    const int vr = blockIdx.x / m.blocks_per_rank;
-    const int bid = blockIdx.x % m.blocks_per_rank;
-    const int nb = m.blocks_per_rank;
-    const CombineEpilogueParams& p = m.r[vr];
-    const int lane = lane_id(), warp = warp_id();
-    const int num_warps = blockDim.x >> 5;
-    const int K = p.num_topk, EL = p.num_local_experts;
-    const int vec_per_row = p.hidden / 8;
-    const uint64_t row_bytes = static_cast<uint64_t>(p.hidden) * 2;
-
-    for (int t = bid * num_warps + warp; t < p.num_tokens; t += nb * num_warps) {
-        // which lanes of the region hold a row for this token
-        int e = -1;
-        if (lane < K) {
-            const int64_t raw = p.topk_idx[static_cast<int64_t>(t) * K + lane];
-            e = (raw >= 0 && raw < static_cast<int64_t>(EL) * p.num_ranks) ? static_cast<int>(raw) : -1;
-        }
-        const int slot_lane = e < 0 ? -1 : (p.use_rank_layout ? e / EL : lane);
-        uint32_t mask = 0;
-        {
-            uint32_t mine = slot_lane >= 0 ? (1u << slot_lane) : 0u;
-#pragma unroll
-            for (int o = 16; o > 0; o >>= 1) mine |= __shfl_xor_sync(0xffffffffu, mine, o);
-            mask = mine;
-        }
-        if (p.combined_topk_weights != nullptr && lane < K) {
-            float wv = 0.f;
-            if (slot_lane >= 0 && p.region_w != nullptr)
-                wv = p.region_w[(static_cast<uint64_t>(slot_lane) * p.num_max_tokens + t) * K + lane];
-            p.combined_topk_weights[static_cast<int64_t>(t) * K + lane] = wv;
-        }
-        const uint8_t* b0 = p.bias0 != nullptr ? p.bias0 + t * row_bytes : nullptr;
-        const uint8_t* b1 = p.bias1 != nullptr ? p.bias1 + t * row_bytes : nullptr;
-        if (__popc(mask) == 1 && b0 == nullptr && b1 == nullptr) {
-            // a single contribution (e.g. one rank): the sum is a copy; keep four loads in flight per lane
-            const uint8_t* src = p.region_x + (static_cast<uint64_t>(__ffs(mask) - 1) * p.num_max_tokens + t) * row_bytes;
-            uint8_t* dst = p.combined_x + t * row_bytes;
-            for (int v = lane; v < vec_per_row; v += 128) {
-                int4 raw[4];
-#pragma unroll
-                for (int j = 0; j < 4; ++j)
-                    if (v + 32 * j < vec_per_row) raw[j] = ld_nc_int4(src + (v + 32 * j) * 16);
-#pragma unroll
-                for (int j = 0; j < 4; ++j)
-                    if (v + 32 * j < vec_per_row) st_na_int4(dst + (v + 32 * j) * 16, raw[j]);
-            }
-            continue;
-        }
-        for (int v = lane; v < vec_per_row; v += 32) {
-            float acc[8];
-#pragma unroll
-            for (int j = 0; j < 8; ++j) acc[j] = 0.f;
-            // all loads of a group of eight lanes are issued before the first add (memory-level parallelism);
-            // the adds then run in ascending lane order
-            for (int base = 0; base < p.num_lanes; base += 8) {
-                const uint32_t group = (mask >> base) & 0xffu;
-                if (group == 0) continue;
-                int4 raw[8];
-#pragma unroll
-                for (int l = 0; l < 8; ++l)
-                    if ((group >> l) & 1u)
-                        raw[l] = ld_nc_int4(p.region_x + (static_cast<uint64_t>(base + l) * p.num_max_tokens + t) * row_bytes + v * 16);
-#pragma unroll
-                for (int l = 0; l < 8; ++l)
-                    if ((group >> l) & 1u) accumulate_bf16x8(acc, raw[l]);
-            }
-            if (b0 != nullptr) accumulate_bf16x8(acc, ld_nc_int4(b0 + v * 16));
-            if (b1 != nullptr) accumulate_bf16x8(acc, ld_nc_int4(b1 + v * 16));
-            st_na_int4(p.combined_x + t * row_bytes + v * 16, pack_bf16x8(acc));
-        }
     }
 }
 
@@ -270,6 +354,7 @@ bool plan_combine(const CombineParams& p, int num_sms, int smem_optin, CombineLa
     if (warps < 1) return false;
     out->num_sms = num_sms;
     out->num_warps = warps;
+    out->num_reduce_warps = p.fuse_reduce ? 32 - warps : 0;
     out->smem_bytes = warps * stage;
     return true;
 }
@@ -279,7 +364,7 @@ cudaError_t launch_combine(const Multi<CombineParams>& m, const CombineLaunch& l
     if (err != cudaSuccess) return err;
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3(m.num_vranks * m.blocks_per_rank);
-    cfg.blockDim = dim3(l.num_warps * 32);
+    cfg.blockDim = dim3((l.num_warps + l.num_reduce_warps) * 32);
     cfg.dynamicSmemBytes = l.smem_bytes;
     cfg.stream = stream;
     cudaLaunchAttribute attr[1];
@@ -287,7 +372,9 @@ cudaError_t launch_combine(const Multi<CombineParams>& m, const CombineLaunch& l
     attr[0].val.cooperative = 1;
     cfg.attrs = attr;
     cfg.numAttrs = 1;
-    return cudaLaunchKernelEx(&cfg, combine_kernel, m);
+    Multi<CombineParams> copy = m;
+    for (int v = 0; v < copy.num_vranks; ++v) copy.r[v].num_send_warps = l.num_warps;
+    return cudaLaunchKernelEx(&cfg, combine_kernel, copy);
 }
 
 cudaError_t launch_combine_epilogue(const CombineEpilogueParams* params, int num_vranks, int num_sms, cudaStream_t stream) {

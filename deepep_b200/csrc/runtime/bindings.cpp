@@ -103,6 +103,8 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
         .def_readwrite("num_sms", &CombineArgs::num_sms)
         .def_readwrite("do_expand", &CombineArgs::do_expand)
         .def_readwrite("allow_multiple_reduction", &CombineArgs::allow_multiple_reduction)
+        .def_readwrite("dst_slot", &CombineArgs::dst_slot)
+        .def_readwrite("fuse_reduce", &CombineArgs::fuse_reduce)
         .def_readwrite("sc", &CombineArgs::sc);
 
     py::class_<CombineResult>(m, "CombineResult")

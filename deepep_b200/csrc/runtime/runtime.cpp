@@ -452,6 +452,9 @@ std::vector<CombineResult> Runtime::combine(const std::vector<std::shared_ptr<Ru
     const int num_lanes = std::max(R, K);
     int num_sms = a0.num_sms > 0 ? a0.num_sms : 24;
     if (num_sms * V > rt0.num_device_sms_) num_sms = rt0.num_device_sms_ / V;
+    // with a single rank both halves are local copies and two plain kernels on all SMs are faster
+    bool fuse = a0.fuse_reduce && R > 1 && !a0.sc.previous_event_before_epilogue.has_value();
+    for (const auto& a : args) fuse = fuse && a.dst_slot.has_value();
 
     Multi<CombineParams> m;
     m.num_vranks = V;
@@ -521,6 +524,18 @@ std::vector<CombineResult> Runtime::combine(const std::vector<std::shared_ptr<Ru
         }
         q.combined_x = static_cast<uint8_t*>(r.combined_x.data_ptr());
         q.combined_topk_weights = r.combined_topk_weights.has_value() ? r.combined_topk_weights->data_ptr<float>() : nullptr;
+        p.fuse_reduce = fuse ? 1 : 0;
+        p.num_send_warps = 0;        // filled in by the launcher
+        p.flag_chunks = lay.combine_flag_chunks;
+        p.off_comb_flag = lay.combine_flag;
+        p.dst_slot = nullptr;
+        p.red = q;
+        if (fuse) {
+            EP_HOST_ASSERT(a.dst_slot->scalar_type() == at::kInt && a.dst_slot->is_contiguous() && a.dst_slot->dim() == 2 &&
+                           a.dst_slot->size(0) == T && a.dst_slot->size(1) == R);
+            p.dst_slot = a.dst_slot->data_ptr<int>();
+            touched.push_back(*a.dst_slot);
+        }
         for (const at::Tensor& t : {r.combined_x, a.x, a.recv_src_metadata, a.topk_idx, a.psum_rank}) touched.push_back(t);
         for (const auto& t : {r.combined_topk_weights, a.topk_weights, a.bias0, a.bias1})
             if (t.has_value()) touched.push_back(*t);
@@ -531,8 +546,10 @@ std::vector<CombineResult> Runtime::combine(const std::vector<std::shared_ptr<Ru
     CUDA_RUNTIME_CHECK(launch_combine(m, launch, stream));
     rt0.prof_record(4, stream);
     if (a0.sc.previous_event_before_epilogue.has_value()) a0.sc.previous_event_before_epilogue->stream_wait(scope.comm);
-    const int epi_sms = std::max(1, rt0.num_device_sms_ / V);
-    CUDA_RUNTIME_CHECK(launch_combine_epilogue(ep.data(), V, epi_sms, stream));
+    if (!fuse) {
+        const int epi_sms = std::max(1, rt0.num_device_sms_ / V);
+        CUDA_RUNTIME_CHECK(launch_combine_epilogue(ep.data(), V, epi_sms, stream));
+    }
     rt0.prof_record(5, stream);
     rt0.prof_valid_[1] = rt0.profiling_;
     auto event = scope.finish(a0.sc, touched);

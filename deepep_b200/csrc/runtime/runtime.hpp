@@ -78,6 +78,10 @@ struct CombineArgs {
     at::Tensor recv_src_metadata, topk_idx, psum_rank;
     int num_experts = 0, num_max_tokens = 0, num_sms = 0;
     bool do_expand = false, allow_multiple_reduction = true;
+    // [T, R] row of every token in each destination's receive region (the dispatch handle has it). With it, and
+    // unless an event has to be awaited between send and reduce, the reduce runs inside the send kernel.
+    std::optional<at::Tensor> dst_slot;
+    bool fuse_reduce = true;
     StreamControl sc;
 };
 
