@@ -225,7 +225,10 @@ def main():
         group = SingleProcessGroup()
 
     import deepep_b200
-    from deepep_b200.utils import gate
+    from deepep_b200.utils import gate, numa
+
+    # host threads and the pinned input buffers go to the NUMA node of this rank's GPU
+    numa_binding = numa.bind_to_gpu_node(dev.index if dev.index is not None else 0)
 
     T, H, E, K = args.num_tokens, args.hidden, args.num_experts, args.num_topk
     assert E % world == 0
@@ -472,6 +475,7 @@ def main():
         'config': {'model': 'DeepSeek-V3 MoE routing shape', 'tokens_per_rank': T, 'global_batch': T * world, 'seq_len': 1,
                    'hidden': H, 'num_experts': E, 'num_topk': K, 'num_sms': args.num_sms, 'parallelism': f'ep{world}',
                    'l2': 'inputs rotate over 4 buffers of 117 MB and every step writes > 126 MB of receive rows',
+                   'numa_binding_rank0': numa_binding,
                    'baseline': 'reference README EP8 SM100: 726 GB/s dispatch, 740 GB/s combine (kernel only, 64 SMs), per GPU'},
         'clocks': clocks,
         'e2e': {'value': round(e2e_value, 2), 'unit': 'GB/s', 'ms_per_step': round(e2e_ms, 4), 'steps': e2e_steps,

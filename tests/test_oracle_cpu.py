@@ -136,3 +136,23 @@ def test_logfmt_roundtrip_oracle():
     # the extreme values of a group are grid points
     amax = b.abs().amax(dim=1)
     assert torch.allclose(a.abs().amax(dim=1), amax, rtol=1e-5)
+
+
+def test_numa_helpers(tmp_path):
+    """CPU-list parsing and the sysfs lookups of utils/numa.py against a fake /sys tree."""
+    from deepep_b200.utils import numa
+    assert numa.parse_cpu_list('0-3,8,10-11\n') == [0, 1, 2, 3, 8, 10, 11]
+    assert numa.parse_cpu_list('') == []
+    dev = tmp_path / 'bus/pci/devices/0000:1b:00.0'
+    dev.mkdir(parents=True)
+    (dev / 'numa_node').write_text('1\n')
+    node = tmp_path / 'devices/system/node/node1'
+    node.mkdir(parents=True)
+    (node / 'cpulist').write_text('32-63\n')
+    assert numa.pci_numa_node('0000:1B:00.0', str(tmp_path)) == 1
+    assert numa.pci_numa_node('00000000:1b:00.0', str(tmp_path)) == 1      # NVML spelling
+    assert numa.pci_numa_node('0000:2c:00.0', str(tmp_path)) is None
+    (dev / 'numa_node').write_text('-1\n')
+    assert numa.pci_numa_node('0000:1b:00.0', str(tmp_path)) is None
+    assert numa.node_cpus(1, str(tmp_path)) == list(range(32, 64))
+    assert numa.node_cpus(7, str(tmp_path)) == []
