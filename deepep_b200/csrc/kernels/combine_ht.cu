@@ -47,6 +47,49 @@ __device__ __forceinline__ int4 pack_bf16x8(const float (&acc)[8]) {
     return out;
 }
 
+// NV columns (16 bytes each) per lane and pass, rows taken NR at a time.
+template <int NV, int NR>
+__device__ __forceinline__ void reduce_columns(const CombineEpilogueParams& p, int t, uint32_t mask, int lane, const uint8_t* b0,
+                                               const uint8_t* b1) {
+    const int vec_per_row = p.hidden / 8;
+    const uint64_t row_bytes = static_cast<uint64_t>(p.hidden) * 2;
+    for (int v = lane; v < vec_per_row; v += 32 * NV) {
+        float acc[NV][8];
+#pragma unroll
+        for (int j = 0; j < NV; ++j)
+#pragma unroll
+            for (int i = 0; i < 8; ++i) acc[j][i] = 0.f;
+        uint32_t todo = mask;
+        while (todo) {
+            int rows[NR];
+#pragma unroll
+            for (int r = 0; r < NR; ++r) {
+                rows[r] = todo ? __ffs(todo) - 1 : -1;
+                todo &= todo - 1;       // 0 stays 0
+            }
+            int4 raw[NR][NV];
+#pragma unroll
+            for (int r = 0; r < NR; ++r)
+#pragma unroll
+                for (int j = 0; j < NV; ++j)
+                    if (rows[r] >= 0 && v + 32 * j < vec_per_row)
+                        raw[r][j] = ld_nc_int4(p.region_x + (static_cast<uint64_t>(rows[r]) * p.num_max_tokens + t) * row_bytes + (v + 32 * j) * 16);
+#pragma unroll
+            for (int r = 0; r < NR; ++r)
+#pragma unroll
+                for (int j = 0; j < NV; ++j)
+                    if (rows[r] >= 0 && v + 32 * j < vec_per_row) accumulate_bf16x8(acc[j], raw[r][j]);
+        }
+#pragma unroll
+        for (int j = 0; j < NV; ++j) {
+            if (v + 32 * j >= vec_per_row) break;
+            if (b0 != nullptr) accumulate_bf16x8(acc[j], ld_nc_int4(b0 + (v + 32 * j) * 16));
+            if (b1 != nullptr) accumulate_bf16x8(acc[j], ld_nc_int4(b1 + (v + 32 * j) * 16));
+            st_na_int4(p.combined_x + t * row_bytes + (v + 32 * j) * 16, pack_bf16x8(acc[j]));
+        }
+    }
+}
+
 // ==================================================================== reduce of one token (one warp)
 // combined_x[t] = sum over the lanes that hold a row for the token, ascending, fp32, + bias_0 + bias_1, one bf16 rounding.
 // `e` is the lane's expert (-1 = unused top-k lane), identical on both callers.
@@ -81,28 +124,12 @@ __device__ __forceinline__ void reduce_token(const CombineEpilogueParams& p, int
         }
         return;
     }
-    for (int v = lane; v < vec_per_row; v += 32) {
-        float acc[8];
-#pragma unroll
-        for (int j = 0; j < 8; ++j) acc[j] = 0.f;
-        // all loads of a group of eight lanes are issued before the first add (memory-level parallelism);
-        // the adds then run in ascending lane order
-        for (int base = 0; base < p.num_lanes; base += 8) {
-            const uint32_t group = (mask >> base) & 0xffu;
-            if (group == 0) continue;
-            int4 raw[8];
-#pragma unroll
-            for (int l = 0; l < 8; ++l)
-                if ((group >> l) & 1u)
-                    raw[l] = ld_nc_int4(p.region_x + (static_cast<uint64_t>(base + l) * p.num_max_tokens + t) * row_bytes + v * 16);
-#pragma unroll
-            for (int l = 0; l < 8; ++l)
-                if ((group >> l) & 1u) accumulate_bf16x8(acc, raw[l]);
-        }
-        if (b0 != nullptr) accumulate_bf16x8(acc, ld_nc_int4(b0 + v * 16));
-        if (b1 != nullptr) accumulate_bf16x8(acc, ld_nc_int4(b1 + v * 16));
-        st_na_int4(p.combined_x + t * row_bytes + v * 16, pack_bf16x8(acc));
-    }
+    // Eight 16-byte loads are in flight per lane before the first add: eight rows of one column, or (when at most
+    // four lanes contribute) four rows of two columns. The adds run in ascending lane order either way.
+    if (__popc(mask) <= 4)
+        reduce_columns<2, 4>(p, t, mask, lane, b0, b1);
+    else
+        reduce_columns<1, 8>(p, t, mask, lane, b0, b1);
 }
 
 __device__ __forceinline__ int token_expert(const CombineEpilogueParams& p, int t, int lane) {

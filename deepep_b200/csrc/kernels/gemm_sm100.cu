@@ -6,6 +6,8 @@
 //
 // The reference library contains no GEMM; this is the compute half of the fused MoE layer and of
 // the all-gather -> GEMM / GEMM -> reduce-scatter operators (tp_fused.cu).
+#include <cstdlib>
+
 #include "gemm_api.hpp"
 #include "gemm_sm100.cuh"
 
@@ -21,9 +23,9 @@ struct Tile {
 // Walks the tiles of a (grouped) problem in a fixed order: group, then n-block, then m-block.
 struct Scheduler {
     const GemmParams& p;
-    int tiles_n, BN;
+    int tiles_n, BN, BM;
     int g = 0, base = 0, start = 0, end = 0;
-    __device__ Scheduler(const GemmParams& p_, int bn) : p(p_), tiles_n(p_.N / bn), BN(bn) {
+    __device__ Scheduler(const GemmParams& p_, int bn, int bm = gemm::BM) : p(p_), tiles_n(p_.N / bn), BN(bn), BM(bm) {
         end = p.group_end != nullptr ? p.group_end[0] : p.M;
     }
     __device__ bool get(int t, Tile& out) {
@@ -256,6 +258,163 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
     }
 }
 
+// ==================================================================== CTA-pair kernel (bf16, 256 x 256 tiles)
+// A cluster of two CTAs owns a 256 x 256 tile: CTA r loads rows [128 r, 128 r + 128) of the A tile and of the B tile
+// (32 KB per stage instead of 48 KB for a lone CTA, so six stages fit and a third less shared-memory fill traffic
+// per flop), the leader's MMA warp issues tcgen05.mma.cta_group::2 (M = 256), each CTA's epilogue warps drain the
+// 128 accumulator rows in their own tensor memory. Barriers: `full` lives in the leader and counts the bytes of both
+// CTAs; `empty` and `tmem_full` are signalled in both CTAs by one multicast commit; the leader's `tmem_empty`
+// collects the epilogue threads of both CTAs.
+struct PairCfg {
+    static constexpr int BN = 256, BK = 64, UMMA_K = 16;
+    static constexpr int A_BYTES = BM * 128, B_BYTES = (BN / 2) * 128, STAGE = A_BYTES + B_BYTES;
+    static constexpr int kStages = 6;
+    static constexpr int kAccStages = 2;
+    static constexpr int kEpiWarps = 4;
+    static constexpr int kThreads = (2 + kEpiWarps) * 32;
+    static constexpr int kBarBytes = (2 * kStages + 2 * kAccStages) * 8 + 16;
+    static constexpr int kSmem = kStages * STAGE + kBarBytes + 1024;
+    static constexpr int kTmemCols = kAccStages * BN;
+};
+
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(PairCfg::kThreads, 1)
+gemm_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b, const GemmParams p) {
+    using C = PairCfg;
+    extern __shared__ uint8_t smem_raw[];
+    uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~static_cast<uintptr_t>(1023));
+    uint64_t* full = reinterpret_cast<uint64_t*>(smem + C::kStages * C::STAGE);
+    uint64_t* empty = full + C::kStages;
+    uint64_t* tmem_full = empty + C::kStages;
+    uint64_t* tmem_empty = tmem_full + C::kAccStages;
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(tmem_empty + C::kAccStages);
+
+    const int warp = warp_id(), lane = lane_id();
+    const uint32_t cta = cluster_ctarank();
+    const bool leader = cta == 0;
+    const int pair = blockIdx.x >> 1, num_pairs = gridDim.x >> 1;
+    const int num_kb = p.K / C::BK;
+    PipeCtx pc{p.error, globaltimer_ns() + p.timeout_ns};
+
+    if (warp == 0 && lane == 0) {
+        prefetch_tensormap(&map_a);
+        prefetch_tensormap(&map_b);
+        for (int s = 0; s < C::kStages; ++s) {
+            mbar_init(full + s, 1);
+            mbar_init(empty + s, 1);
+        }
+        for (int a = 0; a < C::kAccStages; ++a) {
+            mbar_init(tmem_full + a, 1);
+            mbar_init(tmem_empty + a, 2 * C::kEpiWarps * 32);
+        }
+        fence_mbar_init();
+    }
+    if (warp == 1) {
+        tmem_alloc_pair(tmem_slot, C::kTmemCols);
+        tmem_relinquish_pair();
+    }
+    tc_fence_before();
+    cluster_sync_all();          // barriers of both CTAs are initialised before anything arrives on them
+    tc_fence_after();
+    const uint32_t tmem_base = *tmem_slot;
+
+    if (warp == 0) {
+        // ------------------------------------------------------------ TMA producer (both CTAs)
+        if (lane == 0) {
+            Scheduler sched(p, C::BN, 2 * BM);
+            Tile t;
+            int s = 0;
+            uint32_t ph = 0;
+            bool ok = true;
+            for (int ti = pair; ok && sched.get(ti, t); ti += num_pairs) {
+                for (int kb = 0; kb < num_kb; ++kb) {
+                    if (!(ok = pipe_wait(pc, empty + s, ph ^ 1))) break;
+                    uint8_t* sa = smem + s * C::STAGE;
+                    if (leader) mbar_arrive_expect_tx(full + s, 2 * C::STAGE);
+                    const uint32_t bar = map_to_cta(smem_u32(full + s), 0);
+                    tma_load_2d_pair(sa, &map_a, kb * C::BK, t.m0 + static_cast<int>(cta) * BM, bar);
+                    tma_load_2d_pair(sa + C::A_BYTES, &map_b, kb * C::BK, t.g * p.N + t.n0 + static_cast<int>(cta) * (C::BN / 2), bar);
+                    if (++s == C::kStages) { s = 0; ph ^= 1; }
+                }
+            }
+        }
+    } else if (warp == 1) {
+        // ------------------------------------------------------------ MMA issuer (leader only)
+        if (leader && lane == 0) {
+            Scheduler sched(p, C::BN, 2 * BM);
+            Tile t;
+            constexpr uint32_t idesc = make_idesc<false>(2 * BM, C::BN);
+            int s = 0, acc = 0;
+            uint32_t ph = 0, acc_ph = 0;
+            bool ok = true;
+            for (int ti = pair; ok && sched.get(ti, t); ti += num_pairs) {
+                if (!(ok = pipe_wait(pc, tmem_empty + acc, acc_ph ^ 1))) break;
+                tc_fence_after();
+                for (int kb = 0; kb < num_kb; ++kb) {
+                    if (!(ok = pipe_wait(pc, full + s, ph))) break;
+                    tc_fence_after();
+                    const uint8_t* sa = smem + s * C::STAGE;
+                    const uint64_t da = make_smem_desc(sa), db = make_smem_desc(sa + C::A_BYTES);
+                    const uint32_t d_addr = tmem_base + acc * C::BN;
+#pragma unroll
+                    for (int k = 0; k < C::BK / C::UMMA_K; ++k) umma_pair_bf16(d_addr, da + 2 * k, db + 2 * k, idesc, (kb | k) != 0);
+                    umma_commit_pair(empty + s);
+                    if (++s == C::kStages) { s = 0; ph ^= 1; }
+                }
+                if (!ok) break;
+                umma_commit_pair(tmem_full + acc);
+                if (++acc == C::kAccStages) { acc = 0; acc_ph ^= 1; }
+            }
+        }
+    } else {
+        // ------------------------------------------------------------ epilogue warps (both CTAs, own 128 rows)
+        const int quarter = warp & 3;
+        Scheduler sched(p, C::BN, 2 * BM);
+        Tile t;
+        int acc = 0;
+        uint32_t acc_ph = 0;
+        bool ok = true;
+        for (int ti = pair; ok && sched.get(ti, t); ti += num_pairs) {
+            const int row = t.m0 + static_cast<int>(cta) * BM + quarter * 32 + lane;
+            const bool row_ok = row < t.m_end && row < p.M;
+            const bool zero_row = !row_ok && p.zero_gap && row < p.M && row < align_up(t.m_end, p.group_alignment);
+            const uint32_t lane_addr = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16);
+            __nv_bfloat16* c_row = p.C + static_cast<int64_t>(row) * p.ldc + t.n0;
+            if (!(ok = pipe_wait(pc, tmem_full + acc, acc_ph))) break;
+            tc_fence_after();
+#pragma unroll 1
+            for (int c = 0; c < C::BN / 32; ++c) {
+                uint32_t r[32];
+                tmem_ld_32x32(lane_addr + acc * C::BN + c * 32, r);
+                tmem_ld_wait();
+                if (row_ok) {
+#pragma unroll
+                    for (int v = 0; v < 4; ++v) {
+                        int4 out;
+                        __nv_bfloat162* o2 = reinterpret_cast<__nv_bfloat162*>(&out);
+#pragma unroll
+                        for (int i = 0; i < 4; ++i)
+                            o2[i] = __floats2bfloat162_rn(__uint_as_float(r[v * 8 + 2 * i]), __uint_as_float(r[v * 8 + 2 * i + 1]));
+                        *reinterpret_cast<int4*>(c_row + c * 32 + v * 8) = out;
+                    }
+                } else if (zero_row) {
+#pragma unroll
+                    for (int v = 0; v < 4; ++v) *reinterpret_cast<int4*>(c_row + c * 32 + v * 8) = make_int4(0, 0, 0, 0);
+                }
+            }
+            tc_fence_before();
+            mbar_arrive_cluster(map_to_cta(smem_u32(tmem_empty + acc), 0));
+            if (++acc == C::kAccStages) { acc = 0; acc_ph ^= 1; }
+        }
+    }
+
+    tc_fence_before();
+    cluster_sync_all();          // nobody frees tensor memory, or leaves, while the peer may still signal or read
+    if (warp == 1) {
+        tc_fence_after();
+        tmem_dealloc_pair(tmem_base, C::kTmemCols);
+    }
+}
+
 // ---------------------------------------------------------------- host side
 using EncodeFn = CUresult (*)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
                               const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
@@ -305,12 +464,22 @@ cudaError_t launch_gemm(const GemmParams& p, const void* a, int64_t a_row_stride
     const int bn = fp8 ? 128 : ((p.N % 256 == 0) ? 256 : 128);
     const int bk = fp8 ? 128 : 64;
     if (p.N % bn != 0 || p.K % bk != 0 || p.M <= 0) return cudaErrorInvalidValue;
+    // bf16 with 256-wide tiles runs on CTA pairs (EP_GEMM_CTA_PAIR=0 keeps one CTA per tile); a pair needs two SMs
+    const char* pair_env = std::getenv("EP_GEMM_CTA_PAIR");
+    const bool pair_enabled = pair_env == nullptr || pair_env[0] != '0';
+    const bool use_pair = !fp8 && bn == 256 && pair_enabled && num_sms >= 2;
     CUtensorMap map_a, map_b;
     if (!make_kmajor_map(&map_a, a, elem, static_cast<uint64_t>(p.M), static_cast<uint64_t>(p.K), static_cast<uint64_t>(a_row_stride_bytes), BM) ||
         !make_kmajor_map(&map_b, b, elem, static_cast<uint64_t>(p.num_groups) * p.N, static_cast<uint64_t>(p.K),
-                         static_cast<uint64_t>(b_row_stride_bytes), static_cast<uint32_t>(bn)))
+                         static_cast<uint64_t>(b_row_stride_bytes), static_cast<uint32_t>(use_pair ? bn / 2 : bn)))
         return cudaErrorInvalidValue;
     if (fp8) return launch_cfg<128, true>(map_a, map_b, p, num_sms, stream);
+    if (bn == 256 && use_pair) {
+        cudaError_t err = cudaFuncSetAttribute(gemm_pair_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, PairCfg::kSmem);
+        if (err != cudaSuccess) return err;
+        gemm_pair_kernel<<<num_sms & ~1, PairCfg::kThreads, PairCfg::kSmem, stream>>>(map_a, map_b, p);
+        return cudaGetLastError();
+    }
     if (bn == 256) return launch_cfg<256, false>(map_a, map_b, p, num_sms, stream);
     return launch_cfg<128, false>(map_a, map_b, p, num_sms, stream);
 }

@@ -10,9 +10,13 @@ def _rel_err(got, ref):
     return ((got.float() - ref.float()).norm() / ref.float().norm().clamp(min=1e-6)).item()
 
 
-@pytest.mark.parametrize('M,N,K', [(128, 128, 64), (256, 256, 512), (1000, 384, 1024), (4096, 2304, 7168)])
-def test_gemm_bf16(M, N, K):
+@pytest.mark.parametrize('pair', ['1', '0'])
+@pytest.mark.parametrize('M,N,K', [(128, 128, 64), (256, 256, 512), (1000, 384, 1024), (1000, 512, 1024), (4096, 2304, 7168)])
+def test_gemm_bf16(M, N, K, pair, monkeypatch):
+    """`pair` selects the CTA-pair kernel (tcgen05 cta_group::2, 256-row tiles; used when N is a multiple of 256)
+    or one CTA per 128-row tile."""
     import deepep_b200
+    monkeypatch.setenv('EP_GEMM_CTA_PAIR', pair)
     g = torch.Generator(device='cuda').manual_seed(0)
     a = torch.randn((M, K), device='cuda', generator=g).bfloat16()
     b = (torch.randn((N, K), device='cuda', generator=g) * 0.05).bfloat16()
@@ -23,10 +27,12 @@ def test_gemm_bf16(M, N, K):
     assert _rel_err(out, ref) < 1e-2
 
 
-def test_grouped_gemm_bf16_with_gaps():
+@pytest.mark.parametrize('pair', ['1', '0'])
+@pytest.mark.parametrize('counts', [[200, 0, 130, 57], [100, 50, 300, 1], [128, 128, 700]])
+def test_grouped_gemm_bf16_with_gaps(counts, pair, monkeypatch):
     import deepep_b200
-    G, N, K, align = 4, 256, 512, 128
-    counts = [200, 0, 130, 57]
+    monkeypatch.setenv('EP_GEMM_CTA_PAIR', pair)
+    G, N, K, align = len(counts), 256, 512, 128
     g = torch.Generator(device='cuda').manual_seed(1)
     ends, start = [], 0
     for c in counts:
