@@ -122,9 +122,11 @@ class ElasticBuffer:
         assert 1 <= self.num_ranks <= _C.MAX_RANKS, f'one NVLink domain holds at most {_C.MAX_RANKS} ranks'
         self.allow_hybrid_mode = allow_hybrid_mode
         self.allow_multiple_reduction = allow_multiple_reduction
-        # the combine sums a token's rows inside the send kernel while later rows are still in flight;
-        # EP_COMBINE_FUSED_REDUCE=0 brings back the separate reduce kernel on all SMs
-        self.fuse_combine_reduce = os.environ.get('EP_COMBINE_FUSED_REDUCE', '1') != '0'
+        # EP_COMBINE_FUSED_REDUCE=1: the combine sums a token's rows inside the send kernel while later rows are
+        # still in flight (opt-in: on 8 x B200 the separate reduce kernel on all SMs is faster)
+        self.fuse_combine_reduce = int(os.environ.get('EP_COMBINE_FUSED_REDUCE', '0'))
+        # blocks on top of num_sms that only reduce (fused reduce); 0 = the spare warps of the send blocks do it all
+        self.num_combine_reduce_sms = int(os.environ.get('EP_COMBINE_REDUCE_SMS', '0'))
         self.prefer_overlap_with_compute = prefer_overlap_with_compute
         self.deterministic = deterministic
         self.use_fp8_dispatch = use_fp8_dispatch
@@ -500,6 +502,7 @@ class ElasticBuffer:
         a.allow_multiple_reduction = self.allow_multiple_reduction
         a.dst_slot = handle.dst_buffer_slot_idx
         a.fuse_reduce = self.fuse_combine_reduce
+        a.num_reduce_sms = self.num_combine_reduce_sms
         sc = a.sc
         sc.previous_event = previous_event
         sc.previous_event_before_epilogue = previous_event_before_epilogue

@@ -11,14 +11,15 @@
 // reading the half it is about to overwrite.
 //
 // Reduce: combined_x[t] = sum over lanes in ascending order (fp32) + bias_0 + bias_1, one bf16
-// rounding at the end; top-k weights are gathered back. With more than one rank it runs inside
+// rounding at the end; top-k weights are gathered back. By default a separate epilogue kernel on
+// all SMs does it. Optionally (fuse_reduce) it runs inside
 // the send kernel: a block carries more warps than staging buffers, the extra warps (and the
 // send warps once their rows are gone) take this rank's tokens in ascending order and sum a
 // token as soon as every rank that contributes to it has raised the arrival flag of the 32-row
 // group holding its row. Senders count a row as landed three rows late (wait_group confirms the
 // remote writes by then), so the NVLink round trip never stalls a send warp. The rows just
-// received are still in L2 when they are summed. A separate epilogue kernel on all SMs does the
-// same sum for a single rank, or when an event has to be awaited between send and reduce.
+// received are still in L2 when they are summed. Measured at EP8 (24 send SMs) the fused form
+// is reduce-bound (a warp per token needs the parallelism of the whole GPU), hence opt-in.
 //
 // Parity: deep_ep/include/deep_ep/impls/combine.cuh:15-243, impls/combine_utils.cuh:41-170
 // and impls/combine_reduce_epilogue.cuh:12-143 of the reference.
@@ -159,7 +160,8 @@ __global__ void __launch_bounds__(1024, 1) combine_kernel(const __grid_constant_
     const WaitCtx w = make_wait_ctx(c);
     const int tid = threadIdx.x, lane = lane_id(), warp = warp_id();
     const int num_warps = p.num_send_warps;           // warps that send; the block may carry more, which only reduce
-    const bool is_sender = warp < num_warps;
+    const int nb_send = p.num_send_blocks;            // blocks [nb_send, nb) have no send warps at all
+    const bool is_sender = warp < num_warps && bid < nb_send;
     const int R = c.num_ranks, K = p.num_topk;
     uint64_t* my_ctl = reinterpret_cast<uint64_t*>(c.heap[c.rank]);
 
@@ -233,7 +235,7 @@ __global__ void __launch_bounds__(1024, 1) combine_kernel(const __grid_constant_
     for (; g < total_steps && !fatal; g = next_g) {
         // the next index is requested now and only read at the end of the step (latency hidden)
         long long fetched = 0;
-        if (lane == 0) fetched = static_cast<long long>(atomicAdd(work, 1ull)) + static_cast<long long>(nb) * num_warps;
+        if (lane == 0) fetched = static_cast<long long>(atomicAdd(work, 1ull)) + static_cast<long long>(nb_send) * num_warps;
         do {
         const int d = (c.rank + 1 + static_cast<int>(g % R)) % R;
         const int idx = static_cast<int>(g / R);
@@ -401,6 +403,8 @@ cudaError_t launch_combine(const Multi<CombineParams>& m, const CombineLaunch& l
     cfg.numAttrs = 1;
     Multi<CombineParams> copy = m;
     for (int v = 0; v < copy.num_vranks; ++v) copy.r[v].num_send_warps = l.num_warps;
+    // blocks_per_rank counts the reduce-only blocks too
+
     return cudaLaunchKernelEx(&cfg, combine_kernel, copy);
 }
 

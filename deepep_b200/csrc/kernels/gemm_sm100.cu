@@ -464,9 +464,9 @@ cudaError_t launch_gemm(const GemmParams& p, const void* a, int64_t a_row_stride
     const int bn = fp8 ? 128 : ((p.N % 256 == 0) ? 256 : 128);
     const int bk = fp8 ? 128 : 64;
     if (p.N % bn != 0 || p.K % bk != 0 || p.M <= 0) return cudaErrorInvalidValue;
-    // bf16 with 256-wide tiles can run on CTA pairs (EP_GEMM_CTA_PAIR=1); a pair needs two SMs
+    // bf16 with 256-wide tiles runs on CTA pairs (EP_GEMM_CTA_PAIR=0 keeps one CTA per tile); a pair needs two SMs
     const char* pair_env = std::getenv("EP_GEMM_CTA_PAIR");
-    const bool pair_enabled = pair_env != nullptr && pair_env[0] == '1';
+    const bool pair_enabled = pair_env == nullptr || pair_env[0] != '0';
     const bool use_pair = !fp8 && bn == 256 && pair_enabled && num_sms >= 2;
     CUtensorMap map_a, map_b;
     if (!make_kmajor_map(&map_a, a, elem, static_cast<uint64_t>(p.M), static_cast<uint64_t>(p.K), static_cast<uint64_t>(a_row_stride_bytes), BM) ||

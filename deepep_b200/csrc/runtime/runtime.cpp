@@ -452,13 +452,17 @@ std::vector<CombineResult> Runtime::combine(const std::vector<std::shared_ptr<Ru
     const int num_lanes = std::max(R, K);
     int num_sms = a0.num_sms > 0 ? a0.num_sms : 24;
     if (num_sms * V > rt0.num_device_sms_) num_sms = rt0.num_device_sms_ / V;
-    // with a single rank both halves are local copies and two plain kernels on all SMs are faster
-    bool fuse = a0.fuse_reduce && R > 1 && !a0.sc.previous_event_before_epilogue.has_value();
+    // Optional: the reduce inside the send kernel. Measured on 8 x B200 it loses to the separate reduce kernel
+    // (a warp per token needs the parallelism of all SMs to reach memory speed), so it is opt-in.
+    bool fuse = a0.fuse_reduce != 0 && !a0.sc.previous_event_before_epilogue.has_value();
     for (const auto& a : args) fuse = fuse && a.dst_slot.has_value();
+    int num_reduce_sms = fuse ? std::max(0, a0.num_reduce_sms) : 0;
+    if ((num_sms + num_reduce_sms) * V > rt0.num_device_sms_) num_reduce_sms = rt0.num_device_sms_ / V - num_sms;
+    const int num_blocks = num_sms + num_reduce_sms;
 
     Multi<CombineParams> m;
     m.num_vranks = V;
-    m.blocks_per_rank = num_sms;
+    m.blocks_per_rank = num_blocks;
     std::vector<CombineResult> res(V);
     std::vector<CombineEpilogueParams> ep(V);
     std::vector<at::Tensor> touched;
@@ -495,7 +499,8 @@ std::vector<CombineResult> Runtime::combine(const std::vector<std::shared_ptr<Ru
         p.off_comb_x = lay.combine_x[slot];
         p.off_comb_w = lay.combine_w[slot];
         p.grid_bar_base = rt.grid_bar_base;
-        rt.grid_bar_base += num_sms;
+        rt.grid_bar_base += num_blocks;
+        p.num_send_blocks = num_sms;
 
         auto& r = res[v];
         r.combined_x = at::empty({T, H}, opts(at::kBFloat16, device));
@@ -541,7 +546,7 @@ std::vector<CombineResult> Runtime::combine(const std::vector<std::shared_ptr<Ru
             if (t.has_value()) touched.push_back(*t);
     }
     CombineLaunch launch;
-    EP_HOST_ASSERT_MSG(plan_combine(m.r[0], num_sms, rt0.smem_optin_, &launch), "a token row does not fit into shared memory");
+    EP_HOST_ASSERT_MSG(plan_combine(m.r[0], num_blocks, rt0.smem_optin_, &launch), "a token row does not fit into shared memory");
     rt0.prof_record(3, stream);
     CUDA_RUNTIME_CHECK(launch_combine(m, launch, stream));
     rt0.prof_record(4, stream);

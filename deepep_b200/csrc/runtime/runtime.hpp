@@ -81,7 +81,8 @@ struct CombineArgs {
     // [T, R] row of every token in each destination's receive region (the dispatch handle has it). With it, and
     // unless an event has to be awaited between send and reduce, the reduce runs inside the send kernel.
     std::optional<at::Tensor> dst_slot;
-    bool fuse_reduce = true;
+    int fuse_reduce = 0;       // non-zero: reduce inside the send kernel (opt-in)
+    int num_reduce_sms = 0;    // fused reduce: extra blocks that only reduce (on top of num_sms)
     StreamControl sc;
 };
 

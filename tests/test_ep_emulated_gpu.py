@@ -9,10 +9,14 @@ from conftest import make_routed_inputs
 pytestmark = pytest.mark.gpu
 
 
-def _cluster(num_ranks, num_max_tokens, hidden, num_topk, **kw):
+def _cluster(num_ranks, num_max_tokens, hidden, num_topk, fuse_reduce=None, **kw):
     from deepep_b200.parallel.local_cluster import LocalCluster
-    return LocalCluster(num_ranks, num_max_tokens_per_rank=num_max_tokens, hidden=hidden, num_topk=num_topk,
-                        num_gpu_timeout_secs=5, num_cpu_timeout_secs=20, **kw)
+    cl = LocalCluster(num_ranks, num_max_tokens_per_rank=num_max_tokens, hidden=hidden, num_topk=num_topk,
+                      num_gpu_timeout_secs=5, num_cpu_timeout_secs=20, **kw)
+    if fuse_reduce is not None:     # 0: separate reduce kernel, 2: reduce inside the combine's send kernel
+        for b in cl.buffers:
+            b.fuse_combine_reduce = fuse_reduce
+    return cl
 
 
 def _oracle(xs, idxs, ws, num_experts, num_max_tokens, sfs=None):
@@ -33,10 +37,11 @@ def _as_bytes(t):
     (4, 96, 1024, 32, 6, 4),
     (8, 128, 7168, 256, 8, 6),
 ])
-def test_dispatch_combine_bf16(num_ranks, num_tokens, hidden, num_experts, num_topk, num_sms):
+@pytest.mark.parametrize('fuse_reduce', [0, 2])
+def test_dispatch_combine_bf16(num_ranks, num_tokens, hidden, num_experts, num_topk, num_sms, fuse_reduce):
     from deepep_b200.utils import refs
     T_max = num_tokens
-    cl = _cluster(num_ranks, T_max, hidden, num_topk)
+    cl = _cluster(num_ranks, T_max, hidden, num_topk, fuse_reduce=fuse_reduce)
     xs, idxs, ws = make_routed_inputs(num_ranks, num_tokens, hidden, num_experts, num_topk, seed=1, device='cuda',
                                       masked_ratio=0.05)
     stats = [torch.zeros(num_experts // num_ranks, dtype=torch.int32, device='cuda') for _ in range(num_ranks)]
@@ -107,10 +112,11 @@ def test_dispatch_fp8(fused, col_major):
 
 
 @pytest.mark.parametrize('alignment,zero_padding', [(1, False), (16, True)])
-def test_dispatch_expand_and_combine(alignment, zero_padding):
+@pytest.mark.parametrize('fuse_reduce', [0, 2])
+def test_dispatch_expand_and_combine(alignment, zero_padding, fuse_reduce):
     from deepep_b200.utils import refs
     R, T, H, E, K = 4, 72, 512, 16, 3
-    cl = _cluster(R, T, H, K)
+    cl = _cluster(R, T, H, K, fuse_reduce=fuse_reduce)
     xs, idxs, ws = make_routed_inputs(R, T, H, E, K, seed=3, device='cuda', masked_ratio=0.1)
     out = cl.dispatch([dict(x=xs[r], topk_idx=idxs[r], topk_weights=ws[r], num_experts=E, num_sms=3, do_expand=True,
                             expert_alignment=alignment, do_zero_padding=zero_padding) for r in range(R)])
@@ -154,6 +160,36 @@ def test_dispatch_expand_and_combine(alignment, zero_padding):
     for r in range(R):
         ref = refs.combine_local(partial, srcs, r, xs[r].size(0), T)
         assert torch.equal(comb[r][0].cpu(), ref)
+    cl.destroy()
+
+
+@pytest.mark.parametrize('fuse_reduce', [0, 2])
+def test_combine_topk_layout_single_rounding(fuse_reduce):
+    """allow_multiple_reduction=False: every expert row travels on its own and the source rank sums them in fp32 in
+    ascending top-k order with one rounding."""
+    R, T, H, E, K = 4, 40, 512, 16, 4
+    EL = E // R
+    cl = _cluster(R, T, H, K, fuse_reduce=fuse_reduce, allow_multiple_reduction=False)
+    xs, idxs, ws = make_routed_inputs(R, T, H, E, K, seed=5, device='cuda', masked_ratio=0.1)
+    out = cl.dispatch([dict(x=xs[r], topk_idx=idxs[r], topk_weights=ws[r], num_experts=E, num_sms=3, do_expand=True)
+                       for r in range(R)])
+    torch.cuda.synchronize()
+    cl.check_status()
+    for call in range(2):
+        ys = [torch.randn(out[r][0].shape, generator=torch.Generator().manual_seed(20 + 10 * call + r)).bfloat16().cuda()
+              for r in range(R)]
+        comb = cl.combine([dict(x=ys[r], handle=out[r][3]) for r in range(R)])
+        torch.cuda.synchronize()
+        cl.check_status()
+        for r in range(R):
+            rows = out[r][3].dst_expanded_row_idx.cpu()
+            ref = torch.zeros((xs[r].size(0), H), dtype=torch.float32)
+            for k in range(K):
+                e = idxs[r][:, k].cpu()
+                for t in range(xs[r].size(0)):
+                    if e[t] >= 0:
+                        ref[t] += ys[int(e[t]) // EL][int(rows[t, k])].cpu().float()
+            assert torch.equal(comb[r][0].cpu(), ref.bfloat16())
     cl.destroy()
 
 

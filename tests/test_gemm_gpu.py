@@ -10,7 +10,7 @@ def _rel_err(got, ref):
     return ((got.float() - ref.float()).norm() / ref.float().norm().clamp(min=1e-6)).item()
 
 
-@pytest.mark.parametrize('pair', ['0'])
+@pytest.mark.parametrize('pair', ['1', '0'])
 @pytest.mark.parametrize('M,N,K', [(128, 128, 64), (256, 256, 512), (1000, 384, 1024), (1000, 512, 1024), (4096, 2304, 7168)])
 def test_gemm_bf16(M, N, K, pair, monkeypatch):
     """`pair` selects the CTA-pair kernel (tcgen05 cta_group::2, 256-row tiles; used when N is a multiple of 256)
@@ -27,7 +27,7 @@ def test_gemm_bf16(M, N, K, pair, monkeypatch):
     assert _rel_err(out, ref) < 1e-2
 
 
-@pytest.mark.parametrize('pair', ['0'])
+@pytest.mark.parametrize('pair', ['1', '0'])
 @pytest.mark.parametrize('counts', [[200, 0, 130, 57], [100, 50, 300, 1], [128, 128, 700]])
 def test_grouped_gemm_bf16_with_gaps(counts, pair, monkeypatch):
     import deepep_b200
