@@ -20,8 +20,10 @@ struct Tile {
     int g, m0, m_end, n0;
 };
 
-// Walks the tiles of a (grouped) problem in a fixed order: group, then n-block, then m-block.
+// Walks the tiles of a (grouped) problem in a fixed order: group, then bands of kBandM m-blocks, inside a band
+// n-block then m-block.
 struct Scheduler {
+    static constexpr int kBandM = 8;
     const GemmParams& p;
     int tiles_n, BN, BM;
     int g = 0, base = 0, start = 0, end = 0;
@@ -35,10 +37,14 @@ struct Scheduler {
             const int tiles = tiles_m * tiles_n;
             if (t < base + tiles) {
                 const int local = t - base;
+                // m-blocks run fastest, in bands of kBandM m-blocks: the tiles that are in flight at the same time
+                // then share few A row-blocks AND few B row-blocks, which keeps both resident in L2
+                const int band = local / (kBandM * tiles_n), rem = local % (kBandM * tiles_n);
+                const int band_m = min(kBandM, tiles_m - band * kBandM);
                 out.g = g;
-                out.m0 = start + (local % tiles_m) * BM;
+                out.m0 = start + (band * kBandM + rem % band_m) * BM;
                 out.m_end = end;
-                out.n0 = (local / tiles_m) * BN;
+                out.n0 = (rem / band_m) * BN;
                 return true;
             }
             base += tiles;
