@@ -48,6 +48,19 @@ __device__ __forceinline__ int4 pack_bf16x8(const float (&acc)[8]) {
     return out;
 }
 
+// Row copy through registers (no shared-memory staging): eight 16-byte loads in flight per lane, then posted stores.
+__device__ __noinline__ void copy_row_regs(const uint8_t* src, uint8_t* dst, int vec_per_row, int lane) {
+    for (int v = lane; v < vec_per_row; v += 256) {
+        int4 raw[8];
+#pragma unroll
+        for (int j = 0; j < 8; ++j)
+            if (v + 32 * j < vec_per_row) raw[j] = ld_nc_int4(src + (v + 32 * j) * 16);
+#pragma unroll
+        for (int j = 0; j < 8; ++j)
+            if (v + 32 * j < vec_per_row) st_na_int4(dst + (v + 32 * j) * 16, raw[j]);
+    }
+}
+
 // NV columns (16 bytes each) per lane and pass, rows taken NR at a time.
 template <int NV, int NR>
 __device__ __forceinline__ void reduce_columns(const CombineEpilogueParams& p, int t, uint32_t mask, int lane, const uint8_t* b0,
@@ -150,6 +163,9 @@ __global__ void __launch_bounds__(512) combine_epilogue_kernel(const __grid_cons
     for (int t = bid * num_warps + warp; t < p.num_tokens; t += nb * num_warps) reduce_token(p, t, token_expert(p, t, lane), lane);
 }
 
+// kFused: with the reduce of the receive side (more registers per thread; compiled apart so that the plain send
+// kernel does not pay for it)
+template <bool kFused>
 __global__ void __launch_bounds__(1024, 1) combine_kernel(const __grid_constant__ Multi<CombineParams> m) {
     extern __shared__ __align__(128) uint8_t smem[];
     const int vr = blockIdx.x / m.blocks_per_rank;
@@ -197,7 +213,7 @@ __global__ void __launch_bounds__(1024, 1) combine_kernel(const __grid_constant_
     };
     int pend0 = -1, pend1 = -1, pend2 = -1;       // flag groups of the last three rows sent (oldest first)
     auto row_sent = [&](int row) {               // after bulk_commit of the row's only store
-        if (!p.fuse_reduce) return;
+        if (!kFused) return;
         bulk_wait<3>();
         if (pend0 >= 0) chunk_row_landed(pend0);
         pend0 = pend1;
@@ -205,7 +221,7 @@ __global__ void __launch_bounds__(1024, 1) combine_kernel(const __grid_constant_
         pend2 = row / kCombineFlagRows;
     };
     auto flush_sent = [&]() {
-        if (!p.fuse_reduce) return;
+        if (!kFused) return;
         bulk_wait_all();
         if (pend0 >= 0) chunk_row_landed(pend0);
         if (pend1 >= 0) chunk_row_landed(pend1);
@@ -229,7 +245,17 @@ __global__ void __launch_bounds__(1024, 1) combine_kernel(const __grid_constant_
     const int64_t total_steps = static_cast<int64_t>(max_group) * R;
     // rows are handed out dynamically (SMs differ in how fast their peer stores drain)
     unsigned long long* work = reinterpret_cast<unsigned long long*>(c.local_ws + kWsWork);
-    int64_t g = is_sender ? static_cast<int64_t>(bid) * num_warps + warp : total_steps;
+    // Warps beyond the staging buffers can send too, through registers: their rows occupy no shared memory, which
+    // adds bytes in flight when few SMs have to fill the NVLink pipe.
+    const bool reg_sender = !is_sender && !kFused && bid < nb_send && warp < num_warps + p.num_reg_warps;
+    int64_t g = total_steps;
+    if (is_sender) {
+        g = static_cast<int64_t>(bid) * num_warps + warp;
+    } else if (reg_sender) {
+        long long first = 0;
+        if (lane == 0) first = static_cast<long long>(atomicAdd(work, 1ull)) + static_cast<long long>(nb_send) * num_warps;
+        g = __shfl_sync(0xffffffffu, first, 0);
+    }
     int64_t next_g = 0;
     bool fatal = false;
     for (; g < total_steps && !fatal; g = next_g) {
@@ -252,7 +278,7 @@ __global__ void __launch_bounds__(1024, 1) combine_kernel(const __grid_constant_
         __syncwarp();
         if (!p.do_expand) {
             // one row per received token: forward it as it is
-            if (lane == 0) {
+            if (is_sender && lane == 0) {
                 mbar_arrive_expect_tx(bar, p.row_bytes);
                 bulk_g2s(buf, p.x + static_cast<int64_t>(i) * p.x_stride_bytes, p.row_bytes, bar);
             }
@@ -260,6 +286,10 @@ __global__ void __launch_bounds__(1024, 1) combine_kernel(const __grid_constant_
             const uint64_t dst_row = static_cast<uint64_t>(slot_lane) * p.num_max_tokens + src_token;
             if (p.topk_weights != nullptr && lane < K)
                 reinterpret_cast<float*>(heap + p.off_comb_w)[dst_row * K + lane] = p.topk_weights[static_cast<int64_t>(i) * K + lane];
+            if (!is_sender) {
+                copy_row_regs(p.x + static_cast<int64_t>(i) * p.x_stride_bytes, heap + p.off_comb_x + dst_row * p.row_bytes, vec_per_row, lane);
+                break;
+            }
             const bool landed = mbar_wait(w, bar, parity, kStatusTmaLoad, i);
             parity ^= 1;
             if (!__all_sync(0xffffffffu, landed)) { fatal = true; break; }
@@ -283,11 +313,16 @@ __global__ void __launch_bounds__(1024, 1) combine_kernel(const __grid_constant_
                     const int row = __shfl_sync(0xffffffffu, my_row, k);
                     accumulate_bf16x8(acc, ld_nc_int4(p.x + static_cast<int64_t>(row) * p.x_stride_bytes + v * 16));
                 }
-                reinterpret_cast<int4*>(buf)[v] = pack_bf16x8(acc);
+                if (is_sender)
+                    reinterpret_cast<int4*>(buf)[v] = pack_bf16x8(acc);
+                else
+                    st_na_int4(heap + p.off_comb_x + (static_cast<uint64_t>(c.rank) * p.num_max_tokens + src_token) * p.row_bytes + v * 16,
+                               pack_bf16x8(acc));
             }
             const uint64_t dst_row = static_cast<uint64_t>(c.rank) * p.num_max_tokens + src_token;
             if (p.topk_weights != nullptr && my_row >= 0)
                 reinterpret_cast<float*>(heap + p.off_comb_w)[dst_row * K + lane] = p.topk_weights[my_row];
+            if (!is_sender) break;
             fence_proxy_async_smem();
             __syncwarp();
             if (lane == 0) {
@@ -306,6 +341,11 @@ __global__ void __launch_bounds__(1024, 1) combine_kernel(const __grid_constant_
                 const int k = __ffs(todo) - 1;
                 todo &= todo - 1;
                 const int row = __shfl_sync(0xffffffffu, my_row, k);
+                if (!is_sender) {
+                    copy_row_regs(p.x + static_cast<int64_t>(row) * p.x_stride_bytes,
+                                  heap + p.off_comb_x + (static_cast<uint64_t>(k) * p.num_max_tokens + src_token) * p.row_bytes, vec_per_row, lane);
+                    continue;
+                }
                 bulk_wait_read_all();
                 __syncwarp();
                 if (lane == 0) {
@@ -321,7 +361,7 @@ __global__ void __launch_bounds__(1024, 1) combine_kernel(const __grid_constant_
                 }
             }
             if (failed) fatal = true;
-            if (lane == 0 && p.fuse_reduce) {     // several stores per token: settle all of them, then count the token
+            if (is_sender && lane == 0 && kFused) {     // several stores per token: settle all of them, then count the token
                 flush_sent();
                 chunk_row_landed(i / kCombineFlagRows);
             }
@@ -334,7 +374,7 @@ __global__ void __launch_bounds__(1024, 1) combine_kernel(const __grid_constant_
     __syncwarp();
 
     // ---- fused reduce: tokens in ascending order, each by one warp, as soon as the flags of its contributions are up
-    if (p.fuse_reduce) {
+    if constexpr (kFused) {
         const CombineEpilogueParams& q = p.red;
         unsigned long long* next_token = reinterpret_cast<unsigned long long*>(c.local_ws + kWsWorkReduce);
         const uint64_t* my_flags = reinterpret_cast<const uint64_t*>(c.heap[c.rank] + p.off_comb_flag);
@@ -383,13 +423,15 @@ bool plan_combine(const CombineParams& p, int num_sms, int smem_optin, CombineLa
     if (warps < 1) return false;
     out->num_sms = num_sms;
     out->num_warps = warps;
-    out->num_reduce_warps = p.fuse_reduce ? 32 - warps : 0;
+    out->num_reduce_warps = p.fuse_reduce ? 32 - warps : min(p.num_reg_warps, 32 - warps);
     out->smem_bytes = warps * stage;
     return true;
 }
 
 cudaError_t launch_combine(const Multi<CombineParams>& m, const CombineLaunch& l, cudaStream_t stream) {
-    cudaError_t err = cudaFuncSetAttribute(combine_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, l.smem_bytes);
+    const bool fused = m.r[0].fuse_reduce != 0;
+    cudaError_t err = cudaFuncSetAttribute(fused ? combine_kernel<true> : combine_kernel<false>,
+                                           cudaFuncAttributeMaxDynamicSharedMemorySize, l.smem_bytes);
     if (err != cudaSuccess) return err;
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3(m.num_vranks * m.blocks_per_rank);
@@ -402,10 +444,13 @@ cudaError_t launch_combine(const Multi<CombineParams>& m, const CombineLaunch& l
     cfg.attrs = attr;
     cfg.numAttrs = 1;
     Multi<CombineParams> copy = m;
-    for (int v = 0; v < copy.num_vranks; ++v) copy.r[v].num_send_warps = l.num_warps;
+    for (int v = 0; v < copy.num_vranks; ++v) {
+        copy.r[v].num_send_warps = l.num_warps;
+        copy.r[v].num_reg_warps = l.num_reduce_warps;
+    }
     // blocks_per_rank counts the reduce-only blocks too
 
-    return cudaLaunchKernelEx(&cfg, combine_kernel, copy);
+    return fused ? cudaLaunchKernelEx(&cfg, combine_kernel<true>, copy) : cudaLaunchKernelEx(&cfg, combine_kernel<false>, copy);
 }
 
 cudaError_t launch_combine_epilogue(const CombineEpilogueParams* params, int num_vranks, int num_sms, cudaStream_t stream) {
