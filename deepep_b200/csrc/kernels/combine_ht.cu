@@ -256,6 +256,16 @@ __global__ void __launch_bounds__(1024, 1) combine_kernel(const __grid_constant_
         if (lane == 0) first = static_cast<long long>(atomicAdd(work, 1ull)) + static_cast<long long>(nb_send) * num_warps;
         g = __shfl_sync(0xffffffffu, first, 0);
     }
+    if (p.direct_out) {
+        // tokens without any valid expert receive no row: their result is zero
+        const int all_warps = blockDim.x >> 5;
+        for (int t = bid * all_warps + warp; t < p.red.num_tokens; t += nb * all_warps) {
+            if (__any_sync(0xffffffffu, token_expert(p.red, t, lane) >= 0)) continue;
+            for (int v = lane; v < vec_per_row; v += 32)
+                st_na_int4(p.red.combined_x + static_cast<uint64_t>(t) * p.row_bytes + v * 16, make_int4(0, 0, 0, 0));
+            if (p.red.combined_topk_weights != nullptr && lane < K) p.red.combined_topk_weights[static_cast<int64_t>(t) * K + lane] = 0.f;
+        }
+    }
     int64_t next_g = 0;
     bool fatal = false;
     for (; g < total_steps && !fatal; g = next_g) {
@@ -284,17 +294,25 @@ __global__ void __launch_bounds__(1024, 1) combine_kernel(const __grid_constant_
             }
             const int slot_lane = p.use_rank_layout ? c.rank : master_lane;
             const uint64_t dst_row = static_cast<uint64_t>(slot_lane) * p.num_max_tokens + src_token;
-            if (p.topk_weights != nullptr && lane < K)
+            uint8_t* dst_ptr = heap + p.off_comb_x + dst_row * p.row_bytes;
+            if (p.direct_out) {
+                // single rank: the row is the token's only contribution, it goes straight to the result
+                dst_ptr = p.red.combined_x + static_cast<uint64_t>(src_token) * p.row_bytes;
+                if (p.red.combined_topk_weights != nullptr && lane < K)
+                    p.red.combined_topk_weights[static_cast<int64_t>(src_token) * K + lane] =
+                        token_expert(p.red, src_token, lane) >= 0 && p.topk_weights != nullptr ? p.topk_weights[static_cast<int64_t>(i) * K + lane] : 0.f;
+            } else if (p.topk_weights != nullptr && lane < K) {
                 reinterpret_cast<float*>(heap + p.off_comb_w)[dst_row * K + lane] = p.topk_weights[static_cast<int64_t>(i) * K + lane];
+            }
             if (!is_sender) {
-                copy_row_regs(p.x + static_cast<int64_t>(i) * p.x_stride_bytes, heap + p.off_comb_x + dst_row * p.row_bytes, vec_per_row, lane);
+                copy_row_regs(p.x + static_cast<int64_t>(i) * p.x_stride_bytes, dst_ptr, vec_per_row, lane);
                 break;
             }
             const bool landed = mbar_wait(w, bar, parity, kStatusTmaLoad, i);
             parity ^= 1;
             if (!__all_sync(0xffffffffu, landed)) { fatal = true; break; }
             if (lane == 0) {
-                bulk_s2g(heap + p.off_comb_x + dst_row * p.row_bytes, buf, p.row_bytes);
+                bulk_s2g(dst_ptr, buf, p.row_bytes);
                 bulk_commit();
                 row_sent(i);
             }
@@ -302,6 +320,9 @@ __global__ void __launch_bounds__(1024, 1) combine_kernel(const __grid_constant_
             // expanded input: sum this token's local-expert rows in fp32 (ascending top-k lane), round once, send
             int my_row = lane < K ? md[2 + lane] : -1;
             const uint32_t valid = __ballot_sync(0xffffffffu, my_row >= 0);
+            const uint64_t dst_row = static_cast<uint64_t>(c.rank) * p.num_max_tokens + src_token;
+            uint8_t* dst_ptr = p.direct_out ? p.red.combined_x + static_cast<uint64_t>(src_token) * p.row_bytes
+                                            : heap + p.off_comb_x + dst_row * p.row_bytes;
             for (int v = lane; v < vec_per_row; v += 32) {
                 float acc[8];
 #pragma unroll
@@ -316,17 +337,20 @@ __global__ void __launch_bounds__(1024, 1) combine_kernel(const __grid_constant_
                 if (is_sender)
                     reinterpret_cast<int4*>(buf)[v] = pack_bf16x8(acc);
                 else
-                    st_na_int4(heap + p.off_comb_x + (static_cast<uint64_t>(c.rank) * p.num_max_tokens + src_token) * p.row_bytes + v * 16,
-                               pack_bf16x8(acc));
+                    st_na_int4(dst_ptr + v * 16, pack_bf16x8(acc));
             }
-            const uint64_t dst_row = static_cast<uint64_t>(c.rank) * p.num_max_tokens + src_token;
-            if (p.topk_weights != nullptr && my_row >= 0)
+            if (p.direct_out) {
+                if (p.red.combined_topk_weights != nullptr && lane < K)
+                    p.red.combined_topk_weights[static_cast<int64_t>(src_token) * K + lane] =
+                        my_row >= 0 && p.topk_weights != nullptr ? p.topk_weights[my_row] : 0.f;
+            } else if (p.topk_weights != nullptr && my_row >= 0) {
                 reinterpret_cast<float*>(heap + p.off_comb_w)[dst_row * K + lane] = p.topk_weights[my_row];
+            }
             if (!is_sender) break;
             fence_proxy_async_smem();
             __syncwarp();
             if (lane == 0) {
-                bulk_s2g(heap + p.off_comb_x + dst_row * p.row_bytes, buf, p.row_bytes);
+                bulk_s2g(dst_ptr, buf, p.row_bytes);
                 bulk_commit();
                 row_sent(i);
             }

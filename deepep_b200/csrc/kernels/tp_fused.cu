@@ -18,6 +18,8 @@
 // The reference has neither operator (its AGRS path is a copy-engine all-gather only, and
 // reduce-scatter is listed as not implemented); the baseline to beat is NCCL all-gather /
 // reduce-scatter followed / preceded by an unfused GEMM.
+#include <cstdlib>
+
 #include "gemm_api.hpp"
 #include "gemm_sm100.cuh"
 #include "tp_api.hpp"
@@ -71,15 +73,50 @@ __device__ __forceinline__ void mma_role(const PipeCtx& pc, uint8_t* smem, uint6
     }
 }
 
+// CTA-pair form (leader CTA only): 256-row tiles, stages of A_BYTES + B_BYTES / 2 per CTA, barriers of both CTAs
+// released by multicast commits (see gemm_sm100.cuh)
+constexpr int STAGE_PAIR = A_BYTES + B_BYTES / 2;
+template <int kStages>
+__device__ __forceinline__ void mma_role_pair(const PipeCtx& pc, uint8_t* smem, uint64_t* full, uint64_t* empty, uint64_t* tmem_full,
+                                              uint64_t* tmem_empty, uint32_t tmem_base, int num_tiles_mine, int num_kb) {
+    constexpr uint32_t idesc = make_idesc<false>(2 * BM, BN);
+    int s = 0, acc = 0;
+    uint32_t ph = 0, acc_ph = 0;
+    for (int i = 0; i < num_tiles_mine; ++i) {
+        if (!pipe_wait(pc, tmem_empty + acc, acc_ph ^ 1)) return;
+        tc_fence_after();
+        for (int kb = 0; kb < num_kb; ++kb) {
+            if (!pipe_wait(pc, full + s, ph)) return;
+            tc_fence_after();
+            const uint8_t* sa = smem + s * STAGE_PAIR;
+            const uint64_t da = make_smem_desc(sa), db = make_smem_desc(sa + A_BYTES);
+#pragma unroll
+            for (int k = 0; k < BK / UMMA_K; ++k) umma_pair_bf16(tmem_base + acc * BN, da + 2 * k, db + 2 * k, idesc, (kb | k) != 0);
+            umma_commit_pair(empty + s);
+            if (++s == kStages) { s = 0; ph ^= 1; }
+        }
+        umma_commit_pair(tmem_full + acc);
+        acc ^= 1;
+        if (acc == 0) acc_ph ^= 1;
+    }
+}
+
 __device__ __forceinline__ int tiles_of(int total, int first, int stride) {
     return total > first ? (total - first + stride - 1) / stride : 0;
 }
 
 // ==================================================================== all-gather -> GEMM
-constexpr int kAgStages = 4;
-constexpr int kAgBarBytes = (2 * kAgStages + 4) * 8 + 16;
-constexpr int kAgSmem = kAgStages * STAGE + kAgBarBytes + 1024;
 constexpr int kAgThreads = 6 * 32;
+// kPair: GEMM CTAs work in clusters of two on two 128-row chunks and one 256-column block of B (cta_group::2)
+template <bool kPair>
+struct AgCfg {
+    static constexpr int kStages = kPair ? 6 : 4;
+    static constexpr int kStage = kPair ? STAGE_PAIR : STAGE;
+    static constexpr int kBarBytes = (2 * kStages + 4) * 8 + 16;
+    static constexpr int kSmem = kStages * kStage + kBarBytes + 1024;
+};
+constexpr int kAgSmem = AgCfg<false>::kSmem;   // both forms: 192 KB of stages
+static_assert(AgCfg<true>::kSmem == AgCfg<false>::kSmem + 4 * 8, "the comm CTAs size their row buffers by kAgSmem");
 
 // one launch may carry several virtual ranks (single-GPU emulation): CTAs [v * ctas_per_rank, ...) act as rank v
 struct AgLaunch {
@@ -93,7 +130,10 @@ struct RsLaunch {
     CUtensorMap map_a[kTpMaxVRanks], map_b[kTpMaxVRanks];
 };
 
+template <bool kPair>
 __global__ void __launch_bounds__(kAgThreads, 1) ag_gemm_kernel(const __grid_constant__ AgLaunch L) {
+    constexpr int kAgStages = AgCfg<kPair>::kStages;
+    constexpr int kStageBytes = AgCfg<kPair>::kStage;
     const int vr = blockIdx.x / L.ctas_per_rank;
     const int bid = blockIdx.x % L.ctas_per_rank, nctas = L.ctas_per_rank;
     const AgGemmParams& p = L.p[vr];
@@ -195,28 +235,36 @@ __global__ void __launch_bounds__(kAgThreads, 1) ag_gemm_kernel(const __grid_con
     PipeCtx pc{p.error, globaltimer_ns() + c.timeout_ns};
     const int num_kb = K / BK;
     const int tiles_n = p.N / BN;
-    const int total_tiles = R * chunks * tiles_n;
-    const int first = bid - p.num_comm_ctas, stride = nctas - p.num_comm_ctas;
+    // pair: work item = (two consecutive entries of the arrival order, n block); CTA `cta` of the pair takes entry 2 * op + cta
+    const uint32_t cta = kPair ? cluster_ctarank() : 0u;
+    const int total_tiles = (kPair ? R * chunks / 2 : R * chunks) * tiles_n;
+    const int first = kPair ? (bid - p.num_comm_ctas) >> 1 : bid - p.num_comm_ctas;
+    const int stride = kPair ? (nctas - p.num_comm_ctas) >> 1 : nctas - p.num_comm_ctas;
     const int mine = tiles_of(total_tiles, first, stride);
 
     if (warp == 0 && lane == 0) {
         prefetch_tensormap(&map_local);
         prefetch_tensormap(&map_gather);
         prefetch_tensormap(&map_b);
-        init_pipeline(full, empty, tmem_full, tmem_empty, kAgStages, 4 * 32);
+        init_pipeline(full, empty, tmem_full, tmem_empty, kAgStages, kPair ? 8 * 32 : 4 * 32);
     }
     if (warp == 1) {
-        tmem_alloc(tmem_slot, 2 * BN);
-        tmem_relinquish();
+        if constexpr (kPair) {
+            tmem_alloc_pair(tmem_slot, 2 * BN);
+            tmem_relinquish_pair();
+        } else {
+            tmem_alloc(tmem_slot, 2 * BN);
+            tmem_relinquish();
+        }
     }
     tc_fence_before();
-    __syncthreads();
+    if constexpr (kPair) cluster_sync_all(); else __syncthreads();
     tc_fence_after();
     const uint32_t tmem_base = *tmem_slot;
 
     // tile t -> (order index o, n block): o walks own rows first, then chunk by chunk over the sources rank+1, rank+2, ...
     auto decode = [&](int t, int& src, int& chunk, int& n0) {
-        const int o = t / tiles_n;
+        const int o = kPair ? 2 * (t / tiles_n) + static_cast<int>(cta) : t / tiles_n;
         n0 = (t % tiles_n) * BN;
         if (o < chunks) {
             src = c.rank;
@@ -246,17 +294,29 @@ __global__ void __launch_bounds__(kAgThreads, 1) ag_gemm_kernel(const __grid_con
                 }
                 for (int kb = 0; kb < num_kb; ++kb) {
                     if (!(ok = pipe_wait(pc, empty + s, ph ^ 1))) break;
-                    uint8_t* sa = smem + s * STAGE;
-                    mbar_arrive_expect_tx(full + s, STAGE);
-                    if (src == c.rank) tma_load_2d(sa, &map_local, kb * BK, chunk * BM, full + s);
-                    else tma_load_2d(sa, &map_gather, kb * BK, src * Ml + chunk * BM, full + s);
-                    tma_load_2d(sa + A_BYTES, &map_b, kb * BK, n0, full + s);
+                    uint8_t* sa = smem + s * kStageBytes;
+                    if constexpr (kPair) {
+                        if (cta == 0) mbar_arrive_expect_tx(full + s, 2 * kStageBytes);
+                        const uint32_t bar = map_to_cta(smem_u32(full + s), 0);
+                        if (src == c.rank) tma_load_2d_pair(sa, &map_local, kb * BK, chunk * BM, bar);
+                        else tma_load_2d_pair(sa, &map_gather, kb * BK, src * Ml + chunk * BM, bar);
+                        tma_load_2d_pair(sa + A_BYTES, &map_b, kb * BK, n0 + static_cast<int>(cta) * (BN / 2), bar);
+                    } else {
+                        mbar_arrive_expect_tx(full + s, STAGE);
+                        if (src == c.rank) tma_load_2d(sa, &map_local, kb * BK, chunk * BM, full + s);
+                        else tma_load_2d(sa, &map_gather, kb * BK, src * Ml + chunk * BM, full + s);
+                        tma_load_2d(sa + A_BYTES, &map_b, kb * BK, n0, full + s);
+                    }
                     if (++s == kAgStages) { s = 0; ph ^= 1; }
                 }
             }
         }
     } else if (warp == 1) {
-        if (lane == 0) mma_role<kAgStages>(pc, smem, full, empty, tmem_full, tmem_empty, tmem_base, mine, num_kb);
+        if constexpr (kPair) {
+            if (cta == 0 && lane == 0) mma_role_pair<kAgStages>(pc, smem, full, empty, tmem_full, tmem_empty, tmem_base, mine, num_kb);
+        } else {
+            if (lane == 0) mma_role<kAgStages>(pc, smem, full, empty, tmem_full, tmem_empty, tmem_base, mine, num_kb);
+        }
     } else {
         const int quarter = warp & 3;
         int acc = 0;
@@ -284,28 +344,39 @@ __global__ void __launch_bounds__(kAgThreads, 1) ag_gemm_kernel(const __grid_con
                 }
             }
             tc_fence_before();
-            mbar_arrive(tmem_empty + acc);
+            if constexpr (kPair) mbar_arrive_cluster(map_to_cta(smem_u32(tmem_empty + acc), 0));
+            else mbar_arrive(tmem_empty + acc);
             acc ^= 1;
             if (acc == 0) acc_ph ^= 1;
         }
     }
     tc_fence_before();
-    __syncthreads();
+    if constexpr (kPair) cluster_sync_all(); else __syncthreads();
     if (warp == 1) {
         tc_fence_after();
-        tmem_dealloc(tmem_base, 2 * BN);
+        if constexpr (kPair) tmem_dealloc_pair(tmem_base, 2 * BN);
+        else tmem_dealloc(tmem_base, 2 * BN);
     }
 }
 
 // ==================================================================== GEMM -> reduce-scatter
-constexpr int kRsStages = 3;
 constexpr int kRsRowPitch = BN * 2 + 16;                       // padded rows: lanes of a warp fall into different banks
 constexpr int kRsStageTile = BM * kRsRowPitch;                 // bf16 staging tile of the epilogue
-constexpr int kRsBarBytes = (2 * kRsStages + 4) * 8 + 16;
-constexpr int kRsSmem = kRsStages * STAGE + kRsStageTile + kRsBarBytes + 1024;
 constexpr int kRsThreads = 6 * 32;
+// kPair: two CTAs of a cluster share a 256-row tile (tcgen05 cta_group::2): each loads its 128 rows of A and half of
+// the B tile, four 32 KB stages instead of three 48 KB ones fit next to the staging tile.
+template <bool kPair>
+struct RsCfg {
+    static constexpr int kStages = kPair ? 4 : 3;
+    static constexpr int kStage = kPair ? STAGE_PAIR : STAGE;
+    static constexpr int kBarBytes = (2 * kStages + 4) * 8 + 16;
+    static constexpr int kSmem = kStages * kStage + kRsStageTile + kBarBytes + 1024;
+};
 
+template <bool kPair>
 __global__ void __launch_bounds__(kRsThreads, 1) gemm_rs_kernel(const __grid_constant__ RsLaunch L) {
+    constexpr int kRsStages = RsCfg<kPair>::kStages;
+    constexpr int kStageBytes = RsCfg<kPair>::kStage;
     const int vr = blockIdx.x / L.ctas_per_rank;
     const int bid = blockIdx.x % L.ctas_per_rank, nctas = L.ctas_per_rank;
     const GemmRsParams& p = L.p[vr];
@@ -313,7 +384,7 @@ __global__ void __launch_bounds__(kRsThreads, 1) gemm_rs_kernel(const __grid_con
     const CUtensorMap& map_b = L.map_b[vr];
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~static_cast<uintptr_t>(1023));
-    uint8_t* stage_tile = smem + kRsStages * STAGE;
+    uint8_t* stage_tile = smem + kRsStages * kStageBytes;
     uint64_t* full = reinterpret_cast<uint64_t*>(stage_tile + kRsStageTile);
     uint64_t* empty = full + kRsStages;
     uint64_t* tmem_full = empty + kRsStages;
@@ -328,29 +399,39 @@ __global__ void __launch_bounds__(kRsThreads, 1) gemm_rs_kernel(const __grid_con
     const int num_kb = p.K / BK;
     const WaitCtx w = make_wait_ctx(c);
     PipeCtx pc{p.error, globaltimer_ns() + c.timeout_ns};
-    const int first = bid, stride = nctas;
-    const int mine = tiles_of(total_tiles, first, stride);
+    // pair: the unit of work is a 256-row tile owned by CTAs (2j, 2j + 1); CTA `cta` computes chunk 2 * c + cta of it
+    const uint32_t cta = kPair ? cluster_ctarank() : 0u;
+    const int first = kPair ? bid >> 1 : bid, stride = kPair ? nctas >> 1 : nctas;
+    const int work_per_dst = kPair ? tiles_per_dst / 2 : tiles_per_dst;
+    const int total_work = R * work_per_dst;
+    const int mine = tiles_of(total_work, first, stride);
     const int half = p.epoch & 1;
     const uint64_t part_off = p.off_partial[half], flag_off = p.off_flags[half];
 
     if (warp == 0 && lane == 0) {
         prefetch_tensormap(&map_a);
         prefetch_tensormap(&map_b);
-        init_pipeline(full, empty, tmem_full, tmem_empty, kRsStages, 4 * 32);
+        init_pipeline(full, empty, tmem_full, tmem_empty, kRsStages, kPair ? 8 * 32 : 4 * 32);
     }
     if (warp == 1) {
-        tmem_alloc(tmem_slot, 2 * BN);
-        tmem_relinquish();
+        if constexpr (kPair) {
+            tmem_alloc_pair(tmem_slot, 2 * BN);
+            tmem_relinquish_pair();
+        } else {
+            tmem_alloc(tmem_slot, 2 * BN);
+            tmem_relinquish();
+        }
     }
     tc_fence_before();
-    __syncthreads();
+    if constexpr (kPair) cluster_sync_all(); else __syncthreads();
     tc_fence_after();
     const uint32_t tmem_base = *tmem_slot;
 
-    // tile t -> destination (next rank first, own rows last), tile index inside the destination's chunk
+    // work item t -> destination (next rank first, own rows last) and the 128-row tile this CTA computes of it
     auto decode = [&](int t, int& dst, int& local_tile) {
-        dst = (c.rank + 1 + t / tiles_per_dst) % R;
-        local_tile = t % tiles_per_dst;
+        dst = (c.rank + 1 + t / work_per_dst) % R;
+        const int u = t % work_per_dst;
+        local_tile = kPair ? ((u / tiles_n) * 2 + static_cast<int>(cta)) * tiles_n + u % tiles_n : u;
     };
 
     if (warp == 0) {
@@ -358,29 +439,40 @@ __global__ void __launch_bounds__(kRsThreads, 1) gemm_rs_kernel(const __grid_con
             int s = 0;
             uint32_t ph = 0;
             bool ok = true;
-            for (int t = first; ok && t < total_tiles; t += stride) {
+            for (int t = first; ok && t < total_work; t += stride) {
                 int dst, lt;
                 decode(t, dst, lt);
                 const int m0 = dst * Ml + (lt / tiles_n) * BM, n0 = (lt % tiles_n) * BN;
                 for (int kb = 0; kb < num_kb; ++kb) {
                     if (!(ok = pipe_wait(pc, empty + s, ph ^ 1))) break;
-                    uint8_t* sa = smem + s * STAGE;
-                    mbar_arrive_expect_tx(full + s, STAGE);
-                    tma_load_2d(sa, &map_a, kb * BK, m0, full + s);
-                    tma_load_2d(sa + A_BYTES, &map_b, kb * BK, n0, full + s);
+                    uint8_t* sa = smem + s * kStageBytes;
+                    if constexpr (kPair) {
+                        if (cta == 0) mbar_arrive_expect_tx(full + s, 2 * kStageBytes);
+                        const uint32_t bar = map_to_cta(smem_u32(full + s), 0);
+                        tma_load_2d_pair(sa, &map_a, kb * BK, m0, bar);
+                        tma_load_2d_pair(sa + A_BYTES, &map_b, kb * BK, n0 + static_cast<int>(cta) * (BN / 2), bar);
+                    } else {
+                        mbar_arrive_expect_tx(full + s, STAGE);
+                        tma_load_2d(sa, &map_a, kb * BK, m0, full + s);
+                        tma_load_2d(sa + A_BYTES, &map_b, kb * BK, n0, full + s);
+                    }
                     if (++s == kRsStages) { s = 0; ph ^= 1; }
                 }
             }
         }
     } else if (warp == 1) {
-        if (lane == 0) mma_role<kRsStages>(pc, smem, full, empty, tmem_full, tmem_empty, tmem_base, mine, num_kb);
+        if constexpr (kPair) {
+            if (cta == 0 && lane == 0) mma_role_pair<kRsStages>(pc, smem, full, empty, tmem_full, tmem_empty, tmem_base, mine, num_kb);
+        } else {
+            if (lane == 0) mma_role<kRsStages>(pc, smem, full, empty, tmem_full, tmem_empty, tmem_base, mine, num_kb);
+        }
     } else {
         // epilogue: accumulator -> bf16 -> staging tile -> bulk stores into the destination's partial slot -> flag
         const int quarter = warp & 3;
         int acc = 0;
         uint32_t acc_ph = 0;
         uint64_t* prev_flag = nullptr;
-        for (int t = first; t < total_tiles; t += stride) {
+        for (int t = first; t < total_work; t += stride) {
             int dst, lt;
             decode(t, dst, lt);
             const int local_m0 = (lt / tiles_n) * BM, n0 = (lt % tiles_n) * BN;
@@ -405,7 +497,8 @@ __global__ void __launch_bounds__(kRsThreads, 1) gemm_rs_kernel(const __grid_con
                 }
             }
             tc_fence_before();
-            mbar_arrive(tmem_empty + acc);
+            if constexpr (kPair) mbar_arrive_cluster(map_to_cta(smem_u32(tmem_empty + acc), 0));
+            else mbar_arrive(tmem_empty + acc);
             acc ^= 1;
             if (acc == 0) acc_ph ^= 1;
             fence_proxy_async_smem();
@@ -438,10 +531,11 @@ __global__ void __launch_bounds__(kRsThreads, 1) gemm_rs_kernel(const __grid_con
 
     // ---------------------------------------------------------------- reduction of this rank's own tiles
     tc_fence_before();
-    __syncthreads();
+    if constexpr (kPair) cluster_sync_all(); else __syncthreads();
     if (warp == 1) {
         tc_fence_after();
-        tmem_dealloc(tmem_base, 2 * BN);
+        if constexpr (kPair) tmem_dealloc_pair(tmem_base, 2 * BN);
+        else tmem_dealloc(tmem_base, 2 * BN);
     }
     const uint64_t* my_flags = reinterpret_cast<const uint64_t*>(c.heap[c.rank] + flag_off);
     const uint8_t* my_part = c.heap[c.rank] + part_off;
@@ -500,6 +594,31 @@ __global__ void __launch_bounds__(kRsThreads, 1) gemm_rs_kernel(const __grid_con
 
 }  // namespace
 
+static bool tp_pairs_enabled() {
+    const char* e = std::getenv("EP_TP_CTA_PAIR");
+    return e != nullptr && e[0] == '1';
+}
+
+// cooperative launch (all CTAs resident: they wait for one another) in clusters of two
+template <typename Kernel, typename Launch>
+static cudaError_t coop_pairs(Kernel kernel, const Launch& L, int grid, int block, int smem, cudaStream_t stream) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(grid);
+    cfg.blockDim = dim3(block);
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[2];
+    attr[0].id = cudaLaunchAttributeCooperative;
+    attr[0].val.cooperative = 1;
+    attr[1].id = cudaLaunchAttributeClusterDimension;
+    attr[1].val.clusterDim.x = 2;
+    attr[1].val.clusterDim.y = 1;
+    attr[1].val.clusterDim.z = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 2;
+    return cudaLaunchKernelEx(&cfg, kernel, L);
+}
+
 static cudaError_t coop(const void* fn, void* arg, int grid, int block, int smem, cudaStream_t stream) {
     void* args[] = {arg};
     return cudaLaunchCooperativeKernel(fn, dim3(grid), dim3(block), args, smem, stream);
@@ -511,6 +630,10 @@ cudaError_t launch_ag_gemm(const AgGemmParams* params, const void* const* b, con
     AgLaunch L;
     L.num_vranks = num_vranks;
     L.ctas_per_rank = ctas_per_rank;
+    // CTA pairs: comm CTAs and GEMM CTAs must both come in twos, and the arrival order must have an even length
+    bool pair = tp_pairs_enabled() && ctas_per_rank % 2 == 0;
+    for (int v = 0; v < num_vranks; ++v)
+        pair = pair && params[v].num_comm_ctas % 2 == 0 && (params[v].c.num_ranks * (params[v].rows_per_rank / BM)) % 2 == 0;
     for (int v = 0; v < num_vranks; ++v) {
         const AgGemmParams& p = params[v];
         const int R = p.c.num_ranks;
@@ -521,12 +644,17 @@ cudaError_t launch_ag_gemm(const AgGemmParams* params, const void* const* b, con
         L.p[v] = p;
         if (!make_kmajor_map(&L.map_local[v], p.a_local, 2, p.rows_per_rank, p.K, p.a_stride_bytes, BM) ||
             !make_kmajor_map(&L.map_gather[v], gather_base[v], 2, static_cast<uint64_t>(R) * p.rows_per_rank, p.K, static_cast<uint64_t>(p.K) * 2, BM) ||
-            !make_kmajor_map(&L.map_b[v], b[v], 2, p.N, p.K, static_cast<uint64_t>(p.K) * 2, BN))
+            !make_kmajor_map(&L.map_b[v], b[v], 2, p.N, p.K, static_cast<uint64_t>(p.K) * 2, pair ? BN / 2 : BN))
             return cudaErrorInvalidValue;
     }
-    cudaError_t err = cudaFuncSetAttribute(ag_gemm_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kAgSmem);
+    if (pair) {
+        cudaError_t err = cudaFuncSetAttribute(ag_gemm_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, AgCfg<true>::kSmem);
+        if (err != cudaSuccess) return err;
+        return coop_pairs(ag_gemm_kernel<true>, L, num_vranks * ctas_per_rank, kAgThreads, AgCfg<true>::kSmem, stream);
+    }
+    cudaError_t err = cudaFuncSetAttribute(ag_gemm_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, kAgSmem);
     if (err != cudaSuccess) return err;
-    return coop(reinterpret_cast<const void*>(ag_gemm_kernel), &L, num_vranks * ctas_per_rank, kAgThreads, kAgSmem, stream);
+    return coop(reinterpret_cast<const void*>(ag_gemm_kernel<false>), &L, num_vranks * ctas_per_rank, kAgThreads, kAgSmem, stream);
 }
 
 cudaError_t launch_gemm_rs(const GemmRsParams* params, const void* const* a, const int64_t* a_stride_bytes, const void* const* b,
@@ -535,18 +663,26 @@ cudaError_t launch_gemm_rs(const GemmRsParams* params, const void* const* a, con
     RsLaunch L;
     L.num_vranks = num_vranks;
     L.ctas_per_rank = ctas_per_rank;
+    // CTA pairs need an even CTA count per rank and an even number of 128-row chunks (EP_TP_CTA_PAIR=0 turns them off)
+    bool pair = tp_pairs_enabled() && ctas_per_rank % 2 == 0;
+    for (int v = 0; v < num_vranks; ++v) pair = pair && (params[v].rows_per_rank / BM) % 2 == 0;
     for (int v = 0; v < num_vranks; ++v) {
         const GemmRsParams& p = params[v];
         const int R = p.c.num_ranks;
         if (p.N % BN != 0 || p.K % BK != 0 || p.rows_per_rank % BM != 0) return cudaErrorInvalidValue;
         L.p[v] = p;
         if (!make_kmajor_map(&L.map_a[v], a[v], 2, static_cast<uint64_t>(R) * p.rows_per_rank, p.K, a_stride_bytes[v], BM) ||
-            !make_kmajor_map(&L.map_b[v], b[v], 2, p.N, p.K, static_cast<uint64_t>(p.K) * 2, BN))
+            !make_kmajor_map(&L.map_b[v], b[v], 2, p.N, p.K, static_cast<uint64_t>(p.K) * 2, pair ? BN / 2 : BN))
             return cudaErrorInvalidValue;
     }
-    cudaError_t err = cudaFuncSetAttribute(gemm_rs_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kRsSmem);
+    if (pair) {
+        cudaError_t err = cudaFuncSetAttribute(gemm_rs_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, RsCfg<true>::kSmem);
+        if (err != cudaSuccess) return err;
+        return coop_pairs(gemm_rs_kernel<true>, L, num_vranks * ctas_per_rank, kRsThreads, RsCfg<true>::kSmem, stream);
+    }
+    cudaError_t err = cudaFuncSetAttribute(gemm_rs_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, RsCfg<false>::kSmem);
     if (err != cudaSuccess) return err;
-    return coop(reinterpret_cast<const void*>(gemm_rs_kernel), &L, num_vranks * ctas_per_rank, kRsThreads, kRsSmem, stream);
+    return coop(reinterpret_cast<const void*>(gemm_rs_kernel<false>), &L, num_vranks * ctas_per_rank, kRsThreads, RsCfg<false>::kSmem, stream);
 }
 
 }  // namespace gemm

@@ -456,6 +456,9 @@ std::vector<CombineResult> Runtime::combine(const std::vector<std::shared_ptr<Ru
     // (a warp per token needs the parallelism of all SMs to reach memory speed), so it is opt-in.
     bool fuse = a0.fuse_reduce != 0 && !a0.sc.previous_event_before_epilogue.has_value();
     for (const auto& a : args) fuse = fuse && a.dst_slot.has_value();
+    // One rank: every token has at most one row (rank layout), so the send kernel can write the result itself.
+    bool direct = R == 1 && rank_layout && !fuse && !a0.sc.previous_event_before_epilogue.has_value();
+    for (const auto& a : args) direct = direct && !a.bias0.has_value() && !a.bias1.has_value();
     int num_reduce_sms = fuse ? std::max(0, a0.num_reduce_sms) : 0;
     if ((num_sms + num_reduce_sms) * V > rt0.num_device_sms_) num_reduce_sms = rt0.num_device_sms_ / V - num_sms;
     const int num_blocks = num_sms + num_reduce_sms;
@@ -502,6 +505,7 @@ std::vector<CombineResult> Runtime::combine(const std::vector<std::shared_ptr<Ru
         rt.grid_bar_base += num_blocks;
         p.num_send_blocks = num_sms;
         p.num_reg_warps = fuse ? 0 : std::max(0, a0.num_reg_warps);
+        p.direct_out = 0;            // decided below, once the biases are known
 
         auto& r = res[v];
         r.combined_x = at::empty({T, H}, opts(at::kBFloat16, device));
@@ -531,6 +535,7 @@ std::vector<CombineResult> Runtime::combine(const std::vector<std::shared_ptr<Ru
         q.combined_x = static_cast<uint8_t*>(r.combined_x.data_ptr());
         q.combined_topk_weights = r.combined_topk_weights.has_value() ? r.combined_topk_weights->data_ptr<float>() : nullptr;
         p.fuse_reduce = fuse ? 1 : 0;
+        p.direct_out = direct ? 1 : 0;
         p.num_send_warps = 0;        // filled in by the launcher
         p.flag_chunks = lay.combine_flag_chunks;
         p.off_comb_flag = lay.combine_flag;
@@ -552,7 +557,7 @@ std::vector<CombineResult> Runtime::combine(const std::vector<std::shared_ptr<Ru
     CUDA_RUNTIME_CHECK(launch_combine(m, launch, stream));
     rt0.prof_record(4, stream);
     if (a0.sc.previous_event_before_epilogue.has_value()) a0.sc.previous_event_before_epilogue->stream_wait(scope.comm);
-    if (!fuse) {
+    if (!fuse && !direct) {
         const int epi_sms = std::max(1, rt0.num_device_sms_ / V);
         CUDA_RUNTIME_CHECK(launch_combine_epilogue(ep.data(), V, epi_sms, stream));
     }

@@ -86,6 +86,15 @@ def test_dispatch_combine_bf16(num_ranks, num_tokens, hidden, num_experts, num_t
         valid = idxs[r] >= 0
         assert torch.equal(torch.where(valid, combined_w, torch.zeros_like(combined_w)).cpu(),
                            torch.where(valid, ws[r], torch.zeros_like(ws[r])).cpu())
+    # without a bias (a single rank then writes the result from the send kernel, tokens nobody took are zeroed there)
+    comb = cl.combine([dict(x=ys[r], handle=out[r][3], topk_weights=out[r][2]) for r in range(num_ranks)])
+    torch.cuda.synchronize()
+    cl.check_status()
+    for r in range(num_ranks):
+        ref = refs.combine_local([y.cpu() for y in ys], srcs, r, xs[r].size(0), T_max)
+        assert torch.equal(comb[r][0].cpu(), ref)
+        valid = idxs[r] >= 0
+        assert torch.equal(comb[r][1].cpu(), torch.where(valid, ws[r], torch.zeros_like(ws[r])).cpu())
     cl.destroy()
 
 

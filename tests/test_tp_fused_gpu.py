@@ -19,9 +19,12 @@ def _rel(got, ref):
     return ((got.float() - ref).norm() / ref.norm()).item()
 
 
+@pytest.mark.parametrize('pair', ['1', '0'])
 @pytest.mark.parametrize('R', [1, 2, 4])
-def test_all_gather_gemm(R):
+def test_all_gather_gemm(R, pair, monkeypatch):
+    """`pair`: GEMM CTAs in clusters of two (tcgen05 cta_group::2) or one CTA per tile."""
     from deepep_b200.parallel.tp_fused import fused_multi
+    monkeypatch.setenv('EP_TP_CTA_PAIR', pair)
     Ml, K, N = 256, 512, 512
     ctxs = _contexts(R, Ml, K, N)
     g = torch.Generator(device='cuda').manual_seed(5)
@@ -40,9 +43,11 @@ def test_all_gather_gemm(R):
         c.destroy()
 
 
+@pytest.mark.parametrize('pair', ['1', '0'])
 @pytest.mark.parametrize('R', [1, 2, 4])
-def test_gemm_reduce_scatter(R):
+def test_gemm_reduce_scatter(R, pair, monkeypatch):
     from deepep_b200.parallel.tp_fused import fused_multi
+    monkeypatch.setenv('EP_TP_CTA_PAIR', pair)
     Ml, Kl, N = 256, 256, 512
     ctxs = _contexts(R, Ml, 512, N)
     g = torch.Generator(device='cuda').manual_seed(6)
