@@ -174,6 +174,25 @@ class ElasticBuffer:
         if self.num_ranks > 1:
             dist.barrier(group=self.group)
         torch.cuda.synchronize()
+        self._connect_host_segments()
+
+    def _connect_host_segments(self) -> None:
+        """``num_cpu_bytes > 0``: one pinned host segment per rank (POSIX shared memory registered with CUDA), mapped
+        by every rank of the machine. ``host_segments[r]`` is rank r's segment as this process addresses it."""
+        self.host_segments = []
+        if self.num_cpu_bytes <= 0:
+            return
+        own = _C.HostSegment.create(self.num_cpu_bytes)
+        if getattr(self.group, 'is_local_emulation', False):
+            self.host_segments = [own]          # completed by the emulated cluster once all ranks exist
+            return
+        names: List[Optional[str]] = [None] * self.num_ranks
+        if self.num_ranks > 1:
+            dist.all_gather_object(names, own.name, group=self.group)
+        self.host_segments = [own if r == self.rank_idx else _C.HostSegment.open(names[r], self.num_cpu_bytes)
+                              for r in range(self.num_ranks)]
+        if self.num_ranks > 1:
+            dist.barrier(group=self.group)     # everybody has opened every name before an owner may unlink it
 
     def destroy(self) -> None:
         """Releases the heap. Collective when ``explicitly_destroy`` was set (peers unmap first)."""
@@ -183,6 +202,9 @@ class ElasticBuffer:
         torch.cuda.synchronize()
         if self.num_ranks > 1 and not getattr(self.group, 'is_local_emulation', False) and self.explicitly_destroy:
             dist.barrier(group=self.group)
+        for seg in getattr(self, 'host_segments', []):
+            seg.release()
+        self.host_segments = []
         self.runtime.destroy()
 
     def __del__(self):

@@ -97,10 +97,30 @@ __global__ void __launch_bounds__(1024, 1) engram_kernel(const __grid_constant__
         const bool valid = e >= 0 && owner < c.num_ranks;
         bulk_wait_read_all();
         __syncwarp();
-        if (valid) {
+        if (valid && p.table_on_host) {
+            // host segment: sixteen bytes per lane and load, eight loads in flight, straight to the output
+            const uint8_t* src = p.table[owner] + static_cast<uint64_t>(row) * p.row_bytes;
+            uint8_t* dst = p.out + static_cast<uint64_t>(i) * p.row_bytes;
+            const int vecs = p.row_bytes / 16;
+            for (int v = lane; v < vecs; v += 256) {
+                int4 raw[8];
+#pragma unroll
+                for (int j = 0; j < 8; ++j)
+                    if (v + 32 * j < vecs) raw[j] = ld_nc_int4(src + (v + 32 * j) * 16);
+#pragma unroll
+                for (int j = 0; j < 8; ++j)
+                    if (v + 32 * j < vecs) *reinterpret_cast<int4*>(dst + (v + 32 * j) * 16) = raw[j];
+            }
+            if (p.sf_table != nullptr) {
+                const int token = i / p.entries_per_token, slot = i % p.entries_per_token;
+                for (int k = lane; k < p.sf_packs; k += 32)
+                    p.out_sf[token * p.out_sf_token_stride + (slot * p.sf_packs + k) * p.out_sf_pack_stride] =
+                        p.sf_table[static_cast<int64_t>(e) * p.sf_packs + k];
+            }
+        } else if (valid) {
             if (lane == 0) {
                 mbar_arrive_expect_tx(bar, p.row_bytes);
-                bulk_g2s(buf, c.heap[owner] + p.off_table + static_cast<uint64_t>(row) * p.row_bytes, p.row_bytes, bar);
+                bulk_g2s(buf, p.table[owner] + static_cast<uint64_t>(row) * p.row_bytes, p.row_bytes, bar);
             }
             if (p.sf_table != nullptr) {
                 const int token = i / p.entries_per_token, slot = i % p.entries_per_token;

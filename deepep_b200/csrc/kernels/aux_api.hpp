@@ -38,7 +38,8 @@ struct EngramParams {
     int num_indices;
     int entries_per_rank;
     int row_bytes;
-    uint64_t off_table;
+    const uint8_t* table[kMaxRanks];   // rank r's shard as this rank's kernels address it: heap[r] + offset, or r's host segment
+    int table_on_host;                 // the shards are pinned host memory: fetched with plain loads over PCIe
     uint8_t* out;
     // optional replicated scale table (local memory): sf_packs 4-byte packs per entry
     const uint32_t* sf_table;

@@ -227,7 +227,7 @@ __global__ void __launch_bounds__(kAgThreads, 1) ag_gemm_kernel(const __grid_con
     }
 
     // ---------------------------------------------------------------- GEMM CTAs
-    uint64_t* full = reinterpret_cast<uint64_t*>(smem + kAgStages * STAGE);
+    uint64_t* full = reinterpret_cast<uint64_t*>(smem + kAgStages * kStageBytes);
     uint64_t* empty = full + kAgStages;
     uint64_t* tmem_full = empty + kAgStages;
     uint64_t* tmem_empty = tmem_full + 2;

@@ -9,6 +9,7 @@
 #include <torch/extension.h>
 
 #include "../kernels/aux_api.hpp"
+#include "host_segment.hpp"
 #include "runtime.hpp"
 
 namespace py = pybind11;
@@ -87,7 +88,8 @@ void reduce_slots(Runtime& rt, int64_t offset, int64_t slot_stride_bytes, int nu
 // rows of a table that is sharded over the ranks' heaps; returns (data, gathered scales or None)
 std::vector<std::tuple<at::Tensor, std::optional<at::Tensor>>> engram_gather(
     const std::vector<std::shared_ptr<Runtime>>& rts, const std::vector<at::Tensor>& indices, int64_t table_offset, int entries_per_rank,
-    int hidden, at::ScalarType dtype, const std::vector<std::optional<at::Tensor>>& sf_tables, bool col_major_sf, int num_sms) {
+    int hidden, at::ScalarType dtype, const std::vector<std::optional<at::Tensor>>& sf_tables, bool col_major_sf, int num_sms,
+    const std::vector<std::vector<std::shared_ptr<HostSegment>>>& host_tables) {
     const int V = static_cast<int>(rts.size());
     EP_HOST_ASSERT(V >= 1 && V <= kMaxVRanks && static_cast<int>(indices.size()) == V);
     auto& rt0 = *rts[0];
@@ -113,7 +115,19 @@ std::vector<std::tuple<at::Tensor, std::optional<at::Tensor>>> engram_gather(
         p.num_indices = tokens * per_token;
         p.entries_per_rank = entries_per_rank;
         p.row_bytes = row_bytes;
-        p.off_table = static_cast<uint64_t>(table_offset);
+        // host_tables[v][r]: rank r's CPU segment as mapped by (virtual) rank v's process; empty = the shards are in the heaps
+        const bool on_host = !host_tables.empty();
+        EP_HOST_ASSERT(!on_host || (static_cast<int>(host_tables.size()) == V && static_cast<int>(host_tables[v].size()) == rt.num_ranks()));
+        p.table_on_host = on_host ? 1 : 0;
+        for (int r = 0; r < kMaxRanks; ++r) p.table[r] = nullptr;
+        for (int r = 0; r < rt.num_ranks(); ++r) {
+            if (on_host) {
+                EP_HOST_ASSERT(static_cast<int64_t>(entries_per_rank) * row_bytes <= static_cast<int64_t>(host_tables[v][r]->num_bytes()));
+                p.table[r] = host_tables[v][r]->device_ptr();
+            } else {
+                p.table[r] = rt.heap().peer(r) + table_offset;
+            }
+        }
         p.out = static_cast<uint8_t*>(data.data_ptr());
         p.sf_table = nullptr;
         p.sf_packs = 0;
@@ -154,6 +168,23 @@ void register_aux_bindings(py::module_& m) {
     m.def("copy_from_heap", &copy_from_heap);
     m.def("reduce_slots", &reduce_slots);
     m.def("engram_gather", &engram_gather);
+    py::class_<HostSegment, std::shared_ptr<HostSegment>>(m, "HostSegment")
+        .def_static("create", &HostSegment::create)
+        .def_static("open", &HostSegment::open)
+        .def_property_readonly("name", &HostSegment::name)
+        .def_property_readonly("num_bytes", &HostSegment::num_bytes)
+        .def("device_ptr", [](const HostSegment& s) { return reinterpret_cast<int64_t>(s.device_ptr()); })
+        .def("release", &HostSegment::release)
+        // device tensor -> segment (asynchronous on the current stream) and a CPU view for checks
+        .def("copy_from_device", [](HostSegment& s, const at::Tensor& src, int64_t offset) {
+            EP_HOST_ASSERT(src.is_cuda() && src.is_contiguous() && offset >= 0);
+            const int64_t bytes = src.numel() * src.element_size();
+            EP_HOST_ASSERT(offset + bytes <= static_cast<int64_t>(s.num_bytes()));
+            CUDA_RUNTIME_CHECK(cudaMemcpyAsync(s.host_ptr() + offset, src.data_ptr(), bytes, cudaMemcpyDeviceToHost, cur_stream()));
+        })
+        .def("as_tensor", [](const std::shared_ptr<HostSegment>& s) {
+            return at::from_blob(s->host_ptr(), {static_cast<int64_t>(s->num_bytes())}, [s](void*) {}, at::TensorOptions().dtype(at::kByte));
+        });
     m.attr("CTL_AGRS_SIGNALS") = static_cast<int64_t>(kCtlAgrsSignals * 8);
     m.attr("CTL_PP_SIGNALS") = static_cast<int64_t>(kCtlPPSignals * 8);
     m.attr("MAX_AGRS_INFLIGHT") = kMaxAgrsInflight;

@@ -37,6 +37,14 @@ class LocalGroup:
         self._cluster._register(self._rank, buffer)
 
 
+def _share_host_segments(buffers) -> None:
+    """One process holds all ranks: every buffer sees the others' host segments through the same mappings."""
+    if all(getattr(b, 'host_segments', None) for b in buffers) and all(hasattr(b, 'runtime') for b in buffers):
+        own = [b.host_segments[0] for b in buffers]
+        for b in buffers:
+            b.host_segments = list(own)
+
+
 class LocalCluster:
     """``num_ranks`` virtual ranks on the current device.
 
@@ -51,6 +59,7 @@ class LocalCluster:
         self._pending: List[Optional[ElasticBuffer]] = [None] * num_ranks
         self.buffers: List[ElasticBuffer] = [ElasticBuffer(LocalGroup(self, r), **buffer_kwargs) for r in range(num_ranks)]
         self._C.Runtime.connect_local([b.runtime for b in self.buffers])
+        _share_host_segments(self.buffers)
         torch.cuda.synchronize()
 
     def _register(self, rank: int, buffer) -> None:
@@ -162,4 +171,5 @@ class VirtualRanks:
     def connect(self) -> None:
         buffers = [self._registered[r] for r in range(self.num_ranks)]
         self._C.Runtime.connect_local([b.runtime for b in buffers])
+        _share_host_segments(buffers)
         torch.cuda.synchronize()

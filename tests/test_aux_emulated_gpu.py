@@ -7,11 +7,12 @@ import torch
 pytestmark = pytest.mark.gpu
 
 
-def _buffers(R, num_bytes):
+def _buffers(R, num_bytes, num_cpu_bytes=0):
     import deepep_b200
     from deepep_b200.parallel.local_cluster import VirtualRanks
     vr = VirtualRanks(R)
-    bufs = [deepep_b200.ElasticBuffer(vr.groups[r], num_bytes=num_bytes, num_gpu_timeout_secs=5) for r in range(R)]
+    bufs = [deepep_b200.ElasticBuffer(vr.groups[r], num_bytes=num_bytes, num_cpu_bytes=num_cpu_bytes, num_gpu_timeout_secs=5)
+            for r in range(R)]
     vr.connect()
     return bufs
 
@@ -92,12 +93,15 @@ def test_pp_ring_random_schedule():
         b.destroy()
 
 
+@pytest.mark.parametrize('on_host', [False, True])
 @pytest.mark.parametrize('fp8', [False, True])
-def test_engram_fetch(fp8):
+def test_engram_fetch(fp8, on_host):
+    """`on_host`: the shards live in the ranks' pinned host segments (num_cpu_bytes) and are fetched over PCIe."""
     from deepep_b200.parallel.engram import EngramStore
     R, per_rank, hidden = 4, 64, 256
-    bufs = _buffers(R, 16 << 20)
+    bufs = _buffers(R, 16 << 20, num_cpu_bytes=(1 << 20) if on_host else 0)
     stores = [b._engram_store() for b in bufs]
+    assert all(s.on_host == on_host for s in stores)
     g = torch.Generator(device='cuda').manual_seed(2)
     table = torch.randn((R * per_rank, hidden), device='cuda', generator=g).bfloat16()
     sf = torch.rand((R * per_rank, 2), device='cuda', generator=g) if fp8 else None
@@ -115,6 +119,10 @@ def test_engram_fetch(fp8):
         if fp8:
             assert torch.equal(got_sf, sf[flat].view(17, 6))
             assert got_sf.stride(0) == 1
+    if on_host:     # the table really is in host memory
+        seg = bufs[1].host_segments[1].as_tensor()
+        want = full[per_rank:2 * per_rank].contiguous().view(torch.uint8).flatten().cpu()
+        assert torch.equal(seg[:want.numel()], want)
     for b in bufs:
         b.check_status()
         b.destroy()
