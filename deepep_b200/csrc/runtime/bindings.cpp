@@ -130,6 +130,7 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
         .def("clear_status", &Runtime::clear_status)
         .def("set_gpu_timeout", &Runtime::set_gpu_timeout)
         .def("enable_profiling", &Runtime::enable_profiling)
+        .def("num_kernel_launches", &Runtime::num_kernel_launches)
         .def("last_timings", &Runtime::last_timings)
         .def("last_dispatch_phases", &Runtime::last_dispatch_phases)
         .def("rank", &Runtime::rank)

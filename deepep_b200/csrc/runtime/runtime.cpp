@@ -190,6 +190,7 @@ void Runtime::barrier(const std::vector<std::shared_ptr<Runtime>>& rts, bool use
         m.r[v].epoch = ++rts[v]->barrier_epoch;
     }
     CUDA_RUNTIME_CHECK(launch_barrier(m, stream));
+    ++rt0.num_launches_;
     if (use_comm_stream) stream_wait(compute, stream);
     if (with_cpu_sync) {
         CUDA_RUNTIME_CHECK(cudaStreamSynchronize(stream));
@@ -318,6 +319,7 @@ std::vector<DispatchResult> Runtime::dispatch(const std::vector<std::shared_ptr<
     EP_HOST_ASSERT_MSG(plan_dispatch(m.r[0], num_sms, rt0.smem_optin_, &launch), "a token row does not fit into shared memory");
     rt0.prof_record(0, stream);
     CUDA_RUNTIME_CHECK(launch_dispatch(m, launch, stream));
+    ++rt0.num_launches_;
     rt0.prof_record(1, stream);
 
     // ---- sizes of the outputs
@@ -422,6 +424,7 @@ std::vector<DispatchResult> Runtime::dispatch(const std::vector<std::shared_ptr<
     if (a0.sc.previous_event_before_epilogue.has_value()) a0.sc.previous_event_before_epilogue->stream_wait(scope.comm);
     const int epi_sms = std::max(1, rt0.num_device_sms_ / V);
     CUDA_RUNTIME_CHECK(launch_dispatch_epilogue(ep.data(), V, epi_sms, rt0.smem_optin_, stream));
+    ++rt0.num_launches_;
     rt0.prof_record(2, stream);
     rt0.prof_valid_[0] = rt0.profiling_;
 
@@ -555,11 +558,13 @@ std::vector<CombineResult> Runtime::combine(const std::vector<std::shared_ptr<Ru
     EP_HOST_ASSERT_MSG(plan_combine(m.r[0], num_blocks, rt0.smem_optin_, &launch), "a token row does not fit into shared memory");
     rt0.prof_record(3, stream);
     CUDA_RUNTIME_CHECK(launch_combine(m, launch, stream));
+    ++rt0.num_launches_;
     rt0.prof_record(4, stream);
     if (a0.sc.previous_event_before_epilogue.has_value()) a0.sc.previous_event_before_epilogue->stream_wait(scope.comm);
     if (!fuse && !direct) {
         const int epi_sms = std::max(1, rt0.num_device_sms_ / V);
         CUDA_RUNTIME_CHECK(launch_combine_epilogue(ep.data(), V, epi_sms, stream));
+        ++rt0.num_launches_;
     }
     rt0.prof_record(5, stream);
     rt0.prof_valid_[1] = rt0.profiling_;

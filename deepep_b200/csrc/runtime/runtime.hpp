@@ -124,6 +124,8 @@ public:
     // Optional device timing of the last dispatch / combine: events around the communication
     // kernel and around the local epilogue (what the reference reports as two separate kernels).
     void enable_profiling(bool on);
+    // kernels this runtime has launched so far (barrier, dispatch, combine and their epilogues)
+    int64_t num_kernel_launches() const { return num_launches_; }
     std::vector<float> last_timings();   // {dispatch kernel, dispatch epilogue, combine kernel, combine epilogue} in ms, -1 = not run
 
     // Phase timestamps (ns) that block 0 of the last dispatch kernel wrote: start, counted, exchanged,
@@ -166,6 +168,7 @@ private:
     int num_device_sms_ = 0, smem_optin_ = 0;
     bool destroyed_ = false;
     bool profiling_ = false;
+    int64_t num_launches_ = 0;
     cudaEvent_t prof_events_[6] = {nullptr, nullptr, nullptr, nullptr, nullptr, nullptr};
     bool prof_valid_[2] = {false, false};
     void prof_record(int idx, cudaStream_t stream) {

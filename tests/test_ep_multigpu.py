@@ -150,6 +150,17 @@ def _subsystems_worker(rank: int, world: int, port: int):
     dist.barrier()
     buf.destroy()
 
+    # ---- the same table in the ranks' pinned host segments (one POSIX shared-memory object per rank, read over PCIe)
+    hbuf = deepep_b200.ElasticBuffer(group, num_bytes=16 << 20, num_cpu_bytes=1 << 20, num_gpu_timeout_secs=10, explicitly_destroy=True)
+    assert len(hbuf.host_segments) == world
+    hbuf.engram_write(table[rank * per_rank:(rank + 1) * per_rank].contiguous())
+    data, _ = hbuf.engram_fetch(q)()
+    torch.cuda.synchronize()
+    assert torch.equal(data, table[q.flatten().long()])
+    hbuf.check_status()
+    dist.barrier()
+    hbuf.destroy()
+
     # ---- fused tensor-parallel GEMMs against NCCL + matmul
     from deepep_b200.parallel.tp_fused import TensorParallelContext, nccl_all_gather_gemm, nccl_gemm_reduce_scatter
     ctx = TensorParallelContext(group, 256, 512, 512, num_gpu_timeout_secs=10)

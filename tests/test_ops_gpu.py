@@ -50,3 +50,33 @@ def test_swiglu_forward_backward_and_fused_cast():
     assert torch.allclose(dx.float(), xf.grad, rtol=3e-2, atol=3e-2)
     t = C.transpose_bf16(x)
     assert torch.equal(t, x.t().contiguous())
+
+
+def test_ops_package_wrappers():
+    """deepep_b200.ops: the typed entry points and their fp32 references agree."""
+    from deepep_b200 import ops
+    g = torch.Generator(device='cuda').manual_seed(3)
+    a = torch.randn((300, 512), device='cuda', generator=g).bfloat16()
+    b = (torch.randn((256, 512), device='cuda', generator=g) * 0.05).bfloat16()
+    ref = ops.ref_gemm(a, b)
+    assert ((ops.gemm(a, b).float() - ref).norm() / ref.norm()).item() < 1e-2
+    # grouped, fp8 with block scales
+    G, N, K = 3, 256, 512
+    ends = torch.tensor([100, 300, 520], dtype=torch.int32, device='cuda')      # starts 0, 128, 384
+    M = 640
+    x = torch.randn((M, K), device='cuda', generator=g).bfloat16()
+    w = (torch.randn((G, N, K), device='cuda', generator=g) * 0.05).bfloat16()
+    out = ops.grouped_gemm(x, w, ends, 128)
+    ref = ops.ref_grouped_gemm(x, w, ends, 128)
+    for s0, e0 in ((0, 100), (128, 300), (384, 520)):
+        assert ((out[s0:e0].float() - ref[s0:e0]).norm() / ref[s0:e0].norm()).item() < 1e-2
+    xq, sfa = ops.quant_1x128(x)
+    got8 = ops.gemm(xq, b.to(torch.float8_e4m3fn), sfa, torch.ones((2, 4), device='cuda'))
+    ref8 = ops.ref_gemm(xq, b.to(torch.float8_e4m3fn), sfa, torch.ones((2, 4), device='cuda'))
+    assert ((got8.float() - ref8).norm() / ref8.norm()).item() < 1e-2
+    idx, wts = ops.router_topk(torch.randn((50, 64), device='cuda', generator=g), 4)
+    assert idx.shape == (50, 4) and torch.allclose(wts.sum(dim=1), torch.ones(50, device='cuda'), atol=1e-5)
+    y, _ = ops.swiglu(x)
+    assert torch.allclose(y.float(), ops.ref_swiglu(x), rtol=2e-2, atol=2e-2)
+    assert torch.equal(ops.transpose(x), x.t().contiguous())
+    assert torch.equal(ops.dequant_1x128(xq, sfa), (xq.float() * sfa.repeat_interleave(128, dim=1)).bfloat16())

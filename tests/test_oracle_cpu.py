@@ -156,3 +156,21 @@ def test_numa_helpers(tmp_path):
     assert numa.pci_numa_node('0000:1b:00.0', str(tmp_path)) is None
     assert numa.node_cpus(1, str(tmp_path)) == list(range(32, 64))
     assert numa.node_cpus(7, str(tmp_path)) == []
+
+
+def test_ops_references_cpu():
+    """The fp32 reference functions of deepep_b200.ops are plain torch and run anywhere."""
+    from deepep_b200 import ops
+    torch.manual_seed(0)
+    a, b = torch.randn(5, 256), torch.randn(128, 256)
+    assert torch.allclose(ops.ref_gemm(a, b), a @ b.t())
+    sfa, sfb = torch.full((5, 2), 2.0), torch.full((1, 2), 0.5)
+    assert torch.allclose(ops.ref_gemm(a, b, sfa, sfb), a @ b.t(), rtol=1e-5, atol=1e-4)
+    ends = torch.tensor([3, 5], dtype=torch.int32)
+    w = torch.randn(2, 4, 256)
+    out = ops.ref_grouped_gemm(a, w, ends, 1)
+    assert torch.allclose(out[:3], a[:3] @ w[0].t()) and torch.allclose(out[3:], a[3:] @ w[1].t())
+    idx, wt = ops.ref_router_topk(torch.randn(7, 16), 3)
+    assert idx.shape == (7, 3) and torch.allclose(wt.sum(1), torch.ones(7))
+    x = torch.randn(4, 8)
+    assert torch.allclose(ops.ref_swiglu(x), torch.nn.functional.silu(x[:, :4]) * x[:, 4:])
