@@ -43,6 +43,7 @@ def main():
     ap.add_argument('--k', type=int, default=7168)
     ap.add_argument('--iters', type=int, default=10)
     ap.add_argument('--warmup', type=int, default=3)
+    ap.add_argument('--baseline', action='store_true', help='gemm: also time torch.matmul on the same tensors')
     a = ap.parse_args()
 
     import deepep_b200
@@ -83,6 +84,9 @@ def main():
         out = torch.empty((a.m, a.n), device='cuda', dtype=torch.bfloat16)
         ms = _timeit(lambda: C.gemm(x, wt, out=out), a.iters, a.warmup)
         print(f'gemm bf16 {a.m}x{a.n}x{a.k}: {ms * 1e3:.1f} us, {2 * a.m * a.n * a.k / ms / 1e9:.0f} TFLOP/s')
+        if a.baseline:     # the library GEMM on the same tensors, as the yardstick only
+            ms = _timeit(lambda: torch.matmul(x, wt.t(), out=out), a.iters, a.warmup)
+            print(f'cuBLAS (torch.matmul) same tensors: {ms * 1e3:.1f} us, {2 * a.m * a.n * a.k / ms / 1e9:.0f} TFLOP/s')
     elif a.op == 'gemm_fp8_grouped':
         G, rows = 8, a.m // 8 // 128 * 128
         M = G * rows
