@@ -149,6 +149,7 @@ class ElasticBuffer:
         self.runtime = _C.Runtime(self.rank_idx, self.num_ranks, num_bytes, float(num_gpu_timeout_secs),
                                   float(num_cpu_timeout_secs))
         self._destroyed = False
+        self._connect_host_segments()
         self._connect()
 
         self.num_scaleout_ranks, self.num_scaleup_ranks = self.get_logical_domain_size()
@@ -174,7 +175,6 @@ class ElasticBuffer:
         if self.num_ranks > 1:
             dist.barrier(group=self.group)
         torch.cuda.synchronize()
-        self._connect_host_segments()
 
     def _connect_host_segments(self) -> None:
         """``num_cpu_bytes > 0``: one pinned host segment per rank (POSIX shared memory registered with CUDA), mapped

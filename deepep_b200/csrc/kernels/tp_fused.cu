@@ -596,7 +596,7 @@ __global__ void __launch_bounds__(kRsThreads, 1) gemm_rs_kernel(const __grid_con
 
 static bool tp_pairs_enabled() {
     const char* e = std::getenv("EP_TP_CTA_PAIR");
-    return e != nullptr && e[0] == '1';
+    return e == nullptr || e[0] != '0';
 }
 
 // cooperative launch (all CTAs resident: they wait for one another) in clusters of two
