@@ -134,7 +134,57 @@ __global__ void __launch_bounds__(1024, 1) dispatch_kernel(const __grid_constant
     if (stamper) stamps[0] = globaltimer_ns();
 
     if (!p.cached) {
-        // ------------------------------------------------------------ A. count
+        // ------------------------------------------------------------ A0. count
+        // Totals only: how many tokens this block sends to every rank and how many (token, expert) pairs to
+        // every expert. They are all the exchange needs, so they go out first; the order-preserving pass that gives
+        // every token its position (A1 below) then runs while the peers' totals are on their way.
+        for (int e = tid; e < E; e += nthreads) s_exp_tot[e] = 0;
+        if (tid < kMaxRanks) s_flags[tid] = 0;
+        __syncthreads();
+        for (int t = t0 + tid; t < t1; t += nthreads) {
+            uint32_t mask = 0;
+            for (int k = 0; k < K; ++k) {
+                const int64_t raw = p.topk_idx[static_cast<int64_t>(t) * K + k];
+                if (raw >= 0 && raw < E) {
+                    atomicAdd(s_exp_tot + static_cast<int>(raw), 1);
+                    mask |= 1u << (static_cast<int>(raw) / EL);
+                }
+            }
+            for (int d = 0; d < R; ++d)
+                if ((mask >> d) & 1u) atomicAdd(s_flags + d, 1);
+        }
+        __syncthreads();
+        int* tot_cnt = blk_cnt + kTotOffset;   // [CW] totals over the blocks
+        for (int j = tid; j < CW; j += nthreads) {
+            const int v = j < R ? s_flags[j] : s_exp_tot[j - R];
+            blk_cnt[bid * CW + j] = v;
+            if (v != 0) atomicAdd(tot_cnt + j, v);
+        }
+        __threadfence();
+        ok &= grid_barrier(w, grid_counter, p.grid_bar_base + nb, 1);
+        if (stamper) stamps[1] = globaltimer_ns();
+
+        // ------------------------------------------------------------ B. exchange (send the totals, sum the earlier blocks)
+        for (int j = tid; j < CW; j += nthreads) {
+            if (bid == 0) {
+                const uint64_t word = pack_epoch(p.epoch, static_cast<uint32_t>(__ldcg(tot_cnt + j)));
+                const int col = j < R ? j : kMaxRanks + (j - R);
+                for (int d = 0; d < R; ++d) {
+                    uint64_t* remote = reinterpret_cast<uint64_t*>(c.heap[d]) + kCtlDispatchCnt + static_cast<size_t>(c.rank) * kCntStride + col;
+                    st_relaxed_sys_u64(remote, word);
+                }
+            }
+            int before = 0;
+            for (int b0 = 0; b0 < bid; b0 += 8) {
+                int v[8];
+#pragma unroll
+                for (int u = 0; u < 8; ++u) v[u] = (b0 + u < bid) ? __ldcg(blk_cnt + (b0 + u) * CW + j) : 0;
+#pragma unroll
+                for (int u = 0; u < 8; ++u) before += v[u];
+            }
+            if (j < R) s_rank_base[j] = before; else s_exp_base[j - R] = before;
+        }
+        // ------------------------------------------------------------ A1. positions of this block's tokens
         // The routing of the chunk is staged in shared memory (the send buffers are idle now).
         // The chunk is cut into contiguous sub-ranges, one per counting warp; every warp ranks its
         // (token, rank) and (token, expert) pairs among its own earlier tokens, a prefix over the
@@ -149,6 +199,7 @@ __global__ void __launch_bounds__(1024, 1) dispatch_kernel(const __grid_constant
         int* s_idx = s_wrank + cw * kMaxRanks;                  // [cap_tokens][K]
         const int cap_tokens = max(32, ((scratch_bytes - cw * (E + kMaxRanks) * 4) / ((K + R) * 4)) & ~31);
         int* s_slot = s_idx + cap_tokens * K;                   // [cap_tokens][R]
+        __syncthreads();
         for (int e = tid; e < E; e += nthreads) s_exp_tot[e] = 0;
         if (tid < kMaxRanks) s_flags[tid] = 0;
         for (int tile0 = t0; tile0 < t1; tile0 += cap_tokens) {
@@ -236,36 +287,7 @@ __global__ void __launch_bounds__(1024, 1) dispatch_kernel(const __grid_constant
             }
         }
         __syncthreads();
-        int* tot_cnt = blk_cnt + kTotOffset;   // [CW] totals over the blocks
-        for (int j = tid; j < CW; j += nthreads) {
-            const int v = j < R ? s_flags[j] : s_exp_tot[j - R];
-            blk_cnt[bid * CW + j] = v;
-            if (v != 0) atomicAdd(tot_cnt + j, v);
-        }
-        __threadfence();
-        ok &= grid_barrier(w, grid_counter, p.grid_bar_base + nb, 1);
-        if (stamper) stamps[1] = globaltimer_ns();
-
-        // ------------------------------------------------------------ B. exchange
-        for (int j = tid; j < CW; j += nthreads) {
-            if (bid == 0) {
-                const uint64_t word = pack_epoch(p.epoch, static_cast<uint32_t>(__ldcg(tot_cnt + j)));
-                const int col = j < R ? j : kMaxRanks + (j - R);
-                for (int d = 0; d < R; ++d) {
-                    uint64_t* remote = reinterpret_cast<uint64_t*>(c.heap[d]) + kCtlDispatchCnt + static_cast<size_t>(c.rank) * kCntStride + col;
-                    st_relaxed_sys_u64(remote, word);
-                }
-            }
-            int before = 0;
-            for (int b0 = 0; b0 < bid; b0 += 8) {
-                int v[8];
-#pragma unroll
-                for (int u = 0; u < 8; ++u) v[u] = (b0 + u < bid) ? __ldcg(blk_cnt + (b0 + u) * CW + j) : 0;
-#pragma unroll
-                for (int u = 0; u < 8; ++u) before += v[u];
-            }
-            if (j < R) s_rank_base[j] = before; else s_exp_base[j - R] = before;
-        }
+        // ------------------------------------------------------------ B'. the peers' totals -> first rows
         for (int j = tid; j < CW; j += nthreads) {
             const int col = j < R ? j : kMaxRanks + (j - R);
             const uint64_t* words = my_ctl + kCtlDispatchCnt + col;
