@@ -1,15 +1,16 @@
 // High-throughput expert-parallel dispatch for one NVLink/NVSwitch domain (sm_100a).
 //
 // ONE cooperative kernel per rank does, in order:
-//   A. count     every block scans its contiguous chunk of tokens: destination-rank set per
-//                token and the position of each (token, rank) and (token, expert) pair
-//                among the block's earlier tokens (token order, so the result is the same
-//                on every run)
-//   B. exchange  block 0 all-gathers this rank's per-rank and per-expert totals into every
-//                peer's control area as epoch-tagged words; every block waits for the whole
-//                matrix and derives, without further communication, the first row of its own
-//                tokens in each destination's receive region and in each expert's segment of
-//                the expanded (expert-major) layout
+//   A0. totals   every block counts what its contiguous chunk of tokens sends to each rank and
+//                each expert (histogram, no order)
+//   B.  exchange block 0 all-gathers this rank's per-rank and per-expert totals into every
+//                peer's control area as epoch-tagged words
+//   A1. order    while those words travel, every block works out the destination-rank set per
+//                token and the position of each (token, rank) and (token, expert) pair among
+//                the block's earlier tokens (token order, so the result is the same on every run)
+//   B'. bases    every block waits for the whole matrix of totals and derives, without further
+//                communication, the first row of its own tokens in each destination's receive
+//                region and in each expert's segment of the expanded (expert-major) layout
 //   C. send      one warp per token: bulk-load the row into shared memory, optionally cast it
 //                to e4m3 with 1x128 scales, build the meta row, and bulk-store payload and
 //                meta straight to row `slot` of every destination rank's receive region
