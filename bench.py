@@ -144,6 +144,92 @@ def reference_arm(args):
                       'needs the NCCL Gin device API (NCCL >= 2.30.4; image has 2.28.9) and NVSHMEM headers need infiniband/mlx5dv.h'}))
 
 
+def moe_layer_section(buf, world, rank, dev, hidden, num_experts, num_topk, max_over_ranks, num_tokens=4096, intermediate=2048,
+                      iters=5):
+    """Forward + backward of the fused MoE layer (FP8 dispatch and expert GEMMs, bf16 gradients), Zipf-skewed routing."""
+    import torch
+    import torch.distributed as dist
+    from deepep_b200.models.moe import ExpertWeights, MoEConfig, _SingleRankComm, moe_backward, moe_forward
+    from deepep_b200.utils import gate
+    el = num_experts // world
+    cfg = MoEConfig(hidden=hidden, intermediate=intermediate, num_experts=num_experts, num_topk=num_topk, use_fp8=True, num_sms=24)
+    g = torch.Generator(device=dev).manual_seed(7 + rank)
+    w13 = (torch.randn((el, 2 * intermediate, hidden), device=dev, generator=g) * 0.02).bfloat16()
+    w2 = (torch.randn((el, hidden, intermediate), device=dev, generator=g) * 0.02).bfloat16()
+    weights = ExpertWeights(w13, w2, True)
+    comm = _SingleRankComm(buf)
+    gen = torch.Generator().manual_seed(17 + rank)
+    x = torch.randn((num_tokens, hidden), generator=gen).bfloat16().to(dev)
+    scores = gate.get_zipf_scores(num_tokens, num_experts, 1.2, generator=gen) if hasattr(gate, 'get_zipf_scores') \
+        else gate.get_balanced_scores(num_tokens, num_experts, generator=gen)
+    idx, w = gate.topk_from_scores(scores, num_topk)
+    idx, w = idx.to(dev), w.to(dev)
+    dy = torch.randn((num_tokens, hidden), device=dev, generator=g).bfloat16()
+
+    def step():
+        ys, ctxs = moe_forward(comm, [weights], [x], [idx], [w], cfg)
+        return moe_backward(comm, [weights], ctxs, [dy], cfg)
+
+    for _ in range(2):
+        step()
+    torch.cuda.synchronize()
+    if world > 1:
+        dist.barrier()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(iters):
+        step()
+    e1.record()
+    torch.cuda.synchronize()
+    buf.check_status()
+    ms = max_over_ranks(e0.elapsed_time(e1) / iters)
+    flops = 3 * 2 * num_tokens * num_topk * 3 * hidden * intermediate       # fwd + 2x bwd, three GEMMs of hidden x intermediate per pair
+    res = {'tokens_per_rank': num_tokens, 'hidden': hidden, 'intermediate': intermediate, 'num_experts': num_experts,
+           'num_topk': num_topk, 'routing': 'zipf 1.2', 'fwd_bwd_ms': round(ms, 3),
+           'expert_tflops_per_gpu': round(flops / (ms * 1e-3) / 1e12, 1)}
+    if world > 1:
+        dist.barrier()
+    return res
+
+
+def tp_section(group, world, rank, dev, max_over_ranks, tokens=8192, hidden=7168, ffn=18432, iters=5):
+    """Fused all-gather -> GEMM and GEMM -> reduce-scatter against NCCL + cuBLAS (bf16)."""
+    import torch
+    import torch.distributed as dist
+    from deepep_b200.parallel.tp_fused import TensorParallelContext, nccl_all_gather_gemm, nccl_gemm_reduce_scatter
+    ml, fl = tokens // world, ffn // world
+    ctx = TensorParallelContext(group, ml, hidden, hidden, num_gpu_timeout_secs=20)
+    g = torch.Generator(device=dev).manual_seed(rank)
+    x_shard = torch.randn((ml, hidden), device=dev, generator=g).bfloat16()
+    w1 = (torch.randn((fl, hidden), device=dev, generator=g) * 0.02).bfloat16()
+    x2 = torch.randn((tokens, fl), device=dev, generator=g).bfloat16()
+    w2 = (torch.randn((hidden, fl), device=dev, generator=g) * 0.02).bfloat16()
+
+    def timeit(fn):
+        for _ in range(2):
+            fn()
+        torch.cuda.synchronize()
+        dist.barrier()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(iters):
+            fn()
+        e1.record()
+        torch.cuda.synchronize()
+        return max_over_ranks(e0.elapsed_time(e1) / iters) * 1e3
+
+    res = {'tokens': tokens, 'hidden': hidden, 'ffn': ffn,
+           'ag_gemm_fused_us': round(timeit(lambda: ctx.all_gather_gemm(x_shard, w1)), 1),
+           'ag_gemm_nccl_cublas_us': round(timeit(lambda: nccl_all_gather_gemm(x_shard, w1, group)), 1),
+           'gemm_rs_fused_us': round(timeit(lambda: ctx.gemm_reduce_scatter(x2, w2)), 1),
+           'gemm_rs_cublas_nccl_us': round(timeit(lambda: nccl_gemm_reduce_scatter(x2, w2, group)), 1)}
+    ctx.check_status()
+    dist.barrier()
+    torch.cuda.synchronize()
+    ctx.destroy()
+    return res
+
+
 def low_latency_section(deepep_b200, group, world, rank, dev, hidden, num_experts, num_topk, max_over_ranks, num_tokens=128,
                         iters=200):
     """p50 / p99 of one decode step (dispatch + combine, 128 tokens per rank) replayed from a CUDA graph."""
@@ -398,6 +484,18 @@ def main():
             detail['low_latency'] = low_latency_section(deepep_b200, group, world, rank, dev, H, E, K, max_over_ranks)
         except Exception as exc:   # noqa: BLE001 - a failure here must not take the headline number down
             detail['low_latency'] = {'error': f'{type(exc).__name__}: {exc}'[:200]}
+        # ---- fused MoE layer forward + backward (FP8 forward, bf16 gradients); needs the experts of a rank to fit comfortably
+        if E // world <= 64:
+            try:
+                detail['moe_layer'] = moe_layer_section(buf, world, rank, dev, H, E, K, max_over_ranks)
+            except Exception as exc:   # noqa: BLE001
+                detail['moe_layer'] = {'error': f'{type(exc).__name__}: {exc}'[:200]}
+        # ---- fused tensor-parallel GEMMs against NCCL + cuBLAS
+        if world > 1:
+            try:
+                detail['tp'] = tp_section(group, world, rank, dev, max_over_ranks)
+            except Exception as exc:   # noqa: BLE001
+                detail['tp'] = {'error': f'{type(exc).__name__}: {exc}'[:200]}
         # ---- plain NCCL all-to-all of the same FP8 rows (baseline, not the product)
         if world > 1:
             try:
