@@ -233,6 +233,16 @@ def test_cached_dispatch_no_cpu_sync_zero_copy():
         n = int(handle.psum_num_recv_tokens_per_scaleup_rank[-1].item())
         assert recv_x.size(0) == R * T and n == exp[r]['recv_x'].size(0)
         assert torch.equal(recv_x[:n].cpu(), exp[r]['recv_x'])
+    # ... and the combine takes the worst-case shaped tensor as it is (the true row count is read on the device)
+    from deepep_b200.utils import refs
+    comb = cl.combine([dict(x=third[r][0], handle=third[r][3]) for r in range(R)])
+    torch.cuda.synchronize()
+    cl.check_status()
+    ns = [int(third[r][3].psum_num_recv_tokens_per_scaleup_rank[-1].item()) for r in range(R)]
+    srcs = [third[r][3].recv_src_metadata[:ns[r], 0].cpu() for r in range(R)]
+    for r in range(R):
+        ref = refs.combine_local([third[q][0][:ns[q]].cpu() for q in range(R)], srcs, r, xs[r].size(0), T)
+        assert torch.equal(comb[r][0].cpu(), ref)
     cl.destroy()
 
 
