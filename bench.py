@@ -442,10 +442,14 @@ def main():
             for q in range(4):
                 samples[q].append(t[q])
         acc = [max_over_ranks(sorted(v)[len(v) // 2]) for v in samples]
+        # block 0's timestamps inside the last dispatch kernel of this rank: totals counted and through the grid barrier,
+        # first rows known (exchange done), all rows issued, own stores complete, peers' rows complete
+        phases = [round(v / 1e3, 1) for v in buf.runtime.last_dispatch_phases()]
         n = true_recv_tokens(h)
         return {'num_sms': num_sms,
                 'dispatch_kernel_us': round(acc[0] * 1e3, 1), 'dispatch_epilogue_us': round(acc[1] * 1e3, 1),
                 'combine_kernel_us': round(acc[2] * 1e3, 1), 'combine_epilogue_us': round(acc[3] * 1e3, 1),
+                'dispatch_phases_us_rank0': phases,
                 'dispatch_kernel_gbs': round(n * disp_bytes_tok / (acc[0] * 1e-3) / 1e9, 1),
                 'combine_kernel_gbs': round(n * comb_bytes_tok / (acc[2] * 1e-3) / 1e9, 1),
                 'dispatch_e2e_gbs': round(n * disp_bytes_tok / ((acc[0] + acc[1]) * 1e-3) / 1e9, 1),
