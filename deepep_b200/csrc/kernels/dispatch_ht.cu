@@ -142,17 +142,26 @@ __global__ void __launch_bounds__(1024, 1) dispatch_kernel(const __grid_constant
         for (int e = tid; e < E; e += nthreads) s_exp_tot[e] = 0;
         if (tid < kMaxRanks) s_flags[tid] = 0;
         __syncthreads();
-        for (int t = t0 + tid; t < t1; t += nthreads) {
+        for (int base = t0 + warp * 32; base < t1; base += nthreads) {      // a warp takes 32 consecutive tokens
+            const int t = base + lane;
             uint32_t mask = 0;
-            for (int k = 0; k < K; ++k) {
-                const int64_t raw = p.topk_idx[static_cast<int64_t>(t) * K + k];
-                if (raw >= 0 && raw < E) {
-                    atomicAdd(s_exp_tot + static_cast<int>(raw), 1);
-                    mask |= 1u << (static_cast<int>(raw) / EL);
+            if (t < t1) {
+                for (int k = 0; k < K; ++k) {
+                    const int64_t raw = p.topk_idx[static_cast<int64_t>(t) * K + k];
+                    if (raw >= 0 && raw < E) {
+                        atomicAdd(s_exp_tot + static_cast<int>(raw), 1);
+                        mask |= 1u << (static_cast<int>(raw) / EL);
+                    }
                 }
             }
-            for (int d = 0; d < R; ++d)
-                if ((mask >> d) & 1u) atomicAdd(s_flags + d, 1);
+            // one shared-memory atomic per warp and destination rank instead of one per token
+#pragma unroll
+            for (int d = 0; d < kMaxRanks; ++d) {
+                if (d < R) {
+                    const int n = __popc(__ballot_sync(0xffffffffu, (mask >> d) & 1u));
+                    if (lane == d && n != 0) atomicAdd(s_flags + d, n);
+                }
+            }
         }
         __syncthreads();
         int* tot_cnt = blk_cnt + kTotOffset;   // [CW] totals over the blocks
