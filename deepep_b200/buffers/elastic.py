@@ -127,8 +127,6 @@ class ElasticBuffer:
         self.fuse_combine_reduce = int(os.environ.get('EP_COMBINE_FUSED_REDUCE', '0'))
         # blocks on top of num_sms that only reduce (fused reduce); 0 = the spare warps of the send blocks do it all
         self.num_combine_reduce_sms = int(os.environ.get('EP_COMBINE_REDUCE_SMS', '0'))
-        # combine: warps beyond the shared-memory staging buffers that send rows through registers
-        self.num_combine_reg_warps = int(os.environ.get('EP_COMBINE_REG_WARPS', '0'))
         self.prefer_overlap_with_compute = prefer_overlap_with_compute
         self.deterministic = deterministic
         self.use_fp8_dispatch = use_fp8_dispatch
@@ -527,7 +525,6 @@ class ElasticBuffer:
         a.dst_slot = handle.dst_buffer_slot_idx
         a.fuse_reduce = self.fuse_combine_reduce
         a.num_reduce_sms = self.num_combine_reduce_sms
-        a.num_reg_warps = self.num_combine_reg_warps
         sc = a.sc
         sc.previous_event = previous_event
         sc.previous_event_before_epilogue = previous_event_before_epilogue

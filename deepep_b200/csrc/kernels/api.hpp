@@ -148,7 +148,6 @@ struct CombineParams {
     int fuse_reduce;
     int num_send_warps;       // warps [0, num_send_warps) send; the block may carry more warps that only reduce
     int num_send_blocks;      // blocks [0, num_send_blocks) send (and reduce); further blocks only reduce
-    int num_reg_warps;        // extra warps per send block that copy rows through registers (no staging buffer)
     int direct_out;           // single rank, no bias, one row per token: rows go straight to red.combined_x, no reduce
     int flag_chunks;          // flag words per source rank = ceil(ranks * max tokens / kCombineFlagRows)
     const int* dst_slot;      // [T, R] row of each of this rank's tokens in every destination's receive region (-1 = none)

@@ -48,19 +48,6 @@ __device__ __forceinline__ int4 pack_bf16x8(const float (&acc)[8]) {
     return out;
 }
 
-// Row copy through registers (no shared-memory staging): eight 16-byte loads in flight per lane, then posted stores.
-__device__ __noinline__ void copy_row_regs(const uint8_t* src, uint8_t* dst, int vec_per_row, int lane) {
-    for (int v = lane; v < vec_per_row; v += 256) {
-        int4 raw[8];
-#pragma unroll
-        for (int j = 0; j < 8; ++j)
-            if (v + 32 * j < vec_per_row) raw[j] = ld_nc_int4(src + (v + 32 * j) * 16);
-#pragma unroll
-        for (int j = 0; j < 8; ++j)
-            if (v + 32 * j < vec_per_row) st_na_int4(dst + (v + 32 * j) * 16, raw[j]);
-    }
-}
-
 // NV columns (16 bytes each) per lane and pass, rows taken NR at a time.
 template <int NV, int NR>
 __device__ __forceinline__ void reduce_columns(const CombineEpilogueParams& p, int t, uint32_t mask, int lane, const uint8_t* b0,
@@ -245,27 +232,7 @@ __global__ void __launch_bounds__(1024, 1) combine_kernel(const __grid_constant_
     const int64_t total_steps = static_cast<int64_t>(max_group) * R;
     // rows are handed out dynamically (SMs differ in how fast their peer stores drain)
     unsigned long long* work = reinterpret_cast<unsigned long long*>(c.local_ws + kWsWork);
-    // Warps beyond the staging buffers can send too, through registers: their rows occupy no shared memory, which
-    // adds bytes in flight when few SMs have to fill the NVLink pipe.
-    const bool reg_sender = !is_sender && !kFused && bid < nb_send && warp < num_warps + p.num_reg_warps;
-    int64_t g = total_steps;
-    if (is_sender) {
-        g = static_cast<int64_t>(bid) * num_warps + warp;
-    } else if (reg_sender) {
-        long long first = 0;
-        if (lane == 0) first = static_cast<long long>(atomicAdd(work, 1ull)) + static_cast<long long>(nb_send) * num_warps;
-        g = __shfl_sync(0xffffffffu, first, 0);
-    }
-    if (p.direct_out) {
-        // tokens without any valid expert receive no row: their result is zero
-        const int all_warps = blockDim.x >> 5;
-        for (int t = bid * all_warps + warp; t < p.red.num_tokens; t += nb * all_warps) {
-            if (__any_sync(0xffffffffu, token_expert(p.red, t, lane) >= 0)) continue;
-            for (int v = lane; v < vec_per_row; v += 32)
-                st_na_int4(p.red.combined_x + static_cast<uint64_t>(t) * p.row_bytes + v * 16, make_int4(0, 0, 0, 0));
-            if (p.red.combined_topk_weights != nullptr && lane < K) p.red.combined_topk_weights[static_cast<int64_t>(t) * K + lane] = 0.f;
-        }
-    }
+    int64_t g = is_sender ? static_cast<int64_t>(bid) * num_warps + warp : total_steps;
     int64_t next_g = 0;
     bool fatal = false;
     for (; g < total_steps && !fatal; g = next_g) {
@@ -288,7 +255,7 @@ __global__ void __launch_bounds__(1024, 1) combine_kernel(const __grid_constant_
         __syncwarp();
         if (!p.do_expand) {
             // one row per received token: forward it as it is
-            if (is_sender && lane == 0) {
+            if (lane == 0) {
                 mbar_arrive_expect_tx(bar, p.row_bytes);
                 bulk_g2s(buf, p.x + static_cast<int64_t>(i) * p.x_stride_bytes, p.row_bytes, bar);
             }
@@ -303,10 +270,6 @@ __global__ void __launch_bounds__(1024, 1) combine_kernel(const __grid_constant_
                         token_expert(p.red, src_token, lane) >= 0 && p.topk_weights != nullptr ? p.topk_weights[static_cast<int64_t>(i) * K + lane] : 0.f;
             } else if (p.topk_weights != nullptr && lane < K) {
                 reinterpret_cast<float*>(heap + p.off_comb_w)[dst_row * K + lane] = p.topk_weights[static_cast<int64_t>(i) * K + lane];
-            }
-            if (!is_sender) {
-                copy_row_regs(p.x + static_cast<int64_t>(i) * p.x_stride_bytes, dst_ptr, vec_per_row, lane);
-                break;
             }
             const bool landed = mbar_wait(w, bar, parity, kStatusTmaLoad, i);
             parity ^= 1;
@@ -334,10 +297,7 @@ __global__ void __launch_bounds__(1024, 1) combine_kernel(const __grid_constant_
                     const int row = __shfl_sync(0xffffffffu, my_row, k);
                     accumulate_bf16x8(acc, ld_nc_int4(p.x + static_cast<int64_t>(row) * p.x_stride_bytes + v * 16));
                 }
-                if (is_sender)
-                    reinterpret_cast<int4*>(buf)[v] = pack_bf16x8(acc);
-                else
-                    st_na_int4(dst_ptr + v * 16, pack_bf16x8(acc));
+                reinterpret_cast<int4*>(buf)[v] = pack_bf16x8(acc);
             }
             if (p.direct_out) {
                 if (p.red.combined_topk_weights != nullptr && lane < K)
@@ -346,7 +306,6 @@ __global__ void __launch_bounds__(1024, 1) combine_kernel(const __grid_constant_
             } else if (p.topk_weights != nullptr && my_row >= 0) {
                 reinterpret_cast<float*>(heap + p.off_comb_w)[dst_row * K + lane] = p.topk_weights[my_row];
             }
-            if (!is_sender) break;
             fence_proxy_async_smem();
             __syncwarp();
             if (lane == 0) {
@@ -365,11 +324,6 @@ __global__ void __launch_bounds__(1024, 1) combine_kernel(const __grid_constant_
                 const int k = __ffs(todo) - 1;
                 todo &= todo - 1;
                 const int row = __shfl_sync(0xffffffffu, my_row, k);
-                if (!is_sender) {
-                    copy_row_regs(p.x + static_cast<int64_t>(row) * p.x_stride_bytes,
-                                  heap + p.off_comb_x + (static_cast<uint64_t>(k) * p.num_max_tokens + src_token) * p.row_bytes, vec_per_row, lane);
-                    continue;
-                }
                 bulk_wait_read_all();
                 __syncwarp();
                 if (lane == 0) {
@@ -385,7 +339,7 @@ __global__ void __launch_bounds__(1024, 1) combine_kernel(const __grid_constant_
                 }
             }
             if (failed) fatal = true;
-            if (is_sender && lane == 0 && kFused) {     // several stores per token: settle all of them, then count the token
+            if (lane == 0 && kFused) {     // several stores per token: settle all of them, then count the token
                 flush_sent();
                 chunk_row_landed(i / kCombineFlagRows);
             }
@@ -447,7 +401,7 @@ bool plan_combine(const CombineParams& p, int num_sms, int smem_optin, CombineLa
     if (warps < 1) return false;
     out->num_sms = num_sms;
     out->num_warps = warps;
-    out->num_reduce_warps = p.fuse_reduce ? 32 - warps : min(p.num_reg_warps, 32 - warps);
+    out->num_reduce_warps = p.fuse_reduce ? 32 - warps : 0;
     out->smem_bytes = warps * stage;
     return true;
 }
@@ -468,10 +422,7 @@ cudaError_t launch_combine(const Multi<CombineParams>& m, const CombineLaunch& l
     cfg.attrs = attr;
     cfg.numAttrs = 1;
     Multi<CombineParams> copy = m;
-    for (int v = 0; v < copy.num_vranks; ++v) {
-        copy.r[v].num_send_warps = l.num_warps;
-        copy.r[v].num_reg_warps = l.num_reduce_warps;
-    }
+    for (int v = 0; v < copy.num_vranks; ++v) copy.r[v].num_send_warps = l.num_warps;
     // blocks_per_rank counts the reduce-only blocks too
 
     return fused ? cudaLaunchKernelEx(&cfg, combine_kernel<true>, copy) : cudaLaunchKernelEx(&cfg, combine_kernel<false>, copy);

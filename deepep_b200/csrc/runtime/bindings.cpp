@@ -106,7 +106,6 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
         .def_readwrite("dst_slot", &CombineArgs::dst_slot)
         .def_readwrite("fuse_reduce", &CombineArgs::fuse_reduce)
         .def_readwrite("num_reduce_sms", &CombineArgs::num_reduce_sms)
-        .def_readwrite("num_reg_warps", &CombineArgs::num_reg_warps)
         .def_readwrite("sc", &CombineArgs::sc);
 
     py::class_<CombineResult>(m, "CombineResult")

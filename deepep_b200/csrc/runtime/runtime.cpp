@@ -507,7 +507,6 @@ std::vector<CombineResult> Runtime::combine(const std::vector<std::shared_ptr<Ru
         p.grid_bar_base = rt.grid_bar_base;
         rt.grid_bar_base += num_blocks;
         p.num_send_blocks = num_sms;
-        p.num_reg_warps = fuse ? 0 : std::max(0, a0.num_reg_warps);
         p.direct_out = 0;            // decided below, once the biases are known
 
         auto& r = res[v];

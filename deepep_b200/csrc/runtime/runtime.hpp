@@ -83,7 +83,6 @@ struct CombineArgs {
     std::optional<at::Tensor> dst_slot;
     int fuse_reduce = 0;       // non-zero: reduce inside the send kernel (opt-in)
     int num_reduce_sms = 0;    // fused reduce: extra blocks that only reduce (on top of num_sms)
-    int num_reg_warps = 0;     // extra warps per block that send rows through registers (up to 32 warps per block)
     StreamControl sc;
 };
 

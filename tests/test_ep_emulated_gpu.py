@@ -10,18 +10,13 @@ pytestmark = pytest.mark.gpu
 
 
 def _cluster(num_ranks, num_max_tokens, hidden, num_topk, fuse_reduce=None, **kw):
-    # fuse_reduce: 0 separate reduce kernel, 2 reduce inside the combine's send kernel, 'regs' extra sender warps that
-    # copy rows through registers (separate reduce kernel)
-    reg_warps = 0
-    if fuse_reduce == 'regs':
-        fuse_reduce, reg_warps = 0, 32
+    # fuse_reduce: 0 separate reduce kernel, 2 reduce inside the combine's send kernel
     from deepep_b200.parallel.local_cluster import LocalCluster
     cl = LocalCluster(num_ranks, num_max_tokens_per_rank=num_max_tokens, hidden=hidden, num_topk=num_topk,
                       num_gpu_timeout_secs=5, num_cpu_timeout_secs=20, **kw)
     if fuse_reduce is not None:
         for b in cl.buffers:
             b.fuse_combine_reduce = fuse_reduce
-            b.num_combine_reg_warps = reg_warps
     return cl
 
 
@@ -43,7 +38,7 @@ def _as_bytes(t):
     (4, 96, 1024, 32, 6, 4),
     (8, 128, 7168, 256, 8, 6),
 ])
-@pytest.mark.parametrize('fuse_reduce', [0, 2, 'regs'])
+@pytest.mark.parametrize('fuse_reduce', [0, 2])
 def test_dispatch_combine_bf16(num_ranks, num_tokens, hidden, num_experts, num_topk, num_sms, fuse_reduce):
     from deepep_b200.utils import refs
     T_max = num_tokens
@@ -127,7 +122,7 @@ def test_dispatch_fp8(fused, col_major):
 
 
 @pytest.mark.parametrize('alignment,zero_padding', [(1, False), (16, True)])
-@pytest.mark.parametrize('fuse_reduce', [0, 2, 'regs'])
+@pytest.mark.parametrize('fuse_reduce', [0, 2])
 def test_dispatch_expand_and_combine(alignment, zero_padding, fuse_reduce):
     from deepep_b200.utils import refs
     R, T, H, E, K = 4, 72, 512, 16, 3
@@ -178,7 +173,7 @@ def test_dispatch_expand_and_combine(alignment, zero_padding, fuse_reduce):
     cl.destroy()
 
 
-@pytest.mark.parametrize('fuse_reduce', [0, 2, 'regs'])
+@pytest.mark.parametrize('fuse_reduce', [0, 2])
 def test_combine_topk_layout_single_rounding(fuse_reduce):
     """allow_multiple_reduction=False: every expert row travels on its own and the source rank sums them in fp32 in
     ascending top-k order with one rounding."""
