@@ -166,8 +166,11 @@ def moe_layer_section(buf, world, rank, dev, hidden, num_experts, num_topk, max_
     idx, w = idx.to(dev), w.to(dev)
     dy = torch.randn((num_tokens, hidden), device=dev, generator=g).bfloat16()
 
+    rows = [0]
+
     def step():
         ys, ctxs = moe_forward(comm, [weights], [x], [idx], [w], cfg)
+        rows[0] = int(ctxs[0]['handle'].num_expanded_tokens)      # (token, expert) rows this rank's experts process
         return moe_backward(comm, [weights], ctxs, [dy], cfg)
 
     for _ in range(2):
@@ -183,10 +186,13 @@ def moe_layer_section(buf, world, rank, dev, hidden, num_experts, num_topk, max_
     torch.cuda.synchronize()
     buf.check_status()
     ms = max_over_ranks(e0.elapsed_time(e1) / iters)
-    flops = 3 * 2 * num_tokens * num_topk * 3 * hidden * intermediate       # fwd + 2x bwd, three GEMMs of hidden x intermediate per pair
+    # the step time is set by the rank whose experts are the popular ones: rate it by that rank's rows
+    busiest = int(max_over_ranks(float(rows[0])))
+    flops = 3 * 2 * busiest * 3 * hidden * intermediate       # fwd + 2x bwd, three GEMMs of hidden x intermediate per row
     res = {'tokens_per_rank': num_tokens, 'hidden': hidden, 'intermediate': intermediate, 'num_experts': num_experts,
            'num_topk': num_topk, 'routing': 'zipf 1.2', 'fwd_bwd_ms': round(ms, 3),
-           'expert_tflops_per_gpu': round(flops / (ms * 1e-3) / 1e12, 1)}
+           'expert_rows_busiest_rank': busiest, 'expert_rows_mean': num_tokens * num_topk,
+           'expert_tflops_busiest_gpu': round(flops / (ms * 1e-3) / 1e12, 1)}
     if world > 1:
         dist.barrier()
     return res

@@ -291,11 +291,22 @@ __global__ void __launch_bounds__(1024, 1) combine_kernel(const __grid_constant_
 #pragma unroll
                 for (int j = 0; j < 8; ++j) acc[j] = 0.f;
                 uint32_t todo = valid;
-                while (todo) {
-                    const int k = __ffs(todo) - 1;
-                    todo &= todo - 1;
-                    const int row = __shfl_sync(0xffffffffu, my_row, k);
-                    accumulate_bf16x8(acc, ld_nc_int4(p.x + static_cast<int64_t>(row) * p.x_stride_bytes + v * 16));
+                while (todo) {      // four rows in flight per lane, added in ascending top-k lane order
+                    int rows[4];
+#pragma unroll
+                    for (int r = 0; r < 4; ++r) {
+                        const int k = todo ? __ffs(todo) - 1 : -1;
+                        todo &= todo - 1;       // 0 stays 0
+                        const int row = __shfl_sync(0xffffffffu, my_row, k < 0 ? 0 : k);
+                        rows[r] = k < 0 ? -1 : row;
+                    }
+                    int4 raw[4];
+#pragma unroll
+                    for (int r = 0; r < 4; ++r)
+                        if (rows[r] >= 0) raw[r] = ld_nc_int4(p.x + static_cast<int64_t>(rows[r]) * p.x_stride_bytes + v * 16);
+#pragma unroll
+                    for (int r = 0; r < 4; ++r)
+                        if (rows[r] >= 0) accumulate_bf16x8(acc, raw[r]);
                 }
                 reinterpret_cast<int4*>(buf)[v] = pack_bf16x8(acc);
             }
