@@ -233,6 +233,16 @@ __global__ void __launch_bounds__(1024, 1) combine_kernel(const __grid_constant_
     // rows are handed out dynamically (SMs differ in how fast their peer stores drain)
     unsigned long long* work = reinterpret_cast<unsigned long long*>(c.local_ws + kWsWork);
     int64_t g = is_sender ? static_cast<int64_t>(bid) * num_warps + warp : total_steps;
+    if (p.direct_out) {
+        // tokens without any valid expert receive no row: their result is zero
+        const int all_warps = blockDim.x >> 5;
+        for (int t = bid * all_warps + warp; t < p.red.num_tokens; t += nb * all_warps) {
+            if (__any_sync(0xffffffffu, token_expert(p.red, t, lane) >= 0)) continue;
+            for (int v = lane; v < vec_per_row; v += 32)
+                st_na_int4(p.red.combined_x + static_cast<uint64_t>(t) * p.row_bytes + v * 16, make_int4(0, 0, 0, 0));
+            if (p.red.combined_topk_weights != nullptr && lane < K) p.red.combined_topk_weights[static_cast<int64_t>(t) * K + lane] = 0.f;
+        }
+    }
     int64_t next_g = 0;
     bool fatal = false;
     for (; g < total_steps && !fatal; g = next_g) {
