@@ -140,7 +140,7 @@ def reference_arm(args):
         except Exception as exc:   # noqa: BLE001
             print(json.dumps({'impl': 'reference', 'unavailable': f'baseline/_ref does not import: {type(exc).__name__}: {exc}'[:300]}))
             return
-    print(json.dumps({'impl': 'reference', 'unavailable': 'offline pip install of /root/reference failed: csrc/kernels/backend/nccl.cu '
+    print(json.dumps({'impl': 'reference', 'unavailable': 'offline pip install of the reference source failed: csrc/kernels/backend/nccl.cu '
                       'needs the NCCL Gin device API (NCCL >= 2.30.4; image has 2.28.9) and NVSHMEM headers need infiniband/mlx5dv.h'}))
 
 

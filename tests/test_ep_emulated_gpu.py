@@ -45,6 +45,8 @@ def test_dispatch_combine_bf16(num_ranks, num_tokens, hidden, num_experts, num_t
     cl = _cluster(num_ranks, T_max, hidden, num_topk, fuse_reduce=fuse_reduce)
     xs, idxs, ws = make_routed_inputs(num_ranks, num_tokens, hidden, num_experts, num_topk, seed=1, device='cuda',
                                       masked_ratio=0.05)
+    for idx in idxs:
+        idx[::9] = -1       # whole tokens that nobody takes: they must come back as zeros (+ bias)
     stats = [torch.zeros(num_experts // num_ranks, dtype=torch.int32, device='cuda') for _ in range(num_ranks)]
     out = cl.dispatch([dict(x=xs[r], topk_idx=idxs[r], topk_weights=ws[r], num_experts=num_experts, num_sms=num_sms,
                             cumulative_local_expert_recv_stats=stats[r]) for r in range(num_ranks)])
