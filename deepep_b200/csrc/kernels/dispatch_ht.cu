@@ -647,6 +647,14 @@ __global__ void __launch_bounds__(1024, 1) dispatch_epilogue_kernel(const __grid
                 reinterpret_cast<int4*>(p.recv_x)[v] = make_int4(0, 0, 0, 0);
             if (p.recv_topk_weights != nullptr)
                 for (int r = begin + threadIdx.x; r < end; r += blockDim.x) p.recv_topk_weights[r] = 0.f;
+            // the scales of the padding rows too: 0 x (whatever was in memory) would not be 0 for a NaN or an infinity
+            if (p.recv_sf != nullptr && p.sf_bytes > 0) {
+                const int packs = p.sf_bytes / 4;
+                for (int i = threadIdx.x; i < (end - begin) * packs; i += blockDim.x) {
+                    const int r = begin + i / packs, k = i % packs;
+                    reinterpret_cast<uint32_t*>(p.recv_sf)[static_cast<int64_t>(r) * p.recv_sf_row_stride + static_cast<int64_t>(k) * p.recv_sf_pack_stride] = 0u;
+                }
+            }
         }
     }
     bulk_wait_all();

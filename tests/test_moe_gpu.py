@@ -18,6 +18,9 @@ def test_moe_forward_backward_emulated(use_fp8):
     from deepep_b200.parallel.local_cluster import LocalCluster
     R, T, H, I, E, K = 2, 96, 256, 256, 8, 2
     EL = E // R
+    # poison the allocator's free blocks: padding rows and their scales must not leak stale memory into the result
+    junk = torch.full((64 << 20,), float('nan'), device='cuda')
+    del junk
     cfg = MoEConfig(hidden=H, intermediate=I, num_experts=E, num_topk=K, use_fp8=use_fp8, num_sms=4)
     cl = LocalCluster(R, num_max_tokens_per_rank=T, hidden=H, num_topk=K, num_gpu_timeout_secs=5)
     xs, idxs, ws = make_routed_inputs(R, T, H, E, K, seed=21, device='cuda', vary_tokens=True)
