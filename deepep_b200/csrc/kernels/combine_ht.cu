@@ -139,15 +139,98 @@ __device__ __forceinline__ int token_expert(const CombineEpilogueParams& p, int 
     return (raw >= 0 && raw < static_cast<int64_t>(p.num_local_experts) * p.num_ranks) ? static_cast<int>(raw) : -1;
 }
 
+__device__ __noinline__ void reduce_token_registers(const CombineEpilogueParams& p, int t, int e, int lane) {
+    reduce_token(p, t, e, lane);
+}
+
 // ==================================================================== reduce epilogue (local, all SMs)
-__global__ void __launch_bounds__(512) combine_epilogue_kernel(const __grid_constant__ Multi<CombineEpilogueParams> m) {
+// Rows are staged through shared memory with bulk copies: a warp keeps kEpiStages chunks of 512 bytes of every
+// contributing row in flight (three times the bytes a lane could hold in registers), then every lane sums its 16 bytes
+// of the chunk over the rows in ascending lane order. Tokens with at most one row, more than kEpiRows rows, or a row
+// size that is not a multiple of 512 bytes take the register path (reduce_token).
+constexpr int kEpiStages = 3, kEpiRows = 8, kEpiChunk = 512, kEpiWarps = 16;
+constexpr int kEpiWarpBytes = kEpiStages * kEpiRows * kEpiChunk;
+constexpr int kEpiSmem = kEpiWarps * kEpiWarpBytes + kEpiWarps * kEpiStages * 8;
+
+__global__ void __launch_bounds__(kEpiWarps * 32) combine_epilogue_kernel(const __grid_constant__ Multi<CombineEpilogueParams> m) {
+    extern __shared__ __align__(128) uint8_t epi_smem[];
     const int vr = blockIdx.x / m.blocks_per_rank;
     const int bid = blockIdx.x % m.blocks_per_rank;
     const int nb = m.blocks_per_rank;
     const CombineEpilogueParams& p = m.r[vr];
     const int lane = lane_id(), warp = warp_id();
     const int num_warps = blockDim.x >> 5;
-    for (int t = bid * num_warps + warp; t < p.num_tokens; t += nb * num_warps) reduce_token(p, t, token_expert(p, t, lane), lane);
+    uint8_t* sbuf = epi_smem + static_cast<size_t>(warp) * kEpiWarpBytes;
+    uint64_t* bars = reinterpret_cast<uint64_t*>(epi_smem + kEpiWarps * kEpiWarpBytes) + warp * kEpiStages;
+    if (lane == 0) {
+        for (int s = 0; s < kEpiStages; ++s) mbar_init(bars + s, 1);
+        fence_mbar_init();
+    }
+    __syncwarp();
+    uint32_t parity = 0;                    // bit s = phase the next wait on stage s expects
+    bool staged_ok = true;                  // a wait that ever ran out sends the rest through the register path
+    const int K = p.num_topk, EL = p.num_local_experts;
+    const uint64_t row_bytes = static_cast<uint64_t>(p.hidden) * 2;
+    const int nchunks = static_cast<int>(row_bytes / kEpiChunk);
+    const bool chunkable = row_bytes % kEpiChunk == 0;
+    const uint64_t deadline = globaltimer_ns() + 2000000000ull;
+
+    for (int t = bid * num_warps + warp; t < p.num_tokens; t += nb * num_warps) {
+        const int e = token_expert(p, t, lane);
+        const int slot_lane = e < 0 ? -1 : (p.use_rank_layout ? e / EL : lane);
+        uint32_t mask = slot_lane >= 0 ? (1u << slot_lane) : 0u;
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) mask |= __shfl_xor_sync(0xffffffffu, mask, o);
+        const int n = __popc(mask);
+        if (!chunkable || !staged_ok || n < 2 || n > kEpiRows) {
+            reduce_token_registers(p, t, e, lane);
+            continue;
+        }
+        if (p.combined_topk_weights != nullptr && lane < K) {
+            float wv = 0.f;
+            if (slot_lane >= 0 && p.region_w != nullptr)
+                wv = p.region_w[(static_cast<uint64_t>(slot_lane) * p.num_max_tokens + t) * K + lane];
+            p.combined_topk_weights[static_cast<int64_t>(t) * K + lane] = wv;
+        }
+        const uint8_t* b0 = p.bias0 != nullptr ? p.bias0 + t * row_bytes : nullptr;
+        const uint8_t* b1 = p.bias1 != nullptr ? p.bias1 + t * row_bytes : nullptr;
+        // lane r < n loads row r = the r-th contributing lane of the region (ascending)
+        const int my_slot = lane < n ? static_cast<int>(__fns(mask, 0, lane + 1)) : 0;
+        const uint8_t* my_src = p.region_x + (static_cast<uint64_t>(my_slot) * p.num_max_tokens + t) * row_bytes;
+        uint8_t* dst = p.combined_x + t * row_bytes;
+        for (int c = 0; c < nchunks + kEpiStages - 1 && staged_ok; ++c) {
+            if (c < nchunks) {
+                const int s = c % kEpiStages;
+                fence_proxy_async_smem();       // this stage was read (generic proxy) one iteration ago
+                __syncwarp();
+                if (lane == 0) mbar_arrive_expect_tx(bars + s, static_cast<uint32_t>(n) * kEpiChunk);
+                __syncwarp();
+                if (lane < n) bulk_g2s(sbuf + (s * kEpiRows + lane) * kEpiChunk, my_src + static_cast<uint64_t>(c) * kEpiChunk, kEpiChunk, bars + s);
+            }
+            if (c >= kEpiStages - 1) {
+                const int cc = c - (kEpiStages - 1), s = cc % kEpiStages;
+                uint32_t spins = 0;
+                bool ok = true;
+                while (!mbar_try_wait(bars + s, (parity >> s) & 1u)) {
+                    if ((++spins & 1023u) == 0 && globaltimer_ns() > deadline) { ok = false; break; }
+                }
+                staged_ok = __all_sync(0xffffffffu, ok);
+                if (!staged_ok) break;
+                parity ^= 1u << s;
+                float acc[8];
+#pragma unroll
+                for (int i = 0; i < 8; ++i) acc[i] = 0.f;
+#pragma unroll
+                for (int r = 0; r < kEpiRows; ++r)
+                    if (r < n) accumulate_bf16x8(acc, *reinterpret_cast<const int4*>(sbuf + (s * kEpiRows + r) * kEpiChunk + lane * 16));
+                const int off = cc * kEpiChunk + lane * 16;
+                if (b0 != nullptr) accumulate_bf16x8(acc, ld_nc_int4(b0 + off));
+                if (b1 != nullptr) accumulate_bf16x8(acc, ld_nc_int4(b1 + off));
+                st_na_int4(dst + off, pack_bf16x8(acc));
+            }
+        }
+        if (!staged_ok) reduce_token_registers(p, t, e, lane);     // redo this token the slow way; later tokens skip the staging
+    }
 }
 
 // kFused: with the reduce of the receive side (more registers per thread; compiled apart so that the plain send
@@ -454,7 +537,9 @@ cudaError_t launch_combine_epilogue(const CombineEpilogueParams* params, int num
     m.num_vranks = num_vranks;
     m.blocks_per_rank = num_sms;
     for (int v = 0; v < num_vranks; ++v) m.r[v] = params[v];
-    combine_epilogue_kernel<<<num_vranks * num_sms, 512, 0, stream>>>(m);
+    cudaError_t err = cudaFuncSetAttribute(combine_epilogue_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kEpiSmem);
+    if (err != cudaSuccess) return err;
+    combine_epilogue_kernel<<<num_vranks * num_sms, kEpiWarps * 32, kEpiSmem, stream>>>(m);
     return cudaGetLastError();
 }
 
