@@ -560,6 +560,7 @@ __global__ void __launch_bounds__(1024, 1) dispatch_epilogue_kernel(const __grid
     uint32_t parity = 0;
     const int expert_begin = p.rank * EL;
     const int sf_packs = p.sf_bytes / 4;
+    const int my_psum = lane < R ? p.psum_rank[lane] : 0x7fffffff;
 
     for (int i = bid * num_warps + warp; i < N; i += nb * num_warps) {
         if (move_rows) {
@@ -584,8 +585,8 @@ __global__ void __launch_bounds__(1024, 1) dispatch_epilogue_kernel(const __grid
         const int local_e = local ? e - expert_begin : -1;
         if (!p.do_expand || !local) row = -1;
         const uint32_t local_mask = __ballot_sync(0xffffffffu, local);
-        int src_rank = 0;
-        while (src_rank < R - 1 && i >= p.psum_rank[src_rank]) ++src_rank;
+        // source rank of row i: how many of the inclusive prefix sums it has passed (lane r holds psum_rank[r])
+        const int src_rank = __popc(__ballot_sync(0xffffffffu, lane < R - 1 && i >= my_psum));
 
         if (!p.do_expand) {
             if (lane < K) {
