@@ -562,7 +562,25 @@ __global__ void __launch_bounds__(1024, 1) dispatch_epilogue_kernel(const __grid
     const int sf_packs = p.sf_bytes / 4;
     const int my_psum = lane < R ? p.psum_rank[lane] : 0x7fffffff;
 
-    for (int i = bid * num_warps + warp; i < N; i += nb * num_warps) {
+    // the routing words of a row are loaded one iteration ahead, so their latency overlaps the stores of the row before
+    auto load_meta = [&](int i, int& e, float& wt, int& row, int& src_token) {
+        const int* meta_idx = reinterpret_cast<const int*>(p.region_meta + static_cast<uint64_t>(i) * p.meta_bytes + p.sf_bytes);
+        e = -1;
+        row = -1;
+        wt = 0.f;
+        if (lane < K) {
+            e = meta_idx[lane];
+            wt = reinterpret_cast<const float*>(meta_idx)[K + lane];
+            row = meta_idx[2 * K + lane];
+        }
+        src_token = meta_idx[3 * K];
+    };
+    const int first_row = bid * num_warps + warp, row_step = nb * num_warps;
+    int next_e = -1, next_row = -1, next_src_token = 0;
+    float next_wt = 0.f;
+    if (first_row < N) load_meta(first_row, next_e, next_wt, next_row, next_src_token);
+
+    for (int i = first_row; i < N; i += row_step) {
         if (move_rows) {
             bulk_wait_read_all();
             __syncwarp();
@@ -572,15 +590,10 @@ __global__ void __launch_bounds__(1024, 1) dispatch_epilogue_kernel(const __grid
             }
         }
         const uint8_t* meta = p.region_meta + static_cast<uint64_t>(i) * p.meta_bytes;
-        const int* meta_idx = reinterpret_cast<const int*>(meta + p.sf_bytes);
-        int e = -1, row = -1;
-        float wt = 0.f;
-        if (lane < K) {
-            e = meta_idx[lane];
-            wt = reinterpret_cast<const float*>(meta_idx)[K + lane];
-            row = meta_idx[2 * K + lane];
-        }
-        const int src_token = meta_idx[3 * K];
+        const int e = next_e, src_token = next_src_token;
+        int row = next_row;
+        const float wt = next_wt;
+        if (i + row_step < N) load_meta(i + row_step, next_e, next_wt, next_row, next_src_token);
         const bool local = e >= expert_begin && e < expert_begin + EL;
         const int local_e = local ? e - expert_begin : -1;
         if (!p.do_expand || !local) row = -1;
