@@ -144,11 +144,13 @@ __device__ __noinline__ void reduce_token_registers(const CombineEpilogueParams&
 }
 
 // ==================================================================== reduce epilogue (local, all SMs)
-// Rows are staged through shared memory with bulk copies: a warp keeps kEpiStages chunks of 512 bytes of every
-// contributing row in flight (three times the bytes a lane could hold in registers), then every lane sums its 16 bytes
-// of the chunk over the rows in ascending lane order. Tokens with at most one row, more than kEpiRows rows, or a row
-// size that is not a multiple of 512 bytes take the register path (reduce_token).
-constexpr int kEpiStages = 3, kEpiRows = 8, kEpiChunk = 512, kEpiWarps = 16;
+// Rows are staged through shared memory with bulk copies: a warp keeps kEpiStages chunks of 1 KB of every contributing
+// row in flight (several times the bytes a lane could hold in registers), then every lane sums its two 16-byte pieces
+// of the chunk over the rows in ascending lane order. The chunk size matters: every chunk costs a proxy fence, two
+// warp barriers and an mbarrier round, and with 512-byte chunks that fixed cost, not memory, set the pace (147 us
+// against 130 us for the EP8-shaped case). Tokens with at most one row, more than kEpiRows rows, or a row size that is
+// not a multiple of the chunk take the register path (reduce_token).
+constexpr int kEpiStages = 2, kEpiRows = 8, kEpiChunk = 1024, kEpiWarps = 12;
 constexpr int kEpiWarpBytes = kEpiStages * kEpiRows * kEpiChunk;
 constexpr int kEpiSmem = kEpiWarps * kEpiWarpBytes + kEpiWarps * kEpiStages * 8;
 
@@ -217,16 +219,19 @@ __global__ void __launch_bounds__(kEpiWarps * 32) combine_epilogue_kernel(const 
                 staged_ok = __all_sync(0xffffffffu, ok);
                 if (!staged_ok) break;
                 parity ^= 1u << s;
-                float acc[8];
 #pragma unroll
-                for (int i = 0; i < 8; ++i) acc[i] = 0.f;
+                for (int h = 0; h < kEpiChunk / 512; ++h) {
+                    float acc[8];
 #pragma unroll
-                for (int r = 0; r < kEpiRows; ++r)
-                    if (r < n) accumulate_bf16x8(acc, *reinterpret_cast<const int4*>(sbuf + (s * kEpiRows + r) * kEpiChunk + lane * 16));
-                const int off = cc * kEpiChunk + lane * 16;
-                if (b0 != nullptr) accumulate_bf16x8(acc, ld_nc_int4(b0 + off));
-                if (b1 != nullptr) accumulate_bf16x8(acc, ld_nc_int4(b1 + off));
-                st_na_int4(dst + off, pack_bf16x8(acc));
+                    for (int i = 0; i < 8; ++i) acc[i] = 0.f;
+#pragma unroll
+                    for (int r = 0; r < kEpiRows; ++r)
+                        if (r < n) accumulate_bf16x8(acc, *reinterpret_cast<const int4*>(sbuf + (s * kEpiRows + r) * kEpiChunk + h * 512 + lane * 16));
+                    const int off = cc * kEpiChunk + h * 512 + lane * 16;
+                    if (b0 != nullptr) accumulate_bf16x8(acc, ld_nc_int4(b0 + off));
+                    if (b1 != nullptr) accumulate_bf16x8(acc, ld_nc_int4(b1 + off));
+                    st_na_int4(dst + off, pack_bf16x8(acc));
+                }
             }
         }
         if (!staged_ok) reduce_token_registers(p, t, e, lane);     // redo this token the slow way; later tokens skip the staging
