@@ -39,8 +39,9 @@ def parse_args():
     p.add_argument('--hidden', type=int, default=7168)
     p.add_argument('--num-experts', type=int, default=256)
     p.add_argument('--num-topk', type=int, default=8)
-    p.add_argument('--num-sms', type=int, default=0, help='SMs of the communication kernels; 0 = 24 with peers, all SMs at EP1 '
-                   '(no NVLink traffic to leave SMs free for: the SM model of the library picks the whole GPU there too)')
+    p.add_argument('--num-sms', type=int, default=0, help="SMs of the communication kernels; 0 = the library's SM model "
+                   '(ElasticBuffer.get_theoretical_num_sms: 24 at EP8, the whole GPU at EP1 where no NVLink traffic exists)')
+    p.add_argument('--repeats', type=int, default=5, help='the timed loop of --steps steps is run this many times; the median is reported')
     p.add_argument('--no-extra', action='store_true', help='skip the kernel-only / 64-SM / NCCL detail sections')
     return p.parse_args()
 
@@ -144,8 +145,75 @@ def reference_arm(args):
                       'needs the NCCL Gin device API (NCCL >= 2.30.4; image has 2.28.9) and NVSHMEM headers need infiniband/mlx5dv.h'}))
 
 
+def moe_unfused_baseline_ms(group, world, dev, x, idx, w, w13, w2, dy, num_experts, max_over_ranks, iters=3):
+    """Baseline, not the product: the same layer with library pieces only -- NCCL all-to-all of bf16 rows (one per token
+    and expert, splits exchanged once outside the timed region), one torch.matmul pair per local expert, eager SwiGLU,
+    all-to-all back, weighted index_add; backward through autograd. bf16 throughout."""
+    import torch
+    import torch.distributed as dist
+    from torch.distributed.nn.functional import all_to_all_single as a2a
+    T, H = x.shape
+    K = idx.size(1)
+    el = num_experts // world
+    inter = w13.size(1) // 2
+    flat = idx.flatten()
+    key = torch.where(flat >= 0, flat, torch.full_like(flat, num_experts))
+    order = torch.argsort(key, stable=True)[:int((flat >= 0).sum().item())]
+    tok = order // K
+    per_expert = torch.bincount(flat[order], minlength=num_experts)
+    recv_per_expert = torch.empty_like(per_expert)
+    if world > 1:
+        dist.all_to_all_single(recv_per_expert, per_expert, group=group)
+    else:
+        recv_per_expert.copy_(per_expert)
+    sc = per_expert.view(world, el).sum(dim=1).tolist()
+    rcm = recv_per_expert.view(world, el)                          # rows from source s for local expert e
+    rc = rcm.sum(dim=1).tolist()
+    n_recv = sum(rc)
+    # received rows come grouped by (source, expert): permutation to expert-major and the per-expert bounds
+    src_of = torch.repeat_interleave(torch.arange(world, device=dev), torch.tensor(rc, device=dev))
+    exp_of = torch.repeat_interleave(torch.arange(el, device=dev).repeat(world), rcm.flatten())
+    perm = torch.argsort(exp_of * world + src_of, stable=True)
+    inv = torch.empty_like(perm)
+    inv[perm] = torch.arange(n_recv, device=dev)
+    bounds = [0] + torch.cumsum(rcm.sum(dim=0), 0).tolist()
+    wsel = w.flatten()[order].unsqueeze(1).bfloat16()
+    xg = x.detach().clone().requires_grad_(True)
+    w13g, w2g = w13.detach().clone().requires_grad_(True), w2.detach().clone().requires_grad_(True)
+
+    def step():
+        rows = xg[tok]
+        recv = a2a(torch.empty((n_recv, H), dtype=rows.dtype, device=dev), rows, rc, sc, group=group) if world > 1 else rows
+        h = recv[perm]
+        outs = []
+        for e in range(el):
+            seg = h[bounds[e]:bounds[e + 1]]
+            h1 = seg @ w13g[e].t()
+            a = torch.nn.functional.silu(h1[:, :inter]) * h1[:, inter:]
+            outs.append(a @ w2g[e].t())
+        h2 = torch.cat(outs, dim=0)[inv]
+        back = a2a(torch.empty((len(tok), H), dtype=h2.dtype, device=dev), h2, sc, rc, group=group) if world > 1 else h2
+        y = torch.zeros((T, H), dtype=torch.bfloat16, device=dev).index_add(0, tok, back * wsel)
+        y.backward(dy)
+        xg.grad = None
+        w13g.grad = None
+        w2g.grad = None
+
+    step()
+    torch.cuda.synchronize()
+    if world > 1:
+        dist.barrier()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(iters):
+        step()
+    e1.record()
+    torch.cuda.synchronize()
+    return max_over_ranks(e0.elapsed_time(e1) / iters)
+
+
 def moe_layer_section(buf, world, rank, dev, hidden, num_experts, num_topk, max_over_ranks, num_tokens=4096, intermediate=2048,
-                      iters=5):
+                      iters=5, group=None):
     """Forward + backward of the fused MoE layer (FP8 dispatch and expert GEMMs, bf16 gradients), Zipf-skewed routing."""
     import torch
     import torch.distributed as dist
@@ -193,9 +261,51 @@ def moe_layer_section(buf, world, rank, dev, hidden, num_experts, num_topk, max_
            'num_topk': num_topk, 'routing': 'zipf 1.2', 'fwd_bwd_ms': round(ms, 3),
            'expert_rows_busiest_rank': busiest, 'expert_rows_mean': num_tokens * num_topk,
            'expert_tflops_busiest_gpu': round(flops / (ms * 1e-3) / 1e12, 1)}
+    # correctness of the timed configuration: the forward output against a dense fp32 evaluation of this rank's tokens
+    # over all experts (weights gathered from their owners), on a slice of the tokens
+    verified = None
+    try:
+        ys, _ = moe_forward(comm, [weights], [x], [idx], [w], cfg)
+        if world > 1:
+            all13 = [torch.empty_like(w13) for _ in range(world)]
+            all2 = [torch.empty_like(w2) for _ in range(world)]
+            dist.all_gather(all13, w13)
+            dist.all_gather(all2, w2)
+            w13_all, w2_all = torch.cat(all13), torch.cat(all2)
+        else:
+            w13_all, w2_all = w13, w2
+        from deepep_b200.models.moe import reference_moe
+        n = 16
+        ref = reference_moe([x[:n]], [idx[:n]], [w[:n]], w13_all, w2_all)[0]
+        err = ((ys[0][:n].float() - ref).norm() / ref.norm().clamp(min=1e-6)).item()
+        verified = max_over_ranks(0.0 if err < 0.08 else 1.0) == 0.0
+        res['rel_err_forward_vs_fp32'] = round(max_over_ranks(err), 4)
+        del w13_all, w2_all
+    except Exception as exc:   # noqa: BLE001
+        res['verify_error'] = f'{type(exc).__name__}: {exc}'[:200]
+        verified = False
+    res['verified'] = verified
+    try:
+        base = moe_unfused_baseline_ms(group, world, dev, x, idx, w, w13, w2, dy, num_experts, max_over_ranks)
+        res['baseline_ms'] = round(base, 3)
+        res['baseline'] = 'NCCL all-to-all + torch.matmul per expert + autograd, bf16 (baseline, not the product)'
+        res['speedup_vs_baseline'] = round(base / ms, 3)
+    except Exception as exc:   # noqa: BLE001
+        res['baseline_error'] = f'{type(exc).__name__}: {exc}'[:200]
     if world > 1:
         dist.barrier()
-    return res
+    return res, bool(verified)
+
+
+def measured_peaks():
+    """The driver's measurements on this pool (MEASURED_PEAKS.json beside this file), else the stated fallback."""
+    path = os.path.join(os.path.dirname(os.path.abspath(__file__)), 'MEASURED_PEAKS.json')
+    try:
+        with open(path) as f:
+            d = json.load(f)
+        return {'hbm_gbs': float(d['hbm_gbs']), 'bf16_tflops': float(d['bf16_tflops']), 'source': 'measured'}
+    except Exception:   # noqa: BLE001
+        return {'hbm_gbs': 6650.0, 'bf16_tflops': 1590.0, 'source': 'fallback'}
 
 
 def tp_section(group, world, rank, dev, max_over_ranks, tokens=8192, hidden=7168, ffn=18432, iters=5):
@@ -204,6 +314,7 @@ def tp_section(group, world, rank, dev, max_over_ranks, tokens=8192, hidden=7168
     import torch.distributed as dist
     from deepep_b200.parallel.tp_fused import TensorParallelContext, nccl_all_gather_gemm, nccl_gemm_reduce_scatter
     ml, fl = tokens // world, ffn // world
+    peak_tflops = measured_peaks()['bf16_tflops']
     ctx = TensorParallelContext(group, ml, hidden, hidden, num_gpu_timeout_secs=20)
     g = torch.Generator(device=dev).manual_seed(rank)
     x_shard = torch.randn((ml, hidden), device=dev, generator=g).bfloat16()
@@ -224,21 +335,90 @@ def tp_section(group, world, rank, dev, max_over_ranks, tokens=8192, hidden=7168
         torch.cuda.synchronize()
         return max_over_ranks(e0.elapsed_time(e1) / iters) * 1e3
 
-    res = {'tokens': tokens, 'hidden': hidden, 'ffn': ffn,
+    # both fused operators against NCCL + matmul on the very tensors that are timed
+    a, b = ctx.all_gather_gemm(x_shard, w1), nccl_all_gather_gemm(x_shard, w1, group)
+    c, d = ctx.gemm_reduce_scatter(x2, w2), nccl_gemm_reduce_scatter(x2, w2, group)
+    torch.cuda.synchronize()
+    err_ag = ((a.float() - b.float()).norm() / b.float().norm()).item()
+    err_rs = ((c.float() - d.float()).norm() / d.float().norm()).item()
+    verified = max_over_ranks(0.0 if (err_ag < 1e-2 and err_rs < 2e-2) else 1.0) == 0.0
+    del a, b, c, d
+    # roofline: the slower of the FLOPs at the measured cuBLAS bf16 rate and the bytes that must cross NVLink at the
+    # measured peer-copy rate (770 GB/s per direction per GPU)
+    flops_ag, flops_rs = 2.0 * tokens * fl * hidden, 2.0 * tokens * hidden * fl
+    wire_ag = (world - 1) * ml * hidden * 2          # every rank receives the other shards
+    wire_rs = (world - 1) * ml * hidden * 2          # every rank sends one bf16 partial tile set per peer
+    roof_ag = max(flops_ag / (peak_tflops * 1e12), wire_ag / 770e9) * 1e6
+    roof_rs = max(flops_rs / (peak_tflops * 1e12), wire_rs / 770e9) * 1e6
+    res = {'tokens': tokens, 'hidden': hidden, 'ffn': ffn, 'verified': verified,
+           'rel_err': {'ag_gemm': round(max_over_ranks(err_ag), 5), 'gemm_rs': round(max_over_ranks(err_rs), 5)},
            'ag_gemm_fused_us': round(timeit(lambda: ctx.all_gather_gemm(x_shard, w1)), 1),
            'ag_gemm_nccl_cublas_us': round(timeit(lambda: nccl_all_gather_gemm(x_shard, w1, group)), 1),
            'gemm_rs_fused_us': round(timeit(lambda: ctx.gemm_reduce_scatter(x2, w2)), 1),
            'gemm_rs_cublas_nccl_us': round(timeit(lambda: nccl_gemm_reduce_scatter(x2, w2, group)), 1)}
+    res['ag_gemm_fused_over_baseline'] = round(res['ag_gemm_fused_us'] / res['ag_gemm_nccl_cublas_us'], 3)
+    res['gemm_rs_fused_over_baseline'] = round(res['gemm_rs_fused_us'] / res['gemm_rs_cublas_nccl_us'], 3)
+    res['roofline_us'] = {'ag_gemm': round(roof_ag, 1), 'gemm_rs': round(roof_rs, 1), 'gemm_peak_tflops_measured': peak_tflops}
+    res['achieved_over_roofline'] = {'ag_gemm': round(roof_ag / res['ag_gemm_fused_us'], 3), 'gemm_rs': round(roof_rs / res['gemm_rs_fused_us'], 3)}
     ctx.check_status()
     dist.barrier()
     torch.cuda.synchronize()
     ctx.destroy()
-    return res
+    return res, verified
+
+
+def nccl_decode_step_baseline(group, world, dev, x, idx, w, num_experts, iters=100):
+    """Baseline, not the product: the same decode step (tokens to their experts' ranks and back, weighted sum) on
+    ``dist.all_to_all_single``. Splits are exchanged once outside the timed region (the library step has to find them
+    every time); the timed part is gather + all-to-all of the e4m3 rows + all-to-all of the bf16 rows back + weighted sum."""
+    import torch
+    import torch.distributed as dist
+    from deepep_b200.utils.math import per_token_cast_to_fp8
+    T, H = x.shape
+    K = idx.size(1)
+    el = num_experts // world
+    dst = torch.where(idx >= 0, idx // el, torch.full_like(idx, world))           # [T, K] owner rank of every pair
+    order = torch.argsort(dst.flatten(), stable=True)
+    send_counts = torch.bincount(dst.flatten(), minlength=world + 1)[:world]
+    n_send = int(send_counts.sum().item())
+    order = order[:n_send]
+    tok = order // K
+    recv_counts = torch.empty_like(send_counts)
+    dist.all_to_all_single(recv_counts, send_counts, group=group)
+    sc, rc = send_counts.tolist(), recv_counts.tolist()
+    n_recv = sum(rc)
+    xq = per_token_cast_to_fp8(x)[0].view(torch.uint8)
+    recv = torch.empty((n_recv, H), dtype=torch.uint8, device=dev)
+    back = torch.empty((n_send, H), dtype=torch.bfloat16, device=dev)
+    y = torch.randn((n_recv, H), device=dev, dtype=torch.bfloat16)
+    wflat = w.flatten()[order].unsqueeze(1)
+    out = torch.zeros((T, H), dtype=torch.float32, device=dev)
+
+    def step():
+        dist.all_to_all_single(recv, xq[tok], rc, sc, group=group)
+        dist.all_to_all_single(back, y, sc, rc, group=group)
+        out.zero_()
+        out.index_add_(0, tok, back.float() * wflat)
+
+    for _ in range(5):
+        step()
+    torch.cuda.synchronize()
+    dist.barrier()
+    starts = [torch.cuda.Event(enable_timing=True) for _ in range(iters)]
+    ends = [torch.cuda.Event(enable_timing=True) for _ in range(iters)]
+    for i in range(iters):
+        starts[i].record()
+        step()
+        ends[i].record()
+    torch.cuda.synchronize()
+    return sorted(s.elapsed_time(e) * 1e3 for s, e in zip(starts, ends))
 
 
 def low_latency_section(deepep_b200, group, world, rank, dev, hidden, num_experts, num_topk, max_over_ranks, num_tokens=128,
                         iters=200):
-    """p50 / p99 of one decode step (dispatch + combine, 128 tokens per rank) replayed from a CUDA graph."""
+    """p50 / p99 of one decode step (dispatch + combine, 128 tokens per rank) replayed from a CUDA graph. The
+    replayed step is checked: experts act as the identity (their input rows, dequantised once, are the rows the
+    combine sends back), so every replay must return x * sum_k w_k within FP8 precision, bit-identical every time."""
     import torch
     import torch.distributed as dist
     from deepep_b200.utils import gate
@@ -250,7 +430,12 @@ def low_latency_section(deepep_b200, group, world, rank, dev, hidden, num_expert
     idx, w = idx.to(dev), w.to(dev)
     out = torch.empty_like(x)
     el = num_experts // world
-    y = torch.randn((el, world * num_tokens, hidden), device=dev, dtype=torch.bfloat16)
+    # identity experts: y = the received rows, dequantised (positions are deterministic, so one eager dispatch fixes them)
+    (rx0, rsf0), cnt0, _, _, _ = ll.low_latency_dispatch(x, idx, num_tokens, num_experts, use_fp8=True)
+    torch.cuda.synchronize()
+    y = (rx0.float().view(el, world * num_tokens, hidden // 128, 128) * rsf0.float().unsqueeze(-1)).view(el, world * num_tokens, hidden).bfloat16()
+    del rx0, rsf0
+    want = x.float() * torch.where(idx >= 0, w, torch.zeros_like(w)).sum(dim=1, keepdim=True)
 
     def step():
         (rx, rsf), cnt, handle, _, _ = ll.low_latency_dispatch(x, idx, num_tokens, num_experts, use_fp8=True)
@@ -271,6 +456,9 @@ def low_latency_section(deepep_b200, group, world, rank, dev, hidden, num_expert
     for _ in range(10):
         graph.replay()
     torch.cuda.synchronize()
+    first = out.clone()
+    err = ((first.float() - want).norm() / want.norm()).item()
+    ok = err < 0.05
     if world > 1:
         dist.barrier()
     starts = [torch.cuda.Event(enable_timing=True) for _ in range(iters)]
@@ -281,15 +469,25 @@ def low_latency_section(deepep_b200, group, world, rank, dev, hidden, num_expert
         ends[i].record()
     torch.cuda.synchronize()
     ll.check_status()
+    ok = ok and bool(torch.equal(out, first))           # the last replay returns the same bits as the first
+    verified = max_over_ranks(0.0 if ok else 1.0) == 0.0
     us = sorted(s.elapsed_time(e) * 1e3 for s, e in zip(starts, ends))
     res = {'tokens_per_rank': num_tokens, 'iters': iters, 'step': 'fp8 dispatch + bf16 weighted combine (two kernels), replayed from a CUDA graph',
            'p50_us': round(max_over_ranks(us[len(us) // 2]), 1), 'p99_us': round(max_over_ranks(us[int(len(us) * 0.99) - 1]), 1),
-           'min_us': round(max_over_ranks(us[0]), 1)}
+           'min_us': round(max_over_ranks(us[0]), 1), 'verified': verified, 'rel_err_vs_x_times_sum_w': round(max_over_ranks(err), 4)}
     if world > 1:
+        dist.barrier()
+        try:
+            base = nccl_decode_step_baseline(group, world, dev, x, idx, w, num_experts)
+            res['baseline_nccl_all_to_all_p50_us'] = round(max_over_ranks(base[len(base) // 2]), 1)
+            res['baseline_nccl_all_to_all_p99_us'] = round(max_over_ranks(base[int(len(base) * 0.99) - 1]), 1)
+            res['baseline_note'] = 'dist.all_to_all_single both ways, splits known in advance, eager launches; baseline, not the product'
+        except Exception as exc:   # noqa: BLE001
+            res['baseline_error'] = f'{type(exc).__name__}: {exc}'[:200]
         dist.barrier()
     torch.cuda.synchronize()
     ll.destroy()
-    return res
+    return res, verified
 
 
 def main():
@@ -324,11 +522,10 @@ def main():
 
     T, H, E, K = args.num_tokens, args.hidden, args.num_experts, args.num_topk
     assert E % world == 0
-    if args.num_sms <= 0:
-        args.num_sms = 24 if world > 1 else torch.cuda.get_device_properties(dev).multi_processor_count
     buf = deepep_b200.ElasticBuffer(group, num_max_tokens_per_rank=T, hidden=H, num_topk=K, use_fp8_dispatch=True,
                                     num_gpu_timeout_secs=20, explicitly_destroy=True)
-    buf.runtime.enable_profiling(True)
+    if args.num_sms <= 0:
+        args.num_sms = buf.get_theoretical_num_sms(E, K)      # 24 at EP8 / 256 experts / top-8; all SMs with one rank
 
     # synthetic seeded tokens and router outputs; the pool is larger than L2 (4 x 117 MB)
     gen = torch.Generator(device='cpu').manual_seed(1234 + rank)
@@ -359,6 +556,48 @@ def main():
         t = torch.tensor([v], dtype=torch.float64, device=dev)
         dist.all_reduce(t, op=dist.ReduceOp.SUM)
         return float(t.item())
+
+    # ------------------------------------------------------------------ correctness of what is about to be timed
+    # The same calls (fused FP8 cast, zero copy, no CPU sync, same SM count) on a slice of the tokens, compared bit
+    # for bit with the collective oracle (utils/refs.py: all ranks' inputs gathered, expected rows built in PyTorch).
+    from deepep_b200.utils import refs
+    from deepep_b200.utils.math import per_token_cast_to_fp8
+
+    def verify_ht() -> bool:
+        tv = min(T, 384) - rank % 3                      # different counts per rank
+        xv, iv, wv = xs[0][:tv], idxs[0][:tv].clone(), ws[0][:tv]
+        iv[::11, 0] = -1                                 # some unused lanes
+        (rx, rsf), ridx, rw, h, _ = buf.dispatch(xv, topk_idx=iv, topk_weights=wv, num_experts=E, num_sms=args.num_sms,
+                                                 zero_copy=True, do_cpu_sync=False)
+        torch.cuda.synchronize()
+        n = int(h.psum_num_recv_tokens_per_scaleup_rank[-1].item())
+        q = per_token_cast_to_fp8(xv)
+        if world > 1:
+            (ex, esf), eidx, ew, esrc, _ = refs.dispatch(q, iv, wv, T, E)
+        else:
+            e = refs.dispatch_local([q[0].view(torch.uint8).cpu()], [iv.cpu()], [wv.cpu()], 0, E, T, sfs=[q[1].cpu()])
+            ex, esf = e['recv_x'].to(dev).view(torch.float8_e4m3fn), e['recv_sf'].to(dev)
+            eidx, ew, esrc = e['recv_topk_idx'].to(dev), e['recv_topk_weights'].to(dev), e['recv_src_token_idx'].to(dev)
+        ok = n == ex.size(0)
+        ok = ok and torch.equal(rx[:n].view(torch.uint8), ex.view(torch.uint8)) and torch.equal(rsf[:n], esf)
+        ok = ok and torch.equal(ridx[:n], eidx) and torch.equal(rw[:n], ew) and torch.equal(h.recv_src_metadata[:n, 0], esrc)
+        yv = torch.zeros((rx.size(0), H), device=dev, dtype=torch.bfloat16)
+        yv[:n] = (rx[:n].float().view(n, H // 128, 128) * rsf[:n].float().unsqueeze(-1)).view(n, H).bfloat16() * (1 + 0.25 * rank)
+        out, _, _ = buf.combine(yv, h, topk_weights=rw)
+        torch.cuda.synchronize()
+        if world > 1:
+            ref = refs.combine(yv[:n], h.recv_src_metadata[:n, 0], tv, T)
+        else:
+            ref = refs.combine_local([yv[:n].cpu()], [h.recv_src_metadata[:n, 0].cpu()], 0, tv, T).to(dev)
+        ok = ok and torch.equal(out, ref)
+        buf.check_status()
+        return max_over_ranks(0.0 if ok else 1.0) == 0.0
+
+    verified = {'ht': verify_ht()}
+    if not verified['ht']:
+        if rank == 0:
+            print(json.dumps({'error': 'dispatch / combine output differs from the oracle', 'verified': verified}), flush=True)
+        sys.exit(3)
 
     y_cache = {}
 
@@ -393,6 +632,8 @@ def main():
         return max_over_ranks(e0.elapsed_time(e1) / steps)
 
     # ------------------------------------------------------------------ headline: device-timed full steps
+    # The loop of `steps` steps is timed `repeats` times (each between a barrier + synchronize on both sides, max over
+    # ranks); the median repeat is the reported figure, so one descheduled host thread does not decide it.
     sampler = ClockSampler(local_rank) if rank == 0 else None
     if sampler:
         sampler.start()
@@ -400,18 +641,21 @@ def main():
         step(i, args.num_sms)
     sync_all()
     t_wall0 = time.time()
-    launches0 = buf.runtime.num_kernel_launches()
-    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    e0.record()
-    last = None
-    for i in range(args.steps):
-        last = step(args.warmup + i, args.num_sms)
-    e1.record()
-    gpu_launches = buf.runtime.num_kernel_launches() - launches0      # counted by the runtime at every kernel launch
-    sync_all()
+    repeat_ms, last, gpu_launches = [], None, 0
+    for rep_i in range(max(1, args.repeats)):
+        sync_all()
+        launches0 = buf.runtime.num_kernel_launches()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for i in range(args.steps):
+            last = step(args.warmup + i, args.num_sms)
+        e1.record()
+        gpu_launches = buf.runtime.num_kernel_launches() - launches0      # counted by the runtime at every kernel launch
+        sync_all()
+        repeat_ms.append(max_over_ranks(e0.elapsed_time(e1) / args.steps))
     t_wall1 = time.time()
     clocks = sampler.stop(t_wall0, t_wall1) if sampler else None
-    ms_per_step = max_over_ranks(e0.elapsed_time(e1) / args.steps)
+    ms_per_step = statistics.median(repeat_ms)
     buf.check_status()
 
     recv_x, combined, handle = last
@@ -430,36 +674,50 @@ def main():
     detail = {'num_recv_tokens_rank0': n_recv, 'baseline_gbs_per_gpu_folded': round(baseline_per_gpu, 1)}
 
     def kernel_only(num_sms: int, iters: int = 11):
-        # median over the iterations: on a shared host a descheduled launch thread now and then leaves the GPU idle
-        # between two kernels of an iteration, which a mean would book as kernel time
-        samples = [[], [], [], []]
-        for i in range(3):
-            step(i, num_sms)
+        """Two passes. (1) events also between kernel and epilogue (the launches are then serialised): kernel-only
+        figures, what the reference publishes. (2) events around each pair only, overlap as in production: what the
+        dispatch / the combine cost with their epilogues. Medians over the iterations (on a shared host a descheduled
+        launch thread now and then leaves the GPU idle between two kernels, which a mean would book as kernel time)."""
         dummy = torch.ones(1, device=dev)
-        for i in range(iters):
-            torch.cuda.synchronize()
-            if world > 1:
-                # same pre-synchronisation as the reference's kernel timing: a long GPU sleep lets the host
-                # run ahead, the all-reduce then releases all ranks together, so launch skew is not timed
-                torch.cuda._sleep(int(4e6))
-                dist.all_reduce(dummy)
-            _, _, h = step(i, num_sms)
-            t = buf.runtime.last_timings()
-            for q in range(4):
-                samples[q].append(t[q])
-        acc = [max_over_ranks(sorted(v)[len(v) // 2]) for v in samples]
-        # block 0's timestamps inside the last dispatch kernel of this rank: totals counted and through the grid barrier,
-        # first rows known (exchange done), all rows issued, own stores complete, peers' rows complete
+
+        def run(mode):
+            buf.runtime.enable_profiling(mode)
+            samples = [[] for _ in range(6)]
+            for i in range(3):
+                step(i, num_sms)
+            h = None
+            for i in range(iters):
+                torch.cuda.synchronize()
+                if world > 1:
+                    # same pre-synchronisation as the reference's kernel timing: a long GPU sleep lets the host
+                    # run ahead, the all-reduce then releases all ranks together, so launch skew is not timed
+                    torch.cuda._sleep(int(4e6))
+                    dist.all_reduce(dummy)
+                _, _, h = step(i, num_sms)
+                t = buf.runtime.last_timings()
+                for q in range(6):
+                    samples[q].append(t[q])
+            return [max_over_ranks(sorted(v)[len(v) // 2]) for v in samples], h
+
+        split, h = run(2)
+        # block 0's timestamps inside the last dispatch kernel of this rank (us after its start): totals counted and
+        # through the grid barrier, order pass done, peers' totals in, first rows published, block 0 out of tokens,
+        # its stores complete, last block done (completion words sent)
         phases = [round(v / 1e3, 1) for v in buf.runtime.last_dispatch_phases()]
+        pair, h = run(1)
+        # %globaltimer spans of the four kernels of the last step (us, relative to the start of the dispatch kernel)
+        timeline = [round(v / 1e3, 1) for v in buf.runtime.last_timeline()]
+        buf.runtime.enable_profiling(0)
         n = true_recv_tokens(h)
         return {'num_sms': num_sms,
-                'dispatch_kernel_us': round(acc[0] * 1e3, 1), 'dispatch_epilogue_us': round(acc[1] * 1e3, 1),
-                'combine_kernel_us': round(acc[2] * 1e3, 1), 'combine_epilogue_us': round(acc[3] * 1e3, 1),
-                'dispatch_phases_us_rank0': phases,
-                'dispatch_kernel_gbs': round(n * disp_bytes_tok / (acc[0] * 1e-3) / 1e9, 1),
-                'combine_kernel_gbs': round(n * comb_bytes_tok / (acc[2] * 1e-3) / 1e9, 1),
-                'dispatch_e2e_gbs': round(n * disp_bytes_tok / ((acc[0] + acc[1]) * 1e-3) / 1e9, 1),
-                'combine_e2e_gbs': round(n * comb_bytes_tok / ((acc[2] + acc[3]) * 1e-3) / 1e9, 1)}
+                'dispatch_kernel_us': round(split[0] * 1e3, 1), 'dispatch_epilogue_us': round(split[1] * 1e3, 1),
+                'combine_kernel_us': round(split[2] * 1e3, 1), 'combine_epilogue_us': round(split[3] * 1e3, 1),
+                'dispatch_with_epilogue_us': round(pair[4] * 1e3, 1), 'combine_with_reduce_us': round(pair[5] * 1e3, 1),
+                'dispatch_phases_us_rank0': phases, 'kernel_spans_us_rank0': timeline,
+                'dispatch_kernel_gbs': round(n * disp_bytes_tok / (split[0] * 1e-3) / 1e9, 1),
+                'combine_kernel_gbs': round(n * comb_bytes_tok / (split[2] * 1e-3) / 1e9, 1),
+                'dispatch_e2e_gbs': round(n * disp_bytes_tok / (pair[4] * 1e-3) / 1e9, 1),
+                'combine_e2e_gbs': round(n * comb_bytes_tok / (pair[5] * 1e-3) / 1e9, 1)}
 
     if not args.no_extra:
         detail['sms_%d' % args.num_sms] = kernel_only(args.num_sms)
@@ -474,11 +732,11 @@ def main():
                     d['dispatch_frac_of_nvlink_measured'] = round(d['dispatch_kernel_gbs'] * frac / 770.0, 3)
                     d['combine_frac_of_nvlink_measured'] = round(d['combine_kernel_gbs'] * frac / 770.0, 3)
         # the reference's own measurement takes pre-quantised FP8 input (no cast inside the kernel): same kernel, cast outside
-        from deepep_b200.utils.math import per_token_cast_to_fp8
         xq = per_token_cast_to_fp8(xs[0])
 
         def prequant_dispatch_us(num_sms: int, iters: int = 11) -> float:
             dummy = torch.ones(1, device=dev)
+            buf.runtime.enable_profiling(2)
             vals = []
             for i in range(iters + 2):
                 torch.cuda.synchronize()
@@ -490,6 +748,7 @@ def main():
                 t = buf.runtime.last_timings()
                 if i >= 2:
                     vals.append(t[0])
+            buf.runtime.enable_profiling(0)
             return max_over_ranks(sorted(vals)[len(vals) // 2]) * 1e3, true_recv_tokens(h)
 
         for sms in sorted({args.num_sms, 64}):
@@ -500,25 +759,27 @@ def main():
 
         # ---- low-latency decode: 128 tokens per rank, FP8 dispatch + BF16 combine, captured in a CUDA graph
         try:
-            detail['low_latency'] = low_latency_section(deepep_b200, group, world, rank, dev, H, E, K, max_over_ranks)
+            detail['low_latency'], verified['ll'] = low_latency_section(deepep_b200, group, world, rank, dev, H, E, K, max_over_ranks)
         except Exception as exc:   # noqa: BLE001 - a failure here must not take the headline number down
             detail['low_latency'] = {'error': f'{type(exc).__name__}: {exc}'[:200]}
+            verified['ll'] = False
         # ---- fused MoE layer forward + backward (FP8 forward, bf16 gradients); needs the experts of a rank to fit comfortably
         if E // world <= 64:
             try:
-                detail['moe_layer'] = moe_layer_section(buf, world, rank, dev, H, E, K, max_over_ranks)
+                detail['moe_layer'], verified['moe'] = moe_layer_section(buf, world, rank, dev, H, E, K, max_over_ranks, group=group)
             except Exception as exc:   # noqa: BLE001
                 detail['moe_layer'] = {'error': f'{type(exc).__name__}: {exc}'[:200]}
+                verified['moe'] = False
         # ---- fused tensor-parallel GEMMs against NCCL + cuBLAS
         if world > 1:
             try:
-                detail['tp'] = tp_section(group, world, rank, dev, max_over_ranks)
+                detail['tp'], verified['tp'] = tp_section(group, world, rank, dev, max_over_ranks)
             except Exception as exc:   # noqa: BLE001
                 detail['tp'] = {'error': f'{type(exc).__name__}: {exc}'[:200]}
+                verified['tp'] = False
         # ---- plain NCCL all-to-all of the same FP8 rows (baseline, not the product)
         if world > 1:
             try:
-                from deepep_b200.utils import refs
                 xq8 = per_token_cast_to_fp8(xs[0])[0].view(torch.uint8)
                 for _ in range(2):
                     refs.nccl_all_to_all_dispatch(xq8, idxs[0], E)
@@ -599,6 +860,9 @@ def main():
                    'numa_binding_rank0': numa_binding,
                    'baseline': 'reference README EP8 SM100: 726 GB/s dispatch, 740 GB/s combine (kernel only, 64 SMs), per GPU'},
         'clocks': clocks,
+        'repeats': {'n': len(repeat_ms), 'ms_per_step': [round(v, 4) for v in repeat_ms], 'reported': 'median',
+                    'min': round(min(repeat_ms), 4), 'max': round(max(repeat_ms), 4)},
+        'verified': verified,
         'e2e': {'value': round(e2e_value, 2), 'unit': 'GB/s', 'ms_per_step': round(e2e_ms, 4), 'steps': e2e_steps,
                 'h2d_bytes_per_step': h2d, 'd2h_bytes_per_step': d2h,
                 'note': 'public API; the host->device copy of step i+1 is issued during step i on a copy stream (every step copies its own inputs)'},
@@ -611,6 +875,8 @@ def main():
     buf.destroy()
     if world > 1:
         dist.destroy_process_group()
+    if not all(bool(v) for v in verified.values()):      # a timed section whose output did not match its reference
+        sys.exit(3)
 
 
 if __name__ == '__main__':

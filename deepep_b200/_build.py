@@ -26,7 +26,6 @@ CSRC = ROOT / 'csrc'
 BUILD = ROOT.parent / 'build' / 'deepep_b200'
 EXT_SUFFIX = sysconfig.get_config_var('EXT_SUFFIX')
 TARGET = ROOT / f'_C{EXT_SUFFIX}'
-CAPI_TARGET = ROOT / 'libdeepep_b200_capi.so'
 
 NVCC_ARCH = ['-gencode', 'arch=compute_100a,code=sm_100a']
 NVCC_FLAGS = NVCC_ARCH + ['-O3', '-std=c++17', '-lineinfo', '--expt-relaxed-constexpr', '-Xcompiler', '-fPIC',
@@ -39,21 +38,6 @@ def cuda_home() -> str:
         if os.environ.get(key):
             return os.environ[key]
     return '/usr/local/cuda'
-
-
-def _cutlass_include() -> List[str]:
-    """CuTe / CUTLASS headers vendored with a Python package of the image (header-only use)."""
-    import importlib.util
-    out = []
-    for pkg, rel in (('flashinfer', 'data/cutlass/include'), ('tilelang', '3rdparty/cutlass/include')):
-        spec = importlib.util.find_spec(pkg)
-        if spec is None or not spec.submodule_search_locations:
-            continue
-        path = Path(list(spec.submodule_search_locations)[0]) / rel
-        if path.is_dir():
-            out.append(str(path))
-            break
-    return out
 
 
 def _headers_digest() -> str:
@@ -92,11 +76,10 @@ def build(force: bool = False, verbose: bool = False) -> Path:
     py_inc = sysconfig.get_paths()['include']
     cuda_inc = os.path.join(cuda_home(), 'include')
     headers = _headers_digest()
-    cutlass = _cutlass_include()
 
     jobs = []
     for src in sorted((CSRC / 'kernels').glob('*.cu')):
-        prefix = [nvcc] + NVCC_FLAGS + [f'-I{p}' for p in cutlass]
+        prefix = [nvcc] + NVCC_FLAGS
         if verbose:
             prefix += ['-Xptxas', '-v']
         obj = _object_for(src, prefix, headers)

@@ -14,8 +14,11 @@ Differences a caller can see:
 * ``dispatch(x_bf16, ..., use_fp8_dispatch / fused_fp8=True)`` can cast to e4m3 with 1x128
   scales inside the dispatch kernel (the reference takes pre-quantised tuples only; those
   work here too);
-* ``dispatch(..., zero_copy=True)`` returns ``recv_x`` as a view of the receive region (valid
-  until the second next dispatch on this buffer) and skips the payload copy of the epilogue;
+* ``dispatch(..., zero_copy=True)`` returns ``recv_x`` (and row-major ``recv_sf``) as strided views of
+  the receive region (valid until the second next dispatch on any rank of the group overwrites that half
+  of the region) and skips the payload copy of the epilogue;
+* ``combine(..., weighted=True)`` multiplies expanded rows by their top-k weights before summing;
+* ``topk_idx`` may be int64 or int32 (``deepep_b200.topk_idx_t`` follows ``EP_NUM_TOPK_IDX_BITS``);
 * device waits never trap: a wait that runs out records a status that :meth:`check_status`
   turns into :class:`EPTimeoutError`.
 """
@@ -91,6 +94,8 @@ class EPHandle:
         self.token_metadata_at_forward = token_metadata_at_forward
         self.channel_linked_list = channel_linked_list
         self._psum_expert_full: Optional[torch.Tensor] = None   # [local experts + 1], last = expanded rows
+        # [ranks, ranks] tokens that rank i sent to rank j in this dispatch (every rank gets the whole matrix)
+        self.num_tokens_per_rank_matrix: Optional[torch.Tensor] = None
 
     def deterministic_sort(self, *tensors):
         """Rows already arrive in (source rank, token) order; returns the tensors unchanged."""
@@ -122,10 +127,12 @@ class ElasticBuffer:
         assert 1 <= self.num_ranks <= _C.MAX_RANKS, f'one NVLink domain holds at most {_C.MAX_RANKS} ranks'
         self.allow_hybrid_mode = allow_hybrid_mode
         self.allow_multiple_reduction = allow_multiple_reduction
-        # EP_COMBINE_FUSED_REDUCE=1: the combine sums a token's rows inside the send kernel while later rows are
-        # still in flight (opt-in: on 8 x B200 the separate reduce kernel on all SMs is faster)
-        self.fuse_combine_reduce = int(os.environ.get('EP_COMBINE_FUSED_REDUCE', '0'))
-        # blocks on top of num_sms that only reduce (fused reduce); 0 = the spare warps of the send blocks do it all
+        # How the combine's reduce overlaps the sends (EP_COMBINE_FUSED_REDUCE): 1 (default) = a reduce kernel runs
+        # beside the send kernel on the SMs it leaves free and sums a token as soon as the arrival flags of its
+        # rows are up; 2 = the reduce runs inside the send kernel on spare warps; 0 = the reduce kernel runs after
+        # the send kernel.
+        self.fuse_combine_reduce = int(os.environ.get('EP_COMBINE_FUSED_REDUCE', '1'))
+        # mode 2 only: blocks on top of num_sms that only reduce; 0 = the spare warps of the send blocks do it all
         self.num_combine_reduce_sms = int(os.environ.get('EP_COMBINE_REDUCE_SMS', '0'))
         self.prefer_overlap_with_compute = prefer_overlap_with_compute
         self.deterministic = deterministic
@@ -402,7 +409,7 @@ class ElasticBuffer:
                             num_max_tokens_per_rank, expert_alignment, num_sms, previous_event,
                             previous_event_before_epilogue, async_with_compute_stream, allocate_on_comm_stream, handle,
                             do_cpu_sync, do_expand, do_zero_padding, use_tma_aligned_col_major_sf, zero_copy, fused_fp8,
-                            round_scale):
+                            round_scale, num_worst_tokens=0):
         a = _C.DispatchArgs()
         if isinstance(x, tuple):
             a.x, a.sf = x
@@ -443,6 +450,7 @@ class ElasticBuffer:
         a.do_zero_padding = do_zero_padding
         a.do_cpu_sync = value_or(do_cpu_sync, True)
         a.zero_copy = zero_copy
+        a.num_worst_tokens = num_worst_tokens
         a.col_major_sf = use_tma_aligned_col_major_sf
         sc = a.sc
         sc.previous_event = previous_event
@@ -461,6 +469,7 @@ class ElasticBuffer:
                                   r.psum_rank, r.psum_expert[:num_local], r.num_unaligned, r.recv_src_metadata,
                                   r.token_slot, r.pair_row)
             new_handle._psum_expert_full = r.psum_expert
+            new_handle.num_tokens_per_rank_matrix = r.count_matrix
         else:
             new_handle = handle
         recv_x = (r.recv_x, r.recv_sf) if r.recv_sf is not None else r.recv_x
@@ -474,7 +483,8 @@ class ElasticBuffer:
                  async_with_compute_stream: bool = False, allocate_on_comm_stream: bool = False,
                  handle: Optional[EPHandle] = None, do_handle_copy: bool = True, do_cpu_sync: Optional[bool] = None,
                  do_expand: bool = False, do_zero_padding: bool = False, use_tma_aligned_col_major_sf: bool = False,
-                 zero_copy: bool = False, fused_fp8: Optional[bool] = None, round_scale: bool = False):
+                 zero_copy: bool = False, fused_fp8: Optional[bool] = None, round_scale: bool = False,
+                 num_worst_tokens: int = 0):
         """Sends every token to the ranks that own its selected experts.
 
         Arguments follow the reference (deep_ep/buffers/elastic.py:855-923): ``x`` is bf16
@@ -482,7 +492,10 @@ class ElasticBuffer:
         -1 for unused lanes; ``handle`` replays an earlier routing. Extras: ``fused_fp8`` casts a bf16
         ``x`` to e4m3 with 1x128 float scales inside the kernel (default: on when the buffer was built
         with ``use_fp8_dispatch`` and ``x`` is bf16); ``round_scale`` makes those scales powers of two;
-        ``zero_copy`` returns ``recv_x`` as a view of the receive region.
+        ``zero_copy`` returns ``recv_x`` (and row-major scales) as strided views of the receive region: they stay
+        valid until the second next dispatch of any rank of the group, which overwrites that half of the region;
+        ``num_worst_tokens`` (with ``do_cpu_sync=False``) sets the row count of the outputs, whose routing rows
+        past the received count are filled with -1 / 0.
 
         Returns ``(recv_x | (recv_x, recv_sf), recv_topk_idx, recv_topk_weights, handle, event)``.
         In the expanded layout ``recv_topk_idx`` is ``None`` and ``recv_topk_weights`` is 1-D.
@@ -494,7 +507,7 @@ class ElasticBuffer:
                                      num_max_tokens_per_rank, expert_alignment, num_sms, previous_event,
                                      previous_event_before_epilogue, async_with_compute_stream, allocate_on_comm_stream,
                                      handle, do_cpu_sync, do_expand, do_zero_padding, use_tma_aligned_col_major_sf,
-                                     zero_copy, fused_fp8, round_scale)
+                                     zero_copy, fused_fp8, round_scale, num_worst_tokens)
         r = _C.Runtime.dispatch([self.runtime], [a])[0]
         return self._wrap_dispatch_result(r, a, do_handle_copy, handle)
 
@@ -509,7 +522,7 @@ class ElasticBuffer:
         return bias[0], bias[1]
 
     def _make_combine_args(self, x, handle, topk_weights, bias, num_sms, previous_event, previous_event_before_epilogue,
-                           async_with_compute_stream, allocate_on_comm_stream):
+                           async_with_compute_stream, allocate_on_comm_stream, weighted=False):
         a = _C.CombineArgs()
         a.x = x
         a.topk_weights = topk_weights
@@ -521,6 +534,7 @@ class ElasticBuffer:
         a.num_max_tokens = handle.num_max_tokens_per_rank
         a.num_sms = num_sms if num_sms > 0 else handle.num_sms
         a.do_expand = handle.do_expand
+        a.weighted = bool(weighted)
         a.allow_multiple_reduction = self.allow_multiple_reduction
         a.dst_slot = handle.dst_buffer_slot_idx
         a.fuse_reduce = self.fuse_combine_reduce
@@ -536,19 +550,21 @@ class ElasticBuffer:
     def combine(self, x: torch.Tensor, handle: EPHandle, topk_weights: Optional[torch.Tensor] = None,
                 bias: Union[None, torch.Tensor, Tuple[torch.Tensor, torch.Tensor]] = None, num_sms: int = 0,
                 num_qps: int = 0, previous_event=None, previous_event_before_epilogue=None,
-                async_with_compute_stream: bool = False, allocate_on_comm_stream: bool = False):
+                async_with_compute_stream: bool = False, allocate_on_comm_stream: bool = False, weighted: bool = False):
         """Sends expert outputs back to the tokens' source ranks and sums them there.
 
         ``x`` is bf16: one row per received token (non-expand; the caller has summed its local
         experts) or one row per expanded row. The result is the plain sum of all contributions plus
         ``bias`` (fp32 accumulation in ascending rank order, one bf16 rounding at the end; with the
         expanded layout and ``allow_multiple_reduction`` each rank's partial sum is rounded once
-        more). ``topk_weights`` are only carried back to ``combined_topk_weights``.
+        more). ``topk_weights`` are carried back to ``combined_topk_weights``; with ``weighted=True`` (expanded
+        layout only) every expanded row is also multiplied by its weight before it is added, i.e. the result is
+        ``sum_k w_k * x_k`` as the low-latency combine computes it.
 
         Returns ``(combined_x, combined_topk_weights, event)``.
         """
         check_torch_deterministic()
         a = self._make_combine_args(x, handle, topk_weights, bias, num_sms, previous_event, previous_event_before_epilogue,
-                                    async_with_compute_stream, allocate_on_comm_stream)
+                                    async_with_compute_stream, allocate_on_comm_stream, weighted)
         r = _C.Runtime.combine([self.runtime], [a])[0]
         return r.combined_x, r.combined_topk_weights, EventOverlap(r.event)

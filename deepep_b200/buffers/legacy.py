@@ -11,6 +11,8 @@ Arguments that only make sense with RDMA (``num_qps_per_rank``, ``allow_mnnvl``,
 """
 from __future__ import annotations
 
+import contextlib
+
 from typing import Any, Callable, List, Optional, Tuple, Union
 
 import torch
@@ -188,11 +190,14 @@ class Buffer:
             assert num_tokens_per_expert is not None
             num_experts = num_tokens_per_expert.numel()
         t_max = self._max_tokens(hidden, topk_idx.size(1))
+        # num_worst_tokens > 0: no CPU sync (graph-safe); the outputs have exactly that many rows and the routing
+        # rows past the received count hold -1 / 0 (csrc/legacy/buffer.hpp:571-577, intranode.cu:536-540 of the reference)
+        assert num_worst_tokens <= self.group_size * t_max, 'num_worst_tokens exceeds what the buffer can receive'
         recv_x, recv_topk_idx, recv_topk_weights, ep_handle, event = self._elastic.dispatch(
             x, topk_idx=topk_idx, topk_weights=topk_weights, num_experts=num_experts, num_max_tokens_per_rank=t_max,
             expert_alignment=expert_alignment, num_sms=config.num_sms, previous_event=prev,
             async_with_compute_stream=async_finish, allocate_on_comm_stream=allocate_on_comm_stream,
-            do_cpu_sync=num_worst_tokens == 0, fused_fp8=False)
+            do_cpu_sync=num_worst_tokens == 0, fused_fp8=False, num_worst_tokens=num_worst_tokens)
         if recv_topk_weights is not None:
             # weights of experts that live elsewhere carry no meaning on this rank
             if async_finish:
@@ -203,10 +208,32 @@ class Buffer:
                 recv_topk_weights.masked_fill_(recv_topk_idx < 0, 0)
         if is_token_in_rank is None:
             is_token_in_rank = ep_handle.dst_buffer_slot_idx >= 0
-        empty = torch.empty(0, dtype=torch.int32, device=topk_idx.device)
-        legacy = LegacyHandle((ep_handle.psum_num_recv_tokens_per_scaleup_rank, empty, empty, ep_handle.recv_src_metadata[:, 0],
-                               is_token_in_rank, ep_handle.dst_buffer_slot_idx), ep_handle)
+        legacy = LegacyHandle(self._legacy_handle_tensors(ep_handle, is_token_in_rank, async_finish), ep_handle)
         return recv_x, recv_topk_idx, recv_topk_weights, ep_handle.num_recv_tokens_per_expert_list, legacy, event
+
+    def _legacy_handle_tensors(self, ep_handle, is_token_in_rank, on_comm_stream: bool):
+        """The six tensors of the reference's intranode handle (deep_ep/buffers/legacy.py:401), filled from what
+        the dispatch left behind. There is one "channel" here (tokens are not cut into channel ranges):
+
+        * ``rank_prefix_matrix[i, j]``: tokens that ranks ``0..i`` sent to rank ``j`` (the count exchange of the
+          dispatch kernel gives every rank the whole matrix of totals);
+        * ``channel_prefix_matrix[j, 0]``: tokens this rank sent to rank ``j``;
+        * ``recv_channel_prefix_matrix[i, 0]``: tokens this rank received from rank ``i``;
+        * ``recv_src_idx``, ``is_token_in_rank``;
+        * ``send_head[t, j]``: position of token ``t`` among this rank's tokens for rank ``j`` (-1 = not sent).
+        """
+        R = self.group_size
+        ctx = torch.cuda.stream(self.get_comm_stream()) if on_comm_stream else contextlib.nullcontext()
+        with ctx:
+            counts = ep_handle.num_tokens_per_rank_matrix      # [source, destination]
+            rank_prefix_matrix = torch.cumsum(counts, dim=0).int()
+            channel_prefix_matrix = counts[self.rank].clone().view(R, 1)
+            recv_channel_prefix_matrix = counts[:, self.rank].clone().view(R, 1)
+            slot = ep_handle.dst_buffer_slot_idx
+            base = (rank_prefix_matrix[self.rank] - counts[self.rank]).view(1, R)
+            send_head = torch.where(slot >= 0, slot - base, slot)
+        return (rank_prefix_matrix, channel_prefix_matrix, recv_channel_prefix_matrix, ep_handle.recv_src_metadata[:, 0],
+                is_token_in_rank, send_head)
 
     def combine(self, x: torch.Tensor, handle: Tuple, topk_weights: Optional[torch.Tensor] = None,
                 bias: Union[None, torch.Tensor, Tuple[torch.Tensor, torch.Tensor]] = None, config: Optional[Config] = None,

@@ -104,6 +104,30 @@ __device__ __forceinline__ int atom_add_acq_rel_gpu_s32(int* p, int v) {
     return old;
 }
 
+__device__ __forceinline__ uint64_t atom_add_acq_rel_gpu_u64(uint64_t* p, uint64_t v) {
+    uint64_t old;
+    asm volatile("atom.add.acq_rel.gpu.global.u64 %0, [%1], %2;" : "=l"(old) : "l"(p), "l"(v) : "memory");
+    return old;
+}
+
+// ---------------------------------------------------------------- programmatic dependent launch
+// A kernel launched with the programmatic-stream-serialization attribute may start while its predecessor in the
+// stream still runs: its blocks become resident once every block of the predecessor has called
+// launch_dependents() (or exited). dependency_wait() then blocks until the predecessor has completed and its
+// memory operations are visible. Both are no-ops in a kernel launched without the attribute.
+__device__ __forceinline__ void launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+__device__ __forceinline__ void dependency_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+
+// Routing entry i of a top-k index tensor that holds int64 or int32 values; anything outside [0, limit) is -1.
+__device__ __forceinline__ int load_topk_idx(const void* base, bool idx32, int64_t i, int limit) {
+    if (idx32) {
+        const int v = reinterpret_cast<const int*>(base)[i];
+        return (v >= 0 && v < limit) ? v : -1;
+    }
+    const int64_t v = reinterpret_cast<const int64_t*>(base)[i];
+    return (v >= 0 && v < limit) ? static_cast<int>(v) : -1;
+}
+
 // 16-byte streaming accesses (read-once data: keep it out of L1).
 __device__ __forceinline__ int4 ld_nc_int4(const void* p) {
     int4 v;

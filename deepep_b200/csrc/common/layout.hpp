@@ -60,7 +60,8 @@ enum StatusCode : int {
 // ---------------------------------------------------------------- private (per-rank, not peer-mapped) workspace, in uint64 words
 constexpr int kWsGridBarrier = 0;    // monotonically growing arrival counter
 constexpr int kWsPoison = 1;         // non-zero after any wait of this rank gave up
-constexpr int kWsStamps = 2;         // [8] phase timestamps of the last dispatch (block 0, ns)
+constexpr int kWsStamps = 2;         // [8] phase timestamps of the last dispatch (ns): start, counted, ordered, totals in, bases
+                                     // published, last row issued (all of block 0), own stores complete, all blocks done
 constexpr int kWsWork = 10;          // next token index handed out by the dynamic send loops
 constexpr int kWsLLCalls = 11;       // [4] low-latency call counters: dispatch send, dispatch recv, combine send, combine recv
 constexpr int kWsWorkReduce = 15;    // next token handed out by the fused reduce of the combine
@@ -78,7 +79,10 @@ constexpr size_t kWsTpInts = 64 * kMaxRanks;
 // [kMaxBlocks][kMaxRanks + kMaxExperts] the published first rows of every block's chunk
 constexpr size_t kWsStealOffsetBytes = kWsTpOffsetBytes + kWsTpInts * 4;
 constexpr size_t kWsStealInts = 2 * static_cast<size_t>(kMaxBlocks) + static_cast<size_t>(kMaxBlocks) * (kMaxRanks + kMaxExperts);
-constexpr size_t kWsBytes = kWsStealOffsetBytes + kWsStealInts * 4 + 4096;
+// kernel timeline (uint64 ns, %globaltimer): [8 kernels][start of block 0, end of the last block to leave]
+constexpr size_t kWsTimelineOffsetBytes = align_up<size_t>(kWsStealOffsetBytes + kWsStealInts * 4, 8);
+constexpr int kTlDispatch = 0, kTlDispatchEpilogue = 1, kTlCombine = 2, kTlCombineReduce = 3;
+constexpr size_t kWsBytes = kWsTimelineOffsetBytes + 16 * 8 + 4096;
 
 // ---------------------------------------------------------------- control area of the symmetric heap, in uint64 words
 constexpr size_t kCtlBarrier = 0;                                        // [kMaxRanks]
@@ -112,25 +116,31 @@ struct Multi {
 };
 
 // ---------------------------------------------------------------- high-throughput EP layout
-// Meta row that travels with every (token, destination rank):
-//   [scale factors][topk idx int32 x K][topk weights f32 x K][expanded rows int32 x K][src token int32][pad]
+// One record travels per (token, destination rank), as ONE bulk store:
+//   [payload row][scale factors][topk idx int32 x K][topk weights f32 x K][expanded rows int32 x K][src token int32][pad]
+// The part after the payload is the "meta" of the record. Records sit `pitch` bytes apart in the receive
+// region (a multiple of 128, so every record starts on a full NVLink packet / cache line); payload and
+// scale factors are handed to the caller as strided views when it asks for zero copy.
 EP_HD int ht_meta_bytes(int sf_bytes, int num_topk) {
     return static_cast<int>(align_up<int>(sf_bytes + 12 * num_topk + 4, 16));
 }
 EP_HD int ht_meta_bytes_max(int hidden, int num_topk) {
     return ht_meta_bytes(ceil_div(hidden, 128) * 4, num_topk);
 }
+EP_HD int ht_record_bytes(int x_row_bytes, int sf_bytes, int num_topk) { return x_row_bytes + ht_meta_bytes(sf_bytes, num_topk); }
+EP_HD int ht_record_pitch(int x_row_bytes, int sf_bytes, int num_topk) {
+    return align_up<int>(ht_record_bytes(x_row_bytes, sf_bytes, num_topk), 128);
+}
 
-// received rows per arrival flag of the combine with fused reduce
+// received rows per arrival flag of the combine (flag-driven reduce)
 constexpr int kCombineFlagRows = 32;
 
 struct HtLayout {
     // all offsets are bytes from the heap base
-    uint64_t dispatch_x[2];
-    uint64_t dispatch_meta[2];
+    uint64_t dispatch_rec[2];  // [ranks * max tokens] records
     uint64_t combine_x[2];
     uint64_t combine_w[2];
-    uint64_t combine_flag;     // [ranks][flag chunks] arrival flags of the fused reduce + [flag chunks] int32 counters
+    uint64_t combine_flag;     // [ranks][flag chunks] arrival flags of the flag-driven reduce + [flag chunks] int32 counters
     int combine_flag_chunks;
     uint64_t end;
 };
@@ -140,13 +150,12 @@ struct HtLayout {
 EP_HD HtLayout ht_layout(int num_ranks, int num_max_tokens, int hidden, int num_topk) {
     HtLayout l;
     const uint64_t rows = static_cast<uint64_t>(num_ranks) * num_max_tokens;
-    const uint64_t x_bytes = align_up<uint64_t>(rows * hidden * 2, 256);
-    const uint64_t meta_bytes = align_up<uint64_t>(rows * ht_meta_bytes_max(hidden, num_topk), 256);
+    const uint64_t rec_bytes = align_up<uint64_t>(rows * align_up<uint64_t>(hidden * 2 + ht_meta_bytes_max(hidden, num_topk), 128), 256);
     const int lanes = num_ranks > num_topk ? num_ranks : num_topk;   // rank layout or top-k layout
     const uint64_t crow = align_up<uint64_t>(static_cast<uint64_t>(lanes) * num_max_tokens * hidden * 2, 256);
     const uint64_t cw = align_up<uint64_t>(static_cast<uint64_t>(lanes) * num_max_tokens * num_topk * 4, 256);
     uint64_t off = kCtlBytes;
-    for (int s = 0; s < 2; ++s) { l.dispatch_x[s] = off; off += x_bytes; l.dispatch_meta[s] = off; off += meta_bytes; }
+    for (int s = 0; s < 2; ++s) { l.dispatch_rec[s] = off; off += rec_bytes; }
     for (int s = 0; s < 2; ++s) { l.combine_x[s] = off; off += crow; l.combine_w[s] = off; off += cw; }
     l.combine_flag_chunks = static_cast<int>(ceil_div<uint64_t>(rows, kCombineFlagRows));
     l.combine_flag = off;

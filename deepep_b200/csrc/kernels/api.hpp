@@ -38,18 +38,21 @@ struct DispatchParams {
     int src_row_bytes;      // bytes of one input row
     int x_row_bytes;        // bytes of one payload row as it is sent and received
     int sf_bytes;           // bytes of scale factors per token (0 = none)
-    int meta_bytes;         // bytes of one meta row
+    int meta_bytes;         // bytes of the record's meta part (ht_meta_bytes)
+    int rec_pitch;          // bytes between records of the receive region (multiple of 128)
     int quant_mode;
     int expert_alignment;
     int do_expand;          // expert prefix sums follow the expanded layout
     int cached;             // reuse token_slot / pair_row of an earlier dispatch, no counting
+    int idx32;              // topk_idx holds int32 (else int64)
+    int smem_scratch_bytes; // dynamic shared memory after the header (filled in by the launcher)
     // inputs
     const uint8_t* x;
     int64_t x_stride_bytes;
     const uint8_t* sf;          // 4-byte packs, [tokens][packs] with the strides below (in packs)
     int64_t sf_token_stride;
     int64_t sf_pack_stride;
-    const int64_t* topk_idx;    // [T, K], -1 = unused lane
+    const void* topk_idx;       // [T, K] int64 or int32, -1 = unused lane
     const float* topk_weights;  // [T, K] or null
     // handle tensors (device, owned by the caller)
     int* token_slot;        // [T, R]  row in the destination rank's receive region, -1 = not sent
@@ -58,9 +61,9 @@ struct DispatchParams {
     int* psum_expert;       // [E_local + 1]
     int* num_unaligned;     // [E_local] received (token, expert) pairs per local expert
     int* recv_stats;        // [E_local] cumulative statistics or null
+    int* count_matrix;      // [R, R] tokens that rank i sends to rank j (every rank sees the whole matrix), or null
     // heap
-    uint64_t off_recv_x;
-    uint64_t off_recv_meta;
+    uint64_t off_recv;      // receive region (records) of this call's parity
     uint32_t epoch;
     uint64_t grid_bar_base;
     uint64_t* host_counts;  // mapped pinned: [0] received tokens, [1] expanded rows, [2 + e] per local expert (aligned)
@@ -70,42 +73,47 @@ struct DispatchLaunch {
     int num_sms;            // blocks per rank
     int num_warps;          // send warps per block
     int smem_bytes;
+    int scratch_bytes;      // smem_bytes minus the header
 };
-// Picks warps / shared memory for a dispatch of this shape. Returns false if a row does not fit.
+// Picks warps / shared memory for a dispatch of this shape. Returns false if a row (or the routing
+// scratch of the ordering pass) does not fit.
 bool plan_dispatch(const DispatchParams& p, int num_sms, int smem_optin, DispatchLaunch* out);
 cudaError_t launch_dispatch(const Multi<DispatchParams>& m, const DispatchLaunch& l, cudaStream_t stream);
 
 struct DispatchEpilogueParams {
     // receive side of one rank
-    int rank;
+    CommCtx c;               // for the bounded wait on the peers' completion words
+    uint32_t epoch;          // of the dispatch whose records are unpacked
+    int wait_done;           // 1: wait until every peer has reported its rows of `epoch` as landed
     int num_ranks;
     int num_topk;
     int num_local_experts;
     int num_max_tokens;
     int x_row_bytes;
     int sf_bytes;
-    int meta_bytes;
+    int rec_pitch;
     int do_expand;
     int copy_x;              // 0: recv_x aliases the receive region (zero copy), rows are not moved
     int expert_alignment;
     int do_zero_padding;
     int write_metadata;      // 0 for cached dispatches (metadata is reused)
-    const uint8_t* region_x;
-    const uint8_t* region_meta;
+    int idx32;               // recv_topk_idx holds int32 (else int64)
+    const uint8_t* region;   // records
     const int* psum_rank;    // [R] inclusive; [R-1] = number of received rows
     const int* psum_expert;  // [E_local + 1]
     const int* num_unaligned;
     // outputs
     uint8_t* recv_x;          // [rows, x_row_bytes]
-    uint8_t* recv_sf;         // packs of 4 bytes
+    uint8_t* recv_sf;         // packs of 4 bytes, or null (none, or the caller reads them in place)
     int64_t recv_sf_row_stride, recv_sf_pack_stride;   // in packs
-    int64_t* recv_topk_idx;   // [N, K] (non-expand) or null
-    float* recv_topk_weights; // [N, K] or [rows] (expand) or null
-    int* recv_src_metadata;   // [N, K + 2]
+    void* recv_topk_idx;      // [num_idx_rows, K] (non-expand) or null
+    float* recv_topk_weights; // [num_idx_rows, K] or [rows] (expand) or null
+    int* recv_src_metadata;   // [num_idx_rows, K + 2]
     int num_out_rows;         // capacity of recv_x in rows (expand: expanded rows)
+    int num_idx_rows;         // rows of the routing outputs; rows past the received count are filled with -1 / 0
 };
 cudaError_t launch_dispatch_epilogue(const DispatchEpilogueParams* params, int num_vranks, int num_sms, int smem_optin,
-                                     cudaStream_t stream);
+                                     cudaStream_t stream, bool programmatic = false);
 
 // ---------------------------------------------------------------- high-throughput combine
 struct CombineEpilogueParams {
@@ -117,13 +125,23 @@ struct CombineEpilogueParams {
     int hidden;               // bf16 elements
     int num_lanes;
     int use_rank_layout;
+    int idx32;                // topk_idx holds int32 (else int64)
+    int weighted;             // top-k layout only: row k is multiplied by its top-k weight (region_w) before it is added
     const uint8_t* region_x;
     const float* region_w;    // [lanes][T_max][K] or null
-    const int64_t* topk_idx;  // [T, K] the dispatch's routing
+    const void* topk_idx;     // [T, K] the dispatch's routing
     const uint8_t* bias0;
     const uint8_t* bias1;
     uint8_t* combined_x;              // [T, hidden] bf16
     float* combined_topk_weights;     // [T, K] or null
+    // Flag-driven mode (flags != null): the kernel runs beside the send kernel and sums a token as soon as the
+    // arrival flags of all its rows are up; every wait is bounded through `c`.
+    CommCtx c;
+    uint32_t epoch;
+    const uint64_t* flags;    // [R][flag_chunks] epoch-tagged arrival words in this rank's heap, or null
+    int flag_chunks;
+    const int* dst_slot;      // [T, R] row of each of this rank's tokens in every destination's receive order (-1 = none)
+    uint64_t* local_ws;       // private workspace (kernel timeline)
 };
 struct CombineParams {
     CommCtx c;
@@ -133,6 +151,7 @@ struct CombineParams {
     int do_expand;
     int num_lanes;            // rows per token in the receive region (ranks, or top-k)
     int use_rank_layout;      // 1: lane = sending rank (pre-reduced), 0: lane = top-k slot
+    int weighted;             // expanded input: rows are multiplied by their top-k weight (rank layout: in the pre-reduce)
     const uint8_t* x;         // [N or expanded rows, hidden] bf16
     int64_t x_stride_bytes;
     const float* topk_weights;   // non-expand [N, K]; expand [rows]; or null
@@ -142,9 +161,10 @@ struct CombineParams {
     uint64_t off_comb_w;
     uint32_t epoch;
     uint64_t grid_bar_base;
-    // Reduce fused into the send kernel: every `kCombineFlagRows` received rows that have landed raise one flag at
-    // their source rank(s); warps that have no row to send (and the send warps once they are done) sum this rank's
-    // tokens as soon as the flags of all their contributions are up. No epilogue launch then.
+    // Arrival flags (fuse_reduce >= 1): every `kCombineFlagRows` received rows that have landed raise one flag at
+    // their source rank(s). fuse_reduce == 1: a reduce kernel launched right behind this one (programmatic dependent
+    // launch, on the SMs this kernel leaves free) sums tokens as their flags come up. fuse_reduce == 2: warps of
+    // this kernel that have no row to send (and the send warps once they are done) do that themselves.
     int fuse_reduce;
     int num_send_warps;       // warps [0, num_send_warps) send; the block may carry more warps that only reduce
     int num_send_blocks;      // blocks [0, num_send_blocks) send (and reduce); further blocks only reduce
@@ -157,13 +177,15 @@ struct CombineParams {
 struct CombineLaunch {
     int num_sms;
     int num_warps;            // send warps (one staging buffer each)
-    int num_reduce_warps;     // extra warps: fused reduce, or senders that copy through registers
+    int num_reduce_warps;     // extra warps of the in-kernel reduce
     int smem_bytes;
 };
 bool plan_combine(const CombineParams& p, int num_sms, int smem_optin, CombineLaunch* out);
 cudaError_t launch_combine(const Multi<CombineParams>& m, const CombineLaunch& l, cudaStream_t stream);
 
-cudaError_t launch_combine_epilogue(const CombineEpilogueParams* params, int num_vranks, int num_sms, cudaStream_t stream);
+// `programmatic`: launched as a programmatic dependent of the kernel before it in the stream (the send kernel).
+cudaError_t launch_combine_epilogue(const CombineEpilogueParams* params, int num_vranks, int num_sms, cudaStream_t stream,
+                                    bool programmatic = false);
 
 // ---------------------------------------------------------------- layout (legacy get_dispatch_layout)
 cudaError_t launch_dispatch_layout(const int64_t* topk_idx, int num_tokens, int num_topk, int num_ranks, int num_experts,

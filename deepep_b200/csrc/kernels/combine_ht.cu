@@ -11,15 +11,18 @@
 // reading the half it is about to overwrite.
 //
 // Reduce: combined_x[t] = sum over lanes in ascending order (fp32) + bias_0 + bias_1, one bf16
-// rounding at the end; top-k weights are gathered back. By default a separate epilogue kernel on
-// all SMs does it. Optionally (fuse_reduce) it runs inside
-// the send kernel: a block carries more warps than staging buffers, the extra warps (and the
-// send warps once their rows are gone) take this rank's tokens in ascending order and sum a
-// token as soon as every rank that contributes to it has raised the arrival flag of the 32-row
-// group holding its row. Senders count a row as landed three rows late (wait_group confirms the
-// remote writes by then), so the NVLink round trip never stalls a send warp. The rows just
-// received are still in L2 when they are summed. Measured at EP8 (24 send SMs) the fused form
-// is reduce-bound (a warp per token needs the parallelism of the whole GPU), hence opt-in.
+// rounding at the end; top-k weights are gathered back. Three ways to run it:
+//   * flag-driven, beside the send kernel (default with peers): senders raise one arrival flag per
+//     32-row group of a receiver's rows (a row counts as landed three rows late, when wait_group
+//     has confirmed its remote writes, so the NVLink round trip never stalls a send warp); the
+//     reduce kernel is launched as a programmatic dependent of the send kernel -- it becomes
+//     resident on the SMs the send kernel leaves free once every send block is running -- and sums
+//     a token as soon as the flags of all its rows are up, while later rows are still in flight;
+//   * the same reduce kernel after the send kernel (no flags), e.g. when an event gates the reduce;
+//   * inside the send kernel on spare warps (fuse_reduce == 2; reduce-bound at 24 SMs, kept for
+//     experiments).
+// With `weighted`, expanded rows are multiplied by their top-k weight: in the sender's fp32
+// pre-reduce (rank layout) or in the reduce (top-k layout).
 //
 // Parity: deep_ep/include/deep_ep/impls/combine.cuh:15-243, impls/combine_utils.cuh:41-170
 // and impls/combine_reduce_epilogue.cuh:12-143 of the reference.
@@ -38,6 +41,21 @@ __device__ __forceinline__ void accumulate_bf16x8(float (&acc)[8], const int4& r
         acc[2 * i] += v.x;
         acc[2 * i + 1] += v.y;
     }
+}
+
+__device__ __forceinline__ void accumulate_bf16x8_scaled(float (&acc)[8], const int4& raw, float wt) {
+    const __nv_bfloat162* h2 = reinterpret_cast<const __nv_bfloat162*>(&raw);
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        const float2 v = __bfloat1622float2(h2[i]);
+        acc[2 * i] = fmaf(wt, v.x, acc[2 * i]);
+        acc[2 * i + 1] = fmaf(wt, v.y, acc[2 * i + 1]);
+    }
+}
+
+// top-k layout, weighted: the weight of the row in lane `row` of token t (its own top-k weight)
+__device__ __forceinline__ float row_weight(const CombineEpilogueParams& p, int t, int row) {
+    return p.region_w[(static_cast<uint64_t>(row) * p.num_max_tokens + t) * p.num_topk + row];
 }
 
 __device__ __forceinline__ int4 pack_bf16x8(const float (&acc)[8]) {
@@ -69,17 +87,23 @@ __device__ __forceinline__ void reduce_columns(const CombineEpilogueParams& p, i
                 todo &= todo - 1;       // 0 stays 0
             }
             int4 raw[NR][NV];
+            float wt[NR];
 #pragma unroll
-            for (int r = 0; r < NR; ++r)
+            for (int r = 0; r < NR; ++r) {
+                wt[r] = (p.weighted && rows[r] >= 0) ? row_weight(p, t, rows[r]) : 1.f;
 #pragma unroll
                 for (int j = 0; j < NV; ++j)
                     if (rows[r] >= 0 && v + 32 * j < vec_per_row)
                         raw[r][j] = ld_nc_int4(p.region_x + (static_cast<uint64_t>(rows[r]) * p.num_max_tokens + t) * row_bytes + (v + 32 * j) * 16);
+            }
 #pragma unroll
             for (int r = 0; r < NR; ++r)
 #pragma unroll
                 for (int j = 0; j < NV; ++j)
-                    if (rows[r] >= 0 && v + 32 * j < vec_per_row) accumulate_bf16x8(acc[j], raw[r][j]);
+                    if (rows[r] >= 0 && v + 32 * j < vec_per_row) {
+                        if (p.weighted) accumulate_bf16x8_scaled(acc[j], raw[r][j], wt[r]);
+                        else accumulate_bf16x8(acc[j], raw[r][j]);
+                    }
         }
 #pragma unroll
         for (int j = 0; j < NV; ++j) {
@@ -110,7 +134,7 @@ __device__ __forceinline__ void reduce_token(const CombineEpilogueParams& p, int
     }
     const uint8_t* b0 = p.bias0 != nullptr ? p.bias0 + t * row_bytes : nullptr;
     const uint8_t* b1 = p.bias1 != nullptr ? p.bias1 + t * row_bytes : nullptr;
-    if (__popc(mask) == 1 && b0 == nullptr && b1 == nullptr) {
+    if (__popc(mask) == 1 && b0 == nullptr && b1 == nullptr && !p.weighted) {
         // a single contribution (e.g. one rank): the sum is a copy; keep four loads in flight per lane
         const uint8_t* src = p.region_x + (static_cast<uint64_t>(__ffs(mask) - 1) * p.num_max_tokens + t) * row_bytes;
         uint8_t* dst = p.combined_x + t * row_bytes;
@@ -135,8 +159,7 @@ __device__ __forceinline__ void reduce_token(const CombineEpilogueParams& p, int
 
 __device__ __forceinline__ int token_expert(const CombineEpilogueParams& p, int t, int lane) {
     if (lane >= p.num_topk) return -1;
-    const int64_t raw = p.topk_idx[static_cast<int64_t>(t) * p.num_topk + lane];
-    return (raw >= 0 && raw < static_cast<int64_t>(p.num_local_experts) * p.num_ranks) ? static_cast<int>(raw) : -1;
+    return load_topk_idx(p.topk_idx, p.idx32 != 0, static_cast<int64_t>(t) * p.num_topk + lane, p.num_local_experts * p.num_ranks);
 }
 
 __device__ __noinline__ void reduce_token_registers(const CombineEpilogueParams& p, int t, int e, int lane) {
@@ -176,9 +199,30 @@ __global__ void __launch_bounds__(kEpiWarps * 32) combine_epilogue_kernel(const 
     const int nchunks = static_cast<int>(row_bytes / kEpiChunk);
     const bool chunkable = row_bytes % kEpiChunk == 0;
     const uint64_t deadline = globaltimer_ns() + 2000000000ull;
+    uint64_t* timeline = reinterpret_cast<uint64_t*>(reinterpret_cast<uint8_t*>(p.local_ws) + kWsTimelineOffsetBytes) + 2 * kTlCombineReduce;
+    if (bid == 0 && threadIdx.x == 0) timeline[0] = globaltimer_ns();
+    // Flag-driven mode: this kernel runs beside the send kernel (it never waits for it as a whole); the tokens of
+    // a warp are visited in ascending order, which is also the order in which their rows arrive.
+    const bool flagged = p.flags != nullptr;
+    const WaitCtx w = make_wait_ctx(p.c);
+    bool flags_ok = true;
 
-    for (int t = bid * num_warps + warp; t < p.num_tokens; t += nb * num_warps) {
+    for (int t = bid * num_warps + warp; t < p.num_tokens && flags_ok; t += nb * num_warps) {
         const int e = token_expert(p, t, lane);
+        if (flagged) {
+            bool ok = true;
+            if (e >= 0) {
+                const int src = e / EL;
+                const int slot = p.dst_slot[static_cast<int64_t>(t) * p.num_ranks + src];
+                if (slot >= 0) {
+                    const uint64_t* flag = p.flags + static_cast<uint64_t>(src) * p.flag_chunks + slot / kCombineFlagRows;
+                    ok = bounded_wait(w, kStatusCombineDone, src, t, [&]() { return epoch_reached(ld_acquire_sys_u64(flag), p.epoch); });
+                }
+            }
+            flags_ok = __all_sync(0xffffffffu, ok);
+            if (!flags_ok) break;
+            fence_proxy_async_all();    // the rows are read through the async proxy below
+        }
         const int slot_lane = e < 0 ? -1 : (p.use_rank_layout ? e / EL : lane);
         uint32_t mask = slot_lane >= 0 ? (1u << slot_lane) : 0u;
 #pragma unroll
@@ -198,6 +242,7 @@ __global__ void __launch_bounds__(kEpiWarps * 32) combine_epilogue_kernel(const 
         const uint8_t* b1 = p.bias1 != nullptr ? p.bias1 + t * row_bytes : nullptr;
         // lane r < n loads row r = the r-th contributing lane of the region (ascending)
         const int my_slot = lane < n ? static_cast<int>(__fns(mask, 0, lane + 1)) : 0;
+        const float my_wt = (p.weighted && lane < n) ? row_weight(p, t, my_slot) : 1.f;
         const uint8_t* my_src = p.region_x + (static_cast<uint64_t>(my_slot) * p.num_max_tokens + t) * row_bytes;
         uint8_t* dst = p.combined_x + t * row_bytes;
         for (int c = 0; c < nchunks + kEpiStages - 1 && staged_ok; ++c) {
@@ -225,8 +270,14 @@ __global__ void __launch_bounds__(kEpiWarps * 32) combine_epilogue_kernel(const 
 #pragma unroll
                     for (int i = 0; i < 8; ++i) acc[i] = 0.f;
 #pragma unroll
-                    for (int r = 0; r < kEpiRows; ++r)
-                        if (r < n) accumulate_bf16x8(acc, *reinterpret_cast<const int4*>(sbuf + (s * kEpiRows + r) * kEpiChunk + h * 512 + lane * 16));
+                    for (int r = 0; r < kEpiRows; ++r) {
+                        const float wt = p.weighted ? __shfl_sync(0xffffffffu, my_wt, r) : 1.f;
+                        if (r < n) {
+                            const int4 raw = *reinterpret_cast<const int4*>(sbuf + (s * kEpiRows + r) * kEpiChunk + h * 512 + lane * 16);
+                            if (p.weighted) accumulate_bf16x8_scaled(acc, raw, wt);
+                            else accumulate_bf16x8(acc, raw);
+                        }
+                    }
                     const int off = cc * kEpiChunk + h * 512 + lane * 16;
                     if (b0 != nullptr) accumulate_bf16x8(acc, ld_nc_int4(b0 + off));
                     if (b1 != nullptr) accumulate_bf16x8(acc, ld_nc_int4(b1 + off));
@@ -236,12 +287,16 @@ __global__ void __launch_bounds__(kEpiWarps * 32) combine_epilogue_kernel(const 
         }
         if (!staged_ok) reduce_token_registers(p, t, e, lane);     // redo this token the slow way; later tokens skip the staging
     }
+    __syncthreads();
+    if (threadIdx.x == 0) atomicMax(reinterpret_cast<unsigned long long*>(timeline + 1), static_cast<unsigned long long>(globaltimer_ns()));
 }
 
-// kFused: with the reduce of the receive side (more registers per thread; compiled apart so that the plain send
-// kernel does not pay for it)
-template <bool kFused>
+// kMode 0: plain send. 1: senders raise arrival flags (a reduce kernel beside this one consumes them). 2: flags and
+// the reduce inside this kernel (more registers per thread; compiled apart so that the plain send kernel does not
+// pay for it).
+template <int kMode>
 __global__ void __launch_bounds__(1024, 1) combine_kernel(const __grid_constant__ Multi<CombineParams> m) {
+    constexpr bool kFlags = kMode >= 1, kFused = kMode == 2;
     extern __shared__ __align__(128) uint8_t smem[];
     const int vr = blockIdx.x / m.blocks_per_rank;
     const int bid = blockIdx.x % m.blocks_per_rank;
@@ -255,6 +310,10 @@ __global__ void __launch_bounds__(1024, 1) combine_kernel(const __grid_constant_
     const bool is_sender = warp < num_warps && bid < nb_send;
     const int R = c.num_ranks, K = p.num_topk;
     uint64_t* my_ctl = reinterpret_cast<uint64_t*>(c.heap[c.rank]);
+    uint64_t* timeline = reinterpret_cast<uint64_t*>(reinterpret_cast<uint8_t*>(c.local_ws) + kWsTimelineOffsetBytes) + 2 * kTlCombine;
+    if (bid == 0 && tid == 0) timeline[0] = globaltimer_ns();
+    // every block of this grid is running: a reduce kernel launched as programmatic dependent may take the free SMs
+    launch_dependents();
 
     const int stage = align_up(p.row_bytes, 128) + 16;
     uint8_t* buf = smem + static_cast<size_t>(is_sender ? warp : 0) * stage;
@@ -288,7 +347,7 @@ __global__ void __launch_bounds__(1024, 1) combine_kernel(const __grid_constant_
     };
     int pend0 = -1, pend1 = -1, pend2 = -1;       // flag groups of the last three rows sent (oldest first)
     auto row_sent = [&](int row) {               // after bulk_commit of the row's only store
-        if (!kFused) return;
+        if (!kFlags) return;
         bulk_wait<3>();
         if (pend0 >= 0) chunk_row_landed(pend0);
         pend0 = pend1;
@@ -296,7 +355,7 @@ __global__ void __launch_bounds__(1024, 1) combine_kernel(const __grid_constant_
         pend2 = row / kCombineFlagRows;
     };
     auto flush_sent = [&]() {
-        if (!kFused) return;
+        if (!kFlags) return;
         bulk_wait_all();
         if (pend0 >= 0) chunk_row_landed(pend0);
         if (pend1 >= 0) chunk_row_landed(pend1);
@@ -399,12 +458,18 @@ __global__ void __launch_bounds__(1024, 1) combine_kernel(const __grid_constant_
                         rows[r] = k < 0 ? -1 : row;
                     }
                     int4 raw[4];
+                    float wt[4];
 #pragma unroll
-                    for (int r = 0; r < 4; ++r)
+                    for (int r = 0; r < 4; ++r) {
                         if (rows[r] >= 0) raw[r] = ld_nc_int4(p.x + static_cast<int64_t>(rows[r]) * p.x_stride_bytes + v * 16);
+                        wt[r] = (p.weighted && rows[r] >= 0) ? p.topk_weights[rows[r]] : 1.f;
+                    }
 #pragma unroll
                     for (int r = 0; r < 4; ++r)
-                        if (rows[r] >= 0) accumulate_bf16x8(acc, raw[r]);
+                        if (rows[r] >= 0) {
+                            if (p.weighted) accumulate_bf16x8_scaled(acc, raw[r], wt[r]);
+                            else accumulate_bf16x8(acc, raw[r]);
+                        }
                 }
                 reinterpret_cast<int4*>(buf)[v] = pack_bf16x8(acc);
             }
@@ -448,7 +513,7 @@ __global__ void __launch_bounds__(1024, 1) combine_kernel(const __grid_constant_
                 }
             }
             if (failed) fatal = true;
-            if (lane == 0 && kFused) {     // several stores per token: settle all of them, then count the token
+            if (lane == 0 && kFlags) {     // several stores per token: settle all of them, then count the token
                 flush_sent();
                 chunk_row_landed(i / kCombineFlagRows);
             }
@@ -499,6 +564,7 @@ __global__ void __launch_bounds__(1024, 1) combine_kernel(const __grid_constant_
         const uint64_t* word = my_ctl + kCtlCombineDone + tid;
         bounded_wait(w, kStatusCombineDone, tid, 0, [&]() { return epoch_reached(ld_acquire_sys_u64(word), p.epoch); });
     }
+    if (tid == 0) atomicMax(reinterpret_cast<unsigned long long*>(timeline + 1), static_cast<unsigned long long>(globaltimer_ns()));
 }
 
 }  // namespace
@@ -510,15 +576,15 @@ bool plan_combine(const CombineParams& p, int num_sms, int smem_optin, CombineLa
     if (warps < 1) return false;
     out->num_sms = num_sms;
     out->num_warps = warps;
-    out->num_reduce_warps = p.fuse_reduce ? 32 - warps : 0;
+    out->num_reduce_warps = p.fuse_reduce == 2 ? 32 - warps : 0;
     out->smem_bytes = warps * stage;
     return true;
 }
 
 cudaError_t launch_combine(const Multi<CombineParams>& m, const CombineLaunch& l, cudaStream_t stream) {
-    const bool fused = m.r[0].fuse_reduce != 0;
-    cudaError_t err = cudaFuncSetAttribute(fused ? combine_kernel<true> : combine_kernel<false>,
-                                           cudaFuncAttributeMaxDynamicSharedMemorySize, l.smem_bytes);
+    const int mode = m.r[0].fuse_reduce;
+    void (*kernel)(const Multi<CombineParams>) = mode == 2 ? combine_kernel<2> : (mode == 1 ? combine_kernel<1> : combine_kernel<0>);
+    cudaError_t err = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, l.smem_bytes);
     if (err != cudaSuccess) return err;
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3(m.num_vranks * m.blocks_per_rank);
@@ -534,18 +600,28 @@ cudaError_t launch_combine(const Multi<CombineParams>& m, const CombineLaunch& l
     for (int v = 0; v < copy.num_vranks; ++v) copy.r[v].num_send_warps = l.num_warps;
     // blocks_per_rank counts the reduce-only blocks too
 
-    return fused ? cudaLaunchKernelEx(&cfg, combine_kernel<true>, copy) : cudaLaunchKernelEx(&cfg, combine_kernel<false>, copy);
+    return cudaLaunchKernelEx(&cfg, kernel, copy);
 }
 
-cudaError_t launch_combine_epilogue(const CombineEpilogueParams* params, int num_vranks, int num_sms, cudaStream_t stream) {
+cudaError_t launch_combine_epilogue(const CombineEpilogueParams* params, int num_vranks, int num_sms, cudaStream_t stream,
+                                    bool programmatic) {
     Multi<CombineEpilogueParams> m;
     m.num_vranks = num_vranks;
     m.blocks_per_rank = num_sms;
     for (int v = 0; v < num_vranks; ++v) m.r[v] = params[v];
     cudaError_t err = cudaFuncSetAttribute(combine_epilogue_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kEpiSmem);
     if (err != cudaSuccess) return err;
-    combine_epilogue_kernel<<<num_vranks * num_sms, kEpiWarps * 32, kEpiSmem, stream>>>(m);
-    return cudaGetLastError();
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(num_vranks * num_sms);
+    cfg.blockDim = dim3(kEpiWarps * 32);
+    cfg.dynamicSmemBytes = kEpiSmem;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = programmatic ? 1 : 0;
+    return cudaLaunchKernelEx(&cfg, combine_epilogue_kernel, m);
 }
 
 }  // namespace ep

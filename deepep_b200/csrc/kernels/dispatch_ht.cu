@@ -12,19 +12,24 @@
 //                communication, the first row of its own tokens in each destination's receive
 //                region and in each expert's segment of the expanded (expert-major) layout
 //   C. send      one warp per token: bulk-load the row into shared memory, optionally cast it
-//                to e4m3 with 1x128 scales, build the meta row, and bulk-store payload and
-//                meta straight to row `slot` of every destination rank's receive region
-//                (peer pointers over NVLink; plain 1-D bulk copies, never multicast)
-//   D. finish    wait for the stores, tell every peer "my rows have landed", wait for theirs.
+//                to e4m3 with 1x128 scales, append scales and routing words behind the payload,
+//                and bulk-store the whole record -- ONE store per destination rank -- straight
+//                to record `slot` of that rank's receive region (peer pointers over NVLink;
+//                plain 1-D bulk copies, never multicast)
+//   D. finish    wait for the own stores; the last block to get there tells every peer "my rows
+//                have landed". Nobody waits for the peers here: that wait opens the epilogue.
 //
-// Rows arrive grouped by source rank in token order, i.e. already in the order of the
-// non-expanded output: with zero copy the receive region IS recv_x. The epilogue kernel at
-// the bottom only unpacks the small meta rows, and moves payload rows when the caller wants
-// tensors of its own or the expanded layout.
+// Records arrive grouped by source rank in token order, i.e. already in the order of the
+// non-expanded output: with zero copy the payload column of the receive region IS recv_x (a
+// strided view) and the scale column is recv_sf. The epilogue kernel at the bottom is launched
+// with programmatic stream serialization, so its blocks are resident before the dispatch
+// kernel has drained; it waits for the peers' completion words, unpacks the routing words and
+// moves payload rows only when the caller wants tensors of its own or the expanded layout.
 //
-// Parity: deep_ep/include/deep_ep/impls/dispatch.cuh:17-409 (notify + dispatch warps) and
-// impls/dispatch_copy_epilogue.cuh:11-323 of the reference; the fused cast follows the
-// arithmetic of csrc/kernels/legacy/internode_ll.cu:212-249.
+// Parity: deep_ep/include/deep_ep/impls/dispatch.cuh:17-409 (notify + dispatch warps, one bulk
+// store of hidden + SF + metadata per destination at :371-379, programmatic launch of the
+// epilogue at :403) and impls/dispatch_copy_epilogue.cuh:11-323 of the reference; the fused
+// cast follows the arithmetic of csrc/kernels/legacy/internode_ll.cu:212-249.
 #include "api.hpp"
 #include "../common/device_utils.cuh"
 
@@ -35,24 +40,19 @@ namespace {
 constexpr int kCntStride = kMaxRanks + kMaxExperts;   // words per source rank in the count matrix
 constexpr int kTotOffset = (kMaxBlocks - 1) * (kMaxRanks + kMaxExperts);   // last row of the per-block scratch: totals
 
+// Per-warp staging buffer: [input row][meta as assembled][mbarrier]. Without the fused cast the
+// meta sits right behind the payload, so the buffer front IS the record. With the cast the e4m3
+// row overwrites the front of the bf16 row (see quantize_row) and the meta is then copied to
+// the end of the e4m3 row.
 struct StageLayout {
-    int src_off, out_off, meta_off, bar_off, bytes;
+    int meta_off, bar_off, bytes;
 };
 
-__host__ __device__ inline StageLayout stage_layout(int src_row_bytes, int x_row_bytes, int meta_bytes, bool quant) {
+__host__ __device__ inline StageLayout stage_layout(int src_row_bytes, int meta_bytes) {
     StageLayout s;
-    // With the fused cast the e4m3 row overwrites the front of the bf16 row (see quantize_row),
-    // so payload and cast share one buffer.
-    (void)x_row_bytes;
-    (void)quant;
-    s.src_off = 0;
-    int off = align_up(src_row_bytes, 128);
-    s.out_off = 0;
-    s.meta_off = off;
-    off += align_up(meta_bytes, 16);
-    s.bar_off = off;
-    off += 16;
-    s.bytes = align_up(off, 128);
+    s.meta_off = src_row_bytes;                       // rows are multiples of 16 bytes
+    s.bar_off = align_up(s.meta_off + meta_bytes, 16);
+    s.bytes = align_up(s.bar_off + 16, 128);
     return s;
 }
 
@@ -60,10 +60,16 @@ __host__ __device__ inline int header_bytes(int num_experts) {
     return align_up((3 * kMaxRanks + 2 * num_experts) * 4, 128);
 }
 
+// shared memory the ordering pass (A1) needs for one tile of 32 tokens with a single counting warp
+__host__ __device__ inline int order_scratch_min_bytes(int num_experts, int num_topk, int num_ranks) {
+    return 2 * (num_experts + kMaxRanks) * 4 + 32 * (num_topk + num_ranks) * 4;
+}
+
 // bf16 row in shared memory -> e4m3 row + one float scale per 128 channels. `out` may alias
 // `src`: a step covers channels [base, base + 1024), reads bytes [2*base, 2*base + 2048) and
 // writes bytes [base, base + 1024), which only earlier steps have read, and the lanes of a step
 // have all loaded (the shuffles of the reduction are past) before any of them stores.
+// `scales` must not overlap the row.
 __device__ __forceinline__ void quantize_row(const uint8_t* src, uint8_t* out, float* scales, int hidden, bool pow2, int lane) {
     constexpr int kUnroll = 4;   // independent 256-channel steps in flight per lane (hides shuffle / divide latency)
     for (int base = 0; base < hidden; base += 256 * kUnroll) {
@@ -102,6 +108,7 @@ __device__ __forceinline__ void quantize_row(const uint8_t* src, uint8_t* out, f
 
 __global__ void __launch_bounds__(1024, 1) dispatch_kernel(const __grid_constant__ Multi<DispatchParams> m) {
     extern __shared__ __align__(128) uint8_t smem[];
+    __shared__ int s_last;
     const int vr = blockIdx.x / m.blocks_per_rank;
     const int bid = blockIdx.x % m.blocks_per_rank;
     const int nb = m.blocks_per_rank;
@@ -112,6 +119,7 @@ __global__ void __launch_bounds__(1024, 1) dispatch_kernel(const __grid_constant
     const int num_warps = nthreads >> 5;
     const int R = c.num_ranks, E = p.num_experts, K = p.num_topk, T = p.num_tokens, EL = p.num_local_experts;
     const int CW = R + E;
+    const bool idx32 = p.idx32 != 0;
 
     int* s_rank_base = reinterpret_cast<int*>(smem);   // [kMaxRanks] first row of this block's tokens per destination
     int* s_recv_from = s_rank_base + kMaxRanks;         // [kMaxRanks] tokens this rank receives per source
@@ -128,11 +136,16 @@ __global__ void __launch_bounds__(1024, 1) dispatch_kernel(const __grid_constant
     int* steal_next = reinterpret_cast<int*>(reinterpret_cast<uint8_t*>(c.local_ws) + kWsStealOffsetBytes);   // [nb]
     uint32_t* steal_ready = reinterpret_cast<uint32_t*>(steal_next + kMaxBlocks);                               // [nb]
     int* steal_base = reinterpret_cast<int*>(steal_ready + kMaxBlocks);                                          // [nb][CW]
+    uint64_t* timeline = reinterpret_cast<uint64_t*>(reinterpret_cast<uint8_t*>(c.local_ws) + kWsTimelineOffsetBytes) + 2 * kTlDispatch;
     bool ok = true;
-    // phase timestamps of block 0 (ns, %globaltimer): start, counted, exchanged, sent, finished
+    // phase timestamps of block 0 (ns, %globaltimer), see kWsStamps
     uint64_t* stamps = c.local_ws + kWsStamps;
     const bool stamper = bid == 0 && tid == 0;
-    if (stamper) stamps[0] = globaltimer_ns();
+    if (stamper) {
+        const uint64_t now = globaltimer_ns();
+        stamps[0] = now;
+        timeline[0] = now;
+    }
 
     if (!p.cached) {
         // ------------------------------------------------------------ A0. count
@@ -147,10 +160,10 @@ __global__ void __launch_bounds__(1024, 1) dispatch_kernel(const __grid_constant
             uint32_t mask = 0;
             if (t < t1) {
                 for (int k = 0; k < K; ++k) {
-                    const int64_t raw = p.topk_idx[static_cast<int64_t>(t) * K + k];
-                    if (raw >= 0 && raw < E) {
-                        atomicAdd(s_exp_tot + static_cast<int>(raw), 1);
-                        mask |= 1u << (static_cast<int>(raw) / EL);
+                    const int e = load_topk_idx(p.topk_idx, idx32, static_cast<int64_t>(t) * K + k, E);
+                    if (e >= 0) {
+                        atomicAdd(s_exp_tot + e, 1);
+                        mask |= 1u << (e / EL);
                     }
                 }
             }
@@ -184,13 +197,14 @@ __global__ void __launch_bounds__(1024, 1) dispatch_kernel(const __grid_constant
                     st_relaxed_sys_u64(remote, word);
                 }
             }
+            // counts of the earlier blocks: 32 independent loads in flight per round
             int before = 0;
-            for (int b0 = 0; b0 < bid; b0 += 8) {
-                int v[8];
+            for (int b0 = 0; b0 < bid; b0 += 32) {
+                int v[32];
 #pragma unroll
-                for (int u = 0; u < 8; ++u) v[u] = (b0 + u < bid) ? __ldcg(blk_cnt + (b0 + u) * CW + j) : 0;
+                for (int u = 0; u < 32; ++u) v[u] = (b0 + u < bid) ? __ldcg(blk_cnt + (b0 + u) * CW + j) : 0;
 #pragma unroll
-                for (int u = 0; u < 8; ++u) before += v[u];
+                for (int u = 0; u < 32; ++u) before += v[u];
             }
             if (j < R) s_rank_base[j] = before; else s_exp_base[j - R] = before;
         }
@@ -200,13 +214,13 @@ __global__ void __launch_bounds__(1024, 1) dispatch_kernel(const __grid_constant
         // (token, rank) and (token, expert) pairs among its own earlier tokens, a prefix over the
         // warps turns that into positions inside the block. Everything is in token order, so the
         // result does not depend on timing.
-        const StageLayout sl0 = stage_layout(p.src_row_bytes, p.x_row_bytes, p.meta_bytes, p.quant_mode != kQuantNone);
-        const int scratch_bytes = num_warps * sl0.bytes;
-        int cw = min(num_warps, 16);
-        while (cw > 1 && cw * (E + kMaxRanks) * 4 > scratch_bytes / 2) --cw;
+        const int scratch_bytes = p.smem_scratch_bytes;
+        int cw = num_warps;
+        while (cw > 1 && (cw * (E + kMaxRanks) * 4 > scratch_bytes / 2 || scratch_bytes - cw * (E + kMaxRanks) * 4 < 32 * (K + R) * 4)) --cw;
         int* s_wcnt = reinterpret_cast<int*>(s_bufs);          // [cw][E]  per-warp expert counters, then bases
         int* s_wrank = s_wcnt + cw * E;                         // [cw][kMaxRanks]
         int* s_idx = s_wrank + cw * kMaxRanks;                  // [cap_tokens][K]
+        // (the launcher guarantees room for at least one tile of 32 tokens)
         const int cap_tokens = max(32, ((scratch_bytes - cw * (E + kMaxRanks) * 4) / ((K + R) * 4)) & ~31);
         int* s_slot = s_idx + cap_tokens * K;                   // [cap_tokens][R]
         __syncthreads();
@@ -218,10 +232,8 @@ __global__ void __launch_bounds__(1024, 1) dispatch_kernel(const __grid_constant
             const int n_pairs = n_tok * K;
             const int tpw = ceil_div(n_tok, cw);
             __syncthreads();
-            for (int i = tid; i < n_pairs; i += nthreads) {
-                const int64_t raw = p.topk_idx[static_cast<int64_t>(tile0) * K + i];
-                s_idx[i] = (raw >= 0 && raw < E) ? static_cast<int>(raw) : -1;
-            }
+            for (int i = tid; i < n_pairs; i += nthreads)
+                s_idx[i] = load_topk_idx(p.topk_idx, idx32, static_cast<int64_t>(tile0) * K + i, E);
             for (int i = tid; i < cw * E; i += nthreads) s_wcnt[i] = 0;
             __syncthreads();
             if (warp < cw) {
@@ -297,6 +309,7 @@ __global__ void __launch_bounds__(1024, 1) dispatch_kernel(const __grid_constant
             }
         }
         __syncthreads();
+        if (stamper) stamps[2] = globaltimer_ns();
         // ------------------------------------------------------------ B'. the peers' totals -> first rows
         for (int j = tid; j < CW; j += nthreads) {
             const int col = j < R ? j : kMaxRanks + (j - R);
@@ -321,6 +334,7 @@ __global__ void __launch_bounds__(1024, 1) dispatch_kernel(const __grid_constant
                     tot += cnt;
                     if (s < c.rank) pre += cnt;
                     if (j == c.rank) s_recv_from[s] = cnt;
+                    if (j < R && bid == 0 && p.count_matrix != nullptr) p.count_matrix[s * R + j] = cnt;
                 }
             }
             if (j < R) {
@@ -331,6 +345,7 @@ __global__ void __launch_bounds__(1024, 1) dispatch_kernel(const __grid_constant
             }
         }
         ok = !__syncthreads_or(!ok);
+        if (stamper) stamps[3] = globaltimer_ns();
         if (ok) {
             // First row of every expert's segment on its rank (alignment applied): one warp per
             // destination rank runs an exclusive scan over that rank's experts. The warp that scans
@@ -399,15 +414,15 @@ __global__ void __launch_bounds__(1024, 1) dispatch_kernel(const __grid_constant
         ok = !__syncthreads_or(!ok);
     }
 
-    if (stamper) stamps[2] = globaltimer_ns();
+    if (stamper) stamps[4] = globaltimer_ns();
     // ---------------------------------------------------------------- C. send
     const bool quant = p.quant_mode != kQuantNone;
-    const StageLayout sl = stage_layout(p.src_row_bytes, p.x_row_bytes, p.meta_bytes, quant);
-    uint8_t* my = s_bufs + static_cast<size_t>(warp) * sl.bytes;
-    uint8_t* buf_src = my + sl.src_off;
-    uint8_t* buf_out = quant ? my + sl.out_off : buf_src;
-    uint8_t* buf_meta = my + sl.meta_off;
-    uint64_t* bar = reinterpret_cast<uint64_t*>(my + sl.bar_off);
+    const StageLayout sl = stage_layout(p.src_row_bytes, p.meta_bytes);
+    uint8_t* buf = s_bufs + static_cast<size_t>(warp) * sl.bytes;      // input row; its front becomes the record
+    uint8_t* buf_meta = buf + sl.meta_off;                              // meta as assembled
+    uint8_t* rec_meta = buf + p.x_row_bytes;                            // meta inside the record (== buf_meta without the cast)
+    uint64_t* bar = reinterpret_cast<uint64_t*>(buf + sl.bar_off);
+    const int rec_bytes = p.x_row_bytes + p.meta_bytes;
     if (ok) {
         if (lane == 0) {
             mbar_init(bar, 1);
@@ -425,7 +440,6 @@ __global__ void __launch_bounds__(1024, 1) dispatch_kernel(const __grid_constant
         // split would leave the fast ones idle. Every chunk has a counter; a block serves its own chunk
         // first and then walks the other chunks, taking whatever tokens are left there.
         int victim = bid, v_t0 = t0, v_t1 = t1;
-        constexpr int visited_base = 0;
         int t_local = 0;
         if (lane == 0) t_local = atomicAdd(steal_next + victim, 1);
         t_local = __shfl_sync(0xffffffffu, t_local, 0);
@@ -436,14 +450,14 @@ __global__ void __launch_bounds__(1024, 1) dispatch_kernel(const __grid_constant
                 // 32 at a time, and take a token from the first one that still has some.
                 int found = -1;
                 for (int off = 1; off < nb && found < 0; off += 32) {
-                    const int cand = (bid + visited_base + off + lane) % nb;
+                    const int cand = (bid + off + lane) % nb;
                     bool has = false;
                     if (off + lane < nb) {
                         const int c0 = min(T, cand * chunk), c1 = min(T, c0 + chunk);
                         has = c0 + __ldcg(steal_next + cand) < c1;
                     }
                     const uint32_t bal = __ballot_sync(0xffffffffu, has);
-                    if (bal != 0) found = (bid + visited_base + off + (__ffs(bal) - 1)) % nb;
+                    if (bal != 0) found = (bid + off + (__ffs(bal) - 1)) % nb;
                 }
                 if (found < 0) { victim = -1; break; }
                 victim = found;
@@ -463,11 +477,11 @@ __global__ void __launch_bounds__(1024, 1) dispatch_kernel(const __grid_constant
             const bool foreign = victim != bid;
             int fetched = 0;
             if (lane == 0) fetched = atomicAdd(steal_next + victim, 1);   // next index, read at the end of the step
-            bulk_wait_read_all();   // the previous stores of every lane have read the buffers
+            bulk_wait_read_all();   // the previous stores of every lane have read the buffer
             __syncwarp();
             if (lane == 0) {
                 mbar_arrive_expect_tx(bar, p.src_row_bytes + (sf_bulk ? p.sf_bytes : 0));
-                bulk_g2s(buf_src, p.x + static_cast<int64_t>(t) * p.x_stride_bytes, p.src_row_bytes, bar);
+                bulk_g2s(buf, p.x + static_cast<int64_t>(t) * p.x_stride_bytes, p.src_row_bytes, bar);
                 if (sf_bulk) bulk_g2s(buf_meta, p.sf + static_cast<int64_t>(t) * p.sf_token_stride * 4, p.sf_bytes, bar);
             }
             int slot = -1;
@@ -480,8 +494,7 @@ __global__ void __launch_bounds__(1024, 1) dispatch_kernel(const __grid_constant
             }
             if (lane < K) {
                 const int64_t pi = static_cast<int64_t>(t) * K + lane;
-                const int64_t raw = p.topk_idx[pi];
-                const int e = (raw >= 0 && raw < E) ? static_cast<int>(raw) : -1;
+                const int e = load_topk_idx(p.topk_idx, idx32, pi, E);
                 int row = p.pair_row[pi];
                 if (!p.cached && e >= 0) {
                     row += foreign ? __ldcg(steal_base + victim * CW + R + e) : s_exp_base[e];
@@ -500,13 +513,16 @@ __global__ void __launch_bounds__(1024, 1) dispatch_kernel(const __grid_constant
             const bool landed = mbar_wait(w, bar, parity, kStatusTmaLoad, t);
             parity ^= 1;
             if (!__all_sync(0xffffffffu, landed)) break;
-            if (quant) quantize_row(buf_src, buf_out, reinterpret_cast<float*>(buf_meta), p.src_row_bytes / 2, p.quant_mode == kQuantE4M3Pow2, lane);
+            if (quant) {
+                quantize_row(buf, buf, reinterpret_cast<float*>(buf_meta), p.src_row_bytes / 2, p.quant_mode == kQuantE4M3Pow2, lane);
+                __syncwarp();       // every lane is done with the bf16 row: its tail may now take the meta
+                for (int i = lane; i < p.meta_bytes / 16; i += 32)
+                    reinterpret_cast<int4*>(rec_meta)[i] = reinterpret_cast<const int4*>(buf_meta)[i];
+            }
             fence_proxy_async_smem();
             __syncwarp();
             if (slot >= 0) {
-                uint8_t* heap = c.heap[lane];
-                bulk_s2g(heap + p.off_recv_x + static_cast<uint64_t>(slot) * p.x_row_bytes, buf_out, p.x_row_bytes);
-                bulk_s2g(heap + p.off_recv_meta + static_cast<uint64_t>(slot) * p.meta_bytes, buf_meta, p.meta_bytes);
+                bulk_s2g(c.heap[lane] + p.off_recv + static_cast<uint64_t>(slot) * p.rec_pitch, buf, rec_bytes);
                 bulk_commit();
             }
             t_local = __shfl_sync(0xffffffffu, fetched, 0);
@@ -514,40 +530,54 @@ __global__ void __launch_bounds__(1024, 1) dispatch_kernel(const __grid_constant
     }
 
     // ---------------------------------------------------------------- D. finish
+    if (stamper) stamps[5] = globaltimer_ns();
+    launch_dependents();          // the epilogue's blocks may become resident from here on
     bulk_wait_all();
     fence_proxy_async_all();
     __threadfence_system();
-    if (stamper) stamps[3] = globaltimer_ns();
-    grid_barrier(w, grid_counter, p.grid_bar_base + (p.cached ? 1 : 2) * static_cast<uint64_t>(nb), 2);
-    if (stamper) stamps[4] = globaltimer_ns();
-    if (bid == 0) {   // ready for the next launch (stream order)
-        for (int b = tid; b < nb; b += nthreads) steal_next[b] = 0;
-        if (!p.cached) {
-            int* tot_cnt = blk_cnt + kTotOffset;
-            for (int j = tid; j < CW; j += nthreads) tot_cnt[j] = 0;
-        }
+    if (stamper) stamps[6] = globaltimer_ns();
+    // The last block to arrive cleans up and tells the peers; nobody spins here.
+    __syncthreads();
+    if (tid == 0) {
+        const uint64_t target = p.grid_bar_base + (p.cached ? 1 : 2) * static_cast<uint64_t>(nb);
+        s_last = atom_add_acq_rel_gpu_u64(grid_counter, 1) + 1 == target;
     }
-    if (bid == 0 && tid < R) {
+    __syncthreads();
+    if (!s_last) return;
+    for (int b = tid; b < nb; b += nthreads) steal_next[b] = 0;      // ready for the next launch (stream order)
+    if (!p.cached) {
+        int* tot_cnt = blk_cnt + kTotOffset;
+        for (int j = tid; j < CW; j += nthreads) tot_cnt[j] = 0;
+    }
+    if (tid < R) {
         uint64_t* remote = reinterpret_cast<uint64_t*>(c.heap[tid]) + kCtlDispatchDone + c.rank;
         st_release_sys_u64(remote, pack_epoch(p.epoch, 0));
-        const uint64_t* word = my_ctl + kCtlDispatchDone + tid;
-        bounded_wait(w, kStatusDispatchDone, tid, 0, [&]() { return epoch_reached(ld_acquire_sys_u64(word), p.epoch); });
     }
-    if (stamper) stamps[5] = globaltimer_ns();
+    if (tid == 0) {
+        const uint64_t now = globaltimer_ns();
+        stamps[7] = now;
+        timeline[1] = now;
+    }
 }
 
 // ==================================================================== epilogue (local, all SMs)
+// 1. waits (bounded) until every peer has reported the rows of this dispatch as landed;
+// 2. routing words of all records -> recv_topk_idx (local expert ids), recv_topk_weights, recv_src_metadata,
+//    one thread per (record, top-k lane); scale factors -> recv_sf unless the caller reads them in place;
+// 3. payload rows -> recv_x[i] (own tensor) or to every expanded row of the token, one warp per record
+//    through shared memory (1-D bulk copies); skipped entirely for zero copy;
+// 4. zeroes the alignment gaps of the expanded layout when asked to.
 __global__ void __launch_bounds__(1024, 1) dispatch_epilogue_kernel(const __grid_constant__ Multi<DispatchEpilogueParams> m) {
     extern __shared__ __align__(128) uint8_t smem[];
     const int vr = blockIdx.x / m.blocks_per_rank;
     const int bid = blockIdx.x % m.blocks_per_rank;
     const int nb = m.blocks_per_rank;
     const DispatchEpilogueParams& p = m.r[vr];
-    const int lane = lane_id(), warp = warp_id();
-    const int num_warps = blockDim.x >> 5;
+    const int tid = threadIdx.x, nthreads = blockDim.x, lane = lane_id(), warp = warp_id();
+    const int num_warps = nthreads >> 5;
     const int R = p.num_ranks, K = p.num_topk, EL = p.num_local_experts;
-    const int N = p.psum_rank[R - 1];
     const bool move_rows = p.copy_x || p.do_expand;
+    uint64_t* timeline = reinterpret_cast<uint64_t*>(reinterpret_cast<uint8_t*>(p.c.local_ws) + kWsTimelineOffsetBytes) + 2 * kTlDispatchEpilogue;
 
     const int stage = align_up(p.x_row_bytes, 128) + 16;
     uint8_t* buf = smem + static_cast<size_t>(warp) * stage;
@@ -557,90 +587,109 @@ __global__ void __launch_bounds__(1024, 1) dispatch_epilogue_kernel(const __grid
         fence_mbar_init();
     }
     __syncwarp();
-    uint32_t parity = 0;
-    const int expert_begin = p.rank * EL;
+
+    dependency_wait();      // the dispatch kernel of this rank has completed (all its writes are visible)
+    if (bid == 0 && tid == 0) timeline[0] = globaltimer_ns();
+    const WaitCtx w = make_wait_ctx(p.c);
+    bool ok = true;
+    if (p.wait_done && tid < R) {
+        const uint64_t* word = reinterpret_cast<const uint64_t*>(p.c.heap[p.c.rank]) + kCtlDispatchDone + tid;
+        ok = bounded_wait(w, kStatusDispatchDone, tid, 0, [&]() { return epoch_reached(ld_acquire_sys_u64(word), p.epoch); });
+    }
+    ok = !__syncthreads_or(!ok);
+    if (!ok) return;        // the status word says why; the outputs stay as they are
+
+    const int N = min(p.psum_rank[R - 1], p.num_idx_rows);
+    const int expert_begin = p.c.rank * EL;
     const int sf_packs = p.sf_bytes / 4;
-    const int my_psum = lane < R ? p.psum_rank[lane] : 0x7fffffff;
+    const int64_t gtid = static_cast<int64_t>(bid) * nthreads + tid, gthreads = static_cast<int64_t>(nb) * nthreads;
+    const bool idx32 = p.idx32 != 0;
+    auto meta_of = [&](int i) { return reinterpret_cast<const int*>(p.region + static_cast<uint64_t>(i) * p.rec_pitch + p.x_row_bytes + p.sf_bytes); };
 
-    // the routing words of a row are loaded one iteration ahead, so their latency overlaps the stores of the row before
-    auto load_meta = [&](int i, int& e, float& wt, int& row, int& src_token) {
-        const int* meta_idx = reinterpret_cast<const int*>(p.region_meta + static_cast<uint64_t>(i) * p.meta_bytes + p.sf_bytes);
-        e = -1;
-        row = -1;
-        wt = 0.f;
-        if (lane < K) {
-            e = meta_idx[lane];
-            wt = reinterpret_cast<const float*>(meta_idx)[K + lane];
-            row = meta_idx[2 * K + lane];
+    // ---- 2. routing words, one thread per (record, lane); rows past the received count get -1 / 0
+    for (int64_t j = gtid; j < static_cast<int64_t>(p.num_idx_rows) * K; j += gthreads) {
+        const int i = static_cast<int>(j / K), k = static_cast<int>(j % K);
+        int local_e = -1, row = -1;
+        float wt = 0.f;
+        if (i < N) {
+            const int* mi = meta_of(i);
+            const int e = mi[k];
+            wt = reinterpret_cast<const float*>(mi)[K + k];
+            const bool local = e >= expert_begin && e < expert_begin + EL;
+            local_e = local ? e - expert_begin : -1;
+            if (p.do_expand && local) row = mi[2 * K + k];
+            if (row >= p.num_out_rows) row = -1;
+            if (p.write_metadata && k == 0) {
+                int first_local = 0;
+                for (int kk = K - 1; kk >= 0; --kk) {
+                    const int ee = mi[kk];
+                    if (ee >= expert_begin && ee < expert_begin + EL) first_local = kk;
+                }
+                int src_rank = 0;
+                for (int r = 0; r < R - 1; ++r) src_rank += i >= p.psum_rank[r];
+                int* md = p.recv_src_metadata + static_cast<int64_t>(i) * (K + 2);
+                md[0] = src_rank * p.num_max_tokens + mi[3 * K];
+                md[1] = src_rank * K + first_local;
+            }
+        } else if (p.write_metadata && k == 0) {
+            int* md = p.recv_src_metadata + static_cast<int64_t>(i) * (K + 2);
+            md[0] = -1;
+            md[1] = -1;
         }
-        src_token = meta_idx[3 * K];
-    };
-    const int first_row = bid * num_warps + warp, row_step = nb * num_warps;
-    int next_e = -1, next_row = -1, next_src_token = 0;
-    float next_wt = 0.f;
-    if (first_row < N) load_meta(first_row, next_e, next_wt, next_row, next_src_token);
+        if (!p.do_expand) {
+            if (p.recv_topk_idx != nullptr) {
+                if (idx32) reinterpret_cast<int*>(p.recv_topk_idx)[j] = local_e;
+                else reinterpret_cast<int64_t*>(p.recv_topk_idx)[j] = local_e;
+            }
+            if (p.recv_topk_weights != nullptr) p.recv_topk_weights[j] = wt;
+        } else if (row >= 0 && p.recv_topk_weights != nullptr) {
+            p.recv_topk_weights[row] = wt;
+        }
+        if (p.write_metadata) p.recv_src_metadata[static_cast<int64_t>(i) * (K + 2) + 2 + k] = row;
+    }
 
-    for (int i = first_row; i < N; i += row_step) {
-        if (move_rows) {
+    // ---- scale factors, one thread per (record, pack)
+    if (p.recv_sf != nullptr && sf_packs > 0) {
+        uint32_t* out = reinterpret_cast<uint32_t*>(p.recv_sf);
+        for (int64_t j = gtid; j < static_cast<int64_t>(N) * sf_packs; j += gthreads) {
+            const int i = static_cast<int>(j / sf_packs), k = static_cast<int>(j % sf_packs);
+            const uint32_t v = reinterpret_cast<const uint32_t*>(p.region + static_cast<uint64_t>(i) * p.rec_pitch + p.x_row_bytes)[k];
+            if (!p.do_expand) {
+                if (i < p.num_out_rows) out[static_cast<int64_t>(i) * p.recv_sf_row_stride + static_cast<int64_t>(k) * p.recv_sf_pack_stride] = v;
+            } else {
+                const int* mi = meta_of(i);
+                for (int kk = 0; kk < K; ++kk) {
+                    const int e = mi[kk];
+                    if (e < expert_begin || e >= expert_begin + EL) continue;
+                    const int row = mi[2 * K + kk];
+                    if (row >= 0 && row < p.num_out_rows)
+                        out[static_cast<int64_t>(row) * p.recv_sf_row_stride + static_cast<int64_t>(k) * p.recv_sf_pack_stride] = v;
+                }
+            }
+        }
+    }
+
+    // ---- 3. payload rows, one warp per record
+    if (move_rows) {
+        uint32_t parity = 0;
+        for (int i = bid * num_warps + warp; i < N; i += nb * num_warps) {
             bulk_wait_read_all();
             __syncwarp();
             if (lane == 0) {
                 mbar_arrive_expect_tx(bar, p.x_row_bytes);
-                bulk_g2s(buf, p.region_x + static_cast<uint64_t>(i) * p.x_row_bytes, p.x_row_bytes, bar);
+                bulk_g2s(buf, p.region + static_cast<uint64_t>(i) * p.rec_pitch, p.x_row_bytes, bar);
             }
-        }
-        const uint8_t* meta = p.region_meta + static_cast<uint64_t>(i) * p.meta_bytes;
-        const int e = next_e, src_token = next_src_token;
-        int row = next_row;
-        const float wt = next_wt;
-        if (i + row_step < N) load_meta(i + row_step, next_e, next_wt, next_row, next_src_token);
-        const bool local = e >= expert_begin && e < expert_begin + EL;
-        const int local_e = local ? e - expert_begin : -1;
-        if (!p.do_expand || !local) row = -1;
-        const uint32_t local_mask = __ballot_sync(0xffffffffu, local);
-        // source rank of row i: how many of the inclusive prefix sums it has passed (lane r holds psum_rank[r])
-        const int src_rank = __popc(__ballot_sync(0xffffffffu, lane < R - 1 && i >= my_psum));
-
-        if (!p.do_expand) {
-            if (lane < K) {
-                if (p.recv_topk_idx != nullptr) p.recv_topk_idx[static_cast<int64_t>(i) * K + lane] = local_e;
-                if (p.recv_topk_weights != nullptr) p.recv_topk_weights[static_cast<int64_t>(i) * K + lane] = wt;
+            int row = -1;
+            if (p.do_expand && lane < K) {
+                const int* mi = meta_of(i);
+                const int e = mi[lane];
+                if (e >= expert_begin && e < expert_begin + EL) row = mi[2 * K + lane];
             }
-            if (p.recv_sf != nullptr) {
-                const uint32_t* sf = reinterpret_cast<const uint32_t*>(meta);
-                for (int k = lane; k < sf_packs; k += 32)
-                    reinterpret_cast<uint32_t*>(p.recv_sf)[static_cast<int64_t>(i) * p.recv_sf_row_stride + k * p.recv_sf_pack_stride] = sf[k];
-            }
-        } else {
-            if (row >= 0 && p.recv_topk_weights != nullptr) p.recv_topk_weights[row] = wt;
-            if (p.recv_sf != nullptr) {
-                const uint32_t* sf = reinterpret_cast<const uint32_t*>(meta);
-                uint32_t todo = local_mask;
-                while (todo) {
-                    const int src_lane = __ffs(todo) - 1;
-                    todo &= todo - 1;
-                    const int out_row = __shfl_sync(0xffffffffu, row, src_lane);
-                    for (int k = lane; k < sf_packs; k += 32)
-                        reinterpret_cast<uint32_t*>(p.recv_sf)[static_cast<int64_t>(out_row) * p.recv_sf_row_stride + k * p.recv_sf_pack_stride] = sf[k];
-                }
-            }
-        }
-        if (p.write_metadata) {
-            int* md = p.recv_src_metadata + static_cast<int64_t>(i) * (K + 2);
-            if (lane == 0) {
-                md[0] = src_rank * p.num_max_tokens + src_token;
-                md[1] = src_rank * K + (local_mask ? __ffs(local_mask) - 1 : 0);
-            }
-            if (lane < K) md[2 + lane] = row;
-        }
-        if (move_rows) {
-            // no WaitCtx here: a local bulk load cannot miss, but keep the wait bounded all the same
-            bool landed = false;
-            for (int spin = 0; spin < (1 << 24) && !landed; ++spin) landed = mbar_try_wait(bar, parity);
+            const bool landed = mbar_wait(w, bar, parity, kStatusTmaLoad, i);
             parity ^= 1;
             if (!__all_sync(0xffffffffu, landed)) break;
             if (!p.do_expand) {
-                if (lane == 0) {
+                if (lane == 0 && i < p.num_out_rows) {
                     bulk_s2g(p.recv_x + static_cast<uint64_t>(i) * p.x_row_bytes, buf, p.x_row_bytes);
                     bulk_commit();
                 }
@@ -651,40 +700,46 @@ __global__ void __launch_bounds__(1024, 1) dispatch_epilogue_kernel(const __grid
         }
     }
 
-    // zero the alignment gaps of the expanded layout
+    // ---- 4. zero the alignment gaps of the expanded layout
     if (p.do_expand && p.do_zero_padding) {
         const int vec_per_row = p.x_row_bytes / 16;
         for (int le = bid; le < EL; le += nb) {
             const int begin = p.psum_expert[le];                               // start + real count
             const int end = min(align_up(begin, p.expert_alignment), p.num_out_rows);
-            for (int64_t v = static_cast<int64_t>(begin) * vec_per_row + threadIdx.x; v < static_cast<int64_t>(end) * vec_per_row; v += blockDim.x)
+            for (int64_t v = static_cast<int64_t>(begin) * vec_per_row + tid; v < static_cast<int64_t>(end) * vec_per_row; v += nthreads)
                 reinterpret_cast<int4*>(p.recv_x)[v] = make_int4(0, 0, 0, 0);
             if (p.recv_topk_weights != nullptr)
-                for (int r = begin + threadIdx.x; r < end; r += blockDim.x) p.recv_topk_weights[r] = 0.f;
+                for (int r = begin + tid; r < end; r += nthreads) p.recv_topk_weights[r] = 0.f;
             // the scales of the padding rows too: 0 x (whatever was in memory) would not be 0 for a NaN or an infinity
-            if (p.recv_sf != nullptr && p.sf_bytes > 0) {
-                const int packs = p.sf_bytes / 4;
-                for (int i = threadIdx.x; i < (end - begin) * packs; i += blockDim.x) {
-                    const int r = begin + i / packs, k = i % packs;
+            if (p.recv_sf != nullptr && sf_packs > 0) {
+                for (int i = tid; i < (end - begin) * sf_packs; i += nthreads) {
+                    const int r = begin + i / sf_packs, k = i % sf_packs;
                     reinterpret_cast<uint32_t*>(p.recv_sf)[static_cast<int64_t>(r) * p.recv_sf_row_stride + static_cast<int64_t>(k) * p.recv_sf_pack_stride] = 0u;
                 }
             }
         }
     }
     bulk_wait_all();
+    if (bid == 0 && tid == 0) timeline[1] = globaltimer_ns();
 }
 
 }  // namespace
 
 bool plan_dispatch(const DispatchParams& p, int num_sms, int smem_optin, DispatchLaunch* out) {
-    const StageLayout sl = stage_layout(p.src_row_bytes, p.x_row_bytes, p.meta_bytes, p.quant_mode != kQuantNone);
-    const int avail = smem_optin - header_bytes(p.num_experts);
+    const StageLayout sl = stage_layout(p.src_row_bytes, p.meta_bytes);
+    const int avail = smem_optin - header_bytes(p.num_experts) - 128;   // 128: static shared memory of the kernel
     int warps = avail / sl.bytes;
     if (warps > 32) warps = 32;
     if (warps < 2) return false;
+    // the ordering pass borrows the staging buffers: make sure one tile of routing words fits
+    const int need = order_scratch_min_bytes(p.num_experts, p.num_topk, p.c.num_ranks);
+    int scratch = warps * sl.bytes;
+    if (scratch < need) scratch = align_up(need, 128);
+    if (scratch > avail) return false;
     out->num_sms = num_sms;
     out->num_warps = warps;
-    out->smem_bytes = header_bytes(p.num_experts) + warps * sl.bytes;
+    out->scratch_bytes = scratch;
+    out->smem_bytes = header_bytes(p.num_experts) + scratch;
     return true;
 }
 
@@ -701,24 +756,36 @@ cudaError_t launch_dispatch(const Multi<DispatchParams>& m, const DispatchLaunch
     attr[0].val.cooperative = 1;
     cfg.attrs = attr;
     cfg.numAttrs = 1;
-    return cudaLaunchKernelEx(&cfg, dispatch_kernel, m);
+    Multi<DispatchParams> copy = m;
+    for (int v = 0; v < copy.num_vranks; ++v) copy.r[v].smem_scratch_bytes = l.scratch_bytes;
+    return cudaLaunchKernelEx(&cfg, dispatch_kernel, copy);
 }
 
 cudaError_t launch_dispatch_epilogue(const DispatchEpilogueParams* params, int num_vranks, int num_sms, int smem_optin,
-                                     cudaStream_t stream) {
+                                     cudaStream_t stream, bool programmatic) {
     Multi<DispatchEpilogueParams> m;
     m.num_vranks = num_vranks;
     m.blocks_per_rank = num_sms;
     for (int v = 0; v < num_vranks; ++v) m.r[v] = params[v];
+    const bool move_rows = params[0].copy_x || params[0].do_expand;
     const int stage = align_up(params[0].x_row_bytes, 128) + 16;
-    int warps = smem_optin / stage;
-    if (warps > 16) warps = 16;
+    int warps = move_rows ? smem_optin / stage : 32;
+    if (warps > (move_rows ? 16 : 32)) warps = move_rows ? 16 : 32;
     if (warps < 1) return cudaErrorInvalidValue;
-    const int smem_bytes = warps * stage;
+    const int smem_bytes = move_rows ? warps * stage : 0;
     cudaError_t err = cudaFuncSetAttribute(dispatch_epilogue_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_bytes);
     if (err != cudaSuccess) return err;
-    dispatch_epilogue_kernel<<<num_vranks * num_sms, warps * 32, smem_bytes, stream>>>(m);
-    return cudaGetLastError();
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(num_vranks * num_sms);
+    cfg.blockDim = dim3(warps * 32);
+    cfg.dynamicSmemBytes = smem_bytes;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = programmatic ? 1 : 0;
+    return cudaLaunchKernelEx(&cfg, dispatch_epilogue_kernel, m);
 }
 
 }  // namespace ep

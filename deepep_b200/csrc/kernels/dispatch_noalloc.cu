@@ -27,10 +27,10 @@ constexpr size_t a256(size_t v) { return (v + 255) / 256 * 256; }
 
 // carve-up of the scratch array (byte offsets, all 256-aligned)
 constexpr size_t kOffHeap = 0;                                            // control words of the one-rank "heap"
-constexpr size_t kOffRecvX = a256(kCtlWords * 8);                         // receive region, payload rows
-constexpr size_t kOffRecvMeta = kOffRecvX + a256(kMaxTokens * kMaxRowBytes);
-constexpr size_t kMetaMax = (kMaxRowBytes / 128 / 2) * 4 + 12 * kMaxTopkNA + 16;   // scales of an fp8 row + routing
-constexpr size_t kOffWs = kOffRecvMeta + a256(kMaxTokens * a256(kMetaMax));
+constexpr size_t kOffRecv = a256(kCtlWords * 8);                          // receive region: one record per token
+constexpr size_t kMetaMax = 12 * kMaxTopkNA + 16;                          // routing words of a record (no scale factors here)
+constexpr size_t kPitchMax = (kMaxRowBytes + kMetaMax + 127) / 128 * 128;
+constexpr size_t kOffWs = kOffRecv + a256(kMaxTokens * kPitchMax);
 constexpr size_t kOffTokenSlot = kOffWs + a256(kWsBytes);
 constexpr size_t kOffPairRow = kOffTokenSlot + a256(kMaxTokens * 4);
 constexpr size_t kOffPsumRank = kOffPairRow + a256(kMaxTokens * kMaxTopkNA * 4);
@@ -94,6 +94,10 @@ extern "C" int deepep_b200_dispatch_local_noalloc(const void* x, long long x_str
         psum_num_recv_per_expert == nullptr || num_recv_tokens == nullptr || expert_alignment < 1 ||
         x_stride_bytes % 16 != 0 || reinterpret_cast<uintptr_t>(x) % 16 != 0 || reinterpret_cast<uintptr_t>(recv_x) % 16 != 0)
         return DEEPEP_B200_NOALLOC_ERR_ARGUMENT;
+    // the output must hold the worst case: the kernels place rows by routing data and never look at the caller's sizes again
+    const long long rows_needed = do_expand ? static_cast<long long>(num_tokens) * num_topk + static_cast<long long>(num_experts) * (expert_alignment - 1)
+                                            : num_tokens;
+    if (num_recv_x_rows < rows_needed) return DEEPEP_B200_NOALLOC_ERR_ARGUMENT;
 
     std::lock_guard<std::mutex> lock(g_mutex);
     DeviceState* st = nullptr;
@@ -122,6 +126,9 @@ extern "C" int deepep_b200_dispatch_local_noalloc(const void* x, long long x_str
     p.x_row_bytes = row_bytes;
     p.sf_bytes = 0;
     p.meta_bytes = ht_meta_bytes(0, num_topk);
+    p.rec_pitch = ht_record_pitch(row_bytes, 0, num_topk);
+    p.idx32 = 0;
+    p.smem_scratch_bytes = 0;
     p.quant_mode = kQuantNone;
     p.expert_alignment = expert_alignment;
     p.do_expand = do_expand ? 1 : 0;
@@ -131,7 +138,7 @@ extern "C" int deepep_b200_dispatch_local_noalloc(const void* x, long long x_str
     p.sf = nullptr;
     p.sf_token_stride = 0;
     p.sf_pack_stride = 0;
-    p.topk_idx = reinterpret_cast<const int64_t*>(topk_idx);
+    p.topk_idx = topk_idx;
     p.topk_weights = topk_weights;
     p.token_slot = reinterpret_cast<int*>(s + kOffTokenSlot);
     p.pair_row = reinterpret_cast<int*>(s + kOffPairRow);
@@ -139,33 +146,38 @@ extern "C" int deepep_b200_dispatch_local_noalloc(const void* x, long long x_str
     p.psum_expert = psum_num_recv_per_expert;
     p.num_unaligned = reinterpret_cast<int*>(s + kOffUnaligned);
     p.recv_stats = nullptr;
-    p.off_recv_x = kOffRecvX;
-    p.off_recv_meta = kOffRecvMeta;
-    p.epoch = ++st->epoch;
+    p.count_matrix = nullptr;
+    p.off_recv = kOffRecv;
+    // the call counter and the barrier base move only once the launch has happened: a refused launch must not
+    // leave the host ahead of the device counters
+    p.epoch = st->epoch + 1;
     p.grid_bar_base = st->grid_bar_base;
     p.host_counts = nullptr;
-    st->grid_bar_base += 2ull * num_sms;
 
     DispatchLaunch launch;
     if (!plan_dispatch(p, num_sms, st->smem_optin, &launch)) return DEEPEP_B200_NOALLOC_ERR_ROW_BYTES;
     if (launch_dispatch(m, launch, stream) != cudaSuccess) return DEEPEP_B200_NOALLOC_ERR_CUDA;
+    st->epoch = p.epoch;
+    st->grid_bar_base += 2ull * num_sms;
 
     DispatchEpilogueParams q;
-    q.rank = 0;
+    q.c = p.c;
+    q.epoch = p.epoch;
+    q.wait_done = 1;
+    q.idx32 = 0;
+    q.rec_pitch = p.rec_pitch;
     q.num_ranks = 1;
     q.num_topk = num_topk;
     q.num_local_experts = num_experts;
     q.num_max_tokens = static_cast<int>(kMaxTokens);
     q.x_row_bytes = row_bytes;
     q.sf_bytes = 0;
-    q.meta_bytes = p.meta_bytes;
     q.do_expand = p.do_expand;
     q.copy_x = 1;
     q.expert_alignment = expert_alignment;
     q.do_zero_padding = 0;
     q.write_metadata = 1;
-    q.region_x = s + kOffRecvX;
-    q.region_meta = s + kOffRecvMeta;
+    q.region = s + kOffRecv;
     q.psum_rank = num_recv_tokens;
     q.psum_expert = psum_num_recv_per_expert;
     q.num_unaligned = p.num_unaligned;
@@ -173,11 +185,25 @@ extern "C" int deepep_b200_dispatch_local_noalloc(const void* x, long long x_str
     q.recv_sf = nullptr;
     q.recv_sf_row_stride = 0;
     q.recv_sf_pack_stride = 0;
-    q.recv_topk_idx = do_expand ? nullptr : reinterpret_cast<int64_t*>(recv_topk_idx);
+    q.recv_topk_idx = do_expand ? nullptr : static_cast<void*>(recv_topk_idx);
     q.recv_topk_weights = recv_topk_weights;
     q.recv_src_metadata = recv_src_metadata;
     q.num_out_rows = num_recv_x_rows;
+    q.num_idx_rows = num_tokens;
     if (launch_dispatch_epilogue(&q, 1, st->num_sms, st->smem_optin, stream) != cudaSuccess) return DEEPEP_B200_NOALLOC_ERR_CUDA;
+    return DEEPEP_B200_NOALLOC_OK;
+}
+
+extern "C" int deepep_b200_noalloc_reset(void) {
+    std::lock_guard<std::mutex> lock(g_mutex);
+    DeviceState* st = nullptr;
+    if (state_for_current_device(&st) != cudaSuccess) return DEEPEP_B200_NOALLOC_ERR_CUDA;
+    if (cudaDeviceSynchronize() != cudaSuccess) return DEEPEP_B200_NOALLOC_ERR_CUDA;
+    // private workspace (barrier counter, poison word, hand-out counters) and the status word start over; the
+    // control words keep their call tags, so the call counter goes on
+    if (cudaMemset(st->scratch + kOffWs, 0, kWsBytes) != cudaSuccess) return DEEPEP_B200_NOALLOC_ERR_CUDA;
+    if (cudaMemset(st->scratch + kOffStatus, 0, 256) != cudaSuccess) return DEEPEP_B200_NOALLOC_ERR_CUDA;
+    st->grid_bar_base = 0;
     return DEEPEP_B200_NOALLOC_OK;
 }
 

@@ -43,7 +43,10 @@
  * bookkeeping is protected by a mutex; that does not order the kernels.
  *
  * Errors. The kernels never trap. If one of their bounded waits runs out they record a status
- * word in the scratch array; deepep_b200_noalloc_status() copies it out (0 = healthy).
+ * word in the scratch array; deepep_b200_noalloc_status() copies it out (0 = healthy). A
+ * non-zero status is sticky: from then on every wait of later calls on that device falls
+ * through at once and their outputs are not to be trusted. Once the cause is gone,
+ * deepep_b200_noalloc_reset() waits for the device and clears the status and the counters.
  */
 #ifndef DEEPEP_B200_DISPATCH_NOALLOC_H_
 #define DEEPEP_B200_DISPATCH_NOALLOC_H_
@@ -60,7 +63,7 @@
 #define DEEPEP_B200_NOALLOC_ERR_ROW_BYTES 2  /* row_bytes beyond the maximum or not a multiple of 16 */
 #define DEEPEP_B200_NOALLOC_ERR_TOPK 3
 #define DEEPEP_B200_NOALLOC_ERR_EXPERTS 4
-#define DEEPEP_B200_NOALLOC_ERR_ARGUMENT 5   /* null / misaligned pointer, bad alignment value */
+#define DEEPEP_B200_NOALLOC_ERR_ARGUMENT 5   /* null / misaligned pointer, bad alignment value, recv_x with too few rows */
 #define DEEPEP_B200_NOALLOC_ERR_CUDA 6       /* a CUDA call failed (cudaGetLastError has the reason) */
 
 #ifdef __cplusplus
@@ -81,7 +84,8 @@ size_t deepep_b200_noalloc_scratch_bytes(void);
  *   topk_weights       [num_tokens, num_topk] float, or NULL
  * outputs
  *   recv_x             [num_recv_x_rows] rows of `row_bytes`; needs num_tokens rows (do_expand = 0) or
- *                      num_tokens * num_topk + num_experts * (expert_alignment - 1) rows (do_expand = 1)
+ *                      num_tokens * num_topk + num_experts * (expert_alignment - 1) rows (do_expand = 1);
+ *                      fewer rows are refused with DEEPEP_B200_NOALLOC_ERR_ARGUMENT
  *   recv_topk_idx      [num_tokens, num_topk] int64 (do_expand = 0; may be NULL)
  *   recv_topk_weights  [num_tokens, num_topk] (do_expand = 0) or [num_recv_x_rows] (do_expand = 1); may be NULL
  *   recv_src_metadata  [num_tokens, num_topk + 2] int32: {source token, first used lane, row per lane or -1}
@@ -98,6 +102,10 @@ int deepep_b200_dispatch_local_noalloc(const void* x, long long x_stride_bytes, 
 /* Copies the status word of the current device to *record (0 = no wait has ever run out).
  * Synchronises with the device. */
 int deepep_b200_noalloc_status(unsigned long long* record);
+
+/* After a non-zero status: waits for the device, then clears the status word and the counters
+ * in the scratch array of the current device so that later calls work again. Allocates nothing. */
+int deepep_b200_noalloc_reset(void);
 
 #ifdef __cplusplus
 }

@@ -33,6 +33,7 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
     m.attr("HEAP_ALIGNMENT") = static_cast<int64_t>(kHeapAlignment);
     m.attr("CONTROL_BYTES") = static_cast<int64_t>(kCtlBytes);
 
+
     py::class_<EventHandle>(m, "EventHandle")
         .def(py::init<>())
         .def("current_stream_wait", &EventHandle::current_stream_wait);
@@ -60,6 +61,7 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
         .def_readwrite("do_zero_padding", &DispatchArgs::do_zero_padding)
         .def_readwrite("do_cpu_sync", &DispatchArgs::do_cpu_sync)
         .def_readwrite("zero_copy", &DispatchArgs::zero_copy)
+        .def_readwrite("num_worst_tokens", &DispatchArgs::num_worst_tokens)
         .def_readwrite("col_major_sf", &DispatchArgs::col_major_sf)
         .def_readwrite("cached", &DispatchArgs::cached)
         .def_readwrite("h_token_slot", &DispatchArgs::h_token_slot)
@@ -83,6 +85,7 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
         .def_readonly("psum_expert", &DispatchResult::psum_expert)
         .def_readonly("num_unaligned", &DispatchResult::num_unaligned)
         .def_readonly("recv_src_metadata", &DispatchResult::recv_src_metadata)
+        .def_readonly("count_matrix", &DispatchResult::count_matrix)
         .def_readonly("num_recv_tokens", &DispatchResult::num_recv_tokens)
         .def_readonly("num_expanded_tokens", &DispatchResult::num_expanded_tokens)
         .def_readonly("num_sms", &DispatchResult::num_sms)
@@ -103,6 +106,7 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
         .def_readwrite("num_sms", &CombineArgs::num_sms)
         .def_readwrite("do_expand", &CombineArgs::do_expand)
         .def_readwrite("allow_multiple_reduction", &CombineArgs::allow_multiple_reduction)
+        .def_readwrite("weighted", &CombineArgs::weighted)
         .def_readwrite("dst_slot", &CombineArgs::dst_slot)
         .def_readwrite("fuse_reduce", &CombineArgs::fuse_reduce)
         .def_readwrite("num_reduce_sms", &CombineArgs::num_reduce_sms)
@@ -132,6 +136,7 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
         .def("num_kernel_launches", &Runtime::num_kernel_launches)
         .def("last_timings", &Runtime::last_timings)
         .def("last_dispatch_phases", &Runtime::last_dispatch_phases)
+        .def("last_timeline", &Runtime::last_timeline)
         .def("rank", &Runtime::rank)
         .def("num_ranks", &Runtime::num_ranks)
         .def("num_bytes", &Runtime::num_bytes)
@@ -143,9 +148,13 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
             return std::make_tuple(static_cast<int64_t>(s.id()), static_cast<int64_t>(s.device_index()),
                                    static_cast<int64_t>(s.device_type()));
         })
-        .def_static("barrier", &Runtime::barrier, py::arg("runtimes"), py::arg("use_comm_stream") = true, py::arg("with_cpu_sync") = false)
-        .def_static("dispatch", &Runtime::dispatch)
-        .def_static("combine", &Runtime::combine)
+        // The drivers may block on the host for a long time (the wait for the received counts, a stream
+        // synchronisation): they run without the GIL so that Python threads of this process -- the heartbeat of the
+        // failure detector among them -- keep running meanwhile.
+        .def_static("barrier", &Runtime::barrier, py::arg("runtimes"), py::arg("use_comm_stream") = true, py::arg("with_cpu_sync") = false,
+                    py::call_guard<py::gil_scoped_release>())
+        .def_static("dispatch", &Runtime::dispatch, py::call_guard<py::gil_scoped_release>())
+        .def_static("combine", &Runtime::combine, py::call_guard<py::gil_scoped_release>())
         .def_static("ht_buffer_size", &Runtime::ht_buffer_size);
 
     register_extra_bindings(m);

@@ -32,6 +32,11 @@ const char* status_name(int code) {
     }
 }
 
+bool env_flag(const char* name) {
+    const char* v = std::getenv(name);
+    return v != nullptr && v[0] != '\0' && v[0] != '0';
+}
+
 // Everything the stream-control arguments ask for before the first launch.
 struct StreamScope {
     at::cuda::CUDAStream compute, comm;
@@ -50,8 +55,16 @@ struct StreamScope {
         std::optional<EventHandle> event;
         if (sc.async_with_compute_stream) {
             event = EventHandle(comm);
+            // EP_AVOID_RECORD_STREAM=1: the event keeps the tensors alive instead (the caller holds the event until it
+            // has waited on it); record_stream delays the reuse of a block by the caching allocator in a way that is
+            // hard to predict (csrc/elastic/buffer.hpp:556-584 of the reference offers the same switch).
+            static const bool avoid_record_stream = env_flag("EP_AVOID_RECORD_STREAM");
             for (const auto& t : tensors) {
                 if (!t.defined() || !t.is_cuda()) continue;
+                if (avoid_record_stream) {
+                    event->keep_alive.push_back(t);
+                    continue;
+                }
                 // (views of the heap are not owned by the caching allocator; record_stream ignores them)
                 t.record_stream(comm);
                 if (sc.allocate_on_comm_stream) t.record_stream(compute);
@@ -85,6 +98,7 @@ Runtime::Runtime(int rank, int num_ranks, int64_t num_bytes, double gpu_timeout_
     cudaDeviceProp prop;
     CUDA_RUNTIME_CHECK(cudaGetDeviceProperties(&prop, heap_->device()));
     num_device_sms_ = prop.multiProcessorCount;
+    use_pdl_ = !env_flag("EP_DISABLE_PDL");
     smem_optin_ = static_cast<int>(prop.sharedMemPerBlockOptin);
     CUDA_RUNTIME_CHECK(cudaDeviceSynchronize());
 }
@@ -102,30 +116,43 @@ void Runtime::destroy() {
     host_words_ = nullptr;
 }
 
-void Runtime::enable_profiling(bool on) {
-    if (on && prof_events_[0] == nullptr)
+void Runtime::enable_profiling(int mode) {
+    EP_HOST_ASSERT(mode >= 0 && mode <= 2);
+    if (mode != 0 && prof_events_[0] == nullptr)
         for (auto& e : prof_events_) CUDA_RUNTIME_CHECK(cudaEventCreate(&e));
-    profiling_ = on;
+    profiling_ = mode;
     prof_valid_[0] = prof_valid_[1] = false;
 }
 
 std::vector<float> Runtime::last_timings() {
-    std::vector<float> out(4, -1.f);
+    std::vector<float> out(6, -1.f);
     for (int op = 0; op < 2; ++op) {
         if (!prof_valid_[op]) continue;
         CUDA_RUNTIME_CHECK(cudaEventSynchronize(prof_events_[3 * op + 2]));
-        CUDA_RUNTIME_CHECK(cudaEventElapsedTime(&out[2 * op], prof_events_[3 * op], prof_events_[3 * op + 1]));
-        CUDA_RUNTIME_CHECK(cudaEventElapsedTime(&out[2 * op + 1], prof_events_[3 * op + 1], prof_events_[3 * op + 2]));
+        CUDA_RUNTIME_CHECK(cudaEventElapsedTime(&out[4 + op], prof_events_[3 * op], prof_events_[3 * op + 2]));
+        if (prof_split_[op]) {
+            CUDA_RUNTIME_CHECK(cudaEventElapsedTime(&out[2 * op], prof_events_[3 * op], prof_events_[3 * op + 1]));
+            CUDA_RUNTIME_CHECK(cudaEventElapsedTime(&out[2 * op + 1], prof_events_[3 * op + 1], prof_events_[3 * op + 2]));
+        }
     }
     return out;
 }
 
 std::vector<int64_t> Runtime::last_dispatch_phases() {
     CUDA_RUNTIME_CHECK(cudaDeviceSynchronize());
-    uint64_t raw[6];
+    uint64_t raw[8];
     CUDA_RUNTIME_CHECK(cudaMemcpy(raw, local_ws_ + kWsStamps, sizeof(raw), cudaMemcpyDeviceToHost));
     std::vector<int64_t> out;
-    for (int i = 1; i < 6; ++i) out.push_back(static_cast<int64_t>(raw[i] - raw[0]));
+    for (int i = 1; i < 8; ++i) out.push_back(static_cast<int64_t>(raw[i] - raw[0]));
+    return out;
+}
+
+std::vector<int64_t> Runtime::last_timeline() {
+    CUDA_RUNTIME_CHECK(cudaDeviceSynchronize());
+    uint64_t raw[8];
+    CUDA_RUNTIME_CHECK(cudaMemcpy(raw, reinterpret_cast<uint8_t*>(local_ws_) + kWsTimelineOffsetBytes, sizeof(raw), cudaMemcpyDeviceToHost));
+    std::vector<int64_t> out;
+    for (int i = 0; i < 8; ++i) out.push_back(raw[i] == 0 ? -1 : static_cast<int64_t>(raw[i] - raw[0]));
     return out;
 }
 
@@ -228,12 +255,16 @@ std::vector<DispatchResult> Runtime::dispatch(const std::vector<std::shared_ptr<
     EP_HOST_ASSERT_MSG(src_row_bytes % 16 == 0 && x_row_bytes % 16 == 0, "hidden bytes must be a multiple of 16");
     EP_HOST_ASSERT(sf_bytes <= ceil_div(H, 128) * 4);
     const int meta_bytes = ht_meta_bytes(sf_bytes, K);
+    const int rec_pitch = ht_record_pitch(x_row_bytes, sf_bytes, K);
     const HtLayout lay = ht_layout(R, T_max, H, K);
     EP_HOST_ASSERT_MSG(lay.end <= rt0.heap_->num_bytes(), "symmetric buffer too small for this dispatch");
     const at::ScalarType out_dtype = quant ? at::kFloat8_e4m3fn : a0.x.scalar_type();
+    const at::ScalarType idx_dtype = a0.topk_idx->scalar_type();
+    EP_HOST_ASSERT_MSG(idx_dtype == at::kLong || idx_dtype == at::kInt, "topk_idx must be int64 or int32");
     const bool has_sf = sf_packs > 0;
     const bool cached = a0.cached;
-    int num_sms = a0.num_sms > 0 ? a0.num_sms : 24;
+    EP_HOST_ASSERT_MSG(a0.num_sms > 0, "num_sms must be given (the Python front end fills in the SM model's value)");
+    int num_sms = a0.num_sms;
     if (num_sms * V > rt0.num_device_sms_) num_sms = rt0.num_device_sms_ / V;
 
     Multi<DispatchParams> m;
@@ -246,7 +277,7 @@ std::vector<DispatchResult> Runtime::dispatch(const std::vector<std::shared_ptr<
         EP_HOST_ASSERT(rt.heap_->connected() && rt.num_ranks_ == R);
         EP_HOST_ASSERT(a.x.dim() == 2 && a.x.is_cuda() && a.x.size(1) == H && a.x.stride(1) == 1 && a.x.scalar_type() == a0.x.scalar_type());
         EP_HOST_ASSERT((a.x.stride(0) * elem) % 16 == 0 && reinterpret_cast<uintptr_t>(a.x.data_ptr()) % 16 == 0);
-        EP_HOST_ASSERT(a.topk_idx.has_value() && a.topk_idx->scalar_type() == at::kLong && a.topk_idx->is_contiguous() && a.topk_idx->size(1) == K);
+        EP_HOST_ASSERT(a.topk_idx.has_value() && a.topk_idx->scalar_type() == idx_dtype && a.topk_idx->is_contiguous() && a.topk_idx->size(1) == K);
         const int T = static_cast<int>(a.x.size(0));
         EP_HOST_ASSERT(T <= T_max && a.topk_idx->size(0) == T);
         EP_HOST_ASSERT(a.num_experts == E && a.num_max_tokens == T_max && a.cached == cached && a.do_expand == a0.do_expand &&
@@ -267,16 +298,19 @@ std::vector<DispatchResult> Runtime::dispatch(const std::vector<std::shared_ptr<
         p.x_row_bytes = x_row_bytes;
         p.sf_bytes = sf_bytes;
         p.meta_bytes = meta_bytes;
+        p.rec_pitch = rec_pitch;
         p.quant_mode = a.quant_mode;
         p.expert_alignment = a.expert_alignment;
         p.do_expand = a.do_expand;
         p.cached = cached;
+        p.idx32 = idx_dtype == at::kInt ? 1 : 0;
+        p.smem_scratch_bytes = 0;    // filled in by the launcher
         p.x = static_cast<const uint8_t*>(a.x.data_ptr());
         p.x_stride_bytes = a.x.stride(0) * elem;
         p.sf = (has_sf && !quant) ? static_cast<const uint8_t*>(a.sf->data_ptr()) : nullptr;
         p.sf_token_stride = (has_sf && !quant) ? a.sf->stride(0) : 0;
         p.sf_pack_stride = (has_sf && !quant) ? a.sf->stride(1) : 0;
-        p.topk_idx = a.topk_idx->data_ptr<int64_t>();
+        p.topk_idx = a.topk_idx->data_ptr();
         p.topk_weights = a.topk_weights.has_value() ? a.topk_weights->data_ptr<float>() : nullptr;
         auto& r = res[v];
         if (cached) {
@@ -295,6 +329,7 @@ std::vector<DispatchResult> Runtime::dispatch(const std::vector<std::shared_ptr<
             r.psum_rank = at::empty({R}, opts(at::kInt, device));
             r.psum_expert = at::empty({EL + 1}, opts(at::kInt, device));
             r.num_unaligned = at::empty({EL}, opts(at::kInt, device));
+            r.count_matrix = at::empty({R, R}, opts(at::kInt, device));
         }
         p.token_slot = r.token_slot.data_ptr<int>();
         p.pair_row = r.pair_row.data_ptr<int>();
@@ -302,16 +337,15 @@ std::vector<DispatchResult> Runtime::dispatch(const std::vector<std::shared_ptr<
         p.psum_expert = r.psum_expert.data_ptr<int>();
         p.num_unaligned = r.num_unaligned.data_ptr<int>();
         p.recv_stats = nullptr;
+        p.count_matrix = r.count_matrix.defined() ? r.count_matrix.data_ptr<int>() : nullptr;
         if (a.cumulative_stats.has_value()) {
             EP_HOST_ASSERT(a.cumulative_stats->scalar_type() == at::kInt && a.cumulative_stats->numel() == EL && a.cumulative_stats->is_contiguous());
             p.recv_stats = a.cumulative_stats->data_ptr<int>();
         }
-        p.epoch = ++rt.dispatch_epoch;
-        const int slot = p.epoch & 1;
-        p.off_recv_x = lay.dispatch_x[slot];
-        p.off_recv_meta = lay.dispatch_meta[slot];
+        // the counters of the runtime move only once the launch has happened (below)
+        p.epoch = rt.dispatch_epoch + 1;
+        p.off_recv = lay.dispatch_rec[p.epoch & 1];
         p.grid_bar_base = rt.grid_bar_base;
-        rt.grid_bar_base += static_cast<uint64_t>(cached ? 1 : 2) * num_sms;
         p.host_counts = (a.do_cpu_sync && !cached) ? rt.host_words_dev_ + kHostStatusWords : nullptr;
     }
 
@@ -319,8 +353,14 @@ std::vector<DispatchResult> Runtime::dispatch(const std::vector<std::shared_ptr<
     EP_HOST_ASSERT_MSG(plan_dispatch(m.r[0], num_sms, rt0.smem_optin_, &launch), "a token row does not fit into shared memory");
     rt0.prof_record(0, stream);
     CUDA_RUNTIME_CHECK(launch_dispatch(m, launch, stream));
+    for (int v = 0; v < V; ++v) {
+        ++rts[v]->dispatch_epoch;
+        rts[v]->grid_bar_base += static_cast<uint64_t>(cached ? 1 : 2) * num_sms;
+    }
     ++rt0.num_launches_;
-    rt0.prof_record(1, stream);
+    // an event between the two launches would serialise them (no programmatic overlap): only in split mode
+    const bool split = rt0.profiling_ == 2;
+    if (split) rt0.prof_record(1, stream);
 
     // ---- sizes of the outputs
     const int worst_rows = R * T_max;
@@ -354,7 +394,8 @@ std::vector<DispatchResult> Runtime::dispatch(const std::vector<std::shared_ptr<
             r.num_recv_tokens_per_expert_list.resize(EL);
             for (int le = 0; le < EL; ++le) r.num_recv_tokens_per_expert_list[le] = wait_word(2 + le);
         } else {
-            r.num_recv_tokens = worst_rows;
+            r.num_recv_tokens = a.num_worst_tokens > 0 ? a.num_worst_tokens : worst_rows;
+            EP_HOST_ASSERT_MSG(r.num_recv_tokens <= worst_rows, "num_worst_tokens exceeds ranks x num_max_tokens_per_rank");
             r.num_expanded_tokens = worst_expanded;
         }
     }
@@ -370,18 +411,27 @@ std::vector<DispatchResult> Runtime::dispatch(const std::vector<std::shared_ptr<
         const int N = r.num_recv_tokens;
         const int rows = a.do_expand ? r.num_expanded_tokens : N;
         const bool zero_copy = a.zero_copy && !a.do_expand;
+        uint8_t* region = rt.heap_->base() + p.off_recv;
+        bool sf_in_place = false;
         if (zero_copy) {
-            r.recv_x = at::from_blob(rt.heap_->base() + p.off_recv_x, {N, H}, opts(out_dtype, device));
+            // payload (and row-major scales) are read where they landed: strided views of the receive region
+            r.recv_x = at::from_blob(region, {N, H}, {rec_pitch / static_cast<int64_t>(c10::elementSize(out_dtype)), 1}, opts(out_dtype, device));
         } else {
             r.recv_x = at::empty({rows, H}, opts(out_dtype, device));
         }
         if (has_sf) {
             const at::ScalarType sf_dtype = (!quant && a.sf->scalar_type() == at::kInt) ? at::kInt : at::kFloat;
-            if (a.col_major_sf) r.recv_sf = at::empty_strided({rows, sf_packs}, {1, align_up(std::max(rows, 1), 4)}, opts(sf_dtype, device));
-            else r.recv_sf = at::empty({rows, sf_packs}, opts(sf_dtype, device));
+            if (a.col_major_sf) {
+                r.recv_sf = at::empty_strided({rows, sf_packs}, {1, align_up(std::max(rows, 1), 4)}, opts(sf_dtype, device));
+            } else if (zero_copy) {
+                r.recv_sf = at::from_blob(region + x_row_bytes, {N, sf_packs}, {rec_pitch / 4, 1}, opts(sf_dtype, device));
+                sf_in_place = true;
+            } else {
+                r.recv_sf = at::empty({rows, sf_packs}, opts(sf_dtype, device));
+            }
         }
         if (!a.do_expand) {
-            r.recv_topk_idx = at::empty({N, K}, opts(at::kLong, device));
+            r.recv_topk_idx = at::empty({N, K}, opts(idx_dtype, device));
             if (a.topk_weights.has_value()) r.recv_topk_weights = at::empty({N, K}, opts(at::kFloat, device));
         } else if (a.topk_weights.has_value()) {
             r.recv_topk_weights = at::empty({rows}, opts(at::kFloat, device));
@@ -389,44 +439,51 @@ std::vector<DispatchResult> Runtime::dispatch(const std::vector<std::shared_ptr<
         if (!cached) r.recv_src_metadata = at::empty({N, K + 2}, opts(at::kInt, device));
 
         DispatchEpilogueParams& q = ep[v];
-        q.rank = rt.rank_;
+        q.c = p.c;
+        q.epoch = p.epoch;
+        q.wait_done = 1;
         q.num_ranks = R;
         q.num_topk = K;
         q.num_local_experts = EL;
         q.num_max_tokens = T_max;
         q.x_row_bytes = x_row_bytes;
         q.sf_bytes = sf_bytes;
-        q.meta_bytes = meta_bytes;
+        q.rec_pitch = rec_pitch;
         q.do_expand = a.do_expand;
         q.copy_x = zero_copy ? 0 : 1;
         q.expert_alignment = a.expert_alignment;
         q.do_zero_padding = a.do_zero_padding;
         q.write_metadata = cached ? 0 : 1;
-        q.region_x = rt.heap_->base() + p.off_recv_x;
-        q.region_meta = rt.heap_->base() + p.off_recv_meta;
+        q.idx32 = p.idx32;
+        q.region = region;
         q.psum_rank = p.psum_rank;
         q.psum_expert = p.psum_expert;
         q.num_unaligned = p.num_unaligned;
         q.recv_x = static_cast<uint8_t*>(r.recv_x.data_ptr());
-        q.recv_sf = has_sf ? static_cast<uint8_t*>(r.recv_sf->data_ptr()) : nullptr;
+        q.recv_sf = (has_sf && !sf_in_place) ? static_cast<uint8_t*>(r.recv_sf->data_ptr()) : nullptr;
         q.recv_sf_row_stride = has_sf ? r.recv_sf->stride(0) : 0;
         q.recv_sf_pack_stride = has_sf ? r.recv_sf->stride(1) : 0;
-        q.recv_topk_idx = r.recv_topk_idx.has_value() ? r.recv_topk_idx->data_ptr<int64_t>() : nullptr;
+        q.recv_topk_idx = r.recv_topk_idx.has_value() ? r.recv_topk_idx->data_ptr() : nullptr;
         q.recv_topk_weights = r.recv_topk_weights.has_value() ? r.recv_topk_weights->data_ptr<float>() : nullptr;
         q.recv_src_metadata = r.recv_src_metadata.data_ptr<int>();
         q.num_out_rows = rows;
+        q.num_idx_rows = static_cast<int>(r.recv_src_metadata.size(0));
         for (const at::Tensor& t : {r.recv_x, r.token_slot, r.pair_row, r.psum_rank, r.psum_expert, r.num_unaligned, r.recv_src_metadata,
                                     a.x, *a.topk_idx})
             touched.push_back(t);
         for (const auto& t : {r.recv_sf, r.recv_topk_idx, r.recv_topk_weights, a.sf, a.topk_weights, a.cumulative_stats})
             if (t.has_value()) touched.push_back(*t);
     }
-    if (a0.sc.previous_event_before_epilogue.has_value()) a0.sc.previous_event_before_epilogue->stream_wait(scope.comm);
+    const bool gated = a0.sc.previous_event_before_epilogue.has_value();
+    if (gated) a0.sc.previous_event_before_epilogue->stream_wait(scope.comm);
     const int epi_sms = std::max(1, rt0.num_device_sms_ / V);
-    CUDA_RUNTIME_CHECK(launch_dispatch_epilogue(ep.data(), V, epi_sms, rt0.smem_optin_, stream));
+    // programmatic dependent launch: the epilogue's blocks get resident while the dispatch kernel drains
+    CUDA_RUNTIME_CHECK(launch_dispatch_epilogue(ep.data(), V, epi_sms, rt0.smem_optin_, stream,
+                                                /*programmatic=*/!gated && !split && rt0.use_pdl_));
     ++rt0.num_launches_;
     rt0.prof_record(2, stream);
-    rt0.prof_valid_[0] = rt0.profiling_;
+    rt0.prof_valid_[0] = rt0.profiling_ != 0;
+    rt0.prof_split_[0] = split;
 
     auto event = scope.finish(a0.sc, touched);
     for (auto& r : res) r.event = event;
@@ -453,18 +510,27 @@ std::vector<CombineResult> Runtime::combine(const std::vector<std::shared_ptr<Ru
     EP_HOST_ASSERT_MSG(lay.end <= rt0.heap_->num_bytes(), "symmetric buffer too small for this combine");
     const bool rank_layout = !a0.do_expand || a0.allow_multiple_reduction;
     const int num_lanes = std::max(R, K);
-    int num_sms = a0.num_sms > 0 ? a0.num_sms : 24;
+    const at::ScalarType idx_dtype = a0.topk_idx.scalar_type();
+    EP_HOST_ASSERT_MSG(idx_dtype == at::kLong || idx_dtype == at::kInt, "topk_idx must be int64 or int32");
+    EP_HOST_ASSERT_MSG(a0.num_sms > 0, "num_sms must be given (the Python front end fills in the handle's value)");
+    int num_sms = a0.num_sms;
     if (num_sms * V > rt0.num_device_sms_) num_sms = rt0.num_device_sms_ / V;
-    // Optional: the reduce inside the send kernel. Measured on 8 x B200 it loses to the separate reduce kernel
-    // (a warp per token needs the parallelism of all SMs to reach memory speed), so it is opt-in.
-    bool fuse = a0.fuse_reduce != 0 && !a0.sc.previous_event_before_epilogue.has_value();
-    for (const auto& a : args) fuse = fuse && a.dst_slot.has_value();
+    const bool gated = a0.sc.previous_event_before_epilogue.has_value();
+    const bool split = rt0.profiling_ == 2;
     // One rank: every token has at most one row (rank layout), so the send kernel can write the result itself.
-    bool direct = R == 1 && rank_layout && !fuse && !a0.sc.previous_event_before_epilogue.has_value();
+    bool direct = R == 1 && rank_layout && !gated && !(a0.weighted && a0.do_expand);
     for (const auto& a : args) direct = direct && !a.bias0.has_value() && !a.bias1.has_value();
-    int num_reduce_sms = fuse ? std::max(0, a0.num_reduce_sms) : 0;
+    // Reduce mode: 1 = arrival flags + the reduce kernel beside the send kernel (default with peers), 2 = reduce inside
+    // the send kernel (opt-in), 0 = the reduce kernel after the send kernel.
+    int mode = direct ? 0 : a0.fuse_reduce;
+    for (const auto& a : args) if (!a.dst_slot.has_value()) mode = 0;
+    if (gated && mode != 0) mode = 0;
+    EP_HOST_ASSERT(mode >= 0 && mode <= 2);
+    int num_reduce_sms = mode == 2 ? std::max(0, a0.num_reduce_sms) : 0;
     if ((num_sms + num_reduce_sms) * V > rt0.num_device_sms_) num_reduce_sms = rt0.num_device_sms_ / V - num_sms;
     const int num_blocks = num_sms + num_reduce_sms;
+    const bool weighted = a0.weighted && a0.do_expand;
+    if (weighted) EP_HOST_ASSERT_MSG(a0.topk_weights.has_value(), "a weighted combine needs the top-k weights of the expanded rows");
 
     Multi<CombineParams> m;
     m.num_vranks = V;
@@ -479,8 +545,8 @@ std::vector<CombineResult> Runtime::combine(const std::vector<std::shared_ptr<Ru
         EP_HOST_ASSERT(a.x.dim() == 2 && a.x.is_cuda() && a.x.size(1) == H && a.x.stride(1) == 1 && a.x.scalar_type() == at::kBFloat16);
         EP_HOST_ASSERT((a.x.stride(0) * 2) % 16 == 0 && reinterpret_cast<uintptr_t>(a.x.data_ptr()) % 16 == 0);
         EP_HOST_ASSERT(a.recv_src_metadata.scalar_type() == at::kInt && a.recv_src_metadata.is_contiguous() && a.recv_src_metadata.size(1) == K + 2);
-        EP_HOST_ASSERT(a.topk_idx.scalar_type() == at::kLong && a.topk_idx.is_contiguous());
-        EP_HOST_ASSERT(a.do_expand == a0.do_expand && a.num_max_tokens == T_max && a.num_experts == E);
+        EP_HOST_ASSERT(a.topk_idx.scalar_type() == idx_dtype && a.topk_idx.is_contiguous());
+        EP_HOST_ASSERT(a.do_expand == a0.do_expand && a.num_max_tokens == T_max && a.num_experts == E && a.weighted == a0.weighted);
         const int T = static_cast<int>(a.topk_idx.size(0));
         if (a.topk_weights.has_value()) {
             EP_HOST_ASSERT(a.topk_weights->scalar_type() == at::kFloat && a.topk_weights->is_contiguous());
@@ -495,19 +561,19 @@ std::vector<CombineResult> Runtime::combine(const std::vector<std::shared_ptr<Ru
         p.do_expand = a.do_expand;
         p.num_lanes = num_lanes;
         p.use_rank_layout = rank_layout;
+        p.weighted = weighted ? 1 : 0;
         p.x = static_cast<const uint8_t*>(a.x.data_ptr());
         p.x_stride_bytes = a.x.stride(0) * 2;
         p.topk_weights = a.topk_weights.has_value() ? a.topk_weights->data_ptr<float>() : nullptr;
         p.recv_src_metadata = a.recv_src_metadata.data_ptr<int>();
         p.psum_rank = a.psum_rank.data_ptr<int>();
-        p.epoch = ++rt.combine_epoch;
+        // the counters of the runtime move only once the launch has happened (below)
+        p.epoch = rt.combine_epoch + 1;
         const int slot = p.epoch & 1;
         p.off_comb_x = lay.combine_x[slot];
         p.off_comb_w = lay.combine_w[slot];
         p.grid_bar_base = rt.grid_bar_base;
-        rt.grid_bar_base += num_blocks;
         p.num_send_blocks = num_sms;
-        p.direct_out = 0;            // decided below, once the biases are known
 
         auto& r = res[v];
         r.combined_x = at::empty({T, H}, opts(at::kBFloat16, device));
@@ -521,9 +587,11 @@ std::vector<CombineResult> Runtime::combine(const std::vector<std::shared_ptr<Ru
         q.hidden = H;
         q.num_lanes = num_lanes;
         q.use_rank_layout = rank_layout;
+        q.idx32 = idx_dtype == at::kInt ? 1 : 0;
+        q.weighted = (weighted && !rank_layout) ? 1 : 0;     // rank layout: the senders have applied the weights
         q.region_x = rt.heap_->base() + p.off_comb_x;
         q.region_w = a.topk_weights.has_value() ? reinterpret_cast<const float*>(rt.heap_->base() + p.off_comb_w) : nullptr;
-        q.topk_idx = a.topk_idx.data_ptr<int64_t>();
+        q.topk_idx = a.topk_idx.data_ptr();
         q.bias0 = nullptr;
         q.bias1 = nullptr;
         if (a.bias0.has_value()) {
@@ -536,19 +604,29 @@ std::vector<CombineResult> Runtime::combine(const std::vector<std::shared_ptr<Ru
         }
         q.combined_x = static_cast<uint8_t*>(r.combined_x.data_ptr());
         q.combined_topk_weights = r.combined_topk_weights.has_value() ? r.combined_topk_weights->data_ptr<float>() : nullptr;
-        p.fuse_reduce = fuse ? 1 : 0;
+        q.c = p.c;
+        q.epoch = p.epoch;
+        q.flags = nullptr;
+        q.flag_chunks = lay.combine_flag_chunks;
+        q.dst_slot = nullptr;
+        q.local_ws = rt.local_ws_;
+        p.fuse_reduce = mode;
         p.direct_out = direct ? 1 : 0;
         p.num_send_warps = 0;        // filled in by the launcher
         p.flag_chunks = lay.combine_flag_chunks;
         p.off_comb_flag = lay.combine_flag;
         p.dst_slot = nullptr;
-        p.red = q;
-        if (fuse) {
+        if (mode != 0) {
             EP_HOST_ASSERT(a.dst_slot->scalar_type() == at::kInt && a.dst_slot->is_contiguous() && a.dst_slot->dim() == 2 &&
                            a.dst_slot->size(0) == T && a.dst_slot->size(1) == R);
             p.dst_slot = a.dst_slot->data_ptr<int>();
             touched.push_back(*a.dst_slot);
+            if (mode == 1) {
+                q.flags = reinterpret_cast<const uint64_t*>(rt.heap_->base() + lay.combine_flag);
+                q.dst_slot = p.dst_slot;
+            }
         }
+        p.red = q;
         for (const at::Tensor& t : {r.combined_x, a.x, a.recv_src_metadata, a.topk_idx, a.psum_rank}) touched.push_back(t);
         for (const auto& t : {r.combined_topk_weights, a.topk_weights, a.bias0, a.bias1})
             if (t.has_value()) touched.push_back(*t);
@@ -557,16 +635,25 @@ std::vector<CombineResult> Runtime::combine(const std::vector<std::shared_ptr<Ru
     EP_HOST_ASSERT_MSG(plan_combine(m.r[0], num_blocks, rt0.smem_optin_, &launch), "a token row does not fit into shared memory");
     rt0.prof_record(3, stream);
     CUDA_RUNTIME_CHECK(launch_combine(m, launch, stream));
+    for (int v = 0; v < V; ++v) {
+        ++rts[v]->combine_epoch;
+        rts[v]->grid_bar_base += num_blocks;
+    }
     ++rt0.num_launches_;
-    rt0.prof_record(4, stream);
-    if (a0.sc.previous_event_before_epilogue.has_value()) a0.sc.previous_event_before_epilogue->stream_wait(scope.comm);
-    if (!fuse && !direct) {
-        const int epi_sms = std::max(1, rt0.num_device_sms_ / V);
-        CUDA_RUNTIME_CHECK(launch_combine_epilogue(ep.data(), V, epi_sms, stream));
+    if (split) rt0.prof_record(4, stream);
+    if (gated) a0.sc.previous_event_before_epilogue->stream_wait(scope.comm);
+    if (mode != 2 && !direct) {
+        // Flag-driven: the reduce runs beside the send kernel, on the SMs that kernel leaves free (it is launched as
+        // a programmatic dependent, so all send blocks are resident before the first reduce block starts).
+        const bool beside = mode == 1 && !split && rt0.use_pdl_;
+        const int free_sms = rt0.num_device_sms_ / V - num_sms;
+        const int epi_sms = beside && free_sms >= 8 ? free_sms : std::max(1, rt0.num_device_sms_ / V);
+        CUDA_RUNTIME_CHECK(launch_combine_epilogue(ep.data(), V, epi_sms, stream, beside));
         ++rt0.num_launches_;
     }
     rt0.prof_record(5, stream);
-    rt0.prof_valid_[1] = rt0.profiling_;
+    rt0.prof_valid_[1] = rt0.profiling_ != 0;
+    rt0.prof_split_[1] = split;
     auto event = scope.finish(a0.sc, touched);
     for (auto& r : res) r.event = event;
     return res;

@@ -56,6 +56,9 @@ struct DispatchArgs {
     std::optional<at::Tensor> sf, topk_idx, topk_weights, cumulative_stats;
     int num_experts = 0, num_max_tokens = 0, expert_alignment = 1, num_sms = 0, quant_mode = 0;
     bool do_expand = false, do_zero_padding = false, do_cpu_sync = true, zero_copy = false, col_major_sf = false;
+    // without CPU sync: rows of the outputs (0 = ranks x num_max_tokens); the routing outputs past the received
+    // count are filled with -1 / 0 (csrc/legacy/buffer.hpp:571-577 and intranode.cu:536-540 of the reference)
+    int num_worst_tokens = 0;
     // cached dispatch: tensors of an earlier handle
     bool cached = false;
     std::optional<at::Tensor> h_token_slot, h_pair_row, h_psum_rank, h_psum_expert, h_num_unaligned, h_recv_src_metadata;
@@ -67,6 +70,7 @@ struct DispatchResult {
     at::Tensor recv_x;
     std::optional<at::Tensor> recv_sf, recv_topk_idx, recv_topk_weights;
     at::Tensor token_slot, pair_row, psum_rank, psum_expert, num_unaligned, recv_src_metadata;
+    at::Tensor count_matrix;   // [R, R] tokens rank i sent to rank j (undefined for cached dispatches)
     int num_recv_tokens = 0, num_expanded_tokens = 0, num_sms = 0;
     std::vector<int> num_recv_tokens_per_expert_list;
     std::optional<EventHandle> event;
@@ -78,11 +82,12 @@ struct CombineArgs {
     at::Tensor recv_src_metadata, topk_idx, psum_rank;
     int num_experts = 0, num_max_tokens = 0, num_sms = 0;
     bool do_expand = false, allow_multiple_reduction = true;
+    bool weighted = false;     // expanded rows are multiplied by their top-k weight before they are summed
     // [T, R] row of every token in each destination's receive region (the dispatch handle has it). With it, and
-    // unless an event has to be awaited between send and reduce, the reduce runs inside the send kernel.
+    // unless an event has to be awaited between send and reduce, the reduce overlaps the sends.
     std::optional<at::Tensor> dst_slot;
-    int fuse_reduce = 0;       // non-zero: reduce inside the send kernel (opt-in)
-    int num_reduce_sms = 0;    // fused reduce: extra blocks that only reduce (on top of num_sms)
+    int fuse_reduce = 1;       // 1: flag-driven reduce kernel beside the send kernel, 2: reduce inside the send kernel, 0: after it
+    int num_reduce_sms = 0;    // fuse_reduce == 2: extra blocks that only reduce (on top of num_sms)
     StreamControl sc;
 };
 
@@ -122,13 +127,21 @@ public:
 
     // Optional device timing of the last dispatch / combine: events around the communication
     // kernel and around the local epilogue (what the reference reports as two separate kernels).
-    void enable_profiling(bool on);
+    // mode 1: events around each pair (kernel + epilogue; their overlap stays as in production). mode 2: also an event
+    // between the two launches, which serialises them: kernel-only figures as the reference reports them.
+    void enable_profiling(int mode);
     // kernels this runtime has launched so far (barrier, dispatch, combine and their epilogues)
     int64_t num_kernel_launches() const { return num_launches_; }
-    std::vector<float> last_timings();   // {dispatch kernel, dispatch epilogue, combine kernel, combine epilogue} in ms, -1 = not run
+    // {dispatch kernel, dispatch epilogue, combine kernel, combine epilogue, dispatch pair, combine pair} in ms,
+    // -1 = not measured (the first four need mode 2)
+    std::vector<float> last_timings();
+    // %globaltimer stamps of the last dispatch kernel, dispatch epilogue, combine send and combine reduce kernel:
+    // {start, end} each, ns relative to the start of the dispatch kernel (-1 = never ran). Synchronises the device.
+    std::vector<int64_t> last_timeline();
 
-    // Phase timestamps (ns) that block 0 of the last dispatch kernel wrote: start, counted, exchanged,
-    // send loop done (block 0), all blocks done, peers done. Synchronises the device.
+    // Phase timestamps (ns after kernel start) of the last dispatch kernel: totals counted, order pass done, peers'
+    // totals in, first rows published, block 0 out of tokens, its stores complete, last block done.
+    // Synchronises the device.
     std::vector<int64_t> last_dispatch_phases();
 
     // drivers
@@ -166,12 +179,14 @@ private:
     at::cuda::CUDAStream comm_stream_;
     int num_device_sms_ = 0, smem_optin_ = 0;
     bool destroyed_ = false;
-    bool profiling_ = false;
+    int profiling_ = 0;
+    bool use_pdl_ = true;
+    bool prof_split_[2] = {false, false};
     int64_t num_launches_ = 0;
     cudaEvent_t prof_events_[6] = {nullptr, nullptr, nullptr, nullptr, nullptr, nullptr};
     bool prof_valid_[2] = {false, false};
     void prof_record(int idx, cudaStream_t stream) {
-        if (profiling_) cudaEventRecord(prof_events_[idx], stream);
+        if (profiling_ != 0) cudaEventRecord(prof_events_[idx], stream);
     }
 };
 

@@ -79,7 +79,7 @@ class LocalCluster:
                         previous_event_before_epilogue=None, async_with_compute_stream=False,
                         allocate_on_comm_stream=False, handle=None, do_cpu_sync=None, do_expand=False,
                         do_zero_padding=False, use_tma_aligned_col_major_sf=False, zero_copy=False, fused_fp8=False,
-                        round_scale=False)
+                        round_scale=False, num_worst_tokens=0)
         args, metas = [], []
         for buf, kw in zip(self.buffers, per_rank_kwargs):
             kw = dict(kw)
@@ -93,7 +93,7 @@ class LocalCluster:
 
     def combine(self, per_rank_kwargs: Sequence[dict]):
         defaults = dict(topk_weights=None, bias=None, num_sms=0, previous_event=None, previous_event_before_epilogue=None,
-                        async_with_compute_stream=False, allocate_on_comm_stream=False)
+                        async_with_compute_stream=False, allocate_on_comm_stream=False, weighted=False)
         args = [buf._make_combine_args(**{**defaults, **kw}) for buf, kw in zip(self.buffers, per_rank_kwargs)]
         results = self._C.Runtime.combine(self.runtimes, args)
         return [(r.combined_x, r.combined_topk_weights, EventOverlap(r.event)) for r in results]

@@ -57,7 +57,7 @@ def main():
 
     if a.op.startswith('dispatch') or a.op == 'combine':
         buf = deepep_b200.ElasticBuffer(SingleProcessGroup(), num_max_tokens_per_rank=T, hidden=H, num_topk=K, num_gpu_timeout_secs=20)
-        buf.runtime.enable_profiling(True)
+        buf.runtime.enable_profiling(2)
         x = torch.randn((T, H), generator=g).bfloat16().cuda()
         idx, w = gate.topk_from_scores(gate.get_balanced_scores(T, E, generator=g), K)
         idx, w = idx.cuda(), w.cuda()

@@ -10,7 +10,7 @@ pytestmark = pytest.mark.gpu
 
 
 def _cluster(num_ranks, num_max_tokens, hidden, num_topk, fuse_reduce=None, **kw):
-    # fuse_reduce: 0 separate reduce kernel, 2 reduce inside the combine's send kernel
+    # fuse_reduce: 0 reduce kernel after the send kernel, 1 flag-driven reduce kernel beside it, 2 reduce inside the send kernel
     from deepep_b200.parallel.local_cluster import LocalCluster
     cl = LocalCluster(num_ranks, num_max_tokens_per_rank=num_max_tokens, hidden=hidden, num_topk=num_topk,
                       num_gpu_timeout_secs=5, num_cpu_timeout_secs=20, **kw)
@@ -39,7 +39,7 @@ def _as_bytes(t):
     (4, 96, 1024, 32, 6, 4),
     (8, 128, 7168, 256, 8, 6),
 ])
-@pytest.mark.parametrize('fuse_reduce', [0, 2])
+@pytest.mark.parametrize('fuse_reduce', [0, 1, 2])
 def test_dispatch_combine_bf16(num_ranks, num_tokens, hidden, num_experts, num_topk, num_sms, fuse_reduce):
     from deepep_b200.utils import refs
     T_max = num_tokens
@@ -125,7 +125,7 @@ def test_dispatch_fp8(fused, col_major):
 
 
 @pytest.mark.parametrize('alignment,zero_padding', [(1, False), (16, True)])
-@pytest.mark.parametrize('fuse_reduce', [0, 2])
+@pytest.mark.parametrize('fuse_reduce', [0, 1, 2])
 def test_dispatch_expand_and_combine(alignment, zero_padding, fuse_reduce):
     from deepep_b200.utils import refs
     R, T, H, E, K = 4, 72, 512, 16, 3
@@ -176,7 +176,7 @@ def test_dispatch_expand_and_combine(alignment, zero_padding, fuse_reduce):
     cl.destroy()
 
 
-@pytest.mark.parametrize('fuse_reduce', [0, 2])
+@pytest.mark.parametrize('fuse_reduce', [0, 1, 2])
 def test_combine_topk_layout_single_rounding(fuse_reduce):
     """allow_multiple_reduction=False: every expert row travels on its own and the source rank sums them in fp32 in
     ascending top-k order with one rounding."""
@@ -241,6 +241,109 @@ def test_cached_dispatch_no_cpu_sync_zero_copy():
     for r in range(R):
         ref = refs.combine_local([third[q][0][:ns[q]].cpu() for q in range(R)], srcs, r, xs[r].size(0), T)
         assert torch.equal(comb[r][0].cpu(), ref)
+    cl.destroy()
+
+
+def test_zero_copy_views_of_the_receive_region():
+    """zero_copy: payload and row-major scales are strided views of the records where they landed."""
+    from deepep_b200.utils.math import per_token_cast_to_fp8
+    R, T, H, E, K = 4, 80, 1024, 32, 4
+    cl = _cluster(R, T, H, K, use_fp8_dispatch=True)
+    xs, idxs, ws = make_routed_inputs(R, T, H, E, K, seed=12, device='cuda')
+    q = [per_token_cast_to_fp8(x) for x in xs]
+    out = cl.dispatch([dict(x=xs[r], fused_fp8=True, topk_idx=idxs[r], topk_weights=ws[r], num_experts=E, num_sms=4,
+                            zero_copy=True) for r in range(R)])
+    torch.cuda.synchronize()
+    cl.check_status()
+    exp = _oracle([a for a, _ in q], idxs, ws, E, T, sfs=[b for _, b in q])
+    for r in range(R):
+        (recv_x, recv_sf), recv_idx, recv_w, handle, _ = out[r]
+        assert recv_x.stride(0) > H and recv_x.stride(0) % 128 == 0 and recv_x.stride(1) == 1      # rows sit a record apart
+        assert recv_sf.stride(0) * 4 == recv_x.stride(0) and recv_sf.stride(1) == 1
+        assert torch.equal(recv_x.view(torch.uint8).cpu(), exp[r]['recv_x'])
+        assert torch.equal(recv_sf.cpu(), exp[r]['recv_sf'])
+        assert torch.equal(recv_idx.cpu(), exp[r]['recv_topk_idx'])
+        assert torch.equal(recv_w.cpu(), exp[r]['recv_topk_weights'])
+    cl.destroy()
+
+
+def test_int32_topk_idx():
+    """Routing indices may be int32 (EP_NUM_TOPK_IDX_BITS=32 of the reference): same rows, int32 local ids back."""
+    from deepep_b200.utils import refs
+    R, T, H, E, K = 4, 48, 512, 16, 4
+    cl = _cluster(R, T, H, K)
+    xs, idxs, ws = make_routed_inputs(R, T, H, E, K, seed=13, device='cuda', masked_ratio=0.1)
+    out = cl.dispatch([dict(x=xs[r], topk_idx=idxs[r].int(), topk_weights=ws[r], num_experts=E, num_sms=3) for r in range(R)])
+    torch.cuda.synchronize()
+    cl.check_status()
+    exp = _oracle(xs, idxs, ws, E, T)
+    for r in range(R):
+        recv_x, recv_idx, recv_w, handle, _ = out[r]
+        assert recv_idx.dtype == torch.int32 and handle.topk_idx.dtype == torch.int32
+        assert torch.equal(recv_x.cpu(), exp[r]['recv_x'])
+        assert torch.equal(recv_idx.cpu().long(), exp[r]['recv_topk_idx'])
+        counts = handle.num_tokens_per_rank_matrix.cpu()
+        assert int(counts[:, r].sum()) == recv_x.size(0)
+    comb = cl.combine([dict(x=out[r][0], handle=out[r][3]) for r in range(R)])
+    torch.cuda.synchronize()
+    cl.check_status()
+    srcs = [out[r][3].recv_src_metadata[:, 0].cpu() for r in range(R)]
+    for r in range(R):
+        ref = refs.combine_local([out[q][0].cpu() for q in range(R)], srcs, r, xs[r].size(0), T)
+        assert torch.equal(comb[r][0].cpu(), ref)
+    cl.destroy()
+
+
+def test_num_worst_tokens_fills_the_tail():
+    """Without CPU sync and with ``num_worst_tokens``: outputs have exactly that many rows; routing rows past the
+    received count hold -1 / 0 even when the memory was poisoned before."""
+    R, T, H, E, K = 4, 32, 256, 16, 2
+    cl = _cluster(R, T, H, K)
+    xs, idxs, ws = make_routed_inputs(R, T, H, E, K, seed=14, device='cuda')
+    worst = 100
+    out = cl.dispatch([dict(x=xs[r], topk_idx=idxs[r], topk_weights=ws[r], num_experts=E, num_sms=2, do_cpu_sync=False,
+                            num_worst_tokens=worst) for r in range(R)])
+    torch.cuda.synchronize()
+    cl.check_status()
+    exp = _oracle(xs, idxs, ws, E, T)
+    for r in range(R):
+        recv_x, recv_idx, recv_w, handle, _ = out[r]
+        n = exp[r]['recv_x'].size(0)
+        assert recv_x.size(0) == worst and recv_idx.size(0) == worst and n <= worst
+        assert torch.equal(recv_x[:n].cpu(), exp[r]['recv_x'])
+        assert torch.equal(recv_idx[:n].cpu(), exp[r]['recv_topk_idx'])
+        assert (recv_idx[n:] == -1).all() and (recv_w[n:] == 0).all()
+        assert (handle.recv_src_metadata[n:] == -1).all()
+    cl.destroy()
+
+
+@pytest.mark.parametrize('allow_multiple_reduction', [True, False])
+@pytest.mark.parametrize('fuse_reduce', [0, 1])
+def test_weighted_combine(allow_multiple_reduction, fuse_reduce):
+    """weighted=True on the expanded layout: combined_x[t] = sum_k w[t, k] * y_k (fp32 accumulation)."""
+    R, T, H, E, K = 4, 40, 512, 16, 4
+    EL = E // R
+    cl = _cluster(R, T, H, K, fuse_reduce=fuse_reduce, allow_multiple_reduction=allow_multiple_reduction)
+    xs, idxs, ws = make_routed_inputs(R, T, H, E, K, seed=15, device='cuda', masked_ratio=0.1)
+    out = cl.dispatch([dict(x=xs[r], topk_idx=idxs[r], topk_weights=ws[r], num_experts=E, num_sms=3, do_expand=True)
+                       for r in range(R)])
+    torch.cuda.synchronize()
+    cl.check_status()
+    ys = [torch.randn(out[r][0].shape, generator=torch.Generator().manual_seed(30 + r)).bfloat16().cuda() for r in range(R)]
+    comb = cl.combine([dict(x=ys[r], handle=out[r][3], topk_weights=out[r][2], weighted=True) for r in range(R)])
+    torch.cuda.synchronize()
+    cl.check_status()
+    for r in range(R):
+        rows = out[r][3].dst_expanded_row_idx.cpu()
+        ref = torch.zeros((xs[r].size(0), H), dtype=torch.float32)
+        for k in range(K):
+            e = idxs[r][:, k].cpu()
+            for t in range(xs[r].size(0)):
+                if e[t] >= 0:
+                    ref[t] += float(ws[r][t, k]) * ys[int(e[t]) // EL][int(rows[t, k])].cpu().float()
+        got = comb[r][0].cpu().float()
+        assert torch.allclose(got, ref, rtol=2e-2, atol=2e-2)
+        assert (got - ref).abs().max().item() < 0.1
     cl.destroy()
 
 
