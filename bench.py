@@ -707,13 +707,19 @@ def main():
         pair, h = run(1)
         # %globaltimer spans of the four kernels of the last step (us, relative to the start of the dispatch kernel)
         timeline = [round(v / 1e3, 1) for v in buf.runtime.last_timeline()]
+        per_rank = [timeline]
+        if world > 1:
+            per_rank = [None] * world
+            dist.all_gather_object(per_rank, timeline)
         buf.runtime.enable_profiling(0)
         n = true_recv_tokens(h)
         return {'num_sms': num_sms,
                 'dispatch_kernel_us': round(split[0] * 1e3, 1), 'dispatch_epilogue_us': round(split[1] * 1e3, 1),
                 'combine_kernel_us': round(split[2] * 1e3, 1), 'combine_epilogue_us': round(split[3] * 1e3, 1),
                 'dispatch_with_epilogue_us': round(pair[4] * 1e3, 1), 'combine_with_reduce_us': round(pair[5] * 1e3, 1),
-                'dispatch_phases_us_rank0': phases, 'kernel_spans_us_rank0': timeline,
+                'dispatch_phases_us_rank0': phases,
+                # [dispatch start, end, its epilogue start, end, combine send start, end, combine reduce start, end] per rank
+                'kernel_spans_us_per_rank': per_rank,
                 'dispatch_kernel_gbs': round(n * disp_bytes_tok / (split[0] * 1e-3) / 1e9, 1),
                 'combine_kernel_gbs': round(n * comb_bytes_tok / (split[2] * 1e-3) / 1e9, 1),
                 'dispatch_e2e_gbs': round(n * disp_bytes_tok / (pair[4] * 1e-3) / 1e9, 1),

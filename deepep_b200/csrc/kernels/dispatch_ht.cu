@@ -183,7 +183,7 @@ __global__ void __launch_bounds__(1024, 1) dispatch_kernel(const __grid_constant
             blk_cnt[bid * CW + j] = v;
             if (v != 0) atomicAdd(tot_cnt + j, v);
         }
-        __threadfence();
+        // (the barrier's block-wide sync followed by its release at GPU scope publishes the counts above)
         ok &= grid_barrier(w, grid_counter, p.grid_bar_base + nb, 1);
         if (stamper) stamps[1] = globaltimer_ns();
 
@@ -398,8 +398,7 @@ __global__ void __launch_bounds__(1024, 1) dispatch_kernel(const __grid_constant
         if (ok) {
             for (int j = tid; j < CW; j += nthreads) steal_base[bid * CW + j] = j < R ? s_rank_base[j] : s_exp_base[j - R];
         }
-        __threadfence();
-        __syncthreads();
+        __syncthreads();    // ... and the release below (GPU scope, cumulative) publishes what the block wrote
         if (tid == 0 && ok) st_release_gpu_u32(steal_ready + bid, p.epoch);
     } else {
         // ------------------------------------------------------------ cached: only announce entry and wait for the peers

@@ -198,6 +198,140 @@ def _subsystems_worker(rank: int, world: int, port: int):
     dist.destroy_process_group()
 
 
+def _digest(*tensors) -> str:
+    import hashlib
+    h = hashlib.sha256()
+    for t in tensors:
+        if t is None:
+            continue
+        t = t.contiguous()
+        h.update(t.view(torch.uint8).cpu().numpy().tobytes())
+    return h.hexdigest()
+
+
+def _pressure_worker(rank: int, world: int, port: int, num_seeds: int):
+    """Seed loop on real ranks, a new buffer per seed (tests/elastic/test_ep.py:387-404,547-557 of the reference): every
+    seed draws a workload (token counts, masking, FP8 or bf16, plain or expanded), runs dispatch + combine twice and
+    wants (a) the oracle's rows the first time and (b) the very same bits the second time."""
+    import random
+    import torch.distributed as dist
+    os.environ['MASTER_ADDR'] = '127.0.0.1'
+    os.environ['MASTER_PORT'] = str(port)
+    os.environ.setdefault('NCCL_NVLS_ENABLE', '0')
+    torch.cuda.set_device(rank)
+    dev = torch.device('cuda', rank)
+    dist.init_process_group('nccl', rank=rank, world_size=world, device_id=dev)
+    import deepep_b200
+    from deepep_b200.utils import gate, refs
+    from deepep_b200.utils.math import per_token_cast_to_fp8
+    for seed in range(num_seeds):
+        rng = random.Random(1000 + seed)                      # the same draw on every rank
+        T = rng.choice([64, 200, 512])
+        H = rng.choice([512, 2048, 7168])
+        K = rng.choice([2, 4, 8])
+        E = world * rng.choice([8, 16, 32])
+        fp8 = rng.random() < 0.5
+        expand = rng.random() < 0.4
+        masked = rng.choice([0.0, 0.1, 0.5])
+        sms = rng.choice([2, 6, 24])
+        junk = torch.full((256 << 20,), 0xFF, dtype=torch.uint8, device=dev)      # poison what the allocator hands out next
+        del junk
+        buf = deepep_b200.ElasticBuffer(dist.group.WORLD, num_max_tokens_per_rank=T, hidden=H, num_topk=K,
+                                        num_gpu_timeout_secs=10, explicitly_destroy=True)
+        g = torch.Generator().manual_seed(seed * 131 + rank)
+        t = T - (rank * 7) % 23
+        x = torch.randn((t, H), generator=g).bfloat16().to(dev)
+        idx, w = gate.topk_from_scores(gate.get_balanced_scores(t, E, generator=g), K, masked_ratio=masked, generator=g)
+        idx, w = idx.to(dev), w.to(dev)
+        digests = []
+        for run in range(2):
+            kw = dict(topk_idx=idx, topk_weights=w, num_experts=E, num_sms=sms, do_expand=expand,
+                      expert_alignment=16 if expand else 1, do_zero_padding=expand, fused_fp8=fp8)
+            rx, ridx, rw, handle, _ = buf.dispatch(x, **kw)
+            rxd, rsf = rx if fp8 else (rx, None)
+            y = torch.randn(rxd.shape, generator=torch.Generator().manual_seed(seed + 7 * rank)).bfloat16().to(dev)
+            out, ow, _ = buf.combine(y, handle, topk_weights=rw)
+            torch.cuda.synchronize()
+            buf.check_status()
+            digests.append(_digest(rxd, rsf, ridx, rw, handle.recv_src_metadata, out, ow))
+            if run == 0 and not expand:
+                src = per_token_cast_to_fp8(x) if fp8 else x
+                ex, eidx, ew, esrc, _ = refs.dispatch(src, idx, w, T, E)
+                if fp8:
+                    assert torch.equal(rxd.view(torch.uint8), ex[0].view(torch.uint8)) and torch.equal(rsf, ex[1])
+                else:
+                    assert torch.equal(rxd, ex)
+                assert torch.equal(ridx, eidx) and torch.equal(rw, ew) and torch.equal(handle.recv_src_metadata[:, 0], esrc)
+                assert torch.equal(out, refs.combine(y, esrc, t, T))
+        assert digests[0] == digests[1], f'seed {seed}: two runs of the same workload differ'
+        dist.barrier()
+        buf.destroy()
+    dist.destroy_process_group()
+
+
+def test_pressure_seed_loop_on_real_ranks():
+    n = torch.cuda.device_count()
+    if n < 2:
+        pytest.skip('needs at least two GPUs')
+    world = 8 if n >= 8 else (4 if n >= 4 else 2)
+    torch.multiprocessing.spawn(_pressure_worker, args=(world, _free_port(), 8), nprocs=world, join=True)
+
+
+def _ll_graph_worker(rank: int, world: int, port: int):
+    """The low-latency pair captured in ONE CUDA graph and replayed with new tokens every time; every replay is checked."""
+    import torch.distributed as dist
+    os.environ['MASTER_ADDR'] = '127.0.0.1'
+    os.environ['MASTER_PORT'] = str(port)
+    os.environ.setdefault('NCCL_NVLS_ENABLE', '0')
+    torch.cuda.set_device(rank)
+    dev = torch.device('cuda', rank)
+    dist.init_process_group('nccl', rank=rank, world_size=world, device_id=dev)
+    import deepep_b200
+    from deepep_b200.utils import gate
+    T, H, E, K = 64, 2048, 8 * world, 4
+    ll = deepep_b200.Buffer(dist.group.WORLD, num_rdma_bytes=deepep_b200.Buffer.get_low_latency_rdma_size_hint(T, H, world, E),
+                            low_latency_mode=True, num_gpu_timeout_secs=10, explicitly_destroy=True)
+    g = torch.Generator().manual_seed(77 + rank)
+    x = torch.randn((T, H), generator=g).bfloat16().to(dev)
+    idx, w = gate.topk_from_scores(gate.get_balanced_scores(T, E, generator=g), K, masked_ratio=0.1, generator=g)
+    idx, w = idx.to(dev), w.to(dev)
+    out = torch.empty_like(x)
+
+    def step():
+        rx, cnt, handle, _, _ = ll.low_latency_dispatch(x, idx, T, E, use_fp8=False)
+        ll.low_latency_combine(rx, idx, w, handle, out=out)      # identity experts
+
+    side = torch.cuda.Stream()
+    side.wait_stream(torch.cuda.current_stream())
+    with torch.cuda.stream(side):
+        for _ in range(2):
+            step()
+    torch.cuda.current_stream().wait_stream(side)
+    torch.cuda.synchronize()
+    dist.barrier()
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph):
+        step()
+    valid_w = torch.where(idx >= 0, w, torch.zeros_like(w)).sum(dim=1, keepdim=True)
+    for it in range(12):
+        x.copy_(torch.randn((T, H), generator=g).bfloat16())     # new tokens, same graph
+        graph.replay()
+        torch.cuda.synchronize()
+        assert torch.allclose(out.float(), x.float() * valid_w, rtol=2e-2, atol=2e-2), f'replay {it}'
+    ll.check_status()
+    dist.barrier()
+    ll.destroy()
+    dist.destroy_process_group()
+
+
+def test_low_latency_graph_replay_on_real_ranks():
+    n = torch.cuda.device_count()
+    if n < 2:
+        pytest.skip('needs at least two GPUs')
+    world = 4 if n >= 4 else 2
+    torch.multiprocessing.spawn(_ll_graph_worker, args=(world, _free_port()), nprocs=world, join=True)
+
+
 def test_subsystems_on_real_ranks():
     n = torch.cuda.device_count()
     if n < 2:
