@@ -128,12 +128,9 @@ class ElasticBuffer:
         self.allow_hybrid_mode = allow_hybrid_mode
         self.allow_multiple_reduction = allow_multiple_reduction
         # How the combine's reduce overlaps the sends (EP_COMBINE_FUSED_REDUCE): 1 (default) = a reduce kernel runs
-        # beside the send kernel on the SMs it leaves free and sums a token as soon as the arrival flags of its
-        # rows are up; 2 = the reduce runs inside the send kernel on spare warps; 0 = the reduce kernel runs after
-        # the send kernel.
+        # beside the send kernel on the SMs it leaves free and sums a token as soon as all its rows have been counted
+        # as landed; 0 = the reduce kernel runs after the send kernel.
         self.fuse_combine_reduce = int(os.environ.get('EP_COMBINE_FUSED_REDUCE', '1'))
-        # mode 2 only: blocks on top of num_sms that only reduce; 0 = the spare warps of the send blocks do it all
-        self.num_combine_reduce_sms = int(os.environ.get('EP_COMBINE_REDUCE_SMS', '0'))
         self.prefer_overlap_with_compute = prefer_overlap_with_compute
         self.deterministic = deterministic
         self.use_fp8_dispatch = use_fp8_dispatch
@@ -537,8 +534,8 @@ class ElasticBuffer:
         a.weighted = bool(weighted)
         a.allow_multiple_reduction = self.allow_multiple_reduction
         a.dst_slot = handle.dst_buffer_slot_idx
+        a.count_matrix = handle.num_tokens_per_rank_matrix
         a.fuse_reduce = self.fuse_combine_reduce
-        a.num_reduce_sms = self.num_combine_reduce_sms
         sc = a.sc
         sc.previous_event = previous_event
         sc.previous_event_before_epilogue = previous_event_before_epilogue

@@ -132,7 +132,7 @@ EP_HD int ht_record_pitch(int x_row_bytes, int sf_bytes, int num_topk) {
     return align_up<int>(ht_record_bytes(x_row_bytes, sf_bytes, num_topk), 128);
 }
 
-// received rows per arrival flag of the combine (flag-driven reduce)
+// rows per arrival counter of the combine (arrival-driven reduce)
 constexpr int kCombineFlagRows = 32;
 
 struct HtLayout {
@@ -140,7 +140,7 @@ struct HtLayout {
     uint64_t dispatch_rec[2];  // [ranks * max tokens] records
     uint64_t combine_x[2];
     uint64_t combine_w[2];
-    uint64_t combine_flag;     // [ranks][flag chunks] arrival flags of the flag-driven reduce + [flag chunks] int32 counters
+    uint64_t combine_flag;     // [2 parities][ranks][flag chunks] uint32 rows-landed counters of the arrival-driven reduce
     int combine_flag_chunks;
     uint64_t end;
 };
@@ -159,7 +159,7 @@ EP_HD HtLayout ht_layout(int num_ranks, int num_max_tokens, int hidden, int num_
     for (int s = 0; s < 2; ++s) { l.combine_x[s] = off; off += crow; l.combine_w[s] = off; off += cw; }
     l.combine_flag_chunks = static_cast<int>(ceil_div<uint64_t>(rows, kCombineFlagRows));
     l.combine_flag = off;
-    off += align_up<uint64_t>(static_cast<uint64_t>(l.combine_flag_chunks) * (num_ranks * 8 + 4), 256);
+    off += align_up<uint64_t>(2ull * num_ranks * l.combine_flag_chunks * 4, 256);
     l.end = align_up<uint64_t>(off, kHeapAlignment);
     return l;
 }

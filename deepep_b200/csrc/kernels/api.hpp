@@ -134,13 +134,14 @@ struct CombineEpilogueParams {
     const uint8_t* bias1;
     uint8_t* combined_x;              // [T, hidden] bf16
     float* combined_topk_weights;     // [T, K] or null
-    // Flag-driven mode (flags != null): the kernel runs beside the send kernel and sums a token as soon as the
-    // arrival flags of all its rows are up; every wait is bounded through `c`.
+    // Arrival-driven mode (arrivals != null): the kernel runs beside the send kernel and sums a token as soon as the
+    // arrival counters of all its rows are full; every wait is bounded through `c`.
     CommCtx c;
     uint32_t epoch;
-    const uint64_t* flags;    // [R][flag_chunks] epoch-tagged arrival words in this rank's heap, or null
+    const uint32_t* arrivals; // [R][flag_chunks] rows-landed counters of this combine's parity in this rank's heap, or null
     int flag_chunks;
     const int* dst_slot;      // [T, R] row of each of this rank's tokens in every destination's receive order (-1 = none)
+    const int* count_matrix;  // [R, R] tokens rank i dispatched to rank j (arrival-driven mode)
     uint64_t* local_ws;       // private workspace (kernel timeline)
 };
 struct CombineParams {
@@ -161,23 +162,22 @@ struct CombineParams {
     uint64_t off_comb_w;
     uint32_t epoch;
     uint64_t grid_bar_base;
-    // Arrival flags (fuse_reduce >= 1): every `kCombineFlagRows` received rows that have landed raise one flag at
-    // their source rank(s). fuse_reduce == 1: a reduce kernel launched right behind this one (programmatic dependent
-    // launch, on the SMs this kernel leaves free) sums tokens as their flags come up. fuse_reduce == 2: warps of
-    // this kernel that have no row to send (and the send warps once they are done) do that themselves.
+    // fuse_reduce != 0: every landed row is counted in the receiver's heap (one counter per sender and per
+    // `kCombineFlagRows` consecutive rows of what the sender holds for that receiver); a reduce kernel launched right
+    // behind this one (programmatic dependent launch, on the SMs this kernel leaves free) sums tokens as their
+    // counters fill up.
     int fuse_reduce;
-    int num_send_warps;       // warps [0, num_send_warps) send; the block may carry more warps that only reduce
-    int num_send_blocks;      // blocks [0, num_send_blocks) send (and reduce); further blocks only reduce
+    int num_send_warps;       // warps of a block (one staging buffer each); filled in by the launcher
+    int num_send_blocks;      // blocks of the grid
     int direct_out;           // single rank, no bias, one row per token: rows go straight to red.combined_x, no reduce
-    int flag_chunks;          // flag words per source rank = ceil(ranks * max tokens / kCombineFlagRows)
-    const int* dst_slot;      // [T, R] row of each of this rank's tokens in every destination's receive region (-1 = none)
-    uint64_t off_comb_flag;   // [R][flag_chunks] epoch-tagged words, then [flag_chunks] int32 rows-landed counters
+    int flag_chunks;          // counters per source rank = ceil(ranks * max tokens / kCombineFlagRows)
+    uint64_t off_comb_flag;   // [2 parities][R][flag_chunks] uint32 rows-landed counters
     CombineEpilogueParams red;
 };
 struct CombineLaunch {
     int num_sms;
     int num_warps;            // send warps (one staging buffer each)
-    int num_reduce_warps;     // extra warps of the in-kernel reduce
+    int num_reduce_warps;     // unused (0)
     int smem_bytes;
 };
 bool plan_combine(const CombineParams& p, int num_sms, int smem_optin, CombineLaunch* out);

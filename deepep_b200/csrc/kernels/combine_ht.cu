@@ -11,16 +11,17 @@
 // reading the half it is about to overwrite.
 //
 // Reduce: combined_x[t] = sum over lanes in ascending order (fp32) + bias_0 + bias_1, one bf16
-// rounding at the end; top-k weights are gathered back. Three ways to run it:
-//   * flag-driven, beside the send kernel (default with peers): senders raise one arrival flag per
-//     32-row group of a receiver's rows (a row counts as landed three rows late, when wait_group
-//     has confirmed its remote writes, so the NVLink round trip never stalls a send warp); the
-//     reduce kernel is launched as a programmatic dependent of the send kernel -- it becomes
-//     resident on the SMs the send kernel leaves free once every send block is running -- and sums
-//     a token as soon as the flags of all its rows are up, while later rows are still in flight;
-//   * the same reduce kernel after the send kernel (no flags), e.g. when an event gates the reduce;
-//   * inside the send kernel on spare warps (fuse_reduce == 2; reduce-bound at 24 SMs, kept for
-//     experiments).
+// rounding at the end; top-k weights are gathered back. Two ways to run it:
+//   * arrival-driven, beside the send kernel (default with peers): for every row that has landed the
+//     sender adds one to a counter in the RECEIVER's heap (a fire-and-forget `red.release.sys`, one
+//     counter per sender and per 32 consecutive rows of what that sender holds for the receiver; a
+//     row counts as landed three rows late, when wait_group has confirmed its remote writes, so
+//     neither the NVLink round trip nor the accounting stalls a send warp); the reduce kernel is
+//     launched as a programmatic dependent of the send kernel -- it becomes resident on the SMs the
+//     send kernel leaves free once every send block is running -- and sums a token as soon as the
+//     counters of all its rows are full, while later rows are still in flight. The counters of one
+//     parity are zeroed by the send kernel of the combine before (no peer can be two combines ahead);
+//   * the same reduce kernel after the send kernel (no counters), e.g. when an event gates the reduce.
 // With `weighted`, expanded rows are multiplied by their top-k weight: in the sender's fp32
 // pre-reduce (rank layout) or in the reduce (top-k layout).
 //
@@ -203,9 +204,19 @@ __global__ void __launch_bounds__(kEpiWarps * 32) combine_epilogue_kernel(const 
     if (bid == 0 && threadIdx.x == 0) timeline[0] = globaltimer_ns();
     // Flag-driven mode: this kernel runs beside the send kernel (it never waits for it as a whole); the tokens of
     // a warp are visited in ascending order, which is also the order in which their rows arrive.
-    const bool flagged = p.flags != nullptr;
+    const bool flagged = p.arrivals != nullptr;
     const WaitCtx w = make_wait_ctx(p.c);
     bool flags_ok = true;
+    // per source rank: first row of this rank's tokens in that rank's receive order, and how many rows it holds for us
+    __shared__ int s_base[kMaxRanks], s_held[kMaxRanks];
+    if (flagged && threadIdx.x < p.num_ranks) {
+        const int src = threadIdx.x, me = p.c.rank;
+        int base = 0;
+        for (int i = 0; i < me; ++i) base += p.count_matrix[i * p.num_ranks + src];
+        s_base[src] = base;
+        s_held[src] = p.count_matrix[me * p.num_ranks + src];
+    }
+    __syncthreads();
 
     for (int t = bid * num_warps + warp; t < p.num_tokens && flags_ok; t += nb * num_warps) {
         const int e = token_expert(p, t, lane);
@@ -215,8 +226,12 @@ __global__ void __launch_bounds__(kEpiWarps * 32) combine_epilogue_kernel(const 
                 const int src = e / EL;
                 const int slot = p.dst_slot[static_cast<int64_t>(t) * p.num_ranks + src];
                 if (slot >= 0) {
-                    const uint64_t* flag = p.flags + static_cast<uint64_t>(src) * p.flag_chunks + slot / kCombineFlagRows;
-                    ok = bounded_wait(w, kStatusCombineDone, src, t, [&]() { return epoch_reached(ld_acquire_sys_u64(flag), p.epoch); });
+                    // position of the row among the rows that `src` holds for this rank, and how many of them share its counter
+                    const int idx = slot - s_base[src];
+                    const int g = idx / kCombineFlagRows;
+                    const uint32_t want = static_cast<uint32_t>(min(kCombineFlagRows, s_held[src] - g * kCombineFlagRows));
+                    const uint32_t* cnt = p.arrivals + static_cast<uint64_t>(src) * p.flag_chunks + g;
+                    ok = idx >= 0 && bounded_wait(w, kStatusCombineDone, src, t, [&]() { return ld_acquire_sys_u32(cnt) >= want; });
                 }
             }
             flags_ok = __all_sync(0xffffffffu, ok);
@@ -291,12 +306,9 @@ __global__ void __launch_bounds__(kEpiWarps * 32) combine_epilogue_kernel(const 
     if (threadIdx.x == 0) atomicMax(reinterpret_cast<unsigned long long*>(timeline + 1), static_cast<unsigned long long>(globaltimer_ns()));
 }
 
-// kMode 0: plain send. 1: senders raise arrival flags (a reduce kernel beside this one consumes them). 2: flags and
-// the reduce inside this kernel (more registers per thread; compiled apart so that the plain send kernel does not
-// pay for it).
-template <int kMode>
+// kFlags: senders count landed rows in the receivers' heaps (a reduce kernel beside this one consumes the counters).
+template <bool kFlags>
 __global__ void __launch_bounds__(1024, 1) combine_kernel(const __grid_constant__ Multi<CombineParams> m) {
-    constexpr bool kFlags = kMode >= 1, kFused = kMode == 2;
     extern __shared__ __align__(128) uint8_t smem[];
     const int vr = blockIdx.x / m.blocks_per_rank;
     const int bid = blockIdx.x % m.blocks_per_rank;
@@ -324,44 +336,39 @@ __global__ void __launch_bounds__(1024, 1) combine_kernel(const __grid_constant_
     }
     __syncwarp();
 
-    // ---- arrival accounting of the fused reduce (lane 0 of a send warp): a row counts as landed three rows late,
-    // when wait_group has confirmed its remote writes; the warp that completes a group of kCombineFlagRows rows of
-    // this rank's receive order raises the flag at every source rank that owns one of them.
+    // ---- arrival accounting (lane 0 of a send warp): a row counts as landed three rows late, when wait_group has
+    // confirmed its remote writes; then one fire-and-forget add goes to the counter of its 32-row group in the
+    // receiver's heap. `pend` holds (destination rank << 24 | group) of the last three rows sent, oldest first.
     const int num_recv = p.psum_rank[R - 1];
-    int* landed_cnt = reinterpret_cast<int*>(c.heap[c.rank] + p.off_comb_flag + static_cast<uint64_t>(R) * p.flag_chunks * 8);
-    auto chunk_row_landed = [&](int q) {
+    const uint64_t arrivals_off = p.off_comb_flag + static_cast<uint64_t>(p.epoch & 1) * R * p.flag_chunks * 4;
+    auto row_landed = [&](int tag) {
         fence_proxy_async_all();
-        const int lo = q * kCombineFlagRows;
-        const int hi = min(lo + kCombineFlagRows, num_recv);
-        if (atom_add_acq_rel_gpu_s32(landed_cnt + q, 1) != hi - lo - 1) return;
-        landed_cnt[q] = 0;      // the next combine starts from zero again (stream order)
-        int begin = 0;
-        for (int d = 0; d < R; ++d) {
-            const int end = p.psum_rank[d];
-            if (begin < hi && end > lo) {
-                uint64_t* flag = reinterpret_cast<uint64_t*>(c.heap[d] + p.off_comb_flag) + static_cast<uint64_t>(c.rank) * p.flag_chunks + q;
-                st_release_sys_u64(flag, pack_epoch(p.epoch, 1));
-            }
-            begin = end;
-        }
+        uint32_t* cnt = reinterpret_cast<uint32_t*>(c.heap[tag >> 24] + arrivals_off) + static_cast<uint64_t>(c.rank) * p.flag_chunks + (tag & 0xffffff);
+        asm volatile("red.release.sys.global.add.u32 [%0], 1;" ::"l"(cnt) : "memory");
     };
-    int pend0 = -1, pend1 = -1, pend2 = -1;       // flag groups of the last three rows sent (oldest first)
-    auto row_sent = [&](int row) {               // after bulk_commit of the row's only store
+    int pend0 = -1, pend1 = -1, pend2 = -1;
+    auto row_sent = [&](int d, int idx) {        // after bulk_commit of the row's only store
         if (!kFlags) return;
         bulk_wait<3>();
-        if (pend0 >= 0) chunk_row_landed(pend0);
+        if (pend0 >= 0) row_landed(pend0);
         pend0 = pend1;
         pend1 = pend2;
-        pend2 = row / kCombineFlagRows;
+        pend2 = (d << 24) | (idx / kCombineFlagRows);
     };
     auto flush_sent = [&]() {
         if (!kFlags) return;
         bulk_wait_all();
-        if (pend0 >= 0) chunk_row_landed(pend0);
-        if (pend1 >= 0) chunk_row_landed(pend1);
-        if (pend2 >= 0) chunk_row_landed(pend2);
+        if (pend0 >= 0) row_landed(pend0);
+        if (pend1 >= 0) row_landed(pend1);
+        if (pend2 >= 0) row_landed(pend2);
         pend0 = pend1 = pend2 = -1;
     };
+    if (kFlags) {
+        // zero the counters the NEXT combine will count into (the other parity): no peer starts that combine before
+        // it has seen this rank's completion word, which is sent at the end of this kernel
+        uint32_t* next = reinterpret_cast<uint32_t*>(c.heap[c.rank] + p.off_comb_flag + static_cast<uint64_t>((p.epoch + 1) & 1) * R * p.flag_chunks * 4);
+        for (int i = bid * blockDim.x + tid; i < R * p.flag_chunks; i += nb * blockDim.x) next[i] = 0u;
+    }
 
     // groups of received rows per source rank
     int group_begin = 0, group_size = 0, max_group = 0;
@@ -434,7 +441,7 @@ __global__ void __launch_bounds__(1024, 1) combine_kernel(const __grid_constant_
             if (lane == 0) {
                 bulk_s2g(dst_ptr, buf, p.row_bytes);
                 bulk_commit();
-                row_sent(i);
+                row_sent(d, idx);
             }
         } else if (p.use_rank_layout) {
             // expanded input: sum this token's local-expert rows in fp32 (ascending top-k lane), round once, send
@@ -485,7 +492,7 @@ __global__ void __launch_bounds__(1024, 1) combine_kernel(const __grid_constant_
             if (lane == 0) {
                 bulk_s2g(dst_ptr, buf, p.row_bytes);
                 bulk_commit();
-                row_sent(i);
+                row_sent(d, idx);
             }
         } else {
             // expanded input, top-k layout: every expert row travels on its own
@@ -515,7 +522,7 @@ __global__ void __launch_bounds__(1024, 1) combine_kernel(const __grid_constant_
             if (failed) fatal = true;
             if (lane == 0 && kFlags) {     // several stores per token: settle all of them, then count the token
                 flush_sent();
-                chunk_row_landed(i / kCombineFlagRows);
+                row_landed((d << 24) | (idx / kCombineFlagRows));
             }
         }
         } while (false);
@@ -525,38 +532,12 @@ __global__ void __launch_bounds__(1024, 1) combine_kernel(const __grid_constant_
     if (lane == 0) flush_sent();
     __syncwarp();
 
-    // ---- fused reduce: tokens in ascending order, each by one warp, as soon as the flags of its contributions are up
-    if constexpr (kFused) {
-        const CombineEpilogueParams& q = p.red;
-        unsigned long long* next_token = reinterpret_cast<unsigned long long*>(c.local_ws + kWsWorkReduce);
-        const uint64_t* my_flags = reinterpret_cast<const uint64_t*>(c.heap[c.rank] + p.off_comb_flag);
-        while (!fatal) {
-            unsigned long long tk = 0;
-            if (lane == 0) tk = atomicAdd(next_token, 1ull);
-            const int t = static_cast<int>(__shfl_sync(0xffffffffu, tk, 0));
-            if (t >= q.num_tokens) break;
-            const int e = token_expert(q, t, lane);
-            bool ok = true;
-            if (e >= 0) {
-                const int src = e / q.num_local_experts;
-                const int slot = p.dst_slot[static_cast<int64_t>(t) * R + src];
-                if (slot >= 0) {
-                    const uint64_t* flag = my_flags + static_cast<uint64_t>(src) * p.flag_chunks + slot / kCombineFlagRows;
-                    ok = bounded_wait(w, kStatusCombineDone, src, t, [&]() { return epoch_reached(ld_acquire_sys_u64(flag), p.epoch); });
-                }
-            }
-            if (!__all_sync(0xffffffffu, ok)) break;
-            reduce_token(q, t, e, lane);
-        }
-    }
-
     bulk_wait_all();
     fence_proxy_async_all();
     __threadfence_system();
     grid_barrier(w, c.local_ws + kWsGridBarrier, p.grid_bar_base + nb, 3);
     if (bid == 0 && tid == 0) {   // ready for the next launch (stream order)
         c.local_ws[kWsWork] = 0;
-        c.local_ws[kWsWorkReduce] = 0;
     }
     if (bid == 0 && tid < R) {
         uint64_t* remote = reinterpret_cast<uint64_t*>(c.heap[tid]) + kCtlCombineDone + c.rank;
@@ -576,14 +557,13 @@ bool plan_combine(const CombineParams& p, int num_sms, int smem_optin, CombineLa
     if (warps < 1) return false;
     out->num_sms = num_sms;
     out->num_warps = warps;
-    out->num_reduce_warps = p.fuse_reduce == 2 ? 32 - warps : 0;
+    out->num_reduce_warps = 0;
     out->smem_bytes = warps * stage;
     return true;
 }
 
 cudaError_t launch_combine(const Multi<CombineParams>& m, const CombineLaunch& l, cudaStream_t stream) {
-    const int mode = m.r[0].fuse_reduce;
-    void (*kernel)(const Multi<CombineParams>) = mode == 2 ? combine_kernel<2> : (mode == 1 ? combine_kernel<1> : combine_kernel<0>);
+    void (*kernel)(const Multi<CombineParams>) = m.r[0].fuse_reduce != 0 ? combine_kernel<true> : combine_kernel<false>;
     cudaError_t err = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, l.smem_bytes);
     if (err != cudaSuccess) return err;
     cudaLaunchConfig_t cfg = {};

@@ -108,8 +108,8 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
         .def_readwrite("allow_multiple_reduction", &CombineArgs::allow_multiple_reduction)
         .def_readwrite("weighted", &CombineArgs::weighted)
         .def_readwrite("dst_slot", &CombineArgs::dst_slot)
+        .def_readwrite("count_matrix", &CombineArgs::count_matrix)
         .def_readwrite("fuse_reduce", &CombineArgs::fuse_reduce)
-        .def_readwrite("num_reduce_sms", &CombineArgs::num_reduce_sms)
         .def_readwrite("sc", &CombineArgs::sc);
 
     py::class_<CombineResult>(m, "CombineResult")

@@ -520,15 +520,12 @@ std::vector<CombineResult> Runtime::combine(const std::vector<std::shared_ptr<Ru
     // One rank: every token has at most one row (rank layout), so the send kernel can write the result itself.
     bool direct = R == 1 && rank_layout && !gated && !(a0.weighted && a0.do_expand);
     for (const auto& a : args) direct = direct && !a.bias0.has_value() && !a.bias1.has_value();
-    // Reduce mode: 1 = arrival flags + the reduce kernel beside the send kernel (default with peers), 2 = reduce inside
-    // the send kernel (opt-in), 0 = the reduce kernel after the send kernel.
-    int mode = direct ? 0 : a0.fuse_reduce;
-    for (const auto& a : args) if (!a.dst_slot.has_value()) mode = 0;
-    if (gated && mode != 0) mode = 0;
-    EP_HOST_ASSERT(mode >= 0 && mode <= 2);
-    int num_reduce_sms = mode == 2 ? std::max(0, a0.num_reduce_sms) : 0;
-    if ((num_sms + num_reduce_sms) * V > rt0.num_device_sms_) num_reduce_sms = rt0.num_device_sms_ / V - num_sms;
-    const int num_blocks = num_sms + num_reduce_sms;
+    // Reduce mode: 1 = arrival counters + the reduce kernel beside the send kernel (default with peers), 0 = the
+    // reduce kernel after the send kernel.
+    int mode = (direct || a0.fuse_reduce == 0) ? 0 : 1;
+    for (const auto& a : args) if (!a.dst_slot.has_value() || !a.count_matrix.has_value()) mode = 0;
+    if (gated) mode = 0;
+    const int num_blocks = num_sms;
     const bool weighted = a0.weighted && a0.do_expand;
     if (weighted) EP_HOST_ASSERT_MSG(a0.topk_weights.has_value(), "a weighted combine needs the top-k weights of the expanded rows");
 
@@ -606,25 +603,26 @@ std::vector<CombineResult> Runtime::combine(const std::vector<std::shared_ptr<Ru
         q.combined_topk_weights = r.combined_topk_weights.has_value() ? r.combined_topk_weights->data_ptr<float>() : nullptr;
         q.c = p.c;
         q.epoch = p.epoch;
-        q.flags = nullptr;
+        q.arrivals = nullptr;
         q.flag_chunks = lay.combine_flag_chunks;
         q.dst_slot = nullptr;
+        q.count_matrix = nullptr;
         q.local_ws = rt.local_ws_;
         p.fuse_reduce = mode;
         p.direct_out = direct ? 1 : 0;
         p.num_send_warps = 0;        // filled in by the launcher
         p.flag_chunks = lay.combine_flag_chunks;
         p.off_comb_flag = lay.combine_flag;
-        p.dst_slot = nullptr;
         if (mode != 0) {
             EP_HOST_ASSERT(a.dst_slot->scalar_type() == at::kInt && a.dst_slot->is_contiguous() && a.dst_slot->dim() == 2 &&
                            a.dst_slot->size(0) == T && a.dst_slot->size(1) == R);
-            p.dst_slot = a.dst_slot->data_ptr<int>();
+            EP_HOST_ASSERT(a.count_matrix->scalar_type() == at::kInt && a.count_matrix->is_contiguous() && a.count_matrix->numel() == R * R);
             touched.push_back(*a.dst_slot);
-            if (mode == 1) {
-                q.flags = reinterpret_cast<const uint64_t*>(rt.heap_->base() + lay.combine_flag);
-                q.dst_slot = p.dst_slot;
-            }
+            touched.push_back(*a.count_matrix);
+            q.arrivals = reinterpret_cast<const uint32_t*>(rt.heap_->base() + lay.combine_flag) +
+                         static_cast<size_t>(p.epoch & 1) * R * lay.combine_flag_chunks;
+            q.dst_slot = a.dst_slot->data_ptr<int>();
+            q.count_matrix = a.count_matrix->data_ptr<int>();
         }
         p.red = q;
         for (const at::Tensor& t : {r.combined_x, a.x, a.recv_src_metadata, a.topk_idx, a.psum_rank}) touched.push_back(t);
@@ -642,8 +640,8 @@ std::vector<CombineResult> Runtime::combine(const std::vector<std::shared_ptr<Ru
     ++rt0.num_launches_;
     if (split) rt0.prof_record(4, stream);
     if (gated) a0.sc.previous_event_before_epilogue->stream_wait(scope.comm);
-    if (mode != 2 && !direct) {
-        // Flag-driven: the reduce runs beside the send kernel, on the SMs that kernel leaves free (it is launched as
+    if (!direct) {
+        // Arrival-driven: the reduce runs beside the send kernel, on the SMs that kernel leaves free (it is launched as
         // a programmatic dependent, so all send blocks are resident before the first reduce block starts).
         const bool beside = mode == 1 && !split && rt0.use_pdl_;
         const int free_sms = rt0.num_device_sms_ / V - num_sms;

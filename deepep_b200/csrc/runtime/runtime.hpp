@@ -86,8 +86,8 @@ struct CombineArgs {
     // [T, R] row of every token in each destination's receive region (the dispatch handle has it). With it, and
     // unless an event has to be awaited between send and reduce, the reduce overlaps the sends.
     std::optional<at::Tensor> dst_slot;
-    int fuse_reduce = 1;       // 1: flag-driven reduce kernel beside the send kernel, 2: reduce inside the send kernel, 0: after it
-    int num_reduce_sms = 0;    // fuse_reduce == 2: extra blocks that only reduce (on top of num_sms)
+    std::optional<at::Tensor> count_matrix;   // [R, R] tokens rank i dispatched to rank j (the handle has it)
+    int fuse_reduce = 1;       // 1: arrival-driven reduce kernel beside the send kernel, 0: the reduce kernel after it
     StreamControl sc;
 };
 
