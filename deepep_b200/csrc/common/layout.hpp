@@ -68,8 +68,7 @@ constexpr int kWsWorkReduce = 15;    // next token handed out by the fused reduc
 constexpr int kWsScratch = 16;       // start of per-block scratch counters
 // scratch: int32 [kMaxBlocks][kMaxRanks + kMaxExperts]
 constexpr size_t kWsScratchInts = static_cast<size_t>(kMaxBlocks) * (kMaxRanks + kMaxExperts);
-// low-latency area (int32): [kMaxExperts] dispatch finish counters, [kMaxExperts] combine finish counters,
-// [kMaxRanks] rank mask, [4] blocks-done counters of the four phases
+// low-latency area (int32): [2 * kMaxExperts] unused, [kMaxRanks] rank mask, [4] blocks-done counters of the four phases
 constexpr size_t kWsLLOffsetBytes = kWsScratch * 8 + kWsScratchInts * 4;
 constexpr size_t kWsLLInts = 2 * kMaxExperts + kMaxRanks + 4;
 // tensor-parallel fused operators (int32): [64 chunks][kMaxRanks] rows-landed counters of the all-gather push
@@ -166,11 +165,12 @@ EP_HD HtLayout ht_layout(int num_ranks, int num_max_tokens, int hidden, int num_
 
 // ---------------------------------------------------------------- low-latency EP layout
 // Two halves (calls alternate). Per half:
-//   recv_x        [local experts][ranks][max tokens] messages: 16-byte header {token, top-k lane},
+//   recv_x        [local experts][ranks][max tokens] messages: 16-byte header whose first word is
+//                 (call number << 32 | top-k lane << 16 | token), written last = the arrival flag;
 //                 payload (e4m3 + 1x128 scales, or bf16)
 //   recv_count    [local experts][ranks] epoch-tagged words (count of the messages above)
 //   combine_x     [kMaxLLTopk][max tokens] bf16 rows, indexed by the token's top-k lane
-//   combine_flag  [experts] epoch-tagged words ("all rows of this expert for you have landed")
+//   combine_flag  [kMaxLLTopk][max tokens] call-tagged words ("the row of this (lane, token) has landed")
 //   send_x        [local experts][ranks * max tokens] bf16 rows: optional staging area the caller may
 //                 let its expert GEMM write into (zero-copy combine)
 constexpr int kMaxLLTopk = 16;
@@ -202,7 +202,7 @@ EP_HD LLLayout ll_layout(int num_ranks, int num_max_tokens, int hidden, int num_
     const uint64_t recv = align_up<uint64_t>(static_cast<uint64_t>(num_local) * num_ranks * num_max_tokens * msg, 256);
     const uint64_t cnt = align_up<uint64_t>(static_cast<uint64_t>(num_local) * num_ranks * 8, 256);
     const uint64_t comb = align_up<uint64_t>(static_cast<uint64_t>(kMaxLLTopk) * num_max_tokens * ll_combine_slot_bytes(hidden, true), 256);
-    const uint64_t flag = align_up<uint64_t>(static_cast<uint64_t>(num_experts) * 8, 256);
+    const uint64_t flag = align_up<uint64_t>(static_cast<uint64_t>(kMaxLLTopk) * num_max_tokens * 8, 256);
     const uint64_t send = align_up<uint64_t>(static_cast<uint64_t>(num_local) * num_ranks * num_max_tokens * hidden * 2, 256);
     uint64_t off = kCtlBytes;
     for (int s = 0; s < 2; ++s) {

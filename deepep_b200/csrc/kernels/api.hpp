@@ -13,6 +13,17 @@
 
 namespace ep {
 
+// Shared-memory set-up of a kernel before its launch: the dynamic shared memory it may use, and the largest
+// shared-memory carve-out as the preferred one. All communication kernels ask for the same carve-out, whatever they
+// use: an SM has to drain and reconfigure when consecutive kernels prefer different ones, which costs microseconds
+// between the back-to-back kernels of a dispatch / combine step.
+template <typename Kernel>
+inline cudaError_t prepare_kernel(Kernel kernel, int dynamic_smem_bytes) {
+    cudaError_t err = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, dynamic_smem_bytes);
+    if (err != cudaSuccess) return err;
+    return cudaFuncSetAttribute(kernel, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared);
+}
+
 // ---------------------------------------------------------------- cross-rank barrier
 struct BarrierParams {
     CommCtx c;

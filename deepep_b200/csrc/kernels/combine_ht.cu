@@ -341,10 +341,11 @@ __global__ void __launch_bounds__(1024, 1) combine_kernel(const __grid_constant_
     // receiver's heap. `pend` holds (destination rank << 24 | group) of the last three rows sent, oldest first.
     const int num_recv = p.psum_rank[R - 1];
     const uint64_t arrivals_off = p.off_comb_flag + static_cast<uint64_t>(p.epoch & 1) * R * p.flag_chunks * 4;
+    // (wait_group has confirmed that the row's writes are complete, so a relaxed add suffices; a release fence at
+    // system scope per row costs microseconds, and the reducer's acquire load orders its reads after the counter)
     auto row_landed = [&](int tag) {
-        fence_proxy_async_all();
         uint32_t* cnt = reinterpret_cast<uint32_t*>(c.heap[tag >> 24] + arrivals_off) + static_cast<uint64_t>(c.rank) * p.flag_chunks + (tag & 0xffffff);
-        asm volatile("red.release.sys.global.add.u32 [%0], 1;" ::"l"(cnt) : "memory");
+        asm volatile("red.relaxed.sys.global.add.u32 [%0], 1;" ::"l"(cnt) : "memory");
     };
     int pend0 = -1, pend1 = -1, pend2 = -1;
     auto row_sent = [&](int d, int idx) {        // after bulk_commit of the row's only store
@@ -564,7 +565,7 @@ bool plan_combine(const CombineParams& p, int num_sms, int smem_optin, CombineLa
 
 cudaError_t launch_combine(const Multi<CombineParams>& m, const CombineLaunch& l, cudaStream_t stream) {
     void (*kernel)(const Multi<CombineParams>) = m.r[0].fuse_reduce != 0 ? combine_kernel<true> : combine_kernel<false>;
-    cudaError_t err = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, l.smem_bytes);
+    cudaError_t err = prepare_kernel(kernel, l.smem_bytes);
     if (err != cudaSuccess) return err;
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3(m.num_vranks * m.blocks_per_rank);
@@ -589,7 +590,7 @@ cudaError_t launch_combine_epilogue(const CombineEpilogueParams* params, int num
     m.num_vranks = num_vranks;
     m.blocks_per_rank = num_sms;
     for (int v = 0; v < num_vranks; ++v) m.r[v] = params[v];
-    cudaError_t err = cudaFuncSetAttribute(combine_epilogue_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kEpiSmem);
+    cudaError_t err = prepare_kernel(combine_epilogue_kernel, kEpiSmem);
     if (err != cudaSuccess) return err;
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3(num_vranks * num_sms);

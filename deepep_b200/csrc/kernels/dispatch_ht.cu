@@ -743,7 +743,7 @@ bool plan_dispatch(const DispatchParams& p, int num_sms, int smem_optin, Dispatc
 }
 
 cudaError_t launch_dispatch(const Multi<DispatchParams>& m, const DispatchLaunch& l, cudaStream_t stream) {
-    cudaError_t err = cudaFuncSetAttribute(dispatch_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, l.smem_bytes);
+    cudaError_t err = prepare_kernel(dispatch_kernel, l.smem_bytes);
     if (err != cudaSuccess) return err;
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3(m.num_vranks * m.blocks_per_rank);
@@ -772,7 +772,7 @@ cudaError_t launch_dispatch_epilogue(const DispatchEpilogueParams* params, int n
     if (warps > (move_rows ? 16 : 32)) warps = move_rows ? 16 : 32;
     if (warps < 1) return cudaErrorInvalidValue;
     const int smem_bytes = move_rows ? warps * stage : 0;
-    cudaError_t err = cudaFuncSetAttribute(dispatch_epilogue_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_bytes);
+    cudaError_t err = prepare_kernel(dispatch_epilogue_kernel, smem_bytes);
     if (err != cudaSuccess) return err;
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3(num_vranks * num_sms);

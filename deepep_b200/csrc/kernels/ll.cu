@@ -5,17 +5,25 @@
 // shared-memory message, then one warp per selected expert bulk-stores the message into slot
 // [local expert][source rank][position] of the owner's receive area. Positions are the token's
 // rank among this source's earlier tokens for that expert, so they do not depend on timing.
-// A per-expert completion counter tells the warp responsible for the expert when every message
-// has landed; it then publishes the (epoch-tagged) count to the owner.
-// Dispatch, RECV phase: one block per local expert waits for the counts of all source ranks,
-// and packs the messages expert-major: rows grouped by source rank in ascending order, scales
+// Every message carries its own arrival flag: its 8-byte header (call number, token, top-k lane)
+// is written last, once wait_group has confirmed that the payload's writes are complete (a plain
+// system-scope store then suffices and is what keeps this cheap: a release fence at system scope
+// per message was measured at 7 us, a full async-proxy fence at 5 us, each; the receiver's acquire
+// load orders its own reads of the payload after the flag); a warp
+// does not wait for that round trip before it takes the next token (the header of message i goes
+// out after message i + 1 has been issued). The per-expert counts need no data at all (they come
+// from the routing), so they travel first, as call-tagged words, while the payloads are cast.
+// Dispatch, RECV phase: one block per (local expert, source rank) waits for the counts of the
+// sources before it (prefix) and then, message by message, for the header of each slot; rows are
+// packed expert-major as they land: grouped by source rank in ascending order, scales
 // column-major, plus src_info / layout_range / recv_count for the combine.
 //
 // Combine, SEND phase: every packed row goes back to row [top-k lane][token] of its source
 // rank's combine area (the lane travelled with the token, which keeps the area at
-// lanes x tokens rows, small enough to stay in L2); per (expert, rank) completion counters
-// drive one flag per expert. Combine, RECV phase: per token, wait for the flags of its experts,
-// accumulate sum_k w_k * row_k in fp32 in ascending lane order, round to bf16 once.
+// lanes x tokens rows, small enough to stay in L2), followed -- one row late, as above -- by a
+// call-tagged flag word for exactly that (lane, token). Combine, RECV phase: per token, wait for
+// the flags of its own rows only, accumulate sum_k w_k * row_k in fp32 in ascending lane order,
+// round to bf16 once. Nothing is counted and nothing has to be cleared between calls.
 //
 // No host synchronisation, no launch parameter that changes from call to call: the call
 // counters that select the buffer half and tag the flags live in device memory, so a captured
@@ -23,6 +31,8 @@
 //
 // Parity: csrc/kernels/legacy/internode_ll.cu:128-462 (dispatch), :714-1138 (combine),
 // :21-126 and :1240-1285 (clean / mask) of the reference.
+#include <cstdlib>
+
 #include "api.hpp"
 #include "../common/device_utils.cuh"
 
@@ -33,8 +43,6 @@ namespace {
 __device__ __forceinline__ int* ll_ints(const CommCtx& c) {
     return reinterpret_cast<int*>(reinterpret_cast<uint8_t*>(c.local_ws) + kWsLLOffsetBytes);
 }
-__device__ __forceinline__ int* ll_finish_dispatch(const CommCtx& c) { return ll_ints(c); }
-__device__ __forceinline__ int* ll_finish_combine(const CommCtx& c) { return ll_ints(c) + kMaxExperts; }
 __device__ __forceinline__ int* ll_mask(const CommCtx& c) { return ll_ints(c) + 2 * kMaxExperts; }
 __device__ __forceinline__ int* ll_done(const CommCtx& c) { return ll_ints(c) + 2 * kMaxExperts + kMaxRanks; }
 
@@ -229,30 +237,55 @@ __global__ void __launch_bounds__(1024, 1) ll_dispatch_kernel(const __grid_const
     const int* mask = ll_mask(c);
     uint64_t* stamps = c.local_ws + kWsStamps;          // phase timestamps of block 0 (ns), read by the profiling helpers
     const bool stamper = bid == 0 && tid == 0;
+    // launched as a programmatic dependent: resident early, but nothing is touched before the kernel ahead has finished
+    dependency_wait();
+    launch_dependents();
     if (stamper) stamps[0] = globaltimer_ns();
 
     if (p.phases & kLLSend) {
         const uint32_t epoch = static_cast<uint32_t>(*reinterpret_cast<volatile uint64_t*>(c.local_ws + kWsLLCalls + 0)) + 1;
         const int half = epoch & 1;
-        int* finish = ll_finish_dispatch(c);
         int* s_topk = reinterpret_cast<int*>(smem);                         // [T * K]
         uint8_t* s_msg = smem + align_up(T * K * 4, 128);                   // [2][msg_bytes aligned]
         const int msg_stride = align_up(msg_bytes, 128);
+        // the first row's load is issued before the routing is read: two independent trips to memory overlap
+        int4 first_raw = make_int4(0, 0, 0, 0);
+        if (bid < T && tid * 8 < H) first_raw = ld_nc_int4(p.x + (static_cast<int64_t>(bid) * H + tid * 8) * 2);
         for (int i = tid; i < T * K; i += blockDim.x) {
             const int64_t raw = p.topk_idx[i];
             s_topk[i] = (raw >= 0 && raw < E) ? static_cast<int>(raw) : -1;
         }
         __syncthreads();
 
+        // ---- the per-expert counts first: they depend on the routing only
+        // (by the warps that do not send, while the others cast and send)
+        const int num_publishers = num_warps > K ? num_warps - K : num_warps;
+        auto publish_counts = [&](int pw) {
+            for (int e = bid + pw * nb; e < E; e += nb * num_publishers) {
+                const int dst = e / EL;
+                if (ld_volatile_int(mask + dst) != 0) continue;
+                int total = 0;
+                for (int i = lane; i < T * K; i += 32) total += s_topk[i] == e;
+                total = warp_reduce_sum(total);
+                if (lane == 0) {
+                    uint64_t* word = reinterpret_cast<uint64_t*>(c.heap[dst] + p.off_recv_count[half]) + (e - dst * EL) * R + c.rank;
+                    st_release_sys_u64(word, pack_epoch(epoch, static_cast<uint32_t>(total)));
+                }
+            }
+        };
+        if (num_warps > K && warp >= K) publish_counts(warp - K);
+
         int iter = 0;
+        uint64_t* pending_hdr = nullptr;        // lane 0 of a sending warp: header of the message issued one token ago
+        uint64_t pending_val = 0;
         for (int t = bid; t < T; t += nb, ++iter) {
             uint8_t* msg = s_msg + (iter & 1) * msg_stride;
             uint8_t* payload = msg + 16;
             // ---- cast / copy the row into the message
             const int ch = tid * 8;
             const bool active = ch < H;
-            int4 raw = make_int4(0, 0, 0, 0);
-            if (active) raw = ld_nc_int4(p.x + (static_cast<int64_t>(t) * H + ch) * 2);
+            int4 raw = first_raw;
+            if (active && iter != 0) raw = ld_nc_int4(p.x + (static_cast<int64_t>(t) * H + ch) * 2);
             if (!p.use_fp8) {
                 if (active) *reinterpret_cast<int4*>(payload + ch * 2) = raw;
             } else {
@@ -289,40 +322,40 @@ __global__ void __launch_bounds__(1024, 1) ll_dispatch_kernel(const __grid_const
             if (warp < K) {
                 const int e = s_topk[t * K + warp];
                 const int dst = e >= 0 ? e / EL : -1;
-                if (e >= 0 && ld_volatile_int(mask + dst) == 0) {
+                const bool send = e >= 0 && ld_volatile_int(mask + dst) == 0;
+                int slot = 0;
+                if (send) {
                     int before = 0;
                     for (int i = lane; i < t * K; i += 32) before += s_topk[i] == e;
-                    const int slot = warp_reduce_sum(before);
-                    if (lane == 0) {
+                    slot = warp_reduce_sum(before);
+                }
+                if (lane == 0) {
+                    uint64_t* hdr = nullptr;
+                    if (send) {
                         uint8_t* dst_msg = c.heap[dst] + p.off_recv_x[half] +
                                            ((static_cast<uint64_t>(e - dst * EL) * R + c.rank) * Tm + slot) * msg_bytes;
-                        *reinterpret_cast<int4*>(dst_msg) = make_int4(t, warp, 0, 0);
                         bulk_s2g(dst_msg + 16, payload, msg_bytes - 16);
-                        bulk_commit();
-                        bulk_wait_all();
-                        fence_proxy_async_all();
-                        red_add_release_gpu_s32(finish + e, 1);   // the flag sender acquires this and releases to the peer
+                        hdr = reinterpret_cast<uint64_t*>(dst_msg);
                     }
+                    bulk_commit();              // (an empty group when nothing was sent keeps the group count in step)
+                    // the message before this one has landed once all but the newest group are complete: flag it now
+                    bulk_wait<1>();
+                    if (pending_hdr != nullptr) st_relaxed_sys_u64(pending_hdr, pending_val);
+                    pending_hdr = hdr;
+                    pending_val = pack_epoch(epoch, static_cast<uint32_t>(t | (warp << 16)));
                 }
                 __syncwarp();
             }
         }
-        if (stamper) stamps[1] = globaltimer_ns();
-        // ---- publish the per-expert counts once every message of the expert has landed
-        for (int e = bid + warp * nb; e < E; e += nb * num_warps) {
-            const int dst = e / EL;
-            if (ld_volatile_int(mask + dst) != 0) continue;
-            int total = 0;
-            for (int i = lane; i < T * K; i += 32) total += s_topk[i] == e;
-            total = warp_reduce_sum(total);
+        if (warp < K) {
             if (lane == 0) {
-                bounded_wait(w, kStatusLLRecv, dst, e, [&]() { return ld_acquire_gpu_s32(finish + e) >= total; });
-                finish[e] = 0;
-                uint64_t* word = reinterpret_cast<uint64_t*>(c.heap[dst] + p.off_recv_count[half]) + (e - dst * EL) * R + c.rank;
-                st_release_sys_u64(word, pack_epoch(epoch, static_cast<uint32_t>(total)));
+                bulk_wait_all();
+                if (pending_hdr != nullptr) st_relaxed_sys_u64(pending_hdr, pending_val);
             }
             __syncwarp();
         }
+        if (num_warps <= K) publish_counts(warp);
+        if (stamper) stamps[1] = globaltimer_ns();
         if (stamper) stamps[2] = globaltimer_ns();
         ll_phase_done(c, 0, nb);
         if (stamper) stamps[3] = globaltimer_ns();
@@ -331,70 +364,87 @@ __global__ void __launch_bounds__(1024, 1) ll_dispatch_kernel(const __grid_const
     if (p.phases & kLLRecv) {
         const uint32_t epoch = static_cast<uint32_t>(*reinterpret_cast<volatile uint64_t*>(c.local_ws + kWsLLCalls + 1)) + 1;
         const int half = epoch & 1;
-        __shared__ int s_cnt[kMaxRanks], s_begin[kMaxRanks + 1];
+        // Work item = (local expert, source rank). A block takes its items in rounds of up to kRound: first the count
+        // words of all sources of those experts (the rows of a source start behind the rows of the sources before it),
+        // all in parallel, then -- without another block-wide barrier -- the rows of its own sources, a row cut into
+        // kParts pieces of one warp each so that the few rows of an item keep every warp busy.
+        constexpr int kRound = 8, kParts = 8;
+        __shared__ int s_cnt[kRound][kMaxRanks], s_begin[kRound][kMaxRanks];
         const int rows_per_expert = R * Tm;
         const int sf_per_row = p.use_fp8 ? (p.use_ue8m0 ? H / 512 : H / 128) : 0;
-        // work item = (local expert, source rank): a block waits for the counts of all sources of that expert
-        // (it needs the prefix), then packs the rows of its own source only
-        for (int item = bid; item < EL * R; item += nb) {
-            const int le = item / R, src_rank = item % R;
+        const int vec_per_part = ceil_div(payload_bytes / 16, kParts);
+        for (int item0 = bid; item0 < EL * R; item0 += nb * kRound) {
+            int n_items = 0;
+            while (n_items < kRound && item0 + n_items * nb < EL * R) ++n_items;
             __syncthreads();
-            if (tid < R) {
+            for (int q = tid; q < n_items * R; q += blockDim.x) {
+                const int it = q / R, s = q % R;
+                const int le = (item0 + it * nb) / R;
                 int cnt = 0;
-                if (ld_volatile_int(mask + tid) == 0) {
-                    const uint64_t* word = reinterpret_cast<const uint64_t*>(c.heap[c.rank] + p.off_recv_count[half]) + le * R + tid;
+                if (ld_volatile_int(mask + s) == 0) {
+                    const uint64_t* word = reinterpret_cast<const uint64_t*>(c.heap[c.rank] + p.off_recv_count[half]) + le * R + s;
                     uint64_t v = 0;
-                    const uint64_t t0 = globaltimer_ns();
-                    const bool ok = ll_wait(w, c, p.shrink, kStatusLLRecv, tid, le, [&]() {
+                    const bool ok = ll_wait(w, c, p.shrink, kStatusLLRecv, s, le, [&]() {
                         v = ld_acquire_sys_u64(word);
                         return epoch_matches(v, epoch);
                     });
                     if (ok) cnt = static_cast<int>(static_cast<uint32_t>(v));
-                    if (p.wait_stats != nullptr && src_rank == 0)
-                        atomicAdd(reinterpret_cast<unsigned long long*>(p.wait_stats + tid), globaltimer_ns() - t0);
                 }
-                s_cnt[tid] = cnt;
+                s_cnt[it][s] = cnt;
             }
             __syncthreads();
-            if (tid == 0) {
+            if (tid < n_items) {
+                const int item = item0 + tid * nb, le = item / R, src_rank = item % R;
                 int acc = 0;
                 for (int s = 0; s < R; ++s) {
-                    s_begin[s] = acc;
+                    s_begin[tid][s] = acc;
                     if (src_rank == 0)
-                        p.packed_recv_layout_range[le * R + s] = (static_cast<int64_t>(acc) << 32) | static_cast<uint32_t>(s_cnt[s]);
-                    acc += s_cnt[s];
+                        p.packed_recv_layout_range[le * R + s] = (static_cast<int64_t>(acc) << 32) | static_cast<uint32_t>(s_cnt[tid][s]);
+                    acc += s_cnt[tid][s];
                 }
-                s_begin[R] = acc;
                 if (src_rank == 0) {
                     p.packed_recv_count[le] = acc;
                     if (p.cumulative_stats != nullptr) atomicAdd(p.cumulative_stats + le, acc);
                 }
             }
             __syncthreads();
-            const int begin = s_begin[src_rank], count = s_cnt[src_rank];
-            for (int slot = warp; slot < count; slot += num_warps) {
-                const int j = begin + slot;
-                const uint8_t* src = c.heap[c.rank] + p.off_recv_x[half] + ((static_cast<uint64_t>(le) * R + src_rank) * Tm + slot) * msg_bytes;
-                const int64_t out_row = static_cast<int64_t>(le) * rows_per_expert + j;
-                if (lane == 0) {
-                    const int4 hdr = *reinterpret_cast<const int4*>(src);
-                    p.packed_recv_src_info[out_row] = hdr.x | (hdr.y << 16);
-                }
-                uint8_t* dst = p.packed_recv_x + out_row * payload_bytes;
-                for (int v = lane; v < payload_bytes / 16; v += 32 * 8) {   // eight loads in flight per lane
-                    int4 tmp[8];
+            for (int it = 0; it < n_items; ++it) {
+                const int item = item0 + it * nb, le = item / R, src_rank = item % R;
+                const int begin = s_begin[it][src_rank], count = s_cnt[it][src_rank];
+                for (int u = warp; u < count * kParts; u += num_warps) {
+                    const int slot = u / kParts, part = u % kParts;
+                    const int j = begin + slot;
+                    const uint8_t* src = c.heap[c.rank] + p.off_recv_x[half] + ((static_cast<uint64_t>(le) * R + src_rank) * Tm + slot) * msg_bytes;
+                    const int64_t out_row = static_cast<int64_t>(le) * rows_per_expert + j;
+                    // the header is the message's arrival flag: written last by the sender, tagged with the call number
+                    uint64_t hdr = 0;
+                    const uint64_t t0 = (p.wait_stats != nullptr && lane == 0) ? globaltimer_ns() : 0;
+                    const bool landed = ll_wait(w, c, p.shrink, kStatusLLRecv, src_rank, le, [&]() {
+                        hdr = ld_acquire_sys_u64(reinterpret_cast<const uint64_t*>(src));
+                        return epoch_matches(hdr, epoch);
+                    });
+                    if (!__all_sync(0xffffffffu, landed)) break;      // reported, or the source is masked now: its rows stay unwritten
+                    if (lane == 0 && part == 0) {
+                        p.packed_recv_src_info[out_row] = static_cast<int>(static_cast<uint32_t>(hdr));
+                        if (p.wait_stats != nullptr) atomicAdd(reinterpret_cast<unsigned long long*>(p.wait_stats + src_rank), globaltimer_ns() - t0);
+                    }
+                    uint8_t* dst = p.packed_recv_x + out_row * payload_bytes;
+                    const int v_end = min(payload_bytes / 16, (part + 1) * vec_per_part);
+                    for (int v = part * vec_per_part + lane; v < v_end; v += 32 * 4) {   // four loads in flight per lane
+                        int4 tmp[4];
 #pragma unroll
-                    for (int u = 0; u < 8; ++u)
-                        if (v + 32 * u < payload_bytes / 16) tmp[u] = ld_nc_int4(src + 16 + (v + 32 * u) * 16);
+                        for (int q = 0; q < 4; ++q)
+                            if (v + 32 * q < v_end) tmp[q] = ld_nc_int4(src + 16 + (v + 32 * q) * 16);
 #pragma unroll
-                    for (int u = 0; u < 8; ++u)
-                        if (v + 32 * u < payload_bytes / 16) st_na_int4(dst + (v + 32 * u) * 16, tmp[u]);
-                }
-                if (sf_per_row > 0) {
-                    const uint32_t* sf = reinterpret_cast<const uint32_t*>(src + 16 + H);
-                    uint32_t* out_sf = reinterpret_cast<uint32_t*>(p.packed_recv_sf);
-                    for (int i = lane; i < sf_per_row; i += 32)
-                        out_sf[(static_cast<int64_t>(le) * sf_per_row + i) * rows_per_expert + j] = sf[i];
+                        for (int q = 0; q < 4; ++q)
+                            if (v + 32 * q < v_end) st_na_int4(dst + (v + 32 * q) * 16, tmp[q]);
+                    }
+                    if (sf_per_row > 0 && part == kParts - 1) {
+                        const uint32_t* sf = reinterpret_cast<const uint32_t*>(src + 16 + H);
+                        uint32_t* out_sf = reinterpret_cast<uint32_t*>(p.packed_recv_sf);
+                        for (int i = lane; i < sf_per_row; i += 32)
+                            out_sf[(static_cast<int64_t>(le) * sf_per_row + i) * rows_per_expert + j] = sf[i];
+                    }
                 }
             }
         }
@@ -421,11 +471,16 @@ __global__ void __launch_bounds__(512, 1) ll_combine_kernel(const __grid_constan
     const int meta_bytes = p.use_logfmt ? ll_logfmt_meta_bytes(H) : 0;
     const int slot_bytes = row_bytes + meta_bytes;
     const int* mask = ll_mask(c);
+    dependency_wait();
+    launch_dependents();
+    // phase timestamps of block 0 (ns): start, rows issued, flags raised, send phase handed over, tokens reduced, end
+    uint64_t* stamps = reinterpret_cast<uint64_t*>(reinterpret_cast<uint8_t*>(c.local_ws) + kWsTimelineOffsetBytes) + 8;
+    const bool stamper = bid == 0 && tid == 0;
+    if (stamper) stamps[0] = globaltimer_ns();
 
     if (p.phases & kLLSend) {
         const uint32_t epoch = static_cast<uint32_t>(*reinterpret_cast<volatile uint64_t*>(c.local_ws + kWsLLCalls + 2)) + 1;
         const int half = epoch & 1;
-        int* finish = ll_finish_combine(c);
         __shared__ int s_pref[kMaxLocalExperts + 1];
         // rows per local expert (begin + count of the last source rank), prefix-summed by warp 0
         if (warp == 0) {
@@ -460,6 +515,7 @@ __global__ void __launch_bounds__(512, 1) ll_combine_kernel(const __grid_constan
         }
         __syncwarp();
         uint32_t parity = 0;
+        uint64_t* pending_flag = nullptr;       // lane 0: flag of the row issued one iteration ago
         for (int g = bid * num_warps + warp; g < total_rows; g += nb * num_warps) {
             int le = 0;
             {   // largest le with s_pref[le] <= g
@@ -495,26 +551,22 @@ __global__ void __launch_bounds__(512, 1) ll_combine_kernel(const __grid_constan
             if (lane == 0) {
                 bulk_s2g(c.heap[s] + p.off_combine_x[half] + (static_cast<uint64_t>(k) * Tm + token) * slot_bytes, buf, send_bytes);
                 bulk_commit();
-                bulk_wait_all();
-                fence_proxy_async_all();
-                red_add_release_gpu_s32(finish + le * R + s, 1);
+                // the row before this one has landed once all but the newest group are complete: raise its flag now
+                bulk_wait<1>();
+                if (pending_flag != nullptr) st_relaxed_sys_u64(pending_flag, pack_epoch(epoch, 1));
+                pending_flag = reinterpret_cast<uint64_t*>(c.heap[s] + p.off_combine_flag[half]) + static_cast<uint64_t>(k) * Tm + token;
             }
             __syncwarp();
         }
-        // ---- one flag per (expert, destination rank) once all its rows have landed
-        for (int q = bid + warp * nb; q < EL * R; q += nb * num_warps) {
-            const int le = q / R, s = q % R;
-            const int cnt = static_cast<int>(p.layout_range[q] & 0xffffffff);
-            if (cnt == 0 || ld_volatile_int(mask + s) != 0) continue;
-            if (lane == 0) {
-                bounded_wait(w, kStatusLLCombine, s, q, [&]() { return ld_acquire_gpu_s32(finish + q) >= cnt; });
-                finish[q] = 0;
-                uint64_t* word = reinterpret_cast<uint64_t*>(c.heap[s] + p.off_combine_flag[half]) + (c.rank * EL + le);
-                st_release_sys_u64(word, pack_epoch(epoch, 1));
-            }
-            __syncwarp();
+        if (stamper) stamps[1] = globaltimer_ns();
+        if (lane == 0) {
+            bulk_wait_all();
+            if (pending_flag != nullptr) st_relaxed_sys_u64(pending_flag, pack_epoch(epoch, 1));
         }
+        __syncwarp();
+        if (stamper) stamps[2] = globaltimer_ns();
         ll_phase_done(c, 2, nb);
+        if (stamper) stamps[3] = globaltimer_ns();
     }
 
     if (p.phases & kLLRecv) {
@@ -530,7 +582,7 @@ __global__ void __launch_bounds__(512, 1) ll_combine_kernel(const __grid_constan
                 const int e = (raw >= 0 && raw < E) ? static_cast<int>(raw) : -1;
                 int ok = 0;
                 if (e >= 0 && ld_volatile_int(mask + e / EL) == 0) {
-                    const uint64_t* word = reinterpret_cast<const uint64_t*>(c.heap[c.rank] + p.off_combine_flag[half]) + e;
+                    const uint64_t* word = reinterpret_cast<const uint64_t*>(c.heap[c.rank] + p.off_combine_flag[half]) + static_cast<uint64_t>(tid) * Tm + t;
                     const uint64_t t0 = globaltimer_ns();
                     ok = ll_wait(w, c, p.shrink, kStatusLLCombine, e / EL, e, [&]() { return epoch_matches(ld_acquire_sys_u64(word), epoch); });
                     if (p.wait_stats != nullptr) atomicAdd(reinterpret_cast<unsigned long long*>(p.wait_stats + e / EL), globaltimer_ns() - t0);
@@ -655,7 +707,9 @@ __global__ void __launch_bounds__(512, 1) ll_combine_kernel(const __grid_constan
                 st_na_int4(p.combined_x + (static_cast<int64_t>(t) * H + ch) * 2, out);
             }
         }
+        if (stamper) stamps[4] = globaltimer_ns();
         ll_phase_done(c, 3, nb);
+        if (stamper) stamps[5] = globaltimer_ns();
     }
 }
 
@@ -670,8 +724,33 @@ __global__ void ll_mask_kernel(uint64_t* local_ws, int rank, int value, int* out
     }
 }
 
-cudaError_t coop_launch(const void* fn, void** args, int grid, int block, int smem, cudaStream_t stream) {
-    return cudaLaunchCooperativeKernel(fn, dim3(grid), dim3(block), args, smem, stream);
+// Cooperative (all blocks resident: blocks of one rank wait for blocks of other ranks, which in turn may wait for blocks
+// of this rank that would otherwise not be scheduled yet) and programmatic dependent (the grid may become resident while
+// the kernel ahead of it in the stream drains; it calls dependency_wait() before it touches anything).
+template <typename Params>
+cudaError_t coop_launch(void (*fn)(const Multi<Params>), const Multi<Params>& m, int grid, int block, int smem, cudaStream_t stream) {
+    static const bool plain = [] { const char* v = std::getenv("EP_LL_PLAIN_LAUNCH"); return v != nullptr && v[0] == '1'; }();
+    static const bool no_pdl = [] { const char* v = std::getenv("EP_DISABLE_PDL"); return v != nullptr && v[0] == '1'; }();
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(grid);
+    cfg.blockDim = dim3(block);
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[2];
+    int n = 0;
+    if (!plain) {
+        attr[n].id = cudaLaunchAttributeCooperative;
+        attr[n].val.cooperative = 1;
+        ++n;
+    }
+    if (!no_pdl) {
+        attr[n].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+        attr[n].val.programmaticStreamSerializationAllowed = 1;
+        ++n;
+    }
+    cfg.attrs = attr;
+    cfg.numAttrs = n;
+    return cudaLaunchKernelEx(&cfg, fn, m);
 }
 
 }  // namespace
@@ -680,13 +759,11 @@ cudaError_t launch_ll_dispatch(const Multi<LLDispatchParams>& m, int num_sms, cu
     const LLDispatchParams& p = m.r[0];
     const int msg_stride = align_up(ll_dispatch_msg_bytes(p.hidden, p.use_fp8), 128);
     const int smem_bytes = align_up(p.num_max_tokens * p.num_topk * 4, 128) + 2 * msg_stride;
-    cudaError_t err = cudaFuncSetAttribute(ll_dispatch_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_bytes);
+    cudaError_t err = prepare_kernel(ll_dispatch_kernel, smem_bytes);
     if (err != cudaSuccess) return err;
     Multi<LLDispatchParams> copy = m;
     copy.blocks_per_rank = num_sms;
-    void* args[] = {&copy};
-    // cooperative: the blocks of the SEND phase wait on counters that other blocks advance
-    return coop_launch(reinterpret_cast<const void*>(ll_dispatch_kernel), args, m.num_vranks * num_sms, 1024, smem_bytes, stream);
+    return coop_launch(ll_dispatch_kernel, copy, m.num_vranks * num_sms, 1024, smem_bytes, stream);
 }
 
 cudaError_t launch_ll_combine(const Multi<LLCombineParams>& m, int num_sms, int smem_optin, cudaStream_t stream) {
@@ -698,12 +775,11 @@ cudaError_t launch_ll_combine(const Multi<LLCombineParams>& m, int num_sms, int 
     const int smem_bytes = warps * stage;
     // the receive phase of a LogFMT call keeps three words per (lane, group) in the same shared memory
     if (p.use_logfmt && p.num_topk * (p.hidden / 128) * 12 > smem_bytes) return cudaErrorInvalidValue;
-    cudaError_t err = cudaFuncSetAttribute(ll_combine_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_bytes);
+    cudaError_t err = prepare_kernel(ll_combine_kernel, smem_bytes);
     if (err != cudaSuccess) return err;
     Multi<LLCombineParams> copy = m;
     copy.blocks_per_rank = num_sms;
-    void* args[] = {&copy};
-    return coop_launch(reinterpret_cast<const void*>(ll_combine_kernel), args, m.num_vranks * num_sms, warps * 32, smem_bytes, stream);
+    return coop_launch(ll_combine_kernel, copy, m.num_vranks * num_sms, warps * 32, smem_bytes, stream);
 }
 
 cudaError_t ll_update_mask(uint64_t* local_ws, int rank, int value, cudaStream_t stream) {

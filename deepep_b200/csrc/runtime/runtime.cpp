@@ -149,10 +149,12 @@ std::vector<int64_t> Runtime::last_dispatch_phases() {
 
 std::vector<int64_t> Runtime::last_timeline() {
     CUDA_RUNTIME_CHECK(cudaDeviceSynchronize());
-    uint64_t raw[8];
+    uint64_t raw[16];
     CUDA_RUNTIME_CHECK(cudaMemcpy(raw, reinterpret_cast<uint8_t*>(local_ws_) + kWsTimelineOffsetBytes, sizeof(raw), cudaMemcpyDeviceToHost));
     std::vector<int64_t> out;
     for (int i = 0; i < 8; ++i) out.push_back(raw[i] == 0 ? -1 : static_cast<int64_t>(raw[i] - raw[0]));
+    // the low-latency combine kernel's phase stamps (block 0), relative to its own start
+    for (int i = 8; i < 14; ++i) out.push_back(raw[i] == 0 ? -1 : static_cast<int64_t>(raw[i] - raw[8]));
     return out;
 }
 

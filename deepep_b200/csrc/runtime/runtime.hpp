@@ -136,7 +136,9 @@ public:
     // -1 = not measured (the first four need mode 2)
     std::vector<float> last_timings();
     // %globaltimer stamps of the last dispatch kernel, dispatch epilogue, combine send and combine reduce kernel:
-    // {start, end} each, ns relative to the start of the dispatch kernel (-1 = never ran). Synchronises the device.
+    // {start, end} each, ns relative to the start of the dispatch kernel (-1 = never ran); then six phase stamps of
+    // the last low-latency combine kernel (start, rows issued, flags raised, send handed over, tokens reduced, end)
+    // relative to its start. Synchronises the device.
     std::vector<int64_t> last_timeline();
 
     // Phase timestamps (ns after kernel start) of the last dispatch kernel: totals counted, order pass done, peers'
