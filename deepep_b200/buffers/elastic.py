@@ -148,11 +148,21 @@ class ElasticBuffer:
         self.num_bytes = num_bytes
         self.num_max_tokens_per_rank = num_max_tokens_per_rank
 
+        # EP_HEAP_BACKEND=vmm: the heap comes from CUDA's virtual memory management and the CPU segment, if any, sits
+        # in the same address range right behind the GPU segment; default: cudaMalloc + CUDA IPC, CPU segment apart
+        self.heap_is_vmm = bool(_C.Runtime.heap_backend_is_vmm())
         self.runtime = _C.Runtime(self.rank_idx, self.num_ranks, num_bytes, float(num_gpu_timeout_secs),
-                                  float(num_cpu_timeout_secs))
+                                  float(num_cpu_timeout_secs), num_cpu_bytes if self.heap_is_vmm else 0)
         self._destroyed = False
-        self._connect_host_segments()
+        if not self.heap_is_vmm:
+            self._connect_host_segments()
         self._connect()
+        if self.heap_is_vmm:
+            self.host_segments = []
+            if num_cpu_bytes > 0:
+                # (the emulated cluster completes the list once all virtual ranks exist)
+                ranks = [self.rank_idx] if getattr(self.group, 'is_local_emulation', False) else range(self.num_ranks)
+                self.host_segments = [_C.HostSegment.window(self.runtime, r) for r in ranks]
 
         self.num_scaleout_ranks, self.num_scaleup_ranks = self.get_logical_domain_size()
         self.scaleout_rank_idx = self.rank_idx // self.num_scaleup_ranks
@@ -176,6 +186,7 @@ class ElasticBuffer:
         torch.cuda.synchronize()
         if self.num_ranks > 1:
             dist.barrier(group=self.group)
+            self.runtime.finish_export()       # every peer has mapped this rank's heap: stop handing out descriptors
         torch.cuda.synchronize()
 
     def _connect_host_segments(self) -> None:

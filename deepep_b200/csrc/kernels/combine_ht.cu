@@ -236,7 +236,8 @@ __global__ void __launch_bounds__(kEpiWarps * 32) combine_epilogue_kernel(const 
             }
             flags_ok = __all_sync(0xffffffffu, ok);
             if (!flags_ok) break;
-            fence_proxy_async_all();    // the rows are read through the async proxy below
+            // (the rows are then read with bulk copies, which fetch from L2, where the senders' completed writes are;
+            // a full async-proxy fence per token would serialise the warps of the SM at microseconds apiece)
         }
         const int slot_lane = e < 0 ? -1 : (p.use_rank_layout ? e / EL : lane);
         uint32_t mask = slot_lane >= 0 ? (1u << slot_lane) : 0u;
@@ -533,9 +534,10 @@ __global__ void __launch_bounds__(1024, 1) combine_kernel(const __grid_constant_
     if (lane == 0) flush_sent();
     __syncwarp();
 
+    // (no fence here: wait_group confirms the rows; the grid barrier's release / acquire at GPU scope and the release
+    // store of the completion words at system scope order every store of this grid, the top-k weights written with
+    // plain peer stores included, before those words)
     bulk_wait_all();
-    fence_proxy_async_all();
-    __threadfence_system();
     grid_barrier(w, c.local_ws + kWsGridBarrier, p.grid_bar_base + nb, 3);
     if (bid == 0 && tid == 0) {   // ready for the next launch (stream order)
         c.local_ws[kWsWork] = 0;

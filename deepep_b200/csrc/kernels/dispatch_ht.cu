@@ -531,9 +531,11 @@ __global__ void __launch_bounds__(1024, 1) dispatch_kernel(const __grid_constant
     // ---------------------------------------------------------------- D. finish
     if (stamper) stamps[5] = globaltimer_ns();
     launch_dependents();          // the epilogue's blocks may become resident from here on
+    // wait_group confirms that the records have been written. No fence follows: fences at system scope and full
+    // async-proxy fences were measured at 5 to 7 us each while stores of other warps are still in flight, and the chain
+    // below (block-wide barrier, acquire-release add on the grid counter, release store of the completion words by the
+    // last block) already orders every store of this grid before the completion words.
     bulk_wait_all();
-    fence_proxy_async_all();
-    __threadfence_system();
     if (stamper) stamps[6] = globaltimer_ns();
     // The last block to arrive cleans up and tells the peers; nobody spins here.
     __syncthreads();

@@ -16,6 +16,12 @@ struct GemmParams {
                                  // null = one group with rows [0, M)
     int group_alignment;
     int zero_gap;                // 1: rows of a tile beyond its group's end are written as zeros (needs group_alignment % 128 == 0)
+    // Groups along K (bf16 only): C[g][M, N] = A[:, k range of g] * B[:, k range of g]^T with the k range of group g =
+    // [align(group_end[g-1], group_alignment), group_end[g]) -- the weight gradients of all experts in one launch, the
+    // rows of an expert being the contraction dimension. A is [M, K], B is [N, K] (one matrix), columns of a range
+    // beyond its end up to the next multiple of 64 must be zero. A group without rows gives zeros.
+    int k_grouped;
+    int64_t c_group_stride;      // elements between C[g] and C[g + 1]
     __nv_bfloat16* C;
     int64_t ldc;                 // elements between rows of C
     // e4m3 inputs: fp32 block scales (ignored for bf16)

@@ -18,6 +18,7 @@ namespace {
 
 struct Tile {
     int g, m0, m_end, n0;
+    int kb0, kb1;       // k-blocks [kb0, kb1) of this tile (all of K unless the problem is grouped along K)
 };
 
 // Walks the tiles of a (grouped) problem in a fixed order: group, then bands of kBandM m-blocks, inside a band
@@ -25,12 +26,32 @@ struct Tile {
 struct Scheduler {
     static constexpr int kBandM = 8;
     const GemmParams& p;
-    int tiles_n, BN, BM;
+    int tiles_n, BN, BM, BK;
     int g = 0, base = 0, start = 0, end = 0;
-    __device__ Scheduler(const GemmParams& p_, int bn, int bm = gemm::BM) : p(p_), tiles_n(p_.N / bn), BN(bn), BM(bm) {
-        end = p.group_end != nullptr ? p.group_end[0] : p.M;
+    __device__ Scheduler(const GemmParams& p_, int bn, int bm = gemm::BM, int bk = 64) : p(p_), tiles_n(p_.N / bn), BN(bn), BM(bm), BK(bk) {
+        end = (p.group_end != nullptr && !p.k_grouped) ? p.group_end[0] : p.M;
     }
     __device__ bool get(int t, Tile& out) {
+        if (p.k_grouped) {
+            // groups along K: every group is a full M x N problem over its own range of k (the rows of one expert)
+            const int tiles_m = ceil_div(p.M, BM);
+            const int tiles = tiles_m * tiles_n;
+            if (t >= p.num_groups * tiles) return false;
+            const int gk = t / tiles, local = t % tiles;
+            const int band = local / (kBandM * tiles_n), rem = local % (kBandM * tiles_n);
+            const int band_m = min(kBandM, tiles_m - band * kBandM);
+            out.g = gk;
+            out.m0 = (band * kBandM + rem % band_m) * BM;
+            out.m_end = p.M;
+            out.n0 = (rem / band_m) * BN;
+            const int k_start = gk == 0 ? 0 : align_up(p.group_end[gk - 1], p.group_alignment);
+            const int k_end = max(p.group_end[gk], k_start);
+            out.kb0 = k_start / BK;
+            out.kb1 = ceil_div(k_end, BK);
+            return true;
+        }
+        out.kb0 = 0;
+        out.kb1 = p.K / BK;
         while (g < p.num_groups) {
             const int rows = max(end - start, 0);
             const int tiles_m = ceil_div(rows, BM);
@@ -99,7 +120,9 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
         }
         for (int a = 0; a < C::kAccStages; ++a) {
             mbar_init(tmem_full + a, 1);
-            mbar_init(tmem_empty + a, C::kEpiWarps * 32);
+            // bf16: every epilogue thread arrives once per tile; FP8: one arrival per warp and k-block (an accumulator
+            // pass per k-block makes per-thread arrivals the bottleneck)
+            mbar_init(tmem_empty + a, kFp8 ? C::kEpiWarps : C::kEpiWarps * 32);
         }
         fence_mbar_init();
     }
@@ -115,18 +138,19 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
     if (warp == 0) {
         // ------------------------------------------------------------ TMA producer
         if (lane == 0) {
-            Scheduler sched(p, BN);
+            Scheduler sched(p, BN, BM, C::BK);
             Tile t;
             int s = 0;
             uint32_t ph = 0;
             bool ok = true;
             for (int ti = blockIdx.x; ok && sched.get(ti, t); ti += gridDim.x) {
-                for (int kb = 0; kb < num_kb; ++kb) {
+                const int b_row = (p.k_grouped ? 0 : t.g * p.N) + t.n0;
+                for (int kb = t.kb0; kb < t.kb1; ++kb) {
                     if (!(ok = pipe_wait(pc, empty + s, ph ^ 1))) break;
                     uint8_t* sa = smem + s * C::STAGE;
                     mbar_arrive_expect_tx(full + s, C::STAGE);
                     tma_load_2d(sa, &map_a, kb * C::BK, t.m0, full + s);
-                    tma_load_2d(sa + C::A_BYTES, &map_b, kb * C::BK, t.g * p.N + t.n0, full + s);
+                    tma_load_2d(sa + C::A_BYTES, &map_b, kb * C::BK, b_row, full + s);
                     if (++s == C::kStages) { s = 0; ph ^= 1; }
                 }
             }
@@ -134,7 +158,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
     } else if (warp == 1) {
         // ------------------------------------------------------------ MMA issuer
         if (lane == 0) {
-            Scheduler sched(p, BN);
+            Scheduler sched(p, BN, BM, C::BK);
             Tile t;
             constexpr uint32_t idesc = make_idesc<kFp8>(BM, BN);
             int s = 0, acc = 0;
@@ -145,7 +169,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
                     if (!(ok = pipe_wait(pc, tmem_empty + acc, acc_ph ^ 1))) break;
                     tc_fence_after();
                 }
-                for (int kb = 0; kb < num_kb; ++kb) {
+                for (int kb = t.kb0; kb < t.kb1; ++kb) {
                     if constexpr (kFp8) {
                         if (!(ok = pipe_wait(pc, tmem_empty + acc, acc_ph ^ 1))) break;
                     }
@@ -156,7 +180,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
                     const uint32_t d_addr = tmem_base + acc * BN;
 #pragma unroll
                     for (int k = 0; k < C::BK / C::UMMA_K; ++k) {
-                        const uint32_t accumulate = kFp8 ? (k != 0) : ((kb | k) != 0);
+                        const uint32_t accumulate = kFp8 ? (k != 0) : (kb != t.kb0 || k != 0);
                         umma<kFp8>(d_addr, da + 2 * k, db + 2 * k, idesc, accumulate);
                     }
                     umma_commit(empty + s);
@@ -168,7 +192,8 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
                 }
                 if constexpr (!kFp8) {
                     if (!ok) break;
-                    umma_commit(tmem_full + acc);
+                    if (t.kb1 > t.kb0) umma_commit(tmem_full + acc);
+                    else mbar_arrive(tmem_full + acc);        // an empty k range: nothing was issued, the epilogue writes zeros
                     if (++acc == C::kAccStages) { acc = 0; acc_ph ^= 1; }
                 }
             }
@@ -178,7 +203,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
         const int quarter = warp & 3;                  // the TMEM lanes this warp may read: [32 * quarter, +32)
         const int part = (warp - 2) / 4;               // fp8: which quarter of the columns
         constexpr int kCols = kFp8 ? BN / 4 : BN;      // columns per thread
-        Scheduler sched(p, BN);
+        Scheduler sched(p, BN, BM, C::BK);
         Tile t;
         int acc = 0;
         uint32_t acc_ph = 0;
@@ -188,15 +213,21 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
             const bool row_ok = row < t.m_end && row < p.M;
             const bool zero_row = !row_ok && p.zero_gap && row < p.M;   // alignment gap of the expanded layout
             const uint32_t lane_addr = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16);
-            __nv_bfloat16* c_row = p.C + static_cast<int64_t>(row) * p.ldc + t.n0 + part * kCols;
+            __nv_bfloat16* c_row = p.C + (p.k_grouped ? static_cast<int64_t>(t.g) * p.c_group_stride : 0) +
+                                   static_cast<int64_t>(row) * p.ldc + t.n0 + part * kCols;
             if constexpr (!kFp8) {
                 if (!(ok = pipe_wait(pc, tmem_full + acc, acc_ph))) break;
                 tc_fence_after();
+                const bool empty_k = t.kb1 <= t.kb0;
 #pragma unroll 1
                 for (int c = 0; c < BN / 32; ++c) {
                     uint32_t r[32];
                     tmem_ld_32x32(lane_addr + acc * BN + c * 32, r);
                     tmem_ld_wait();
+                    if (empty_k) {
+#pragma unroll
+                        for (int i = 0; i < 32; ++i) r[i] = 0u;
+                    }
                     if (row_ok) {
 #pragma unroll
                         for (int v = 0; v < 4; ++v) {
@@ -233,7 +264,8 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
                     tmem_ld_32x32(lane_addr + acc * BN + part * kCols, r0);
                     tmem_ld_wait();
                     tc_fence_before();
-                    mbar_arrive(tmem_empty + acc);      // the values are in registers: the accumulator can be reused
+                    __syncwarp();
+                    if (lane == 0) mbar_arrive(tmem_empty + acc);      // the values are in registers: the accumulator can be reused
                     if (++acc == C::kAccStages) { acc = 0; acc_ph ^= 1; }
 #pragma unroll
                     for (int i = 0; i < 32; ++i) sum[i] = fmaf(scale, __uint_as_float(r0[i]), sum[i]);
@@ -326,19 +358,20 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
     if (warp == 0) {
         // ------------------------------------------------------------ TMA producer (both CTAs)
         if (lane == 0) {
-            Scheduler sched(p, C::BN, 2 * BM);
+            Scheduler sched(p, C::BN, 2 * BM, C::BK);
             Tile t;
             int s = 0;
             uint32_t ph = 0;
             bool ok = true;
             for (int ti = pair; ok && sched.get(ti, t); ti += num_pairs) {
-                for (int kb = 0; kb < num_kb; ++kb) {
+                const int b_row = (p.k_grouped ? 0 : t.g * p.N) + t.n0 + static_cast<int>(cta) * (C::BN / 2);
+                for (int kb = t.kb0; kb < t.kb1; ++kb) {
                     if (!(ok = pipe_wait(pc, empty + s, ph ^ 1))) break;
                     uint8_t* sa = smem + s * C::STAGE;
                     if (leader) mbar_arrive_expect_tx(full + s, 2 * C::STAGE);
                     const uint32_t bar = map_to_cta(smem_u32(full + s), 0);
                     tma_load_2d_pair(sa, &map_a, kb * C::BK, t.m0 + static_cast<int>(cta) * BM, bar);
-                    tma_load_2d_pair(sa + C::A_BYTES, &map_b, kb * C::BK, t.g * p.N + t.n0 + static_cast<int>(cta) * (C::BN / 2), bar);
+                    tma_load_2d_pair(sa + C::A_BYTES, &map_b, kb * C::BK, b_row, bar);
                     if (++s == C::kStages) { s = 0; ph ^= 1; }
                 }
             }
@@ -346,7 +379,7 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
     } else if (warp == 1) {
         // ------------------------------------------------------------ MMA issuer (leader only)
         if (leader && lane == 0) {
-            Scheduler sched(p, C::BN, 2 * BM);
+            Scheduler sched(p, C::BN, 2 * BM, C::BK);
             Tile t;
             constexpr uint32_t idesc = make_idesc<false>(2 * BM, C::BN);
             int s = 0, acc = 0;
@@ -355,26 +388,31 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
             for (int ti = pair; ok && sched.get(ti, t); ti += num_pairs) {
                 if (!(ok = pipe_wait(pc, tmem_empty + acc, acc_ph ^ 1))) break;
                 tc_fence_after();
-                for (int kb = 0; kb < num_kb; ++kb) {
+                for (int kb = t.kb0; kb < t.kb1; ++kb) {
                     if (!(ok = pipe_wait(pc, full + s, ph))) break;
                     tc_fence_after();
                     const uint8_t* sa = smem + s * C::STAGE;
                     const uint64_t da = make_smem_desc(sa), db = make_smem_desc(sa + C::A_BYTES);
                     const uint32_t d_addr = tmem_base + acc * C::BN;
 #pragma unroll
-                    for (int k = 0; k < C::BK / C::UMMA_K; ++k) umma_pair_bf16(d_addr, da + 2 * k, db + 2 * k, idesc, (kb | k) != 0);
+                    for (int k = 0; k < C::BK / C::UMMA_K; ++k) umma_pair_bf16(d_addr, da + 2 * k, db + 2 * k, idesc, kb != t.kb0 || k != 0);
                     umma_commit_pair(empty + s);
                     if (++s == C::kStages) { s = 0; ph ^= 1; }
                 }
                 if (!ok) break;
-                umma_commit_pair(tmem_full + acc);
+                if (t.kb1 > t.kb0) {
+                    umma_commit_pair(tmem_full + acc);
+                } else {                                     // an empty k range: nothing was issued, the epilogues write zeros
+                    mbar_arrive_cluster(map_to_cta(smem_u32(tmem_full + acc), 0));
+                    mbar_arrive_cluster(map_to_cta(smem_u32(tmem_full + acc), 1));
+                }
                 if (++acc == C::kAccStages) { acc = 0; acc_ph ^= 1; }
             }
         }
     } else {
         // ------------------------------------------------------------ epilogue warps (both CTAs, own 128 rows)
         const int quarter = warp & 3;
-        Scheduler sched(p, C::BN, 2 * BM);
+        Scheduler sched(p, C::BN, 2 * BM, C::BK);
         Tile t;
         int acc = 0;
         uint32_t acc_ph = 0;
@@ -384,14 +422,19 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
             const bool row_ok = row < t.m_end && row < p.M;
             const bool zero_row = !row_ok && p.zero_gap && row < p.M && row < align_up(t.m_end, p.group_alignment);
             const uint32_t lane_addr = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16);
-            __nv_bfloat16* c_row = p.C + static_cast<int64_t>(row) * p.ldc + t.n0;
+            __nv_bfloat16* c_row = p.C + (p.k_grouped ? static_cast<int64_t>(t.g) * p.c_group_stride : 0) + static_cast<int64_t>(row) * p.ldc + t.n0;
             if (!(ok = pipe_wait(pc, tmem_full + acc, acc_ph))) break;
             tc_fence_after();
+            const bool empty_k = t.kb1 <= t.kb0;
 #pragma unroll 1
             for (int c = 0; c < C::BN / 32; ++c) {
                 uint32_t r[32];
                 tmem_ld_32x32(lane_addr + acc * C::BN + c * 32, r);
                 tmem_ld_wait();
+                if (empty_k) {
+#pragma unroll
+                    for (int i = 0; i < 32; ++i) r[i] = 0u;
+                }
                 if (row_ok) {
 #pragma unroll
                     for (int v = 0; v < 4; ++v) {
@@ -415,6 +458,178 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
 
     tc_fence_before();
     cluster_sync_all();          // nobody frees tensor memory, or leaves, while the peer may still signal or read
+    if (warp == 1) {
+        tc_fence_after();
+        tmem_dealloc_pair(tmem_base, C::kTmemCols);
+    }
+}
+
+// ==================================================================== CTA-pair kernel, e4m3 with software block scaling (256 x 256 tiles)
+// Same division of labour as gemm_pair_kernel; a stage holds a 128-wide k-block (128 bytes per row), and every
+// k-block is an accumulator pass of its own (two passes fit into the 512 columns of tensor memory): the leader
+// commits the pass, the sixteen epilogue warps of each CTA -- four lane quarters x four column quarters of 64 --
+// drain it sixteen columns at a time and add it, times the product of the 1x128 scale of the row and the 128x128
+// scale of the weight block, to fp32 sums in registers. Per flop a pair loads a third less than two lone CTAs with
+// 128 x 128 tiles would, which is what the FP8 rate needs: the main loop is bound by the fill of shared memory.
+struct PairFp8Cfg {
+    static constexpr int BN = 256, BK = 128, UMMA_K = 32;
+    static constexpr int A_BYTES = BM * 128, B_BYTES = (BN / 2) * 128, STAGE = A_BYTES + B_BYTES;
+    static constexpr int kStages = 6;
+    static constexpr int kAccStages = 2;
+    static constexpr int kEpiWarps = 16;
+    static constexpr int kThreads = (2 + kEpiWarps) * 32;
+    static constexpr int kBarBytes = (2 * kStages + 2 * kAccStages) * 8 + 16;
+    static constexpr int kSmem = kStages * STAGE + kBarBytes + 1024;
+    static constexpr int kTmemCols = kAccStages * BN;
+    static constexpr int kColsPerThread = BN / 4;
+};
+
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(PairFp8Cfg::kThreads, 1)
+gemm_pair_fp8_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b, const GemmParams p) {
+    using C = PairFp8Cfg;
+    extern __shared__ uint8_t smem_raw[];
+    uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~static_cast<uintptr_t>(1023));
+    uint64_t* full = reinterpret_cast<uint64_t*>(smem + C::kStages * C::STAGE);
+    uint64_t* empty = full + C::kStages;
+    uint64_t* tmem_full = empty + C::kStages;
+    uint64_t* tmem_empty = tmem_full + C::kAccStages;
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(tmem_empty + C::kAccStages);
+
+    const int warp = warp_id(), lane = lane_id();
+    const uint32_t cta = cluster_ctarank();
+    const bool leader = cta == 0;
+    const int pair = blockIdx.x >> 1, num_pairs = gridDim.x >> 1;
+    const int num_kb = p.K / C::BK;
+    PipeCtx pc{p.error, globaltimer_ns() + p.timeout_ns};
+
+    if (warp == 0 && lane == 0) {
+        prefetch_tensormap(&map_a);
+        prefetch_tensormap(&map_b);
+        for (int s = 0; s < C::kStages; ++s) {
+            mbar_init(full + s, 1);
+            mbar_init(empty + s, 1);
+        }
+        for (int a = 0; a < C::kAccStages; ++a) {
+            mbar_init(tmem_full + a, 1);
+            mbar_init(tmem_empty + a, 2 * C::kEpiWarps);      // one arrival per epilogue warp of either CTA and k-block
+        }
+        fence_mbar_init();
+    }
+    if (warp == 1) {
+        tmem_alloc_pair(tmem_slot, C::kTmemCols);
+        tmem_relinquish_pair();
+    }
+    tc_fence_before();
+    cluster_sync_all();
+    tc_fence_after();
+    const uint32_t tmem_base = *tmem_slot;
+
+    if (warp == 0) {
+        // ------------------------------------------------------------ TMA producer (both CTAs)
+        if (lane == 0) {
+            Scheduler sched(p, C::BN, 2 * BM, C::BK);
+            Tile t;
+            int s = 0;
+            uint32_t ph = 0;
+            bool ok = true;
+            for (int ti = pair; ok && sched.get(ti, t); ti += num_pairs) {
+                for (int kb = 0; kb < num_kb; ++kb) {
+                    if (!(ok = pipe_wait(pc, empty + s, ph ^ 1))) break;
+                    uint8_t* sa = smem + s * C::STAGE;
+                    if (leader) mbar_arrive_expect_tx(full + s, 2 * C::STAGE);
+                    const uint32_t bar = map_to_cta(smem_u32(full + s), 0);
+                    tma_load_2d_pair(sa, &map_a, kb * C::BK, t.m0 + static_cast<int>(cta) * BM, bar);
+                    tma_load_2d_pair(sa + C::A_BYTES, &map_b, kb * C::BK, t.g * p.N + t.n0 + static_cast<int>(cta) * (C::BN / 2), bar);
+                    if (++s == C::kStages) { s = 0; ph ^= 1; }
+                }
+            }
+        }
+    } else if (warp == 1) {
+        // ------------------------------------------------------------ MMA issuer (leader only): one accumulator pass per k-block
+        if (leader && lane == 0) {
+            Scheduler sched(p, C::BN, 2 * BM, C::BK);
+            Tile t;
+            constexpr uint32_t idesc = make_idesc<true>(2 * BM, C::BN);
+            int s = 0, acc = 0;
+            uint32_t ph = 0, acc_ph = 0;
+            bool ok = true;
+            for (int ti = pair; ok && sched.get(ti, t); ti += num_pairs) {
+                for (int kb = 0; kb < num_kb; ++kb) {
+                    if (!(ok = pipe_wait(pc, tmem_empty + acc, acc_ph ^ 1))) break;
+                    if (!(ok = pipe_wait(pc, full + s, ph))) break;
+                    tc_fence_after();
+                    const uint8_t* sa = smem + s * C::STAGE;
+                    const uint64_t da = make_smem_desc(sa), db = make_smem_desc(sa + C::A_BYTES);
+                    const uint32_t d_addr = tmem_base + acc * C::BN;
+#pragma unroll
+                    for (int k = 0; k < C::BK / C::UMMA_K; ++k) umma_pair_fp8(d_addr, da + 2 * k, db + 2 * k, idesc, k != 0);
+                    umma_commit_pair(empty + s);
+                    umma_commit_pair(tmem_full + acc);
+                    if (++s == C::kStages) { s = 0; ph ^= 1; }
+                    if (++acc == C::kAccStages) { acc = 0; acc_ph ^= 1; }
+                }
+            }
+        }
+    } else {
+        // ------------------------------------------------------------ epilogue warps (both CTAs, own 128 rows)
+        const int quarter = warp & 3;                  // the TMEM lanes this warp may read: [32 * quarter, +32)
+        const int part = (warp - 2) / 4;               // which quarter of the 256 columns
+        constexpr int kCols = C::kColsPerThread;
+        Scheduler sched(p, C::BN, 2 * BM, C::BK);
+        Tile t;
+        int acc = 0;
+        uint32_t acc_ph = 0;
+        bool ok = true;
+        const int kblocks_b = p.K / 128;
+        for (int ti = pair; ok && sched.get(ti, t); ti += num_pairs) {
+            const int row = t.m0 + static_cast<int>(cta) * BM + quarter * 32 + lane;
+            const bool row_ok = row < t.m_end && row < p.M;
+            const bool zero_row = !row_ok && p.zero_gap && row < p.M && row < align_up(t.m_end, p.group_alignment);
+            const uint32_t lane_addr = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16);
+            __nv_bfloat16* c_row = p.C + static_cast<int64_t>(row) * p.ldc + t.n0 + part * kCols;
+            float sum[kCols];
+#pragma unroll
+            for (int i = 0; i < kCols; ++i) sum[i] = 0.f;
+            const float* sfb = p.sfb + (static_cast<int64_t>(t.g) * (p.N / 128) + (t.n0 + part * kCols) / 128) * kblocks_b;
+            const float* sfa = p.sfa + static_cast<int64_t>(row_ok ? row : 0) * p.sfa_row_stride;
+            float next_scale = sfa[0] * sfb[0];
+            for (int kb = 0; kb < num_kb; ++kb) {
+                const float scale = next_scale;
+                if (kb + 1 < num_kb) next_scale = sfa[static_cast<int64_t>(kb + 1) * p.sfa_k_stride] * sfb[kb + 1];
+                if (!(ok = pipe_wait(pc, tmem_full + acc, acc_ph))) break;
+                tc_fence_after();
+#pragma unroll
+                for (int c = 0; c < kCols / 16; ++c) {
+                    uint32_t r[16];
+                    tmem_ld_32x16(lane_addr + acc * C::BN + part * kCols + c * 16, r);
+                    tmem_ld_wait();
+#pragma unroll
+                    for (int i = 0; i < 16; ++i) sum[c * 16 + i] = fmaf(scale, __uint_as_float(r[i]), sum[c * 16 + i]);
+                }
+                tc_fence_before();
+                __syncwarp();
+                if (lane == 0) mbar_arrive_cluster(map_to_cta(smem_u32(tmem_empty + acc), 0));
+                if (++acc == C::kAccStages) { acc = 0; acc_ph ^= 1; }
+            }
+            if (ok && zero_row) {
+#pragma unroll
+                for (int v = 0; v < kCols / 8; ++v) *reinterpret_cast<int4*>(c_row + v * 8) = make_int4(0, 0, 0, 0);
+            }
+            if (ok && row_ok) {
+#pragma unroll
+                for (int v = 0; v < kCols / 8; ++v) {
+                    int4 out;
+                    __nv_bfloat162* o2 = reinterpret_cast<__nv_bfloat162*>(&out);
+#pragma unroll
+                    for (int i = 0; i < 4; ++i) o2[i] = __floats2bfloat162_rn(sum[v * 8 + 2 * i], sum[v * 8 + 2 * i + 1]);
+                    *reinterpret_cast<int4*>(c_row + v * 8) = out;
+                }
+            }
+        }
+    }
+
+    tc_fence_before();
+    cluster_sync_all();
     if (warp == 1) {
         tc_fence_after();
         tmem_dealloc_pair(tmem_base, C::kTmemCols);
@@ -467,18 +682,30 @@ static cudaError_t launch_cfg(const CUtensorMap& map_a, const CUtensorMap& map_b
 cudaError_t launch_gemm(const GemmParams& p, const void* a, int64_t a_row_stride_bytes, const void* b, int64_t b_row_stride_bytes,
                         bool fp8, int num_sms, cudaStream_t stream) {
     const int elem = fp8 ? 1 : 2;
-    const int bn = fp8 ? 128 : ((p.N % 256 == 0) ? 256 : 128);
+    // bf16 with 256-wide tiles runs on CTA pairs (EP_GEMM_CTA_PAIR=0 keeps one CTA per tile); a pair needs two SMs.
+    // e4m3 on CTA pairs is opt-in (EP_GEMM_FP8_PAIR=1): with software block scaling the 256 x 256 tile halves the
+    // shared-memory fill per flop, but only two accumulator passes fit into tensor memory and the drain of a pass
+    // (64 columns per epilogue thread) then sets the pace: 0.94 PFLOP/s measured against 1.3 with 128 x 128 tiles and
+    // four passes in flight.
+    const char* pair_env = std::getenv("EP_GEMM_CTA_PAIR");
+    const char* fp8_pair_env = std::getenv("EP_GEMM_FP8_PAIR");
+    const bool pair_enabled = fp8 ? (fp8_pair_env != nullptr && fp8_pair_env[0] == '1') : (pair_env == nullptr || pair_env[0] != '0');
+    const bool use_pair = p.N % 256 == 0 && pair_enabled && num_sms >= 2;
+    const int bn = fp8 ? (use_pair ? 256 : 128) : ((p.N % 256 == 0) ? 256 : 128);
     const int bk = fp8 ? 128 : 64;
     if (p.N % bn != 0 || p.K % bk != 0 || p.M <= 0) return cudaErrorInvalidValue;
-    // bf16 with 256-wide tiles runs on CTA pairs (EP_GEMM_CTA_PAIR=0 keeps one CTA per tile); a pair needs two SMs
-    const char* pair_env = std::getenv("EP_GEMM_CTA_PAIR");
-    const bool pair_enabled = pair_env == nullptr || pair_env[0] != '0';
-    const bool use_pair = !fp8 && bn == 256 && pair_enabled && num_sms >= 2;
+    if (p.k_grouped && (fp8 || p.group_end == nullptr || p.group_alignment % bk != 0)) return cudaErrorInvalidValue;
     CUtensorMap map_a, map_b;
     if (!make_kmajor_map(&map_a, a, elem, static_cast<uint64_t>(p.M), static_cast<uint64_t>(p.K), static_cast<uint64_t>(a_row_stride_bytes), BM) ||
         !make_kmajor_map(&map_b, b, elem, static_cast<uint64_t>(p.num_groups) * p.N, static_cast<uint64_t>(p.K),
                          static_cast<uint64_t>(b_row_stride_bytes), static_cast<uint32_t>(use_pair ? bn / 2 : bn)))
         return cudaErrorInvalidValue;
+    if (fp8 && use_pair) {
+        cudaError_t err = cudaFuncSetAttribute(gemm_pair_fp8_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, PairFp8Cfg::kSmem);
+        if (err != cudaSuccess) return err;
+        gemm_pair_fp8_kernel<<<num_sms & ~1, PairFp8Cfg::kThreads, PairFp8Cfg::kSmem, stream>>>(map_a, map_b, p);
+        return cudaGetLastError();
+    }
     if (fp8) return launch_cfg<128, true>(map_a, map_b, p, num_sms, stream);
     if (bn == 256 && use_pair) {
         cudaError_t err = cudaFuncSetAttribute(gemm_pair_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, PairCfg::kSmem);

@@ -178,34 +178,60 @@ __global__ void __launch_bounds__(256) swiglu_kernel(const uint8_t* __restrict__
     }
 }
 
-// d(gate|up) from d(out): dgate = dout * up * sig * (1 + gate * (1 - sig)), dup = dout * silu(gate)
+// d(gate|up) from d(out): dgate = dout * up * sig * (1 + gate * (1 - sig)), dup = dout * silu(gate), both times the
+// row's gate weight. One block per row (grid-strided), so that the two by-products of the MoE backward pass come out
+// of the same read of (gate, up, dout): the weighted activation silu(gate) * up * w (the operand of the W2 weight
+// gradient) and the gradient of the gate weight, sum_i dout_i * silu(gate_i) * up_i (a row dot product).
 __global__ void __launch_bounds__(256) swiglu_bwd_kernel(const uint8_t* __restrict__ x, const uint8_t* __restrict__ dout, int rows, int inter,
-                                                         const float* __restrict__ row_weight, uint8_t* __restrict__ dx) {
+                                                         const float* __restrict__ row_weight, uint8_t* __restrict__ dx,
+                                                         uint8_t* __restrict__ act_out, float* __restrict__ dweight) {
+    __shared__ float s_part[8];
     const int vec_per_row = inter / 8;
-    const int64_t total = static_cast<int64_t>(rows) * vec_per_row;
-    for (int64_t i = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x; i < total; i += static_cast<int64_t>(gridDim.x) * blockDim.x) {
-        const int row = static_cast<int>(i / vec_per_row), ch = static_cast<int>(i % vec_per_row) * 8;
-        const uint8_t* src = x + (static_cast<int64_t>(row) * 2 * inter + ch) * 2;
-        const int4 g = ld_nc_int4(src), u = ld_nc_int4(src + static_cast<int64_t>(inter) * 2);
-        const int4 d = ld_nc_int4(dout + (static_cast<int64_t>(row) * inter + ch) * 2);
+    for (int row = blockIdx.x; row < rows; row += gridDim.x) {
         const float wr = row_weight != nullptr ? row_weight[row] : 1.f;
-        const __nv_bfloat162* g2 = reinterpret_cast<const __nv_bfloat162*>(&g);
-        const __nv_bfloat162* u2 = reinterpret_cast<const __nv_bfloat162*>(&u);
-        const __nv_bfloat162* d2 = reinterpret_cast<const __nv_bfloat162*>(&d);
-        int4 og, ou;
-        __nv_bfloat162* og2 = reinterpret_cast<__nv_bfloat162*>(&og);
-        __nv_bfloat162* ou2 = reinterpret_cast<__nv_bfloat162*>(&ou);
+        float dot = 0.f;
+        for (int v = threadIdx.x; v < vec_per_row; v += blockDim.x) {
+            const int ch = v * 8;
+            const uint8_t* src = x + (static_cast<int64_t>(row) * 2 * inter + ch) * 2;
+            const int4 g = ld_nc_int4(src), u = ld_nc_int4(src + static_cast<int64_t>(inter) * 2);
+            const int4 d = ld_nc_int4(dout + (static_cast<int64_t>(row) * inter + ch) * 2);
+            const __nv_bfloat162* g2 = reinterpret_cast<const __nv_bfloat162*>(&g);
+            const __nv_bfloat162* u2 = reinterpret_cast<const __nv_bfloat162*>(&u);
+            const __nv_bfloat162* d2 = reinterpret_cast<const __nv_bfloat162*>(&d);
+            int4 og, ou, oa;
+            __nv_bfloat162* og2 = reinterpret_cast<__nv_bfloat162*>(&og);
+            __nv_bfloat162* ou2 = reinterpret_cast<__nv_bfloat162*>(&ou);
+            __nv_bfloat162* oa2 = reinterpret_cast<__nv_bfloat162*>(&oa);
 #pragma unroll
-        for (int j = 0; j < 4; ++j) {
-            const float2 gv = __bfloat1622float2(g2[j]), uv = __bfloat1622float2(u2[j]), dv = __bfloat1622float2(d2[j]);
-            const float sx = 1.f / (1.f + __expf(-gv.x)), sy = 1.f / (1.f + __expf(-gv.y));
-            const float dx_ = dv.x * wr, dy_ = dv.y * wr;
-            og2[j] = __floats2bfloat162_rn(dx_ * uv.x * sx * (1.f + gv.x * (1.f - sx)), dy_ * uv.y * sy * (1.f + gv.y * (1.f - sy)));
-            ou2[j] = __floats2bfloat162_rn(dx_ * gv.x * sx, dy_ * gv.y * sy);
+            for (int j = 0; j < 4; ++j) {
+                const float2 gv = __bfloat1622float2(g2[j]), uv = __bfloat1622float2(u2[j]), dv = __bfloat1622float2(d2[j]);
+                const float sx = 1.f / (1.f + __expf(-gv.x)), sy = 1.f / (1.f + __expf(-gv.y));
+                const float dx_ = dv.x * wr, dy_ = dv.y * wr;
+                og2[j] = __floats2bfloat162_rn(dx_ * uv.x * sx * (1.f + gv.x * (1.f - sx)), dy_ * uv.y * sy * (1.f + gv.y * (1.f - sy)));
+                ou2[j] = __floats2bfloat162_rn(dx_ * gv.x * sx, dy_ * gv.y * sy);
+                // the activation as the forward pass rounded it (bf16), before the weight
+                const __nv_bfloat162 a = __floats2bfloat162_rn(gv.x * sx * uv.x, gv.y * sy * uv.y);
+                const float2 af = __bfloat1622float2(a);
+                dot = fmaf(dv.x, af.x, fmaf(dv.y, af.y, dot));
+                oa2[j] = __floats2bfloat162_rn(af.x * wr, af.y * wr);
+            }
+            uint8_t* dst = dx + (static_cast<int64_t>(row) * 2 * inter + ch) * 2;
+            *reinterpret_cast<int4*>(dst) = og;
+            *reinterpret_cast<int4*>(dst + static_cast<int64_t>(inter) * 2) = ou;
+            if (act_out != nullptr) *reinterpret_cast<int4*>(act_out + (static_cast<int64_t>(row) * inter + ch) * 2) = oa;
         }
-        uint8_t* dst = dx + (static_cast<int64_t>(row) * 2 * inter + ch) * 2;
-        *reinterpret_cast<int4*>(dst) = og;
-        *reinterpret_cast<int4*>(dst + static_cast<int64_t>(inter) * 2) = ou;
+        if (dweight != nullptr) {
+#pragma unroll
+            for (int o = 16; o > 0; o >>= 1) dot += __shfl_xor_sync(0xffffffffu, dot, o);
+            __syncthreads();
+            if ((threadIdx.x & 31) == 0) s_part[threadIdx.x >> 5] = dot;
+            __syncthreads();
+            if (threadIdx.x == 0) {
+                float acc = 0.f;
+                for (int i = 0; i < 8; ++i) acc += s_part[i];      // fixed order: the result does not depend on timing
+                dweight[row] = acc;
+            }
+        }
     }
 }
 
@@ -278,11 +304,13 @@ cudaError_t swiglu(const void* x, int rows, int inter, const float* row_weight, 
     return cudaGetLastError();
 }
 
-cudaError_t swiglu_backward(const void* x, const void* dout, int rows, int inter, const float* row_weight, void* dx, cudaStream_t stream) {
+cudaError_t swiglu_backward(const void* x, const void* dout, int rows, int inter, const float* row_weight, void* dx, void* act_out,
+                            float* dweight, cudaStream_t stream) {
     if (rows == 0) return cudaSuccess;
     if (inter % 8 != 0) return cudaErrorInvalidValue;
-    swiglu_bwd_kernel<<<grid_for(static_cast<int64_t>(rows) * inter / 8), 256, 0, stream>>>(
-        static_cast<const uint8_t*>(x), static_cast<const uint8_t*>(dout), rows, inter, row_weight, static_cast<uint8_t*>(dx));
+    swiglu_bwd_kernel<<<min(rows, 148 * 8), 256, 0, stream>>>(
+        static_cast<const uint8_t*>(x), static_cast<const uint8_t*>(dout), rows, inter, row_weight, static_cast<uint8_t*>(dx),
+        static_cast<uint8_t*>(act_out), dweight);
     return cudaGetLastError();
 }
 

@@ -19,7 +19,10 @@ cudaError_t dequant_1x128(const void* q, const float* scales, int64_t sf_row_str
 // `num_valid_rows` (device, optional) limits the work to the first rows.
 cudaError_t swiglu(const void* x, int rows, int inter, const float* row_weight, const int* num_valid_rows, void* out, bool quant,
                    float* scales, int64_t sf_row_stride, int64_t sf_col_stride, cudaStream_t stream);
-cudaError_t swiglu_backward(const void* x, const void* dout, int rows, int inter, const float* row_weight, void* dx, cudaStream_t stream);
+// dx [rows, 2 * inter] from dout [rows, inter]; optional by-products of the same pass: act_out [rows, inter] bf16 =
+// silu(gate) * up * row_weight and dweight [rows] fp32 = sum_i dout_i * silu(gate_i) * up_i (gradient of the row weight)
+cudaError_t swiglu_backward(const void* x, const void* dout, int rows, int inter, const float* row_weight, void* dx, void* act_out,
+                            float* dweight, cudaStream_t stream);
 cudaError_t transpose_bf16(const void* in, int64_t in_stride, int rows, int cols, void* out, int64_t out_stride, cudaStream_t stream);
 
 }  // namespace ops

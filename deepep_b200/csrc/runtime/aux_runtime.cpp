@@ -4,6 +4,7 @@
 //
 // Parity: csrc/elastic/buffer.hpp:210-524 of the reference (engram_write/fetch, pp_*, agrs_*, all_gather).
 #include <ATen/cuda/CUDAContext.h>
+#include <cstdlib>
 #include <ATen/ops/empty.h>
 #include <pybind11/stl.h>
 #include <torch/extension.h>
@@ -30,8 +31,60 @@ struct FlagSpec {
     bool signal_first = false;
 };
 
+// ---- stream memory operations (0 SMs): the driver writes / waits for a 64-bit word in stream order
+// Parity: csrc/kernels/backend/cuda_driver.cu:12-52 of the reference (batched write / wait-GEQ of AGRS sessions).
+// Opt-in (EP_STREAM_MEMOPS=1): such a wait has no time limit, unlike the wait of the flag kernel, so a peer that
+// never signals blocks the stream until the process gives up; the default keeps every wait bounded.
+struct StreamMemOps {
+    using WriteFn = int (*)(cudaStream_t, unsigned long long, unsigned long long, unsigned int);
+    using WaitFn = int (*)(cudaStream_t, unsigned long long, unsigned long long, unsigned int);
+    WriteFn write = nullptr;
+    WaitFn wait = nullptr;
+    bool enabled = false;
+    StreamMemOps() {
+        const char* v = std::getenv("EP_STREAM_MEMOPS");
+        if (v == nullptr || v[0] != '1') return;
+        cudaDriverEntryPointQueryResult res;
+        void* w = nullptr;
+        void* q = nullptr;
+        if (cudaGetDriverEntryPoint("cuStreamWriteValue64", &w, cudaEnableDefault, &res) != cudaSuccess || res != cudaDriverEntryPointSuccess) return;
+        if (cudaGetDriverEntryPoint("cuStreamWaitValue64", &q, cudaEnableDefault, &res) != cudaSuccess || res != cudaDriverEntryPointSuccess) return;
+        write = reinterpret_cast<WriteFn>(w);
+        wait = reinterpret_cast<WaitFn>(q);
+        enabled = true;
+    }
+};
+
+StreamMemOps& stream_memops() {
+    static StreamMemOps ops;
+    return ops;
+}
+
+bool stream_memops_enabled() { return stream_memops().enabled; }
+
 void flag_op(const std::vector<std::shared_ptr<Runtime>>& rts, const std::vector<FlagSpec>& specs) {
     EP_HOST_ASSERT(!rts.empty() && rts.size() == specs.size() && rts.size() <= kMaxVRanks);
+    if (rts.size() == 1 && stream_memops().enabled) {
+        // one real rank per process: signal and wait as stream operations, no kernel, no SM
+        auto& rt = *rts[0];
+        const auto& s = specs[0];
+        c10::cuda::CUDAGuard guard(static_cast<c10::DeviceIndex>(rt.heap().device()));
+        const cudaStream_t stream = cur_stream();
+        auto signal = [&]() {
+            for (const auto& [peer, off] : s.signals) {
+                EP_HOST_ASSERT(peer >= 0 && peer < rt.num_ranks() && off >= 0 && off + 8 <= rt.num_bytes() && off % 8 == 0);
+                EP_HOST_ASSERT(stream_memops().write(stream, reinterpret_cast<unsigned long long>(rt.heap().peer(peer) + off), s.signal_value, 0) == 0);
+            }
+        };
+        auto wait = [&]() {
+            for (const int64_t off : s.wait_offsets) {
+                EP_HOST_ASSERT(off >= 0 && off + 8 <= rt.num_bytes() && off % 8 == 0);
+                EP_HOST_ASSERT(stream_memops().wait(stream, reinterpret_cast<unsigned long long>(rt.heap().base() + off), s.wait_value, /*CU_STREAM_WAIT_VALUE_GEQ=*/0) == 0);
+            }
+        };
+        if (s.signal_first) { signal(); wait(); } else { wait(); signal(); }
+        return;
+    }
     std::vector<aux::FlagOp> ops(rts.size());
     for (size_t v = 0; v < rts.size(); ++v) {
         auto& rt = *rts[v];
@@ -164,6 +217,7 @@ void register_aux_bindings(py::module_& m) {
         .def_readwrite("status_code", &FlagSpec::status_code)
         .def_readwrite("signal_first", &FlagSpec::signal_first);
     m.def("flag_op", &flag_op);
+    m.def("stream_memops_enabled", &stream_memops_enabled);
     m.def("copy_to_heap", &copy_to_heap);
     m.def("copy_from_heap", &copy_from_heap);
     m.def("reduce_slots", &reduce_slots);
@@ -171,6 +225,11 @@ void register_aux_bindings(py::module_& m) {
     py::class_<HostSegment, std::shared_ptr<HostSegment>>(m, "HostSegment")
         .def_static("create", &HostSegment::create)
         .def_static("open", &HostSegment::open)
+        // the CPU segment of rank `r` inside a virtual-memory heap's address range
+        .def_static("window", [](Runtime& rt, int r) {
+            EP_HOST_ASSERT(rt.heap().num_cpu_bytes() > 0 && r >= 0 && r < rt.num_ranks() && rt.heap().cpu_segment(r) != nullptr);
+            return HostSegment::window(rt.heap().cpu_segment(r), r == rt.rank() ? rt.heap().cpu_segment(r) : nullptr, rt.heap().num_cpu_bytes());
+        })
         .def_property_readonly("name", &HostSegment::name)
         .def_property_readonly("num_bytes", &HostSegment::num_bytes)
         .def("device_ptr", [](const HostSegment& s) { return reinterpret_cast<int64_t>(s.device_ptr()); })
@@ -180,7 +239,9 @@ void register_aux_bindings(py::module_& m) {
             EP_HOST_ASSERT(src.is_cuda() && src.is_contiguous() && offset >= 0);
             const int64_t bytes = src.numel() * src.element_size();
             EP_HOST_ASSERT(offset + bytes <= static_cast<int64_t>(s.num_bytes()));
-            CUDA_RUNTIME_CHECK(cudaMemcpyAsync(s.host_ptr() + offset, src.data_ptr(), bytes, cudaMemcpyDeviceToHost, cur_stream()));
+            // (a segment inside a heap window is addressed through its device mapping)
+            uint8_t* dst = s.host_ptr() != nullptr ? s.host_ptr() : s.device_ptr();
+            CUDA_RUNTIME_CHECK(cudaMemcpyAsync(dst + offset, src.data_ptr(), bytes, cudaMemcpyDefault, cur_stream()));
         })
         .def("as_tensor", [](const std::shared_ptr<HostSegment>& s) {
             return at::from_blob(s->host_ptr(), {static_cast<int64_t>(s->num_bytes())}, [s](void*) {}, at::TensorOptions().dtype(at::kByte));

@@ -118,8 +118,11 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
         .def_readonly("event", &CombineResult::event);
 
     py::class_<Runtime, std::shared_ptr<Runtime>>(m, "Runtime")
-        .def(py::init<int, int, int64_t, double, double>(), py::arg("rank"), py::arg("num_ranks"), py::arg("num_bytes"),
-             py::arg("gpu_timeout_secs") = 100.0, py::arg("cpu_timeout_secs") = 300.0)
+        .def(py::init<int, int, int64_t, double, double, int64_t>(), py::arg("rank"), py::arg("num_ranks"), py::arg("num_bytes"),
+             py::arg("gpu_timeout_secs") = 100.0, py::arg("cpu_timeout_secs") = 300.0, py::arg("num_cpu_bytes") = 0)
+        .def("finish_export", &Runtime::finish_export)
+        .def("heap_is_vmm", &Runtime::heap_is_vmm)
+        .def_static("heap_backend_is_vmm", &Runtime::heap_backend_is_vmm)
         .def("destroy", &Runtime::destroy)
         .def("export_handle", [](const Runtime& rt) { return py::bytes(rt.export_handle()); })
         .def("open_peers", [](Runtime& rt, const std::vector<py::bytes>& handles) {

@@ -12,8 +12,9 @@
 //
 // Parity: ElasticSymmetricMemory / HybridElasticSymmetricMemory of the reference
 // (csrc/kernels/backend/symmetric.hpp: a NUMA-local host segment inside the symmetric window, shared
-// through POSIX file descriptors). Here the host segment is a separate mapping, not part of one
-// contiguous virtual range with the GPU segment.
+// through POSIX file descriptors). With the cudaMalloc / IPC heap the host segment is this separate mapping;
+// with the virtual-memory heap (EP_HEAP_BACKEND=vmm) it is part of the heap's own address range, right behind
+// the GPU segment, and `window()` only wraps those addresses.
 #pragma once
 
 #include <cuda_runtime.h>
@@ -48,6 +49,18 @@ public:
         return std::shared_ptr<HostSegment>(new HostSegment(name, num_bytes, fd, true));
     }
 
+    // A CPU segment that lives inside a symmetric heap's address range (nothing is owned here): `device` is the
+    // address kernels of this process use, `host` the address host code may use (null for a peer's segment).
+    static std::shared_ptr<HostSegment> window(uint8_t* device, uint8_t* host, size_t num_bytes) {
+        auto s = std::shared_ptr<HostSegment>(new HostSegment());
+        s->name_ = "(heap window)";
+        s->num_bytes_ = num_bytes;
+        s->device_ = device;
+        s->host_ = host;
+        s->window_ = true;
+        return s;
+    }
+
     static std::shared_ptr<HostSegment> open(const std::string& name, size_t num_bytes) {
         const int fd = shm_open(name.c_str(), O_RDWR, 0600);
         EP_HOST_ASSERT_MSG(fd >= 0, "shm_open failed for a peer's host segment");
@@ -59,6 +72,10 @@ public:
     HostSegment& operator=(const HostSegment&) = delete;
 
     void release() {
+        if (window_) {
+            host_ = device_ = nullptr;
+            return;
+        }
         if (host_ == nullptr) return;
         cudaHostUnregister(host_);
         munmap(host_, num_bytes_);
@@ -73,6 +90,7 @@ public:
     uint8_t* device_ptr() const { return static_cast<uint8_t*>(device_); }   // address of the pages as seen by kernels of this process
 
 private:
+    HostSegment() : num_bytes_(0), owner_(false) {}
     HostSegment(std::string name, size_t num_bytes, int fd, bool owner) : name_(std::move(name)), num_bytes_(num_bytes), owner_(owner) {
         host_ = mmap(nullptr, num_bytes, PROT_READ | PROT_WRITE, MAP_SHARED, fd, 0);
         close(fd);
@@ -95,6 +113,7 @@ private:
     std::string name_;
     size_t num_bytes_;
     bool owner_;
+    bool window_ = false;
     void* host_ = nullptr;
     void* device_ = nullptr;
 };

@@ -95,6 +95,40 @@ at::Tensor gemm_impl(const at::Tensor& a, const at::Tensor& b, const std::option
 
 cudaStream_t cur_stream() { return at::cuda::getCurrentCUDAStream().stream(); }
 
+// out[g] = a[:, range g] @ b[:, range g]^T for all groups in one launch (bf16): the k range of group g is
+// [align(group_end[g-1], group_alignment), group_end[g]), read from the device array, no host synchronisation.
+at::Tensor gemm_k_grouped(const at::Tensor& a, const at::Tensor& b, const at::Tensor& group_end, int num_groups, int group_alignment,
+                          std::optional<at::Tensor> out, int num_sms) {
+    EP_HOST_ASSERT(a.is_cuda() && b.is_cuda() && a.dim() == 2 && b.dim() == 2 && a.stride(1) == 1 && b.stride(1) == 1);
+    EP_HOST_ASSERT(a.scalar_type() == at::kBFloat16 && b.scalar_type() == at::kBFloat16 && a.size(1) == b.size(1));
+    const int M = static_cast<int>(a.size(0)), N = static_cast<int>(b.size(0)), K = static_cast<int>(a.size(1));
+    EP_HOST_ASSERT_MSG(N % 128 == 0 && K % 64 == 0 && group_alignment % 64 == 0, "N must be a multiple of 128, K and the group alignment of 64");
+    EP_HOST_ASSERT((a.stride(0) * 2) % 16 == 0 && (b.stride(0) * 2) % 16 == 0 && reinterpret_cast<uintptr_t>(a.data_ptr()) % 16 == 0 &&
+                   reinterpret_cast<uintptr_t>(b.data_ptr()) % 16 == 0);
+    EP_HOST_ASSERT(group_end.scalar_type() == at::kInt && group_end.is_contiguous() && group_end.numel() >= num_groups && num_groups >= 1);
+    const int device = a.get_device();
+    c10::cuda::CUDAGuard guard(static_cast<c10::DeviceIndex>(device));
+    if (!out.has_value()) out = at::empty({num_groups, M, N}, a.options());
+    EP_HOST_ASSERT(out->scalar_type() == at::kBFloat16 && out->is_contiguous() && out->numel() == static_cast<int64_t>(num_groups) * M * N);
+    gemm::GemmParams p = {};
+    p.M = M;
+    p.N = N;
+    p.K = K;
+    p.num_groups = num_groups;
+    p.group_end = group_end.data_ptr<int>();
+    p.group_alignment = group_alignment;
+    p.zero_gap = 0;
+    p.k_grouped = 1;
+    p.c_group_stride = static_cast<int64_t>(M) * N;
+    p.C = reinterpret_cast<__nv_bfloat16*>(out->data_ptr());
+    p.ldc = N;
+    p.error = gemm_status(device).data_ptr<int>();
+    p.timeout_ns = 10ull * 1000 * 1000 * 1000;
+    const int sms = num_sms > 0 ? num_sms : at::cuda::getCurrentDeviceProperties()->multiProcessorCount;
+    CUDA_RUNTIME_CHECK(gemm::launch_gemm(p, a.data_ptr(), a.stride(0) * 2, b.data_ptr(), b.stride(0) * 2, false, sms, cur_stream()));
+    return *out;
+}
+
 std::tuple<at::Tensor, at::Tensor> router_topk(const at::Tensor& logits, int num_topk) {
     EP_HOST_ASSERT(logits.is_cuda() && logits.dim() == 2 && logits.scalar_type() == at::kFloat && logits.is_contiguous());
     c10::cuda::CUDAGuard guard(logits.device());
@@ -148,15 +182,24 @@ std::tuple<at::Tensor, std::optional<at::Tensor>> swiglu(const at::Tensor& x, co
     return {out, sf};
 }
 
-at::Tensor swiglu_backward(const at::Tensor& x, const at::Tensor& dout, const std::optional<at::Tensor>& row_weight) {
+// returns dx, or with `with_byproducts` (dx, weighted activation [rows, inter] bf16, gradient of the row weight [rows] fp32)
+py::object swiglu_backward(const at::Tensor& x, const at::Tensor& dout, const std::optional<at::Tensor>& row_weight, bool with_byproducts) {
     EP_HOST_ASSERT(x.is_cuda() && x.scalar_type() == at::kBFloat16 && x.is_contiguous() && dout.scalar_type() == at::kBFloat16 && dout.is_contiguous());
     c10::cuda::CUDAGuard guard(x.device());
     const int M = static_cast<int>(x.size(0)), I = static_cast<int>(x.size(1) / 2);
     EP_HOST_ASSERT(dout.size(0) == M && dout.size(1) == I);
+    if (row_weight.has_value()) EP_HOST_ASSERT(row_weight->scalar_type() == at::kFloat && row_weight->is_contiguous() && row_weight->numel() >= M);
     auto dx = at::empty_like(x);
+    at::Tensor act, dweight;
+    if (with_byproducts) {
+        act = at::empty({M, I}, x.options());
+        dweight = at::empty({M}, x.options().dtype(at::kFloat));
+    }
     CUDA_RUNTIME_CHECK(ops::swiglu_backward(x.data_ptr(), dout.data_ptr(), M, I, row_weight.has_value() ? row_weight->data_ptr<float>() : nullptr,
-                                            dx.data_ptr(), cur_stream()));
-    return dx;
+                                            dx.data_ptr(), with_byproducts ? act.data_ptr() : nullptr,
+                                            with_byproducts ? dweight.data_ptr<float>() : nullptr, cur_stream()));
+    if (with_byproducts) return py::make_tuple(dx, act, dweight);
+    return py::cast(dx);
 }
 
 at::Tensor transpose_bf16(const at::Tensor& x) {
@@ -175,11 +218,15 @@ void register_ops_bindings(py::module_& m) {
     m.def("quant_1x128", &quant_1x128, py::arg("x"), py::arg("pow2") = false, py::arg("col_major_sf") = false);
     m.def("dequant_1x128", &dequant_1x128);
     m.def("swiglu", &swiglu, py::arg("x"), py::arg("row_weight") = py::none(), py::arg("num_valid_rows") = py::none(), py::arg("quant") = false);
-    m.def("swiglu_backward", &swiglu_backward, py::arg("x"), py::arg("dout"), py::arg("row_weight") = py::none());
+    m.def("swiglu_backward", &swiglu_backward, py::arg("x"), py::arg("dout"), py::arg("row_weight") = py::none(),
+          py::arg("with_byproducts") = false);
     m.def("transpose_bf16", &transpose_bf16);
     m.def("gemm", &gemm_impl, py::arg("a"), py::arg("b"), py::arg("sfa") = py::none(), py::arg("sfb") = py::none(),
           py::arg("group_end") = py::none(), py::arg("group_alignment") = 1, py::arg("out") = py::none(), py::arg("num_sms") = 0,
           "C = A @ B^T on the tcgen05 tensor cores (bf16, or e4m3 with 1x128 / 128x128 block scales); 3-D B = grouped");
+    m.def("gemm_k_grouped", &gemm_k_grouped, py::arg("a"), py::arg("b"), py::arg("group_end"), py::arg("num_groups"),
+          py::arg("group_alignment") = 128, py::arg("out") = py::none(), py::arg("num_sms") = 0,
+          "C[g] = A[:, k range g] @ B[:, k range g]^T for all groups in one launch (bf16; the ranges come from a device array)");
     m.def("gemm_check_status", &gemm_check_status);
 }
 

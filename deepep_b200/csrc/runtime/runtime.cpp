@@ -84,11 +84,12 @@ at::TensorOptions opts(at::ScalarType dtype, int device) {
 }  // namespace
 
 // ============================================================================ construction
-Runtime::Runtime(int rank, int num_ranks, int64_t num_bytes, double gpu_timeout_secs, double cpu_timeout_secs)
+Runtime::Runtime(int rank, int num_ranks, int64_t num_bytes, double gpu_timeout_secs, double cpu_timeout_secs, int64_t num_cpu_bytes)
     : rank_(rank), num_ranks_(num_ranks), gpu_timeout_ns_(static_cast<uint64_t>(gpu_timeout_secs * 1e9)),
       cpu_timeout_secs_(cpu_timeout_secs), comm_stream_(at::cuda::getStreamFromPool(/*isHighPriority=*/true)) {
     EP_HOST_ASSERT(num_bytes >= static_cast<int64_t>(kCtlBytes));
-    heap_ = std::make_unique<SymmetricHeap>(rank, num_ranks, align_up<size_t>(static_cast<size_t>(num_bytes), kHeapAlignment));
+    heap_ = std::make_unique<SymmetricHeap>(rank, num_ranks, align_up<size_t>(static_cast<size_t>(num_bytes), kHeapAlignment),
+                                            SymmetricHeap::backend_from_env(), static_cast<size_t>(std::max<int64_t>(num_cpu_bytes, 0)));
     CUDA_RUNTIME_CHECK(cudaMalloc(reinterpret_cast<void**>(&local_ws_), kWsBytes));
     CUDA_RUNTIME_CHECK(cudaMemset(local_ws_, 0, kWsBytes));
     const size_t host_bytes = sizeof(uint64_t) * (kHostStatusWords + kHostCountWords);

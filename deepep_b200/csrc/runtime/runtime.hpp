@@ -100,13 +100,18 @@ struct CombineResult {
 // ------------------------------------------------------------------------ runtime
 class Runtime {
 public:
-    Runtime(int rank, int num_ranks, int64_t num_bytes, double gpu_timeout_secs, double cpu_timeout_secs);
+    // `num_cpu_bytes` > 0 puts a pinned CPU segment behind the GPU segment in the heap's address range (needs the
+    // virtual-memory heap, EP_HEAP_BACKEND=vmm)
+    Runtime(int rank, int num_ranks, int64_t num_bytes, double gpu_timeout_secs, double cpu_timeout_secs, int64_t num_cpu_bytes = 0);
     ~Runtime();
     void destroy();
 
     // peer table
     std::string export_handle() const { return heap_->export_handle(); }
     void open_peers(const std::vector<std::string>& handles) { heap_->open_peers(handles); }
+    void finish_export() { heap_->finish_export(); }     // after a barrier: every peer has mapped this rank's heap
+    bool heap_is_vmm() const { return heap_->backend() == SymmetricHeap::Backend::kVmm; }
+    static bool heap_backend_is_vmm() { return SymmetricHeap::backend_from_env() == SymmetricHeap::Backend::kVmm; }
     static void connect_local(const std::vector<std::shared_ptr<Runtime>>& runtimes);
 
     // status words

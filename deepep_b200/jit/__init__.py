@@ -27,11 +27,13 @@ _initialised = False
 INCLUDE_ROOT = str(Path(__file__).resolve().parent.parent / 'csrc')
 
 
-def init(cache_dir: str = '') -> None:
+def init(cache_dir: str = '', include_root: str = '') -> None:
+    """Sets the cache directory and the root of the library headers that JIT sources may include (default: the
+    ``csrc`` tree of the installed package). The content of every included header is part of the cache key."""
     global _initialised
     C = require_native()
     cache_dir = cache_dir or os.environ.get('EP_JIT_CACHE_DIR') or os.path.join(os.path.expanduser('~'), '.deepep_b200', 'cache')
-    C.jit_init(cache_dir, find_cuda_home(), INCLUDE_ROOT)
+    C.jit_init(cache_dir, find_cuda_home(), include_root or INCLUDE_ROOT)
     _initialised = True
 
 

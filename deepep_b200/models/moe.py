@@ -11,8 +11,10 @@ The expert GEMMs read the dispatch's device-resident prefix array as their group
 but the dispatch itself synchronises with the host. The gate weight is applied inside the SwiGLU
 kernel, which makes the combine a plain sum. Backward reverses the same pipeline: the gradient of
 the combine is a cached (replayed) dispatch, the gradient of the dispatch is a combine, the data
-gradients are grouped GEMMs with the transposed weights, the weight gradients are per-expert GEMMs
-over transposed activations, and the gradient of the gate weights rides back with the combine.
+gradients are grouped GEMMs with the transposed weights, the weight gradients are two GEMM launches
+grouped along the contraction dimension (all experts at once, segment bounds read on the device), and
+the gradient of the gate weights rides back with the combine. The router runs on the same tensor-core
+GEMM (``_RouterFunction``).
 
 The reference library has no model code; this is the "fused MoE layer fwd+bwd" workload that its
 kernels exist to serve. Everything is written over LISTS of ranks so that the single-GPU emulation
@@ -112,19 +114,14 @@ def moe_forward(comm, weights: Sequence[ExpertWeights], xs: Sequence[torch.Tenso
     return [c[0] for c in comb], ctxs
 
 
-def _expert_segments(handle, alignment: int) -> List[Tuple[int, int]]:
-    """(start, padded end) of every local expert's rows, from the host copy of the aligned counts."""
-    counts = handle.num_recv_tokens_per_expert_list
-    assert counts is not None and len(counts) > 0, 'the backward pass needs the CPU-synchronised expert counts'
-    segs, start = [], 0
-    for c in counts:
-        segs.append((start, start + c))
-        start += c
-    return segs
-
-
 def moe_backward(comm, weights: Sequence[ExpertWeights], ctxs, dys: Sequence[torch.Tensor], cfg: MoEConfig):
-    """Gradients of :func:`moe_forward`: ``(dxs, d_topk_weights, dW13s, dW2s)`` (bf16 / fp32 weights grads)."""
+    """Gradients of :func:`moe_forward`: ``(dxs, d_topk_weights, dW13s, dW2s)`` (bf16 / fp32 weights grads).
+
+    Nothing here synchronises with the host: the expert segments are read on the device from the dispatch's prefix
+    array, both by the grouped data-gradient GEMMs and by the two weight-gradient launches (one GEMM over all experts
+    each, grouped along the contraction dimension). The SwiGLU backward kernel also produces the weighted activation
+    (operand of the W2 gradient) and the gradient of the gate weights in the same pass.
+    """
     R = len(dys)
     # gradient of the combine (a sum): replay the dispatch routing with dy as payload
     out = comm.dispatch([dict(x=dys[r].contiguous(), handle=ctxs[r]['handle'], do_expand=True, do_zero_padding=True,
@@ -135,30 +132,63 @@ def moe_backward(comm, weights: Sequence[ExpertWeights], ctxs, dys: Sequence[tor
         c, w = ctxs[r], weights[r]
         handle, h1, recv_w = c['handle'], c['h1'], c['recv_w']
         ends = handle.psum_num_recv_tokens_per_expert
+        el = w.w13.size(0)
         x_rows = c['recv_x']
         if cfg.use_fp8:
             x_rows = _C.dequant_1x128(x_rows[0], x_rows[1].contiguous())
         # data gradients
         da = _C.gemm(dh2, w.w2_t, group_end=ends, group_alignment=cfg.expert_alignment)           # [rows, I]
-        a_unweighted, _ = _C.swiglu(h1, None)                                                       # silu(g) * u
-        dw_rows.append((da.float() * a_unweighted.float()).sum(dim=1))                             # d gate weight per row
-        dh1 = _C.swiglu_backward(h1, da, recv_w)                                                    # [rows, 2I]
+        dh1, a_w, dw_row = _C.swiglu_backward(h1, da, recv_w, True)                                 # [rows, 2I], [rows, I], [rows]
+        dw_rows.append(dw_row)
         dx_rows.append(_C.gemm(dh1, w.w13_t, group_end=ends, group_alignment=cfg.expert_alignment))
-        # weight gradients: per expert, contraction over that expert's (zero padded) rows
-        a_w = (a_unweighted.float() * recv_w[:, None]).bfloat16() if recv_w is not None else a_unweighted
+        # weight gradients: contraction over every expert's (zero padded) rows, all experts in one launch each
         dh2_t, a_t = _C.transpose_bf16(dh2), _C.transpose_bf16(a_w)
         dh1_t, x_t = _C.transpose_bf16(dh1), _C.transpose_bf16(x_rows)
-        dW13 = torch.zeros_like(w.w13)
-        dW2 = torch.zeros_like(w.w2)
-        for e, (s, t) in enumerate(_expert_segments(handle, cfg.expert_alignment)):
-            if t > s:
-                _C.gemm(dh2_t[:, s:t], a_t[:, s:t], out=dW2[e])
-                _C.gemm(dh1_t[:, s:t], x_t[:, s:t], out=dW13[e])
-        dW13s.append(dW13)
-        dW2s.append(dW2)
+        dW2s.append(_C.gemm_k_grouped(dh2_t, a_t, ends, el, cfg.expert_alignment))               # [EL, hidden, I]
+        dW13s.append(_C.gemm_k_grouped(dh1_t, x_t, ends, el, cfg.expert_alignment))              # [EL, 2I, hidden]
     # gradient of the dispatch: a combine that also carries the gate-weight gradients back
     comb = comm.combine([dict(x=dx_rows[r], handle=ctxs[r]['handle'], topk_weights=dw_rows[r].contiguous()) for r in range(R)])
     return [c[0] for c in comb], [c[1] for c in comb], dW13s, dW2s
+
+
+class _RouterFunction(torch.autograd.Function):
+    """Router of the layer on this library's kernels: logits = x @ W_r^T on the tcgen05 GEMM (bf16 operands, fp32
+    accumulation), top-k and softmax over the selected logits in ``router_topk``; the backward pass turns the gradient
+    of the top-k weights into the gradient of the logits (softmax Jacobian over the selected experts, zero elsewhere)
+    and into two more tensor-core GEMMs for dW_r and dx."""
+
+    @staticmethod
+    def forward(ctx, x, router, num_topk):
+        E = router.size(0)
+        router_bf16 = router.detach().to(torch.bfloat16)
+        if E % 128 != 0:                                                        # the GEMM tiles N in multiples of 128: zero rows
+            router_bf16 = torch.nn.functional.pad(router_bf16, (0, 0, 0, -(-E // 128) * 128 - E))
+        router_bf16 = router_bf16.contiguous()
+        logits = _C.gemm(x.detach().contiguous(), router_bf16)[:, :E]          # [T, E] bf16
+        topk_idx, topk_weights = _C.router_topk(logits.float().contiguous(), num_topk)
+        ctx.save_for_backward(x, router_bf16, topk_idx, topk_weights)
+        ctx.router_dtype, ctx.num_experts = router.dtype, E
+        ctx.mark_non_differentiable(topk_idx)
+        return topk_idx, topk_weights
+
+    @staticmethod
+    def backward(ctx, _d_idx, d_weights):
+        x, router_bf16, topk_idx, w = ctx.saved_tensors
+        T, E = x.size(0), router_bf16.size(0)                                  # E: padded to a multiple of 128
+        # d logit_k = w_k * (dw_k - sum_j w_j dw_j) on the selected experts
+        inner = (w * d_weights).sum(dim=1, keepdim=True)
+        d_sel = (w * (d_weights - inner)).to(torch.bfloat16)
+        d_logits = torch.zeros((T, E), dtype=torch.bfloat16, device=x.device)
+        d_logits.scatter_(1, topk_idx.clamp(min=0), torch.where(topk_idx >= 0, d_sel, torch.zeros_like(d_sel)))
+        pad_t = -(-T // 64) * 64                                               # the GEMM wants K (here: tokens) in multiples of 64
+        if pad_t != T:
+            d_logits = torch.nn.functional.pad(d_logits, (0, 0, 0, pad_t - T))
+            x_p = torch.nn.functional.pad(x.detach(), (0, 0, 0, pad_t - T))
+        else:
+            x_p = x.detach()
+        dx = _C.gemm(d_logits[:T].contiguous(), _C.transpose_bf16(router_bf16))                         # [T, H] = dlogits @ W_r
+        d_router = _C.gemm(_C.transpose_bf16(d_logits), _C.transpose_bf16(x_p.contiguous()))             # [E, H] = dlogits^T @ x
+        return dx, d_router[:ctx.num_experts].to(ctx.router_dtype), None
 
 
 class _MoEFunction(torch.autograd.Function):
@@ -201,9 +231,7 @@ class FusedMoE(torch.nn.Module):
         self.weights = ExpertWeights(self.w13.data, self.w2.data, self.cfg.use_fp8)
 
     def forward(self, x: torch.Tensor) -> torch.Tensor:
-        logits = x.float() @ self.router.float().t()
-        topk_idx, _ = route(logits.detach(), self.cfg.num_topk)
-        topk_weights = torch.softmax(logits.gather(1, topk_idx), dim=1)     # differentiable path to the router
+        topk_idx, topk_weights = _RouterFunction.apply(x, self.router, self.cfg.num_topk)
         return _MoEFunction.apply(x, topk_weights, self.w13, self.w2, self, topk_idx)
 
 

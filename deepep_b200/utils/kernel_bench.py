@@ -6,7 +6,8 @@
         python -m deepep_b200.utils.kernel_bench --op dispatch --tokens 8192 --iters 2 --warmup 3
 
 Ops: ``dispatch`` (fused FP8 cast), ``dispatch_prequant``, ``dispatch_bf16``, ``combine``, ``gemm``,
-``gemm_fp8_grouped``, ``ll`` (low-latency dispatch + combine). Times are CUDA-event means on one
+``gemm_fp8_grouped``, ``ll`` (low-latency dispatch + combine), ``ops`` (router, SwiGLU, quantisation, transpose),
+``ag_gemm`` / ``gemm_rs`` (fused tensor-parallel operators with emulated ranks). Times are CUDA-event means on one
 rank (EP1: all traffic is local, so dispatch / combine show the SM-side cost of the kernels, not
 NVLink).
 """
@@ -43,6 +44,7 @@ def main():
     ap.add_argument('--k', type=int, default=7168)
     ap.add_argument('--iters', type=int, default=10)
     ap.add_argument('--warmup', type=int, default=3)
+    ap.add_argument('--ranks', type=int, default=2, help='ag_gemm / gemm_rs: emulated ranks')
     ap.add_argument('--baseline', action='store_true', help='gemm: also time torch.matmul on the same tensors')
     a = ap.parse_args()
 
@@ -114,6 +116,49 @@ def main():
         print(f'll dispatch+combine: {ms * 1e3:.1f} us, tokens {Tl}')
         ll.check_status()
         ll.destroy()
+    elif a.op == 'ops':
+        # the small MoE operators: router top-k, SwiGLU (+ fused cast), SwiGLU backward, 1x128 quantisation, transpose
+        rows, inter = a.m, a.k // 4 // 128 * 128
+        logits = torch.randn((rows, E), generator=g).cuda()
+        h1 = torch.randn((rows, 2 * inter), generator=g).bfloat16().cuda()
+        da = torch.randn((rows, inter), generator=g).bfloat16().cuda()
+        rw = torch.rand((rows,), generator=g).cuda()
+        xr = torch.randn((rows, a.k), generator=g).bfloat16().cuda()
+        for name, fn, nbytes in (
+                ('router_topk', lambda: C.router_topk(logits, K), rows * E * 4),
+                ('swiglu', lambda: C.swiglu(h1, rw), rows * inter * 6),
+                ('swiglu + fp8 cast', lambda: C.swiglu(h1, rw, None, True), rows * inter * 5),
+                ('swiglu_backward (+ activation, gate-weight gradient)', lambda: C.swiglu_backward(h1, da, rw, True), rows * inter * 12),
+                ('quant_1x128', lambda: C.quant_1x128(xr), rows * a.k * 3),
+                ('transpose_bf16', lambda: C.transpose_bf16(xr), rows * a.k * 4)):
+            ms = _timeit(fn, a.iters, a.warmup)
+            print(f'{name}: {ms * 1e3:.1f} us, {nbytes / ms / 1e6:.0f} GB/s of algorithmic bytes (rows {rows})')
+    elif a.op in ('ag_gemm', 'gemm_rs'):
+        # the fused tensor-parallel operators with `--ranks` emulated ranks on this GPU (the device code of the real
+        # multi-GPU run; the "peers" are local, so times show the kernel structure, not NVLink)
+        from deepep_b200.parallel.local_cluster import VirtualRanks
+        from deepep_b200.parallel.tp_fused import TensorParallelContext, fused_multi
+        R = a.ranks
+        Ml, Kd, N = a.m // R, a.k, a.n
+        vr = VirtualRanks(R)
+        ctxs = [TensorParallelContext(vr.groups[r], Ml, Kd, N, num_gpu_timeout_secs=10) for r in range(R)]
+        vr.connect()
+        gg = torch.Generator(device='cuda').manual_seed(1)
+        if a.op == 'ag_gemm':
+            xs = [torch.randn((Ml, Kd), device='cuda', generator=gg).bfloat16() for _ in range(R)]
+            ws = [(torch.randn((N, Kd), device='cuda', generator=gg) * 0.05).bfloat16() for _ in range(R)]
+            fn = lambda: fused_multi(ctxs, 'ag_gemm', xs, ws, num_comm_ctas=2, num_sms=a.sms)
+            flops = 2.0 * R * Ml * N * Kd * R
+        else:
+            xs = [torch.randn((R * Ml, Kd // R), device='cuda', generator=gg).bfloat16() for _ in range(R)]
+            ws = [(torch.randn((N, Kd // R), device='cuda', generator=gg) * 0.05).bfloat16() for _ in range(R)]
+            fn = lambda: fused_multi(ctxs, 'gemm_rs', xs, ws, num_sms=a.sms)
+            flops = 2.0 * R * Ml * N * (Kd // R) * R
+        ms = _timeit(fn, a.iters, a.warmup)
+        print(f'{a.op} with {R} emulated ranks ({a.sms} SMs each): {ms * 1e3:.1f} us, {flops / ms / 1e9:.0f} TFLOP/s over all ranks')
+        for c in ctxs:
+            c.check_status()
+            c.destroy()
     else:
         raise SystemExit(f'unknown op {a.op}')
 

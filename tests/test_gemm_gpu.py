@@ -56,11 +56,14 @@ def test_grouped_gemm_bf16_with_gaps(counts, pair, monkeypatch):
         start = nxt
 
 
+@pytest.mark.parametrize('pair', ['1', '0'])
 @pytest.mark.parametrize('grouped', [False, True])
-def test_gemm_fp8_block_scaled(grouped):
+def test_gemm_fp8_block_scaled(grouped, pair, monkeypatch):
+    """`pair`: 256 x 256 tiles on CTA pairs (tcgen05 cta_group::2, kind::f8f6f4) or 128 x 128 tiles on lone CTAs."""
     import deepep_b200
     from deepep_b200.utils.math import per_token_cast_back, per_token_cast_to_fp8
-    G, M, N, K = (3 if grouped else 1), 384, 256, 1024
+    monkeypatch.setenv('EP_GEMM_FP8_PAIR', pair)
+    G, M, N, K = (3 if grouped else 1), 384, 512, 1024
     g = torch.Generator(device='cuda').manual_seed(2)
     a = torch.randn((M, K), device='cuda', generator=g).bfloat16()
     aq, sfa = per_token_cast_to_fp8(a)
@@ -82,3 +85,33 @@ def test_gemm_fp8_block_scaled(grouped):
     torch.cuda.synchronize()
     assert deepep_b200._C.gemm_check_status() == 0
     assert _rel_err(out, ref) < 1e-2
+
+
+def test_gemm_k_grouped_weight_gradients():
+    """Groups along the contraction dimension: out[g] = A[:, rows of g] @ B[:, rows of g]^T for all groups in one launch,
+    the ranges read from a device prefix array (aligned starts, zero padding between the groups, one empty group)."""
+    import deepep_b200
+    C = deepep_b200._C
+    g = torch.Generator(device='cuda').manual_seed(11)
+    M, N, align = 256, 512, 128
+    counts = [200, 0, 129, 64]
+    starts, ends, cursor = [], [], 0
+    for c in counts:
+        starts.append(cursor)
+        ends.append(cursor + c)
+        cursor = -(-(cursor + c) // align) * align
+    K = max(cursor, align)
+    a = torch.zeros((M, K), device='cuda', dtype=torch.bfloat16)
+    b = torch.zeros((N, K), device='cuda', dtype=torch.bfloat16)
+    for s, e in zip(starts, ends):
+        a[:, s:e] = torch.randn((M, e - s), device='cuda', generator=g).bfloat16()
+        b[:, s:e] = torch.randn((N, e - s), device='cuda', generator=g).bfloat16()
+    out = C.gemm_k_grouped(a, b, torch.tensor(ends, device='cuda', dtype=torch.int32), len(counts), align)
+    torch.cuda.synchronize()
+    assert C.gemm_check_status() == 0
+    for i, (s, e) in enumerate(zip(starts, ends)):
+        ref = a[:, s:e].float() @ b[:, s:e].float().t()
+        if e == s:
+            assert out[i].float().abs().max().item() == 0
+        else:
+            assert ((out[i].float() - ref).norm() / ref.norm()).item() < 1e-2

@@ -13,7 +13,7 @@ import ctypes
 import pytest
 import torch
 
-pytestmark = pytest.mark.gpu
+gpu = pytest.mark.gpu
 
 
 def _lib():
@@ -58,6 +58,7 @@ def _call(lib, x, idx, w, E, do_expand, alignment, rows):
     return recv_x, recv_idx, recv_w, meta, psum, int(n.item())
 
 
+@gpu
 @pytest.mark.parametrize('do_expand,alignment', [(False, 1), (True, 8)])
 def test_noalloc_matches_regular_dispatch(do_expand, alignment):
     import deepep_b200
@@ -94,6 +95,7 @@ def test_noalloc_matches_regular_dispatch(do_expand, alignment):
     buf.destroy()
 
 
+@gpu
 def test_noalloc_rejects_sizes_beyond_the_scratch():
     lib = _lib()
     x = torch.zeros((4, 64), dtype=torch.bfloat16, device='cuda')
@@ -109,3 +111,36 @@ def test_noalloc_rejects_sizes_beyond_the_scratch():
     assert lib.deepep_b200_dispatch_local_noalloc(*args(4, 120, 2, 8)) == 2          # not a multiple of 16
     assert lib.deepep_b200_dispatch_local_noalloc(*args(4, 128, 64, 8)) == 3         # top-k beyond the maximum
     assert lib.deepep_b200_dispatch_local_noalloc(*args(4, 128, 2, 4096)) == 4       # too many experts
+
+
+def test_noalloc_rejects_an_output_that_is_too_small():
+    """An embedder that sizes recv_x too small gets an error code, not an out-of-bounds write. The check runs before
+    anything touches the device, so this test needs no GPU: the pointers are never dereferenced."""
+    lib = _lib()
+    fake = 1 << 20            # any non-null, 16-byte aligned address
+    T, K, E = 64, 4, 8
+
+    def call(do_expand, alignment, rows):
+        return lib.deepep_b200_dispatch_local_noalloc(fake, 256, 256, fake, None, T, K, E, do_expand, alignment, 4, fake, rows,
+                                                      None, None, fake, fake, fake, None)
+
+    assert call(0, 1, T - 1) == 5                                  # non-expanded output needs one row per token
+    assert call(1, 1, T * K - 1) == 5                              # expanded: one row per token and expert ...
+    assert call(1, 16, T * K + E * 15 - 1) == 5                    # ... plus the alignment slack of every expert
+    assert call(0, 0, T) == 5                                      # an alignment of zero
+
+
+@gpu
+def test_noalloc_reset_clears_the_status():
+    """deepep_b200_noalloc_reset() is the way back after a wait that ran out: here it is simply called on a healthy
+    device and a dispatch after it must still be correct."""
+    lib = _lib()
+    lib.deepep_b200_noalloc_reset.restype = ctypes.c_int
+    x, idx, w = _inputs(7, 64, 256, 8, 2)
+    _call(lib, x, idx, w, 8, False, 1, 64)
+    assert lib.deepep_b200_noalloc_reset() == 0
+    record = ctypes.c_ulonglong(1)
+    assert lib.deepep_b200_noalloc_status(ctypes.byref(record)) == 0 and record.value == 0
+    got_x, got_idx, _, _, _, n = _call(lib, x, idx, w, 8, False, 1, 64)
+    sel = (idx >= 0).any(dim=1)
+    assert n == int(sel.sum()) and torch.equal(got_x[:n], x[sel])
