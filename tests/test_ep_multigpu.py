@@ -332,6 +332,69 @@ def test_low_latency_graph_replay_on_real_ranks():
     torch.multiprocessing.spawn(_ll_graph_worker, args=(world, _free_port()), nprocs=world, join=True)
 
 
+def _backend_worker(rank: int, world: int, port: int):
+    """The virtual-memory heap (cuMemCreate + descriptors passed over a unix socket) with a pinned CPU segment in the same
+    address range, and flag rounds as stream memory operations: dispatch / combine, an Engram table in the CPU
+    segments, and an all-gather session must give the same results as with the default heap."""
+    import torch.distributed as dist
+    os.environ['MASTER_ADDR'] = '127.0.0.1'
+    os.environ['MASTER_PORT'] = str(port)
+    os.environ.setdefault('NCCL_NVLS_ENABLE', '0')
+    os.environ['EP_HEAP_BACKEND'] = 'vmm'
+    os.environ['EP_STREAM_MEMOPS'] = '1'
+    torch.cuda.set_device(rank)
+    dev = torch.device('cuda', rank)
+    dist.init_process_group('nccl', rank=rank, world_size=world, device_id=dev)
+    import deepep_b200
+    from deepep_b200.utils import gate, refs
+    T, H, E, K = 128, 1024, 8 * world, 4
+    buf = deepep_b200.ElasticBuffer(dist.group.WORLD, num_max_tokens_per_rank=T, hidden=H, num_topk=K, num_cpu_bytes=1 << 20,
+                                    num_gpu_timeout_secs=10, explicitly_destroy=True)
+    assert buf.heap_is_vmm and len(buf.host_segments) == world
+    g = torch.Generator().manual_seed(900 + rank)
+    x = torch.randn((T, H), generator=g).bfloat16().to(dev)
+    idx, w = gate.topk_from_scores(gate.get_balanced_scores(T, E, generator=g), K)
+    idx, w = idx.to(dev), w.to(dev)
+    for it in range(2):
+        rx, ridx, rw, handle, _ = buf.dispatch(x, topk_idx=idx, topk_weights=w, num_experts=E, num_sms=8)
+        ex, eidx, ew, esrc, _ = refs.dispatch(x, idx, w, T, E)
+        assert torch.equal(rx, ex) and torch.equal(ridx, eidx)
+        out, _, _ = buf.combine(rx, handle)
+        assert torch.equal(out, refs.combine(rx, esrc, T, T))
+    # Engram rows served from the ranks' CPU segments (behind the GPU segment in the same window)
+    per_rank, hidden = 32, 128
+    table = torch.arange(world * per_rank, device=dev).float().unsqueeze(1).expand(-1, hidden).bfloat16().contiguous()
+    buf.engram_write(table[rank * per_rank:(rank + 1) * per_rank].contiguous())
+    q = torch.randint(0, world * per_rank, (9, 2), device=dev, dtype=torch.int32)
+    data, _ = buf.engram_fetch(q)()
+    torch.cuda.synchronize()
+    assert torch.equal(data, table[q.flatten().long()])
+    buf.check_status()
+    dist.barrier()
+    buf.destroy()
+    # an all-gather session whose arrival rounds are stream memory operations (no kernel, no SM)
+    assert deepep_b200._C.stream_memops_enabled()
+    abuf = deepep_b200.ElasticBuffer(dist.group.WORLD, num_bytes=32 << 20, num_gpu_timeout_secs=10, explicitly_destroy=True)
+    abuf.agrs_set_config(1 << 20, 4)
+    for it in range(3):
+        with abuf.agrs_new_session():
+            t = torch.full((256, 64), float(rank * 3 + it), device=dev)
+            gathered, wait = abuf.all_gather(t)
+            wait()
+            assert torch.equal(gathered, torch.stack([torch.full((256, 64), float(r * 3 + it), device=dev) for r in range(world)]))
+            torch.cuda.synchronize()
+    dist.barrier()
+    abuf.destroy()
+    dist.destroy_process_group()
+
+
+def test_vmm_heap_and_stream_memops_on_real_ranks():
+    n = torch.cuda.device_count()
+    if n < 2:
+        pytest.skip('needs at least two GPUs')
+    torch.multiprocessing.spawn(_backend_worker, args=(2, _free_port()), nprocs=2, join=True)
+
+
 def test_subsystems_on_real_ranks():
     n = torch.cuda.device_count()
     if n < 2:
