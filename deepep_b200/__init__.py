@@ -8,6 +8,14 @@ from __future__ import annotations
 
 import os
 
+# defaults fixed when the package was built (setup.py writes deepep_b200/envs.py); the process environment wins
+try:
+    from .envs import persistent_envs as _persistent_envs
+    for _key, _value in _persistent_envs.items():
+        os.environ.setdefault(_key, _value)
+except ImportError:
+    pass
+
 import torch
 
 from ._native import _C, require_native  # noqa: F401

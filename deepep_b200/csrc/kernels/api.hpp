@@ -199,7 +199,7 @@ cudaError_t launch_combine_epilogue(const CombineEpilogueParams* params, int num
                                     bool programmatic = false);
 
 // ---------------------------------------------------------------- layout (legacy get_dispatch_layout)
-cudaError_t launch_dispatch_layout(const int64_t* topk_idx, int num_tokens, int num_topk, int num_ranks, int num_experts,
+cudaError_t launch_dispatch_layout(const void* topk_idx, bool idx32, int num_tokens, int num_topk, int num_ranks, int num_experts,
                                    int* num_tokens_per_rank, int* num_tokens_per_expert, bool* is_token_in_rank,
                                    cudaStream_t stream);
 
@@ -213,7 +213,8 @@ struct LLDispatchParams {
     int phases;
     int shrink;                      // a peer that does not answer in time is masked instead of reported
     const uint8_t* x;                // [T, hidden] bf16
-    const int64_t* topk_idx;         // [T, K]
+    const void* topk_idx;            // [T, K] int64 or int32
+    int idx32;                       // topk_idx holds int32
     uint8_t* packed_recv_x;          // [EL][R * T_max][hidden] e4m3 or bf16
     uint8_t* packed_recv_sf;         // float [EL][hidden / 128][R * T_max] or int32 [EL][hidden / 512][R * T_max]
     int* packed_recv_src_info;       // [EL][R * T_max]  token | lane << 16
@@ -232,7 +233,8 @@ struct LLCombineParams {
     int shrink;
     int use_logfmt;                  // rows travel in the 10-bit log format where a group of 128 channels allows it
     const uint8_t* x;                // [EL][R * T_max][hidden] bf16
-    const int64_t* topk_idx;         // [T, K] routing of the tokens this rank dispatched
+    const void* topk_idx;            // [T, K] routing of the tokens this rank dispatched, int64 or int32
+    int idx32;                       // topk_idx holds int32
     const float* topk_weights;       // [T, K]
     const int* src_info;             // handle
     const int64_t* layout_range;     // handle

@@ -13,10 +13,14 @@
 // Reduce: combined_x[t] = sum over lanes in ascending order (fp32) + bias_0 + bias_1, one bf16
 // rounding at the end; top-k weights are gathered back. Two ways to run it:
 //   * arrival-driven, beside the send kernel (default with peers): for every row that has landed the
-//     sender adds one to a counter in the RECEIVER's heap (a fire-and-forget `red.release.sys`, one
-//     counter per sender and per 32 consecutive rows of what that sender holds for the receiver; a
-//     row counts as landed three rows late, when wait_group has confirmed its remote writes, so
-//     neither the NVLink round trip nor the accounting stalls a send warp); the reduce kernel is
+//     sender adds one to a counter in the RECEIVER's heap (one counter per sender and per 32
+//     consecutive rows of what that sender holds for the receiver). A send warp never fences: three
+//     rows late, when wait_group has confirmed a row's remote writes, it drops the row's tag into a
+//     shared-memory mailbox, and one extra "accountant" warp per block drains all mailboxes, issues
+//     ONE `fence.acq_rel.sys` for everything it drained (a system-scope fence costs microseconds on
+//     an SM with peer stores in flight, so it is paid per batch, not per row; without it a relaxed
+//     add can overtake the row it announces on NVLink) and then the `red.relaxed.sys` adds, so
+//     neither the NVLink round trip nor the accounting stalls a send warp; the reduce kernel is
 //     launched as a programmatic dependent of the send kernel -- it becomes resident on the SMs the
 //     send kernel leaves free once every send block is running -- and sums a token as soon as the
 //     counters of all its rows are full, while later rows are still in flight. The counters of one
@@ -337,16 +341,40 @@ __global__ void __launch_bounds__(1024, 1) combine_kernel(const __grid_constant_
     }
     __syncwarp();
 
-    // ---- arrival accounting (lane 0 of a send warp): a row counts as landed three rows late, when wait_group has
-    // confirmed its remote writes; then one fire-and-forget add goes to the counter of its 32-row group in the
-    // receiver's heap. `pend` holds (destination rank << 24 | group) of the last three rows sent, oldest first.
-    const int num_recv = p.psum_rank[R - 1];
+    // ---- arrival accounting: a row counts as landed three rows late, when wait_group has confirmed its remote
+    // writes to lane 0 of its send warp; that lane drops the row's tag (destination rank << 24 | 32-row group) into
+    // its mailbox and carries on. The accountant warp (the warp after the send warps) drains the mailboxes: the tags
+    // reach it through shared memory with release / acquire at block scope, so ONE system-scope fence of the
+    // accountant orders every drained row (and the top-k weights stored beside it) before the adds that follow.
+    // `pend` holds the tags of the last three rows sent, oldest first.
+    constexpr int kMboxDepth = 4;
+    __shared__ int s_mbox[32][kMboxDepth];
+    __shared__ int s_head[32], s_tail[32];
+    __shared__ int s_senders_done;
+    if (kFlags) {
+        if (tid < 32) s_head[tid] = s_tail[tid] = 0;
+        if (tid == 0) s_senders_done = 0;
+        __syncthreads();
+    }
+    const bool is_accountant = kFlags && warp == num_warps && bid < nb_send;
     const uint64_t arrivals_off = p.off_comb_flag + static_cast<uint64_t>(p.epoch & 1) * R * p.flag_chunks * 4;
-    // (wait_group has confirmed that the row's writes are complete, so a relaxed add suffices; a release fence at
-    // system scope per row costs microseconds, and the reducer's acquire load orders its reads after the counter)
-    auto row_landed = [&](int tag) {
+    auto count_row = [&](int tag) {
         uint32_t* cnt = reinterpret_cast<uint32_t*>(c.heap[tag >> 24] + arrivals_off) + static_cast<uint64_t>(c.rank) * p.flag_chunks + (tag & 0xffffff);
         asm volatile("red.relaxed.sys.global.add.u32 [%0], 1;" ::"l"(cnt) : "memory");
+    };
+    int my_head = 0;
+    auto row_landed = [&](int tag) {             // lane 0 of a send warp
+        int spins = 0;
+        while (my_head - *reinterpret_cast<volatile int*>(&s_tail[warp]) >= kMboxDepth) {
+            if (++spins > (1 << 22)) {           // the accountant gave up: count the row here, at full price
+                fence_acq_rel_sys();
+                count_row(tag);
+                return;
+            }
+        }
+        *reinterpret_cast<volatile int*>(&s_mbox[warp][my_head & (kMboxDepth - 1)]) = tag;
+        __threadfence_block();
+        *reinterpret_cast<volatile int*>(&s_head[warp]) = ++my_head;
     };
     int pend0 = -1, pend1 = -1, pend2 = -1;
     auto row_sent = [&](int d, int idx) {        // after bulk_commit of the row's only store
@@ -532,11 +560,35 @@ __global__ void __launch_bounds__(1024, 1) combine_kernel(const __grid_constant_
     }
 
     if (lane == 0) flush_sent();
+    if (kFlags && is_sender && lane == 0) {
+        __threadfence_block();
+        atomicAdd(&s_senders_done, 1);
+    }
+    if (is_accountant) {
+        // lane l serves the mailbox of send warp l; the loop ends when every send warp has left and nothing is queued
+        int tail = 0;
+        uint32_t idle = 0;
+        while (true) {
+            const int done = *reinterpret_cast<volatile int*>(&s_senders_done);
+            const int head = lane < num_warps ? *reinterpret_cast<volatile int*>(&s_head[lane]) : 0;
+            __threadfence_block();
+            if (__any_sync(0xffffffffu, head != tail)) {
+                fence_acq_rel_sys();
+                for (; tail != head; ++tail) count_row(*reinterpret_cast<volatile int*>(&s_mbox[lane][tail & (kMboxDepth - 1)]));
+                if (lane < num_warps) *reinterpret_cast<volatile int*>(&s_tail[lane]) = tail;
+                idle = 0;
+            } else if (done >= num_warps) {
+                break;
+            } else if ((++idle & 1023u) == 0 && globaltimer_ns() > w.deadline_ns) {
+                break;                           // the send warps record their own time-outs
+            }
+        }
+    }
     __syncwarp();
 
-    // (no fence here: wait_group confirms the rows; the grid barrier's release / acquire at GPU scope and the release
-    // store of the completion words at system scope order every store of this grid, the top-k weights written with
-    // plain peer stores included, before those words)
+    // (no fence here: wait_group confirms the rows to their send warps; the grid barrier's release / acquire at GPU
+    // scope and the release store of the completion words at system scope order every store of this grid, the top-k
+    // weights written with plain peer stores included, before those words)
     bulk_wait_all();
     grid_barrier(w, c.local_ws + kWsGridBarrier, p.grid_bar_base + nb, 3);
     if (bid == 0 && tid == 0) {   // ready for the next launch (stream order)
@@ -556,7 +608,7 @@ __global__ void __launch_bounds__(1024, 1) combine_kernel(const __grid_constant_
 bool plan_combine(const CombineParams& p, int num_sms, int smem_optin, CombineLaunch* out) {
     const int stage = align_up(p.row_bytes, 128) + 16;
     int warps = smem_optin / stage;
-    if (warps > 32) warps = 32;
+    if (warps > 31) warps = 31;        // the 32nd warp of a block is the accountant of the arrival counters
     if (warps < 1) return false;
     out->num_sms = num_sms;
     out->num_warps = warps;
@@ -571,7 +623,7 @@ cudaError_t launch_combine(const Multi<CombineParams>& m, const CombineLaunch& l
     if (err != cudaSuccess) return err;
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3(m.num_vranks * m.blocks_per_rank);
-    cfg.blockDim = dim3((l.num_warps + l.num_reduce_warps) * 32);
+    cfg.blockDim = dim3((l.num_warps + l.num_reduce_warps + (m.r[0].fuse_reduce != 0 ? 1 : 0)) * 32);
     cfg.dynamicSmemBytes = l.smem_bytes;
     cfg.stream = stream;
     cudaLaunchAttribute attr[1];

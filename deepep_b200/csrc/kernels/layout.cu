@@ -11,7 +11,7 @@ namespace ep {
 
 namespace {
 
-__global__ void __launch_bounds__(256) layout_kernel(const int64_t* __restrict__ topk_idx, int num_tokens, int num_topk, int num_ranks,
+__global__ void __launch_bounds__(256) layout_kernel(const void* __restrict__ topk_idx, bool idx32, int num_tokens, int num_topk, int num_ranks,
                                                      int num_experts, int* num_tokens_per_rank, int* num_tokens_per_expert,
                                                      bool* is_token_in_rank) {
     extern __shared__ int s_hist[];   // [num_experts + num_ranks]
@@ -23,10 +23,10 @@ __global__ void __launch_bounds__(256) layout_kernel(const int64_t* __restrict__
     for (int t = blockIdx.x * blockDim.x + threadIdx.x; t < num_tokens; t += gridDim.x * blockDim.x) {
         uint32_t mask = 0;
         for (int k = 0; k < num_topk; ++k) {
-            const int64_t e = topk_idx[static_cast<int64_t>(t) * num_topk + k];
-            if (e >= 0 && e < num_experts) {
+            const int e = load_topk_idx(topk_idx, idx32, static_cast<int64_t>(t) * num_topk + k, num_experts);
+            if (e >= 0) {
                 atomicAdd(s_expert + e, 1);
-                mask |= 1u << (static_cast<int>(e) / experts_per_rank);
+                mask |= 1u << (e / experts_per_rank);
             }
         }
         for (int r = 0; r < num_ranks; ++r) {
@@ -44,7 +44,7 @@ __global__ void __launch_bounds__(256) layout_kernel(const int64_t* __restrict__
 
 }  // namespace
 
-cudaError_t launch_dispatch_layout(const int64_t* topk_idx, int num_tokens, int num_topk, int num_ranks, int num_experts,
+cudaError_t launch_dispatch_layout(const void* topk_idx, bool idx32, int num_tokens, int num_topk, int num_ranks, int num_experts,
                                    int* num_tokens_per_rank, int* num_tokens_per_expert, bool* is_token_in_rank,
                                    cudaStream_t stream) {
     cudaError_t err = cudaMemsetAsync(num_tokens_per_rank, 0, sizeof(int) * num_ranks, stream);
@@ -55,7 +55,7 @@ cudaError_t launch_dispatch_layout(const int64_t* topk_idx, int num_tokens, int 
     int blocks = (num_tokens + 255) / 256;
     if (blocks > 148) blocks = 148;
     layout_kernel<<<blocks, 256, (num_experts + num_ranks) * sizeof(int), stream>>>(
-        topk_idx, num_tokens, num_topk, num_ranks, num_experts, num_tokens_per_rank, num_tokens_per_expert, is_token_in_rank);
+        topk_idx, idx32, num_tokens, num_topk, num_ranks, num_experts, num_tokens_per_rank, num_tokens_per_expert, is_token_in_rank);
     return cudaGetLastError();
 }
 

@@ -6,13 +6,14 @@
 // [local expert][source rank][position] of the owner's receive area. Positions are the token's
 // rank among this source's earlier tokens for that expert, so they do not depend on timing.
 // Every message carries its own arrival flag: its 8-byte header (call number, token, top-k lane)
-// is written last, once wait_group has confirmed that the payload's writes are complete (a plain
-// system-scope store then suffices and is what keeps this cheap: a release fence at system scope
-// per message was measured at 7 us, a full async-proxy fence at 5 us, each; the receiver's acquire
-// load orders its own reads of the payload after the flag); a warp
-// does not wait for that round trip before it takes the next token (the header of message i goes
-// out after message i + 1 has been issued). The per-expert counts need no data at all (they come
-// from the routing), so they travel first, as call-tagged words, while the payloads are cast.
+// is written last. The sending warps wait until wait_group has confirmed their payload and meet
+// one more warp at a named barrier; that warp issues ONE release fence at system scope for the
+// token and writes the K headers (a fence per message was measured at 7 us when the warps of an
+// SM issue them side by side, a full async-proxy fence at 5 us; with no fence at all a header
+// can overtake its payload on NVLink, which showed up as rows packed before they had landed on
+// 4 GPUs). The rest of the block casts the next token meanwhile. The per-expert counts need no
+// data at all (they come from the routing), so they travel first, as call-tagged words, while
+// the payloads are cast.
 // Dispatch, RECV phase: one block per (local expert, source rank) waits for the counts of the
 // sources before it (prefix) and then, message by message, for the header of each slot; rows are
 // packed expert-major as they land: grouped by source rank in ascending order, scales
@@ -20,10 +21,12 @@
 //
 // Combine, SEND phase: every packed row goes back to row [top-k lane][token] of its source
 // rank's combine area (the lane travelled with the token, which keeps the area at
-// lanes x tokens rows, small enough to stay in L2), followed -- one row late, as above -- by a
-// call-tagged flag word for exactly that (lane, token). Combine, RECV phase: per token, wait for
-// the flags of its own rows only, accumulate sum_k w_k * row_k in fp32 in ascending lane order,
-// round to bf16 once. Nothing is counted and nothing has to be cleared between calls.
+// lanes x tokens rows, small enough to stay in L2). A block sends its rows in rounds of one row
+// per warp; behind each round one thread issues the system-scope release fence for the whole
+// block and every warp then writes the call-tagged flag word of its (lane, token). Combine, RECV
+// phase: per token, wait for the flags of its own rows only, accumulate sum_k w_k * row_k in
+// fp32 in ascending lane order, round to bf16 once. Nothing is counted and nothing has to be
+// cleared between calls.
 //
 // No host synchronisation, no launch parameter that changes from call to call: the call
 // counters that select the buffer half and tag the flags live in device memory, so a captured
@@ -252,8 +255,7 @@ __global__ void __launch_bounds__(1024, 1) ll_dispatch_kernel(const __grid_const
         int4 first_raw = make_int4(0, 0, 0, 0);
         if (bid < T && tid * 8 < H) first_raw = ld_nc_int4(p.x + (static_cast<int64_t>(bid) * H + tid * 8) * 2);
         for (int i = tid; i < T * K; i += blockDim.x) {
-            const int64_t raw = p.topk_idx[i];
-            s_topk[i] = (raw >= 0 && raw < E) ? static_cast<int>(raw) : -1;
+            s_topk[i] = load_topk_idx(p.topk_idx, p.idx32 != 0, i, E);
         }
         __syncthreads();
 
@@ -276,8 +278,12 @@ __global__ void __launch_bounds__(1024, 1) ll_dispatch_kernel(const __grid_const
         if (num_warps > K && warp >= K) publish_counts(warp - K);
 
         int iter = 0;
-        uint64_t* pending_hdr = nullptr;        // lane 0 of a sending warp: header of the message issued one token ago
-        uint64_t pending_val = 0;
+        // Headers (= arrival flags) of the K messages of a token: the sending warps park them here once wait_group has
+        // confirmed their payload; warp K then issues ONE release fence at system scope for the whole token and writes the
+        // K headers. (A fence per message costs microseconds apiece when the warps of an SM issue them side by side; a
+        // plain store behind wait_group is not enough: over NVLink the small header can overtake its payload.)
+        __shared__ uint64_t* s_hdr[kMaxLLTopk];
+        __shared__ uint64_t s_hval[kMaxLLTopk];
         for (int t = bid; t < T; t += nb, ++iter) {
             uint8_t* msg = s_msg + (iter & 1) * msg_stride;
             uint8_t* payload = msg + 16;
@@ -335,24 +341,24 @@ __global__ void __launch_bounds__(1024, 1) ll_dispatch_kernel(const __grid_const
                         uint8_t* dst_msg = c.heap[dst] + p.off_recv_x[half] +
                                            ((static_cast<uint64_t>(e - dst * EL) * R + c.rank) * Tm + slot) * msg_bytes;
                         bulk_s2g(dst_msg + 16, payload, msg_bytes - 16);
+                        bulk_commit();
+                        bulk_wait_all();
                         hdr = reinterpret_cast<uint64_t*>(dst_msg);
                     }
-                    bulk_commit();              // (an empty group when nothing was sent keeps the group count in step)
-                    // the message before this one has landed once all but the newest group are complete: flag it now
-                    bulk_wait<1>();
-                    if (pending_hdr != nullptr) st_relaxed_sys_u64(pending_hdr, pending_val);
-                    pending_hdr = hdr;
-                    pending_val = pack_epoch(epoch, static_cast<uint32_t>(t | (warp << 16)));
+                    s_hdr[warp] = hdr;
+                    s_hval[warp] = pack_epoch(epoch, static_cast<uint32_t>(t | (warp << 16)));
                 }
                 __syncwarp();
             }
-        }
-        if (warp < K) {
-            if (lane == 0) {
-                bulk_wait_all();
-                if (pending_hdr != nullptr) st_relaxed_sys_u64(pending_hdr, pending_val);
+            if (warp <= K) {
+                // warps 0..K-1 have their stores confirmed, warp K raises the flags behind one fence
+                asm volatile("bar.sync 1, %0;" ::"r"((K + 1) * 32) : "memory");
+                if (warp == K) {
+                    if (lane == 0) fence_acq_rel_sys();
+                    __syncwarp();
+                    if (lane < K && s_hdr[lane] != nullptr) st_relaxed_sys_u64(s_hdr[lane], s_hval[lane]);
+                }
             }
-            __syncwarp();
         }
         if (num_warps <= K) publish_counts(warp);
         if (stamper) stamps[1] = globaltimer_ns();
@@ -515,8 +521,18 @@ __global__ void __launch_bounds__(512, 1) ll_combine_kernel(const __grid_constan
         }
         __syncwarp();
         uint32_t parity = 0;
-        uint64_t* pending_flag = nullptr;       // lane 0: flag of the row issued one iteration ago
-        for (int g = bid * num_warps + warp; g < total_rows; g += nb * num_warps) {
+        // Rows are taken in rounds (one row per warp and round). Per round: every warp stores its row and waits until
+        // wait_group has confirmed it, the block meets, ONE thread issues a release fence at system scope, the block
+        // meets again and every warp raises the flag of its row. (A fence per row costs microseconds apiece when the
+        // warps of an SM issue them side by side; without any fence the flag can overtake its row on NVLink.)
+        __shared__ int s_alive;
+        if (tid == 0) s_alive = 1;
+        __syncthreads();
+        const int my_rows = max(total_rows - bid * num_warps, 0);
+        const int rounds = ceil_div(my_rows, nb * num_warps);
+        // sends row g if there is one for this warp; returns the address of its flag (lane 0), null if nothing was sent
+        auto send_row = [&](int g) -> uint64_t* {
+            if (g >= total_rows) return nullptr;
             int le = 0;
             {   // largest le with s_pref[le] <= g
                 int lo = 0, hi = EL - 1;
@@ -529,41 +545,44 @@ __global__ void __launch_bounds__(512, 1) ll_combine_kernel(const __grid_constan
             const int j = g - s_pref[le];
             int s = 0;
             while (s < R - 1 && j >= static_cast<int>(p.layout_range[le * R + s + 1] >> 32)) ++s;
-            if (ld_volatile_int(mask + s) != 0) continue;
+            if (ld_volatile_int(mask + s) != 0) return nullptr;
             const int64_t row = static_cast<int64_t>(le) * R * Tm + j;
             const int info = p.src_info[row];
             const int token = info & 0xffff, k = info >> 16;
-            bulk_wait_read_all();
-            __syncwarp();
             if (lane == 0) {
                 mbar_arrive_expect_tx(bar, row_bytes);
                 bulk_g2s(payload, p.x + row * row_bytes, row_bytes, bar);
             }
             const bool landed = mbar_wait(w, bar, parity, kStatusTmaLoad, g);
             parity ^= 1;
-            if (!__all_sync(0xffffffffu, landed)) break;
+            if (!__all_sync(0xffffffffu, landed)) {
+                if (lane == 0) s_alive = 0;       // reported; the block stops after this round
+                return nullptr;
+            }
             int send_bytes = row_bytes;
             if (p.use_logfmt) {
                 send_bytes = meta_bytes + logfmt_encode_row(buf, payload, H, lane);
                 fence_proxy_async_smem();
                 __syncwarp();
             }
+            uint64_t* flag = nullptr;
             if (lane == 0) {
                 bulk_s2g(c.heap[s] + p.off_combine_x[half] + (static_cast<uint64_t>(k) * Tm + token) * slot_bytes, buf, send_bytes);
                 bulk_commit();
-                // the row before this one has landed once all but the newest group are complete: raise its flag now
-                bulk_wait<1>();
-                if (pending_flag != nullptr) st_relaxed_sys_u64(pending_flag, pack_epoch(epoch, 1));
-                pending_flag = reinterpret_cast<uint64_t*>(c.heap[s] + p.off_combine_flag[half]) + static_cast<uint64_t>(k) * Tm + token;
+                bulk_wait_all();
+                flag = reinterpret_cast<uint64_t*>(c.heap[s] + p.off_combine_flag[half]) + static_cast<uint64_t>(k) * Tm + token;
             }
-            __syncwarp();
+            return flag;
+        };
+        for (int r = 0; r < rounds; ++r) {
+            uint64_t* flag = send_row((r * nb + bid) * num_warps + warp);
+            if (stamper) stamps[1] = globaltimer_ns();
+            __syncthreads();
+            if (tid == 0) fence_acq_rel_sys();
+            __syncthreads();
+            if (lane == 0 && flag != nullptr) st_relaxed_sys_u64(flag, pack_epoch(epoch, 1));
+            if (s_alive == 0) break;
         }
-        if (stamper) stamps[1] = globaltimer_ns();
-        if (lane == 0) {
-            bulk_wait_all();
-            if (pending_flag != nullptr) st_relaxed_sys_u64(pending_flag, pack_epoch(epoch, 1));
-        }
-        __syncwarp();
         if (stamper) stamps[2] = globaltimer_ns();
         ll_phase_done(c, 2, nb);
         if (stamper) stamps[3] = globaltimer_ns();
@@ -578,8 +597,7 @@ __global__ void __launch_bounds__(512, 1) ll_combine_kernel(const __grid_constan
         for (int t = bid; t < T; t += nb) {
             __syncthreads();
             if (tid < K) {
-                const int64_t raw = p.topk_idx[static_cast<int64_t>(t) * K + tid];
-                const int e = (raw >= 0 && raw < E) ? static_cast<int>(raw) : -1;
+                const int e = load_topk_idx(p.topk_idx, p.idx32 != 0, static_cast<int64_t>(t) * K + tid, E);
                 int ok = 0;
                 if (e >= 0 && ld_volatile_int(mask + e / EL) == 0) {
                     const uint64_t* word = reinterpret_cast<const uint64_t*>(c.heap[c.rank] + p.off_combine_flag[half]) + static_cast<uint64_t>(tid) * Tm + t;

@@ -175,23 +175,23 @@ __global__ void __launch_bounds__(kAgThreads, 1) ag_gemm_kernel(const __grid_con
         const int workers = p.num_comm_ctas * num_warps;
         const int me = bid * num_warps + warp;
         uint32_t parity = 0;
-        // Two buffers per warp; a buffer is reused once its store has READ it (wait_group.read), while a row is
-        // counted as landed four rows late, once wait_group has confirmed the remote writes. Several rows per
-        // lane are therefore on the wire at any time and the NVLink round trip stays off the critical path.
-        auto landed_row = [&](int chunk) {
-            fence_proxy_async_all();
-            __threadfence();
+        // Two buffers per warp; a buffer is reused once its store has READ it (wait_group.read), while rows are
+        // counted as landed at least four rows late and four at a time, once wait_group has confirmed their remote
+        // writes: ONE system-scope fence then covers the four rows (such a fence costs microseconds on an SM with
+        // peer stores in flight, so it is not paid per row). Several rows per lane are therefore on the wire at any
+        // time and the NVLink round trip stays off the critical path.
+        auto landed_row = [&](int chunk) {       // after a system-scope fence behind the row's wait_group
             const int old = atomicAdd(done + chunk * kMaxRanks + lane, 1);
             if (old == BM - 1) {
                 done[chunk * kMaxRanks + lane] = 0;
-                __threadfence();
+                fence_acq_rel_sys();             // behind the other senders' rows, which their (fenced) adds announced
                 uint64_t* flag = reinterpret_cast<uint64_t*>(c.heap[lane]) + kCtlTileFlags + c.rank * 64 + chunk;
                 st_release_sys_u64(flag, pack_epoch(p.epoch, 1));
             }
         };
         const bool sender = lane < R && lane != c.rank;
         uint8_t* buf2[2] = {buf, buf + num_warps * stage};
-        int pend0 = -1, pend1 = -1, pend2 = -1, pend3 = -1, it = 0;   // chunks of the last four rows sent (oldest first)
+        int it = 0, retired = 0;     // rows of this warp sent / counted as landed (row of iteration j = me + j * workers)
         for (int row = me; row < Ml && R > 1; row += workers, ++it) {
             uint8_t* cur = buf2[it & 1];
             bulk_wait_read<1>();        // the store that used this buffer two rows ago has read it
@@ -206,21 +206,18 @@ __global__ void __launch_bounds__(kAgThreads, 1) ag_gemm_kernel(const __grid_con
             if (sender) {
                 bulk_s2g(c.heap[lane] + p.off_gather + (static_cast<uint64_t>(c.rank) * Ml + row) * row_bytes, cur, row_bytes);
                 bulk_commit();
-                bulk_wait<4>();
-                if (pend0 >= 0) landed_row(pend0);
-                pend0 = pend1;
-                pend1 = pend2;
-                pend2 = pend3;
-                pend3 = row / BM;
+                if (it - 3 - retired >= 4) {         // four more rows are at least four stores old
+                    bulk_wait<4>();
+                    fence_acq_rel_sys();
+                    for (; retired <= it - 4; ++retired) landed_row((me + retired * workers) / BM);
+                }
             }
             __syncwarp();
         }
-        if (sender) {
+        if (sender && retired < it) {
             bulk_wait_all();
-            if (pend0 >= 0) landed_row(pend0);
-            if (pend1 >= 0) landed_row(pend1);
-            if (pend2 >= 0) landed_row(pend2);
-            if (pend3 >= 0) landed_row(pend3);
+            fence_acq_rel_sys();
+            for (; retired < it; ++retired) landed_row((me + retired * workers) / BM);
         }
         bulk_wait_all();
         return;
@@ -510,8 +507,8 @@ __global__ void __launch_bounds__(kRsThreads, 1) gemm_rs_kernel(const __grid_con
             // tile's store only has to have read the staging row before the next tile overwrites it.
             bulk_wait<1>();
             if (prev_flag != nullptr) {
-                fence_proxy_async_all();
-                __threadfence();
+                // every lane's store of the previous tile is complete (wait_group above); the warp barrier collects
+                // them behind the one release add of the tile
                 __syncwarp();
                 if (lane == 0) red_add_release_sys_u64(prev_flag, 1);
             }
@@ -521,8 +518,6 @@ __global__ void __launch_bounds__(kRsThreads, 1) gemm_rs_kernel(const __grid_con
         }
         bulk_wait_all();
         if (prev_flag != nullptr) {
-            fence_proxy_async_all();
-            __threadfence();
             __syncwarp();
             // one arrival per epilogue warp on the tile's flag word: the reducer waits for 4 arrivals per call
             if (lane == 0) red_add_release_sys_u64(prev_flag, 1);

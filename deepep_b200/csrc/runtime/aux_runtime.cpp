@@ -158,7 +158,7 @@ std::vector<std::tuple<at::Tensor, std::optional<at::Tensor>>> engram_gather(
         auto& rt = *rts[v];
         const auto& idx = indices[v];
         EP_HOST_ASSERT(idx.is_cuda() && idx.dim() == 2 && idx.scalar_type() == at::kInt && idx.is_contiguous());
-        EP_HOST_ASSERT(table_offset + static_cast<int64_t>(entries_per_rank) * row_bytes <= rt.num_bytes());
+        EP_HOST_ASSERT(!host_tables.empty() || table_offset + static_cast<int64_t>(entries_per_rank) * row_bytes <= rt.num_bytes());
         const int tokens = static_cast<int>(idx.size(0)), per_token = static_cast<int>(idx.size(1));
         auto data = at::empty({static_cast<int64_t>(tokens) * per_token, hidden}, idx.options().dtype(dtype));
         std::optional<at::Tensor> sf_out;

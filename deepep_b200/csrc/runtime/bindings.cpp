@@ -160,5 +160,14 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
         .def_static("combine", &Runtime::combine, py::call_guard<py::gil_scoped_release>())
         .def_static("ht_buffer_size", &Runtime::ht_buffer_size);
 
+    // A host-side wait of the given length without the GIL: what a driver does while it spins on the received counts
+    // or synchronises a stream. Lets a CPU test check that Python threads (the heartbeat) keep running meanwhile.
+    m.def("debug_blocking_host_wait", [](double seconds) {
+        const auto end = std::chrono::steady_clock::now() + std::chrono::duration<double>(seconds);
+        volatile uint64_t spins = 0;
+        while (std::chrono::steady_clock::now() < end) ++spins;
+        return static_cast<uint64_t>(spins);
+    }, py::call_guard<py::gil_scoped_release>());
+
     register_extra_bindings(m);
 }

@@ -80,7 +80,7 @@ std::optional<EventHandle> ll_dispatch(const std::vector<std::shared_ptr<Runtime
         auto& rt = *rts[v];
         auto& io = *ios[v];
         EP_HOST_ASSERT(io.x.scalar_type() == at::kBFloat16 && io.x.is_contiguous() && io.x.size(1) == H && io.x.size(0) <= Tm);
-        EP_HOST_ASSERT(io.topk_idx.scalar_type() == at::kLong && io.topk_idx.is_contiguous() && io.topk_idx.size(0) == io.x.size(0) && io.topk_idx.size(1) == K);
+        EP_HOST_ASSERT((io.topk_idx.scalar_type() == at::kLong || io.topk_idx.scalar_type() == at::kInt) && io.topk_idx.is_contiguous() && io.topk_idx.size(0) == io.x.size(0) && io.topk_idx.size(1) == K);
         if (!io.packed_recv_x.defined()) {
             io.packed_recv_x = at::empty({EL, R * Tm, H}, opts(use_fp8 ? at::kFloat8_e4m3fn : at::kBFloat16, device));
             io.packed_recv_count = at::empty({EL}, opts(at::kInt, device));
@@ -105,7 +105,8 @@ std::optional<EventHandle> ll_dispatch(const std::vector<std::shared_ptr<Runtime
         p.phases = phases;
         p.shrink = shrink;
         p.x = static_cast<const uint8_t*>(io.x.data_ptr());
-        p.topk_idx = io.topk_idx.data_ptr<int64_t>();
+        p.topk_idx = io.topk_idx.data_ptr();
+        p.idx32 = io.topk_idx.scalar_type() == at::kInt ? 1 : 0;
         p.packed_recv_x = static_cast<uint8_t*>(io.packed_recv_x.data_ptr());
         p.packed_recv_sf = io.packed_recv_sf.has_value() ? static_cast<uint8_t*>(io.packed_recv_sf->data_ptr()) : nullptr;
         p.packed_recv_src_info = io.src_info.data_ptr<int>();
@@ -149,7 +150,7 @@ std::optional<EventHandle> ll_combine(const std::vector<std::shared_ptr<Runtime>
         auto& io = *ios[v];
         EP_HOST_ASSERT(io.x.scalar_type() == at::kBFloat16 && io.x.is_contiguous() && io.x.dim() == 3 && io.x.size(0) == EL &&
                        io.x.size(1) == R * Tm && io.x.size(2) == H);
-        EP_HOST_ASSERT(io.topk_idx.scalar_type() == at::kLong && io.topk_idx.is_contiguous());
+        EP_HOST_ASSERT((io.topk_idx.scalar_type() == at::kLong || io.topk_idx.scalar_type() == at::kInt) && io.topk_idx.is_contiguous());
         EP_HOST_ASSERT(io.topk_weights.scalar_type() == at::kFloat && io.topk_weights.is_contiguous() && io.topk_weights.size(1) == K);
         const int T = static_cast<int>(io.topk_idx.size(0));
         if (!io.combined_x.defined()) io.combined_x = at::empty({T, H}, opts(at::kBFloat16, device));
@@ -166,7 +167,8 @@ std::optional<EventHandle> ll_combine(const std::vector<std::shared_ptr<Runtime>
         p.shrink = shrink;
         p.use_logfmt = ios[0]->use_logfmt ? 1 : 0;
         p.x = static_cast<const uint8_t*>(io.x.data_ptr());
-        p.topk_idx = io.topk_idx.data_ptr<int64_t>();
+        p.topk_idx = io.topk_idx.data_ptr();
+        p.idx32 = io.topk_idx.scalar_type() == at::kInt ? 1 : 0;
         p.topk_weights = io.topk_weights.data_ptr<float>();
         p.src_info = io.src_info.data_ptr<int>();
         p.layout_range = io.layout_range.data_ptr<int64_t>();
@@ -207,7 +209,7 @@ void ll_mask_query(Runtime& rt, at::Tensor out) {
 std::tuple<at::Tensor, at::Tensor, at::Tensor, std::optional<EventHandle>> get_dispatch_layout(
     Runtime& rt, const at::Tensor& topk_idx, int num_experts, std::optional<EventHandle> previous_event, bool async_finish,
     bool allocate_on_comm_stream) {
-    EP_HOST_ASSERT(topk_idx.dim() == 2 && topk_idx.is_contiguous() && topk_idx.scalar_type() == at::kLong && topk_idx.is_cuda());
+    EP_HOST_ASSERT(topk_idx.dim() == 2 && topk_idx.is_contiguous() && (topk_idx.scalar_type() == at::kLong || topk_idx.scalar_type() == at::kInt) && topk_idx.is_cuda());
     EP_HOST_ASSERT(num_experts > 0 && num_experts % rt.num_ranks() == 0 && num_experts <= kMaxExperts);
     const int device = rt.heap().device();
     c10::cuda::CUDAGuard guard(static_cast<c10::DeviceIndex>(device));
@@ -220,7 +222,7 @@ std::tuple<at::Tensor, at::Tensor, at::Tensor, std::optional<EventHandle>> get_d
     auto per_rank = at::empty({R}, opts(at::kInt, device));
     auto per_expert = at::empty({num_experts}, opts(at::kInt, device));
     auto in_rank = at::empty({T, R}, opts(at::kBool, device));
-    CUDA_RUNTIME_CHECK(launch_dispatch_layout(topk_idx.data_ptr<int64_t>(), T, K, R, num_experts, per_rank.data_ptr<int>(),
+    CUDA_RUNTIME_CHECK(launch_dispatch_layout(topk_idx.data_ptr(), topk_idx.scalar_type() == at::kInt, T, K, R, num_experts, per_rank.data_ptr<int>(),
                                               per_expert.data_ptr<int>(), in_rank.data_ptr<bool>(), comm.stream()));
     std::optional<EventHandle> event;
     if (async_finish) {

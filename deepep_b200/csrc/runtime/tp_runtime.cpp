@@ -1,5 +1,6 @@
 // Host drivers of the fused tensor-parallel operators (all-gather -> GEMM, GEMM -> reduce-scatter).
 #include <ATen/cuda/CUDAContext.h>
+#include <cmath>
 #include <ATen/ops/empty.h>
 #include <ATen/ops/zeros.h>
 #include <pybind11/stl.h>
@@ -43,7 +44,15 @@ std::vector<at::Tensor> tp_ag_gemm(const std::vector<std::shared_ptr<Runtime>>& 
     const int Ml = static_cast<int>(a_local[0].size(0)), K = static_cast<int>(a_local[0].size(1)), N = static_cast<int>(b[0].size(0));
     const uint64_t half_bytes = static_cast<uint64_t>(R) * Ml * K * 2;
     if (num_sms <= 0) num_sms = rt0.num_device_sms() / V;
-    if (num_comm_ctas <= 0) num_comm_ctas = R > 1 ? 16 : 0;
+    if (num_comm_ctas <= 0 && R > 1) {
+        // As few push CTAs as move the shard out within about half of the GEMM's time (every CTA taken from the GEMM
+        // costs it 1 / #SMs of its rate): a push CTA was measured at about 40 GB/s, the GEMM at about 1.4 PFLOP/s.
+        const double push_cta_seconds = static_cast<double>(R - 1) * Ml * K * 2 / 40e9;
+        const double gemm_seconds = 2.0 * R * Ml * N * K / 1.4e15;
+        int n = static_cast<int>(std::ceil(push_cta_seconds / (0.5 * gemm_seconds)));
+        n = (std::max(2, std::min(n, 32)) + 1) & ~1;
+        num_comm_ctas = std::min(n, std::max(2, (num_sms / 4) & ~1));
+    }
     if (R == 1) num_comm_ctas = 0;
     std::vector<gemm::AgGemmParams> params(V);
     std::vector<const void*> bptr(V), gptr(V);

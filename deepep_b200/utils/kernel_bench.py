@@ -7,7 +7,8 @@
 
 Ops: ``dispatch`` (fused FP8 cast), ``dispatch_prequant``, ``dispatch_bf16``, ``combine``, ``gemm``,
 ``gemm_fp8_grouped``, ``ll`` (low-latency dispatch + combine), ``ops`` (router, SwiGLU, quantisation, transpose),
-``ag_gemm`` / ``gemm_rs`` (fused tensor-parallel operators with emulated ranks). Times are CUDA-event means on one
+``ag_gemm`` / ``gemm_rs`` (fused tensor-parallel operators with emulated ranks), ``ht_emulated`` (dispatch + combine
+with emulated ranks: all kernels of the multi-rank path). Times are CUDA-event means on one
 rank (EP1: all traffic is local, so dispatch / combine show the SM-side cost of the kernels, not
 NVLink).
 """
@@ -116,6 +117,28 @@ def main():
         print(f'll dispatch+combine: {ms * 1e3:.1f} us, tokens {Tl}')
         ll.check_status()
         ll.destroy()
+    elif a.op == 'ht_emulated':
+        # dispatch + combine with `--ranks` emulated ranks on this GPU: every kernel of the multi-rank path runs (count
+        # exchange, epilogue, arrival-driven reduce), with local "peers"
+        from deepep_b200.parallel.local_cluster import LocalCluster
+        R = a.ranks
+        cl = LocalCluster(R, num_max_tokens_per_rank=T, hidden=H, num_topk=K, use_fp8_dispatch=True, num_gpu_timeout_secs=20)
+        xs = [torch.randn((T, H), generator=g).bfloat16().cuda() for _ in range(R)]
+        routed = [gate.topk_from_scores(gate.get_balanced_scores(T, E, generator=g), K) for _ in range(R)]
+        idxs, ws = [i.cuda() for i, _ in routed], [w.cuda() for _, w in routed]
+        ys = {}
+
+        def step():
+            out = cl.dispatch([dict(x=xs[r], topk_idx=idxs[r], topk_weights=ws[r], num_experts=E, num_sms=a.sms, fused_fp8=True,
+                                    zero_copy=True, do_cpu_sync=False) for r in range(R)])
+            for r in range(R):
+                if r not in ys:
+                    ys[r] = torch.randn((out[r][0][0].size(0), H), device='cuda', dtype=torch.bfloat16)
+            cl.combine([dict(x=ys[r], handle=out[r][3], topk_weights=out[r][2]) for r in range(R)])
+        ms = _timeit(step, a.iters, a.warmup)
+        print(f'dispatch + combine, {R} emulated ranks x {T} tokens, {a.sms} SMs per rank: {ms * 1e3:.1f} us per step')
+        cl.check_status()
+        cl.destroy()
     elif a.op == 'ops':
         # the small MoE operators: router top-k, SwiGLU (+ fused cast), SwiGLU backward, 1x128 quantisation, transpose
         rows, inter = a.m, a.k // 4 // 128 * 128

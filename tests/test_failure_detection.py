@@ -50,6 +50,37 @@ def test_heartbeat_notices_a_rank_that_stops():
     assert dead == [1]
 
 
+class _DictStore:
+    """The two methods of a ``torch.distributed`` store that the heartbeat uses."""
+
+    def __init__(self):
+        self.data = {}
+
+    def set(self, key, value):
+        self.data[key] = value
+
+    def get(self, key):
+        return self.data[key].encode()
+
+
+def test_heartbeat_keeps_beating_while_a_native_call_blocks():
+    """A healthy rank that sits in a long native wait (the drivers release the GIL for the host spin on the received
+    counts and for stream synchronisation) must keep publishing its beat: otherwise the survivors of a real failure
+    would take the waiting victim for dead as well. The wait is made on the host, no GPU is involved."""
+    import deepep_b200
+    from deepep_b200.utils.heartbeat import Heartbeat
+    if deepep_b200._C is None:
+        pytest.skip('native extension not built')
+    store = _DictStore()
+    hb = Heartbeat(store, 0, 2, interval=0.02, timeout=1.0)
+    time.sleep(0.1)
+    before = int(store.get('hb/0'))
+    deepep_b200._C.debug_blocking_host_wait(0.6)        # ~30 beat intervals inside one native call
+    after = int(store.get('hb/0'))
+    hb.stop()
+    assert after - before >= 10, f'the heartbeat advanced by only {after - before} during a blocking native call'
+
+
 @pytest.mark.gpu
 def test_device_wait_runs_out_and_reports():
     import deepep_b200

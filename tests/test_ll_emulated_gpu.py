@@ -162,6 +162,18 @@ def test_ll_recv_hook_split():
         for le in range(E // R):
             c = int(a.packed_recv_count[le].item())
             assert torch.equal(a.packed_recv_x[le, :c], b.packed_recv_x[le, :c])
+    # the routing may come as int32 as well (EP_NUM_TOPK_IDX_BITS=32 builds of the reference): same result
+    idxs32 = [i.int() for i in idxs]
+    narrow = cl.low_latency_dispatch(xs, idxs32, T, E, False, num_sms=4)
+    ys = [torch.randn((E // R, R * T, H), device='cuda').bfloat16() for _ in range(R)]
+    out64 = [c.combined_x.clone() for c in cl.low_latency_combine(ys, idxs, ws, narrow, T, E, num_sms=4)]
+    again = cl.low_latency_dispatch(xs, idxs32, T, E, False, num_sms=4)
+    out32 = [c.combined_x.clone() for c in cl.low_latency_combine(ys, idxs32, ws, again, T, E, num_sms=4)]
+    torch.cuda.synchronize()
+    cl.check_status()
+    for a, b, o64, o32 in zip(narrow, full, out64, out32):
+        assert torch.equal(a.packed_recv_count, b.packed_recv_count) and torch.equal(a.layout_range, b.layout_range)
+        assert torch.equal(o64, o32)
     cl.destroy()
 
 
@@ -178,6 +190,8 @@ def test_legacy_buffer_single_rank_and_graph():
     # layout query + normal mode
     per_rank, _, per_expert, in_rank, _ = buf.get_dispatch_layout(idx, E)
     assert int(per_rank[0]) == T and int(per_expert.sum()) == T * K and bool(in_rank.all())
+    per_rank32, _, per_expert32, _, _ = buf.get_dispatch_layout(idx.int(), E)
+    assert torch.equal(per_rank32, per_rank) and torch.equal(per_expert32, per_expert)
     recv_x, recv_idx, recv_w, counts, handle, _ = buf.dispatch(x, topk_idx=idx, topk_weights=w, num_tokens_per_rank=per_rank,
                                                                is_token_in_rank=in_rank, num_tokens_per_expert=per_expert)
     assert torch.equal(recv_x, x) and counts == per_expert.tolist()
