@@ -172,15 +172,16 @@ __device__ __noinline__ void reduce_token_registers(const CombineEpilogueParams&
 }
 
 // ==================================================================== reduce epilogue (local, all SMs)
-// Rows are staged through shared memory with bulk copies: a warp keeps kEpiStages chunks of 1 KB of every contributing
-// row in flight (several times the bytes a lane could hold in registers), then every lane sums its two 16-byte pieces
-// of the chunk over the rows in ascending lane order. The chunk size matters: every chunk costs a proxy fence, two
+// Rows are staged through shared memory with bulk copies: a warp owns a ring of kEpiSlots chunk slots of 1 KB and keeps
+// floor(kEpiSlots / n) chunks of each of a token's n contributing rows in flight (8 deep for two rows, 2 deep for
+// eight: the bytes in flight per SM, which set the bandwidth a reduce SM reaches, do not depend on the routing), then
+// every lane sums its two 16-byte pieces of the chunk over the rows in ascending lane order. The chunk size matters: every chunk costs a proxy fence, two
 // warp barriers and an mbarrier round, and with 512-byte chunks that fixed cost, not memory, set the pace (147 us
 // against 130 us for the EP8-shaped case). Tokens with at most one row, more than kEpiRows rows, or a row size that is
 // not a multiple of the chunk take the register path (reduce_token).
-constexpr int kEpiStages = 2, kEpiRows = 8, kEpiChunk = 1024, kEpiWarps = 12;
-constexpr int kEpiWarpBytes = kEpiStages * kEpiRows * kEpiChunk;
-constexpr int kEpiSmem = kEpiWarps * kEpiWarpBytes + kEpiWarps * kEpiStages * 8;
+constexpr int kEpiSlots = 16, kEpiMaxDepth = 8, kEpiRows = 8, kEpiChunk = 1024, kEpiWarps = 12;
+constexpr int kEpiWarpBytes = kEpiSlots * kEpiChunk;
+constexpr int kEpiSmem = kEpiWarps * kEpiWarpBytes + kEpiWarps * kEpiMaxDepth * 8;
 
 __global__ void __launch_bounds__(kEpiWarps * 32) combine_epilogue_kernel(const __grid_constant__ Multi<CombineEpilogueParams> m) {
     extern __shared__ __align__(128) uint8_t epi_smem[];
@@ -191,9 +192,9 @@ __global__ void __launch_bounds__(kEpiWarps * 32) combine_epilogue_kernel(const 
     const int lane = lane_id(), warp = warp_id();
     const int num_warps = blockDim.x >> 5;
     uint8_t* sbuf = epi_smem + static_cast<size_t>(warp) * kEpiWarpBytes;
-    uint64_t* bars = reinterpret_cast<uint64_t*>(epi_smem + kEpiWarps * kEpiWarpBytes) + warp * kEpiStages;
+    uint64_t* bars = reinterpret_cast<uint64_t*>(epi_smem + kEpiWarps * kEpiWarpBytes) + warp * kEpiMaxDepth;
     if (lane == 0) {
-        for (int s = 0; s < kEpiStages; ++s) mbar_init(bars + s, 1);
+        for (int s = 0; s < kEpiMaxDepth; ++s) mbar_init(bars + s, 1);
         fence_mbar_init();
     }
     __syncwarp();
@@ -265,17 +266,18 @@ __global__ void __launch_bounds__(kEpiWarps * 32) combine_epilogue_kernel(const 
         const float my_wt = (p.weighted && lane < n) ? row_weight(p, t, my_slot) : 1.f;
         const uint8_t* my_src = p.region_x + (static_cast<uint64_t>(my_slot) * p.num_max_tokens + t) * row_bytes;
         uint8_t* dst = p.combined_x + t * row_bytes;
-        for (int c = 0; c < nchunks + kEpiStages - 1 && staged_ok; ++c) {
+        const int depth = min(kEpiMaxDepth, kEpiSlots / n);      // stage s of this token = slots [s * n, (s + 1) * n)
+        for (int c = 0; c < nchunks + depth - 1 && staged_ok; ++c) {
             if (c < nchunks) {
-                const int s = c % kEpiStages;
+                const int s = c % depth;
                 fence_proxy_async_smem();       // this stage was read (generic proxy) one iteration ago
                 __syncwarp();
                 if (lane == 0) mbar_arrive_expect_tx(bars + s, static_cast<uint32_t>(n) * kEpiChunk);
                 __syncwarp();
-                if (lane < n) bulk_g2s(sbuf + (s * kEpiRows + lane) * kEpiChunk, my_src + static_cast<uint64_t>(c) * kEpiChunk, kEpiChunk, bars + s);
+                if (lane < n) bulk_g2s(sbuf + (s * n + lane) * kEpiChunk, my_src + static_cast<uint64_t>(c) * kEpiChunk, kEpiChunk, bars + s);
             }
-            if (c >= kEpiStages - 1) {
-                const int cc = c - (kEpiStages - 1), s = cc % kEpiStages;
+            if (c >= depth - 1) {
+                const int cc = c - (depth - 1), s = cc % depth;
                 uint32_t spins = 0;
                 bool ok = true;
                 while (!mbar_try_wait(bars + s, (parity >> s) & 1u)) {
@@ -293,7 +295,7 @@ __global__ void __launch_bounds__(kEpiWarps * 32) combine_epilogue_kernel(const 
                     for (int r = 0; r < kEpiRows; ++r) {
                         const float wt = p.weighted ? __shfl_sync(0xffffffffu, my_wt, r) : 1.f;
                         if (r < n) {
-                            const int4 raw = *reinterpret_cast<const int4*>(sbuf + (s * kEpiRows + r) * kEpiChunk + h * 512 + lane * 16);
+                            const int4 raw = *reinterpret_cast<const int4*>(sbuf + (s * n + r) * kEpiChunk + h * 512 + lane * 16);
                             if (p.weighted) accumulate_bf16x8_scaled(acc, raw, wt);
                             else accumulate_bf16x8(acc, raw);
                         }

@@ -121,6 +121,57 @@ void copy_to_heap(Runtime& rt, int peer, int64_t offset, const at::Tensor& src) 
     CUDA_RUNTIME_CHECK(cudaMemcpyAsync(rt.heap().peer(peer) + offset, src.data_ptr(), bytes, cudaMemcpyDeviceToDevice, cur_stream()));
 }
 
+// Several copy-engine transfers side by side: copy i runs on side stream i % kFanStreams, forked from and joined to
+// the current stream with events, so that copies to different peers use different copy engines instead of queueing
+// behind one another. One binding call for all of them (the host cost of a call is of the order of a small copy).
+struct FanOut {
+    static constexpr int kFanStreams = 7;
+    cudaStream_t streams[kFanStreams] = {};
+    cudaEvent_t fork = nullptr, join[kFanStreams] = {};
+    bool ready = false;
+    void init() {
+        if (ready) return;
+        for (auto& st : streams) CUDA_RUNTIME_CHECK(cudaStreamCreateWithFlags(&st, cudaStreamNonBlocking));
+        CUDA_RUNTIME_CHECK(cudaEventCreateWithFlags(&fork, cudaEventDisableTiming));
+        for (auto& ev : join) CUDA_RUNTIME_CHECK(cudaEventCreateWithFlags(&ev, cudaEventDisableTiming));
+        ready = true;
+    }
+};
+
+FanOut& fan_out(int device) {
+    static FanOut pools[64];
+    EP_HOST_ASSERT(device >= 0 && device < 64);
+    pools[device].init();
+    return pools[device];
+}
+
+void copy_fanout(Runtime& rt, const std::vector<std::tuple<int, int64_t, at::Tensor>>& copies) {
+    if (copies.empty()) return;
+    c10::cuda::CUDAGuard guard(static_cast<c10::DeviceIndex>(rt.heap().device()));
+    const cudaStream_t stream = cur_stream();
+    if (copies.size() == 1) {
+        copy_to_heap(rt, std::get<0>(copies[0]), std::get<1>(copies[0]), std::get<2>(copies[0]));
+        return;
+    }
+    FanOut& f = fan_out(rt.heap().device());
+    CUDA_RUNTIME_CHECK(cudaEventRecord(f.fork, stream));
+    const int used = std::min<int>(FanOut::kFanStreams, static_cast<int>(copies.size()));
+    for (int i = 0; i < used; ++i) CUDA_RUNTIME_CHECK(cudaStreamWaitEvent(f.streams[i], f.fork, 0));
+    for (size_t i = 0; i < copies.size(); ++i) {
+        const auto& [peer, offset, src] = copies[i];
+        EP_HOST_ASSERT(src.is_cuda() && src.is_contiguous() && peer >= 0 && peer < rt.num_ranks());
+        const int64_t bytes = src.numel() * src.element_size();
+        EP_HOST_ASSERT(offset >= static_cast<int64_t>(kCtlBytes) && offset + bytes <= rt.num_bytes());
+        if (bytes == 0) continue;
+        CUDA_RUNTIME_CHECK(cudaMemcpyAsync(rt.heap().peer(peer) + offset, src.data_ptr(), bytes, cudaMemcpyDeviceToDevice,
+                                           f.streams[i % FanOut::kFanStreams]));
+    }
+    for (int i = 0; i < used; ++i) {
+        CUDA_RUNTIME_CHECK(cudaEventRecord(f.join[i], f.streams[i]));
+        CUDA_RUNTIME_CHECK(cudaStreamWaitEvent(stream, f.join[i], 0));
+    }
+}
+
 void copy_from_heap(Runtime& rt, int64_t offset, at::Tensor dst) {
     EP_HOST_ASSERT(dst.is_cuda() && dst.is_contiguous());
     const int64_t bytes = dst.numel() * dst.element_size();
@@ -219,6 +270,7 @@ void register_aux_bindings(py::module_& m) {
     m.def("flag_op", &flag_op);
     m.def("stream_memops_enabled", &stream_memops_enabled);
     m.def("copy_to_heap", &copy_to_heap);
+    m.def("copy_fanout", &copy_fanout);
     m.def("copy_from_heap", &copy_from_heap);
     m.def("reduce_slots", &reduce_slots);
     m.def("engram_gather", &engram_gather);

@@ -2,7 +2,8 @@
 chunk all-gather).
 
 Payload moves on the copy engines: every rank issues one ``cudaMemcpyAsync`` per peer into that
-peer's heap on the communication stream, so no SM is used for the transfer. Arrival is published
+peer's heap, each on a side stream forked from the communication stream so that the copies to
+different peers run on different copy engines; no SM is used for the transfer. Arrival is published
 and awaited by a one-block flag kernel (bounded wait). Gathered tensors are views of the heap with a
 leading ``num_ranks`` dimension; a session bounds the life of those views, and ending a session
 tells the peers that this rank is done reading, which is what allows the next session to overwrite
@@ -146,10 +147,9 @@ class AgrsManager:
                     inplace = m.pending_inplace.pop(t.data_ptr(), None)
                     region = inplace[0] if inplace is not None else m._reserve(nbytes)
                     slot = _align(nbytes)
-                    for p in range(m.num_ranks):
-                        if p == m.rank and inplace is not None:
-                            continue
-                        _C.copy_to_heap(m.rt, p, region + m.rank * slot, t)
+                    # peers first, starting behind this rank (no two ranks begin with the same target), own slot last
+                    order = [(m.rank + 1 + i) % m.num_ranks for i in range(m.num_ranks)]
+                    _C.copy_fanout(m.rt, [(p, region + m.rank * slot, t) for p in order if not (p == m.rank and inplace is not None)])
                     if slot == nbytes:
                         view = m.rt.heap_tensor(region, m.num_ranks * slot).view(t.dtype).view(m.num_ranks, *t.shape)
                     else:   # padded slots: a strided view
@@ -192,8 +192,8 @@ class AgrsManager:
                 nbytes = chunks[0].numel() * t.element_size()
                 assert nbytes % 16 == 0
                 region = m._reserve(nbytes)
-                for p in range(m.num_ranks):
-                    _C.copy_to_heap(m.rt, p, region + m.rank * _align(nbytes), chunks[p])
+                order = [(m.rank + 1 + i) % m.num_ranks for i in range(m.num_ranks)]
+                _C.copy_fanout(m.rt, [(p, region + m.rank * _align(nbytes), chunks[p]) for p in order])
                 regions.append((region, nbytes))
             AgrsManager._flag_round(mgrs, mgrs[0].ag_idx)
             for m, t, (region, nbytes) in zip(mgrs, tensors, regions):

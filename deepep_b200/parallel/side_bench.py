@@ -5,7 +5,8 @@ pipeline send / recv ring, the Engram table fetch (GPU and pinned-host segments)
         -m deepep_b200.parallel.side_bench
 
 Every figure is a CUDA-event time on the launching stream (several calls between two events where one call is
-short), maximum over ranks. NCCL collectives of the same shape are timed next to each primitive as the baseline.
+short; the stream is held back by a short sleep kernel first, so the calls are queued when the clock starts and
+the figure is device time, not the host's launch time), maximum over ranks. NCCL collectives of the same shape are timed next to each primitive as the baseline.
 Rank 0 prints one JSON line per primitive. Modelled on the bandwidth sweeps at the end of the reference's
 tests/elastic/test_agrs.py:156-187, test_pp.py, test_engram.py and test_barrier.py.
 """
@@ -46,6 +47,7 @@ def main() -> None:
         total = 0.0
         for _ in range(a.iters):
             e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            torch.cuda._sleep(int(1e6))     # the host queues the calls while the device idles: device time, not launch time
             e0.record()
             for _ in range(calls):
                 fn()
