@@ -338,8 +338,10 @@ def tp_section(group, world, rank, dev, max_over_ranks, tokens=8192, hidden=7168
     # both fused operators against NCCL + matmul on the very tensors that are timed
     a, b = ctx.all_gather_gemm(x_shard, w1), nccl_all_gather_gemm(x_shard, w1, group)
     c, d = ctx.gemm_reduce_scatter(x2, w2), nccl_gemm_reduce_scatter(x2, w2, group)
+    a_sm = ctx.all_gather_gemm(x_shard, w1, push='sm')
     torch.cuda.synchronize()
-    err_ag = ((a.float() - b.float()).norm() / b.float().norm()).item()
+    err_ag = max(((a.float() - b.float()).norm() / b.float().norm()).item(), ((a_sm.float() - b.float()).norm() / b.float().norm()).item())
+    del a_sm
     err_rs = ((c.float() - d.float()).norm() / d.float().norm()).item()
     verified = max_over_ranks(0.0 if (err_ag < 1e-2 and err_rs < 2e-2) else 1.0) == 0.0
     del a, b, c, d
@@ -353,6 +355,7 @@ def tp_section(group, world, rank, dev, max_over_ranks, tokens=8192, hidden=7168
     res = {'tokens': tokens, 'hidden': hidden, 'ffn': ffn, 'verified': verified,
            'rel_err': {'ag_gemm': round(max_over_ranks(err_ag), 5), 'gemm_rs': round(max_over_ranks(err_rs), 5)},
            'ag_gemm_fused_us': round(timeit(lambda: ctx.all_gather_gemm(x_shard, w1)), 1),
+           'ag_gemm_fused_sm_push_us': round(timeit(lambda: ctx.all_gather_gemm(x_shard, w1, push='sm')), 1),
            'ag_gemm_nccl_cublas_us': round(timeit(lambda: nccl_all_gather_gemm(x_shard, w1, group)), 1),
            'gemm_rs_fused_us': round(timeit(lambda: ctx.gemm_reduce_scatter(x2, w2)), 1),
            'gemm_rs_cublas_nccl_us': round(timeit(lambda: nccl_gemm_reduce_scatter(x2, w2, group)), 1)}

@@ -1,19 +1,25 @@
 // Tensor-parallel GEMMs fused with their collective, one kernel each (bf16, sm_100a):
 //
 //   all-gather -> GEMM    C[R*Ml, N] = gather_r(A_r[Ml, K]) * B[N, K]^T
-//       A few "comm" CTAs push this rank's shard, 128-row chunk by chunk, into every peer's gather
-//       buffer with bulk copies over NVLink and raise one flag per (source, chunk) at the peer.
-//       The other CTAs run the tcgen05 main loop; the TMA producer of a tile waits (bounded) for
+//       The shard reaches every peer's gather buffer in 128-row chunks with one arrival flag per
+//       (source, chunk) at the peer, either from a few "comm" CTAs of this kernel (bulk copies over
+//       NVLink) or, with no CTA spent on it, from the copy engines (2-D copies on side streams, each
+//       chunk's flag a 64-bit stream write behind its copy; issued by the host driver).
+//       The GEMM CTAs run the tcgen05 main loop; the TMA producer of a tile waits (bounded) for
 //       the flag of the chunk it is about to read, so the math on early chunks overlaps the
 //       transfer of late ones. Own rows are read straight from the input and go first.
 //       All TMA loads read LOCAL memory (the input or the local gather buffer); none is multicast.
 //
 //   GEMM -> reduce-scatter    out[Ml, N] = sum_r (A_r[R*Ml, Kl] * B_r[N, Kl]^T)[rows of this rank]
-//       Tiles are computed destination by destination (next rank first, own rows last). The
-//       epilogue converts the accumulator to bf16, stages it in shared memory and bulk-stores it
-//       into slot [this rank] of the destination's partial buffer, then raises a per-tile flag
-//       there. After its GEMM tiles a CTA turns to the reduction of this rank's own tiles: it waits
-//       for the flags of all sources and sums the partials in fp32 in rank order.
+//       Tiles are computed destination by destination (next rank first, own rows last). For a
+//       peer's rows the epilogue converts the accumulator to bf16, stages it in shared memory and
+//       bulk-stores it into slot [this rank] of the destination's partial buffer, then raises a
+//       per-tile flag there. For the rank's own rows, which come last, the peers' partial tiles
+//       have arrived by then: the epilogue waits for their flags, adds them to the fp32 accumulator
+//       in rank order and writes the final rows (no partial of its own, no reduction pass).
+//
+// Both kernels walk their tiles in bands of eight row blocks with the row index fastest, so the
+// tiles in flight share few operand blocks (L2 reuse).
 //
 // The reference has neither operator (its AGRS path is a copy-engine all-gather only, and
 // reduce-scatter is listed as not implemented); the baseline to beat is NCCL all-gather /
@@ -129,6 +135,18 @@ struct RsLaunch {
     GemmRsParams p[kTpMaxVRanks];
     CUtensorMap map_a[kTpMaxVRanks], map_b[kTpMaxVRanks];
 };
+
+// Work items of a (rows x tiles_n) grid in bands of kBand rows: inside a band the row index runs fastest, so the CTAs at
+// work at any one time share a few B column blocks and a few A row blocks, which then stay in L2 (with the column
+// index fastest, every pass over one row block streams the whole of B, more than L2 holds, from memory again).
+constexpr int kBand = 8;
+__device__ __forceinline__ void band_order(int u, int rows, int tiles_n, int& m, int& n) {
+    const int band = u / (kBand * tiles_n);
+    const int g = min(kBand, rows - band * kBand);
+    const int v = u - band * kBand * tiles_n;
+    n = v / g;
+    m = band * kBand + v % g;
+}
 
 template <bool kPair>
 __global__ void __launch_bounds__(kAgThreads, 1) ag_gemm_kernel(const __grid_constant__ AgLaunch L) {
@@ -261,8 +279,10 @@ __global__ void __launch_bounds__(kAgThreads, 1) ag_gemm_kernel(const __grid_con
 
     // tile t -> (order index o, n block): o walks own rows first, then chunk by chunk over the sources rank+1, rank+2, ...
     auto decode = [&](int t, int& src, int& chunk, int& n0) {
-        const int o = kPair ? 2 * (t / tiles_n) + static_cast<int>(cta) : t / tiles_n;
-        n0 = (t % tiles_n) * BN;
+        int oi, ni;
+        band_order(t, total_tiles / tiles_n, tiles_n, oi, ni);
+        const int o = kPair ? 2 * oi + static_cast<int>(cta) : oi;
+        n0 = ni * BN;
         if (o < chunks) {
             src = c.rank;
             chunk = o;
@@ -427,8 +447,9 @@ __global__ void __launch_bounds__(kRsThreads, 1) gemm_rs_kernel(const __grid_con
     // work item t -> destination (next rank first, own rows last) and the 128-row tile this CTA computes of it
     auto decode = [&](int t, int& dst, int& local_tile) {
         dst = (c.rank + 1 + t / work_per_dst) % R;
-        const int u = t % work_per_dst;
-        local_tile = kPair ? ((u / tiles_n) * 2 + static_cast<int>(cta)) * tiles_n + u % tiles_n : u;
+        int mi, ni;
+        band_order(t % work_per_dst, work_per_dst / tiles_n, tiles_n, mi, ni);
+        local_tile = (kPair ? mi * 2 + static_cast<int>(cta) : mi) * tiles_n + ni;
     };
 
     if (warp == 0) {
@@ -464,15 +485,32 @@ __global__ void __launch_bounds__(kRsThreads, 1) gemm_rs_kernel(const __grid_con
             if (lane == 0) mma_role<kRsStages>(pc, smem, full, empty, tmem_full, tmem_empty, tmem_base, mine, num_kb);
         }
     } else {
-        // epilogue: accumulator -> bf16 -> staging tile -> bulk stores into the destination's partial slot -> flag
+        // epilogue: accumulator -> bf16 -> staging tile -> bulk stores into the destination's partial slot -> flag.
+        // This rank's own rows come last; by then the peers' partial tiles for them have long arrived (every rank
+        // starts with the rows of the rank behind it), so the epilogue adds them to the fp32 accumulator and writes the
+        // final rows: no partial tile of its own to store and re-read, no reduction pass after the GEMM.
         const int quarter = warp & 3;
         int acc = 0;
         uint32_t acc_ph = 0;
         uint64_t* prev_flag = nullptr;
+        const uint64_t* my_flags = reinterpret_cast<const uint64_t*>(c.heap[c.rank] + flag_off);
+        const uint8_t* my_part = c.heap[c.rank] + part_off;
+        const uint64_t target = static_cast<uint64_t>(p.flag_target);
+        const uint64_t slot_bytes = static_cast<uint64_t>(Ml) * N * 2;
         for (int t = first; t < total_work; t += stride) {
             int dst, lt;
             decode(t, dst, lt);
             const int local_m0 = (lt / tiles_n) * BM, n0 = (lt % tiles_n) * BN;
+            const bool own = dst == c.rank;
+            if (own) {
+                bool arrived = true;
+                if (lane < R && lane != c.rank) {
+                    const uint64_t* flag = my_flags + static_cast<uint64_t>(lane) * tiles_per_dst + lt;
+                    arrived = bounded_wait(w, kStatusTileFlag, lane, lt, [&]() { return ld_acquire_sys_u64(flag) >= target; });
+                }
+                if (!__all_sync(0xffffffffu, arrived) && lane == 0) atomicExch(p.error, static_cast<int>(kStatusTileFlag));
+                __syncwarp();
+            }
             if (!pipe_wait(pc, tmem_full + acc, acc_ph)) break;
             tc_fence_after();
             // (the previous tile's bulk store of this lane has completed: it is waited for right after it is issued)
@@ -483,6 +521,38 @@ __global__ void __launch_bounds__(kRsThreads, 1) gemm_rs_kernel(const __grid_con
                 uint32_t r[32];
                 tmem_ld_32x32(tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + acc * BN + cc * 32, r);
                 tmem_ld_wait();
+                if (own) {
+                    // 64 bytes of every peer's partial row, two peers (eight 16-byte loads) in flight per lane
+                    const uint8_t* base = my_part + ((static_cast<uint64_t>(local_m0) + r_in_tile) * N + n0 + cc * 32) * 2;
+#pragma unroll 1
+                    for (int s0 = 0; s0 < R; s0 += 2) {
+                        int4 pr[2][4];
+#pragma unroll
+                        for (int u = 0; u < 2; ++u) {
+                            const int src = s0 + u;
+                            if (src < R && src != c.rank) {
+#pragma unroll
+                                for (int v = 0; v < 4; ++v) pr[u][v] = ld_nc_int4(base + src * slot_bytes + v * 16);
+                            }
+                        }
+#pragma unroll
+                        for (int u = 0; u < 2; ++u) {
+                            const int src = s0 + u;
+                            if (src < R && src != c.rank) {
+#pragma unroll
+                                for (int v = 0; v < 4; ++v) {
+                                    const __nv_bfloat162* h2 = reinterpret_cast<const __nv_bfloat162*>(&pr[u][v]);
+#pragma unroll
+                                    for (int i = 0; i < 4; ++i) {
+                                        const float2 f = __bfloat1622float2(h2[i]);
+                                        r[v * 8 + 2 * i] = __float_as_uint(__uint_as_float(r[v * 8 + 2 * i]) + f.x);
+                                        r[v * 8 + 2 * i + 1] = __float_as_uint(__uint_as_float(r[v * 8 + 2 * i + 1]) + f.y);
+                                    }
+                                }
+                            }
+                        }
+                    }
+                }
 #pragma unroll
                 for (int v = 0; v < 4; ++v) {
                     int4 out;
@@ -500,7 +570,8 @@ __global__ void __launch_bounds__(kRsThreads, 1) gemm_rs_kernel(const __grid_con
             if (acc == 0) acc_ph ^= 1;
             fence_proxy_async_smem();
             __syncwarp();
-            uint8_t* dst_base = c.heap[dst] + part_off + ((static_cast<uint64_t>(c.rank) * Ml + local_m0 + r_in_tile) * N + n0) * 2;
+            uint8_t* dst_base = own ? reinterpret_cast<uint8_t*>(p.out) + (static_cast<uint64_t>(local_m0 + r_in_tile) * p.ldo + n0) * 2
+                                    : c.heap[dst] + part_off + ((static_cast<uint64_t>(c.rank) * Ml + local_m0 + r_in_tile) * N + n0) * 2;
             bulk_s2g(dst_base, srow, BN * 2);
             bulk_commit();
             // The flag of the PREVIOUS tile is raised now (its stores have had a whole tile time to complete); this
@@ -512,7 +583,7 @@ __global__ void __launch_bounds__(kRsThreads, 1) gemm_rs_kernel(const __grid_con
                 __syncwarp();
                 if (lane == 0) red_add_release_sys_u64(prev_flag, 1);
             }
-            prev_flag = reinterpret_cast<uint64_t*>(c.heap[dst] + flag_off) + static_cast<uint64_t>(c.rank) * tiles_per_dst + lt;
+            prev_flag = own ? nullptr : reinterpret_cast<uint64_t*>(c.heap[dst] + flag_off) + static_cast<uint64_t>(c.rank) * tiles_per_dst + lt;
             bulk_wait_read_all();
             __syncwarp();
         }
@@ -524,66 +595,13 @@ __global__ void __launch_bounds__(kRsThreads, 1) gemm_rs_kernel(const __grid_con
         }
     }
 
-    // ---------------------------------------------------------------- reduction of this rank's own tiles
+    // ---------------------------------------------------------------- tear-down
     tc_fence_before();
     if constexpr (kPair) cluster_sync_all(); else __syncthreads();
     if (warp == 1) {
         tc_fence_after();
         if constexpr (kPair) tmem_dealloc_pair(tmem_base, 2 * BN);
         else tmem_dealloc(tmem_base, 2 * BN);
-    }
-    const uint64_t* my_flags = reinterpret_cast<const uint64_t*>(c.heap[c.rank] + flag_off);
-    const uint8_t* my_part = c.heap[c.rank] + part_off;
-    const uint64_t target = static_cast<uint64_t>(p.flag_target);
-    for (int lt = bid; lt < tiles_per_dst; lt += nctas) {
-        if (threadIdx.x < R) {
-            const uint64_t* flag = my_flags + static_cast<uint64_t>(threadIdx.x) * tiles_per_dst + lt;
-            if (!bounded_wait(w, kStatusTileFlag, threadIdx.x, lt, [&]() { return ld_acquire_sys_u64(flag) >= target; }))
-                atomicExch(p.error, static_cast<int>(kStatusTileFlag));
-        }
-        __syncthreads();
-        const int local_m0 = (lt / tiles_n) * BM, n0 = (lt % tiles_n) * BN;
-        // Two 16-byte columns per thread and pass, all sources loaded before the first add: up to 16 loads in flight
-        // per thread, so the phase runs at memory speed instead of one load latency per source.
-        for (int v0 = threadIdx.x; v0 < BM * BN / 8; v0 += 2 * blockDim.x) {
-            int4 raw[2][kMaxRanks];
-#pragma unroll
-            for (int u = 0; u < 2; ++u) {
-                const int v = v0 + u * blockDim.x;
-                const int r = v / (BN / 8), cv = v % (BN / 8);
-#pragma unroll
-                for (int s = 0; s < kMaxRanks; ++s)
-                    if (s < R && v < BM * BN / 8)
-                        raw[u][s] = ld_nc_int4(my_part + ((static_cast<uint64_t>(s) * Ml + local_m0 + r) * N + n0 + cv * 8) * 2);
-            }
-#pragma unroll
-            for (int u = 0; u < 2; ++u) {
-                const int v = v0 + u * blockDim.x;
-                if (v >= BM * BN / 8) break;
-                const int r = v / (BN / 8), cv = v % (BN / 8);
-                float accv[8];
-#pragma unroll
-                for (int i = 0; i < 8; ++i) accv[i] = 0.f;
-#pragma unroll
-                for (int s = 0; s < kMaxRanks; ++s) {
-                    if (s < R) {
-                        const __nv_bfloat162* h2 = reinterpret_cast<const __nv_bfloat162*>(&raw[u][s]);
-#pragma unroll
-                        for (int i = 0; i < 4; ++i) {
-                            const float2 f = __bfloat1622float2(h2[i]);
-                            accv[2 * i] += f.x;
-                            accv[2 * i + 1] += f.y;
-                        }
-                    }
-                }
-                int4 out;
-                __nv_bfloat162* o2 = reinterpret_cast<__nv_bfloat162*>(&out);
-#pragma unroll
-                for (int i = 0; i < 4; ++i) o2[i] = __floats2bfloat162_rn(accv[2 * i], accv[2 * i + 1]);
-                *reinterpret_cast<int4*>(p.out + (static_cast<int64_t>(local_m0 + r) * p.ldo + n0 + cv * 8)) = out;
-            }
-        }
-        __syncthreads();
     }
 }
 

@@ -12,6 +12,7 @@
 #include "../kernels/aux_api.hpp"
 #include "host_segment.hpp"
 #include "runtime.hpp"
+#include "stream_tools.hpp"
 
 namespace py = pybind11;
 
@@ -31,40 +32,11 @@ struct FlagSpec {
     bool signal_first = false;
 };
 
-// ---- stream memory operations (0 SMs): the driver writes / waits for a 64-bit word in stream order
-// Parity: csrc/kernels/backend/cuda_driver.cu:12-52 of the reference (batched write / wait-GEQ of AGRS sessions).
-// Opt-in (EP_STREAM_MEMOPS=1): such a wait has no time limit, unlike the wait of the flag kernel, so a peer that
-// never signals blocks the stream until the process gives up; the default keeps every wait bounded.
-struct StreamMemOps {
-    using WriteFn = int (*)(cudaStream_t, unsigned long long, unsigned long long, unsigned int);
-    using WaitFn = int (*)(cudaStream_t, unsigned long long, unsigned long long, unsigned int);
-    WriteFn write = nullptr;
-    WaitFn wait = nullptr;
-    bool enabled = false;
-    StreamMemOps() {
-        const char* v = std::getenv("EP_STREAM_MEMOPS");
-        if (v == nullptr || v[0] != '1') return;
-        cudaDriverEntryPointQueryResult res;
-        void* w = nullptr;
-        void* q = nullptr;
-        if (cudaGetDriverEntryPoint("cuStreamWriteValue64", &w, cudaEnableDefault, &res) != cudaSuccess || res != cudaDriverEntryPointSuccess) return;
-        if (cudaGetDriverEntryPoint("cuStreamWaitValue64", &q, cudaEnableDefault, &res) != cudaSuccess || res != cudaDriverEntryPointSuccess) return;
-        write = reinterpret_cast<WriteFn>(w);
-        wait = reinterpret_cast<WaitFn>(q);
-        enabled = true;
-    }
-};
-
-StreamMemOps& stream_memops() {
-    static StreamMemOps ops;
-    return ops;
-}
-
-bool stream_memops_enabled() { return stream_memops().enabled; }
+bool stream_memops_enabled() { return stream_memops().available && stream_memops().waits; }
 
 void flag_op(const std::vector<std::shared_ptr<Runtime>>& rts, const std::vector<FlagSpec>& specs) {
     EP_HOST_ASSERT(!rts.empty() && rts.size() == specs.size() && rts.size() <= kMaxVRanks);
-    if (rts.size() == 1 && stream_memops().enabled) {
+    if (rts.size() == 1 && stream_memops_enabled()) {
         // one real rank per process: signal and wait as stream operations, no kernel, no SM
         auto& rt = *rts[0];
         const auto& s = specs[0];
@@ -121,30 +93,8 @@ void copy_to_heap(Runtime& rt, int peer, int64_t offset, const at::Tensor& src) 
     CUDA_RUNTIME_CHECK(cudaMemcpyAsync(rt.heap().peer(peer) + offset, src.data_ptr(), bytes, cudaMemcpyDeviceToDevice, cur_stream()));
 }
 
-// Several copy-engine transfers side by side: copy i runs on side stream i % kFanStreams, forked from and joined to
-// the current stream with events, so that copies to different peers use different copy engines instead of queueing
-// behind one another. One binding call for all of them (the host cost of a call is of the order of a small copy).
-struct FanOut {
-    static constexpr int kFanStreams = 7;
-    cudaStream_t streams[kFanStreams] = {};
-    cudaEvent_t fork = nullptr, join[kFanStreams] = {};
-    bool ready = false;
-    void init() {
-        if (ready) return;
-        for (auto& st : streams) CUDA_RUNTIME_CHECK(cudaStreamCreateWithFlags(&st, cudaStreamNonBlocking));
-        CUDA_RUNTIME_CHECK(cudaEventCreateWithFlags(&fork, cudaEventDisableTiming));
-        for (auto& ev : join) CUDA_RUNTIME_CHECK(cudaEventCreateWithFlags(&ev, cudaEventDisableTiming));
-        ready = true;
-    }
-};
-
-FanOut& fan_out(int device) {
-    static FanOut pools[64];
-    EP_HOST_ASSERT(device >= 0 && device < 64);
-    pools[device].init();
-    return pools[device];
-}
-
+// Several copy-engine transfers side by side (one side stream per copy, see FanOut). One binding call for all of them
+// (the host cost of a call is of the order of a small copy).
 void copy_fanout(Runtime& rt, const std::vector<std::tuple<int, int64_t, at::Tensor>>& copies) {
     if (copies.empty()) return;
     c10::cuda::CUDAGuard guard(static_cast<c10::DeviceIndex>(rt.heap().device()));
@@ -154,9 +104,8 @@ void copy_fanout(Runtime& rt, const std::vector<std::tuple<int, int64_t, at::Ten
         return;
     }
     FanOut& f = fan_out(rt.heap().device());
-    CUDA_RUNTIME_CHECK(cudaEventRecord(f.fork, stream));
     const int used = std::min<int>(FanOut::kFanStreams, static_cast<int>(copies.size()));
-    for (int i = 0; i < used; ++i) CUDA_RUNTIME_CHECK(cudaStreamWaitEvent(f.streams[i], f.fork, 0));
+    f.fork(stream, used);
     for (size_t i = 0; i < copies.size(); ++i) {
         const auto& [peer, offset, src] = copies[i];
         EP_HOST_ASSERT(src.is_cuda() && src.is_contiguous() && peer >= 0 && peer < rt.num_ranks());
@@ -166,10 +115,7 @@ void copy_fanout(Runtime& rt, const std::vector<std::tuple<int, int64_t, at::Ten
         CUDA_RUNTIME_CHECK(cudaMemcpyAsync(rt.heap().peer(peer) + offset, src.data_ptr(), bytes, cudaMemcpyDeviceToDevice,
                                            f.streams[i % FanOut::kFanStreams]));
     }
-    for (int i = 0; i < used; ++i) {
-        CUDA_RUNTIME_CHECK(cudaEventRecord(f.join[i], f.streams[i]));
-        CUDA_RUNTIME_CHECK(cudaStreamWaitEvent(stream, f.join[i], 0));
-    }
+    f.join(stream, used);
 }
 
 void copy_from_heap(Runtime& rt, int64_t offset, at::Tensor dst) {

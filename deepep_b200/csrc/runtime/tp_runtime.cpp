@@ -1,13 +1,16 @@
 // Host drivers of the fused tensor-parallel operators (all-gather -> GEMM, GEMM -> reduce-scatter).
 #include <ATen/cuda/CUDAContext.h>
 #include <cmath>
+#include <cstdlib>
 #include <ATen/ops/empty.h>
 #include <ATen/ops/zeros.h>
 #include <pybind11/stl.h>
 #include <torch/extension.h>
 
+#include "../kernels/aux_api.hpp"
 #include "../kernels/tp_api.hpp"
 #include "runtime.hpp"
+#include "stream_tools.hpp"
 
 namespace py = pybind11;
 
@@ -31,9 +34,14 @@ int tp_check_status() {
 
 // C_r[R * Ml, N] = gather(A)[R * Ml, K] * B_r[N, K]^T, one launch for all listed (virtual) ranks.
 // `gather_offsets` = the two halves of the gather buffer inside every heap (bytes from the heap base).
+// `push`: 0 = decide here, 1 = push CTAs inside the kernel (bulk stores from SMs), 2 = copy engines: the shard goes out
+// in groups of row chunks with one 2-D copy per peer and group on side streams, every chunk's arrival flag is a 64-bit
+// stream write behind its copy, and ALL SMs run GEMM tiles, whose loader waits for those flags exactly as it waits for
+// the flags of the push CTAs. The entry handshake (a peer's gather half may only be overwritten once that peer has
+// entered this call) then runs as a one-block flag kernel ahead of the GEMM.
 std::vector<at::Tensor> tp_ag_gemm(const std::vector<std::shared_ptr<Runtime>>& rts, const std::vector<at::Tensor>& a_local,
                                    const std::vector<at::Tensor>& b, const std::vector<int64_t>& gather_offsets, int num_comm_ctas,
-                                   int num_sms) {
+                                   int num_sms, int push) {
     const int V = static_cast<int>(rts.size());
     EP_HOST_ASSERT(V >= 1 && V <= gemm::kTpMaxVRanks && static_cast<int>(a_local.size()) == V && static_cast<int>(b.size()) == V);
     EP_HOST_ASSERT(gather_offsets.size() == 2);
@@ -44,13 +52,21 @@ std::vector<at::Tensor> tp_ag_gemm(const std::vector<std::shared_ptr<Runtime>>& 
     const int Ml = static_cast<int>(a_local[0].size(0)), K = static_cast<int>(a_local[0].size(1)), N = static_cast<int>(b[0].size(0));
     const uint64_t half_bytes = static_cast<uint64_t>(R) * Ml * K * 2;
     if (num_sms <= 0) num_sms = rt0.num_device_sms() / V;
-    if (num_comm_ctas <= 0 && R > 1) {
+    // Copy engines need one real rank per process (the kernels of emulated ranks share one GPU and one stream), the
+    // driver's stream writes, and at most 63 row chunks per source (flag word 63 is the entry word).
+    const bool ce_possible = V == 1 && R > 1 && stream_memops().available && Ml % 128 == 0 && Ml / 128 <= 63;
+    static const int env_push = [] { const char* v = std::getenv("EP_TP_PUSH"); return v == nullptr ? 0 : (v[0] == 's' ? 1 : (v[0] == 'c' ? 2 : 0)); }();
+    if (push == 0) push = env_push;
+    if (push == 0) push = 2;
+    const bool use_ce = push == 2 && ce_possible;
+    if (use_ce) num_comm_ctas = 0;
+    if (num_comm_ctas <= 0 && R > 1 && !use_ce) {
         // As few push CTAs as move the shard out within about half of the GEMM's time (every CTA taken from the GEMM
         // costs it 1 / #SMs of its rate): a push CTA was measured at about 40 GB/s, the GEMM at about 1.4 PFLOP/s.
         const double push_cta_seconds = static_cast<double>(R - 1) * Ml * K * 2 / 40e9;
         const double gemm_seconds = 2.0 * R * Ml * N * K / 1.4e15;
         int n = static_cast<int>(std::ceil(push_cta_seconds / (0.5 * gemm_seconds)));
-        n = (std::max(2, std::min(n, 32)) + 1) & ~1;
+        n = (std::max(8, std::min(n, 32)) + 1) & ~1;     // (four push CTAs were measured far slower than eight at TP2)
         num_comm_ctas = std::min(n, std::max(2, (num_sms / 4) & ~1));
     }
     if (R == 1) num_comm_ctas = 0;
@@ -83,7 +99,51 @@ std::vector<at::Tensor> tp_ag_gemm(const std::vector<std::shared_ptr<Runtime>>& 
         bptr[v] = b[v].data_ptr();
         gptr[v] = rt.heap().base() + off;
     }
-    CUDA_RUNTIME_CHECK(gemm::launch_ag_gemm(params.data(), bptr.data(), gptr.data(), V, num_sms, at::cuda::getCurrentCUDAStream().stream()));
+    const cudaStream_t stream = at::cuda::getCurrentCUDAStream().stream();
+    if (!use_ce) {
+        CUDA_RUNTIME_CHECK(gemm::launch_ag_gemm(params.data(), bptr.data(), gptr.data(), V, num_sms, stream));
+        return outs;
+    }
+    auto& rt = rt0;
+    const gemm::AgGemmParams& p = params[0];
+    const int me = rt.rank();
+    // entry handshake, in stream order ahead of everything else of this call
+    aux::FlagOp op{};
+    op.c = rt.ctx();
+    op.status_code = kStatusTileFlag;
+    op.signal_first = 1;
+    op.signal_value = op.wait_value = static_cast<uint64_t>(p.epoch) << 32;
+    for (int r = 0; r < R; ++r) {
+        if (r == me) continue;
+        op.signal_ptrs[op.num_signal++] = reinterpret_cast<uint64_t*>(rt.heap().peer(r)) + kCtlTileFlags + me * 64 + 63;
+        op.wait_ptrs[op.num_wait++] = reinterpret_cast<const uint64_t*>(rt.heap().base()) + kCtlTileFlags + r * 64 + 63;
+    }
+    CUDA_RUNTIME_CHECK(aux::launch_flag_op(&op, 1, stream));
+    FanOut& f = fan_out(device);
+    const int used = std::min<int>(FanOut::kFanStreams, R - 1);
+    f.fork(stream, used);
+    // the GEMM starts on the local chunks while the copies are queued
+    CUDA_RUNTIME_CHECK(gemm::launch_ag_gemm(params.data(), bptr.data(), gptr.data(), V, num_sms, stream));
+    const int chunks = Ml / 128;
+    const int group = std::max(1, chunks / 8);           // row chunks per copy: about eight copies per peer
+    const size_t row_bytes = static_cast<size_t>(K) * 2;
+    const uint64_t arrived = (static_cast<uint64_t>(p.epoch) << 32) | 1u;
+    for (int c0 = 0; c0 < chunks; c0 += group) {
+        const int c1 = std::min(chunks, c0 + group);
+        for (int i = 0; i < R - 1; ++i) {
+            const int peer = (me + 1 + i) % R;
+            const cudaStream_t side = f.streams[i % FanOut::kFanStreams];
+            uint8_t* dst = rt.heap().peer(peer) + p.off_gather + (static_cast<uint64_t>(me) * Ml + static_cast<uint64_t>(c0) * 128) * row_bytes;
+            const uint8_t* src = p.a_local + static_cast<int64_t>(c0) * 128 * p.a_stride_bytes;
+            CUDA_RUNTIME_CHECK(cudaMemcpy2DAsync(dst, row_bytes, src, static_cast<size_t>(p.a_stride_bytes), row_bytes,
+                                                 static_cast<size_t>(c1 - c0) * 128, cudaMemcpyDeviceToDevice, side));
+            for (int c = c0; c < c1; ++c) {
+                uint64_t* flag = reinterpret_cast<uint64_t*>(rt.heap().peer(peer)) + kCtlTileFlags + me * 64 + c;
+                EP_HOST_ASSERT(stream_memops().write(side, reinterpret_cast<unsigned long long>(flag), arrived, 0) == 0);
+            }
+        }
+    }
+    f.join(stream, used);
     return outs;
 }
 
@@ -149,7 +209,7 @@ std::vector<at::Tensor> tp_gemm_rs(const std::vector<std::shared_ptr<Runtime>>& 
 
 void register_tp_bindings(py::module_& m) {
     m.def("tp_ag_gemm", &tp_ag_gemm, py::arg("runtimes"), py::arg("a_local"), py::arg("b"), py::arg("gather_offsets"),
-          py::arg("num_comm_ctas") = 0, py::arg("num_sms") = 0);
+          py::arg("num_comm_ctas") = 0, py::arg("num_sms") = 0, py::arg("push") = 0);
     m.def("tp_gemm_rs", &tp_gemm_rs, py::arg("runtimes"), py::arg("a"), py::arg("b"), py::arg("partial_offsets"), py::arg("flag_offsets"),
           py::arg("num_sms") = 0);
     m.def("tp_check_status", &tp_check_status);

@@ -69,10 +69,15 @@ def main() -> None:
         print(f'world {world}, tokens {M}, hidden {H}, ffn {F}; pairs {os.environ.get("EP_TP_CTA_PAIR", "0")}: '
               f'rel err ag_gemm {err1:.2e} gemm_rs {err2:.2e}', flush=True)
     flops = 2 * M * Fl * H
+    err_ce = rel(ctx.all_gather_gemm(x_shard, w1, push='ce'), nccl_all_gather_gemm(x_shard, w1, group))
+    t = timeit(lambda: ctx.all_gather_gemm(x_shard, w1, push='ce'))
+    if rank == 0:
+        print(f'ag_gemm fused, shard pushed by the copy engines (all SMs on the GEMM): {t * 1e3:.1f} us  {flops / t / 1e9:.0f} TFLOP/s per GPU, '
+              f'rel err {err_ce:.2e}', flush=True)
     for comm in [int(v) for v in a.comm_ctas.split(',')]:
-        t = timeit(lambda: ctx.all_gather_gemm(x_shard, w1, num_comm_ctas=comm))
+        t = timeit(lambda: ctx.all_gather_gemm(x_shard, w1, num_comm_ctas=comm, push='sm'))
         if rank == 0:
-            print(f'ag_gemm fused, {comm} comm CTAs: {t * 1e3:.1f} us  {flops / t / 1e9:.0f} TFLOP/s per GPU', flush=True)
+            print(f'ag_gemm fused, {comm} push CTAs inside the kernel: {t * 1e3:.1f} us  {flops / t / 1e9:.0f} TFLOP/s per GPU', flush=True)
     tb = timeit(lambda: nccl_all_gather_gemm(x_shard, w1, group))
     gathered = torch.empty((M, H), device=dev, dtype=torch.bfloat16)
     tg = timeit(lambda: torch.matmul(gathered, w1.t()))

@@ -58,8 +58,13 @@ class TensorParallelContext:
                                     explicitly_destroy=True)
         self.runtime = self.buffer.runtime
 
-    def all_gather_gemm(self, x_shard: torch.Tensor, w_shard: torch.Tensor, num_comm_ctas: int = 0, num_sms: int = 0) -> torch.Tensor:
-        return _C.tp_ag_gemm([self.runtime], [x_shard], [w_shard], self.gather_offsets, num_comm_ctas, num_sms)[0]
+    def all_gather_gemm(self, x_shard: torch.Tensor, w_shard: torch.Tensor, num_comm_ctas: int = 0, num_sms: int = 0,
+                        push: str = 'auto') -> torch.Tensor:
+        """``push``: how the shard reaches the peers while the GEMM runs. ``'sm'``: push CTAs inside the kernel (bulk
+        stores); ``'ce'``: copy engines on side streams with a stream-ordered flag write per row chunk, all SMs stay
+        with the GEMM; ``'auto'`` (also ``EP_TP_PUSH=sm|ce``): copy engines where the driver offers stream writes."""
+        mode = {'auto': 0, 'sm': 1, 'ce': 2}[push]
+        return _C.tp_ag_gemm([self.runtime], [x_shard], [w_shard], self.gather_offsets, num_comm_ctas, num_sms, mode)[0]
 
     def gemm_reduce_scatter(self, x: torch.Tensor, w_shard: torch.Tensor, num_sms: int = 0) -> torch.Tensor:
         return _C.tp_gemm_rs([self.runtime], [x], [w_shard], self.partial_offsets, self.flag_offsets, num_sms)[0]

@@ -165,10 +165,12 @@ def _subsystems_worker(rank: int, world: int, port: int):
     from deepep_b200.parallel.tp_fused import TensorParallelContext, nccl_all_gather_gemm, nccl_gemm_reduce_scatter
     ctx = TensorParallelContext(group, 256, 512, 512, num_gpu_timeout_secs=10)
     gc = torch.Generator(device='cuda').manual_seed(rank)
-    for it in range(3):
+    for it in range(4):
         xs = torch.randn((256, 512), device=dev, generator=gc).bfloat16()
         w1 = (torch.randn((512, 512), device=dev, generator=gc) * 0.05).bfloat16()
-        a = ctx.all_gather_gemm(xs, w1, num_comm_ctas=2, num_sms=24)
+        # the shard is pushed by CTAs of the kernel on even iterations and by the copy engines on odd ones: both use the
+        # same gather halves and flag words, so they must also work interleaved
+        a = ctx.all_gather_gemm(xs, w1, num_comm_ctas=2, num_sms=24, push='sm' if it % 2 == 0 else 'ce')
         b = nccl_all_gather_gemm(xs, w1, group)
         assert ((a.float() - b.float()).norm() / b.float().norm()).item() < 1e-2
         x2 = torch.randn((world * 256, 256), device=dev, generator=gc).bfloat16()
