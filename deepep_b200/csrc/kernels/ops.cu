@@ -235,19 +235,50 @@ __global__ void __launch_bounds__(256) swiglu_bwd_kernel(const uint8_t* __restri
     }
 }
 
-// ---------------------------------------------------------------- bf16 transpose [rows, cols] -> [cols, rows] (64 x 64 tiles through shared memory)
+// ---------------------------------------------------------------- bf16 transpose [rows, cols] -> [cols, rows], 64 x 64 tiles
+// Interior tiles of aligned tensors move 16 bytes per thread on both sides: a thread loads eight columns of two
+// consecutive rows, pairs them up column by column (one 32-bit word = the same column of both rows) and stores the
+// words transposed into shared memory (pitch 33 words); the write side reads four words = eight rows of one column
+// and stores them as one 16-byte vector. Edge tiles and unaligned tensors take the element-wise path.
 __global__ void __launch_bounds__(256) transpose_kernel(const __nv_bfloat16* __restrict__ in, int64_t in_stride, int rows, int cols,
-                                                        __nv_bfloat16* __restrict__ out, int64_t out_stride) {
-    __shared__ __nv_bfloat16 tile[64][66];
+                                                        __nv_bfloat16* __restrict__ out, int64_t out_stride, int aligned) {
+    __shared__ uint32_t tile_t[64 * 33];      // [column][row pair]
     const int r0 = blockIdx.y * 64, c0 = blockIdx.x * 64;
+    if (aligned && r0 + 64 <= rows && c0 + 64 <= cols) {
+        const int rp = threadIdx.x >> 3, cv = threadIdx.x & 7;
+        const int4 a = ld_nc_int4(reinterpret_cast<const uint8_t*>(in + (r0 + 2 * rp) * in_stride + c0 + cv * 8));
+        const int4 b = ld_nc_int4(reinterpret_cast<const uint8_t*>(in + (r0 + 2 * rp + 1) * in_stride + c0 + cv * 8));
+        const uint32_t aw[4] = {static_cast<uint32_t>(a.x), static_cast<uint32_t>(a.y), static_cast<uint32_t>(a.z), static_cast<uint32_t>(a.w)};
+        const uint32_t bw[4] = {static_cast<uint32_t>(b.x), static_cast<uint32_t>(b.y), static_cast<uint32_t>(b.z), static_cast<uint32_t>(b.w)};
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            // columns 2j and 2j + 1 of this thread's eight: low halves of both rows, then high halves
+            tile_t[(cv * 8 + 2 * j) * 33 + rp] = __byte_perm(aw[j], bw[j], 0x5410);
+            tile_t[(cv * 8 + 2 * j + 1) * 33 + rp] = __byte_perm(aw[j], bw[j], 0x7632);
+        }
+        __syncthreads();
+#pragma unroll
+        for (int u = 0; u < 2; ++u) {
+            const int i = threadIdx.x + u * 256;
+            const int c = i >> 3, rv = i & 7;
+            int4 v;
+            v.x = static_cast<int>(tile_t[c * 33 + 4 * rv]);
+            v.y = static_cast<int>(tile_t[c * 33 + 4 * rv + 1]);
+            v.z = static_cast<int>(tile_t[c * 33 + 4 * rv + 2]);
+            v.w = static_cast<int>(tile_t[c * 33 + 4 * rv + 3]);
+            st_na_int4(reinterpret_cast<uint8_t*>(out + (c0 + c) * out_stride + r0 + rv * 8), v);
+        }
+        return;
+    }
+    __nv_bfloat16* tile = reinterpret_cast<__nv_bfloat16*>(tile_t);     // [64][66]
     for (int i = threadIdx.x; i < 64 * 64; i += 256) {
         const int r = i / 64, c = i % 64;
-        tile[r][c] = (r0 + r < rows && c0 + c < cols) ? in[(r0 + r) * in_stride + c0 + c] : __float2bfloat16(0.f);
+        tile[r * 66 + c] = (r0 + r < rows && c0 + c < cols) ? in[(r0 + r) * in_stride + c0 + c] : __float2bfloat16(0.f);
     }
     __syncthreads();
     for (int i = threadIdx.x; i < 64 * 64; i += 256) {
         const int c = i / 64, r = i % 64;
-        if (c0 + c < cols && r0 + r < rows) out[(c0 + c) * out_stride + r0 + r] = tile[r][c];
+        if (c0 + c < cols && r0 + r < rows) out[(c0 + c) * out_stride + r0 + r] = tile[r * 66 + c];
     }
 }
 
@@ -317,8 +348,10 @@ cudaError_t swiglu_backward(const void* x, const void* dout, int rows, int inter
 cudaError_t transpose_bf16(const void* in, int64_t in_stride, int rows, int cols, void* out, int64_t out_stride, cudaStream_t stream) {
     if (rows == 0 || cols == 0) return cudaSuccess;
     dim3 grid((cols + 63) / 64, (rows + 63) / 64);
+    const int aligned = in_stride % 8 == 0 && out_stride % 8 == 0 && reinterpret_cast<uintptr_t>(in) % 16 == 0 &&
+                        reinterpret_cast<uintptr_t>(out) % 16 == 0;
     transpose_kernel<<<grid, 256, 0, stream>>>(static_cast<const __nv_bfloat16*>(in), in_stride, rows, cols,
-                                               static_cast<__nv_bfloat16*>(out), out_stride);
+                                               static_cast<__nv_bfloat16*>(out), out_stride, aligned);
     return cudaGetLastError();
 }
 

@@ -80,3 +80,16 @@ def test_ops_package_wrappers():
     assert torch.allclose(y.float(), ops.ref_swiglu(x), rtol=2e-2, atol=2e-2)
     assert torch.equal(ops.transpose(x), x.t().contiguous())
     assert torch.equal(ops.dequant_1x128(xq, sfa), (xq.float() * sfa.repeat_interleave(128, dim=1)).bfloat16())
+
+
+@pytest.mark.parametrize('rows,cols', [(64, 64), (200, 328), (130, 72), (1, 7), (512, 4096)])
+def test_transpose_interior_edge_and_unaligned(rows, cols):
+    """Interior tiles of aligned tensors take the 16-byte path, edge tiles and unaligned views the element-wise one."""
+    import deepep_b200
+    C = deepep_b200._C
+    g = torch.Generator(device='cuda').manual_seed(rows * 1000 + cols)
+    x = torch.randn((rows, cols), device='cuda', generator=g).bfloat16()
+    assert torch.equal(C.transpose_bf16(x), x.t().contiguous())
+    if cols > 8:     # a view whose rows start 2 bytes off a 16-byte boundary
+        v = x[:, 1:]
+        assert torch.equal(C.transpose_bf16(v), v.t().contiguous())
