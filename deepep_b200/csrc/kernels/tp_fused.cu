@@ -503,6 +503,15 @@ __global__ void __launch_bounds__(kRsThreads, 1) gemm_rs_kernel(const __grid_con
             const int local_m0 = (lt / tiles_n) * BM, n0 = (lt % tiles_n) * BN;
             const bool own = dst == c.rank;
             if (own) {
+                // Nothing of this rank may still be owed to a peer while it waits for the peers: the arrival of the
+                // previous tile, normally raised one tile late, goes out first (two ranks that each held back the
+                // tile the other one is waiting for would wait for each other).
+                if (prev_flag != nullptr) {
+                    bulk_wait_all();
+                    __syncwarp();
+                    if (lane == 0) red_add_release_sys_u64(prev_flag, 1);
+                    prev_flag = nullptr;
+                }
                 bool arrived = true;
                 if (lane < R && lane != c.rank) {
                     const uint64_t* flag = my_flags + static_cast<uint64_t>(lane) * tiles_per_dst + lt;
