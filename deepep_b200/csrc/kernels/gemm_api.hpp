@@ -28,6 +28,7 @@ struct GemmParams {
     const float* sfa;            // A scales, element (row, kblock) at sfa[row * sfa_row_stride + kblock * sfa_k_stride]
     int64_t sfa_row_stride, sfa_k_stride;
     const float* sfb;            // [num_groups][N / 128][K / 128]
+    int scales_pow2;             // every scale is an exact power of two: the block-scaled tensor-core instruction may apply them
     int* error;                  // device int, set to a StatusCode when a pipeline wait runs out
     uint64_t timeout_ns;
 };

@@ -637,6 +637,226 @@ gemm_pair_fp8_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_con
 }
 
 // ---------------------------------------------------------------- host side
+// ==================================================================== e4m3 with hardware block scaling (128 x 256 tiles)
+// For scales that are exact powers of two the tensor core applies them itself (tcgen05.mma kind::mxf8f6f4.block_scale,
+// UE8M0 scale factors in tensor memory), so a tile accumulates over ALL of K in tensor memory and the epilogue runs once
+// per tile instead of once per k-block. Roles: TMA producer, MMA issuer, eight epilogue warps (two per lane quarter, 128
+// columns each), four scale warps (one per lane quarter). Per k-block of 128 a scale warp writes the slot of that
+// pipeline stage in tensor memory: 4 columns for the rows of A (1x128 scales: all four 32-wide slices share the byte)
+// and 8 columns for the 256 columns of B (128x128 scales: two bytes per k-block, replicated); `full[s]` collects the
+// producer's bytes and the four scale warps, `empty[s]` (an MMA commit) frees both the shared-memory stage and its
+// scale slot. The scale bytes of a tile are staged in shared memory one tile ahead, so the feed never waits for memory.
+// The accumulator (256 columns) is single-buffered: tensor memory has 512 columns and the scale slots need their own.
+struct MxCfg {
+    static constexpr int BN = 256, BK = 128, UMMA_K = 32;
+    static constexpr int kEpiWarps = 8, kSfWarps = 4;
+    static constexpr int kThreads = (2 + kEpiWarps + kSfWarps) * 32;
+    static constexpr int A_BYTES = BM * 128, B_BYTES = BN * 128, STAGE = A_BYTES + B_BYTES;
+    static constexpr int kStages = 4;
+    static constexpr int kSfCols = 16;                 // columns per scale slot: 4 (A) + 8 (B), padded to a store of 16
+    static constexpr int kSfBase = BN;                 // first scale column behind the accumulator
+    static constexpr int kTmemCols = 512;
+    static constexpr int kMaxKb = 64;                  // k-blocks whose scale bytes fit the staging area (K <= 8192)
+    static constexpr int kSfPitch = BM + 16;           // per k-block: 128 bytes for the rows of A, 2 for B
+    static constexpr int kSfStage = kMaxKb * kSfPitch;
+    static constexpr int kBarBytes = (2 * kStages + 2) * 8 + 16;
+    static constexpr int kSmem = kStages * STAGE + 2 * kSfStage + kBarBytes + 1024;
+};
+
+__device__ __forceinline__ uint32_t ue8m0_of(float scale) { return (__float_as_uint(scale) >> 23) & 0xffu; }
+
+__global__ void __launch_bounds__(MxCfg::kThreads, 1)
+gemm_mx_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b, const GemmParams p) {
+    using C = MxCfg;
+    extern __shared__ uint8_t smem_raw[];
+    uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~static_cast<uintptr_t>(1023));
+    uint8_t* sf_stage = smem + C::kStages * C::STAGE;                       // [2][kMaxKb][kSfPitch]
+    uint64_t* full = reinterpret_cast<uint64_t*>(sf_stage + 2 * C::kSfStage);
+    uint64_t* empty = full + C::kStages;
+    uint64_t* tmem_full = empty + C::kStages;
+    uint64_t* tmem_empty = tmem_full + 1;
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(tmem_empty + 1);
+
+    const int warp = warp_id(), lane = lane_id();
+    PipeCtx pc{p.error, globaltimer_ns() + p.timeout_ns};
+
+    if (warp == 0 && lane == 0) {
+        prefetch_tensormap(&map_a);
+        prefetch_tensormap(&map_b);
+        for (int s = 0; s < C::kStages; ++s) {
+            mbar_init(full + s, 1 + C::kSfWarps);      // the producer's arrival (+ bytes) and one arrival per scale warp
+            mbar_init(empty + s, 1);
+        }
+        mbar_init(tmem_full, 1);
+        mbar_init(tmem_empty, C::kEpiWarps);
+        fence_mbar_init();
+    }
+    if (warp == 1) {
+        tmem_alloc(tmem_slot, C::kTmemCols);
+        tmem_relinquish();
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem_base = *tmem_slot;
+
+    if (warp == 0) {
+        // ------------------------------------------------------------ TMA producer
+        if (lane == 0) {
+            Scheduler sched(p, C::BN, BM, C::BK);
+            Tile t;
+            int s = 0;
+            uint32_t ph = 0;
+            bool ok = true;
+            for (int ti = blockIdx.x; ok && sched.get(ti, t); ti += gridDim.x) {
+                const int b_row = t.g * p.N + t.n0;
+                for (int kb = t.kb0; kb < t.kb1; ++kb) {
+                    if (!(ok = pipe_wait(pc, empty + s, ph ^ 1))) break;
+                    uint8_t* sa = smem + s * C::STAGE;
+                    mbar_arrive_expect_tx(full + s, C::STAGE);
+                    tma_load_2d(sa, &map_a, kb * C::BK, t.m0, full + s);
+                    tma_load_2d(sa + C::A_BYTES, &map_b, kb * C::BK, b_row, full + s);
+                    if (++s == C::kStages) { s = 0; ph ^= 1; }
+                }
+            }
+        }
+    } else if (warp == 1) {
+        // ------------------------------------------------------------ MMA issuer
+        if (lane == 0) {
+            Scheduler sched(p, C::BN, BM, C::BK);
+            Tile t;
+            int s = 0;
+            uint32_t ph = 0, acc_ph = 0;
+            bool ok = true;
+            for (int ti = blockIdx.x; ok && sched.get(ti, t); ti += gridDim.x) {
+                if (!(ok = pipe_wait(pc, tmem_empty, acc_ph ^ 1))) break;
+                tc_fence_after();
+                for (int kb = t.kb0; kb < t.kb1; ++kb) {
+                    if (!(ok = pipe_wait(pc, full + s, ph))) break;
+                    tc_fence_after();
+                    const uint8_t* sa = smem + s * C::STAGE;
+                    const uint64_t da = make_smem_desc(sa), db = make_smem_desc(sa + C::A_BYTES);
+                    const uint32_t sfa = tmem_base + C::kSfBase + s * C::kSfCols, sfb = sfa + 4;
+#pragma unroll
+                    for (int k = 0; k < C::BK / C::UMMA_K; ++k)
+                        umma_mx(tmem_base, da + 2 * k, db + 2 * k, make_idesc_mx(BM, C::BN, static_cast<uint32_t>(k)),
+                                (kb != t.kb0 || k != 0) ? 1u : 0u, sfa, sfb);
+                    umma_commit(empty + s);
+                    if (++s == C::kStages) { s = 0; ph ^= 1; }
+                }
+                if (!ok) break;
+                umma_commit(tmem_full);
+                acc_ph ^= 1;
+            }
+        }
+    } else if (warp < 2 + C::kEpiWarps) {
+        // ------------------------------------------------------------ epilogue warps: once per tile
+        const int quarter = warp & 3;
+        const int half = (warp - 2) / 4;               // which 128 of the 256 columns
+        Scheduler sched(p, C::BN, BM, C::BK);
+        Tile t;
+        uint32_t acc_ph = 0;
+        bool ok = true;
+        for (int ti = blockIdx.x; ok && sched.get(ti, t); ti += gridDim.x) {
+            const int row = t.m0 + quarter * 32 + lane;
+            const bool row_ok = row < t.m_end && row < p.M;
+            const bool zero_row = !row_ok && p.zero_gap && row < p.M;
+            const uint32_t lane_addr = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + half * 128;
+            __nv_bfloat16* c_row = p.C + static_cast<int64_t>(row) * p.ldc + t.n0 + half * 128;
+            if (!(ok = pipe_wait(pc, tmem_full, acc_ph))) break;
+            tc_fence_after();
+#pragma unroll 1
+            for (int c = 0; c < 4; ++c) {
+                uint32_t r[32];
+                tmem_ld_32x32(lane_addr + c * 32, r);
+                tmem_ld_wait();
+                if (row_ok) {
+#pragma unroll
+                    for (int v = 0; v < 4; ++v) {
+                        int4 out;
+                        __nv_bfloat162* o2 = reinterpret_cast<__nv_bfloat162*>(&out);
+#pragma unroll
+                        for (int i = 0; i < 4; ++i)
+                            o2[i] = __floats2bfloat162_rn(__uint_as_float(r[v * 8 + 2 * i]), __uint_as_float(r[v * 8 + 2 * i + 1]));
+                        *reinterpret_cast<int4*>(c_row + c * 32 + v * 8) = out;
+                    }
+                } else if (zero_row) {
+#pragma unroll
+                    for (int v = 0; v < 4; ++v) *reinterpret_cast<int4*>(c_row + c * 32 + v * 8) = make_int4(0, 0, 0, 0);
+                }
+            }
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(tmem_empty);
+            acc_ph ^= 1;
+        }
+    } else {
+        // ------------------------------------------------------------ scale warps
+        const int quarter = warp & 3;
+        const int sf_tid = (warp - 2 - C::kEpiWarps) * 32 + lane;      // 0..127 = the row of the tile this thread stages
+        const int kblocks = p.K / 128;
+        Scheduler sched(p, C::BN, BM, C::BK);
+        Tile t, nxt;
+        auto stage_tile = [&](const Tile& tt, uint8_t* dst) {
+            const int row = tt.m0 + sf_tid;
+            const bool valid = row < tt.m_end && row < p.M;
+            const float* src = p.sfa + static_cast<int64_t>(valid ? row : 0) * p.sfa_row_stride;
+            for (int kb = tt.kb0; kb < tt.kb1; ++kb)
+                dst[(kb - tt.kb0) * C::kSfPitch + sf_tid] = static_cast<uint8_t>(valid ? ue8m0_of(src[static_cast<int64_t>(kb) * p.sfa_k_stride]) : 127u);
+            const float* srcb = p.sfb + (static_cast<int64_t>(tt.g) * (p.N / 128) + tt.n0 / 128) * kblocks;
+            for (int i = sf_tid; i < 2 * (tt.kb1 - tt.kb0); i += C::kSfWarps * 32) {
+                const int h = i & 1, kb = tt.kb0 + (i >> 1);
+                dst[(kb - tt.kb0) * C::kSfPitch + BM + h] = static_cast<uint8_t>(ue8m0_of(srcb[static_cast<int64_t>(h) * kblocks + kb]));
+            }
+        };
+        auto sf_barrier = [&]() { asm volatile("bar.sync 3, %0;" ::"r"(C::kSfWarps * 32) : "memory"); };
+        int s = 0, buf = 0;
+        uint32_t ph = 0;
+        bool ok = true;
+        bool have = sched.get(blockIdx.x, t);
+        if (have) stage_tile(t, sf_stage);
+        sf_barrier();
+        for (int ti = blockIdx.x; ok && have; ti += gridDim.x) {
+            const bool have_next = sched.get(ti + gridDim.x, nxt);
+            if (have_next) stage_tile(nxt, sf_stage + (buf ^ 1) * C::kSfStage);      // one tile ahead
+            const uint8_t* mine = sf_stage + buf * C::kSfStage;
+            for (int kb = t.kb0; kb < t.kb1; ++kb) {
+                if (!(ok = pipe_wait(pc, empty + s, ph ^ 1))) break;
+                tc_fence_after();
+                const uint8_t* src = mine + (kb - t.kb0) * C::kSfPitch;
+                uint32_t v[16];
+#pragma unroll
+                for (int j = 0; j < 4; ++j) v[j] = static_cast<uint32_t>(src[lane + 32 * j]) * 0x01010101u;
+#pragma unroll
+                for (int h = 0; h < 2; ++h) {
+                    const uint32_t b = static_cast<uint32_t>(src[BM + h]) * 0x01010101u;
+#pragma unroll
+                    for (int j = 0; j < 4; ++j) v[4 + 4 * h + j] = b;
+                }
+#pragma unroll
+                for (int j = 12; j < 16; ++j) v[j] = 0u;
+                tmem_st_32x16(tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + C::kSfBase + s * C::kSfCols, v);
+                tmem_st_wait();
+                tc_fence_before();
+                __syncwarp();
+                if (lane == 0) mbar_arrive(full + s);
+                if (++s == C::kStages) { s = 0; ph ^= 1; }
+            }
+            sf_barrier();       // the next tile's bytes are complete; nobody reads this tile's any more
+            buf ^= 1;
+            t = nxt;
+            have = have_next;
+        }
+    }
+
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 1) {
+        tc_fence_after();
+        tmem_dealloc(tmem_base, C::kTmemCols);
+    }
+}
+
 using EncodeFn = CUresult (*)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
                               const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
                               CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
@@ -700,6 +920,18 @@ cudaError_t launch_gemm(const GemmParams& p, const void* a, int64_t a_row_stride
         !make_kmajor_map(&map_b, b, elem, static_cast<uint64_t>(p.num_groups) * p.N, static_cast<uint64_t>(p.K),
                          static_cast<uint64_t>(b_row_stride_bytes), static_cast<uint32_t>(use_pair ? bn / 2 : bn)))
         return cudaErrorInvalidValue;
+    // e4m3 with power-of-two scales: the block-scaled instruction kind (EP_GEMM_FP8_MX=0 keeps the software scaling)
+    static const bool mx_enabled = [] { const char* v = std::getenv("EP_GEMM_FP8_MX"); return v == nullptr || v[0] != '0'; }();
+    if (fp8 && p.scales_pow2 && mx_enabled && !use_pair && p.N % 256 == 0 && p.K / 128 <= MxCfg::kMaxKb && !p.k_grouped) {
+        CUtensorMap map_b256;
+        if (!make_kmajor_map(&map_b256, b, elem, static_cast<uint64_t>(p.num_groups) * p.N, static_cast<uint64_t>(p.K),
+                             static_cast<uint64_t>(b_row_stride_bytes), 256))
+            return cudaErrorInvalidValue;
+        cudaError_t err = cudaFuncSetAttribute(gemm_mx_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, MxCfg::kSmem);
+        if (err != cudaSuccess) return err;
+        gemm_mx_kernel<<<num_sms, MxCfg::kThreads, MxCfg::kSmem, stream>>>(map_a, map_b256, p);
+        return cudaGetLastError();
+    }
     if (fp8 && use_pair) {
         cudaError_t err = cudaFuncSetAttribute(gemm_pair_fp8_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, PairFp8Cfg::kSmem);
         if (err != cudaSuccess) return err;

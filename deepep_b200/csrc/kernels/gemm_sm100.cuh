@@ -117,6 +117,41 @@ __device__ __forceinline__ void tmem_ld_32x16(uint32_t taddr, uint32_t (&r)[16])
         : "r"(taddr) : "memory");
 }
 __device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
+// 16 consecutive 32-bit columns of this thread's tensor-memory lane (lane = 32 * (warp % 4) + lane id)
+__device__ __forceinline__ void tmem_st_32x16(uint32_t taddr, const uint32_t (&r)[16]) {
+    asm volatile(
+        "tcgen05.st.sync.aligned.32x32b.x16.b32 [%0], "
+        "{%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16};"
+        ::"r"(taddr), "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]), "r"(r[8]),
+          "r"(r[9]), "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15]) : "memory");
+}
+__device__ __forceinline__ void tmem_st_wait() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
+
+// D[tmem] (+)= (A[smem] * 2^(sfa - 127)) * (B[smem] * 2^(sfb - 127)): e4m3 operands with one UE8M0 scale factor per row
+// (column) and 32 elements of K, read from tensor memory by the tensor core itself. The scale factors of the 128 rows of
+// A occupy four 32-bit columns: in every lane quarter, lane r holds in column j the factors of row r + 32 j, one byte
+// per 32-wide slice of a 128-wide k-block (the byte is picked by the id fields of the instruction descriptor); those of
+// 256 columns of B occupy eight columns in the same arrangement.
+__device__ __forceinline__ void umma_mx(uint32_t tmem_d, uint64_t desc_a, uint64_t desc_b, uint32_t idesc, uint32_t accumulate,
+                                        uint32_t tmem_sfa, uint32_t tmem_sfb) {
+    asm volatile(
+        "{\n"
+        ".reg .pred p;\n"
+        "setp.ne.b32 p, %4, 0;\n"
+        "tcgen05.mma.cta_group::1.kind::mxf8f6f4.block_scale [%0], %1, %2, %3, [%5], [%6], p;\n"
+        "}\n" ::"r"(tmem_d), "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(accumulate), "r"(tmem_sfa), "r"(tmem_sfb) : "memory");
+}
+// Instruction descriptor of the block-scaled kind: A / B e4m3 K-major, scale factors UE8M0, D fp32 (implied).
+// `sf_id` = which byte of a scale-factor column (which 32-wide slice of the 128-wide k-block) both operands use.
+__host__ __device__ constexpr uint32_t make_idesc_mx(int m, int n, uint32_t sf_id) {
+    uint32_t d = 0;
+    d |= (sf_id & 3u) << 4;                         // B scale-factor id
+    d |= static_cast<uint32_t>(n >> 3) << 17;       // N / 8
+    d |= 1u << 23;                                  // scale format: E8M0
+    d |= static_cast<uint32_t>(m >> 4) << 24;       // M / 16
+    d |= (sf_id & 3u) << 29;                        // A scale-factor id
+    return d;
+}
 
 // ---------------------------------------------------------------- CTA-pair (cta_group::2) forms
 // Two CTAs of a cluster work on one 256-row tile: each holds its own 128 rows of A, half of the B tile and the

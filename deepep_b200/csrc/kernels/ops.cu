@@ -125,7 +125,7 @@ __global__ void __launch_bounds__(256) dequant_kernel(const uint8_t* __restrict_
 template <bool kQuant>
 __global__ void __launch_bounds__(256) swiglu_kernel(const uint8_t* __restrict__ x, int rows, int inter, const float* __restrict__ row_weight,
                                                      const int* __restrict__ num_valid_rows, uint8_t* __restrict__ out,
-                                                     float* __restrict__ scales, int64_t sf_row_stride, int64_t sf_col_stride) {
+                                                     float* __restrict__ scales, int64_t sf_row_stride, int64_t sf_col_stride, int pow2) {
     const int vec_per_row = inter / 8;
     const int valid = num_valid_rows != nullptr ? min(*num_valid_rows, rows) : rows;
     const int64_t total = static_cast<int64_t>(valid) * vec_per_row;
@@ -166,7 +166,7 @@ __global__ void __launch_bounds__(256) swiglu_kernel(const uint8_t* __restrict__
             for (int j = 0; j < 8; ++j) amax = fmaxf(amax, fabsf(f[j]));
             amax = warp_reduce_max_width(amax, 16);
             float scale, inv;
-            fp8_scale_from_amax(amax, false, scale, inv);
+            fp8_scale_from_amax(amax, pow2 != 0, scale, inv);
             uint2 packed;
             packed.x = pack4_e4m3(f[0] * inv, f[1] * inv, f[2] * inv, f[3] * inv);
             packed.y = pack4_e4m3(f[4] * inv, f[5] * inv, f[6] * inv, f[7] * inv);
@@ -322,16 +322,16 @@ cudaError_t dequant_1x128(const void* q, const float* scales, int64_t sf_row_str
 }
 
 cudaError_t swiglu(const void* x, int rows, int inter, const float* row_weight, const int* num_valid_rows, void* out, bool quant,
-                   float* scales, int64_t sf_row_stride, int64_t sf_col_stride, cudaStream_t stream) {
+                   float* scales, int64_t sf_row_stride, int64_t sf_col_stride, bool pow2, cudaStream_t stream) {
     if (rows == 0) return cudaSuccess;
     if (inter % 8 != 0 || (quant && inter % 128 != 0)) return cudaErrorInvalidValue;
     const int grid = grid_for(static_cast<int64_t>(rows) * inter / 8);
     if (quant)
         swiglu_kernel<true><<<grid, 256, 0, stream>>>(static_cast<const uint8_t*>(x), rows, inter, row_weight, num_valid_rows,
-                                                      static_cast<uint8_t*>(out), scales, sf_row_stride, sf_col_stride);
+                                                      static_cast<uint8_t*>(out), scales, sf_row_stride, sf_col_stride, pow2 ? 1 : 0);
     else
         swiglu_kernel<false><<<grid, 256, 0, stream>>>(static_cast<const uint8_t*>(x), rows, inter, row_weight, num_valid_rows,
-                                                       static_cast<uint8_t*>(out), nullptr, 0, 0);
+                                                       static_cast<uint8_t*>(out), nullptr, 0, 0, 0);
     return cudaGetLastError();
 }
 

@@ -38,7 +38,8 @@ int gemm_check_status() {
 }
 
 at::Tensor gemm_impl(const at::Tensor& a, const at::Tensor& b, const std::optional<at::Tensor>& sfa, const std::optional<at::Tensor>& sfb,
-                     const std::optional<at::Tensor>& group_end, int group_alignment, std::optional<at::Tensor> out, int num_sms) {
+                     const std::optional<at::Tensor>& group_end, int group_alignment, std::optional<at::Tensor> out, int num_sms,
+                     bool pow2_scales) {
     EP_HOST_ASSERT(a.is_cuda() && b.is_cuda() && a.dim() == 2 && a.stride(1) == 1 && b.stride(-1) == 1);
     EP_HOST_ASSERT(b.dim() == 2 || b.is_contiguous());
     const bool fp8 = a.scalar_type() == at::kFloat8_e4m3fn;
@@ -82,6 +83,7 @@ at::Tensor gemm_impl(const at::Tensor& a, const at::Tensor& b, const std::option
         p.sfa_row_stride = sfa->stride(0);
         p.sfa_k_stride = sfa->stride(1);
         p.sfb = sfb->data_ptr<float>();
+        p.scales_pow2 = pow2_scales ? 1 : 0;
     }
     p.error = gemm_status(device).data_ptr<int>();
     p.timeout_ns = 10ull * 1000 * 1000 * 1000;
@@ -164,7 +166,7 @@ at::Tensor dequant_1x128(const at::Tensor& q, const at::Tensor& sf) {
 
 // returns (out, scales or None)
 std::tuple<at::Tensor, std::optional<at::Tensor>> swiglu(const at::Tensor& x, const std::optional<at::Tensor>& row_weight,
-                                                          const std::optional<at::Tensor>& num_valid_rows, bool quant) {
+                                                          const std::optional<at::Tensor>& num_valid_rows, bool quant, bool pow2) {
     EP_HOST_ASSERT(x.is_cuda() && x.dim() == 2 && x.scalar_type() == at::kBFloat16 && x.is_contiguous() && x.size(1) % 16 == 0);
     c10::cuda::CUDAGuard guard(x.device());
     const int M = static_cast<int>(x.size(0)), I = static_cast<int>(x.size(1) / 2);
@@ -178,7 +180,7 @@ std::tuple<at::Tensor, std::optional<at::Tensor>> swiglu(const at::Tensor& x, co
     std::optional<at::Tensor> sf;
     if (quant) sf = at::empty({M, I / 128}, x.options().dtype(at::kFloat));
     CUDA_RUNTIME_CHECK(ops::swiglu(x.data_ptr(), M, I, rw, nv, out.data_ptr(), quant, quant ? sf->data_ptr<float>() : nullptr,
-                                   quant ? sf->stride(0) : 0, quant ? sf->stride(1) : 0, cur_stream()));
+                                   quant ? sf->stride(0) : 0, quant ? sf->stride(1) : 0, pow2, cur_stream()));
     return {out, sf};
 }
 
@@ -217,13 +219,17 @@ void register_ops_bindings(py::module_& m) {
     m.def("router_topk", &router_topk);
     m.def("quant_1x128", &quant_1x128, py::arg("x"), py::arg("pow2") = false, py::arg("col_major_sf") = false);
     m.def("dequant_1x128", &dequant_1x128);
-    m.def("swiglu", &swiglu, py::arg("x"), py::arg("row_weight") = py::none(), py::arg("num_valid_rows") = py::none(), py::arg("quant") = false);
+    m.def("swiglu", &swiglu, py::arg("x"), py::arg("row_weight") = py::none(), py::arg("num_valid_rows") = py::none(), py::arg("quant") = false,
+          py::arg("pow2") = false);
     m.def("swiglu_backward", &swiglu_backward, py::arg("x"), py::arg("dout"), py::arg("row_weight") = py::none(),
           py::arg("with_byproducts") = false);
     m.def("transpose_bf16", &transpose_bf16);
     m.def("gemm", &gemm_impl, py::arg("a"), py::arg("b"), py::arg("sfa") = py::none(), py::arg("sfb") = py::none(),
           py::arg("group_end") = py::none(), py::arg("group_alignment") = 1, py::arg("out") = py::none(), py::arg("num_sms") = 0,
-          "C = A @ B^T on the tcgen05 tensor cores (bf16, or e4m3 with 1x128 / 128x128 block scales); 3-D B = grouped");
+          py::arg("pow2_scales") = false,
+          "C = A @ B^T on the tcgen05 tensor cores (bf16, or e4m3 with 1x128 / 128x128 block scales); 3-D B = grouped. "
+          "pow2_scales: every scale is an exact power of two (round_scale quantisation), which lets the tensor core apply "
+          "them itself (kind::mxf8f6f4.block_scale) when N is a multiple of 256 and K at most 8192");
     m.def("gemm_k_grouped", &gemm_k_grouped, py::arg("a"), py::arg("b"), py::arg("group_end"), py::arg("num_groups"),
           py::arg("group_alignment") = 128, py::arg("out") = py::none(), py::arg("num_sms") = 0,
           "C[g] = A[:, k range g] @ B[:, k range g]^T for all groups in one launch (bf16; the ranges come from a device array)");

@@ -37,16 +37,20 @@ class MoEConfig:
     num_experts: int
     num_topk: int
     use_fp8: bool = False          # e4m3 dispatch + e4m3 expert GEMMs (weights 128x128 block scaled), bf16 gradients
+    pow2_scales: bool = False      # with use_fp8: every scale is a power of two (UE8M0), applied by the tensor core itself
     expert_alignment: int = 128
     num_sms: int = 24
 
 
-def quantize_weight_128x128(w: torch.Tensor) -> Tuple[torch.Tensor, torch.Tensor]:
-    """``[G, N, K]`` -> (e4m3 ``[G, N, K]``, fp32 scales ``[G, N / 128, K / 128]``)."""
+def quantize_weight_128x128(w: torch.Tensor, pow2: bool = False) -> Tuple[torch.Tensor, torch.Tensor]:
+    """``[G, N, K]`` -> (e4m3 ``[G, N, K]``, fp32 scales ``[G, N / 128, K / 128]``); ``pow2`` rounds the scales up to
+    powers of two."""
     G, N, K = w.shape
     blocks = w.float().view(G, N // 128, 128, K // 128, 128)
     amax = blocks.abs().amax(dim=(2, 4)).clamp(1e-4)
     scale = torch.div(amax, torch.full_like(amax, 448.0))
+    if pow2:
+        scale = torch.exp2(torch.ceil(torch.log2(scale)))
     q = (blocks / scale[:, :, None, :, None]).clamp(-448, 448).to(torch.float8_e4m3fn).view(G, N, K)
     return q, scale.contiguous()
 
@@ -55,8 +59,8 @@ class ExpertWeights:
     """This rank's experts: ``w13 [local experts, 2 * intermediate, hidden]`` (gate rows first, then up) and
     ``w2 [local experts, hidden, intermediate]`` in bf16, plus the derived copies the kernels read."""
 
-    def __init__(self, w13: torch.Tensor, w2: torch.Tensor, use_fp8: bool):
-        self.w13, self.w2, self.use_fp8 = w13.contiguous(), w2.contiguous(), use_fp8
+    def __init__(self, w13: torch.Tensor, w2: torch.Tensor, use_fp8: bool, pow2_scales: bool = False):
+        self.w13, self.w2, self.use_fp8, self.pow2_scales = w13.contiguous(), w2.contiguous(), use_fp8, pow2_scales
         self.refresh()
 
     def refresh(self) -> None:
@@ -64,8 +68,8 @@ class ExpertWeights:
         self.w13_t = self.w13.transpose(1, 2).contiguous()     # [EL, hidden, 2I]
         self.w2_t = self.w2.transpose(1, 2).contiguous()       # [EL, I, hidden]
         if self.use_fp8:
-            self.w13_q, self.w13_sf = quantize_weight_128x128(self.w13)
-            self.w2_q, self.w2_sf = quantize_weight_128x128(self.w2)
+            self.w13_q, self.w13_sf = quantize_weight_128x128(self.w13, self.pow2_scales)
+            self.w2_q, self.w2_sf = quantize_weight_128x128(self.w2, self.pow2_scales)
 
 
 class _SingleRankComm:
@@ -93,7 +97,7 @@ def moe_forward(comm, weights: Sequence[ExpertWeights], xs: Sequence[torch.Tenso
     R = len(xs)
     out = comm.dispatch([dict(x=xs[r], topk_idx=topk_idx[r], topk_weights=topk_weights[r], num_experts=cfg.num_experts,
                               expert_alignment=cfg.expert_alignment, do_expand=True, do_zero_padding=True, num_sms=cfg.num_sms,
-                              fused_fp8=cfg.use_fp8) for r in range(R)])
+                              fused_fp8=cfg.use_fp8, round_scale=cfg.use_fp8 and cfg.pow2_scales) for r in range(R)])
     ctxs, h2s = [], []
     for r in range(R):
         recv_x, _, recv_w, handle, _ = out[r]
@@ -101,9 +105,10 @@ def moe_forward(comm, weights: Sequence[ExpertWeights], xs: Sequence[torch.Tenso
         ends = handle.psum_num_recv_tokens_per_expert
         if cfg.use_fp8:
             xq, xsf = recv_x
-            h1 = _C.gemm(xq, w.w13_q, sfa=xsf, sfb=w.w13_sf, group_end=ends, group_alignment=cfg.expert_alignment)
-            aq, asf = _C.swiglu(h1, recv_w, None, True)
-            h2 = _C.gemm(aq, w.w2_q, sfa=asf, sfb=w.w2_sf, group_end=ends, group_alignment=cfg.expert_alignment)
+            pow2 = cfg.pow2_scales and w.pow2_scales
+            h1 = _C.gemm(xq, w.w13_q, sfa=xsf, sfb=w.w13_sf, group_end=ends, group_alignment=cfg.expert_alignment, pow2_scales=pow2)
+            aq, asf = _C.swiglu(h1, recv_w, None, True, pow2)
+            h2 = _C.gemm(aq, w.w2_q, sfa=asf, sfb=w.w2_sf, group_end=ends, group_alignment=cfg.expert_alignment, pow2_scales=pow2)
         else:
             h1 = _C.gemm(recv_x, w.w13, group_end=ends, group_alignment=cfg.expert_alignment)
             a, _ = _C.swiglu(h1, recv_w)
@@ -224,11 +229,11 @@ class FusedMoE(torch.nn.Module):
         self.router = torch.nn.Parameter((torch.randn((cfg.num_experts, cfg.hidden), generator=g) * 0.02).to(device))
         self.w13 = torch.nn.Parameter((torch.randn((el, 2 * cfg.intermediate, cfg.hidden), generator=g) * 0.02).bfloat16().to(device))
         self.w2 = torch.nn.Parameter((torch.randn((el, cfg.hidden, cfg.intermediate), generator=g) * 0.02).bfloat16().to(device))
-        self.weights = ExpertWeights(self.w13.data, self.w2.data, cfg.use_fp8)
+        self.weights = ExpertWeights(self.w13.data, self.w2.data, cfg.use_fp8, cfg.pow2_scales)
 
     def refresh_weights(self) -> None:
         """Call after an optimizer step: rebuilds the transposed / quantised weight copies."""
-        self.weights = ExpertWeights(self.w13.data, self.w2.data, self.cfg.use_fp8)
+        self.weights = ExpertWeights(self.w13.data, self.w2.data, self.cfg.use_fp8, self.cfg.pow2_scales)
 
     def forward(self, x: torch.Tensor) -> torch.Tensor:
         topk_idx, topk_weights = _RouterFunction.apply(x, self.router, self.cfg.num_topk)

@@ -101,6 +101,18 @@ def main():
         out = torch.empty((M, a.n), device='cuda', dtype=torch.bfloat16)
         ms = _timeit(lambda: C.gemm(xq, wq, sfa=sfa, sfb=sfb, group_end=ends, group_alignment=128, out=out), a.iters, a.warmup)
         print(f'gemm fp8 grouped {G}x{rows}x{a.n}x{a.k}: {ms * 1e3:.1f} us, {2 * M * a.n * a.k / ms / 1e9:.0f} TFLOP/s')
+    elif a.op == 'gemm_fp8_grouped_mx':
+        # the same problem with power-of-two scales: the tensor core applies them (kind::mxf8f6f4.block_scale)
+        G, rows = 8, a.m // 8 // 128 * 128
+        M = G * rows
+        xq = torch.randn((M, a.k), generator=g).cuda().to(torch.float8_e4m3fn)
+        sfa = torch.exp2(torch.randint(-3, 4, (M, a.k // 128), generator=g).float()).cuda()
+        wq = torch.randn((G, a.n, a.k), generator=g).cuda().to(torch.float8_e4m3fn)
+        sfb = torch.exp2(torch.randint(-3, 4, (G, a.n // 128, a.k // 128), generator=g).float()).cuda()
+        ends = (torch.arange(1, G + 1, device='cuda') * rows).int()
+        out = torch.empty((M, a.n), device='cuda', dtype=torch.bfloat16)
+        ms = _timeit(lambda: C.gemm(xq, wq, sfa=sfa, sfb=sfb, group_end=ends, group_alignment=128, out=out, pow2_scales=True), a.iters, a.warmup)
+        print(f'gemm fp8 grouped, hardware block scaling {G}x{rows}x{a.n}x{a.k}: {ms * 1e3:.1f} us, {2 * M * a.n * a.k / ms / 1e9:.0f} TFLOP/s')
     elif a.op == 'll':
         Tl = min(T, 128)
         hint = deepep_b200.Buffer.get_low_latency_rdma_size_hint(Tl, H, 1, E)

@@ -87,6 +87,49 @@ def test_gemm_fp8_block_scaled(grouped, pair, monkeypatch):
     assert _rel_err(out, ref) < 1e-2
 
 
+@pytest.mark.parametrize('grouped', [False, True])
+@pytest.mark.parametrize('M,N,K', [(384, 512, 1024), (256, 256, 7168)])
+def test_gemm_fp8_hardware_block_scaling(grouped, M, N, K):
+    """Power-of-two scales (UE8M0): the tensor core applies them itself and a tile accumulates over all of K in tensor
+    memory. Scales differ per row, per 128-wide k-block and between the two 128-column halves of a 256-wide tile, so a
+    scale factor that lands in the wrong lane, column or byte of tensor memory shows up as an error of a factor of two
+    or more."""
+    import deepep_b200
+    from deepep_b200.utils.math import per_token_cast_back, per_token_cast_to_fp8
+    G = 3 if grouped else 1
+    g = torch.Generator(device='cuda').manual_seed(5)
+    # rows and k-blocks of very different magnitude -> very different scales
+    a = torch.randn((M, K), device='cuda', generator=g) * torch.exp2(torch.randint(-6, 7, (M, 1), device='cuda', generator=g).float())
+    a = (a.view(M, K // 128, 128) * torch.exp2(torch.randint(-3, 4, (M, K // 128, 1), device='cuda', generator=g).float())).view(M, K).bfloat16()
+    aq, sfa = per_token_cast_to_fp8(a, round_scale=True)
+    assert bool((torch.frexp(sfa)[0] == 0.5).all())          # exact powers of two
+    w = torch.randn((G, N, K), device='cuda', generator=g) * 0.05
+    wb = w.view(G, N // 128, 128, K // 128, 128) * torch.exp2(torch.randint(-4, 5, (G, N // 128, 1, K // 128, 1), device='cuda', generator=g).float())
+    amax = wb.abs().amax(dim=(2, 4)).clamp(1e-4)
+    sfb = torch.exp2(torch.ceil(torch.log2(amax / 448.0))).contiguous()
+    wq = (wb / sfb[:, :, None, :, None]).clamp(-448, 448).to(torch.float8_e4m3fn).view(G, N, K)
+    w_deq = (wq.float().view(G, N // 128, 128, K // 128, 128) * sfb[:, :, None, :, None]).view(G, N, K)
+    a_deq = per_token_cast_back(aq, sfa).float()
+    if grouped:
+        rows = M // 128
+        ends = torch.tensor([128 * min(rows, i + 1) for i in range(G)], dtype=torch.int32, device='cuda')
+        out = deepep_b200._C.gemm(aq, wq, sfa=sfa, sfb=sfb, group_end=ends, group_alignment=128, pow2_scales=True)
+        starts = [0] + ends.tolist()[:-1]
+        ref = torch.cat([a_deq[s:e] @ w_deq[i].t() for i, (s, e) in enumerate(zip(starts, ends.tolist()))])
+        n_rows = int(ends[-1].item())
+        out, ref = out[:n_rows], ref[:n_rows]
+    else:
+        out = deepep_b200._C.gemm(aq, wq[0], sfa=sfa, sfb=sfb, pow2_scales=True)
+        ref = a_deq @ w_deq[0].t()
+    torch.cuda.synchronize()
+    assert deepep_b200._C.gemm_check_status() == 0
+    assert _rel_err(out, ref) < 1e-2
+    # the software-scaled kernel on the same operands agrees
+    soft = deepep_b200._C.gemm(aq, wq if grouped else wq[0], sfa=sfa, sfb=sfb, **(dict(group_end=ends, group_alignment=128) if grouped else {}))
+    torch.cuda.synchronize()
+    assert _rel_err(out, soft[:out.size(0)]) < 1e-2
+
+
 def test_gemm_k_grouped_weight_gradients():
     """Groups along the contraction dimension: out[g] = A[:, rows of g] @ B[:, rows of g]^T for all groups in one launch,
     the ranges read from a device prefix array (aligned starts, zero padding between the groups, one empty group)."""
