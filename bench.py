@@ -220,11 +220,13 @@ def moe_layer_section(buf, world, rank, dev, hidden, num_experts, num_topk, max_
     from deepep_b200.models.moe import ExpertWeights, MoEConfig, _SingleRankComm, moe_backward, moe_forward
     from deepep_b200.utils import gate
     el = num_experts // world
-    cfg = MoEConfig(hidden=hidden, intermediate=intermediate, num_experts=num_experts, num_topk=num_topk, use_fp8=True, num_sms=24)
+    # FP8 forward with power-of-two (UE8M0) scales: the expert GEMMs run on the block-scaled tensor-core instruction
+    cfg = MoEConfig(hidden=hidden, intermediate=intermediate, num_experts=num_experts, num_topk=num_topk, use_fp8=True, pow2_scales=True,
+                    num_sms=24)
     g = torch.Generator(device=dev).manual_seed(7 + rank)
     w13 = (torch.randn((el, 2 * intermediate, hidden), device=dev, generator=g) * 0.02).bfloat16()
     w2 = (torch.randn((el, hidden, intermediate), device=dev, generator=g) * 0.02).bfloat16()
-    weights = ExpertWeights(w13, w2, True)
+    weights = ExpertWeights(w13, w2, True, True)
     comm = _SingleRankComm(buf)
     gen = torch.Generator().manual_seed(17 + rank)
     x = torch.randn((num_tokens, hidden), generator=gen).bfloat16().to(dev)
@@ -258,7 +260,7 @@ def moe_layer_section(buf, world, rank, dev, hidden, num_experts, num_topk, max_
     busiest = int(max_over_ranks(float(rows[0])))
     flops = 3 * 2 * busiest * 3 * hidden * intermediate       # fwd + 2x bwd, three GEMMs of hidden x intermediate per row
     res = {'tokens_per_rank': num_tokens, 'hidden': hidden, 'intermediate': intermediate, 'num_experts': num_experts,
-           'num_topk': num_topk, 'routing': 'zipf 1.2', 'fwd_bwd_ms': round(ms, 3),
+           'num_topk': num_topk, 'routing': 'zipf 1.2', 'fp8_scales': 'powers of two (UE8M0), applied by the tensor core', 'fwd_bwd_ms': round(ms, 3),
            'expert_rows_busiest_rank': busiest, 'expert_rows_mean': num_tokens * num_topk,
            'expert_tflops_busiest_gpu': round(flops / (ms * 1e-3) / 1e12, 1)}
     # correctness of the timed configuration: the forward output against a dense fp32 evaluation of this rank's tokens
@@ -278,7 +280,9 @@ def moe_layer_section(buf, world, rank, dev, hidden, num_experts, num_topk, max_
         n = 16
         ref = reference_moe([x[:n]], [idx[:n]], [w[:n]], w13_all, w2_all)[0]
         err = ((ys[0][:n].float() - ref).norm() / ref.norm().clamp(min=1e-6)).item()
-        verified = max_over_ranks(0.0 if err < 0.08 else 1.0) == 0.0
+        # two chained e4m3 GEMMs with e4m3 activations in between; power-of-two scales use a little less of the e4m3
+        # range than exact ones (0.064 measured with exact scales)
+        verified = max_over_ranks(0.0 if err < 0.12 else 1.0) == 0.0
         res['rel_err_forward_vs_fp32'] = round(max_over_ranks(err), 4)
         del w13_all, w2_all
     except Exception as exc:   # noqa: BLE001
