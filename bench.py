@@ -312,7 +312,7 @@ def measured_peaks():
         return {'hbm_gbs': 6650.0, 'bf16_tflops': 1590.0, 'source': 'fallback'}
 
 
-def tp_section(group, world, rank, dev, max_over_ranks, tokens=8192, hidden=7168, ffn=18432, iters=5):
+def tp_section(group, world, rank, dev, max_over_ranks, tokens=8192, hidden=7168, ffn=18432, iters=8):
     """Fused all-gather -> GEMM and GEMM -> reduce-scatter against NCCL + cuBLAS (bf16)."""
     import torch
     import torch.distributed as dist
@@ -326,18 +326,26 @@ def tp_section(group, world, rank, dev, max_over_ranks, tokens=8192, hidden=7168
     x2 = torch.randn((tokens, fl), device=dev, generator=g).bfloat16()
     w2 = (torch.randn((hidden, fl), device=dev, generator=g) * 0.02).bfloat16()
 
+    dummy = torch.ones(1, device=dev)
+
     def timeit(fn):
+        """Mean time of one call in microseconds, max over ranks: every call is timed on its own, the ranks released
+        together by a GPU sleep + all-reduce first (a collective's time is only defined when its ranks start together;
+        back to back, the skew between ranks of one call leaks into the next)."""
         for _ in range(2):
             fn()
-        torch.cuda.synchronize()
-        dist.barrier()
-        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        e0.record()
+        total = 0.0
         for _ in range(iters):
+            torch.cuda.synchronize()
+            torch.cuda._sleep(int(4e6))
+            dist.all_reduce(dummy)
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
             fn()
-        e1.record()
-        torch.cuda.synchronize()
-        return max_over_ranks(e0.elapsed_time(e1) / iters) * 1e3
+            e1.record()
+            torch.cuda.synchronize()
+            total += e0.elapsed_time(e1)
+        return max_over_ranks(total / iters) * 1e3
 
     # both fused operators against NCCL + matmul on the very tensors that are timed
     a, b = ctx.all_gather_gemm(x_shard, w1), nccl_all_gather_gemm(x_shard, w1, group)
