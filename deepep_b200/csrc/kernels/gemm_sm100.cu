@@ -820,27 +820,41 @@ gemm_mx_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
             const bool have_next = sched.get(ti + gridDim.x, nxt);
             if (have_next) stage_tile(nxt, sf_stage + (buf ^ 1) * C::kSfStage);      // one tile ahead
             const uint8_t* mine = sf_stage + buf * C::kSfStage;
-            for (int kb = t.kb0; kb < t.kb1; ++kb) {
-                if (!(ok = pipe_wait(pc, empty + s, ph ^ 1))) break;
-                tc_fence_after();
-                const uint8_t* src = mine + (kb - t.kb0) * C::kSfPitch;
-                uint32_t v[16];
-#pragma unroll
-                for (int j = 0; j < 4; ++j) v[j] = static_cast<uint32_t>(src[lane + 32 * j]) * 0x01010101u;
-#pragma unroll
-                for (int h = 0; h < 2; ++h) {
-                    const uint32_t b = static_cast<uint32_t>(src[BM + h]) * 0x01010101u;
-#pragma unroll
-                    for (int j = 0; j < 4; ++j) v[4 + 4 * h + j] = b;
+            // two k-blocks per round: the wait for the tensor-memory stores (a few hundred cycles) is paid once per round,
+            // otherwise a scale warp, which sees every k-block, could not keep up with the tensor pipe
+            for (int kb = t.kb0; ok && kb < t.kb1; kb += 2) {
+                const int n = min(2, t.kb1 - kb);
+                int sj[2];
+                for (int j = 0; j < n; ++j) {
+                    sj[j] = s;
+                    if (!(ok = pipe_wait(pc, empty + s, ph ^ 1))) break;
+                    if (++s == C::kStages) { s = 0; ph ^= 1; }
                 }
+                if (!ok) break;
+                tc_fence_after();
+                for (int j = 0; j < n; ++j) {
+                    const uint8_t* src = mine + (kb + j - t.kb0) * C::kSfPitch;
+                    uint32_t v[16];
 #pragma unroll
-                for (int j = 12; j < 16; ++j) v[j] = 0u;
-                tmem_st_32x16(tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + C::kSfBase + s * C::kSfCols, v);
+                    for (int i = 0; i < 4; ++i) v[i] = static_cast<uint32_t>(src[lane + 32 * i]) * 0x01010101u;
+#pragma unroll
+                    for (int h = 0; h < 2; ++h) {
+                        const uint32_t b = static_cast<uint32_t>(src[BM + h]) * 0x01010101u;
+#pragma unroll
+                        for (int i = 0; i < 4; ++i) v[4 + 4 * h + i] = b;
+                    }
+#pragma unroll
+                    for (int i = 12; i < 16; ++i) v[i] = 0u;
+                    tmem_st_32x16(tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + C::kSfBase + sj[j] * C::kSfCols, v);
+                }
                 tmem_st_wait();
                 tc_fence_before();
                 __syncwarp();
-                if (lane == 0) mbar_arrive(full + s);
-                if (++s == C::kStages) { s = 0; ph ^= 1; }
+                if (lane == 0) {
+                    for (int j = 0; j < n; ++j) {
+                        mbar_arrive(full + sj[j]);
+                    }
+                }
             }
             sf_barrier();       // the next tile's bytes are complete; nobody reads this tile's any more
             buf ^= 1;
@@ -854,6 +868,240 @@ gemm_mx_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
     if (warp == 1) {
         tc_fence_after();
         tmem_dealloc(tmem_base, C::kTmemCols);
+    }
+}
+
+// ==================================================================== e4m3 with hardware block scaling on CTA pairs (256 x 256 tiles)
+// gemm_mx_kernel's scheme on the CTA-pair division of labour of gemm_pair_kernel: CTA r of the pair loads rows
+// [128 r, 128 r + 128) of the A tile and of the B tile (32 KB per k-block and CTA instead of 48 KB: the block-scaled
+// kernel on lone CTAs is bound by exactly this traffic), the leader issues tcgen05.mma.cta_group::2 with M = 256, each
+// CTA's scale warps write the factors of its own 128 rows of A and of all 256 columns of B into its own tensor memory,
+// each CTA's epilogue warps drain its 128 accumulator rows once per tile. `full` lives in the leader and collects the
+// bytes of both CTAs and the eight scale warps of the pair; one multicast commit frees a stage (and its scale slot) in
+// both CTAs; the leader's `tmem_empty` collects the epilogue warps of both.
+struct MxPairCfg {
+    static constexpr int BN = 256, BK = 128, UMMA_K = 32;
+    static constexpr int kEpiWarps = 8, kSfWarps = 4;
+    static constexpr int kThreads = (2 + kEpiWarps + kSfWarps) * 32;
+    static constexpr int A_BYTES = BM * 128, B_BYTES = (BN / 2) * 128, STAGE = A_BYTES + B_BYTES;
+    static constexpr int kStages = 6;
+    static constexpr int kSfCols = 16, kSfBase = BN, kTmemCols = 512;
+    static constexpr int kMaxKb = 64;
+    static constexpr int kSfPitch = BM + 16;
+    static constexpr int kSfStage = kMaxKb * kSfPitch;
+    static constexpr int kBarBytes = (2 * kStages + 2) * 8 + 16;
+    static constexpr int kSmem = kStages * STAGE + 2 * kSfStage + kBarBytes + 1024;
+};
+
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(MxPairCfg::kThreads, 1)
+gemm_mx_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b, const GemmParams p) {
+    using C = MxPairCfg;
+    extern __shared__ uint8_t smem_raw[];
+    uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~static_cast<uintptr_t>(1023));
+    uint8_t* sf_stage = smem + C::kStages * C::STAGE;
+    uint64_t* full = reinterpret_cast<uint64_t*>(sf_stage + 2 * C::kSfStage);
+    uint64_t* empty = full + C::kStages;
+    uint64_t* tmem_full = empty + C::kStages;
+    uint64_t* tmem_empty = tmem_full + 1;
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(tmem_empty + 1);
+
+    const int warp = warp_id(), lane = lane_id();
+    const uint32_t cta = cluster_ctarank();
+    const bool leader = cta == 0;
+    const int pair = blockIdx.x >> 1, num_pairs = gridDim.x >> 1;
+    PipeCtx pc{p.error, globaltimer_ns() + p.timeout_ns};
+
+    if (warp == 0 && lane == 0) {
+        prefetch_tensormap(&map_a);
+        prefetch_tensormap(&map_b);
+        for (int s = 0; s < C::kStages; ++s) {
+            mbar_init(full + s, 1 + 2 * C::kSfWarps);
+            mbar_init(empty + s, 1);
+        }
+        mbar_init(tmem_full, 1);
+        mbar_init(tmem_empty, 2 * C::kEpiWarps);
+        fence_mbar_init();
+    }
+    if (warp == 1) {
+        tmem_alloc_pair(tmem_slot, C::kTmemCols);
+        tmem_relinquish_pair();
+    }
+    tc_fence_before();
+    cluster_sync_all();
+    tc_fence_after();
+    const uint32_t tmem_base = *tmem_slot;
+
+    if (warp == 0) {
+        // ------------------------------------------------------------ TMA producer (both CTAs)
+        if (lane == 0) {
+            Scheduler sched(p, C::BN, 2 * BM, C::BK);
+            Tile t;
+            int s = 0;
+            uint32_t ph = 0;
+            bool ok = true;
+            for (int ti = pair; ok && sched.get(ti, t); ti += num_pairs) {
+                const int b_row = t.g * p.N + t.n0 + static_cast<int>(cta) * (C::BN / 2);
+                for (int kb = t.kb0; kb < t.kb1; ++kb) {
+                    if (!(ok = pipe_wait(pc, empty + s, ph ^ 1))) break;
+                    uint8_t* sa = smem + s * C::STAGE;
+                    if (leader) mbar_arrive_expect_tx(full + s, 2 * C::STAGE);
+                    const uint32_t bar = map_to_cta(smem_u32(full + s), 0);
+                    tma_load_2d_pair(sa, &map_a, kb * C::BK, t.m0 + static_cast<int>(cta) * BM, bar);
+                    tma_load_2d_pair(sa + C::A_BYTES, &map_b, kb * C::BK, b_row, bar);
+                    if (++s == C::kStages) { s = 0; ph ^= 1; }
+                }
+            }
+        }
+    } else if (warp == 1) {
+        // ------------------------------------------------------------ MMA issuer (leader only)
+        if (leader && lane == 0) {
+            Scheduler sched(p, C::BN, 2 * BM, C::BK);
+            Tile t;
+            int s = 0;
+            uint32_t ph = 0, acc_ph = 0;
+            bool ok = true;
+            for (int ti = pair; ok && sched.get(ti, t); ti += num_pairs) {
+                if (!(ok = pipe_wait(pc, tmem_empty, acc_ph ^ 1))) break;
+                tc_fence_after();
+                for (int kb = t.kb0; kb < t.kb1; ++kb) {
+                    if (!(ok = pipe_wait(pc, full + s, ph))) break;
+                    tc_fence_after();
+                    const uint8_t* sa = smem + s * C::STAGE;
+                    const uint64_t da = make_smem_desc(sa), db = make_smem_desc(sa + C::A_BYTES);
+                    const uint32_t sfa = tmem_base + C::kSfBase + s * C::kSfCols, sfb = sfa + 4;
+#pragma unroll
+                    for (int k = 0; k < C::BK / C::UMMA_K; ++k)
+                        umma_mx_pair(tmem_base, da + 2 * k, db + 2 * k, make_idesc_mx(2 * BM, C::BN, static_cast<uint32_t>(k)),
+                                     (kb != t.kb0 || k != 0) ? 1u : 0u, sfa, sfb);
+                    umma_commit_pair(empty + s);
+                    if (++s == C::kStages) { s = 0; ph ^= 1; }
+                }
+                if (!ok) break;
+                umma_commit_pair(tmem_full);
+                acc_ph ^= 1;
+            }
+        }
+    } else if (warp < 2 + C::kEpiWarps) {
+        // ------------------------------------------------------------ epilogue warps (both CTAs, own 128 rows), once per tile
+        const int quarter = warp & 3;
+        const int half = (warp - 2) / 4;
+        Scheduler sched(p, C::BN, 2 * BM, C::BK);
+        Tile t;
+        uint32_t acc_ph = 0;
+        bool ok = true;
+        for (int ti = pair; ok && sched.get(ti, t); ti += num_pairs) {
+            const int row = t.m0 + static_cast<int>(cta) * BM + quarter * 32 + lane;
+            const bool row_ok = row < t.m_end && row < p.M;
+            const bool zero_row = !row_ok && p.zero_gap && row < p.M && row < align_up(t.m_end, p.group_alignment);
+            const uint32_t lane_addr = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + half * 128;
+            __nv_bfloat16* c_row = p.C + static_cast<int64_t>(row) * p.ldc + t.n0 + half * 128;
+            if (!(ok = pipe_wait(pc, tmem_full, acc_ph))) break;
+            tc_fence_after();
+#pragma unroll 1
+            for (int c = 0; c < 4; ++c) {
+                uint32_t r[32];
+                tmem_ld_32x32(lane_addr + c * 32, r);
+                tmem_ld_wait();
+                if (row_ok) {
+#pragma unroll
+                    for (int v = 0; v < 4; ++v) {
+                        int4 out;
+                        __nv_bfloat162* o2 = reinterpret_cast<__nv_bfloat162*>(&out);
+#pragma unroll
+                        for (int i = 0; i < 4; ++i)
+                            o2[i] = __floats2bfloat162_rn(__uint_as_float(r[v * 8 + 2 * i]), __uint_as_float(r[v * 8 + 2 * i + 1]));
+                        *reinterpret_cast<int4*>(c_row + c * 32 + v * 8) = out;
+                    }
+                } else if (zero_row) {
+#pragma unroll
+                    for (int v = 0; v < 4; ++v) *reinterpret_cast<int4*>(c_row + c * 32 + v * 8) = make_int4(0, 0, 0, 0);
+                }
+            }
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive_cluster(map_to_cta(smem_u32(tmem_empty), 0));
+            acc_ph ^= 1;
+        }
+    } else {
+        // ------------------------------------------------------------ scale warps (both CTAs)
+        const int quarter = warp & 3;
+        const int sf_tid = (warp - 2 - C::kEpiWarps) * 32 + lane;
+        const int kblocks = p.K / 128;
+        Scheduler sched(p, C::BN, 2 * BM, C::BK);
+        Tile t, nxt;
+        auto stage_tile = [&](const Tile& tt, uint8_t* dst) {
+            const int row = tt.m0 + static_cast<int>(cta) * BM + sf_tid;
+            const bool valid = row < tt.m_end && row < p.M;
+            const float* src = p.sfa + static_cast<int64_t>(valid ? row : 0) * p.sfa_row_stride;
+            for (int kb = tt.kb0; kb < tt.kb1; ++kb)
+                dst[(kb - tt.kb0) * C::kSfPitch + sf_tid] = static_cast<uint8_t>(valid ? ue8m0_of(src[static_cast<int64_t>(kb) * p.sfa_k_stride]) : 127u);
+            const float* srcb = p.sfb + (static_cast<int64_t>(tt.g) * (p.N / 128) + tt.n0 / 128) * kblocks;
+            for (int i = sf_tid; i < 2 * (tt.kb1 - tt.kb0); i += C::kSfWarps * 32) {
+                const int h = i & 1, kb = tt.kb0 + (i >> 1);
+                dst[(kb - tt.kb0) * C::kSfPitch + BM + h] = static_cast<uint8_t>(ue8m0_of(srcb[static_cast<int64_t>(h) * kblocks + kb]));
+            }
+        };
+        auto sf_barrier = [&]() { asm volatile("bar.sync 3, %0;" ::"r"(C::kSfWarps * 32) : "memory"); };
+        int s = 0, buf = 0;
+        uint32_t ph = 0;
+        bool ok = true;
+        bool have = sched.get(pair, t);
+        if (have) stage_tile(t, sf_stage);
+        sf_barrier();
+        for (int ti = pair; ok && have; ti += num_pairs) {
+            const bool have_next = sched.get(ti + num_pairs, nxt);
+            if (have_next) stage_tile(nxt, sf_stage + (buf ^ 1) * C::kSfStage);
+            const uint8_t* mine = sf_stage + buf * C::kSfStage;
+            // two k-blocks per round: the wait for the tensor-memory stores (a few hundred cycles) is paid once per round,
+            // otherwise a scale warp, which sees every k-block, could not keep up with the tensor pipe
+            for (int kb = t.kb0; ok && kb < t.kb1; kb += 2) {
+                const int n = min(2, t.kb1 - kb);
+                int sj[2];
+                for (int j = 0; j < n; ++j) {
+                    sj[j] = s;
+                    if (!(ok = pipe_wait(pc, empty + s, ph ^ 1))) break;
+                    if (++s == C::kStages) { s = 0; ph ^= 1; }
+                }
+                if (!ok) break;
+                tc_fence_after();
+                for (int j = 0; j < n; ++j) {
+                    const uint8_t* src = mine + (kb + j - t.kb0) * C::kSfPitch;
+                    uint32_t v[16];
+#pragma unroll
+                    for (int i = 0; i < 4; ++i) v[i] = static_cast<uint32_t>(src[lane + 32 * i]) * 0x01010101u;
+#pragma unroll
+                    for (int h = 0; h < 2; ++h) {
+                        const uint32_t b = static_cast<uint32_t>(src[BM + h]) * 0x01010101u;
+#pragma unroll
+                        for (int i = 0; i < 4; ++i) v[4 + 4 * h + i] = b;
+                    }
+#pragma unroll
+                    for (int i = 12; i < 16; ++i) v[i] = 0u;
+                    tmem_st_32x16(tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + C::kSfBase + sj[j] * C::kSfCols, v);
+                }
+                tmem_st_wait();
+                tc_fence_before();
+                __syncwarp();
+                if (lane == 0) {
+                    for (int j = 0; j < n; ++j) {
+                        // (the stores are complete: tcgen05.wait::st above; the arrival only has to get there)
+                        if (leader) mbar_arrive(full + sj[j]);
+                        else mbar_arrive_cluster_relaxed(map_to_cta(smem_u32(full + sj[j]), 0));
+                    }
+                }
+            }
+            sf_barrier();
+            buf ^= 1;
+            t = nxt;
+            have = have_next;
+        }
+    }
+
+    tc_fence_before();
+    cluster_sync_all();
+    if (warp == 1) {
+        tc_fence_after();
+        tmem_dealloc_pair(tmem_base, C::kTmemCols);
     }
 }
 
@@ -921,8 +1169,25 @@ cudaError_t launch_gemm(const GemmParams& p, const void* a, int64_t a_row_stride
                          static_cast<uint64_t>(b_row_stride_bytes), static_cast<uint32_t>(use_pair ? bn / 2 : bn)))
         return cudaErrorInvalidValue;
     // e4m3 with power-of-two scales: the block-scaled instruction kind (EP_GEMM_FP8_MX=0 keeps the software scaling)
-    static const bool mx_enabled = [] { const char* v = std::getenv("EP_GEMM_FP8_MX"); return v == nullptr || v[0] != '0'; }();
+    const char* mx_env = std::getenv("EP_GEMM_FP8_MX");
+    const bool mx_enabled = mx_env == nullptr || mx_env[0] != '0';
     if (fp8 && p.scales_pow2 && mx_enabled && !use_pair && p.N % 256 == 0 && p.K / 128 <= MxCfg::kMaxKb && !p.k_grouped) {
+        // CTA pairs (EP_GEMM_FP8_MX_PAIR=1): 256 x 256 tiles, each CTA loads 128 rows of A and 128 of B. Opt-in: measured
+        // no faster than lone CTAs (2.21 against 2.16 PFLOP/s), so the fill of shared memory from L2 is not what limits
+        // the lone-CTA kernel; per k-block a CTA's shared memory takes 48 KB from TMA and hands 48 KB to the tensor
+        // core in 541 tensor-pipe cycles either way, more than its 128 bytes per cycle.
+        const char* mx_pair_env = std::getenv("EP_GEMM_FP8_MX_PAIR");
+        const bool mx_pair = mx_pair_env != nullptr && mx_pair_env[0] == '1';
+        if (mx_pair && num_sms >= 2) {
+            CUtensorMap map_b128;
+            if (!make_kmajor_map(&map_b128, b, elem, static_cast<uint64_t>(p.num_groups) * p.N, static_cast<uint64_t>(p.K),
+                                 static_cast<uint64_t>(b_row_stride_bytes), 128))
+                return cudaErrorInvalidValue;
+            cudaError_t err = cudaFuncSetAttribute(gemm_mx_pair_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, MxPairCfg::kSmem);
+            if (err != cudaSuccess) return err;
+            gemm_mx_pair_kernel<<<num_sms & ~1, MxPairCfg::kThreads, MxPairCfg::kSmem, stream>>>(map_a, map_b128, p);
+            return cudaGetLastError();
+        }
         CUtensorMap map_b256;
         if (!make_kmajor_map(&map_b256, b, elem, static_cast<uint64_t>(p.num_groups) * p.N, static_cast<uint64_t>(p.K),
                              static_cast<uint64_t>(b_row_stride_bytes), 256))

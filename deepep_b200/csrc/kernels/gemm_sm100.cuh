@@ -141,6 +141,17 @@ __device__ __forceinline__ void umma_mx(uint32_t tmem_d, uint64_t desc_a, uint64
         "tcgen05.mma.cta_group::1.kind::mxf8f6f4.block_scale [%0], %1, %2, %3, [%5], [%6], p;\n"
         "}\n" ::"r"(tmem_d), "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(accumulate), "r"(tmem_sfa), "r"(tmem_sfb) : "memory");
 }
+// the CTA-pair form: M = 256 (128 rows per CTA), the scale factors of a CTA's own rows of A and of all columns of B are
+// read from that CTA's tensor memory at the same addresses
+__device__ __forceinline__ void umma_mx_pair(uint32_t tmem_d, uint64_t desc_a, uint64_t desc_b, uint32_t idesc, uint32_t accumulate,
+                                             uint32_t tmem_sfa, uint32_t tmem_sfb) {
+    asm volatile(
+        "{\n"
+        ".reg .pred p;\n"
+        "setp.ne.b32 p, %4, 0;\n"
+        "tcgen05.mma.cta_group::2.kind::mxf8f6f4.block_scale [%0], %1, %2, %3, [%5], [%6], p;\n"
+        "}\n" ::"r"(tmem_d), "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(accumulate), "r"(tmem_sfa), "r"(tmem_sfb) : "memory");
+}
 // Instruction descriptor of the block-scaled kind: A / B e4m3 K-major, scale factors UE8M0, D fp32 (implied).
 // `sf_id` = which byte of a scale-factor column (which 32-wide slice of the 128-wide k-block) both operands use.
 __host__ __device__ constexpr uint32_t make_idesc_mx(int m, int n, uint32_t sf_id) {
@@ -174,6 +185,12 @@ __device__ __forceinline__ void cluster_sync_all() {
 }
 __device__ __forceinline__ void mbar_arrive_cluster(uint32_t cluster_addr) {
     asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(cluster_addr) : "memory");
+}
+// the same without release semantics: for a signal whose payload is already complete by other means (tensor-memory
+// stores behind tcgen05.wait::st). A release at cluster scope was measured at about a microsecond per arrival, which
+// is a whole k-block of an e4m3 tile.
+__device__ __forceinline__ void mbar_arrive_cluster_relaxed(uint32_t cluster_addr) {
+    asm volatile("mbarrier.arrive.relaxed.cluster.shared::cluster.b64 _, [%0];" ::"r"(cluster_addr) : "memory");
 }
 // dst in this CTA's shared memory, completion bytes reported to the barrier at `bar_cluster_addr` (the leader's)
 __device__ __forceinline__ void tma_load_2d_pair(void* smem_dst, const CUtensorMap* map, int c0, int c1, uint32_t bar_cluster_addr) {

@@ -87,15 +87,17 @@ def test_gemm_fp8_block_scaled(grouped, pair, monkeypatch):
     assert _rel_err(out, ref) < 1e-2
 
 
+@pytest.mark.parametrize('pair', ['0', '1'])
 @pytest.mark.parametrize('grouped', [False, True])
 @pytest.mark.parametrize('M,N,K', [(384, 512, 1024), (256, 256, 7168)])
-def test_gemm_fp8_hardware_block_scaling(grouped, M, N, K):
+def test_gemm_fp8_hardware_block_scaling(grouped, M, N, K, pair, monkeypatch):
     """Power-of-two scales (UE8M0): the tensor core applies them itself and a tile accumulates over all of K in tensor
     memory. Scales differ per row, per 128-wide k-block and between the two 128-column halves of a 256-wide tile, so a
     scale factor that lands in the wrong lane, column or byte of tensor memory shows up as an error of a factor of two
     or more."""
     import deepep_b200
     from deepep_b200.utils.math import per_token_cast_back, per_token_cast_to_fp8
+    monkeypatch.setenv('EP_GEMM_FP8_MX_PAIR', pair)     # '1': 256 x 256 tiles on CTA pairs (tcgen05 cta_group::2)
     G = 3 if grouped else 1
     g = torch.Generator(device='cuda').manual_seed(5)
     # rows and k-blocks of very different magnitude -> very different scales
