@@ -64,7 +64,6 @@ constexpr int kWsStamps = 2;         // [8] phase timestamps of the last dispatc
                                      // published, last row issued (all of block 0), own stores complete, all blocks done
 constexpr int kWsWork = 10;          // next token index handed out by the dynamic send loops
 constexpr int kWsLLCalls = 11;       // [4] low-latency call counters: dispatch send, dispatch recv, combine send, combine recv
-constexpr int kWsWorkReduce = 15;    // next token handed out by the fused reduce of the combine
 constexpr int kWsScratch = 16;       // start of per-block scratch counters
 // scratch: int32 [kMaxBlocks][kMaxRanks + kMaxExperts]
 constexpr size_t kWsScratchInts = static_cast<size_t>(kMaxBlocks) * (kMaxRanks + kMaxExperts);

@@ -188,7 +188,6 @@ struct CombineParams {
 struct CombineLaunch {
     int num_sms;
     int num_warps;            // send warps (one staging buffer each)
-    int num_reduce_warps;     // unused (0)
     int smem_bytes;
 };
 bool plan_combine(const CombineParams& p, int num_sms, int smem_optin, CombineLaunch* out);

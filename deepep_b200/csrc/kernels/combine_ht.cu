@@ -324,7 +324,7 @@ __global__ void __launch_bounds__(1024, 1) combine_kernel(const __grid_constant_
     const CommCtx& c = p.c;
     const WaitCtx w = make_wait_ctx(c);
     const int tid = threadIdx.x, lane = lane_id(), warp = warp_id();
-    const int num_warps = p.num_send_warps;           // warps that send; the block may carry more, which only reduce
+    const int num_warps = p.num_send_warps;           // warps that send; with kFlags the block carries one more, the accountant
     const int nb_send = p.num_send_blocks;            // blocks [nb_send, nb) have no send warps at all
     const bool is_sender = warp < num_warps && bid < nb_send;
     const int R = c.num_ranks, K = p.num_topk;
@@ -360,9 +360,9 @@ __global__ void __launch_bounds__(1024, 1) combine_kernel(const __grid_constant_
     }
     const bool is_accountant = kFlags && warp == num_warps && bid < nb_send;
     const uint64_t arrivals_off = p.off_comb_flag + static_cast<uint64_t>(p.epoch & 1) * R * p.flag_chunks * 4;
-    auto count_row = [&](int tag) {
+    auto count_rows = [&](int tag, uint32_t n) {
         uint32_t* cnt = reinterpret_cast<uint32_t*>(c.heap[tag >> 24] + arrivals_off) + static_cast<uint64_t>(c.rank) * p.flag_chunks + (tag & 0xffffff);
-        asm volatile("red.relaxed.sys.global.add.u32 [%0], 1;" ::"l"(cnt) : "memory");
+        asm volatile("red.relaxed.sys.global.add.u32 [%0], %1;" ::"l"(cnt), "r"(n) : "memory");
     };
     int my_head = 0;
     auto row_landed = [&](int tag) {             // lane 0 of a send warp
@@ -370,7 +370,7 @@ __global__ void __launch_bounds__(1024, 1) combine_kernel(const __grid_constant_
         while (my_head - *reinterpret_cast<volatile int*>(&s_tail[warp]) >= kMboxDepth) {
             if (++spins > (1 << 22)) {           // the accountant gave up: count the row here, at full price
                 fence_acq_rel_sys();
-                count_row(tag);
+                count_rows(tag, 1u);
                 return;
             }
         }
@@ -576,7 +576,20 @@ __global__ void __launch_bounds__(1024, 1) combine_kernel(const __grid_constant_
             __threadfence_block();
             if (__any_sync(0xffffffffu, head != tail)) {
                 fence_acq_rel_sys();
-                for (; tail != head; ++tail) count_row(*reinterpret_cast<volatile int*>(&s_mbox[lane][tail & (kMboxDepth - 1)]));
+                // Rows that the send warps have in flight at one time mostly belong to the same few 32-row groups (rows
+                // are handed out in order): lanes with the same tag add once, with their number, so a sweep sends about
+                // one add per destination over NVLink instead of one per row.
+#pragma unroll 1
+                for (int k = 0; k < kMboxDepth; ++k) {
+                    const bool has = tail != head;
+                    const int tag = has ? *reinterpret_cast<volatile int*>(&s_mbox[lane][tail & (kMboxDepth - 1)]) : (0x7f000000 | lane);
+                    if (!__any_sync(0xffffffffu, has)) break;
+                    const uint32_t same = __match_any_sync(0xffffffffu, tag);
+                    if (has) {
+                        if ((same & lanemask_lt()) == 0) count_rows(tag, static_cast<uint32_t>(__popc(same)));
+                        ++tail;
+                    }
+                }
                 if (lane < num_warps) *reinterpret_cast<volatile int*>(&s_tail[lane]) = tail;
                 idle = 0;
             } else if (done >= num_warps) {
@@ -614,7 +627,6 @@ bool plan_combine(const CombineParams& p, int num_sms, int smem_optin, CombineLa
     if (warps < 1) return false;
     out->num_sms = num_sms;
     out->num_warps = warps;
-    out->num_reduce_warps = 0;
     out->smem_bytes = warps * stage;
     return true;
 }
@@ -625,7 +637,7 @@ cudaError_t launch_combine(const Multi<CombineParams>& m, const CombineLaunch& l
     if (err != cudaSuccess) return err;
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3(m.num_vranks * m.blocks_per_rank);
-    cfg.blockDim = dim3((l.num_warps + l.num_reduce_warps + (m.r[0].fuse_reduce != 0 ? 1 : 0)) * 32);
+    cfg.blockDim = dim3((l.num_warps + (m.r[0].fuse_reduce != 0 ? 1 : 0)) * 32);     // + the accountant warp
     cfg.dynamicSmemBytes = l.smem_bytes;
     cfg.stream = stream;
     cudaLaunchAttribute attr[1];

@@ -38,6 +38,8 @@ struct GemmRsParams {
     uint64_t off_flags[2];        // per half: [R sources][tiles] arrival counters (zero at set-up, only grow)
     uint32_t epoch;
     int flag_target;              // arrivals a tile flag must have reached for this call
+    int fuse_own;                 // 1: the epilogue of the rank's own rows adds the peers' partial tiles and writes the result;
+                                  // 0: own rows go to the local partial slot and a reduction pass follows the GEMM
     int* error;
 };
 cudaError_t launch_gemm_rs(const GemmRsParams* params, const void* const* a, const int64_t* a_stride_bytes, const void* const* b,

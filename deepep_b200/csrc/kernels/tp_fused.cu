@@ -210,6 +210,10 @@ __global__ void __launch_bounds__(kAgThreads, 1) ag_gemm_kernel(const __grid_con
         const bool sender = lane < R && lane != c.rank;
         uint8_t* buf2[2] = {buf, buf + num_warps * stage};
         int it = 0, retired = 0;     // rows of this warp sent / counted as landed (row of iteration j = me + j * workers)
+        // rows counted per fence: four where a warp has many rows; with few rows per warp (large TP degrees) batching
+        // would hold every chunk's flag back until the warp is done (TP8: 8 rows per warp, 389 us instead of 325)
+        const int rows_per_warp = ceil_div(Ml, workers);
+        const int batch = rows_per_warp >= 32 ? 4 : (rows_per_warp >= 16 ? 2 : 1);
         for (int row = me; row < Ml && R > 1; row += workers, ++it) {
             uint8_t* cur = buf2[it & 1];
             bulk_wait_read<1>();        // the store that used this buffer two rows ago has read it
@@ -224,7 +228,7 @@ __global__ void __launch_bounds__(kAgThreads, 1) ag_gemm_kernel(const __grid_con
             if (sender) {
                 bulk_s2g(c.heap[lane] + p.off_gather + (static_cast<uint64_t>(c.rank) * Ml + row) * row_bytes, cur, row_bytes);
                 bulk_commit();
-                if (it - 3 - retired >= 4) {         // four more rows are at least four stores old
+                if (it - 3 - retired >= batch) {     // `batch` more rows are at least four stores old
                     bulk_wait<4>();
                     fence_acq_rel_sys();
                     for (; retired <= it - 4; ++retired) landed_row((me + retired * workers) / BM);
@@ -424,6 +428,7 @@ __global__ void __launch_bounds__(kRsThreads, 1) gemm_rs_kernel(const __grid_con
     const int mine = tiles_of(total_work, first, stride);
     const int half = p.epoch & 1;
     const uint64_t part_off = p.off_partial[half], flag_off = p.off_flags[half];
+    const bool fuse_own = p.fuse_own != 0;  // the epilogue of the own rows adds the peers' partial tiles itself
 
     if (warp == 0 && lane == 0) {
         prefetch_tensormap(&map_a);
@@ -487,8 +492,11 @@ __global__ void __launch_bounds__(kRsThreads, 1) gemm_rs_kernel(const __grid_con
     } else {
         // epilogue: accumulator -> bf16 -> staging tile -> bulk stores into the destination's partial slot -> flag.
         // This rank's own rows come last; by then the peers' partial tiles for them have long arrived (every rank
-        // starts with the rows of the rank behind it), so the epilogue adds them to the fp32 accumulator and writes the
-        // final rows: no partial tile of its own to store and re-read, no reduction pass after the GEMM.
+        // starts with the rows of the rank behind it). With up to four ranks the epilogue adds them to the fp32
+        // accumulator and writes the final rows: no partial tile of its own to store and re-read, no reduction pass
+        // after the GEMM (887 -> 797 us at TP2). With more ranks that epilogue would read seven partial tiles per own
+        // tile in dependent rounds while the accumulator waits (481 us against 386 us for the baseline at TP8), so the
+        // own rows go to the local partial slot like any other and a reduction pass follows the GEMM.
         const int quarter = warp & 3;
         int acc = 0;
         uint32_t acc_ph = 0;
@@ -501,7 +509,7 @@ __global__ void __launch_bounds__(kRsThreads, 1) gemm_rs_kernel(const __grid_con
             int dst, lt;
             decode(t, dst, lt);
             const int local_m0 = (lt / tiles_n) * BM, n0 = (lt % tiles_n) * BN;
-            const bool own = dst == c.rank;
+            const bool own = fuse_own && dst == c.rank;
             if (own) {
                 // Nothing of this rank may still be owed to a peer while it waits for the peers: the arrival of the
                 // previous tile, normally raised one tile late, goes out first (two ranks that each held back the
@@ -611,6 +619,61 @@ __global__ void __launch_bounds__(kRsThreads, 1) gemm_rs_kernel(const __grid_con
         tc_fence_after();
         if constexpr (kPair) tmem_dealloc_pair(tmem_base, 2 * BN);
         else tmem_dealloc(tmem_base, 2 * BN);
+    }
+    if (fuse_own) return;
+    // ---------------------------------------------------------------- reduction of this rank's own tiles (more than four ranks)
+    const uint64_t* my_flags = reinterpret_cast<const uint64_t*>(c.heap[c.rank] + flag_off);
+    const uint8_t* my_part = c.heap[c.rank] + part_off;
+    const uint64_t target = static_cast<uint64_t>(p.flag_target);
+    for (int lt = bid; lt < tiles_per_dst; lt += nctas) {
+        if (threadIdx.x < R) {
+            const uint64_t* flag = my_flags + static_cast<uint64_t>(threadIdx.x) * tiles_per_dst + lt;
+            if (!bounded_wait(w, kStatusTileFlag, threadIdx.x, lt, [&]() { return ld_acquire_sys_u64(flag) >= target; }))
+                atomicExch(p.error, static_cast<int>(kStatusTileFlag));
+        }
+        __syncthreads();
+        const int local_m0 = (lt / tiles_n) * BM, n0 = (lt % tiles_n) * BN;
+        // Two 16-byte columns per thread and pass, all sources loaded before the first add: up to 16 loads in flight
+        // per thread, so the phase runs at memory speed instead of one load latency per source.
+        for (int v0 = threadIdx.x; v0 < BM * BN / 8; v0 += 2 * blockDim.x) {
+            int4 raw[2][kMaxRanks];
+#pragma unroll
+            for (int u = 0; u < 2; ++u) {
+                const int v = v0 + u * blockDim.x;
+                const int r = v / (BN / 8), cv = v % (BN / 8);
+#pragma unroll
+                for (int s = 0; s < kMaxRanks; ++s)
+                    if (s < R && v < BM * BN / 8)
+                        raw[u][s] = ld_nc_int4(my_part + ((static_cast<uint64_t>(s) * Ml + local_m0 + r) * N + n0 + cv * 8) * 2);
+            }
+#pragma unroll
+            for (int u = 0; u < 2; ++u) {
+                const int v = v0 + u * blockDim.x;
+                if (v >= BM * BN / 8) break;
+                const int r = v / (BN / 8), cv = v % (BN / 8);
+                float accv[8];
+#pragma unroll
+                for (int i = 0; i < 8; ++i) accv[i] = 0.f;
+#pragma unroll
+                for (int s = 0; s < kMaxRanks; ++s) {
+                    if (s < R) {
+                        const __nv_bfloat162* h2 = reinterpret_cast<const __nv_bfloat162*>(&raw[u][s]);
+#pragma unroll
+                        for (int i = 0; i < 4; ++i) {
+                            const float2 f = __bfloat1622float2(h2[i]);
+                            accv[2 * i] += f.x;
+                            accv[2 * i + 1] += f.y;
+                        }
+                    }
+                }
+                int4 out;
+                __nv_bfloat162* o2 = reinterpret_cast<__nv_bfloat162*>(&out);
+#pragma unroll
+                for (int i = 0; i < 4; ++i) o2[i] = __floats2bfloat162_rn(accv[2 * i], accv[2 * i + 1]);
+                *reinterpret_cast<int4*>(p.out + (static_cast<int64_t>(local_m0 + r) * p.ldo + n0 + cv * 8)) = out;
+            }
+        }
+        __syncthreads();
     }
 }
 

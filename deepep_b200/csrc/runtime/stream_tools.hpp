@@ -2,6 +2,7 @@
 // of side streams for copy-engine transfers that run side by side.
 #pragma once
 
+#include <cuda.h>
 #include <cuda_runtime.h>
 
 #include <algorithm>
@@ -19,8 +20,10 @@ namespace ep {
 struct StreamMemOps {
     using WriteFn = int (*)(cudaStream_t, unsigned long long, unsigned long long, unsigned int);
     using WaitFn = int (*)(cudaStream_t, unsigned long long, unsigned long long, unsigned int);
+    using BatchFn = CUresult (*)(CUstream, unsigned int, CUstreamBatchMemOpParams*, unsigned int);
     WriteFn write = nullptr;
     WaitFn wait = nullptr;
+    BatchFn batch = nullptr;      // several writes / waits in one driver call (optional)
     bool available = false;   // both entry points resolved
     bool waits = false;       // EP_STREAM_MEMOPS=1: flag rounds of AGRS / PP run as stream operations
     StreamMemOps() {
@@ -32,6 +35,9 @@ struct StreamMemOps {
         write = reinterpret_cast<WriteFn>(w);
         wait = reinterpret_cast<WaitFn>(q);
         available = true;
+        void* b = nullptr;
+        if (cudaGetDriverEntryPoint("cuStreamBatchMemOp", &b, cudaEnableDefault, &res) == cudaSuccess && res == cudaDriverEntryPointSuccess)
+            batch = reinterpret_cast<BatchFn>(b);
         const char* v = std::getenv("EP_STREAM_MEMOPS");
         waits = v != nullptr && v[0] == '1';
     }
@@ -40,6 +46,27 @@ struct StreamMemOps {
 inline StreamMemOps& stream_memops() {
     static StreamMemOps ops;
     return ops;
+}
+
+// `count` (at most 64) 64-bit writes of `value` to `addrs`, in stream order behind everything queued on `stream`: one
+// driver call where the batched form is available, else one call per word
+inline void stream_write_values(cudaStream_t stream, const unsigned long long* addrs, int count, unsigned long long value) {
+    StreamMemOps& ops = stream_memops();
+    EP_HOST_ASSERT(ops.available && count >= 0 && count <= 64);
+    if (count == 0) return;
+    if (ops.batch != nullptr && count > 1) {
+        CUstreamBatchMemOpParams params[64];
+        for (int i = 0; i < count; ++i) {
+            params[i] = CUstreamBatchMemOpParams{};
+            params[i].writeValue.operation = CU_STREAM_MEM_OP_WRITE_VALUE_64;
+            params[i].writeValue.address = static_cast<CUdeviceptr>(addrs[i]);
+            params[i].writeValue.value64 = value;
+            params[i].writeValue.flags = CU_STREAM_WRITE_VALUE_DEFAULT;
+        }
+        EP_HOST_ASSERT(ops.batch(reinterpret_cast<CUstream>(stream), static_cast<unsigned int>(count), params, 0) == CUDA_SUCCESS);
+        return;
+    }
+    for (int i = 0; i < count; ++i) EP_HOST_ASSERT(ops.write(stream, addrs[i], value, 0) == 0);
 }
 
 // ---- side streams: work item i runs on stream i % kFanStreams, forked from and joined to the caller's stream with

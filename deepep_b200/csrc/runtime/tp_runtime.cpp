@@ -57,7 +57,14 @@ std::vector<at::Tensor> tp_ag_gemm(const std::vector<std::shared_ptr<Runtime>>& 
     const bool ce_possible = V == 1 && R > 1 && stream_memops().available && Ml % 128 == 0 && Ml / 128 <= 63;
     static const int env_push = [] { const char* v = std::getenv("EP_TP_PUSH"); return v == nullptr ? 0 : (v[0] == 's' ? 1 : (v[0] == 'c' ? 2 : 0)); }();
     if (push == 0) push = env_push;
-    if (push == 0) push = 2;
+    if (push == 0) {
+        // Copy engines cost this call about 4 (R - 1) + 20 driver calls of 2.5 us on the host (measured: 539 us at TP8
+        // before the copies and flag writes were batched); they pay where the GEMM outlasts that comfortably (TP2: 724
+        // against 740 us, TP4: 427 against 459 us with push CTAs), else the push CTAs take the shard out.
+        const double gemm_us = 2.0 * R * Ml * N * K / 1.4e15 * 1e6;
+        const double host_us = 2.5 * (4.0 * (R - 1) + 20.0);
+        push = gemm_us >= 2.0 * host_us ? 2 : 1;
+    }
     const bool use_ce = push == 2 && ce_possible;
     if (use_ce) num_comm_ctas = 0;
     if (num_comm_ctas <= 0 && R > 1 && !use_ce) {
@@ -125,7 +132,8 @@ std::vector<at::Tensor> tp_ag_gemm(const std::vector<std::shared_ptr<Runtime>>& 
     // the GEMM starts on the local chunks while the copies are queued
     CUDA_RUNTIME_CHECK(gemm::launch_ag_gemm(params.data(), bptr.data(), gptr.data(), V, num_sms, stream));
     const int chunks = Ml / 128;
-    const int group = std::max(1, chunks / 8);           // row chunks per copy: about eight copies per peer
+    const int group = chunks >= 4 ? (chunks + 1) / 2 : 1;        // row chunks per copy: two copies per peer (the host
+                                                                 // pays per driver call, the copy engine per byte)
     const size_t row_bytes = static_cast<size_t>(K) * 2;
     const uint64_t arrived = (static_cast<uint64_t>(p.epoch) << 32) | 1u;
     for (int c0 = 0; c0 < chunks; c0 += group) {
@@ -135,12 +143,15 @@ std::vector<at::Tensor> tp_ag_gemm(const std::vector<std::shared_ptr<Runtime>>& 
             const cudaStream_t side = f.streams[i % FanOut::kFanStreams];
             uint8_t* dst = rt.heap().peer(peer) + p.off_gather + (static_cast<uint64_t>(me) * Ml + static_cast<uint64_t>(c0) * 128) * row_bytes;
             const uint8_t* src = p.a_local + static_cast<int64_t>(c0) * 128 * p.a_stride_bytes;
-            CUDA_RUNTIME_CHECK(cudaMemcpy2DAsync(dst, row_bytes, src, static_cast<size_t>(p.a_stride_bytes), row_bytes,
-                                                 static_cast<size_t>(c1 - c0) * 128, cudaMemcpyDeviceToDevice, side));
-            for (int c = c0; c < c1; ++c) {
-                uint64_t* flag = reinterpret_cast<uint64_t*>(rt.heap().peer(peer)) + kCtlTileFlags + me * 64 + c;
-                EP_HOST_ASSERT(stream_memops().write(side, reinterpret_cast<unsigned long long>(flag), arrived, 0) == 0);
-            }
+            if (static_cast<size_t>(p.a_stride_bytes) == row_bytes)
+                CUDA_RUNTIME_CHECK(cudaMemcpyAsync(dst, src, row_bytes * static_cast<size_t>(c1 - c0) * 128, cudaMemcpyDeviceToDevice, side));
+            else
+                CUDA_RUNTIME_CHECK(cudaMemcpy2DAsync(dst, row_bytes, src, static_cast<size_t>(p.a_stride_bytes), row_bytes,
+                                                     static_cast<size_t>(c1 - c0) * 128, cudaMemcpyDeviceToDevice, side));
+            unsigned long long flags[64];
+            for (int c = c0; c < c1; ++c)
+                flags[c - c0] = reinterpret_cast<unsigned long long>(reinterpret_cast<uint64_t*>(rt.heap().peer(peer)) + kCtlTileFlags + me * 64 + c);
+            stream_write_values(side, flags, c1 - c0, arrived);
         }
     }
     f.join(stream, used);
@@ -175,7 +186,12 @@ std::vector<at::Tensor> tp_gemm_rs(const std::vector<std::shared_ptr<Runtime>>& 
         EP_HOST_ASSERT(b[v].scalar_type() == at::kBFloat16 && b[v].is_contiguous() && b[v].size(0) == N && b[v].size(1) == K);
         EP_HOST_ASSERT((a[v].stride(0) * 2) % 16 == 0 && reinterpret_cast<uintptr_t>(a[v].data_ptr()) % 16 == 0);
         // arrival counters only grow, so their meaning is tied to the first configuration used on this heap
-        const int64_t config = (static_cast<int64_t>(Ml) << 40) ^ (static_cast<int64_t>(N) << 20) ^ flag_offsets[0] ^ (flag_offsets[1] << 1);
+        // (EP_TP_RS_FUSE_OWN=0 / 1 overrides the choice by rank count; the arrival counters of the own slot only move in
+        // the unfused form, so the form is part of the configuration a buffer is tied to)
+        const char* fuse_env = std::getenv("EP_TP_RS_FUSE_OWN");
+        const int fuse_own = fuse_env != nullptr ? (fuse_env[0] == '1' ? 1 : 0) : (R <= 4 ? 1 : 0);
+        const int64_t config = (static_cast<int64_t>(Ml) << 40) ^ (static_cast<int64_t>(N) << 20) ^ flag_offsets[0] ^ (flag_offsets[1] << 1) ^
+                               (static_cast<int64_t>(fuse_own) << 62);
         if (rt.tp_rs_config == 0) rt.tp_rs_config = config;
         EP_HOST_ASSERT_MSG(rt.tp_rs_config == config, "GEMM->reduce-scatter on one buffer must keep its shape and offsets");
         const uint32_t epoch = ++rt.tp_rs_epoch;
@@ -195,6 +211,7 @@ std::vector<at::Tensor> tp_gemm_rs(const std::vector<std::shared_ptr<Runtime>>& 
         }
         p.epoch = epoch;
         p.flag_target = 4 * static_cast<int>((epoch + 1) / 2);   // four epilogue warps arrive per tile and call on this half
+        p.fuse_own = fuse_own;
         p.error = tp_status(device).data_ptr<int>();
         aptr[v] = a[v].data_ptr();
         bptr[v] = b[v].data_ptr();

@@ -174,3 +174,20 @@ def test_ops_references_cpu():
     assert idx.shape == (7, 3) and torch.allclose(wt.sum(1), torch.ones(7))
     x = torch.randn(4, 8)
     assert torch.allclose(ops.ref_swiglu(x), torch.nn.functional.silu(x[:, :4]) * x[:, 4:])
+
+
+def test_weight_quantisation_pow2_scales_cpu():
+    """128x128 weight quantisation: with ``pow2`` every scale is an exact power of two (what a UE8M0 scale factor of the
+    block-scaled tensor-core instruction can hold), never smaller than the exact scale, and the dequantised weights
+    stay within e4m3 rounding of the originals."""
+    from deepep_b200.models.moe import quantize_weight_128x128
+    g = torch.Generator().manual_seed(3)
+    w = torch.randn((2, 256, 384), generator=g) * torch.exp2(torch.randint(-5, 6, (2, 2, 1, 3, 1), generator=g).float()).expand(2, 2, 128, 3, 128).reshape(2, 256, 384)
+    q, sf = quantize_weight_128x128(w)
+    q2, sf2 = quantize_weight_128x128(w, pow2=True)
+    assert sf.shape == sf2.shape == (2, 2, 3)
+    assert bool((torch.frexp(sf2)[0] == 0.5).all())
+    assert bool((sf2 >= sf).all()) and bool((sf2 < 2 * sf).all())
+    for qq, ss in ((q, sf), (q2, sf2)):
+        deq = (qq.float().view(2, 2, 128, 3, 128) * ss[:, :, None, :, None]).view(2, 256, 384)
+        assert ((deq - w).norm() / w.norm()).item() < 0.04

@@ -43,11 +43,15 @@ def test_all_gather_gemm(R, pair, monkeypatch):
         c.destroy()
 
 
+@pytest.mark.parametrize('fuse_own', ['1', '0'])
 @pytest.mark.parametrize('pair', ['1', '0'])
 @pytest.mark.parametrize('R', [1, 2, 4])
-def test_gemm_reduce_scatter(R, pair, monkeypatch):
+def test_gemm_reduce_scatter(R, pair, fuse_own, monkeypatch):
+    """`fuse_own`: the epilogue of a rank's own rows adds the peers' partial tiles (the form used up to four ranks) or
+    the own rows go through the partial buffer and a reduction pass follows the GEMM (more ranks)."""
     from deepep_b200.parallel.tp_fused import fused_multi
     monkeypatch.setenv('EP_TP_CTA_PAIR', pair)
+    monkeypatch.setenv('EP_TP_RS_FUSE_OWN', fuse_own)
     Ml, Kl, N = 256, 256, 512
     ctxs = _contexts(R, Ml, 512, N)
     g = torch.Generator(device='cuda').manual_seed(6)
