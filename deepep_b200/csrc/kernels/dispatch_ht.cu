@@ -765,6 +765,18 @@ bool plan_dispatch(const DispatchParams& p, int num_sms, int smem_optin, Dispatc
     const int need = order_scratch_min_bytes(p.num_experts, p.num_topk, p.c.num_ranks);
     int scratch = warps * sl.bytes;
     if (scratch < need) scratch = align_up(need, 128);
+    // At eight ranks the send phase is bound by NVLink, and every send warp beyond what saturates the wire only
+    // lengthens the queue in front of it: a warp holds one token (about 40 KB over its destinations), the queue drains
+    // at the wire's rate, and what is queued when the tokens run out is the tail of the kernel (measured at EP8 with
+    // 24 SMs: 360 tokens in flight = 17 us with the cast fused, 720 tokens = 29 us with pre-quantised input). About
+    // 200 tokens in flight per rank keep the wire busy; the cast needs a few more warps to hide its latency. (With
+    // four ranks a quarter of the rows stays local and the cast needs the warps: no cap there.)
+    if (p.c.num_ranks >= 8) {
+        const int target = p.quant_mode != kQuantNone ? 256 : 192;
+        int cap = ceil_div(target, num_sms);
+        if (cap < 4) cap = 4;
+        if (warps > cap) warps = cap;
+    }
     if (scratch > avail) return false;
     out->num_sms = num_sms;
     out->num_warps = warps;
