@@ -73,7 +73,8 @@ std::vector<at::Tensor> tp_ag_gemm(const std::vector<std::shared_ptr<Runtime>>& 
         const double push_cta_seconds = static_cast<double>(R - 1) * Ml * K * 2 / 40e9;
         const double gemm_seconds = 2.0 * R * Ml * N * K / 1.4e15;
         int n = static_cast<int>(std::ceil(push_cta_seconds / (0.5 * gemm_seconds)));
-        n = (std::max(8, std::min(n, 32)) + 1) & ~1;     // (four push CTAs were measured far slower than eight at TP2)
+        n = (std::max(8, std::min(n, 16)) + 1) & ~1;     // (four push CTAs were measured far slower than eight at TP2;
+                                                         //  sixteen beat eight and thirty-two at TP4 and TP8)
         num_comm_ctas = std::min(n, std::max(2, (num_sms / 4) & ~1));
     }
     if (R == 1) num_comm_ctas = 0;
