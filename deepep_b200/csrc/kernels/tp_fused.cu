@@ -3,8 +3,10 @@
 //   all-gather -> GEMM    C[R*Ml, N] = gather_r(A_r[Ml, K]) * B[N, K]^T
 //       The shard reaches every peer's gather buffer in 128-row chunks with one arrival flag per
 //       (source, chunk) at the peer, either from a few "comm" CTAs of this kernel (bulk copies over
-//       NVLink) or, with no CTA spent on it, from the copy engines (2-D copies on side streams, each
-//       chunk's flag a 64-bit stream write behind its copy; issued by the host driver).
+//       NVLink, rows counted behind device-scope fences, the chunk's flag a system-scope release by
+//       the thread that completes it) or, with no CTA spent on it, from the copy engines (two copies
+//       per peer on side streams, the flags of a copy's chunks one batched stream write behind it;
+//       issued by the host driver, which picks the form by the GEMM's length against its own cost).
 //       The GEMM CTAs run the tcgen05 main loop; the TMA producer of a tile waits (bounded) for
 //       the flag of the chunk it is about to read, so the math on early chunks overlaps the
 //       transfer of late ones. Own rows are read straight from the input and go first.
@@ -15,8 +17,10 @@
 //       peer's rows the epilogue converts the accumulator to bf16, stages it in shared memory and
 //       bulk-stores it into slot [this rank] of the destination's partial buffer, then raises a
 //       per-tile flag there. For the rank's own rows, which come last, the peers' partial tiles
-//       have arrived by then: the epilogue waits for their flags, adds them to the fp32 accumulator
-//       in rank order and writes the final rows (no partial of its own, no reduction pass).
+//       have arrived by then: with up to four ranks the epilogue waits for their flags, adds them
+//       to the fp32 accumulator in rank order and writes the final rows (no partial of its own, no
+//       reduction pass); with more ranks the own rows go through the partial buffer as well and
+//       every CTA reduces a share of the rank's tiles after its GEMM tiles.
 //
 // Both kernels walk their tiles in bands of eight row blocks with the row index fastest, so the
 // tiles in flight share few operand blocks (L2 reuse).
