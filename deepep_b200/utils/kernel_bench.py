@@ -129,6 +129,54 @@ def main():
         print(f'll dispatch+combine: {ms * 1e3:.1f} us, tokens {Tl}')
         ll.check_status()
         ll.destroy()
+    elif a.op == 'll_graph':
+        # the low-latency pair (FP8 dispatch + weighted BF16 combine) captured in a CUDA graph and replayed, with block
+        # 0's phase stamps of both kernels; the stream is held back by a sleep kernel so that the replays are queued
+        # when the clock starts (device time, not launch time)
+        Tl = min(T, 128)
+        hint = deepep_b200.Buffer.get_low_latency_rdma_size_hint(Tl, H, 1, E)
+        ll = deepep_b200.Buffer(SingleProcessGroup(), num_rdma_bytes=hint, low_latency_mode=True, num_gpu_timeout_secs=10)
+        x = torch.randn((Tl, H), generator=g).bfloat16().cuda()
+        idx, w = gate.topk_from_scores(gate.get_balanced_scores(Tl, E, generator=g), K)
+        idx, w = idx.cuda(), w.cuda()
+        yy = torch.randn((E, Tl, H), device='cuda', dtype=torch.bfloat16)
+        out = torch.empty_like(x)
+
+        def pair():
+            _, _, h, _, _ = ll.low_latency_dispatch(x, idx, Tl, E, use_fp8=True, num_sms=a.sms)
+            ll.low_latency_combine(yy, idx, w, h, out=out, num_sms=a.sms)
+
+        def dispatch_only():
+            ll.low_latency_dispatch(x, idx, Tl, E, use_fp8=True, num_sms=a.sms)
+        for name, fn in (('dispatch + combine', pair), ('dispatch', dispatch_only)):
+            side = torch.cuda.Stream()
+            side.wait_stream(torch.cuda.current_stream())
+            with torch.cuda.stream(side):
+                for _ in range(3):
+                    fn()
+            torch.cuda.current_stream().wait_stream(side)
+            torch.cuda.synchronize()
+            graph = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(graph):
+                fn()
+            for _ in range(10):
+                graph.replay()
+            torch.cuda.synchronize()
+            n = 100
+            st = [torch.cuda.Event(enable_timing=True) for _ in range(n)]
+            en = [torch.cuda.Event(enable_timing=True) for _ in range(n)]
+            torch.cuda._sleep(int(4e7))
+            for i in range(n):
+                st[i].record()
+                graph.replay()
+                en[i].record()
+            torch.cuda.synchronize()
+            us = sorted(s0.elapsed_time(e0) * 1e3 for s0, e0 in zip(st, en))
+            ph = [round(v / 1e3, 1) for v in ll.runtime.last_dispatch_phases()][:5]
+            tl = [round(v / 1e3, 1) for v in ll.runtime.last_timeline()[8:]]
+            print(f'll {name}, {a.sms} SMs, graph replay: p50 {us[n // 2]:.1f} us, min {us[0]:.1f} us; dispatch stamps {ph}, combine stamps {tl}')
+        ll.check_status()
+        ll.destroy()
     elif a.op == 'ht_emulated':
         # dispatch + combine with `--ranks` emulated ranks on this GPU: every kernel of the multi-rank path runs (count
         # exchange, epilogue, arrival-driven reduce), with local "peers"
