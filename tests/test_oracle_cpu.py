@@ -191,3 +191,18 @@ def test_weight_quantisation_pow2_scales_cpu():
     for qq, ss in ((q, sf), (q2, sf2)):
         deq = (qq.float().view(2, 2, 128, 3, 128) * ss[:, :, None, :, None]).view(2, 256, 384)
         assert ((deq - w).norm() / w.norm()).item() < 0.04
+
+
+def test_bench_reference_arm_reports_unavailable():
+    """`bench.py --impl reference` must answer with one JSON line and exit 0 where the reference cannot be installed."""
+    import json
+    import os
+    import subprocess
+    import sys
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    if os.path.isdir(os.path.join(root, 'baseline', '_ref', 'deep_ep')):
+        pytest.skip('the reference is installed here')
+    res = subprocess.run([sys.executable, os.path.join(root, 'bench.py'), '--impl', 'reference'], capture_output=True, text=True, timeout=300)
+    assert res.returncode == 0
+    line = json.loads(res.stdout.strip().splitlines()[-1])
+    assert line['impl'] == 'reference' and isinstance(line.get('unavailable'), str) and line['unavailable']
