@@ -38,6 +38,7 @@ def _as_bytes(t):
     (2, 40, 384, 8, 2, 2),      # 768-byte rows: the reduce epilogue cannot cut them into 512-byte chunks
     (4, 96, 1024, 32, 6, 4),
     (8, 128, 7168, 256, 8, 6),
+    (8, 96, 7168, 256, 8, 18),  # eight ranks on many SMs: the number of send warps is capped below what shared memory allows
 ])
 @pytest.mark.parametrize('fuse_reduce', [0, 1])
 def test_dispatch_combine_bf16(num_ranks, num_tokens, hidden, num_experts, num_topk, num_sms, fuse_reduce):
